@@ -1,0 +1,10 @@
+"""flashqla_b200: B200 (sm_100a) gated-delta-rule kernels behind FlashQLA's Python API.
+
+Public names follow the reference package (flash_qla/__init__.py:6-38).
+"""
+from .recurrent import flashqla_recurrent_gdn_update, fused_sigmoid_gating_delta_rule_update
+
+__all__ = [
+    "fused_sigmoid_gating_delta_rule_update",
+    "flashqla_recurrent_gdn_update",
+]

@@ -1,0 +1,77 @@
+// Shared host/device helpers for the flashqla_b200 kernels (sm_100a only).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include "../../include/flashqla_b200.h"
+
+namespace qla {
+
+constexpr int kHeadDim = 128;  // K = V = 128 (recurrent_fused.py:6484, chunk/__init__.py:308-315)
+constexpr int kChunk = 64;     // chunk size of the prefill path
+
+// Codes written to the device status word by kernels (0 = fine).
+enum DeviceStatus : int {
+  kStatusOk = 0,
+  kStatusBarrierTimeout = 1,  // a bounded mbarrier wait gave up
+  kStatusBadIndex = 2,        // an index tensor pointed outside its buffer
+};
+
+void set_last_error(const char* fmt, ...);
+
+#define QLA_CHECK_ARG(cond, ...)            \
+  do {                                      \
+    if (!(cond)) {                          \
+      ::qla::set_last_error(__VA_ARGS__);   \
+      return QLA_ERR_INVALID_ARG;           \
+    }                                       \
+  } while (0)
+
+#define QLA_CHECK_SUPPORTED(cond, ...)      \
+  do {                                      \
+    if (!(cond)) {                          \
+      ::qla::set_last_error(__VA_ARGS__);   \
+      return QLA_ERR_UNSUPPORTED;           \
+    }                                       \
+  } while (0)
+
+#define QLA_CHECK_CUDA(expr)                                                              \
+  do {                                                                                    \
+    cudaError_t err__ = (expr);                                                           \
+    if (err__ != cudaSuccess) {                                                           \
+      ::qla::set_last_error("%s failed: %s (%s:%d)", #expr, cudaGetErrorString(err__),    \
+                            __FILE__, __LINE__);                                          \
+      return QLA_ERR_CUDA;                                                                \
+    }                                                                                     \
+  } while (0)
+
+// Load one scalar of a runtime dtype (gates, biases: tiny tensors whose dtype varies by caller).
+__device__ __forceinline__ float load_scalar(const void* p, int dtype, int64_t i) {
+  if (dtype == QLA_DT_F32) return static_cast<const float*>(p)[i];
+  if (dtype == QLA_DT_BF16) return __bfloat162float(static_cast<const __nv_bfloat16*>(p)[i]);
+  return __half2float(static_cast<const __half*>(p)[i]);
+}
+
+template <typename T>
+struct Cvt;
+template <>
+struct Cvt<__nv_bfloat16> {
+  static __device__ __forceinline__ float to_f32(__nv_bfloat16 x) { return __bfloat162float(x); }
+  static __device__ __forceinline__ __nv_bfloat16 from_f32(float x) { return __float2bfloat16_rn(x); }
+};
+template <>
+struct Cvt<__half> {
+  static __device__ __forceinline__ float to_f32(__half x) { return __half2float(x); }
+  static __device__ __forceinline__ __half from_f32(float x) { return __float2half_rn(x); }
+};
+template <>
+struct Cvt<float> {
+  static __device__ __forceinline__ float to_f32(float x) { return x; }
+  static __device__ __forceinline__ float from_f32(float x) { return x; }
+};
+
+}  // namespace qla

@@ -1,0 +1,303 @@
+// Recurrent gated-delta-rule step(s): decode (1 token), spec-decode verify (T draft tokens with a
+// cached state per step), tree verify (a step may restart from the cached state of its parent)
+// and ragged sequences (cu_seqlens).  One kernel covers what the reference spreads over 29
+// generated kernels (flash_qla/ops/gated_delta_rule/recurrent_fused.py:290-6249); the per-token
+// math follows the canonical body at :346-487 and the reload rule of the warp kernels at
+// :5803-5836 (a parent equal to the previous step is not reloaded).
+//
+// The op is HBM-bound: every (sequence, v-head) streams a 64 KiB fp32 state in and out.
+// Mapping: the state of one head is [V=128 rows][K=128 floats]; a row is 512 B.  Eight lanes share
+// a row, each lane owning four float4 (columns j*32 + sub*4 .. +3, j = 0..3), so one warp
+// instruction moves four whole rows = 2 KiB, fully coalesced, 128-bit per lane.  A thread keeps R
+// rows in registers for the whole call (R*16 floats); the K-reductions (S.k and S.q) are three
+// xor-shuffles over the eight lanes of a row.  A CTA of 128 threads covers 16*R rows.
+#include "common.cuh"
+
+namespace qla {
+namespace {
+
+template <typename T>
+__device__ __forceinline__ void load4(const T* p, float (&out)[4]);
+
+template <>
+__device__ __forceinline__ void load4<__nv_bfloat16>(const __nv_bfloat16* p, float (&out)[4]) {
+  uint2 raw = *reinterpret_cast<const uint2*>(p);
+  __nv_bfloat162 lo = *reinterpret_cast<__nv_bfloat162*>(&raw.x);
+  __nv_bfloat162 hi = *reinterpret_cast<__nv_bfloat162*>(&raw.y);
+  float2 a = __bfloat1622float2(lo), b = __bfloat1622float2(hi);
+  out[0] = a.x; out[1] = a.y; out[2] = b.x; out[3] = b.y;
+}
+template <>
+__device__ __forceinline__ void load4<__half>(const __half* p, float (&out)[4]) {
+  uint2 raw = *reinterpret_cast<const uint2*>(p);
+  __half2 lo = *reinterpret_cast<__half2*>(&raw.x);
+  __half2 hi = *reinterpret_cast<__half2*>(&raw.y);
+  float2 a = __half22float2(lo), b = __half22float2(hi);
+  out[0] = a.x; out[1] = a.y; out[2] = b.x; out[3] = b.y;
+}
+template <>
+__device__ __forceinline__ void load4<float>(const float* p, float (&out)[4]) {
+  float4 raw = *reinterpret_cast<const float4*>(p);
+  out[0] = raw.x; out[1] = raw.y; out[2] = raw.z; out[3] = raw.w;
+}
+
+__device__ __forceinline__ void store4(float* p, const float (&x)[4]) {
+  *reinterpret_cast<float4*>(p) = make_float4(x[0], x[1], x[2], x[3]);
+}
+__device__ __forceinline__ void store4(__nv_bfloat16* p, const float (&x)[4]) {
+  __nv_bfloat162 lo = __floats2bfloat162_rn(x[0], x[1]);
+  __nv_bfloat162 hi = __floats2bfloat162_rn(x[2], x[3]);
+  uint2 raw;
+  raw.x = *reinterpret_cast<uint32_t*>(&lo);
+  raw.y = *reinterpret_cast<uint32_t*>(&hi);
+  *reinterpret_cast<uint2*>(p) = raw;
+}
+
+__device__ __forceinline__ float group8_sum(float x) {
+  x += __shfl_xor_sync(0xffffffffu, x, 1);
+  x += __shfl_xor_sync(0xffffffffu, x, 2);
+  x += __shfl_xor_sync(0xffffffffu, x, 4);
+  return x;
+}
+
+template <typename T, typename InterT, int R>
+__global__ void __launch_bounds__(128) recurrent_kernel(const QlaRecurrentArgs p) {
+  constexpr int D = kHeadDim;
+  constexpr int BV = 16 * R;
+  constexpr int kTiles = D / BV;
+  const int tile = blockIdx.x % kTiles;
+  const int nh = blockIdx.x / kTiles;
+  const int h = nh % p.num_v_heads;
+  const int n = nh / p.num_v_heads;
+  const int hk = h / (p.num_v_heads / p.num_k_heads);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int sub = lane & 7, grp = lane >> 3;
+
+  int t0, len;
+  if (p.tokens_per_seq > 0) {
+    t0 = n * p.tokens_per_seq;
+    len = p.tokens_per_seq;
+  } else {
+    t0 = p.cu_seqlens[n];
+    len = p.cu_seqlens[n + 1] - t0;
+  }
+  int64_t sidx = p.state_indices ? p.state_indices[n] : n;
+  if (sidx >= p.state_slots) sidx = -1;  // never touch memory outside the pool
+  int64_t cidx = -1;
+  if (p.inter != nullptr) {
+    cidx = p.inter_indices ? p.inter_indices[n] : n;
+    if (cidx >= p.inter_slots) cidx = -1;
+  }
+
+  const int row0 = tile * BV + warp * 4 + grp;  // row of r = 0; r-th row is row0 + 16 r
+  const int col0 = sub * 4;                     // first owned column of j = 0; j-th is col0 + 32 j
+
+  float S[R][4][4];
+  if (sidx >= 0) {
+    const float* sp = static_cast<const float*>(p.state) + ((sidx * p.num_v_heads + h) * D + row0) * D + col0;
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) load4<float>(sp + (r * 16) * D + j * 32, S[r][j]);
+  } else {
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) S[r][j][i] = 0.f;
+  }
+
+  const T* qb = static_cast<const T*>(p.q);
+  const T* kb = static_cast<const T*>(p.k);
+  const T* vb = static_cast<const T*>(p.v);
+  T* ob = static_cast<T*>(p.o);
+  InterT* ib = static_cast<InterT*>(p.inter);
+  const bool l2norm = (p.flags & QLA_REC_QK_L2NORM) != 0;
+  float a_coef = 0.f, dt_b = 0.f;
+  if (!(p.flags & QLA_REC_A_IS_LOG_DECAY)) {
+    a_coef = -expf(load_scalar(p.A_log, p.a_log_dtype, h));
+    dt_b = load_scalar(p.dt_bias, p.dt_bias_dtype, h);
+  }
+
+  for (int step = 0; step < len; ++step) {
+    const int64_t t = t0 + step;
+
+    if (p.parents != nullptr && step > 0 && cidx >= 0) {
+      const int par = p.parents[static_cast<int64_t>(n) * p.parents_stride + step];
+      if (par != step - 1 && par >= 0 && par < p.inter_steps) {
+        const InterT* src =
+            ib + (((cidx * p.inter_steps + par) * p.num_v_heads + h) * D + row0) * D + col0;
+#pragma unroll
+        for (int r = 0; r < R; ++r)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) load4<InterT>(src + (r * 16) * D + j * 32, S[r][j]);
+      }
+    }
+
+    float qv[4][4], kv[4][4];
+    {
+      const T* qp = qb + (t * p.num_k_heads + hk) * D + col0;
+      const T* kp = kb + (t * p.num_k_heads + hk) * D + col0;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        load4<T>(qp + j * 32, qv[j]);
+        load4<T>(kp + j * 32, kv[j]);
+      }
+    }
+    float vrow[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+      vrow[r] = Cvt<T>::to_f32(vb[(t * p.num_v_heads + h) * D + row0 + 16 * r]);
+
+    float qs = p.scale, ks = 1.f;
+    if (l2norm) {
+      float qq = 0.f, kk = 0.f;
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          qq = fmaf(qv[j][i], qv[j][i], qq);
+          kk = fmaf(kv[j][i], kv[j][i], kk);
+        }
+      qq = group8_sum(qq);
+      kk = group8_sum(kk);
+      qs *= rsqrtf(qq + 1e-6f);
+      ks = rsqrtf(kk + 1e-6f);
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        qv[j][i] *= qs;
+        kv[j][i] *= ks;
+      }
+
+    const float a_raw = load_scalar(p.a, p.a_dtype, t * p.num_v_heads + h);
+    const float b_raw = load_scalar(p.b, p.a_dtype, t * p.num_v_heads + h);
+    float g;
+    if (p.flags & QLA_REC_A_IS_LOG_DECAY) {
+      g = a_raw;
+    } else {
+      const float x = a_raw + dt_b;
+      const float bx = p.softplus_beta * x;
+      const float sp = (bx <= p.softplus_threshold) ? log1pf(expf(bx)) / p.softplus_beta : x;
+      g = a_coef * sp;
+    }
+    const float decay = expf(g);
+    const float beta = (p.flags & QLA_REC_B_IS_BETA) ? b_raw : 1.f / (1.f + expf(-b_raw));
+
+    float dot[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      float acc = 0.f;
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          S[r][j][i] *= decay;
+          acc = fmaf(S[r][j][i], kv[j][i], acc);
+        }
+      dot[r] = acc;
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r) dot[r] = group8_sum(dot[r]);
+
+    float out[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const float delta = (vrow[r] - dot[r]) * beta;
+      float acc = 0.f;
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          S[r][j][i] = fmaf(kv[j][i], delta, S[r][j][i]);
+          acc = fmaf(S[r][j][i], qv[j][i], acc);
+        }
+      out[r] = acc;
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r) out[r] = group8_sum(out[r]);
+    if (sub == 0) {
+#pragma unroll
+      for (int r = 0; r < R; ++r)
+        ob[(t * p.num_v_heads + h) * D + row0 + 16 * r] = Cvt<T>::from_f32(out[r]);
+    }
+
+    if (cidx >= 0 && step < p.inter_steps) {
+      InterT* dst = ib + (((cidx * p.inter_steps + step) * p.num_v_heads + h) * D + row0) * D + col0;
+#pragma unroll
+      for (int r = 0; r < R; ++r)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) store4(dst + (r * 16) * D + j * 32, S[r][j]);
+    }
+  }
+
+  if (!(p.flags & QLA_REC_DISABLE_STATE_UPDATE) && sidx >= 0) {
+    float* sp = static_cast<float*>(p.state) + ((sidx * p.num_v_heads + h) * D + row0) * D + col0;
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) store4(sp + (r * 16) * D + j * 32, S[r][j]);
+  }
+}
+
+template <typename T, typename InterT>
+int launch_recurrent(const QlaRecurrentArgs& a, int rows, cudaStream_t stream) {
+  const int64_t heads = static_cast<int64_t>(a.num_seqs) * a.num_v_heads;
+  if (rows == 16) {
+    recurrent_kernel<T, InterT, 1><<<static_cast<unsigned>(heads * 8), 128, 0, stream>>>(a);
+  } else {
+    recurrent_kernel<T, InterT, 2><<<static_cast<unsigned>(heads * 4), 128, 0, stream>>>(a);
+  }
+  QLA_CHECK_CUDA(cudaGetLastError());
+  return QLA_OK;
+}
+
+}  // namespace
+}  // namespace qla
+
+extern "C" QLA_API int qla_recurrent_update(const QlaRecurrentArgs* args, void* stream) {
+  using namespace qla;
+  QLA_CHECK_ARG(args != nullptr, "args is NULL");
+  const QlaRecurrentArgs& a = *args;
+  QLA_CHECK_ARG(a.num_seqs >= 0 && a.total_tokens >= 0, "negative sizes");
+  if (a.num_seqs == 0 || a.total_tokens == 0) return QLA_OK;
+  QLA_CHECK_ARG(a.num_k_heads > 0 && a.num_v_heads > 0 && a.num_v_heads % a.num_k_heads == 0,
+                "num_value_heads must be divisible by num_key_heads");
+  QLA_CHECK_ARG(a.q && a.k && a.v && a.a && a.b && a.o && a.state, "NULL tensor pointer");
+  QLA_CHECK_ARG((a.flags & QLA_REC_A_IS_LOG_DECAY) || (a.A_log && a.dt_bias),
+                "A_log and dt_bias are required unless a_is_log_decay");
+  QLA_CHECK_ARG(a.tokens_per_seq > 0 || a.cu_seqlens != nullptr,
+                "either tokens_per_seq > 0 or cu_seqlens must be given");
+  QLA_CHECK_ARG(a.tokens_per_seq == 0 ||
+                    static_cast<int64_t>(a.tokens_per_seq) * a.num_seqs == a.total_tokens,
+                "total_tokens must equal num_seqs * tokens_per_seq");
+  QLA_CHECK_SUPPORTED(a.qkv_dtype == QLA_DT_BF16 || a.qkv_dtype == QLA_DT_F16,
+                      "q, k, v must be bf16 or fp16");
+  QLA_CHECK_ARG(a.state_slots > 0, "state_slots must be positive");
+  if (a.inter != nullptr) {
+    QLA_CHECK_ARG(a.inter_slots > 0 && a.inter_steps > 0, "inter extents must be positive");
+    QLA_CHECK_SUPPORTED(a.inter_dtype == QLA_DT_F32 || a.inter_dtype == QLA_DT_BF16,
+                        "intermediate_states_buffer must be fp32 or bf16");
+  }
+  QLA_CHECK_ARG(a.parents == nullptr || a.inter != nullptr,
+                "retrieve_parent_token needs intermediate_states_buffer");
+  QLA_CHECK_ARG(a.rows_per_cta == 0 || a.rows_per_cta == 16 || a.rows_per_cta == 32,
+                "rows_per_cta must be 0, 16 or 32");
+  int rows = a.rows_per_cta;
+  if (rows == 0) {
+    // 32 rows per CTA keeps two independent rows in flight per thread; fall back to 16 rows while
+    // the grid would otherwise leave SMs idle (148 SMs, several CTAs each).
+    rows = (static_cast<int64_t>(a.num_seqs) * a.num_v_heads * 4 >= 4 * 148) ? 32 : 16;
+  }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const bool inter_bf16 = a.inter != nullptr && a.inter_dtype == QLA_DT_BF16;
+  if (a.qkv_dtype == QLA_DT_BF16) {
+    return inter_bf16 ? launch_recurrent<__nv_bfloat16, __nv_bfloat16>(a, rows, s)
+                      : launch_recurrent<__nv_bfloat16, float>(a, rows, s);
+  }
+  return inter_bf16 ? launch_recurrent<__half, __nv_bfloat16>(a, rows, s)
+                    : launch_recurrent<__half, float>(a, rows, s);
+}

@@ -1,0 +1,159 @@
+/*
+ * flashqla_b200 - C ABI of the B200 (sm_100a) gated-delta-rule kernels.
+ *
+ * The reference (FlashQLA) has no C ABI: its boundary is the Python module surface
+ *   flash_qla/__init__.py:6-38.  Each entry point below is what a binding for one of those
+ * Python functions calls; the struct fields carry exactly the tensors / scalars of the
+ * Python signature (raw device pointers, element counts, dtype codes).  No entry point
+ * allocates device memory, synchronises the device or touches torch: the caller owns
+ * every buffer, including the scratch ("workspace") whose size the *_workspace_bytes
+ * functions report.  Everything is launched on the stream passed in (a cudaStream_t).
+ *
+ * Return value: 0 on success, a negative QLA_ERR_* code otherwise;
+ * qla_status_string() maps it to text, qla_last_error() gives the detail of the last
+ * failure on the calling thread.
+ */
+#ifndef FLASHQLA_B200_H_
+#define FLASHQLA_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define QLA_ABI_VERSION 1
+
+#if defined(QLA_BUILDING_LIB)
+#define QLA_API __attribute__((visibility("default")))
+#else
+#define QLA_API
+#endif
+
+enum {
+  QLA_OK = 0,
+  QLA_ERR_INVALID_ARG = -1, /* shape / pointer / flag combination rejected               */
+  QLA_ERR_UNSUPPORTED = -2, /* valid in the reference but outside K=V=128, chunk 64, ...  */
+  QLA_ERR_CUDA = -3,        /* a CUDA runtime / driver call failed                        */
+  QLA_ERR_WORKSPACE = -4,   /* workspace missing or too small                             */
+  QLA_ERR_DEVICE = -5       /* the device status word reported a fault (bounded wait ...) */
+};
+
+enum { QLA_DT_F32 = 0, QLA_DT_BF16 = 1, QLA_DT_F16 = 2 };
+
+enum { /* flags of QlaRecurrentArgs */
+  QLA_REC_QK_L2NORM = 1,            /* use_qk_l2norm_in_kernel                      */
+  QLA_REC_DISABLE_STATE_UPDATE = 2, /* disable_state_update                         */
+  QLA_REC_A_IS_LOG_DECAY = 4,       /* a_is_log_decay: a already holds g            */
+  QLA_REC_B_IS_BETA = 8             /* b_is_beta: b already holds beta              */
+};
+
+/*
+ * Recurrent decode / spec-decode verify / tree verify.
+ * Replaces fused_sigmoid_gating_delta_rule_update,
+ *   flash_qla/ops/gated_delta_rule/recurrent_fused.py:6287-7534 (dispatcher) and the kernels
+ *   :290-487 (ragged), :4003-4256 (decode), :5656-5944 (verify), :5952-6249 (tree verify).
+ * Layouts (all contiguous): q,k [NT,Hk,128]; v,o [NT,Hv,128]; a,b [NT,Hv]; A_log,dt_bias [Hv];
+ * state [slots,Hv,128(V),128(K)] fp32, updated in place; inter [slots,inter_steps,Hv,128,128].
+ */
+typedef struct QlaRecurrentArgs {
+  int32_t num_seqs;        /* N                                                              */
+  int32_t total_tokens;    /* NT                                                             */
+  int32_t tokens_per_seq;  /* > 0: every sequence has this many tokens; 0: use cu_seqlens    */
+  int32_t num_k_heads;     /* Hk                                                             */
+  int32_t num_v_heads;     /* Hv, multiple of Hk                                             */
+  int32_t qkv_dtype;       /* QLA_DT_BF16 | QLA_DT_F16 (q, k, v and o)                       */
+  int32_t a_dtype;         /* dtype of a and b                                               */
+  int32_t a_log_dtype;     /* dtype of A_log                                                 */
+  int32_t dt_bias_dtype;   /* dtype of dt_bias                                               */
+  int32_t inter_dtype;     /* QLA_DT_F32 | QLA_DT_BF16, ignored when inter == NULL           */
+  int32_t inter_steps;     /* second extent of inter                                         */
+  int32_t parents_stride;  /* row stride (elements) of parents                               */
+  int32_t flags;           /* QLA_REC_*                                                      */
+  int32_t rows_per_cta;    /* 0 = choose; 16 or 32 rows of V per CTA                         */
+  int64_t state_slots;     /* first extent of state                                          */
+  int64_t inter_slots;     /* first extent of inter                                          */
+  float scale;
+  float softplus_beta;
+  float softplus_threshold;
+  const void* A_log;
+  const void* a;
+  const void* dt_bias;
+  const void* q;
+  const void* k;
+  const void* v;
+  const void* b;
+  void* state;                  /* initial_state_source                                      */
+  const int32_t* state_indices; /* [N] slot per sequence, < 0 = zero state and no write-back; NULL = identity */
+  const int32_t* cu_seqlens;    /* [N+1] or NULL                                             */
+  void* inter;                  /* intermediate_states_buffer or NULL                        */
+  const int32_t* inter_indices; /* [N] or NULL (identity)                                    */
+  const int32_t* parents;       /* retrieve_parent_token [N,steps] or NULL                   */
+  void* o;
+} QlaRecurrentArgs;
+
+QLA_API int qla_recurrent_update(const QlaRecurrentArgs* args, void* stream);
+
+enum { /* flags of QlaChunkFwdArgs / QlaChunkBwdArgs */
+  QLA_CHUNK_TRANSPOSE_STATE = 1, /* states are [N,Hv,V,K] instead of [N,Hv,K,V]            */
+  QLA_CHUNK_STATE_ONLY = 2,      /* skip q / o: only h, v_new and the final state           */
+  QLA_CHUNK_QK_L2NORM = 4        /* normalise q and k rows inside the kernels               */
+};
+
+/*
+ * Chunked prefill forward (chunk 64, K = V = 128).
+ * Replaces chunk_gated_delta_rule_fwd, flash_qla/ops/gated_delta_rule/chunk/__init__.py:23-86
+ * (chunk_local_cumsum ops/utils/cumsum.py:134, kkt_solve chunk/hopper/kkt_solve.py:302,
+ *  fused_gdr_fwd chunk/hopper/fused_fwd.py:532).
+ * Layouts: q,k [B,T,Hk,128]; v,o,v_new [B,T,Hv,128]; g,beta,g_cumsum [B,T,Hv];
+ * A [B,T,Hv,64]; h [B*NC or total chunks,Hv,128,128] bf16; states fp32 [N,Hv,128,128].
+ * With cu_seqlens (device int32 [N+1]) B must be 1 and T is the packed token count.
+ * seq_map (device int32 [N], optional) gives for every sequence the row of final_state
+ * it writes (< 0: none); NULL = identity.
+ */
+typedef struct QlaChunkFwdArgs {
+  int32_t batch;       /* B                                                                  */
+  int32_t seq_len;     /* T                                                                  */
+  int32_t num_seqs;    /* N: B, or the number of cu_seqlens intervals                        */
+  int32_t num_k_heads;
+  int32_t num_v_heads;
+  int32_t qkv_dtype;   /* QLA_DT_BF16 | QLA_DT_F16                                           */
+  int32_t gate_dtype;  /* dtype of g                                                         */
+  int32_t beta_dtype;  /* dtype of beta                                                      */
+  int32_t flags;       /* QLA_CHUNK_*                                                        */
+  int32_t max_chunks_per_seq; /* upper bound used to size grids; 0 = derive from T           */
+  float scale;
+  const void* q;
+  const void* k;
+  const void* v;
+  const void* g;       /* raw per-token log decay                                            */
+  const void* beta;
+  const void* h0;      /* NULL = zero                                                        */
+  const int32_t* cu_seqlens;
+  const int32_t* seq_map;
+  float* g_cumsum;     /* out (may equal an input produced by a previous call when A != NULL and
+                          QLA_CHUNK_SKIP_PREPARE is set)                                     */
+  void* A;             /* out                                                                */
+  void* o;             /* out, NULL with QLA_CHUNK_STATE_ONLY                                */
+  void* h;             /* out or NULL                                                        */
+  void* v_new;         /* out or NULL                                                        */
+  float* final_state;  /* out or NULL                                                        */
+  void* workspace;
+  size_t workspace_bytes;
+  int32_t* status;     /* device int32, must be 0 on entry; kernels write a non-zero code on a fault */
+} QlaChunkFwdArgs;
+
+#define QLA_CHUNK_SKIP_PREPARE 8 /* g_cumsum and A are inputs (already computed) */
+
+QLA_API size_t qla_chunk_fwd_workspace_bytes(const QlaChunkFwdArgs* args);
+QLA_API int qla_chunk_fwd(const QlaChunkFwdArgs* args, void* stream);
+
+QLA_API const char* qla_status_string(int code);
+QLA_API const char* qla_last_error(void);
+QLA_API int qla_abi_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FLASHQLA_B200_H_ */

@@ -1,0 +1,180 @@
+"""GPU parity of the recurrent op (decode / verify / tree verify / ragged) through the C-ABI,
+against oracle/gdr_oracle.py and the golden vectors of the reference's CPU loop.
+
+Tolerances: o max-abs <= 3e-3, state max-abs <= 1e-4, cached states <= 1e-4 (fp32 scratch) -
+the reference's own gates, benchmark/bench_recurrent_fused_matrix.py:515-517.
+"""
+import pytest
+import torch
+
+from oracle import gdr_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+O_TOL, STATE_TOL = 3e-3, 1e-4
+
+
+@pytest.fixture(scope="module")
+def fq():
+    import flashqla_b200
+    assert torch.cuda.is_available()
+    return flashqla_b200
+
+
+def _inputs(N, T, Hk, Hv, seed, dtype=torch.bfloat16, slots=None):
+    gen = torch.Generator().manual_seed(seed)
+    rn = lambda *s: torch.randn(*s, generator=gen)
+    NT = N * T
+    d = dict(
+        q=orc.l2norm(rn(1, NT, Hk, 128)).to(dtype), k=orc.l2norm(rn(1, NT, Hk, 128)).to(dtype),
+        v=rn(1, NT, Hv, 128).to(dtype),
+        g=torch.nn.functional.logsigmoid(rn(1, NT, Hv)), beta=torch.sigmoid(rn(1, NT, Hv)),
+        a=rn(1, NT, Hv).bfloat16(), b=rn(1, NT, Hv).bfloat16(),
+        A_log=(-0.1 - torch.rand(Hv, generator=gen) * 0.5), dt_bias=(0.4 * rn(Hv)).bfloat16(),
+        state=0.1 * rn(slots or N, Hv, 128, 128))
+    return d
+
+
+def _cuda(d):
+    return {n: (t.cuda() if torch.is_tensor(t) else t) for n, t in d.items()}
+
+
+@pytest.mark.parametrize("case", ["chain_f32", "chain_bf16", "hop_f32", "hop_bf16"])
+def test_golden_verify_cases(fq, golden_dir, case):
+    """Geometry, seed and expected values of tests/test_recurrent_verify_scratch_dtype.py."""
+    fx = torch.load(golden_dir / "recurrent_verify.pt", weights_only=False)
+    i, m, c = _cuda(fx["inputs"]), fx["meta"], fx["cases"][case]
+    dt = torch.float32 if case.endswith("f32") else torch.bfloat16
+    inter = torch.zeros(m["N"], m["T"], m["HV"], 128, 128, dtype=dt, device="cuda")
+    state = i["h0"].clone()
+    o = fq.fused_sigmoid_gating_delta_rule_update(
+        i["A_log"], i["a"], i["dt_bias"], i["q"], i["k"], i["v"], i["b"], state, scale=m["scale"],
+        use_qk_l2norm_in_kernel=True, disable_state_update=True, intermediate_states_buffer=inter,
+        retrieve_parent_token=c["parents"].cuda(), block_dv=4)
+    torch.cuda.synchronize()
+    assert torch.equal(state, i["h0"]), "disable_state_update must leave the pool untouched"
+    o = o.float().cpu().view(m["N"], m["T"], m["HV"], 128)
+    assert orc.max_abs(o, c["o"]) <= O_TOL
+    tol = STATE_TOL if dt == torch.float32 else 4e-3  # bf16 snapshots: one bf16 ulp of |S| <~ 1
+    assert orc.max_abs(inter[:, -1].float().cpu(), c["inter_last"]) <= tol
+
+
+def test_verify_invariants(fq, golden_dir):
+    """Known-answer invariants of the reference test (:9-18): linear-verify o is bitwise equal
+    across scratch dtypes; the bf16 scratch equals round_bf16(fp32 scratch); a chain-shaped
+    tree equals the linear run bitwise."""
+    fx = torch.load(golden_dir / "recurrent_verify.pt", weights_only=False)
+    i, m = _cuda(fx["inputs"]), fx["meta"]
+    chain = fx["cases"]["chain_f32"]["parents"].cuda()
+
+    def run(dt, parents):
+        inter = torch.zeros(m["N"], m["T"], m["HV"], 128, 128, dtype=dt, device="cuda")
+        o = fq.fused_sigmoid_gating_delta_rule_update(
+            i["A_log"], i["a"], i["dt_bias"], i["q"], i["k"], i["v"], i["b"], i["h0"].clone(),
+            scale=m["scale"], disable_state_update=True, intermediate_states_buffer=inter,
+            retrieve_parent_token=parents)
+        return o, inter
+
+    o32, i32 = run(torch.float32, None)
+    o16, i16 = run(torch.bfloat16, None)
+    ot, it = run(torch.float32, chain)
+    assert torch.equal(o32, o16)
+    assert torch.equal(i32.bfloat16(), i16)
+    assert torch.equal(o32, ot) and torch.equal(i32, it)
+
+
+@pytest.mark.parametrize("rows", [None, 16, 32])
+@pytest.mark.parametrize("precomputed", [True, False])
+def test_decode_matches_oracle(fq, rows, precomputed):
+    N, Hk, Hv = 6, 2, 4
+    d = _inputs(N, 1, Hk, Hv, seed=10)
+    c = _cuda(d)
+    state = c["state"].clone()
+    kw = dict(block_dv=rows, assume_regular=True)
+    if precomputed:
+        o = fq.fused_sigmoid_gating_delta_rule_update(
+            None, c["g"], None, c["q"], c["k"], c["v"], c["beta"], state,
+            use_qk_l2norm_in_kernel=False, a_is_log_decay=True, b_is_beta=True, **kw)
+        ref_state = d["state"].clone()
+        o_ref = orc.recurrent_update_ref(None or torch.zeros(Hv), d["g"], torch.zeros(Hv), d["q"], d["k"],
+                                         d["v"], d["beta"], ref_state, use_qk_l2norm=False,
+                                         a_is_log_decay=True, b_is_beta=True)
+    else:
+        o = fq.fused_sigmoid_gating_delta_rule_update(
+            c["A_log"], c["a"], c["dt_bias"], c["q"], c["k"], c["v"], c["b"], state, **kw)
+        ref_state = d["state"].clone()
+        o_ref = orc.recurrent_update_ref(d["A_log"], d["a"], d["dt_bias"], d["q"], d["k"], d["v"],
+                                         d["b"], ref_state)
+    assert orc.max_abs(o.float().cpu(), o_ref) <= O_TOL
+    assert orc.max_abs(state.cpu(), ref_state) <= STATE_TOL
+
+
+@pytest.mark.parametrize("mode", ["identity", "reverse", "negative_last"])
+def test_state_index_modes(fq, mode):
+    """Index modes of benchmark/bench_recurrent_fused_matrix.py:162-172; -1 = zero state, no write-back."""
+    N, T, Hk, Hv, slots = 5, 3, 1, 2, 7
+    d = _inputs(N, T, Hk, Hv, seed=11, slots=slots)
+    idx = {"identity": torch.arange(N), "reverse": torch.arange(N).flip(0) + 2,
+           "negative_last": torch.tensor([0, 1, 2, 3, -1])}[mode].int()
+    c = _cuda(d)
+    state = c["state"].clone()
+    o = fq.fused_sigmoid_gating_delta_rule_update(
+        c["A_log"], c["a"], c["dt_bias"], c["q"], c["k"], c["v"], c["b"], state,
+        initial_state_indices=idx.cuda())
+    ref_state = d["state"].clone()
+    o_ref = orc.recurrent_update_ref(d["A_log"], d["a"], d["dt_bias"], d["q"], d["k"], d["v"], d["b"],
+                                     ref_state, state_indices=idx)
+    assert orc.max_abs(o.float().cpu(), o_ref) <= O_TOL
+    assert orc.max_abs(state.cpu(), ref_state) <= STATE_TOL
+
+
+def test_ragged_cu_seqlens_and_tree(fq):
+    lens = [3, 1, 5, 2]
+    N, Hk, Hv = len(lens), 2, 4
+    cu = torch.tensor([0, 3, 4, 9, 11], dtype=torch.int64)
+    d = _inputs(1, 11, Hk, Hv, seed=12, slots=N)
+    c = _cuda(d)
+    parents = torch.tensor([[-1, 0, 0, 0, 0], [-1, 0, 0, 0, 0], [-1, 0, 1, 1, 2], [-1, 0, 0, 0, 0]]).int()
+    inter = torch.zeros(N, 5, Hv, 128, 128, device="cuda")
+    state = c["state"].clone()
+    o = fq.fused_sigmoid_gating_delta_rule_update(
+        c["A_log"], c["a"], c["dt_bias"], c["q"], c["k"], c["v"], c["b"], state, cu_seqlens=cu.cuda(),
+        intermediate_states_buffer=inter, retrieve_parent_token=parents.cuda())
+    ref_state, ref_inter = d["state"].clone(), torch.zeros(N, 5, Hv, 128, 128)
+    o_ref = orc.recurrent_update_ref(d["A_log"], d["a"], d["dt_bias"], d["q"], d["k"], d["v"], d["b"],
+                                     ref_state, cu_seqlens=cu, inter=ref_inter, parents=parents)
+    assert orc.max_abs(o.float().cpu(), o_ref) <= O_TOL
+    assert orc.max_abs(state.cpu(), ref_state) <= STATE_TOL
+    assert orc.max_abs(inter.cpu(), ref_inter) <= STATE_TOL
+
+
+def test_fp16_inputs_and_repeatability(fq):
+    N, T, Hk, Hv = 4, 2, 2, 2
+    d = _inputs(N, T, Hk, Hv, seed=13, dtype=torch.float16)
+    c = _cuda(d)
+    outs = []
+    for _ in range(20):
+        state = c["state"].clone()
+        o = fq.fused_sigmoid_gating_delta_rule_update(
+            c["A_log"], c["a"], c["dt_bias"], c["q"], c["k"], c["v"], c["b"], state)
+        outs.append((o.clone(), state))
+    for o, s in outs[1:]:
+        assert torch.equal(o, outs[0][0]) and torch.equal(s, outs[0][1])
+    ref_state = d["state"].clone()
+    o_ref = orc.recurrent_update_ref(d["A_log"], d["a"], d["dt_bias"], d["q"], d["k"], d["v"], d["b"], ref_state)
+    assert orc.max_abs(outs[0][0].float().cpu(), o_ref) <= O_TOL
+    assert orc.max_abs(outs[0][1].cpu(), ref_state) <= STATE_TOL
+
+
+def test_python_api_errors_on_gpu(fq):
+    q = torch.zeros(1, 4, 2, 128, dtype=torch.bfloat16, device="cuda")
+    v = torch.zeros(1, 4, 4, 128, dtype=torch.bfloat16, device="cuda")
+    ab = torch.zeros(1, 4, 4, device="cuda")
+    hv = torch.zeros(4, device="cuda")
+    st = torch.zeros(4, 4, 128, 128, device="cuda")
+    with pytest.raises(ValueError, match="contiguous"):
+        fq.fused_sigmoid_gating_delta_rule_update(hv, ab, hv, q, q, v, ab, st.transpose(2, 3))
+    with pytest.raises(ValueError, match="a shape"):
+        fq.fused_sigmoid_gating_delta_rule_update(hv, ab[:, :2], hv, q, q, v, ab, st)
+    with pytest.raises(ValueError, match="K=V=128"):
+        fq.fused_sigmoid_gating_delta_rule_update(hv, ab, hv, q[..., :64], q[..., :64], v, ab, st)
