@@ -1,0 +1,144 @@
+"""Chunked prefill / training op: host-side mirror of the reference's chunk API.
+
+Reference: flash_qla/ops/gated_delta_rule/chunk/__init__.py - ``chunk_gated_delta_rule_fwd`` (:23-86),
+``chunk_gated_delta_rule_bwd`` (:89-182), ``ChunkGatedDeltaRuleFunction`` (:185-290) and
+``chunk_gated_delta_rule`` (:294-350).  Same names, argument order, defaults and error behaviour;
+the work happens in the C-ABI library (``qla_chunk_fwd`` ...).
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from . import _cabi
+from .utils import device_status, host_seqlens, l2norm
+
+CHUNK = 64
+
+
+def _check_common(q, k, v, g, beta, initial_state, cu_seqlens, transpose_state_layout):
+    assert q.dtype == k.dtype == v.dtype, "q, k, v must share a dtype"
+    assert q.dtype != torch.float32, "ChunkGatedDeltaRuleFunction does not support float32. Please use bfloat16."
+    assert q.dim() == 4 and k.shape == q.shape and v.dim() == 4, "q,k [B,T,Hk,K]; v [B,T,Hv,V]"
+    B, T, Hk, K = q.shape
+    Hv, V = v.shape[2], v.shape[3]
+    assert K == 128 and V == 128, "K = V = 128 only"
+    assert Hv % Hk == 0, "the number of v heads must be a multiple of the number of q/k heads"
+    assert tuple(g.shape) == (B, T, Hv) and tuple(beta.shape) == (B, T, Hv), "g, beta must be [B,T,Hv]"
+    N = B
+    if cu_seqlens is not None:
+        if B != 1:
+            raise ValueError(
+                f"The batch size is expected to be 1 rather than {B} when using `cu_seqlens`."
+                "Please flatten variable-length inputs before processing.")
+        N = cu_seqlens.numel() - 1
+    if initial_state is not None:
+        if initial_state.shape[0] != N:
+            raise ValueError(
+                f"The number of initial states is expected to be equal to the number of input sequences, "
+                f"i.e., {N} rather than {initial_state.shape[0]}.")
+        want = (N, Hv, V, K) if transpose_state_layout else (N, Hv, K, V)
+        if tuple(initial_state.shape) != want:
+            raise ValueError(f"initial_state must have shape {want}, got {tuple(initial_state.shape)}")
+    return B, T, Hk, Hv, N
+
+
+def chunk_gated_delta_rule_fwd(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    g: torch.Tensor,
+    beta: torch.Tensor,
+    scale: Optional[float] = None,
+    initial_state: Optional[torch.Tensor] = None,
+    cu_seqlens: Optional[torch.Tensor] = None,
+    output_final_state: bool = True,
+    output_h: bool = False,
+    auto_cp: bool = True,
+    output_v_new: bool = False,
+    transpose_state_layout: bool = False,
+):
+    """Raw forward.  ``g`` is the per-token log decay; returns
+    ``(g_cumsum, A, o, h | None, final_state | None[, v_new])`` where ``g_cumsum`` is the chunk-local
+    cumulative gate and ``A`` the gated WY matrix ``[B,T,Hv,64]``, both in the form the backward
+    expects."""
+    B, T, Hk, Hv, N = _check_common(q, k, v, g, beta, initial_state, cu_seqlens, transpose_state_layout)
+    dev = q.device
+    if not q.is_cuda:
+        raise ValueError("flashqla_b200 requires CUDA tensors")
+    q, k, v, g, beta = (x if x.is_contiguous() else x.contiguous() for x in (q, k, v, g, beta))
+    if scale is None:
+        scale = q.shape[-1] ** -0.5
+    h0 = None
+    if initial_state is not None:
+        h0 = initial_state.to(torch.float32)
+        h0 = h0 if h0.is_contiguous() else h0.contiguous()
+    cu = None
+    lens = None
+    if cu_seqlens is not None:
+        cu = cu_seqlens.to(device=dev, dtype=torch.int32).contiguous()
+        lens = host_seqlens(cu_seqlens)
+
+    g_cumsum = torch.empty(B, T, Hv, dtype=torch.float32, device=dev)
+    A = torch.empty(B, T, Hv, CHUNK, dtype=q.dtype, device=dev)
+    o = torch.empty_like(v)
+    if lens is None:
+        n_chunks = B * ((T + CHUNK - 1) // CHUNK)
+        h_shape = (B, (T + CHUNK - 1) // CHUNK, Hv, 128, 128)
+    else:
+        n_chunks = sum((n + CHUNK - 1) // CHUNK for n in lens)
+        h_shape = (1, n_chunks, Hv, 128, 128)
+    h = torch.empty(h_shape, dtype=q.dtype, device=dev) if output_h else None
+    v_new = torch.empty_like(v) if output_v_new else None
+    final_state = torch.empty(N, Hv, 128, 128, dtype=torch.float32, device=dev) if output_final_state else None
+
+    status = device_status(dev)
+    args = _cabi.QlaChunkFwdArgs(
+        batch=B, seq_len=T, num_seqs=N, num_k_heads=Hk, num_v_heads=Hv,
+        qkv_dtype=_cabi.dtype_code(q.dtype), gate_dtype=_cabi.dtype_code(g.dtype),
+        beta_dtype=_cabi.dtype_code(beta.dtype),
+        flags=_cabi.CHUNK_TRANSPOSE_STATE if transpose_state_layout else 0,
+        max_chunks_per_seq=0, scale=float(scale),
+        q=_cabi.ptr(q), k=_cabi.ptr(k), v=_cabi.ptr(v), g=_cabi.ptr(g), beta=_cabi.ptr(beta),
+        h0=_cabi.ptr(h0), cu_seqlens=_cabi.ptr(cu), seq_map=None, chunk_limit=None,
+        g_cumsum=_cabi.ptr(g_cumsum), A=_cabi.ptr(A), o=_cabi.ptr(o), h=_cabi.ptr(h),
+        v_new=_cabi.ptr(v_new), final_state=_cabi.ptr(final_state), workspace=None, workspace_bytes=0,
+        status=_cabi.ptr(status))
+    lib = _cabi.lib()
+    ws_bytes = lib.qla_chunk_fwd_workspace_bytes(args)
+    ws = None
+    if ws_bytes:
+        ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
+        args.workspace, args.workspace_bytes = ws.data_ptr(), ws_bytes
+    with torch.cuda.device(dev):
+        code = lib.qla_chunk_fwd(args, _cabi.current_stream(dev))
+    _cabi.check(code, "qla_chunk_fwd")
+    if output_v_new:
+        return g_cumsum, A, o, h, final_state, v_new
+    return g_cumsum, A, o, h, final_state
+
+
+@torch.compiler.disable
+def chunk_gated_delta_rule(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    g: torch.Tensor,
+    beta: torch.Tensor,
+    scale: Optional[float] = None,
+    initial_state: Optional[torch.Tensor] = None,
+    output_final_state: bool = False,
+    use_qk_l2norm_in_kernel: bool = False,
+    cu_seqlens: Optional[torch.Tensor] = None,
+    head_first: bool = False,
+    transpose_state_layout: bool = False,
+):
+    """Forward-only entry for now: ``(o, final_state | None)`` (reference: chunk/__init__.py:294-350)."""
+    assert not head_first, "head_first=True is not supported"
+    if use_qk_l2norm_in_kernel:
+        q, k = l2norm(q), l2norm(k)
+    _, _, o, _, final_state = chunk_gated_delta_rule_fwd(
+        q, k, v, g, beta, scale=scale, initial_state=initial_state, cu_seqlens=cu_seqlens,
+        output_final_state=output_final_state, transpose_state_layout=transpose_state_layout)
+    return o.to(q.dtype), final_state

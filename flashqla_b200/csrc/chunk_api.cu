@@ -1,0 +1,85 @@
+// C-ABI entry points of the chunked prefill path: argument checks, workspace carving, launch order
+//   [chunk tables] -> kkt_solve (g_cumsum, A) -> chunk forward scan.
+// Mirrors the launch sequence of chunk_gated_delta_rule_fwd,
+// flash_qla/ops/gated_delta_rule/chunk/__init__.py:23-86.
+#include "chunk_params.cuh"
+
+namespace qla {
+
+
+
+namespace {
+size_t table_bytes(int num_seqs) { return ((static_cast<size_t>(num_seqs) + 1) * sizeof(int32_t) + 15) & ~size_t(15); }
+}  // namespace
+
+}  // namespace qla
+
+extern "C" QLA_API size_t qla_chunk_fwd_workspace_bytes(const QlaChunkFwdArgs* a) {
+  if (a == nullptr || a->cu_seqlens == nullptr || a->num_seqs <= 0) return 0;
+  return 2 * qla::table_bytes(a->num_seqs);
+}
+
+extern "C" QLA_API int qla_chunk_fwd(const QlaChunkFwdArgs* args, void* stream_) {
+  using namespace qla;
+  QLA_CHECK_ARG(args != nullptr, "args is NULL");
+  const QlaChunkFwdArgs& a = *args;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  QLA_CHECK_ARG(a.batch > 0 && a.seq_len >= 0 && a.num_seqs > 0, "batch, seq_len, num_seqs must be positive");
+  QLA_CHECK_ARG(a.num_k_heads > 0 && a.num_v_heads > 0 && a.num_v_heads % a.num_k_heads == 0,
+                "num_v_heads must be a multiple of num_k_heads");
+  QLA_CHECK_SUPPORTED(a.qkv_dtype == QLA_DT_BF16 || a.qkv_dtype == QLA_DT_F16, "q, k, v must be bf16 or fp16");
+  const bool varlen = a.cu_seqlens != nullptr;
+  QLA_CHECK_ARG(!varlen || a.batch == 1, "with cu_seqlens the batch size must be 1");
+  QLA_CHECK_ARG(varlen || a.num_seqs == a.batch, "num_seqs must equal batch without cu_seqlens");
+  const bool state_only = (a.flags & QLA_CHUNK_STATE_ONLY) != 0;
+  const bool skip_prepare = (a.flags & QLA_CHUNK_SKIP_PREPARE) != 0;
+  QLA_CHECK_ARG(a.k && a.beta && a.g_cumsum && a.A && a.status, "k, beta, g_cumsum, A, status are required");
+  QLA_CHECK_ARG((a.flags & QLA_CHUNK_ZERO_V) || a.v, "v is required");
+  QLA_CHECK_ARG(skip_prepare || a.g, "g is required");
+  QLA_CHECK_ARG(state_only || (a.q && a.o), "q and o are required unless QLA_CHUNK_STATE_ONLY");
+  QLA_CHECK_SUPPORTED(!(a.flags & QLA_CHUNK_QK_L2NORM), "in-kernel q/k L2 norm is not available");
+  const int64_t total_tokens = static_cast<int64_t>(a.batch) * a.seq_len;
+  if (total_tokens == 0) return QLA_OK;
+  QLA_CHECK_ARG(total_tokens < (int64_t(1) << 31), "too many tokens");
+  const bool is_bf16 = a.qkv_dtype == QLA_DT_BF16;
+
+  int32_t* pair_offsets = nullptr;
+  int32_t* chunk_offsets = nullptr;
+  if (varlen) {
+    const size_t need = 2 * table_bytes(a.num_seqs);
+    if (a.workspace == nullptr || a.workspace_bytes < need) {
+      set_last_error("workspace of %zu bytes required, %zu given", need, a.workspace_bytes);
+      return QLA_ERR_WORKSPACE;
+    }
+    QLA_CHECK_ARG((reinterpret_cast<uintptr_t>(a.workspace) & 15u) == 0, "workspace must be 16-byte aligned");
+    pair_offsets = static_cast<int32_t*>(a.workspace);
+    chunk_offsets = reinterpret_cast<int32_t*>(static_cast<uint8_t*>(a.workspace) + table_bytes(a.num_seqs));
+    int rc = launch_chunk_tables(a.cu_seqlens, a.num_seqs, pair_offsets, chunk_offsets, stream);
+    if (rc != QLA_OK) return rc;
+  }
+
+  if (!skip_prepare) {
+    KktParams kp{};
+    kp.g = a.g; kp.beta = a.beta; kp.g_cumsum = a.g_cumsum; kp.A = a.A;
+    kp.cu_seqlens = a.cu_seqlens; kp.pair_offsets = pair_offsets; kp.status = a.status;
+    kp.num_seqs = a.num_seqs; kp.seq_len = a.seq_len; kp.num_k_heads = a.num_k_heads; kp.num_v_heads = a.num_v_heads;
+    kp.gate_dtype = a.gate_dtype; kp.beta_dtype = a.beta_dtype;
+    const int pairs_upper = varlen ? static_cast<int>(total_tokens / 128 + a.num_seqs)
+                                   : a.batch * ((a.seq_len + 127) / 128);
+    int rc = launch_kkt_solve(kp, a.k, total_tokens, pairs_upper, is_bf16, stream);
+    if (rc != QLA_OK) return rc;
+  }
+
+  FwdParams fp{};
+  fp.g_cumsum = a.g_cumsum; fp.beta = a.beta; fp.h0 = static_cast<const float*>(a.h0);
+  fp.cu_seqlens = a.cu_seqlens; fp.seq_map = a.seq_map; fp.chunk_offsets = chunk_offsets;
+  fp.chunk_limit = a.chunk_limit; fp.o = a.o; fp.v_new = a.v_new; fp.h = a.h; fp.final_state = a.final_state;
+  fp.status = a.status; fp.num_seqs = a.num_seqs; fp.seq_len = a.seq_len;
+  fp.num_k_heads = a.num_k_heads; fp.num_v_heads = a.num_v_heads; fp.beta_dtype = a.beta_dtype;
+  fp.transpose_state = (a.flags & QLA_CHUNK_TRANSPOSE_STATE) ? 1 : 0;
+  fp.init_identity = (a.flags & QLA_CHUNK_INIT_IDENTITY) ? 1 : 0;
+  fp.zero_v = (a.flags & QLA_CHUNK_ZERO_V) ? 1 : 0;
+  fp.scale = a.scale;
+  const void* v = a.v ? a.v : a.k;  // never dereferenced with QLA_CHUNK_ZERO_V, only used for the tensor map
+  return launch_chunk_fwd(fp, a.q, a.k, v, a.A, total_tokens, is_bf16, state_only, stream);
+}

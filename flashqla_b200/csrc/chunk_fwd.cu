@@ -1,7 +1,573 @@
-// placeholder, replaced by the chunked forward
-#include "common.cuh"
-extern "C" QLA_API size_t qla_chunk_fwd_workspace_bytes(const QlaChunkFwdArgs*) { return 0; }
-extern "C" QLA_API int qla_chunk_fwd(const QlaChunkFwdArgs*, void*) {
-  qla::set_last_error("chunk forward not built yet");
-  return QLA_ERR_UNSUPPORTED;
+// Chunked gated-delta-rule forward for sm_100a: the serial scan over 64-token chunks of one
+// (sequence, v-head) with the recurrent state resident in tensor memory.
+// Reference: fused_gdr_fwd (flash_qla/ops/gated_delta_rule/chunk/hopper/fused_fwd.py:19-656; the gated-A
+// variant chunk/blackwell/fused_fwd.py:383-393) and the state-only pass fused_gdr_h
+// (chunk/hopper/prepare_h.py:13-556); math as in tests/ref_gdr.py:107-260.
+//
+// Per chunk (S0 = state entering the chunk, g = chunk-local cumulative gate, gL its last value):
+//   U  = K S0                  W  = beta .* (V - exp(g) .* U)        Vd = A W          (= "v_new")
+//   O  = s exp(g) .* (Q S0) + (s G .* Q K^T) Vd                      G[c,d] = exp(g_c - g_d), c >= d
+//   S1 = exp(gL) S0 + K^T (exp(gL - g) .* Vd)
+//
+// Everything is computed TRANSPOSED so that each tcgen05.mma has M = 128 (the V dimension on the 128
+// TMEM lanes) and every dependent operand can stay in tensor memory:
+//   MMA0  D0[128,64]  = [K;Q] K^T          (SS)  rows 64..127 are P = Q K^T; state independent
+//   MMA1  D1[128,128] = S0^T_bf16 [K;Q]^T  (TS)  columns 0..63 = U^T, 64..127 = (Q S0)^T
+//   MMA2  D2[128,64]  = W^T A^T            (TS)  = Vd^T
+//   MMA3  S^T[128,128] += V'^T K           (TS, B operand MN-major straight from the K tile)
+//   MMA4  D4[128,64]  = Vd^T Pg^T          (TS)  Pg = s G .* P written to a swizzled smem tile
+// Thread v of a compute warpgroup owns TMEM lane v = column v of the state: it reads U^T/Vd^T rows
+// with tcgen05.ld, applies the gates, and writes the bf16 operand of the next MMA back with
+// tcgen05.st.  The fp32 state never leaves tensor memory between chunks.
+//
+// Warp roles (320 threads): warps 0-3 "chain" (W, Vd, state convert, columns 0..63), warps 4-7 "side"
+// (Pg, output epilogue, state convert of columns 64..127), warp 8 TMA producer + gate vectors, warp 9
+// MMA issuer.  Two smem stages of {K,Q,V,A,gates}; all waits are bounded mbarrier waits that raise a
+// status word instead of hanging.
+#include "chunk_params.cuh"
+
+namespace qla {
+
+
+namespace {
+
+// ---- tensor-memory column map (512 columns)
+constexpr uint32_t kColS = 0;      // fp32 state S^T, 128 columns
+constexpr uint32_t kColSbf = 128;  // bf16 copy of S^T (A operand of MMA1), 64 columns
+constexpr uint32_t kColD1 = 192;   // U^T (192..255, overwritten by W bf16 at 192..223) | (Q S)^T (256..319)
+constexpr uint32_t kColD2 = 320;   // Vd^T; overwritten by Vd bf16 (320..351) and V' bf16 (352..383)
+constexpr uint32_t kColD4 = 384;   // Vd^T Pg^T
+constexpr uint32_t kColD0 = 448;   // [K;Q] K^T
+
+// ---- shared-memory map (offsets from a 1024-byte aligned base)
+constexpr uint32_t kStageKQ = 0;         // 32 KiB: half 0 [K rows | Q rows] (16 KiB), half 1 (16 KiB); SW128
+constexpr uint32_t kStageV = 32768;      // 16 KiB: V tile [64][128], no swizzle
+constexpr uint32_t kStageA = 49152;      // 8 KiB: A tile [64][64], SW128
+constexpr uint32_t kStageGate = 57344;   // 1 KiB + : g[64], gamma[64], rho[64], beta[64], egl
+constexpr uint32_t kStageBytes = 59392;  // 58 KiB, multiple of 1024
+constexpr uint32_t kOffPg = 2 * kStageBytes;         // 8 KiB Pg tile, SW128
+constexpr uint32_t kOffO = kOffPg + 8192;            // 16 KiB output tile [64][128]
+constexpr uint32_t kSmemBytes = kOffO + 16384 + 1024;
+
+struct Gates {
+  float g[64];
+  float gamma[64];
+  float rho[64];
+  float beta[64];
+  float egl;
+  int valid;  // number of valid tokens in the chunk
+};
+
+enum Bar {
+  kFull0 = 0, kFull1, kEmpty0, kEmpty1,
+  kPDone, kPFree, kPgReady, kD1Done, kD1Free, kWReady, kD2Done, kVdReady, kSDone, kSbfReady, kD4Done, kD4Free, kOFree, kOReady,
+  kNumBars
+};
+
+constexpr int kThreads = 320;
+
+template <typename T>
+__device__ __forceinline__ uint32_t pack2(float a, float b);
+template <>
+__device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, float b) {
+  __nv_bfloat162 x = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&x);
 }
+template <>
+__device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
+  __half2 x = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&x);
+}
+
+template <typename T, bool kStateOnly>
+__global__ void __launch_bounds__(kThreads, 1)
+chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                 const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_a,
+                 const __grid_constant__ CUtensorMap tm_o, const FwdParams p) {
+  constexpr uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? ptx::kFmtBF16 : ptx::kFmtF16;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int hv = blockIdx.x % p.num_v_heads;
+  const int seq = blockIdx.x / p.num_v_heads;
+  const int hk = hv / (p.num_v_heads / p.num_k_heads);
+
+  int seq_start, seq_end;
+  if (p.cu_seqlens != nullptr) {
+    seq_start = p.cu_seqlens[seq];
+    seq_end = p.cu_seqlens[seq + 1];
+  } else {
+    seq_start = seq * p.seq_len;
+    seq_end = seq_start + p.seq_len;
+  }
+  int nchunks = (seq_end - seq_start + kChunk - 1) / kChunk;
+  int first_chunk = 0;
+  if (p.chunk_limit != nullptr) {
+    const int lim = p.chunk_limit[seq * p.num_v_heads + hv];
+    if (lim < nchunks) first_chunk = nchunks - lim;
+  }
+  const int nproc = nchunks - first_chunk;
+  const int out_row = p.seq_map ? p.seq_map[seq] : seq;
+  const int64_t chunk_base =
+      p.chunk_offsets ? p.chunk_offsets[seq] : static_cast<int64_t>(seq) * ((p.seq_len + kChunk - 1) / kChunk);
+
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  __shared__ uint64_t bars[kNumBars];
+  __shared__ uint32_t tmem_base_s;
+
+  if (tid == 0) {
+    ptx::mbar_init(&bars[kFull0], 33);
+    ptx::mbar_init(&bars[kFull1], 33);
+    ptx::mbar_init(&bars[kEmpty0], 257);
+    ptx::mbar_init(&bars[kEmpty1], 257);
+    ptx::mbar_init(&bars[kPDone], 1);
+    ptx::mbar_init(&bars[kPFree], 64);
+    ptx::mbar_init(&bars[kPgReady], 64);
+    ptx::mbar_init(&bars[kD1Done], 1);
+    ptx::mbar_init(&bars[kD1Free], 128);
+    ptx::mbar_init(&bars[kWReady], 128);
+    ptx::mbar_init(&bars[kD2Done], 1);
+    ptx::mbar_init(&bars[kVdReady], 128);
+    ptx::mbar_init(&bars[kSDone], 1);
+    ptx::mbar_init(&bars[kSbfReady], 256);
+    ptx::mbar_init(&bars[kD4Done], 1);
+    ptx::mbar_init(&bars[kD4Free], 128);
+    ptx::mbar_init(&bars[kOFree], 1);
+    ptx::mbar_init(&bars[kOReady], 128);
+    ptx::fence_mbar_init();
+  }
+  if (warp == 8) {
+    ptx::tmem_alloc(&tmem_base_s, 512);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  ptx::tc_fence_after_sync();
+  const uint32_t tmem = tmem_base_s;
+  int* status = p.status;
+  constexpr int kTimeout = kStatusBarrierTimeout;
+
+  auto stage_ptr = [&](int s) { return smem + s * kStageBytes; };
+  auto gates_of = [&](int s) { return reinterpret_cast<Gates*>(stage_ptr(s) + kStageGate); };
+
+  if (warp == 8) {
+    // =========================================================== producer: TMA + gate vectors
+    for (int i = 0; i < nproc; ++i) {
+      const int s = i & 1, use = i >> 1;
+      if (use > 0 && !ptx::mbar_wait(&bars[kEmpty0 + s], (use - 1) & 1, status, kTimeout)) break;
+      const int chunk = first_chunk + i;
+      const int t0 = seq_start + chunk * kChunk;
+      const int valid = min(kChunk, seq_end - t0);
+      uint8_t* st = stage_ptr(s);
+      if (lane == 0) {
+        uint32_t bytes = 16384 + 8192;  // K + A
+        if (!kStateOnly) bytes += 16384;  // Q
+        if (!p.zero_v) bytes += 16384;    // V
+        ptx::mbar_expect_tx(&bars[kFull0 + s], bytes);
+        ptx::tma_load_3d(st + kStageKQ, &tm_k, &bars[kFull0 + s], 0, hk, t0);
+        ptx::tma_load_3d(st + kStageKQ + 16384, &tm_k, &bars[kFull0 + s], 64, hk, t0);
+        if (!kStateOnly) {
+          ptx::tma_load_3d(st + kStageKQ + 8192, &tm_q, &bars[kFull0 + s], 0, hk, t0);
+          ptx::tma_load_3d(st + kStageKQ + 16384 + 8192, &tm_q, &bars[kFull0 + s], 64, hk, t0);
+        }
+        if (!p.zero_v) ptx::tma_load_3d(st + kStageV, &tm_v, &bars[kFull0 + s], 0, hv, t0);
+        ptx::tma_load_3d(st + kStageA, &tm_a, &bars[kFull0 + s], 0, hv, t0);
+      }
+      Gates* gs = gates_of(s);
+      const int64_t last_tok = static_cast<int64_t>(t0) + valid - 1;
+      const float gl = p.g_cumsum[last_tok * p.num_v_heads + hv];
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        const int c = lane + 32 * r;
+        const bool ok = c < valid;
+        const int64_t tok = static_cast<int64_t>(t0) + c;
+        const float gc = ok ? p.g_cumsum[tok * p.num_v_heads + hv] : gl;
+        const float bc = ok ? load_scalar(p.beta, p.beta_dtype, tok * p.num_v_heads + hv) : 0.f;
+        gs->g[c] = gc;
+        gs->gamma[c] = __expf(gc);
+        gs->rho[c] = ok ? __expf(gl - gc) : 0.f;
+        gs->beta[c] = bc;
+      }
+      if (lane == 0) {
+        gs->egl = __expf(gl);
+        gs->valid = valid;
+      }
+      ptx::mbar_arrive(&bars[kFull0 + s]);  // 32 arrivals + the expect_tx arrival of lane 0
+    }
+  } else if (warp == 9) {
+    // =========================================================== MMA issuer (one thread)
+    if (lane == 0) {
+      const uint32_t id_n128 = ptx::mma_idesc(128, 128, fmt, ptx::kMajorK, ptx::kMajorK);
+      const uint32_t id_n64 = ptx::mma_idesc(128, 64, fmt, ptx::kMajorK, ptx::kMajorK);
+      const uint32_t id_mn128 = ptx::mma_idesc(128, 128, fmt, ptx::kMajorK, ptx::kMajorMN);
+      const uint32_t pg_addr = ptx::smem_u32(smem + kOffPg);
+      for (int i = 0; i < nproc; ++i) {
+        const int s = i & 1, ph = i & 1, prev = (i - 1) & 1;
+        const uint32_t kq = ptx::smem_u32(stage_ptr(s) + kStageKQ);
+        const uint32_t aa = ptx::smem_u32(stage_ptr(s) + kStageA);
+        if (!ptx::mbar_wait(&bars[kFull0 + s], (i >> 1) & 1, status, kTimeout)) break;
+        if (!kStateOnly) {
+          // MMA0: D0 = [K;Q] K^T   (A = 128 rows, B = first 64 rows of the same tile)
+          if (i > 0 && !ptx::mbar_wait(&bars[kPFree], prev, status, kTimeout)) break;
+          ptx::tc_fence_after_sync();
+#pragma unroll
+          for (int ks = 0; ks < 8; ++ks) {
+            const uint64_t d = ptx::smem_desc_sw128(kq + (ks >> 2) * 16384 + (ks & 3) * 32, 16, 1024);
+            ptx::mma_ss(tmem + kColD0, d, d, id_n64, ks > 0);
+          }
+          ptx::mma_commit(&bars[kPDone]);
+        }
+        // MMA1: D1 = S0^T_bf16 * [K;Q]^T
+        if (!ptx::mbar_wait(&bars[kSbfReady], ph, status, kTimeout)) break;
+        if (!kStateOnly && i > 0 && !ptx::mbar_wait(&bars[kD1Free], prev, status, kTimeout)) break;
+        ptx::tc_fence_after_sync();
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          const uint64_t d = ptx::smem_desc_sw128(kq + (ks >> 2) * 16384 + (ks & 3) * 32, 16, 1024);
+          ptx::mma_ts(tmem + kColD1, tmem + kColSbf + ks * 8, d, kStateOnly ? id_n64 : id_n128, ks > 0);
+        }
+        ptx::mma_commit(&bars[kD1Done]);
+        // MMA2: D2 = W^T A^T
+        if (!ptx::mbar_wait(&bars[kWReady], ph, status, kTimeout)) break;
+        ptx::tc_fence_after_sync();
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) {
+          const uint64_t d = ptx::smem_desc_sw128(aa + ks * 32, 16, 1024);
+          ptx::mma_ts(tmem + kColD2, tmem + kColD1 + ks * 8, d, id_n64, ks > 0);
+        }
+        ptx::mma_commit(&bars[kD2Done]);
+        // MMA3: S^T += V'^T K   (B = K tile read MN-major: 64-column halves are 16 KiB apart)
+        if (!ptx::mbar_wait(&bars[kVdReady], ph, status, kTimeout)) break;
+        ptx::tc_fence_after_sync();
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) {
+          const uint64_t d = ptx::smem_desc_sw128(kq + ks * 2048, 16384, 1024);
+          ptx::mma_ts(tmem + kColS, tmem + kColD2 + 32 + ks * 8, d, id_mn128, true);
+        }
+        ptx::mma_commit(&bars[kSDone]);
+        if (!kStateOnly) {
+          // MMA4: D4 = Vd^T Pg^T
+          if (!ptx::mbar_wait(&bars[kPgReady], ph, status, kTimeout)) break;
+          if (i > 0 && !ptx::mbar_wait(&bars[kD4Free], prev, status, kTimeout)) break;
+          ptx::tc_fence_after_sync();
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks) {
+            const uint64_t d = ptx::smem_desc_sw128(pg_addr + ks * 32, 16, 1024);
+            ptx::mma_ts(tmem + kColD4, tmem + kColD2 + ks * 8, d, id_n64, ks > 0);
+          }
+          ptx::mma_commit(&bars[kD4Done]);
+        }
+        ptx::mma_commit(&bars[kEmpty0 + s]);  // every MMA that reads this stage has completed
+      }
+    }
+  } else {
+    // =========================================================== compute warpgroups
+    const int wg = warp >> 2;              // 0 = chain, 1 = side
+    const int v = tid & 127;               // TMEM lane = state column
+    const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const uint32_t tm = tmem + lane_base;
+    const int col_half = wg * 64;          // this warpgroup converts state columns [col_half, col_half + 64)
+    bool alive = true;
+
+    // ---- initial state: S = exp(gL_0) * S_init (fp32) and its bf16 copy
+    {
+      float egl0 = 1.f;
+      if (nproc > 0) {
+        alive = ptx::mbar_wait(&bars[kFull0], 0, status, kTimeout);
+        egl0 = gates_of(0)->egl;
+      }
+      const float* h0p = nullptr;
+      if (!p.init_identity && p.h0 != nullptr)
+        h0p = p.h0 + (static_cast<int64_t>(seq) * p.num_v_heads + hv) * kHeadDim * kHeadDim;
+#pragma unroll
+      for (int kb = 0; kb < 64; kb += 32) {
+        float x[32];
+        uint32_t sf[32], sb[16];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const int k = col_half + kb + j;
+          x[j] = 0.f;
+          if (p.init_identity) x[j] = (k == v) ? 1.f : 0.f;
+          else if (h0p != nullptr) x[j] = p.transpose_state ? h0p[v * kHeadDim + k] : h0p[k * kHeadDim + v];
+        }
+#pragma unroll
+        for (int j = 0; j < 32; j += 2) {
+          sf[j] = __float_as_uint(x[j] * egl0);
+          sf[j + 1] = __float_as_uint(x[j + 1] * egl0);
+          sb[j >> 1] = pack2<T>(x[j], x[j + 1]);
+        }
+        ptx::tmem_st32(tm + kColS + col_half + kb, sf);
+        ptx::tmem_st16(tm + kColSbf + (col_half + kb) / 2, sb);
+        if (nproc == 0 && p.final_state != nullptr && out_row >= 0) {
+          float* fs = p.final_state + (static_cast<int64_t>(out_row) * p.num_v_heads + hv) * kHeadDim * kHeadDim;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int k = col_half + kb + j;
+            if (p.transpose_state) fs[v * kHeadDim + k] = x[j]; else fs[k * kHeadDim + v] = x[j];
+          }
+        }
+      }
+      ptx::tmem_wait_st();
+      ptx::tc_fence_before_sync();
+      ptx::mbar_arrive(&bars[kSbfReady]);
+    }
+
+    float qs[64];  // side warpgroup: s * gamma_c * (Q S0)^T row, kept from D1 until the epilogue
+
+    for (int i = 0; alive && i < nproc; ++i) {
+      const int s = i & 1, ph = i & 1;
+      const int chunk = first_chunk + i;
+      const int t0 = seq_start + chunk * kChunk;
+      const Gates* gs = gates_of(s);
+      if (i > 0) alive = ptx::mbar_wait(&bars[kFull0 + s], (i >> 1) & 1, status, kTimeout);
+      if (!alive) break;
+      const int valid = gs->valid;
+
+      if (wg == 0) {
+        // ---------------- chain: W = beta .* (V - gamma .* U)
+        if (!(alive = ptx::mbar_wait(&bars[kD1Done], ph, status, kTimeout))) break;
+        ptx::tc_fence_after_sync();
+        const T* vt = reinterpret_cast<const T*>(stage_ptr(s) + kStageV);
+#pragma unroll
+        for (int cb = 0; cb < 64; cb += 32) {
+          uint32_t u[32], w[16];
+          ptx::tmem_ld32(tm + kColD1 + cb, u);
+          ptx::tmem_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 32; j += 2) {
+            const int c = cb + j;
+            const float v0 = p.zero_v ? 0.f : Cvt<T>::to_f32(vt[c * kHeadDim + v]);
+            const float v1 = p.zero_v ? 0.f : Cvt<T>::to_f32(vt[(c + 1) * kHeadDim + v]);
+            const float w0 = gs->beta[c] * (v0 - gs->gamma[c] * __uint_as_float(u[j]));
+            const float w1 = gs->beta[c + 1] * (v1 - gs->gamma[c + 1] * __uint_as_float(u[j + 1]));
+            w[j >> 1] = pack2<T>(w0, w1);
+          }
+          ptx::tmem_st16(tm + kColD1 + cb / 2, w);
+        }
+        ptx::tmem_wait_st();
+        ptx::tc_fence_before_sync();
+        ptx::mbar_arrive(&bars[kWReady]);
+
+        // ---------------- chain: Vd, V' = rho .* Vd
+        if (!(alive = ptx::mbar_wait(&bars[kD2Done], ph, status, kTimeout))) break;
+        ptx::tc_fence_after_sync();
+        T* vn = static_cast<T*>(p.v_new);
+        {
+          // both halves of Vd^T are read before the bf16 operands overwrite the same columns
+          uint32_t d0[32], d1[32], vd[32], vp[32];
+          ptx::tmem_ld32(tm + kColD2, d0);
+          ptx::tmem_ld32(tm + kColD2 + 32, d1);
+          ptx::tmem_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 64; j += 2) {
+            const float a = __uint_as_float(j < 32 ? d0[j & 31] : d1[j & 31]);
+            const float b = __uint_as_float(j < 32 ? d0[(j + 1) & 31] : d1[(j + 1) & 31]);
+            vd[j >> 1] = pack2<T>(a, b);
+            vp[j >> 1] = pack2<T>(a * gs->rho[j], b * gs->rho[j + 1]);
+            if (vn != nullptr) {
+              if (j < valid) vn[(static_cast<int64_t>(t0 + j) * p.num_v_heads + hv) * kHeadDim + v] = Cvt<T>::from_f32(a);
+              if (j + 1 < valid) vn[(static_cast<int64_t>(t0 + j + 1) * p.num_v_heads + hv) * kHeadDim + v] = Cvt<T>::from_f32(b);
+            }
+          }
+          ptx::tmem_st32(tm + kColD2, vd);
+          ptx::tmem_st32(tm + kColD2 + 32, vp);
+        }
+        ptx::tmem_wait_st();
+        ptx::tc_fence_before_sync();
+        ptx::mbar_arrive(&bars[kVdReady]);
+      } else {
+        // ---------------- side: Pg = s * G .* P  (P rows live in TMEM lanes 64..127 -> warps 6, 7)
+        if (!kStateOnly) {
+          if ((warp & 3) >= 2) {
+            if (!(alive = ptx::mbar_wait(&bars[kPDone], ph, status, kTimeout))) break;
+            ptx::tc_fence_after_sync();
+            const int c = v - 64;
+            const float gc = gs->g[c];
+            uint8_t* pg = smem + kOffPg;
+#pragma unroll
+            for (int db = 0; db < 64; db += 32) {
+              uint32_t pr[32];
+              ptx::tmem_ld32(tm + kColD0 + db, pr);
+              ptx::tmem_wait_ld();
+              if (db == 32) {
+                ptx::tc_fence_before_sync();
+                ptx::mbar_arrive(&bars[kPFree]);
+              }
+#pragma unroll
+              for (int j8 = 0; j8 < 32; j8 += 8) {
+                uint32_t w[4];
+#pragma unroll
+                for (int j = 0; j < 8; j += 2) {
+                  const int d0 = db + j8 + j;
+                  const float x0 = (d0 <= c) ? p.scale * __expf(gc - gs->g[d0]) * __uint_as_float(pr[j8 + j]) : 0.f;
+                  const float x1 = (d0 + 1 <= c) ? p.scale * __expf(gc - gs->g[d0 + 1]) * __uint_as_float(pr[j8 + j + 1]) : 0.f;
+                  w[j >> 1] = pack2<T>(x0, x1);
+                }
+                *reinterpret_cast<uint4*>(pg + ptx::sw128_offset(c, (db + j8) >> 3)) = make_uint4(w[0], w[1], w[2], w[3]);
+              }
+            }
+            ptx::fence_proxy_async_smem();
+            ptx::mbar_arrive(&bars[kPgReady]);
+          }
+          // ---------------- side: keep s * gamma_c * (Q S0)^T
+          if (!(alive = ptx::mbar_wait(&bars[kD1Done], ph, status, kTimeout))) break;
+          ptx::tc_fence_after_sync();
+#pragma unroll
+          for (int cb = 0; cb < 64; cb += 32) {
+            uint32_t r[32];
+            ptx::tmem_ld32(tm + kColD1 + 64 + cb, r);
+            ptx::tmem_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) qs[cb + j] = p.scale * gs->gamma[cb + j] * __uint_as_float(r[j]);
+          }
+          ptx::tc_fence_before_sync();
+          ptx::mbar_arrive(&bars[kD1Free]);
+        }
+      }
+
+      // ---------------- both: state convert after MMA3 (this warpgroup's 64 columns)
+      if (!(alive = ptx::mbar_wait(&bars[kSDone], ph, status, kTimeout))) break;
+      ptx::tc_fence_after_sync();
+      const bool last = (i + 1 == nproc);
+      float egl_next = 1.f;
+      if (!last) {
+        if (!(alive = ptx::mbar_wait(&bars[kFull0 + (s ^ 1)], ((i + 1) >> 1) & 1, status, kTimeout))) break;
+        egl_next = gates_of(s ^ 1)->egl;
+      }
+      T* hout = static_cast<T*>(p.h);
+#pragma unroll
+      for (int kb = 0; kb < 64; kb += 32) {
+        uint32_t sf[32], sb[16];
+        ptx::tmem_ld32(tm + kColS + col_half + kb, sf);
+        ptx::tmem_wait_ld();
+        if (last) {
+          if (p.final_state != nullptr && out_row >= 0) {
+            float* fs = p.final_state + (static_cast<int64_t>(out_row) * p.num_v_heads + hv) * kHeadDim * kHeadDim;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const int k = col_half + kb + j;
+              if (p.transpose_state) fs[v * kHeadDim + k] = __uint_as_float(sf[j]);
+              else fs[k * kHeadDim + v] = __uint_as_float(sf[j]);
+            }
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; j += 2) {
+            sb[j >> 1] = pack2<T>(__uint_as_float(sf[j]), __uint_as_float(sf[j + 1]));
+            sf[j] = __float_as_uint(__uint_as_float(sf[j]) * egl_next);
+            sf[j + 1] = __float_as_uint(__uint_as_float(sf[j + 1]) * egl_next);
+          }
+          ptx::tmem_st16(tm + kColSbf + (col_half + kb) / 2, sb);
+          ptx::tmem_st32(tm + kColS + col_half + kb, sf);
+          if (hout != nullptr) {
+            // h[chunk + 1] = state entering the next chunk, [K][V] layout
+            T* hp = hout + ((chunk_base + chunk + 1) * p.num_v_heads + hv) * kHeadDim * kHeadDim;
+            const T* sbh = reinterpret_cast<const T*>(sb);
+#pragma unroll
+            for (int j = 0; j < 32; ++j) hp[(col_half + kb + j) * kHeadDim + v] = sbh[j];
+          }
+        }
+      }
+      if (!last) {
+        ptx::tmem_wait_st();
+        ptx::tc_fence_before_sync();
+        ptx::mbar_arrive(&bars[kSbfReady]);
+      }
+
+      // ---------------- side: output epilogue
+      if (!kStateOnly && wg == 1) {
+        if (!(alive = ptx::mbar_wait(&bars[kD4Done], ph, status, kTimeout))) break;
+        ptx::tc_fence_after_sync();
+        T* so = reinterpret_cast<T*>(smem + kOffO);
+        // The tile is reused every chunk: the previous chunk's TMA store must have finished reading it.
+        // Only mbarriers (bounded waits) are used here, never a CTA or named barrier.
+        if (i > 0) {
+          if (tid == 128) {
+            ptx::tma_store_wait_read();
+            ptx::mbar_arrive(&bars[kOFree]);
+          }
+          if (!(alive = ptx::mbar_wait(&bars[kOFree], (i - 1) & 1, status, kTimeout))) break;
+        }
+#pragma unroll
+        for (int cb = 0; cb < 64; cb += 32) {
+          uint32_t r[32];
+          ptx::tmem_ld32(tm + kColD4 + cb, r);
+          ptx::tmem_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) so[(cb + j) * kHeadDim + v] = Cvt<T>::from_f32(qs[cb + j] + __uint_as_float(r[j]));
+        }
+        ptx::tc_fence_before_sync();
+        ptx::mbar_arrive(&bars[kD4Free]);
+        ptx::fence_proxy_async_smem();
+        ptx::mbar_arrive(&bars[kOReady]);
+        if (valid == kChunk) {
+          if (tid == 128) {
+            if (!(alive = ptx::mbar_wait(&bars[kOReady], ph, status, kTimeout))) break;
+            ptx::tma_store_3d(&tm_o, so, 0, hv, t0);
+            ptx::tma_store_commit();
+          }
+        } else {
+          // ragged tail (always the last chunk of a sequence): row-masked 16-byte stores
+          if (!(alive = ptx::mbar_wait(&bars[kOReady], ph, status, kTimeout))) break;
+          T* ob = static_cast<T*>(p.o);
+          const int tl = tid - 128;  // 16 threads per row (8 elements each), 8 rows per pass
+          for (int r0 = 0; r0 < valid; r0 += 8) {
+            const int row = r0 + (tl >> 4);
+            if (row < valid) {
+              const uint4 x = *reinterpret_cast<const uint4*>(so + row * kHeadDim + (tl & 15) * 8);
+              *reinterpret_cast<uint4*>(ob + (static_cast<int64_t>(t0 + row) * p.num_v_heads + hv) * kHeadDim + (tl & 15) * 8) = x;
+            }
+          }
+        }
+      }
+      ptx::mbar_arrive(&bars[kEmpty0 + s]);  // this thread no longer reads stage s
+    }
+    if (!kStateOnly && tid == 128) ptx::tma_store_wait_all();
+    // h[first chunk] = initial state
+    if (p.h != nullptr && nproc > 0 && wg == 0) {
+      T* hp = static_cast<T*>(p.h) + ((chunk_base + first_chunk) * p.num_v_heads + hv) * kHeadDim * kHeadDim;
+      const float* h0p = (!p.init_identity && p.h0 != nullptr)
+                             ? p.h0 + (static_cast<int64_t>(seq) * p.num_v_heads + hv) * kHeadDim * kHeadDim
+                             : nullptr;
+      for (int k = 0; k < kHeadDim; ++k) {
+        float x = 0.f;
+        if (p.init_identity) x = (k == v) ? 1.f : 0.f;
+        else if (h0p != nullptr) x = p.transpose_state ? h0p[v * kHeadDim + k] : h0p[k * kHeadDim + v];
+        hp[k * kHeadDim + v] = Cvt<T>::from_f32(x);
+      }
+    }
+  }
+
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 8) ptx::tmem_dealloc(tmem, 512);
+}
+
+}  // namespace
+
+int launch_chunk_fwd(const FwdParams& p, const void* q, const void* k, const void* v, const void* A,
+                     int64_t total_tokens, bool is_bf16, bool state_only, cudaStream_t stream) {
+  CUtensorMap tm_q, tm_k, tm_v, tm_a, tm_o;
+  int rc;
+  if ((rc = make_tmap_3d(&tm_k, k, total_tokens, p.num_k_heads, kHeadDim, 64, 64, true, is_bf16)) != QLA_OK) return rc;
+  if ((rc = make_tmap_3d(&tm_q, state_only ? k : q, total_tokens, p.num_k_heads, kHeadDim, 64, 64, true, is_bf16)) != QLA_OK) return rc;
+  if ((rc = make_tmap_3d(&tm_v, v, total_tokens, p.num_v_heads, kHeadDim, 64, 128, false, is_bf16)) != QLA_OK) return rc;
+  if ((rc = make_tmap_3d(&tm_a, A, total_tokens, p.num_v_heads, 64, 64, 64, true, is_bf16)) != QLA_OK) return rc;
+  if ((rc = make_tmap_3d(&tm_o, state_only ? v : p.o, total_tokens, p.num_v_heads, kHeadDim, 64, 128, false, is_bf16)) != QLA_OK) return rc;
+  const unsigned grid = static_cast<unsigned>(p.num_seqs) * p.num_v_heads;
+#define QLA_LAUNCH_FWD(T, SO)                                                                              \
+  do {                                                                                                     \
+    QLA_CHECK_CUDA(cudaFuncSetAttribute(chunk_fwd_kernel<T, SO>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                        static_cast<int>(kSmemBytes)));                                    \
+    chunk_fwd_kernel<T, SO><<<grid, kThreads, kSmemBytes, stream>>>(tm_q, tm_k, tm_v, tm_a, tm_o, p);      \
+  } while (0)
+  if (is_bf16) {
+    if (state_only) QLA_LAUNCH_FWD(__nv_bfloat16, true); else QLA_LAUNCH_FWD(__nv_bfloat16, false);
+  } else {
+    if (state_only) QLA_LAUNCH_FWD(__half, true); else QLA_LAUNCH_FWD(__half, false);
+  }
+#undef QLA_LAUNCH_FWD
+  QLA_CHECK_CUDA(cudaGetLastError());
+  return QLA_OK;
+}
+
+}  // namespace qla

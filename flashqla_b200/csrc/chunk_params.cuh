@@ -1,0 +1,48 @@
+// Parameter blocks shared between the chunk kernels and their host entry points.
+#pragma once
+
+#include "ptx_sm100.cuh"
+
+namespace qla {
+
+struct KktParams {
+  const void* g;
+  const void* beta;
+  float* g_cumsum;
+  void* A;
+  const int32_t* cu_seqlens;    // NULL: equal-length batch of `seq_len` tokens
+  const int32_t* pair_offsets;  // [num_seqs + 1] exclusive scan of ceil(len / 128), varlen only
+  int* status;
+  int num_seqs, seq_len, num_k_heads, num_v_heads;
+  int gate_dtype, beta_dtype;
+};
+
+struct FwdParams {
+  const float* g_cumsum;        // [NT, Hv]
+  const void* beta;             // [NT, Hv]
+  const float* h0;              // [n_h0, Hv, 128, 128] or NULL
+  const int32_t* cu_seqlens;    // [num_seqs + 1] or NULL (equal-length batch)
+  const int32_t* seq_map;       // [num_seqs] row of final_state (< 0: none) or NULL (identity)
+  const int32_t* chunk_offsets; // [num_seqs + 1] first chunk index of each sequence (varlen h output)
+  const int32_t* chunk_limit;   // [num_seqs, Hv] optional: only the LAST chunk_limit chunks are processed
+  void* o;                      // [NT, Hv, 128]
+  void* v_new;                  // [NT, Hv, 128] or NULL
+  void* h;                      // [total_chunks, Hv, 128, 128] bf16/fp16 or NULL
+  float* final_state;           // [n_out, Hv, 128, 128] or NULL
+  int* status;
+  int num_seqs, seq_len, num_k_heads, num_v_heads;
+  int beta_dtype;
+  int transpose_state;          // states stored [V, K] instead of [K, V]
+  int init_identity;            // start from S = I (ignores h0)
+  int zero_v;                   // treat V as 0
+  float scale;
+};
+
+int launch_chunk_tables(const int32_t* cu, int n, int32_t* pair_offsets, int32_t* chunk_offsets,
+                        cudaStream_t stream);
+int launch_kkt_solve(const KktParams& p, const void* k, int64_t total_tokens, int pairs_upper, bool is_bf16,
+                     cudaStream_t stream);
+int launch_chunk_fwd(const FwdParams& p, const void* q, const void* k, const void* v, const void* A,
+                     int64_t total_tokens, bool is_bf16, bool state_only, cudaStream_t stream);
+
+}  // namespace qla

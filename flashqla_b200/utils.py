@@ -1,0 +1,63 @@
+"""Host helpers: L2 norm, per-device status word, host copies of cu_seqlens.
+
+Reference counterparts: flash_qla/utils/math.py:7-21 (l2norm), flash_qla/utils/index.py:13-63
+(tensor_cache, keyed on object identity there; keyed on storage + version here so that in-place edits
+are seen).
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Tuple
+
+import torch
+
+_STATUS: Dict[int, torch.Tensor] = {}
+_SEQLEN_CACHE: Dict[Tuple, List[int]] = {}
+_SEQLEN_CACHE_MAX = 256
+
+
+def l2norm(x: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
+    """``x * rsqrt(sum(x^2, -1) + eps)`` computed in fp32, returned in x's dtype."""
+    xf = x.float()
+    return (xf * torch.rsqrt(xf.pow(2).sum(-1, keepdim=True) + eps)).to(x.dtype)
+
+
+def device_status(device: torch.device) -> torch.Tensor:
+    """The int32 status word the kernels of this device report faults to (0 = fine)."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    st = _STATUS.get(idx)
+    if st is None:
+        st = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", idx))
+        _STATUS[idx] = st
+    return st
+
+
+def check_device_status(device=None) -> None:
+    """Synchronise and raise if any kernel launched so far reported a fault (e.g. a bounded
+    barrier wait that gave up).  The status word is cleared afterwards."""
+    from ._cabi import QlaError
+    devs = list(_STATUS) if device is None else [torch.device(device).index or 0]
+    for idx in devs:
+        st = _STATUS.get(idx)
+        if st is None:
+            continue
+        code = int(st.item())
+        if code != 0:
+            st.zero_()
+            names = {1: "a bounded barrier wait timed out", 2: "an index was out of range"}
+            raise QlaError(f"device {idx} reported status {code}: {names.get(code, 'unknown')}")
+
+
+def host_seqlens(cu_seqlens: torch.Tensor) -> List[int]:
+    """Sequence lengths as Python ints.  One device-to-host copy per distinct cu_seqlens content
+    version; later calls with the same tensor hit the cache."""
+    key = (cu_seqlens.data_ptr(), cu_seqlens.numel(), str(cu_seqlens.device), cu_seqlens._version)
+    lens = _SEQLEN_CACHE.get(key)
+    if lens is None:
+        cu = cu_seqlens.detach().to("cpu", torch.int64).tolist()
+        lens = [cu[i + 1] - cu[i] for i in range(len(cu) - 1)]
+        if any(n < 0 for n in lens):
+            raise ValueError("cu_seqlens must be non-decreasing")
+        if len(_SEQLEN_CACHE) >= _SEQLEN_CACHE_MAX:
+            _SEQLEN_CACHE.pop(next(iter(_SEQLEN_CACHE)))
+        _SEQLEN_CACHE[key] = lens
+    return lens

@@ -98,7 +98,11 @@ QLA_API int qla_recurrent_update(const QlaRecurrentArgs* args, void* stream);
 enum { /* flags of QlaChunkFwdArgs / QlaChunkBwdArgs */
   QLA_CHUNK_TRANSPOSE_STATE = 1, /* states are [N,Hv,V,K] instead of [N,Hv,K,V]            */
   QLA_CHUNK_STATE_ONLY = 2,      /* skip q / o: only h, v_new and the final state           */
-  QLA_CHUNK_QK_L2NORM = 4        /* normalise q and k rows inside the kernels               */
+  QLA_CHUNK_QK_L2NORM = 4,       /* normalise q and k rows inside the kernels (reserved)    */
+  QLA_CHUNK_SKIP_PREPARE = 8,    /* g_cumsum and A are inputs (computed by an earlier call) */
+  QLA_CHUNK_INIT_IDENTITY = 16,  /* start every sequence from S = I instead of h0          */
+  QLA_CHUNK_ZERO_V = 32          /* treat v as zero (with INIT_IDENTITY: the K x K transition
+                                    matrix of the chunks, used by context parallelism)      */
 };
 
 /*
@@ -111,6 +115,8 @@ enum { /* flags of QlaChunkFwdArgs / QlaChunkBwdArgs */
  * With cu_seqlens (device int32 [N+1]) B must be 1 and T is the packed token count.
  * seq_map (device int32 [N], optional) gives for every sequence the row of final_state
  * it writes (< 0: none); NULL = identity.
+ * Workspace: qla_chunk_fwd_workspace_bytes(args) bytes of device memory, 16-byte aligned;
+ * it holds the per-sequence chunk tables when cu_seqlens is given.
  */
 typedef struct QlaChunkFwdArgs {
   int32_t batch;       /* B                                                                  */
@@ -132,9 +138,10 @@ typedef struct QlaChunkFwdArgs {
   const void* h0;      /* NULL = zero                                                        */
   const int32_t* cu_seqlens;
   const int32_t* seq_map;
-  float* g_cumsum;     /* out (may equal an input produced by a previous call when A != NULL and
-                          QLA_CHUNK_SKIP_PREPARE is set)                                     */
-  void* A;             /* out                                                                */
+  const int32_t* chunk_limit; /* device int32 [N,Hv] or NULL: run only the last chunk_limit chunks
+                                 of each (sequence, head), starting from a zero state        */
+  float* g_cumsum;     /* out; in with QLA_CHUNK_SKIP_PREPARE                                */
+  void* A;             /* out; in with QLA_CHUNK_SKIP_PREPARE                                */
   void* o;             /* out, NULL with QLA_CHUNK_STATE_ONLY                                */
   void* h;             /* out or NULL                                                        */
   void* v_new;         /* out or NULL                                                        */
@@ -143,8 +150,6 @@ typedef struct QlaChunkFwdArgs {
   size_t workspace_bytes;
   int32_t* status;     /* device int32, must be 0 on entry; kernels write a non-zero code on a fault */
 } QlaChunkFwdArgs;
-
-#define QLA_CHUNK_SKIP_PREPARE 8 /* g_cumsum and A are inputs (already computed) */
 
 QLA_API size_t qla_chunk_fwd_workspace_bytes(const QlaChunkFwdArgs* args);
 QLA_API int qla_chunk_fwd(const QlaChunkFwdArgs* args, void* stream);

@@ -1,0 +1,141 @@
+"""GPU parity of the chunked prefill forward through the C-ABI against oracle/gdr_oracle.py and the
+golden vectors of the reference oracle.
+
+Tolerances (stated by the task): relative RMS error <= 5e-3 for o and the final state; the
+reference's own gate max|err| <= 2% of max|ref| (tests/test_gdr.py:225-232) is kept as well.
+"""
+import pytest
+import torch
+
+from oracle import gdr_oracle as orc
+
+pytestmark = pytest.mark.gpu
+RMS_TOL, MAXRATIO_TOL = 5e-3, 2e-2
+
+
+@pytest.fixture(scope="module")
+def fq():
+    import flashqla_b200
+    assert torch.cuda.is_available()
+    return flashqla_b200
+
+
+def _cuda(d):
+    return {n: t.cuda() for n, t in d.items()}
+
+
+def _check(name, got, ref):
+    rms, ratio = orc.rel_rms(got.float().cpu(), ref), orc.max_abs_ratio(got.float().cpu(), ref)
+    assert rms <= RMS_TOL and ratio <= MAXRATIO_TOL, f"{name}: rel_rms={rms:.3e} max_ratio={ratio:.3e}"
+
+
+def _run_case(fq, B, T, Hk, Hv, seed, with_h0, gate_div=1.0, zero_gate=0.0, dtype=torch.bfloat16, **kw):
+    inp = orc.make_prefill_inputs(B, T, Hk, Hv, seed=seed, dtype=dtype, with_h0=with_h0, gate_div=gate_div,
+                                  zero_gate_heads=zero_gate)
+    c = _cuda(inp)
+    out = fq.chunk_gated_delta_rule_fwd(c["q"], c["k"], c["v"], c["g"], c["beta"],
+                                        initial_state=c.get("h0"), **kw)
+    fq.check_device_status()
+    ref = orc.chunk_gdr_fwd(inp["q"], inp["k"], inp["v"], inp["g"], inp["beta"], h0=inp.get("h0"))
+    return out, ref, inp
+
+
+@pytest.mark.parametrize("name", ["tail_gqa_bwd", "weak_gate_bwd"])
+def test_golden_forward(fq, golden_dir, name):
+    fx = torch.load(golden_dir / f"{name}.pt", weights_only=False)
+    i = _cuda({n: fx["inputs"][n] for n in ("q", "k", "v", "g", "beta", "h0")})
+    g_cs, A, o, h, fs = fq.chunk_gated_delta_rule_fwd(i["q"], i["k"], i["v"], i["g"], i["beta"],
+                                                      scale=fx["meta"]["scale"], initial_state=i["h0"])
+    fq.check_device_status()
+    assert orc.max_abs(g_cs.cpu(), fx["g_cumsum"]) < 1e-4
+    _check("o", o, fx["o"])
+    _check("final_state", fs, fx["final_state"])
+
+
+@pytest.mark.parametrize("T", [1, 17, 63, 64, 65, 96, 128, 160, 1000])
+def test_lengths_and_tails(fq, T):
+    (g_cs, A, o, h, fs), ref, _ = _run_case(fq, 2, T, 2, 4, seed=100 + T, with_h0=True)
+    assert orc.max_abs(g_cs.cpu(), ref["g_cumsum"]) < 1e-4
+    assert orc.rel_rms(A.float().cpu(), ref["A"]) < 5e-3
+    _check("o", o, ref["o"])
+    _check("final_state", fs, ref["final_state"])
+
+
+def test_stage_outputs_h_and_v_new(fq):
+    (g_cs, A, o, h, fs, v_new), ref, _ = _run_case(fq, 1, 300, 1, 2, seed=7, with_h0=True, output_h=True,
+                                                  output_v_new=True)
+    _check("v_new", v_new, ref["v_new"])
+    _check("h", h, ref["h"])
+    _check("o", o, ref["o"])
+
+
+def test_no_initial_state_and_no_final_state(fq):
+    (g_cs, A, o, h, fs), ref, _ = _run_case(fq, 1, 256, 2, 2, seed=8, with_h0=False, output_final_state=False)
+    assert fs is None and h is None
+    _check("o", o, ref["o"])
+
+
+def test_reference_gate_distribution(fq):
+    """g/16 with zero-gate heads: the state does not decay, so errors accumulate over the sequence."""
+    (g_cs, A, o, h, fs), ref, _ = _run_case(fq, 1, 2048, 2, 4, seed=9, with_h0=True, gate_div=16.0, zero_gate=0.25)
+    _check("o", o, ref["o"])
+    _check("final_state", fs, ref["final_state"])
+
+
+def test_transposed_state_layout(fq):
+    inp = orc.make_prefill_inputs(2, 200, 1, 2, seed=10, with_h0=True)
+    c = _cuda(inp)
+    _, _, o, _, fs = fq.chunk_gated_delta_rule_fwd(c["q"], c["k"], c["v"], c["g"], c["beta"],
+                                                   initial_state=c["h0"].transpose(-1, -2).contiguous(),
+                                                   transpose_state_layout=True)
+    fq.check_device_status()
+    ref = orc.chunk_gdr_fwd(inp["q"], inp["k"], inp["v"], inp["g"], inp["beta"], h0=inp["h0"])
+    _check("o", o, ref["o"])
+    _check("final_state", fs.transpose(-1, -2), ref["final_state"])
+
+
+def test_varlen_matches_per_sequence_oracle(fq):
+    lens = [17, 448, 64, 320, 1, 200]   # partial chunks as in tests/test_bwd_sm12x.py and settings/varlen.csv
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int64)
+    NT, Hk, Hv = int(cu[-1]), 2, 4
+    inp = orc.make_prefill_inputs(1, NT, Hk, Hv, seed=11, with_h0=True, n_states=len(lens))
+    c = _cuda(inp)
+    g_cs, A, o, h, fs = fq.chunk_gated_delta_rule_fwd(c["q"], c["k"], c["v"], c["g"], c["beta"],
+                                                      initial_state=c["h0"], cu_seqlens=cu.cuda(), output_h=True)
+    fq.check_device_status()
+    ref = orc.chunk_gdr_fwd_varlen(inp["q"], inp["k"], inp["v"], inp["g"], inp["beta"], cu, h0=inp["h0"])
+    assert orc.max_abs(g_cs.cpu(), ref["g_cumsum"]) < 1e-4
+    _check("o", o, ref["o"])
+    _check("final_state", fs, ref["final_state"])
+    _check("h", h, ref["h"])
+
+
+def test_fp16_inputs(fq):
+    (g_cs, A, o, h, fs), ref, _ = _run_case(fq, 1, 192, 2, 2, seed=12, with_h0=True, dtype=torch.float16)
+    _check("o", o, ref["o"])
+    _check("final_state", fs, ref["final_state"])
+
+
+def test_repeatable_bitwise(fq):
+    """Race check in the spirit of the reference's 1000x loops (tests/test_gdr.py:211)."""
+    inp = _cuda(orc.make_prefill_inputs(2, 700, 2, 4, seed=13, with_h0=True))
+    outs = []
+    for _ in range(30):
+        _, _, o, _, fs = fq.chunk_gated_delta_rule_fwd(inp["q"], inp["k"], inp["v"], inp["g"], inp["beta"],
+                                                       initial_state=inp["h0"])
+        outs.append((o, fs))
+    fq.check_device_status()
+    for o, fs in outs[1:]:
+        assert torch.equal(o, outs[0][0]) and torch.equal(fs, outs[0][1])
+
+
+def test_api_errors(fq):
+    q = torch.zeros(2, 64, 2, 128, dtype=torch.bfloat16, device="cuda")
+    v = torch.zeros(2, 64, 4, 128, dtype=torch.bfloat16, device="cuda")
+    gb = torch.zeros(2, 64, 4, device="cuda")
+    with pytest.raises(ValueError, match="batch size"):
+        fq.chunk_gated_delta_rule_fwd(q, q, v, gb, gb, cu_seqlens=torch.tensor([0, 64, 128], device="cuda"))
+    with pytest.raises(ValueError, match="initial states"):
+        fq.chunk_gated_delta_rule_fwd(q, q, v, gb, gb, initial_state=torch.zeros(3, 4, 128, 128, device="cuda"))
+    with pytest.raises(AssertionError):
+        fq.chunk_gated_delta_rule_fwd(q.float(), q.float(), v.float(), gb, gb)
