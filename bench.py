@@ -1,0 +1,348 @@
+#!/usr/bin/env python
+"""Benchmark of the GDN hot path on B200.  One JSON line on stdout (rank 0).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+Default workload = the configuration the headline metric is quoted on: chunked prefill forward,
+B=1, T=32768, Hk=16, Hv=32, K=V=128, bf16 q/k/v, fp32 g/beta, zero initial state, final state
+written.  With N > 1 (one process per GPU under torch.distributed.run) the v-heads (and their k-heads)
+are split across ranks - no collective on the data path; the timed region is bracketed by a barrier and
+the reported time is the max over ranks.
+
+Other workloads (own measurements, same JSON shape): ``decode`` and ``verify`` (256 sequences, Hk=16,
+Hv=32; HBM-bound, metric GB/s), ``varlen`` (64 packed sequences, Hk=Hv=8).
+
+``--impl reference`` times the CPU restatement of the reference algorithm (oracle/gdr_oracle.py, all host
+threads) on a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+K = V = 128
+CHUNK = 64
+
+
+def peaks():
+    f = ROOT / "MEASURED_PEAKS.json"
+    if f.exists():
+        p = json.loads(f.read_text())
+        return dict(hbm=p["hbm_gbs"], tf_burst=p["bf16_tflops"], tf_sus=p["bf16_tflops_sustained"], src="measured")
+    return dict(hbm=6650.0, tf_burst=1590.0, tf_sus=1400.0, src="fallback")
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU through NVML while the timed region runs."""
+
+    def __init__(self, index: int, period: float = 0.05):
+        self.index, self.period = index, period
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+
+    def __enter__(self):
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self._nv = pynvml
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(self.index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self._nv = None
+            return self
+        self._thread = threading.Thread(target=self._run, daemon=True)
+        self._thread.start()
+        return self
+
+    def _run(self):
+        nv = self._nv
+        names = {
+            nv.nvmlClocksThrottleReasonHwSlowdown: "hw_slowdown",
+            nv.nvmlClocksThrottleReasonHwThermalSlowdown: "hw_thermal_slowdown",
+            nv.nvmlClocksThrottleReasonSwThermalSlowdown: "sw_thermal_slowdown",
+            nv.nvmlClocksThrottleReasonSwPowerCap: "sw_power_cap",
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM))
+                r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self._h)
+                for bit, name in names.items():
+                    if r & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop.wait(self.period)
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def summary(self):
+        s = sorted(self.samples)
+        med = s[len(s) // 2] if s else None
+        return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(s)}
+
+
+def dist_env():
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    return rank, world, local
+
+
+def timed(fn, steps, warmup, world, device):
+    """W untimed steps, then exactly K steps between CUDA events on the current stream; barrier +
+    synchronize on both sides; max over ranks."""
+    import torch.distributed as dist
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize(device)
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize(device)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize(device)
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dist.barrier()
+        ms = float(t.item())
+    return ms
+
+
+# ------------------------------------------------------------------------------------ workloads
+def prefill_inputs(T, Hk, Hv, seed, n_seqs=1, with_h0=False):
+    from oracle import gdr_oracle as orc
+    return orc.make_prefill_inputs(1, T, Hk, Hv, seed=seed, with_h0=with_h0, n_states=n_seqs)
+
+
+def run_prefill(args, rank, world, device, varlen=False):
+    import flashqla_b200 as fq
+    from flashqla_b200 import _cabi
+    from oracle import gdr_oracle as orc
+    if varlen:
+        gen = torch.Generator().manual_seed(2)
+        lens = torch.randint(512, 16385, (64,), generator=gen).tolist()
+        # token-balanced longest-first assignment of sequences to ranks
+        from flashqla_b200.sharding import balance_sequences
+        mine = balance_sequences(lens, world)[rank]
+        my_lens = [lens[i] for i in mine]
+        Hk = Hv = 8
+        T = sum(my_lens)
+        total_tokens = sum(lens)
+        cu = torch.tensor([0] + list(torch.tensor(my_lens).cumsum(0)), dtype=torch.int32)
+        inp = prefill_inputs(T, Hk, Hv, seed=20 + rank, n_seqs=len(my_lens), with_h0=True)
+        workload = "varlen_prefill_fwd_64seq_U512-16384_Hk8_Hv8"
+        n_states_in = len(my_lens)
+    else:
+        T, Hk_all, Hv_all = args.tokens, 16, 32
+        assert Hv_all % world == 0 and Hk_all % world == 0
+        Hk, Hv = Hk_all // world, Hv_all // world
+        total_tokens = T
+        cu = None
+        inp = prefill_inputs(T, Hk, Hv, seed=1 + rank)
+        workload = f"prefill_fwd_B1_T{T}_Hk{Hk_all}_Hv{Hv_all}_K128_V128_chunk64"
+        n_states_in = 0
+    host = {n: t.pin_memory() for n, t in inp.items()}
+    dev = {n: t.to(device, non_blocking=True) for n, t in host.items()}
+    cu_dev = cu.to(device) if cu is not None else None
+    h0 = dev.get("h0")
+    torch.cuda.synchronize(device)
+
+    def step():
+        return fq.chunk_gated_delta_rule_fwd(dev["q"], dev["k"], dev["v"], dev["g"], dev["beta"],
+                                             initial_state=h0, cu_seqlens=cu_dev, output_final_state=True)
+
+    launches_per_step = fq.chunk.launches_per_forward(varlen=cu is not None)
+    with ClockSampler(torch.cuda.current_device() if device.index is None else device.index) as cs:
+        ms = timed(step, args.steps, args.warmup, world, device)
+    fq.check_device_status()
+
+    # ---- dominant kernel alone (the chunk scan), for the roofline entry
+    g_cs, A, o, _, fs = step()
+    def scan_only():
+        fq.chunk.forward_scan_only(dev["q"], dev["k"], dev["v"], dev["beta"], g_cs, A, o, fs, initial_state=h0,
+                                   cu_seqlens=cu_dev)
+    ms_scan = timed(scan_only, args.steps, args.warmup, world, device) / args.steps
+
+    # ---- end to end through the public API with host buffers
+    o_host = torch.empty(o.shape, dtype=o.dtype).pin_memory()
+    fs_host = torch.empty(fs.shape, dtype=fs.dtype).pin_memory()
+    h2d = sum(host[n].numel() * host[n].element_size() for n in host)
+    d2h = o_host.numel() * o_host.element_size() + fs_host.numel() * fs_host.element_size()
+
+    def e2e_step():
+        d = {n: t.to(device, non_blocking=True) for n, t in host.items()}
+        _, _, oo, _, ff = fq.chunk_gated_delta_rule_fwd(d["q"], d["k"], d["v"], d["g"], d["beta"],
+                                                        initial_state=d.get("h0"), cu_seqlens=cu_dev,
+                                                        output_final_state=True)
+        o_host.copy_(oo, non_blocking=True)
+        fs_host.copy_(ff, non_blocking=True)
+
+    e2e_steps = max(2, min(args.steps, 10))
+    ms_e2e = timed(e2e_step, e2e_steps, 2, world, device)
+    fq.check_device_status()
+
+    pk = peaks()
+    per_step = ms / args.steps
+    value = total_tokens / (per_step * 1e-3)
+    tok_heads_rank = T * Hv
+    scan_flops = tok_heads_rank * (6 * CHUNK * K + 6 * K * V)  # QK^T, A W, Pg Vd + K S, Q S, K^T V'
+    achieved = scan_flops / (ms_scan * 1e-3) / 1e12
+    algo_bytes = orc.prefill_bytes(T, Hk, Hv, n_states_in, n_states_in if varlen else 1)
+    line = {
+        "metric": "gdn_prefill_fwd_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_step, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": workload, "sharding": f"v-heads/{world}" if not varlen else f"sequences/{world}",
+                   "l2": "inputs (>= 0.8 GB per step) exceed the 126 MB L2; no flush needed",
+                   "tokens": total_tokens},
+        "clocks": cs.summary(),
+        "e2e": {"value": total_tokens / (ms_e2e / e2e_steps * 1e-3), "unit": "tokens/s",
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e / e2e_steps},
+        "gpu_launches": launches_per_step * args.steps,
+        "roofline": {"kernel": "chunk_fwd_kernel", "bound": "tensor", "achieved": achieved,
+                     "peak": pk["tf_burst"], "unit": "TFLOP/s", "frac": achieved / pk["tf_burst"],
+                     "peak_source": pk["src"], "ms_per_launch": ms_scan, "traffic": None,
+                     "hbm_frac": algo_bytes / (ms_scan * 1e-3) / 1e9 / pk["hbm"]},
+    }
+    return line
+
+
+def run_recurrent(args, rank, world, device, verify: bool):
+    import flashqla_b200 as fq
+    from oracle import gdr_oracle as orc
+    N_all, Hk, Hv = 256, 16, 32
+    assert N_all % world == 0
+    N = N_all // world
+    T = 4 if verify else 1
+    gen = torch.Generator().manual_seed(4 + rank)
+    rn = lambda *s: torch.randn(*s, generator=gen)
+    q = orc.l2norm(rn(1, N * T, Hk, K)).bfloat16().to(device)
+    k = orc.l2norm(rn(1, N * T, Hk, K)).bfloat16().to(device)
+    v = rn(1, N * T, Hv, V).bfloat16().to(device)
+    g = torch.nn.functional.logsigmoid(rn(1, N * T, Hv)).to(device)
+    beta = torch.sigmoid(rn(1, N * T, Hv)).to(device)
+    state = (0.1 * rn(N, Hv, V, K)).to(device)
+    inter = torch.empty(N, T, Hv, V, K, dtype=torch.float32 if not args.bf16_scratch else torch.bfloat16,
+                        device=device) if verify else None
+
+    def step():
+        return fq.fused_sigmoid_gating_delta_rule_update(
+            None, g, None, q, k, v, beta, state, use_qk_l2norm_in_kernel=False, a_is_log_decay=True,
+            b_is_beta=True, assume_regular=True, disable_state_update=verify, intermediate_states_buffer=inter)
+
+    with ClockSampler(device.index or 0) as cs:
+        ms = timed(step, args.steps, args.warmup, world, device)
+    per_step = ms / args.steps
+    cache_b = 0 if not verify else (2 if args.bf16_scratch else 4)
+    nbytes = orc.state_bytes_decode(N, Hv, T=T, Hk=Hk, cache_bytes=cache_b, write_back=not verify)
+    gbs = nbytes * world / (per_step * 1e-3) / 1e9
+    pk = peaks()
+    return {
+        "metric": "gdn_%s_hbm_gb_per_s" % ("verify" if verify else "decode"), "value": gbs, "unit": "GB/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_step,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"{'verify_T4' if verify else 'decode_T1'}_N{N_all}_Hk16_Hv32",
+                   "scratch": None if not verify else ("bf16" if args.bf16_scratch else "fp32"),
+                   "l2": "state pool (>= 0.5 GB) exceeds the 126 MB L2 at N=1"},
+        "clocks": cs.summary(), "gpu_launches": args.steps,
+        "roofline": {"kernel": "recurrent_kernel", "bound": "hbm", "achieved": gbs / world, "peak": pk["hbm"],
+                     "unit": "GB/s", "frac": gbs / world / pk["hbm"], "peak_source": pk["src"], "traffic": None},
+    }
+
+
+# ------------------------------------------------------------------------------------ CPU arms
+def cpu_prefill_sample(tokens_sample: int, repeats: int = 2):
+    """Oracle forward on the first `tokens_sample` tokens of the default workload, all host threads."""
+    from oracle import gdr_oracle as orc
+    torch.set_num_threads(os.cpu_count() or 1)
+    inp = orc.make_prefill_inputs(1, tokens_sample, 16, 32, seed=1)
+    best = float("inf")
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        orc.chunk_gdr_fwd(inp["q"], inp["k"], inp["v"], inp["g"], inp["beta"])
+        best = min(best, time.perf_counter() - t0)
+    return tokens_sample / best, best
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="prefill_fwd", choices=["prefill_fwd", "varlen", "decode", "verify"])
+    ap.add_argument("--tokens", type=int, default=32768)
+    ap.add_argument("--bf16-scratch", action="store_true")
+    ap.add_argument("--cpu-sample-tokens", type=int, default=4096)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    rank, world, local = dist_env()
+    args.warmup = max(args.warmup, 3)
+
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        steps = max(1, min(args.steps, 3))
+        vals = []
+        for _ in range(max(1, min(args.warmup, 1)) + steps):
+            tps, sec = cpu_prefill_sample(args.cpu_sample_tokens, repeats=1)
+            vals.append(tps)
+        tps = sum(vals[-steps:]) / steps
+        sample = f"first {args.cpu_sample_tokens} tokens of the workload (all 32 v-heads), fp32 oracle port"
+        print(json.dumps({
+            "impl": "reference", "metric": "gdn_prefill_fwd_tokens_per_s", "value": tps, "unit": "tokens/s",
+            "n_gpus": args.gpus, "steps": steps, "warmup": 1, "ms_per_step": args.cpu_sample_tokens / tps * 1e3,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "prefill_fwd_B1_T32768_Hk16_Hv32_K128_V128_chunk64", "tokens": 32768},
+            "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",
+                             "sample": sample},
+            "e2e": {"value": tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}))
+        return
+
+    import torch.distributed as dist
+    device = torch.device("cuda", local)
+    torch.cuda.set_device(device)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=device)
+    if args.workload == "prefill_fwd":
+        line = run_prefill(args, rank, world, device)
+    elif args.workload == "varlen":
+        line = run_prefill(args, rank, world, device, varlen=True)
+    else:
+        line = run_recurrent(args, rank, world, device, verify=args.workload == "verify")
+    if rank == 0:
+        if not args.no_cpu_baseline and args.workload == "prefill_fwd":
+            tps, sec = cpu_prefill_sample(args.cpu_sample_tokens)
+            line["cpu_baseline"] = {
+                "value": tps, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",
+                "sample": f"first {args.cpu_sample_tokens} tokens of the workload (all 32 v-heads), best of 2, "
+                          f"{sec:.2f} s"}
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

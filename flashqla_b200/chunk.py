@@ -44,6 +44,47 @@ def _check_common(q, k, v, g, beta, initial_state, cu_seqlens, transpose_state_l
     return B, T, Hk, Hv, N
 
 
+def _launch_fwd(q, k, v, g, beta, h0, cu, g_cumsum, A, o, h, v_new, final_state, scale, flags=0,
+                seq_map=None, chunk_limit=None, num_seqs=None):
+    """Fill ``QlaChunkFwdArgs`` from tensors and call ``qla_chunk_fwd`` on the current stream."""
+    dev = k.device
+    B, T, Hk = k.shape[0], k.shape[1], k.shape[2]
+    Hv = beta.shape[2]
+    N = num_seqs if num_seqs is not None else (cu.numel() - 1 if cu is not None else B)
+    status = device_status(dev)
+    args = _cabi.QlaChunkFwdArgs(
+        batch=B, seq_len=T, num_seqs=N, num_k_heads=Hk, num_v_heads=Hv,
+        qkv_dtype=_cabi.dtype_code(k.dtype), gate_dtype=0 if g is None else _cabi.dtype_code(g.dtype),
+        beta_dtype=_cabi.dtype_code(beta.dtype), flags=flags, max_chunks_per_seq=0, scale=float(scale),
+        q=_cabi.ptr(q), k=_cabi.ptr(k), v=_cabi.ptr(v), g=_cabi.ptr(g), beta=_cabi.ptr(beta),
+        h0=_cabi.ptr(h0), cu_seqlens=_cabi.ptr(cu), seq_map=_cabi.ptr(seq_map),
+        chunk_limit=_cabi.ptr(chunk_limit), g_cumsum=_cabi.ptr(g_cumsum), A=_cabi.ptr(A), o=_cabi.ptr(o),
+        h=_cabi.ptr(h), v_new=_cabi.ptr(v_new), final_state=_cabi.ptr(final_state), workspace=None,
+        workspace_bytes=0, status=_cabi.ptr(status))
+    lib = _cabi.lib()
+    ws_bytes = lib.qla_chunk_fwd_workspace_bytes(args)
+    if ws_bytes:
+        ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
+        args.workspace, args.workspace_bytes = ws.data_ptr(), ws_bytes
+    with torch.cuda.device(dev):
+        code = lib.qla_chunk_fwd(args, _cabi.current_stream(dev))
+    _cabi.check(code, "qla_chunk_fwd")
+
+
+def launches_per_forward(varlen: bool) -> int:
+    """Kernels one forward call launches: [chunk tables] + kkt_solve + chunk scan."""
+    return 3 if varlen else 2
+
+
+def forward_scan_only(q, k, v, beta, g_cumsum, A, o, final_state, initial_state=None, cu_seqlens=None,
+                      scale=None):
+    """Launch only the chunk scan (the dominant kernel) with ``g_cumsum`` and ``A`` from an earlier
+    forward; used to time that kernel by itself."""
+    cu = None if cu_seqlens is None else cu_seqlens.to(torch.int32)
+    _launch_fwd(q, k, v, None, beta, initial_state, cu, g_cumsum, A, o, None, None, final_state,
+                q.shape[-1] ** -0.5 if scale is None else scale, flags=_cabi.CHUNK_SKIP_PREPARE)
+
+
 def chunk_gated_delta_rule_fwd(
     q: torch.Tensor,
     k: torch.Tensor,
@@ -93,27 +134,8 @@ def chunk_gated_delta_rule_fwd(
     v_new = torch.empty_like(v) if output_v_new else None
     final_state = torch.empty(N, Hv, 128, 128, dtype=torch.float32, device=dev) if output_final_state else None
 
-    status = device_status(dev)
-    args = _cabi.QlaChunkFwdArgs(
-        batch=B, seq_len=T, num_seqs=N, num_k_heads=Hk, num_v_heads=Hv,
-        qkv_dtype=_cabi.dtype_code(q.dtype), gate_dtype=_cabi.dtype_code(g.dtype),
-        beta_dtype=_cabi.dtype_code(beta.dtype),
-        flags=_cabi.CHUNK_TRANSPOSE_STATE if transpose_state_layout else 0,
-        max_chunks_per_seq=0, scale=float(scale),
-        q=_cabi.ptr(q), k=_cabi.ptr(k), v=_cabi.ptr(v), g=_cabi.ptr(g), beta=_cabi.ptr(beta),
-        h0=_cabi.ptr(h0), cu_seqlens=_cabi.ptr(cu), seq_map=None, chunk_limit=None,
-        g_cumsum=_cabi.ptr(g_cumsum), A=_cabi.ptr(A), o=_cabi.ptr(o), h=_cabi.ptr(h),
-        v_new=_cabi.ptr(v_new), final_state=_cabi.ptr(final_state), workspace=None, workspace_bytes=0,
-        status=_cabi.ptr(status))
-    lib = _cabi.lib()
-    ws_bytes = lib.qla_chunk_fwd_workspace_bytes(args)
-    ws = None
-    if ws_bytes:
-        ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
-        args.workspace, args.workspace_bytes = ws.data_ptr(), ws_bytes
-    with torch.cuda.device(dev):
-        code = lib.qla_chunk_fwd(args, _cabi.current_stream(dev))
-    _cabi.check(code, "qla_chunk_fwd")
+    _launch_fwd(q, k, v, g, beta, h0, cu, g_cumsum, A, o, h, v_new, final_state, scale,
+                flags=_cabi.CHUNK_TRANSPOSE_STATE if transpose_state_layout else 0)
     if output_v_new:
         return g_cumsum, A, o, h, final_state, v_new
     return g_cumsum, A, o, h, final_state
