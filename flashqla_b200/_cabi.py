@@ -18,7 +18,7 @@ _DTYPES = {torch.float32: QLA_DT_F32, torch.bfloat16: QLA_DT_BF16, torch.float16
 
 REC_QK_L2NORM, REC_DISABLE_STATE_UPDATE, REC_A_IS_LOG_DECAY, REC_B_IS_BETA = 1, 2, 4, 8
 CHUNK_TRANSPOSE_STATE, CHUNK_STATE_ONLY, CHUNK_QK_L2NORM, CHUNK_SKIP_PREPARE = 1, 2, 4, 8
-CHUNK_INIT_IDENTITY, CHUNK_ZERO_V = 16, 32
+CHUNK_INIT_IDENTITY, CHUNK_ZERO_V, CHUNK_PREPARE_ONLY = 16, 32, 64
 
 
 class QlaError(RuntimeError):
@@ -62,11 +62,29 @@ class QlaChunkFwdArgs(C.Structure):
     ]
 
 
+class QlaCpPlanArgs(C.Structure):
+    _fields_ = [
+        ("num_segments", C.c_int32), ("num_v_heads", C.c_int32), ("threshold", C.c_float),
+        ("g_cumsum", C.c_void_p), ("cu_seqlens", C.c_void_p), ("seg_next", C.c_void_p),
+        ("warm_limit", C.c_void_p), ("m_limit", C.c_void_p),
+    ]
+
+
+class QlaCpChainArgs(C.Structure):
+    _fields_ = [
+        ("num_raw_seqs", C.c_int32), ("num_v_heads", C.c_int32), ("h0", C.c_void_p), ("M", C.c_void_p),
+        ("m_limit", C.c_void_p), ("raw_first_seg", C.c_void_p),
+    ]
+
+
 # Every symbol include/flashqla_b200.h declares; tests check that the built library exports each.
 EXPORTS = {
     "qla_recurrent_update": (C.c_int, [C.POINTER(QlaRecurrentArgs), C.c_void_p]),
     "qla_chunk_fwd_workspace_bytes": (C.c_size_t, [C.POINTER(QlaChunkFwdArgs)]),
     "qla_chunk_fwd": (C.c_int, [C.POINTER(QlaChunkFwdArgs), C.c_void_p]),
+    "qla_cp_plan": (C.c_int, [C.POINTER(QlaCpPlanArgs), C.c_void_p]),
+    "qla_cp_chain": (C.c_int, [C.POINTER(QlaCpChainArgs), C.c_void_p]),
+    "qla_set_trace_buffer": (C.c_int, [C.c_void_p, C.c_size_t]),
     "qla_status_string": (C.c_char_p, [C.c_int]),
     "qla_last_error": (C.c_char_p, []),
     "qla_abi_version": (C.c_int, []),

@@ -11,7 +11,7 @@ from typing import Optional
 
 import torch
 
-from . import _cabi
+from . import _cabi, cp
 from .utils import device_status, host_seqlens, l2norm
 
 CHUNK = 64
@@ -50,6 +50,8 @@ def _launch_fwd(q, k, v, g, beta, h0, cu, g_cumsum, A, o, h, v_new, final_state,
     dev = k.device
     B, T, Hk = k.shape[0], k.shape[1], k.shape[2]
     Hv = beta.shape[2]
+    if cu is not None:  # packed view: [B, T, ...] is contiguous, i.e. [1, B*T, ...]
+        B, T = 1, B * T
     N = num_seqs if num_seqs is not None else (cu.numel() - 1 if cu is not None else B)
     status = device_status(dev)
     args = _cabi.QlaChunkFwdArgs(
@@ -71,8 +73,12 @@ def _launch_fwd(q, k, v, g, beta, h0, cu, g_cumsum, A, o, h, v_new, final_state,
     _cabi.check(code, "qla_chunk_fwd")
 
 
-def launches_per_forward(varlen: bool) -> int:
-    """Kernels one forward call launches: [chunk tables] + kkt_solve + chunk scan."""
+def launches_per_forward(varlen: bool, use_cp: bool = False) -> int:
+    """Kernels of this library one forward call launches.  Plain: [chunk tables] + kkt_solve + chunk
+    scan.  With context parallelism: [tables] + kkt_solve, plan, tables + warm-up scan, tables + transition
+    scan, chain, tables + main scan."""
+    if use_cp:
+        return (2 if varlen else 1) + 1 + 2 + 2 + 1 + 2
     return 3 if varlen else 2
 
 
@@ -134,8 +140,24 @@ def chunk_gated_delta_rule_fwd(
     v_new = torch.empty_like(v) if output_v_new else None
     final_state = torch.empty(N, Hv, 128, 128, dtype=torch.float32, device=dev) if output_final_state else None
 
-    _launch_fwd(q, k, v, g, beta, h0, cu, g_cumsum, A, o, h, v_new, final_state, scale,
-                flags=_cabi.CHUNK_TRANSPOSE_STATE if transpose_state_layout else 0)
+    plan = cp.get_plan(lens if lens is not None else [T] * B, Hv, dev) if auto_cp else None
+    if plan is not None and plan.use_cp:
+        # g_cumsum and A on the original sequences, then per-segment initial states, then the scan
+        # over segments (segments are whole chunks, so chunk numbering is unchanged)
+        _launch_fwd(None, k, None, g, beta, None, cu, g_cumsum, A, None, None, None, None, scale,
+                    flags=_cabi.CHUNK_PREPARE_ONLY)
+        h0_kv = h0.transpose(-1, -2) if (h0 is not None and transpose_state_layout) else h0
+        cp_h0 = cp.segment_initial_states(plan, k, v, beta, g_cumsum, A, h0_kv, scale, _launch_fwd)
+        fs = final_state
+        if transpose_state_layout and final_state is not None:
+            fs = torch.empty_like(final_state)
+        _launch_fwd(q, k, v, None, beta, cp_h0, plan.dev["cu"], g_cumsum, A, o, h, v_new, fs, scale,
+                    flags=_cabi.CHUNK_SKIP_PREPARE, seq_map=plan.dev["seg_raw"], num_seqs=len(plan.seg_next))
+        if fs is not final_state:
+            final_state.copy_(fs.transpose(-1, -2))
+    else:
+        _launch_fwd(q, k, v, g, beta, h0, cu, g_cumsum, A, o, h, v_new, final_state, scale,
+                    flags=_cabi.CHUNK_TRANSPOSE_STATE if transpose_state_layout else 0)
     if output_v_new:
         return g_cumsum, A, o, h, final_state, v_new
     return g_cumsum, A, o, h, final_state

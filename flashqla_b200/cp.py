@@ -1,0 +1,128 @@
+"""Gate-driven intra-card context parallelism (CP) for the chunked forward.
+
+Host-side mirror of flash_qla/ops/gated_delta_rule/chunk/cp_context.py: ``_calc_cp_seqs`` (:36-114,
+the planner) and ``intra_card_cp_preprocess`` (:117-176, the warm-up / chaining sequence).  The
+planner's constants are re-derived for B200 (148 SMs, one resident chunk-scan CTA per SM):
+
+* CP is used when the (sequence, v-head) chains alone cannot fill the machine:
+  ``chains < 2 * SMs`` and some sequence is long enough to be cut.
+* The segment length aims at ``CTAS_PER_SM`` segment-CTAs per SM, so that dynamic CTA scheduling
+  evens out the tail, with a floor of ``MIN_SEG_CHUNKS`` chunks to keep the warm-up pass (a few
+  trailing chunks per segment, state only) a small fraction of the work.
+
+Everything that depends on tensor VALUES (warm-up lengths, fallback heads) is decided on the device
+(``qla_cp_plan``); the host plan depends on the sequence LENGTHS only, so a cached plan never needs a
+device-to-host copy.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+from . import _cabi
+
+CHUNK = 64
+CTAS_PER_SM = 4
+MIN_SEG_CHUNKS = 8
+WARMUP_THRESHOLD = -10.0  # exp(-10) ~ 4.5e-5: what a dropped prefix may contribute (cp_fwd.py:29-61)
+
+
+@dataclass
+class CpPlan:
+    use_cp: bool
+    seg_chunks: int = 0
+    cu: Optional[List[int]] = None           # segment boundaries, len = n_seg + 1
+    seg_next: Optional[List[int]] = None     # successor segment or -1
+    seg_raw: Optional[List[int]] = None      # raw sequence of a segment that ENDS it, else -1
+    raw_first: Optional[List[int]] = None    # first segment of every raw sequence, len = n_raw + 1
+    dev: Optional[Dict[str, torch.Tensor]] = None
+
+
+_PLAN_CACHE: Dict[Tuple, CpPlan] = {}
+
+
+def plan_segments(lens: Sequence[int], num_v_heads: int, num_sms: int = 148) -> CpPlan:
+    """Decide whether to cut sequences and where.  Pure function of lengths, head count, SM count."""
+    chunks = [(n + CHUNK - 1) // CHUNK for n in lens]
+    chains = len(lens) * num_v_heads
+    total = sum(chunks) * num_v_heads
+    if not chunks or chains >= 2 * num_sms or max(chunks) < 2 * MIN_SEG_CHUNKS:
+        return CpPlan(use_cp=False)
+    seg = max(MIN_SEG_CHUNKS, -(-total // (CTAS_PER_SM * num_sms)))
+    if max(chunks) <= seg:
+        return CpPlan(use_cp=False)
+    cu, seg_next, seg_raw, raw_first = [0], [], [], [0]
+    start = 0
+    for r, n in enumerate(lens):
+        pieces = max(1, -(-chunks[r] // seg))
+        for p in range(pieces):
+            end_tok = min(n, (p + 1) * seg * CHUNK) if p + 1 < pieces else n
+            cu.append(start + end_tok)
+            last = p + 1 == pieces
+            seg_next.append(-1 if last else len(seg_next) + 1)
+            seg_raw.append(r if last else -1)
+        start += n
+        raw_first.append(len(seg_next))
+    return CpPlan(True, seg, cu, seg_next, seg_raw, raw_first)
+
+
+def get_plan(lens: Sequence[int], num_v_heads: int, device: torch.device) -> CpPlan:
+    key = (tuple(lens), num_v_heads, str(device))
+    plan = _PLAN_CACHE.get(key)
+    if plan is None:
+        sms = torch.cuda.get_device_properties(device).multi_processor_count
+        plan = plan_segments(lens, num_v_heads, sms)
+        if plan.use_cp:
+            i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=device)
+            n_seg = len(plan.seg_next)
+            plan.dev = dict(
+                cu=i32(plan.cu), seg_next=i32(plan.seg_next), seg_raw=i32(plan.seg_raw),
+                raw_first=i32(plan.raw_first),
+                # row of cp_h0 a segment's end state is written to by the warm-up pass
+                warm_map=i32([s if s >= 0 else -1 for s in plan.seg_next]),
+                identity=i32(list(range(n_seg))),
+                first_rows=torch.tensor(plan.raw_first[:-1], dtype=torch.int64, device=device))
+        if len(_PLAN_CACHE) >= 256:
+            _PLAN_CACHE.pop(next(iter(_PLAN_CACHE)))
+        _PLAN_CACHE[key] = plan
+    return plan
+
+
+def segment_initial_states(plan: CpPlan, k, v, beta, g_cumsum, A, h0, scale, launch_fwd):
+    """Run plan -> warm-up -> transition matrices -> chaining.  Returns ``cp_h0`` fp32
+    ``[n_seg, Hv, 128, 128]``: the state every segment starts from.  ``launch_fwd`` is
+    ``chunk._launch_fwd``."""
+    dev = k.device
+    Hv = beta.shape[2]
+    d = plan.dev
+    n_seg = len(plan.seg_next)
+    lib = _cabi.lib()
+    stream = _cabi.current_stream(dev)
+    warm_limit = torch.empty(n_seg, Hv, dtype=torch.int32, device=dev)
+    m_limit = torch.empty(n_seg, Hv, dtype=torch.int32, device=dev)
+    pa = _cabi.QlaCpPlanArgs(num_segments=n_seg, num_v_heads=Hv, threshold=WARMUP_THRESHOLD,
+                             g_cumsum=g_cumsum.data_ptr(), cu_seqlens=d["cu"].data_ptr(),
+                             seg_next=d["seg_next"].data_ptr(), warm_limit=warm_limit.data_ptr(),
+                             m_limit=m_limit.data_ptr())
+    with torch.cuda.device(dev):
+        _cabi.check(lib.qla_cp_plan(pa, stream), "qla_cp_plan")
+
+    cp_h0 = torch.zeros(n_seg, Hv, 128, 128, dtype=torch.float32, device=dev)
+    if h0 is not None:
+        cp_h0.index_copy_(0, d["first_rows"], h0)
+    flags = _cabi.CHUNK_STATE_ONLY | _cabi.CHUNK_SKIP_PREPARE
+    # segment-end states from the trailing `warm_limit` chunks, written straight into the successor's row
+    launch_fwd(None, k, v, None, beta, None, d["cu"], g_cumsum, A, None, None, None, cp_h0, scale,
+               flags=flags, seq_map=d["warm_map"], chunk_limit=warm_limit, num_seqs=n_seg)
+    # transition matrices of the (segment, head) pairs that never decayed below the threshold
+    M = torch.empty(n_seg, Hv, 128, 128, dtype=torch.float32, device=dev)
+    launch_fwd(None, k, None, None, beta, None, d["cu"], g_cumsum, A, None, None, None, M, scale,
+               flags=flags | _cabi.CHUNK_INIT_IDENTITY | _cabi.CHUNK_ZERO_V, seq_map=d["identity"],
+               chunk_limit=m_limit, num_seqs=n_seg)
+    ca = _cabi.QlaCpChainArgs(num_raw_seqs=len(plan.raw_first) - 1, num_v_heads=Hv, h0=cp_h0.data_ptr(),
+                              M=M.data_ptr(), m_limit=m_limit.data_ptr(), raw_first_seg=d["raw_first"].data_ptr())
+    with torch.cuda.device(dev):
+        _cabi.check(lib.qla_cp_chain(ca, stream), "qla_cp_chain")
+    return cp_h0

@@ -9,10 +9,23 @@ namespace qla {
 
 
 namespace {
+long long* g_trace = nullptr;
 size_t table_bytes(int num_seqs) { return ((static_cast<size_t>(num_seqs) + 1) * sizeof(int32_t) + 15) & ~size_t(15); }
 }  // namespace
 
+long long* current_trace_buffer() { return g_trace; }
+
 }  // namespace qla
+
+extern "C" QLA_API int qla_set_trace_buffer(long long* device_buffer, size_t count) {
+  using namespace qla;
+  if (device_buffer != nullptr && count < static_cast<size_t>(kTraceRoles * kTraceChunks * kTraceEvents)) {
+    set_last_error("trace buffer needs %d entries", kTraceRoles * kTraceChunks * kTraceEvents);
+    return QLA_ERR_INVALID_ARG;
+  }
+  g_trace = device_buffer;
+  return QLA_OK;
+}
 
 extern "C" QLA_API size_t qla_chunk_fwd_workspace_bytes(const QlaChunkFwdArgs* a) {
   if (a == nullptr || a->cu_seqlens == nullptr || a->num_seqs <= 0) return 0;
@@ -34,9 +47,10 @@ extern "C" QLA_API int qla_chunk_fwd(const QlaChunkFwdArgs* args, void* stream_)
   const bool state_only = (a.flags & QLA_CHUNK_STATE_ONLY) != 0;
   const bool skip_prepare = (a.flags & QLA_CHUNK_SKIP_PREPARE) != 0;
   QLA_CHECK_ARG(a.k && a.beta && a.g_cumsum && a.A && a.status, "k, beta, g_cumsum, A, status are required");
-  QLA_CHECK_ARG((a.flags & QLA_CHUNK_ZERO_V) || a.v, "v is required");
+  QLA_CHECK_ARG((a.flags & (QLA_CHUNK_ZERO_V | QLA_CHUNK_PREPARE_ONLY)) || a.v, "v is required");
   QLA_CHECK_ARG(skip_prepare || a.g, "g is required");
-  QLA_CHECK_ARG(state_only || (a.q && a.o), "q and o are required unless QLA_CHUNK_STATE_ONLY");
+  QLA_CHECK_ARG(state_only || (a.flags & QLA_CHUNK_PREPARE_ONLY) || (a.q && a.o),
+                "q and o are required unless QLA_CHUNK_STATE_ONLY");
   QLA_CHECK_SUPPORTED(!(a.flags & QLA_CHUNK_QK_L2NORM), "in-kernel q/k L2 norm is not available");
   const int64_t total_tokens = static_cast<int64_t>(a.batch) * a.seq_len;
   if (total_tokens == 0) return QLA_OK;
@@ -70,6 +84,8 @@ extern "C" QLA_API int qla_chunk_fwd(const QlaChunkFwdArgs* args, void* stream_)
     if (rc != QLA_OK) return rc;
   }
 
+  if (a.flags & QLA_CHUNK_PREPARE_ONLY) return QLA_OK;
+
   FwdParams fp{};
   fp.g_cumsum = a.g_cumsum; fp.beta = a.beta; fp.h0 = static_cast<const float*>(a.h0);
   fp.cu_seqlens = a.cu_seqlens; fp.seq_map = a.seq_map; fp.chunk_offsets = chunk_offsets;
@@ -80,6 +96,7 @@ extern "C" QLA_API int qla_chunk_fwd(const QlaChunkFwdArgs* args, void* stream_)
   fp.init_identity = (a.flags & QLA_CHUNK_INIT_IDENTITY) ? 1 : 0;
   fp.zero_v = (a.flags & QLA_CHUNK_ZERO_V) ? 1 : 0;
   fp.scale = a.scale;
+  fp.trace = current_trace_buffer();
   const void* v = a.v ? a.v : a.k;  // never dereferenced with QLA_CHUNK_ZERO_V, only used for the tensor map
   return launch_chunk_fwd(fp, a.q, a.k, v, a.A, total_tokens, is_bf16, state_only, stream);
 }

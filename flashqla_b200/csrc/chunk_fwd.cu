@@ -66,6 +66,13 @@ enum Bar {
 
 constexpr int kThreads = 320;
 
+// One arrival per warp: every lane has finished (and fenced) its own writes, the warp converges, and
+// lane 0 signals the barrier.
+__device__ __forceinline__ void warp_arrive(uint64_t* bar, int lane) {
+  __syncwarp();
+  if (lane == 0) ptx::mbar_arrive(bar);
+}
+
 template <typename T>
 __device__ __forceinline__ uint32_t pack2(float a, float b);
 template <>
@@ -102,6 +109,7 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   int first_chunk = 0;
   if (p.chunk_limit != nullptr) {
     const int lim = p.chunk_limit[seq * p.num_v_heads + hv];
+    if (lim <= 0) return;  // nothing asked of this (sequence, head); uniform for the whole CTA
     if (lim < nchunks) first_chunk = nchunks - lim;
   }
   const int nproc = nchunks - first_chunk;
@@ -110,29 +118,30 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       p.chunk_offsets ? p.chunk_offsets[seq] : static_cast<int64_t>(seq) * ((p.seq_len + kChunk - 1) / kChunk);
 
   extern __shared__ __align__(1024) uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  // align up with pointer arithmetic on the shared array so that the compiler keeps the address space
+  uint8_t* smem = smem_raw + ((1024u - (ptx::smem_u32(smem_raw) & 1023u)) & 1023u);
   __shared__ uint64_t bars[kNumBars];
   __shared__ uint32_t tmem_base_s;
 
   if (tid == 0) {
     ptx::mbar_init(&bars[kFull0], 33);
     ptx::mbar_init(&bars[kFull1], 33);
-    ptx::mbar_init(&bars[kEmpty0], 257);
-    ptx::mbar_init(&bars[kEmpty1], 257);
+    ptx::mbar_init(&bars[kEmpty0], 9);
+    ptx::mbar_init(&bars[kEmpty1], 9);
     ptx::mbar_init(&bars[kPDone], 1);
-    ptx::mbar_init(&bars[kPFree], 64);
-    ptx::mbar_init(&bars[kPgReady], 64);
+    ptx::mbar_init(&bars[kPFree], 2);
+    ptx::mbar_init(&bars[kPgReady], 2);
     ptx::mbar_init(&bars[kD1Done], 1);
-    ptx::mbar_init(&bars[kD1Free], 128);
-    ptx::mbar_init(&bars[kWReady], 128);
+    ptx::mbar_init(&bars[kD1Free], 4);
+    ptx::mbar_init(&bars[kWReady], 4);
     ptx::mbar_init(&bars[kD2Done], 1);
-    ptx::mbar_init(&bars[kVdReady], 128);
+    ptx::mbar_init(&bars[kVdReady], 4);
     ptx::mbar_init(&bars[kSDone], 1);
-    ptx::mbar_init(&bars[kSbfReady], 256);
+    ptx::mbar_init(&bars[kSbfReady], 8);
     ptx::mbar_init(&bars[kD4Done], 1);
-    ptx::mbar_init(&bars[kD4Free], 128);
+    ptx::mbar_init(&bars[kD4Free], 4);
     ptx::mbar_init(&bars[kOFree], 1);
-    ptx::mbar_init(&bars[kOReady], 128);
+    ptx::mbar_init(&bars[kOReady], 4);
     ptx::fence_mbar_init();
   }
   if (warp == 8) {
@@ -146,6 +155,13 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   int* status = p.status;
   constexpr int kTimeout = kStatusBarrierTimeout;
 
+  // phase trace: leaders of CTA 0 stamp clock64() for chunks kTraceFirstChunk.. (off when p.trace is NULL)
+  const bool tracing = p.trace != nullptr && blockIdx.x == 0;
+  auto trace = [&](int role, int i, int ev) {
+    if (tracing && i >= kTraceFirstChunk && i < kTraceFirstChunk + kTraceChunks)
+      p.trace[(role * kTraceChunks + (i - kTraceFirstChunk)) * kTraceEvents + ev] = clock64();
+  };
+
   auto stage_ptr = [&](int s) { return smem + s * kStageBytes; };
   auto gates_of = [&](int s) { return reinterpret_cast<Gates*>(stage_ptr(s) + kStageGate); };
 
@@ -153,7 +169,7 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     // =========================================================== producer: TMA + gate vectors
     for (int i = 0; i < nproc; ++i) {
       const int s = i & 1, use = i >> 1;
-      if (use > 0 && !ptx::mbar_wait(&bars[kEmpty0 + s], (use - 1) & 1, status, kTimeout)) break;
+      if (use > 0 && !ptx::mbar_wait_warp(&bars[kEmpty0 + s], (use - 1) & 1, status, kTimeout)) break;
       const int chunk = first_chunk + i;
       const int t0 = seq_start + chunk * kChunk;
       const int valid = min(kChunk, seq_end - t0);
@@ -205,6 +221,7 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         const uint32_t kq = ptx::smem_u32(stage_ptr(s) + kStageKQ);
         const uint32_t aa = ptx::smem_u32(stage_ptr(s) + kStageA);
         if (!ptx::mbar_wait(&bars[kFull0 + s], (i >> 1) & 1, status, kTimeout)) break;
+        trace(0, i, 0);
         if (!kStateOnly) {
           // MMA0: D0 = [K;Q] K^T   (A = 128 rows, B = first 64 rows of the same tile)
           if (i > 0 && !ptx::mbar_wait(&bars[kPFree], prev, status, kTimeout)) break;
@@ -215,10 +232,12 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             ptx::mma_ss(tmem + kColD0, d, d, id_n64, ks > 0);
           }
           ptx::mma_commit(&bars[kPDone]);
+          trace(0, i, 1);
         }
         // MMA1: D1 = S0^T_bf16 * [K;Q]^T
         if (!ptx::mbar_wait(&bars[kSbfReady], ph, status, kTimeout)) break;
         if (!kStateOnly && i > 0 && !ptx::mbar_wait(&bars[kD1Free], prev, status, kTimeout)) break;
+        trace(0, i, 2);
         ptx::tc_fence_after_sync();
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
@@ -226,8 +245,10 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           ptx::mma_ts(tmem + kColD1, tmem + kColSbf + ks * 8, d, kStateOnly ? id_n64 : id_n128, ks > 0);
         }
         ptx::mma_commit(&bars[kD1Done]);
+        trace(0, i, 3);
         // MMA2: D2 = W^T A^T
         if (!ptx::mbar_wait(&bars[kWReady], ph, status, kTimeout)) break;
+        trace(0, i, 4);
         ptx::tc_fence_after_sync();
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks) {
@@ -235,8 +256,10 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           ptx::mma_ts(tmem + kColD2, tmem + kColD1 + ks * 8, d, id_n64, ks > 0);
         }
         ptx::mma_commit(&bars[kD2Done]);
+        trace(0, i, 5);
         // MMA3: S^T += V'^T K   (B = K tile read MN-major: 64-column halves are 16 KiB apart)
         if (!ptx::mbar_wait(&bars[kVdReady], ph, status, kTimeout)) break;
+        trace(0, i, 6);
         ptx::tc_fence_after_sync();
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks) {
@@ -244,6 +267,7 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           ptx::mma_ts(tmem + kColS, tmem + kColD2 + 32 + ks * 8, d, id_mn128, true);
         }
         ptx::mma_commit(&bars[kSDone]);
+        trace(0, i, 7);
         if (!kStateOnly) {
           // MMA4: D4 = Vd^T Pg^T
           if (!ptx::mbar_wait(&bars[kPgReady], ph, status, kTimeout)) break;
@@ -255,6 +279,7 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             ptx::mma_ts(tmem + kColD4, tmem + kColD2 + ks * 8, d, id_n64, ks > 0);
           }
           ptx::mma_commit(&bars[kD4Done]);
+          trace(0, i, 8);
         }
         ptx::mma_commit(&bars[kEmpty0 + s]);  // every MMA that reads this stage has completed
       }
@@ -272,7 +297,7 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     {
       float egl0 = 1.f;
       if (nproc > 0) {
-        alive = ptx::mbar_wait(&bars[kFull0], 0, status, kTimeout);
+        alive = ptx::mbar_wait_warp(&bars[kFull0], 0, status, kTimeout);
         egl0 = gates_of(0)->egl;
       }
       const float* h0p = nullptr;
@@ -308,7 +333,7 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       }
       ptx::tmem_wait_st();
       ptx::tc_fence_before_sync();
-      ptx::mbar_arrive(&bars[kSbfReady]);
+      warp_arrive(&bars[kSbfReady], lane);
     }
 
     float qs[64];  // side warpgroup: s * gamma_c * (Q S0)^T row, kept from D1 until the epilogue
@@ -318,14 +343,16 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       const int chunk = first_chunk + i;
       const int t0 = seq_start + chunk * kChunk;
       const Gates* gs = gates_of(s);
-      if (i > 0) alive = ptx::mbar_wait(&bars[kFull0 + s], (i >> 1) & 1, status, kTimeout);
+      if (i > 0) alive = ptx::mbar_wait_warp(&bars[kFull0 + s], (i >> 1) & 1, status, kTimeout);
       if (!alive) break;
+      if (tid == 128) trace(2, i, 0);
       const int valid = gs->valid;
 
       if (wg == 0) {
         // ---------------- chain: W = beta .* (V - gamma .* U)
-        if (!(alive = ptx::mbar_wait(&bars[kD1Done], ph, status, kTimeout))) break;
+        if (!(alive = ptx::mbar_wait_warp(&bars[kD1Done], ph, status, kTimeout))) break;
         ptx::tc_fence_after_sync();
+        if (tid == 0) trace(1, i, 0);
         const T* vt = reinterpret_cast<const T*>(stage_ptr(s) + kStageV);
 #pragma unroll
         for (int cb = 0; cb < 64; cb += 32) {
@@ -333,23 +360,31 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           ptx::tmem_ld32(tm + kColD1 + cb, u);
           ptx::tmem_wait_ld();
 #pragma unroll
-          for (int j = 0; j < 32; j += 2) {
+          for (int j = 0; j < 32; j += 4) {
             const int c = cb + j;
-            const float v0 = p.zero_v ? 0.f : Cvt<T>::to_f32(vt[c * kHeadDim + v]);
-            const float v1 = p.zero_v ? 0.f : Cvt<T>::to_f32(vt[(c + 1) * kHeadDim + v]);
-            const float w0 = gs->beta[c] * (v0 - gs->gamma[c] * __uint_as_float(u[j]));
-            const float w1 = gs->beta[c + 1] * (v1 - gs->gamma[c + 1] * __uint_as_float(u[j + 1]));
+            const float4 b4 = *reinterpret_cast<const float4*>(&gs->beta[c]);
+            const float4 g4 = *reinterpret_cast<const float4*>(&gs->gamma[c]);
+            float vv[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) vv[e] = p.zero_v ? 0.f : Cvt<T>::to_f32(vt[(c + e) * kHeadDim + v]);
+            const float w0 = b4.x * (vv[0] - g4.x * __uint_as_float(u[j]));
+            const float w1 = b4.y * (vv[1] - g4.y * __uint_as_float(u[j + 1]));
+            const float w2 = b4.z * (vv[2] - g4.z * __uint_as_float(u[j + 2]));
+            const float w3 = b4.w * (vv[3] - g4.w * __uint_as_float(u[j + 3]));
             w[j >> 1] = pack2<T>(w0, w1);
+            w[(j >> 1) + 1] = pack2<T>(w2, w3);
           }
           ptx::tmem_st16(tm + kColD1 + cb / 2, w);
         }
         ptx::tmem_wait_st();
         ptx::tc_fence_before_sync();
-        ptx::mbar_arrive(&bars[kWReady]);
+        warp_arrive(&bars[kWReady], lane);
+        if (tid == 0) trace(1, i, 1);
 
         // ---------------- chain: Vd, V' = rho .* Vd
-        if (!(alive = ptx::mbar_wait(&bars[kD2Done], ph, status, kTimeout))) break;
+        if (!(alive = ptx::mbar_wait_warp(&bars[kD2Done], ph, status, kTimeout))) break;
         ptx::tc_fence_after_sync();
+        if (tid == 0) trace(1, i, 2);
         T* vn = static_cast<T*>(p.v_new);
         {
           // both halves of Vd^T are read before the bf16 operands overwrite the same columns
@@ -357,29 +392,50 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           ptx::tmem_ld32(tm + kColD2, d0);
           ptx::tmem_ld32(tm + kColD2 + 32, d1);
           ptx::tmem_wait_ld();
+          if (tid == 0) trace(1, i, 6);
 #pragma unroll
-          for (int j = 0; j < 64; j += 2) {
-            const float a = __uint_as_float(j < 32 ? d0[j & 31] : d1[j & 31]);
-            const float b = __uint_as_float(j < 32 ? d0[(j + 1) & 31] : d1[(j + 1) & 31]);
-            vd[j >> 1] = pack2<T>(a, b);
-            vp[j >> 1] = pack2<T>(a * gs->rho[j], b * gs->rho[j + 1]);
-            if (vn != nullptr) {
-              if (j < valid) vn[(static_cast<int64_t>(t0 + j) * p.num_v_heads + hv) * kHeadDim + v] = Cvt<T>::from_f32(a);
-              if (j + 1 < valid) vn[(static_cast<int64_t>(t0 + j + 1) * p.num_v_heads + hv) * kHeadDim + v] = Cvt<T>::from_f32(b);
-            }
+          for (int j = 0; j < 32; j += 4) {
+            const float4 r0 = *reinterpret_cast<const float4*>(&gs->rho[j]);
+            const float4 r1 = *reinterpret_cast<const float4*>(&gs->rho[32 + j]);
+            const float a0 = __uint_as_float(d0[j]), a1 = __uint_as_float(d0[j + 1]);
+            const float a2 = __uint_as_float(d0[j + 2]), a3 = __uint_as_float(d0[j + 3]);
+            const float b0 = __uint_as_float(d1[j]), b1 = __uint_as_float(d1[j + 1]);
+            const float b2 = __uint_as_float(d1[j + 2]), b3 = __uint_as_float(d1[j + 3]);
+            vd[j >> 1] = pack2<T>(a0, a1);
+            vd[(j >> 1) + 1] = pack2<T>(a2, a3);
+            vd[16 + (j >> 1)] = pack2<T>(b0, b1);
+            vd[16 + (j >> 1) + 1] = pack2<T>(b2, b3);
+            vp[j >> 1] = pack2<T>(a0 * r0.x, a1 * r0.y);
+            vp[(j >> 1) + 1] = pack2<T>(a2 * r0.z, a3 * r0.w);
+            vp[16 + (j >> 1)] = pack2<T>(b0 * r1.x, b1 * r1.y);
+            vp[16 + (j >> 1) + 1] = pack2<T>(b2 * r1.z, b3 * r1.w);
           }
+          if (tid == 0) trace(1, i, 7);
           ptx::tmem_st32(tm + kColD2, vd);
           ptx::tmem_st32(tm + kColD2 + 32, vp);
+          if (tid == 0) trace(1, i, 8);
+          if (vn != nullptr) {
+            T* dst = vn + (static_cast<int64_t>(t0) * p.num_v_heads + hv) * kHeadDim + v;
+            const int64_t stride = static_cast<int64_t>(p.num_v_heads) * kHeadDim;
+            const T* vdt = reinterpret_cast<const T*>(vd);
+#pragma unroll
+            for (int j = 0; j < 64; ++j)
+              if (j < valid) dst[j * stride] = vdt[j];
+          }
         }
         ptx::tmem_wait_st();
+        if (tid == 0) trace(1, i, 9);
         ptx::tc_fence_before_sync();
-        ptx::mbar_arrive(&bars[kVdReady]);
+        warp_arrive(&bars[kVdReady], lane);
+        if (tid == 0) trace(1, i, 3);
       } else {
         // ---------------- side: Pg = s * G .* P  (P rows live in TMEM lanes 64..127 -> warps 6, 7)
         if (!kStateOnly) {
           if ((warp & 3) >= 2) {
-            if (!(alive = ptx::mbar_wait(&bars[kPDone], ph, status, kTimeout))) break;
+            if (tid == 192) trace(2, i, 8);
+            if (!(alive = ptx::mbar_wait_warp(&bars[kPDone], ph, status, kTimeout))) break;
             ptx::tc_fence_after_sync();
+            if (tid == 192) trace(2, i, 9);
             const int c = v - 64;
             const float gc = gs->g[c];
             uint8_t* pg = smem + kOffPg;
@@ -390,47 +446,63 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
               ptx::tmem_wait_ld();
               if (db == 32) {
                 ptx::tc_fence_before_sync();
-                ptx::mbar_arrive(&bars[kPFree]);
+                warp_arrive(&bars[kPFree], lane);
               }
+              // branch-free: every lane evaluates all 32 entries, the causal mask is a select
 #pragma unroll
               for (int j8 = 0; j8 < 32; j8 += 8) {
-                uint32_t w[4];
+                const float4 ga = *reinterpret_cast<const float4*>(&gs->g[db + j8]);
+                const float4 gb = *reinterpret_cast<const float4*>(&gs->g[db + j8 + 4]);
+                const float gd[8] = {ga.x, ga.y, ga.z, ga.w, gb.x, gb.y, gb.z, gb.w};
+                float x[8];
 #pragma unroll
-                for (int j = 0; j < 8; j += 2) {
-                  const int d0 = db + j8 + j;
-                  const float x0 = (d0 <= c) ? p.scale * __expf(gc - gs->g[d0]) * __uint_as_float(pr[j8 + j]) : 0.f;
-                  const float x1 = (d0 + 1 <= c) ? p.scale * __expf(gc - gs->g[d0 + 1]) * __uint_as_float(pr[j8 + j + 1]) : 0.f;
-                  w[j >> 1] = pack2<T>(x0, x1);
+                for (int j = 0; j < 8; ++j) {
+                  const float e = __expf(fminf(gc - gd[j], 0.f));
+                  const float val = p.scale * e * __uint_as_float(pr[j8 + j]);
+                  x[j] = (db + j8 + j <= c) ? val : 0.f;
                 }
-                *reinterpret_cast<uint4*>(pg + ptx::sw128_offset(c, (db + j8) >> 3)) = make_uint4(w[0], w[1], w[2], w[3]);
+                *reinterpret_cast<uint4*>(pg + ptx::sw128_offset(c, (db + j8) >> 3)) =
+                    make_uint4(pack2<T>(x[0], x[1]), pack2<T>(x[2], x[3]), pack2<T>(x[4], x[5]), pack2<T>(x[6], x[7]));
               }
             }
             ptx::fence_proxy_async_smem();
-            ptx::mbar_arrive(&bars[kPgReady]);
+            warp_arrive(&bars[kPgReady], lane);
+            if (tid == 192) trace(2, i, 10);
           }
           // ---------------- side: keep s * gamma_c * (Q S0)^T
-          if (!(alive = ptx::mbar_wait(&bars[kD1Done], ph, status, kTimeout))) break;
+          if (tid == 128) trace(2, i, 1);
+          if (!(alive = ptx::mbar_wait_warp(&bars[kD1Done], ph, status, kTimeout))) break;
           ptx::tc_fence_after_sync();
+          if (tid == 128) trace(2, i, 2);
 #pragma unroll
           for (int cb = 0; cb < 64; cb += 32) {
             uint32_t r[32];
             ptx::tmem_ld32(tm + kColD1 + 64 + cb, r);
             ptx::tmem_wait_ld();
 #pragma unroll
-            for (int j = 0; j < 32; ++j) qs[cb + j] = p.scale * gs->gamma[cb + j] * __uint_as_float(r[j]);
+            for (int j = 0; j < 32; j += 4) {
+              const float4 g4 = *reinterpret_cast<const float4*>(&gs->gamma[cb + j]);
+              qs[cb + j] = p.scale * g4.x * __uint_as_float(r[j]);
+              qs[cb + j + 1] = p.scale * g4.y * __uint_as_float(r[j + 1]);
+              qs[cb + j + 2] = p.scale * g4.z * __uint_as_float(r[j + 2]);
+              qs[cb + j + 3] = p.scale * g4.w * __uint_as_float(r[j + 3]);
+            }
           }
           ptx::tc_fence_before_sync();
-          ptx::mbar_arrive(&bars[kD1Free]);
+          warp_arrive(&bars[kD1Free], lane);
+          if (tid == 128) trace(2, i, 3);
         }
       }
 
       // ---------------- both: state convert after MMA3 (this warpgroup's 64 columns)
-      if (!(alive = ptx::mbar_wait(&bars[kSDone], ph, status, kTimeout))) break;
+      if (!(alive = ptx::mbar_wait_warp(&bars[kSDone], ph, status, kTimeout))) break;
       ptx::tc_fence_after_sync();
+      if (tid == 0) trace(1, i, 4);
+      if (tid == 128) trace(2, i, 4);
       const bool last = (i + 1 == nproc);
       float egl_next = 1.f;
       if (!last) {
-        if (!(alive = ptx::mbar_wait(&bars[kFull0 + (s ^ 1)], ((i + 1) >> 1) & 1, status, kTimeout))) break;
+        if (!(alive = ptx::mbar_wait_warp(&bars[kFull0 + (s ^ 1)], ((i + 1) >> 1) & 1, status, kTimeout))) break;
         egl_next = gates_of(s ^ 1)->egl;
       }
       T* hout = static_cast<T*>(p.h);
@@ -470,13 +542,17 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       if (!last) {
         ptx::tmem_wait_st();
         ptx::tc_fence_before_sync();
-        ptx::mbar_arrive(&bars[kSbfReady]);
+        warp_arrive(&bars[kSbfReady], lane);
+        if (tid == 0) trace(1, i, 5);
+        if (tid == 128) trace(2, i, 5);
+        if (tid == 192) trace(2, i, 13);
       }
 
       // ---------------- side: output epilogue
       if (!kStateOnly && wg == 1) {
-        if (!(alive = ptx::mbar_wait(&bars[kD4Done], ph, status, kTimeout))) break;
+        if (!(alive = ptx::mbar_wait_warp(&bars[kD4Done], ph, status, kTimeout))) break;
         ptx::tc_fence_after_sync();
+        if (tid == 128) trace(2, i, 6);
         T* so = reinterpret_cast<T*>(smem + kOffO);
         // The tile is reused every chunk: the previous chunk's TMA store must have finished reading it.
         // Only mbarriers (bounded waits) are used here, never a CTA or named barrier.
@@ -485,7 +561,7 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             ptx::tma_store_wait_read();
             ptx::mbar_arrive(&bars[kOFree]);
           }
-          if (!(alive = ptx::mbar_wait(&bars[kOFree], (i - 1) & 1, status, kTimeout))) break;
+          if (!(alive = ptx::mbar_wait_warp(&bars[kOFree], (i - 1) & 1, status, kTimeout))) break;
         }
 #pragma unroll
         for (int cb = 0; cb < 64; cb += 32) {
@@ -496,18 +572,19 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           for (int j = 0; j < 32; ++j) so[(cb + j) * kHeadDim + v] = Cvt<T>::from_f32(qs[cb + j] + __uint_as_float(r[j]));
         }
         ptx::tc_fence_before_sync();
-        ptx::mbar_arrive(&bars[kD4Free]);
+        warp_arrive(&bars[kD4Free], lane);
+        if (tid == 192) trace(2, i, 11);
+        if (tid == 128) trace(2, i, 12);
         ptx::fence_proxy_async_smem();
-        ptx::mbar_arrive(&bars[kOReady]);
+        warp_arrive(&bars[kOReady], lane);
+        if (!(alive = ptx::mbar_wait_warp(&bars[kOReady], ph, status, kTimeout))) break;
         if (valid == kChunk) {
           if (tid == 128) {
-            if (!(alive = ptx::mbar_wait(&bars[kOReady], ph, status, kTimeout))) break;
             ptx::tma_store_3d(&tm_o, so, 0, hv, t0);
             ptx::tma_store_commit();
           }
         } else {
           // ragged tail (always the last chunk of a sequence): row-masked 16-byte stores
-          if (!(alive = ptx::mbar_wait(&bars[kOReady], ph, status, kTimeout))) break;
           T* ob = static_cast<T*>(p.o);
           const int tl = tid - 128;  // 16 threads per row (8 elements each), 8 rows per pass
           for (int r0 = 0; r0 < valid; r0 += 8) {
@@ -519,7 +596,8 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           }
         }
       }
-      ptx::mbar_arrive(&bars[kEmpty0 + s]);  // this thread no longer reads stage s
+      if (tid == 128) trace(2, i, 7);
+      warp_arrive(&bars[kEmpty0 + s], lane);  // this warp no longer reads stage s
     }
     if (!kStateOnly && tid == 128) ptx::tma_store_wait_all();
     // h[first chunk] = initial state

@@ -1,0 +1,95 @@
+// Intra-card context parallelism for the chunked forward: a long sequence is cut into segments that
+// run as independent CTAs; each non-final segment first produces the state it hands to its successor.
+// Reference: flash_qla/ops/gated_delta_rule/chunk/cp_context.py:117-176 (orchestration),
+// chunk/hopper/cp_fwd.py:7-63 (warm-up lengths) and :102-250 (chaining of the initial states).
+//
+//   plan  : per (segment, head) walk the chunk-end gates backwards from the segment end until the
+//           accumulated log decay drops below `threshold`; that many trailing chunks, started from a
+//           zero state, reproduce the segment-end state to exp(threshold).  If the whole segment does
+//           not decay that far the (segment, head) is a "fallback": all chunks are run and the exact
+//           K x K transition matrix M of the segment is needed as well.
+//   chain : for fallback entries  h0[seg + 1] += M[seg] * h0[seg], in segment order.
+#include "chunk_params.cuh"
+
+namespace qla {
+namespace {
+
+__global__ void cp_plan_kernel(const float* __restrict__ g_cumsum, const int32_t* __restrict__ cu,
+                               const int32_t* __restrict__ seg_next, int num_heads, float threshold,
+                               int32_t* __restrict__ warm_limit, int32_t* __restrict__ m_limit) {
+  const int seg = blockIdx.x;
+  const int h = threadIdx.x;
+  if (h >= num_heads) return;
+  const int start = cu[seg], end = cu[seg + 1];
+  const int nchunks = (end - start + kChunk - 1) / kChunk;
+  int warm = 0, ml = 0;
+  if (seg_next[seg] >= 0 && nchunks > 0) {
+    float acc = 0.f;
+    bool reached = false;
+    for (int c = nchunks - 1; c >= 0; --c) {
+      const int last = min(end, start + (c + 1) * kChunk) - 1;
+      acc += g_cumsum[static_cast<int64_t>(last) * num_heads + h];
+      ++warm;
+      if (acc < threshold) { reached = true; break; }
+    }
+    if (!reached) ml = nchunks;  // warm == nchunks here
+  }
+  warm_limit[seg * num_heads + h] = warm;
+  m_limit[seg * num_heads + h] = ml;
+}
+
+// One CTA: one (raw sequence, head, 32-column slab of the state).  Thread t owns row k = t of the slab.
+__global__ void __launch_bounds__(128) cp_chain_kernel(float* __restrict__ h0, const float* __restrict__ M,
+                                                       const int32_t* __restrict__ m_limit,
+                                                       const int32_t* __restrict__ raw_first_seg, int num_heads) {
+  const int vt = blockIdx.x, h = blockIdx.y, r = blockIdx.z;
+  const int s0 = raw_first_seg[r], s1 = raw_first_seg[r + 1];
+  const int k = threadIdx.x;
+  __shared__ float sh[kHeadDim][33];
+  for (int seg = s0; seg + 1 < s1; ++seg) {
+    if (m_limit[seg * num_heads + h] == 0) continue;  // uniform across the CTA
+    const float* src = h0 + (static_cast<int64_t>(seg) * num_heads + h) * kHeadDim * kHeadDim + vt * 32;
+    float* dst = h0 + (static_cast<int64_t>(seg + 1) * num_heads + h) * kHeadDim * kHeadDim + vt * 32;
+    const float* m = M + (static_cast<int64_t>(seg) * num_heads + h) * kHeadDim * kHeadDim;
+    __syncthreads();
+    for (int i = threadIdx.x; i < kHeadDim * 32; i += 128) sh[i >> 5][i & 31] = src[(i >> 5) * kHeadDim + (i & 31)];
+    __syncthreads();
+    float acc[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) acc[j] = 0.f;
+    for (int j = 0; j < kHeadDim; ++j) {
+      const float mk = m[k * kHeadDim + j];
+#pragma unroll
+      for (int c = 0; c < 32; ++c) acc[c] = fmaf(mk, sh[j][c], acc[c]);
+    }
+#pragma unroll
+    for (int c = 0; c < 32; ++c) dst[k * kHeadDim + c] += acc[c];
+    __threadfence();  // the next iteration of THIS CTA reads dst (same slab, same CTA): ordering only
+  }
+}
+
+}  // namespace
+}  // namespace qla
+
+extern "C" QLA_API int qla_cp_plan(const QlaCpPlanArgs* a, void* stream) {
+  using namespace qla;
+  QLA_CHECK_ARG(a != nullptr && a->g_cumsum && a->cu_seqlens && a->seg_next && a->warm_limit && a->m_limit,
+                "NULL pointer in QlaCpPlanArgs");
+  QLA_CHECK_ARG(a->num_segments > 0 && a->num_v_heads > 0 && a->num_v_heads <= 1024, "bad sizes");
+  const int threads = ((a->num_v_heads + 31) / 32) * 32;
+  cp_plan_kernel<<<a->num_segments, threads, 0, static_cast<cudaStream_t>(stream)>>>(
+      a->g_cumsum, a->cu_seqlens, a->seg_next, a->num_v_heads, a->threshold, a->warm_limit, a->m_limit);
+  QLA_CHECK_CUDA(cudaGetLastError());
+  return QLA_OK;
+}
+
+extern "C" QLA_API int qla_cp_chain(const QlaCpChainArgs* a, void* stream) {
+  using namespace qla;
+  QLA_CHECK_ARG(a != nullptr && a->h0 && a->M && a->m_limit && a->raw_first_seg, "NULL pointer in QlaCpChainArgs");
+  QLA_CHECK_ARG(a->num_raw_seqs > 0 && a->num_v_heads > 0, "bad sizes");
+  dim3 grid(kHeadDim / 32, a->num_v_heads, a->num_raw_seqs);
+  cp_chain_kernel<<<grid, 128, 0, static_cast<cudaStream_t>(stream)>>>(a->h0, a->M, a->m_limit, a->raw_first_seg,
+                                                                       a->num_v_heads);
+  QLA_CHECK_CUDA(cudaGetLastError());
+  return QLA_OK;
+}

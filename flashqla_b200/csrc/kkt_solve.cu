@@ -72,9 +72,9 @@ __global__ void __launch_bounds__(128) kkt_solve_kernel(const __grid_constant__ 
   const int tok0 = seq_start + local_pair * 128;
 
   extern __shared__ __align__(1024) uint8_t smem_raw[];
-  uint8_t* sK = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sK = smem_raw + ((1024u - (ptx::smem_u32(smem_raw) & 1023u)) & 1023u);
   float* sL = reinterpret_cast<float*>(sK + 32768);  // [2][64][kLStride]
-  __shared__ float s_g[128];
+  __shared__ __align__(16) float s_g[128];
   __shared__ float s_part[4];
   __shared__ uint64_t bar_tma, bar_mma;
   __shared__ uint32_t tmem_base_s;
@@ -156,13 +156,19 @@ __global__ void __launch_bounds__(128) kkt_solve_kernel(const __grid_constant__ 
 
     // L[c][d] = beta_c * exp(g_c - g_d) * (k_c . k_d) for d < c
     const float* gch = s_g + ci * 64;
+    // branch-free (the causal mask is a select): a data-dependent branch per entry would diverge
 #pragma unroll
     for (int d4 = 0; d4 < 64; d4 += 4) {
+      const float4 g4 = *reinterpret_cast<const float4*>(gch + d4);
       float4 l;
-      l.x = (d4 + 0 < c) ? bv * __expf(gcs - gch[d4 + 0]) * kk[d4 + 0] : 0.f;
-      l.y = (d4 + 1 < c) ? bv * __expf(gcs - gch[d4 + 1]) * kk[d4 + 1] : 0.f;
-      l.z = (d4 + 2 < c) ? bv * __expf(gcs - gch[d4 + 2]) * kk[d4 + 2] : 0.f;
-      l.w = (d4 + 3 < c) ? bv * __expf(gcs - gch[d4 + 3]) * kk[d4 + 3] : 0.f;
+      l.x = bv * __expf(fminf(gcs - g4.x, 0.f)) * kk[d4 + 0];
+      l.y = bv * __expf(fminf(gcs - g4.y, 0.f)) * kk[d4 + 1];
+      l.z = bv * __expf(fminf(gcs - g4.z, 0.f)) * kk[d4 + 2];
+      l.w = bv * __expf(fminf(gcs - g4.w, 0.f)) * kk[d4 + 3];
+      l.x = (d4 + 0 < c) ? l.x : 0.f;
+      l.y = (d4 + 1 < c) ? l.y : 0.f;
+      l.z = (d4 + 2 < c) ? l.z : 0.f;
+      l.w = (d4 + 3 < c) ? l.w : 0.f;
       *reinterpret_cast<float4*>(Lc + c * kLStride + d4) = l;
     }
     __syncthreads();

@@ -70,6 +70,12 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* s
   return false;
 }
 
+// Same wait executed by a converged warp; the verdict is made warp-uniform so that no lane leaves a
+// loop alone (later __syncwarp / .sync.aligned instructions need the whole warp).
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, int* status, int code) {
+  return __all_sync(0xffffffffu, mbar_wait(bar, parity, status, code)) != 0;
+}
+
 // ------------------------------------------------------------------------------ fences
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");

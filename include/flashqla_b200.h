@@ -101,8 +101,9 @@ enum { /* flags of QlaChunkFwdArgs / QlaChunkBwdArgs */
   QLA_CHUNK_QK_L2NORM = 4,       /* normalise q and k rows inside the kernels (reserved)    */
   QLA_CHUNK_SKIP_PREPARE = 8,    /* g_cumsum and A are inputs (computed by an earlier call) */
   QLA_CHUNK_INIT_IDENTITY = 16,  /* start every sequence from S = I instead of h0          */
-  QLA_CHUNK_ZERO_V = 32          /* treat v as zero (with INIT_IDENTITY: the K x K transition
+  QLA_CHUNK_ZERO_V = 32,         /* treat v as zero (with INIT_IDENTITY: the K x K transition
                                     matrix of the chunks, used by context parallelism)      */
+  QLA_CHUNK_PREPARE_ONLY = 64    /* compute g_cumsum and A only; no scan                     */
 };
 
 /*
@@ -153,6 +154,56 @@ typedef struct QlaChunkFwdArgs {
 
 QLA_API size_t qla_chunk_fwd_workspace_bytes(const QlaChunkFwdArgs* args);
 QLA_API int qla_chunk_fwd(const QlaChunkFwdArgs* args, void* stream);
+
+/*
+ * Intra-card context parallelism (long sequences, few heads): helpers around qla_chunk_fwd.
+ * Replaces intra_card_cp_preprocess, flash_qla/ops/gated_delta_rule/chunk/cp_context.py:117-176
+ * (get_warmup_chunks chunk/hopper/cp_fwd.py:66, correct_initial_states chunk/hopper/cp_fwd.py:253;
+ * the segment-end states come from qla_chunk_fwd with QLA_CHUNK_STATE_ONLY and chunk_limit).
+ *
+ * qla_cp_plan: for every (segment, head) the number of trailing chunks whose accumulated log decay
+ * first drops below `threshold` (warm_limit), or - when the segment never decays that far - all its
+ * chunks, in which case m_limit holds the same count (0 otherwise) and the K x K transition matrix of
+ * the segment is required.  seg_next[s] = index of the segment that continues segment s, < 0 if s ends
+ * its sequence (then both limits are 0).
+ */
+typedef struct QlaCpPlanArgs {
+  int32_t num_segments;
+  int32_t num_v_heads;
+  float threshold;            /* e.g. -10: contributions below exp(-10) are dropped            */
+  const float* g_cumsum;      /* [NT, Hv] chunk-local cumulative gates                          */
+  const int32_t* cu_seqlens;  /* [num_segments + 1] segment boundaries (multiples of 64 inside a sequence) */
+  const int32_t* seg_next;    /* [num_segments]                                                 */
+  int32_t* warm_limit;        /* out [num_segments, Hv]                                         */
+  int32_t* m_limit;           /* out [num_segments, Hv]                                         */
+} QlaCpPlanArgs;
+
+QLA_API int qla_cp_plan(const QlaCpPlanArgs* args, void* stream);
+
+/*
+ * qla_cp_chain: h0[seg + 1] += M[seg] * h0[seg] for every (segment, head) with m_limit != 0, walking
+ * the segments of each original sequence in order.  h0 and M are fp32 [num_segments, Hv, 128, 128]
+ * ([K, V] and [K, K]); raw_first_seg [num_raw_seqs + 1] gives the first segment of every original
+ * sequence.
+ */
+typedef struct QlaCpChainArgs {
+  int32_t num_raw_seqs;
+  int32_t num_v_heads;
+  float* h0;
+  const float* M;
+  const int32_t* m_limit;
+  const int32_t* raw_first_seg;
+} QlaCpChainArgs;
+
+QLA_API int qla_cp_chain(const QlaCpChainArgs* args, void* stream);
+
+/*
+ * Tracing (no counterpart in the reference, whose profiling is torch.profiler around whole kernels,
+ * flash_qla/utils/profiler.py:8-25): when a device buffer of at least 192 int64 is registered, CTA 0 of
+ * every later chunk-scan launch stamps clock64() at its phase boundaries for chunks 4..7, laid out as
+ * [role: 0 MMA issuer, 1 chain warpgroup, 2 side warpgroup][chunk][16 events].  NULL switches it off.
+ */
+QLA_API int qla_set_trace_buffer(long long* device_buffer, size_t count);
 
 QLA_API const char* qla_status_string(int code);
 QLA_API const char* qla_last_error(void);

@@ -139,3 +139,47 @@ def test_api_errors(fq):
         fq.chunk_gated_delta_rule_fwd(q, q, v, gb, gb, initial_state=torch.zeros(3, 4, 128, 128, device="cuda"))
     with pytest.raises(AssertionError):
         fq.chunk_gated_delta_rule_fwd(q.float(), q.float(), v.float(), gb, gb)
+
+
+# ----------------------------------------------------------------------------- context parallelism
+def test_cp_plan_is_used_for_long_sequences(fq):
+    from flashqla_b200 import cp
+    plan = cp.plan_segments([32768], 32, 148)
+    assert plan.use_cp and plan.seg_chunks >= cp.MIN_SEG_CHUNKS
+    assert plan.cu[-1] == 32768 and all((b - a) % 64 == 0 for a, b in zip(plan.cu[:-2], plan.cu[1:-1]))
+    assert not cp.plan_segments([4096] * 64, 8, 148).use_cp   # enough chains already
+
+
+@pytest.mark.parametrize("gate_div,zero_gate", [(1.0, 0.0), (16.0, 0.25)])
+def test_cp_matches_oracle(fq, gate_div, zero_gate):
+    """One long sequence, few heads: segments + warm-up; with g/16 and zero-gate heads the transition
+    matrix fallback is exercised (the reference's SWA heads, tests/test_gdr.py:108-112)."""
+    T = 4096 + 37
+    inp = orc.make_prefill_inputs(1, T, 2, 4, seed=21, with_h0=True, gate_div=gate_div, zero_gate_heads=zero_gate)
+    c = _cuda(inp)
+    from flashqla_b200 import cp
+    assert cp.get_plan([T], 4, c["q"].device).use_cp
+    g_cs, A, o, h, fs = fq.chunk_gated_delta_rule_fwd(c["q"], c["k"], c["v"], c["g"], c["beta"],
+                                                      initial_state=c["h0"], output_h=True)
+    _, _, o1, h1, fs1 = fq.chunk_gated_delta_rule_fwd(c["q"], c["k"], c["v"], c["g"], c["beta"],
+                                                      initial_state=c["h0"], output_h=True, auto_cp=False)
+    fq.check_device_status()
+    ref = orc.chunk_gdr_fwd(inp["q"], inp["k"], inp["v"], inp["g"], inp["beta"], h0=inp["h0"])
+    for name, got, key in (("o", o, "o"), ("final_state", fs, "final_state"), ("h", h, "h"),
+                           ("o without cp", o1, "o"), ("final_state without cp", fs1, "final_state")):
+        _check(name, got, ref[key])
+
+
+def test_cp_varlen_mixed_lengths(fq):
+    lens = [3000, 100, 2077]
+    cu = torch.tensor([0, 3000, 3100, 5177], dtype=torch.int32)
+    inp = orc.make_prefill_inputs(1, 5177, 1, 2, seed=22, with_h0=True, n_states=3, gate_div=4.0)
+    c = _cuda(inp)
+    from flashqla_b200 import cp
+    assert cp.get_plan(lens, 2, c["q"].device).use_cp
+    _, _, o, _, fs = fq.chunk_gated_delta_rule_fwd(c["q"], c["k"], c["v"], c["g"], c["beta"],
+                                                   initial_state=c["h0"], cu_seqlens=cu.cuda())
+    fq.check_device_status()
+    ref = orc.chunk_gdr_fwd_varlen(inp["q"], inp["k"], inp["v"], inp["g"], inp["beta"], cu, h0=inp["h0"])
+    _check("o", o, ref["o"])
+    _check("final_state", fs, ref["final_state"])
