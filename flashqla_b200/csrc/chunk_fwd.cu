@@ -12,17 +12,18 @@
 // Everything is computed TRANSPOSED so that each tcgen05.mma has M = 128 (the V dimension on the 128
 // TMEM lanes) and every dependent operand can stay in tensor memory:
 //   MMA0  D0[128,64]  = [K;Q] K^T          (SS)  rows 64..127 are P = Q K^T; state independent
+//   MMAu  D2[128,64]  = V^T Ab^T           (SS)  Ab = A diag(beta); state independent part of Vd^T
 //   MMA1  D1[128,128] = S0^T_bf16 [K;Q]^T  (TS)  columns 0..63 = U^T, 64..127 = (Q S0)^T
-//   MMA2  D2[128,64]  = W^T A^T            (TS)  = Vd^T
+//   MMA2  D2[128,64] += W^T Ab^T           (TS)  W = -exp(g) .* U, so D2 = Vd^T = (Ab (V - exp(g) .* U))^T
 //   MMA3  S^T[128,128] += V'^T K           (TS, B operand MN-major straight from the K tile)
-//   MMA4  D4[128,64]  = Vd^T Pg^T          (TS)  Pg = s G .* P written to a swizzled smem tile
+//   MMA4  D4[128,64]  = Vd^T Pg^T          (SS)  Pg = s G .* P and Vd^T are swizzled smem tiles; off the chain
 // Thread v of a compute warpgroup owns TMEM lane v = column v of the state: it reads U^T/Vd^T rows
 // with tcgen05.ld, applies the gates, and writes the bf16 operand of the next MMA back with
 // tcgen05.st.  The fp32 state never leaves tensor memory between chunks.
 //
-// Warp roles (320 threads): warps 0-3 "chain" (W, Vd, state convert, columns 0..63), warps 4-7 "side"
-// (Pg, output epilogue, state convert of columns 64..127), warp 8 TMA producer + gate vectors, warp 9
-// MMA issuer.  Two smem stages of {K,Q,V,A,gates}; all waits are bounded mbarrier waits that raise a
+// Warp roles (384 threads): warps 0-3 "chain" (W, Vd, state convert of columns 0..63), warps 4-7 "side"
+// (output epilogue, state convert of columns 64..127), warp 8 TMA producer + gate vectors, warp 9 MMA
+// issuer, warps 10-11 "aux" (operand tiles A diag(beta) and Pg).  Two smem stages of {K,Q,V,A,gates}; all waits are bounded mbarrier waits that raise a
 // status word instead of hanging.
 #include "chunk_params.cuh"
 
@@ -35,19 +36,20 @@ namespace {
 constexpr uint32_t kColS = 0;      // fp32 state S^T, 128 columns
 constexpr uint32_t kColSbf = 128;  // bf16 copy of S^T (A operand of MMA1), 64 columns
 constexpr uint32_t kColD1 = 192;   // U^T (192..255, overwritten by W bf16 at 192..223) | (Q S)^T (256..319)
-constexpr uint32_t kColD2 = 320;   // Vd^T; overwritten by Vd bf16 (320..351) and V' bf16 (352..383)
+constexpr uint32_t kColD2 = 320;   // Vd^T; columns 352..383 are overwritten by V' bf16 (A operand of MMA3)
 constexpr uint32_t kColD4 = 384;   // Vd^T Pg^T
 constexpr uint32_t kColD0 = 448;   // [K;Q] K^T
 
 // ---- shared-memory map (offsets from a 1024-byte aligned base)
 constexpr uint32_t kStageKQ = 0;         // 32 KiB: half 0 [K rows | Q rows] (16 KiB), half 1 (16 KiB); SW128
-constexpr uint32_t kStageV = 32768;      // 16 KiB: V tile [64][128], no swizzle
-constexpr uint32_t kStageA = 49152;      // 8 KiB: A tile [64][64], SW128
+constexpr uint32_t kStageV = 32768;      // 16 KiB: V tile as two [64][64] halves (columns 0..63 | 64..127), SW128
+constexpr uint32_t kStageA = 49152;      // 8 KiB: A tile [64][64], SW128; scaled in place to A diag(beta)
 constexpr uint32_t kStageGate = 57344;   // 1 KiB + : g[64], gamma[64], rho[64], beta[64], egl
 constexpr uint32_t kStageBytes = 59392;  // 58 KiB, multiple of 1024
 constexpr uint32_t kOffPg = 2 * kStageBytes;         // 8 KiB Pg tile, SW128
-constexpr uint32_t kOffO = kOffPg + 8192;            // 16 KiB output tile [64][128]
-constexpr uint32_t kSmemBytes = kOffO + 16384 + 1024;
+constexpr uint32_t kOffO = kOffPg + 8192;            // 2 x 16 KiB output tiles [64][128]
+constexpr uint32_t kOffVd = kOffO + 2 * 16384;       // 2 x 16 KiB Vd^T tiles [128 v][64 d], SW128 (A of MMA4)
+constexpr uint32_t kSmemBytes = kOffVd + 2 * 16384 + 1024;
 
 struct Gates {
   float g[64];
@@ -60,11 +62,11 @@ struct Gates {
 
 enum Bar {
   kFull0 = 0, kFull1, kEmpty0, kEmpty1,
-  kPDone, kPFree, kPgReady, kD1Done, kD1Free, kWReady, kD2Done, kVdReady, kSDone, kSbfReady, kD4Done, kD4Free, kOFree, kOReady,
+  kPDone, kPFree, kPgReady, kD1Done, kD1Free, kWReady, kD2Done, kVdReady, kSDone, kSbfReady, kSScaled, kAbReady0, kAbReady1, kD4Done, kD4Free, kOFree, kOReady,
   kNumBars
 };
 
-constexpr int kThreads = 320;
+constexpr int kThreads = 384;
 
 // One arrival per warp: every lane has finished (and fenced) its own writes, the warp converges, and
 // lane 0 signals the barrier.
@@ -122,12 +124,13 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   uint8_t* smem = smem_raw + ((1024u - (ptx::smem_u32(smem_raw) & 1023u)) & 1023u);
   __shared__ uint64_t bars[kNumBars];
   __shared__ uint32_t tmem_base_s;
+  __shared__ __align__(16) float aux_g[2 * 2 * 64];  // [aux warp][chunk parity][64] cumulative gates
 
   if (tid == 0) {
     ptx::mbar_init(&bars[kFull0], 33);
     ptx::mbar_init(&bars[kFull1], 33);
-    ptx::mbar_init(&bars[kEmpty0], 9);
-    ptx::mbar_init(&bars[kEmpty1], 9);
+    ptx::mbar_init(&bars[kEmpty0], 11);
+    ptx::mbar_init(&bars[kEmpty1], 11);
     ptx::mbar_init(&bars[kPDone], 1);
     ptx::mbar_init(&bars[kPFree], 2);
     ptx::mbar_init(&bars[kPgReady], 2);
@@ -138,6 +141,9 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     ptx::mbar_init(&bars[kVdReady], 4);
     ptx::mbar_init(&bars[kSDone], 1);
     ptx::mbar_init(&bars[kSbfReady], 8);
+    ptx::mbar_init(&bars[kSScaled], 8);
+    ptx::mbar_init(&bars[kAbReady0], 2);
+    ptx::mbar_init(&bars[kAbReady1], 2);
     ptx::mbar_init(&bars[kD4Done], 1);
     ptx::mbar_init(&bars[kD4Free], 4);
     ptx::mbar_init(&bars[kOFree], 1);
@@ -167,14 +173,50 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 
   if (warp == 8) {
     // =========================================================== producer: TMA + gate vectors
+    // L2 prefetch runs kPrefetchAhead chunks ahead of the demand loads: with every SM streaming its own
+    // sequence the DRAM latency of a tile exceeds one chunk period, and only two stages fit in shared
+    // memory, so the tiles are pulled into L2 early and the demand TMA then hits L2.
+    constexpr int kPrefetchAhead = 4;
+    auto prefetch_chunk = [&](int j) {
+      const int pt0 = seq_start + (first_chunk + j) * kChunk;
+      ptx::tma_prefetch_l2_3d(&tm_k, 0, hk, pt0);
+      ptx::tma_prefetch_l2_3d(&tm_k, 64, hk, pt0);
+      if (!kStateOnly) {
+        ptx::tma_prefetch_l2_3d(&tm_q, 0, hk, pt0);
+        ptx::tma_prefetch_l2_3d(&tm_q, 64, hk, pt0);
+      }
+      if (!p.zero_v) {
+        ptx::tma_prefetch_l2_3d(&tm_v, 0, hv, pt0);
+        ptx::tma_prefetch_l2_3d(&tm_v, 64, hv, pt0);
+      }
+      ptx::tma_prefetch_l2_3d(&tm_a, 0, hv, pt0);
+    };
+    if (lane == 0)
+      for (int j = 2; j < kPrefetchAhead && j < nproc; ++j) prefetch_chunk(j);
     for (int i = 0; i < nproc; ++i) {
       const int s = i & 1, use = i >> 1;
-      if (use > 0 && !ptx::mbar_wait_warp(&bars[kEmpty0 + s], (use - 1) & 1, status, kTimeout)) break;
+      if (lane == 0) trace(0, i, 9);
       const int chunk = first_chunk + i;
       const int t0 = seq_start + chunk * kChunk;
       const int valid = min(kChunk, seq_end - t0);
+      // gate values are fetched into registers BEFORE waiting for the stage, so their global-memory
+      // latency overlaps the wait
+      const int64_t last_tok = static_cast<int64_t>(t0) + valid - 1;
+      const float gl = p.g_cumsum[last_tok * p.num_v_heads + hv];
+      float gcv[2], bcv[2];
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        const int c = lane + 32 * r;
+        const bool okc = c < valid;
+        const int64_t tok = static_cast<int64_t>(t0) + c;
+        gcv[r] = okc ? p.g_cumsum[tok * p.num_v_heads + hv] : gl;
+        bcv[r] = okc ? load_scalar(p.beta, p.beta_dtype, tok * p.num_v_heads + hv) : 0.f;
+      }
+      if (use > 0 && !ptx::mbar_wait_warp(&bars[kEmpty0 + s], (use - 1) & 1, status, kTimeout)) break;
+      if (lane == 0) trace(0, i, 10);
       uint8_t* st = stage_ptr(s);
       if (lane == 0) {
+        if (i + kPrefetchAhead < nproc) prefetch_chunk(i + kPrefetchAhead);
         uint32_t bytes = 16384 + 8192;  // K + A
         if (!kStateOnly) bytes += 16384;  // Q
         if (!p.zero_v) bytes += 16384;    // V
@@ -185,19 +227,18 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           ptx::tma_load_3d(st + kStageKQ + 8192, &tm_q, &bars[kFull0 + s], 0, hk, t0);
           ptx::tma_load_3d(st + kStageKQ + 16384 + 8192, &tm_q, &bars[kFull0 + s], 64, hk, t0);
         }
-        if (!p.zero_v) ptx::tma_load_3d(st + kStageV, &tm_v, &bars[kFull0 + s], 0, hv, t0);
+        if (!p.zero_v) {
+          ptx::tma_load_3d(st + kStageV, &tm_v, &bars[kFull0 + s], 0, hv, t0);
+          ptx::tma_load_3d(st + kStageV + 8192, &tm_v, &bars[kFull0 + s], 64, hv, t0);
+        }
         ptx::tma_load_3d(st + kStageA, &tm_a, &bars[kFull0 + s], 0, hv, t0);
       }
       Gates* gs = gates_of(s);
-      const int64_t last_tok = static_cast<int64_t>(t0) + valid - 1;
-      const float gl = p.g_cumsum[last_tok * p.num_v_heads + hv];
 #pragma unroll
       for (int r = 0; r < 2; ++r) {
         const int c = lane + 32 * r;
         const bool ok = c < valid;
-        const int64_t tok = static_cast<int64_t>(t0) + c;
-        const float gc = ok ? p.g_cumsum[tok * p.num_v_heads + hv] : gl;
-        const float bc = ok ? load_scalar(p.beta, p.beta_dtype, tok * p.num_v_heads + hv) : 0.f;
+        const float gc = gcv[r], bc = bcv[r];
         gs->g[c] = gc;
         gs->gamma[c] = __expf(gc);
         gs->rho[c] = ok ? __expf(gl - gc) : 0.f;
@@ -208,6 +249,7 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         gs->valid = valid;
       }
       ptx::mbar_arrive(&bars[kFull0 + s]);  // 32 arrivals + the expect_tx arrival of lane 0
+      if (lane == 0) trace(0, i, 11);
     }
   } else if (warp == 9) {
     // =========================================================== MMA issuer (one thread)
@@ -215,73 +257,198 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       const uint32_t id_n128 = ptx::mma_idesc(128, 128, fmt, ptx::kMajorK, ptx::kMajorK);
       const uint32_t id_n64 = ptx::mma_idesc(128, 64, fmt, ptx::kMajorK, ptx::kMajorK);
       const uint32_t id_mn128 = ptx::mma_idesc(128, 128, fmt, ptx::kMajorK, ptx::kMajorMN);
-      const uint32_t pg_addr = ptx::smem_u32(smem + kOffPg);
-      for (int i = 0; i < nproc; ++i) {
+      const uint32_t id_u = ptx::mma_idesc(128, 64, fmt, ptx::kMajorMN, ptx::kMajorK);
+      // Descriptors are built once; inside the loop an operand step is one 64-bit add of
+      // (byte offset >> 4) so that the single issuing thread spends its cycles on tcgen05.mma only.
+      uint64_t d_kq[2], d_kmn[2], d_a[2], d_v[2];
+#pragma unroll
+      for (int s = 0; s < 2; ++s) {
+        d_kq[s] = ptx::smem_desc_sw128(ptx::smem_u32(stage_ptr(s) + kStageKQ), 16, 1024);      // K-major rows
+        d_kmn[s] = ptx::smem_desc_sw128(ptx::smem_u32(stage_ptr(s) + kStageKQ), 16384, 1024);  // K tile, MN-major
+        d_a[s] = ptx::smem_desc_sw128(ptx::smem_u32(stage_ptr(s) + kStageA), 16, 1024);
+        d_v[s] = ptx::smem_desc_sw128(ptx::smem_u32(stage_ptr(s) + kStageV), 8192, 1024);      // V tile, MN-major
+      }
+      const uint64_t d_pg = ptx::smem_desc_sw128(ptx::smem_u32(smem + kOffPg), 16, 1024);
+      // Issue order (software pipelined): the state-dependent MMAs 1 -> 2 -> 3 of a chunk are separated
+      // by ALU phases of the chain warpgroup; the state-independent ones (MMA4 of the previous chunk,
+      // MMAu and MMA0 of this chunk) are issued into those gaps so the tensor pipe executes them while the
+      // chain computes, and MMA1 of the next chunk is never queued behind them.
+      const uint64_t d_vd0 = ptx::smem_desc_sw128(ptx::smem_u32(smem + kOffVd), 16, 1024);
+      const uint64_t d_vd1 = ptx::smem_desc_sw128(ptx::smem_u32(smem + kOffVd + 16384), 16, 1024);
+      // MMA4 of chunk j: D4 = Vd^T Pg^T, both operands from shared memory (Vd tile j & 1)
+      auto issue_mma4 = [&](int j) {
+        const uint64_t dv = (j & 1) ? d_vd1 : d_vd0;
+        ptx::tc_fence_after_sync();
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks)
+          ptx::mma_ss(tmem + kColD4, dv + ks * (32 >> 4), d_pg + ks * (32 >> 4), id_n64, ks > 0);
+        ptx::mma_commit(&bars[kD4Done]);
+      };
+      bool ok = true;
+      for (int i = 0; ok && i < nproc; ++i) {
         const int s = i & 1, ph = i & 1, prev = (i - 1) & 1;
-        const uint32_t kq = ptx::smem_u32(stage_ptr(s) + kStageKQ);
-        const uint32_t aa = ptx::smem_u32(stage_ptr(s) + kStageA);
-        if (!ptx::mbar_wait(&bars[kFull0 + s], (i >> 1) & 1, status, kTimeout)) break;
+        // selects instead of dynamic indexing keep the descriptors in registers
+        const uint64_t kq = s ? d_kq[1] : d_kq[0], kmn = s ? d_kmn[1] : d_kmn[0];
+        const uint64_t aa = s ? d_a[1] : d_a[0], vv = s ? d_v[1] : d_v[0];
+        if (!(ok = ptx::mbar_spin(&bars[kFull0 + s], (i >> 1) & 1, status, kTimeout))) break;
         trace(0, i, 0);
+        // MMA1: D1 = S0^T_bf16 * [K;Q]^T
+        if (!(ok = ptx::mbar_spin(&bars[kSbfReady], ph, status, kTimeout))) break;
+        if (!kStateOnly && i > 0 && !(ok = ptx::mbar_spin(&bars[kD1Free], prev, status, kTimeout))) break;
+        trace(0, i, 2);
+        ptx::tc_fence_after_sync();
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          const uint64_t d = kq + ((ks >> 2) * (16384 >> 4) + (ks & 3) * (32 >> 4));
+          ptx::mma_ts(tmem + kColD1, tmem + kColSbf + ks * 8, d, kStateOnly ? id_n64 : id_n128, ks > 0);
+        }
+        ptx::mma_commit(&bars[kD1Done]);
+        trace(0, i, 3);
+        // gap 1 (chain computes W): MMA4 of the previous chunk (its Pg tile was produced during that chunk's
+        // second half), so that the side warpgroup can finish that chunk's output while the chain works
+        if (!kStateOnly && i > 0) {
+          if (!(ok = ptx::mbar_spin(&bars[kPgReady], prev, status, kTimeout))) break;
+          if (i > 1 && !(ok = ptx::mbar_spin(&bars[kD4Free], i & 1, status, kTimeout))) break;
+          issue_mma4(i - 1);
+          trace(0, i, 8);
+        }
+        // MMAu: D2 = V^T (A diag(beta))^T.  A operand = V tile read MN-major (two 64-column halves 8 KiB
+        // apart), B operand = the A tile after the aux warps scaled its columns by beta in place.  D2 is
+        // free: MMA3 of the previous chunk (its last reader) precedes this in the tensor pipe.
+        if (!(ok = ptx::mbar_spin(&bars[kAbReady0 + s], (i >> 1) & 1, status, kTimeout))) break;
+        if (!p.zero_v) {
+          ptx::tc_fence_after_sync();
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks)
+            ptx::mma_ss(tmem + kColD2, vv + ks * (2048 >> 4), aa + ks * (32 >> 4), id_u, ks > 0);
+        }
+        // MMA2: D2 += W^T Ab^T
+        if (!(ok = ptx::mbar_spin(&bars[kWReady], ph, status, kTimeout))) break;
+        trace(0, i, 4);
+        ptx::tc_fence_after_sync();
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks)
+          ptx::mma_ts(tmem + kColD2, tmem + kColD1 + ks * 8, aa + ks * (32 >> 4), id_n64, ks > 0 || !p.zero_v);
+        ptx::mma_commit(&bars[kD2Done]);
+        trace(0, i, 5);
+        // gap 2 (chain computes Vd): MMA0: D0 = [K;Q] K^T (A = 128 rows, B = first 64 rows of the tile),
+        // 
         if (!kStateOnly) {
-          // MMA0: D0 = [K;Q] K^T   (A = 128 rows, B = first 64 rows of the same tile)
-          if (i > 0 && !ptx::mbar_wait(&bars[kPFree], prev, status, kTimeout)) break;
+          if (i > 0 && !(ok = ptx::mbar_spin(&bars[kPFree], prev, status, kTimeout))) break;
           ptx::tc_fence_after_sync();
 #pragma unroll
           for (int ks = 0; ks < 8; ++ks) {
-            const uint64_t d = ptx::smem_desc_sw128(kq + (ks >> 2) * 16384 + (ks & 3) * 32, 16, 1024);
+            const uint64_t d = kq + ((ks >> 2) * (16384 >> 4) + (ks & 3) * (32 >> 4));
             ptx::mma_ss(tmem + kColD0, d, d, id_n64, ks > 0);
           }
           ptx::mma_commit(&bars[kPDone]);
           trace(0, i, 1);
         }
-        // MMA1: D1 = S0^T_bf16 * [K;Q]^T
-        if (!ptx::mbar_wait(&bars[kSbfReady], ph, status, kTimeout)) break;
-        if (!kStateOnly && i > 0 && !ptx::mbar_wait(&bars[kD1Free], prev, status, kTimeout)) break;
-        trace(0, i, 2);
-        ptx::tc_fence_after_sync();
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
-          const uint64_t d = ptx::smem_desc_sw128(kq + (ks >> 2) * 16384 + (ks & 3) * 32, 16, 1024);
-          ptx::mma_ts(tmem + kColD1, tmem + kColSbf + ks * 8, d, kStateOnly ? id_n64 : id_n128, ks > 0);
-        }
-        ptx::mma_commit(&bars[kD1Done]);
-        trace(0, i, 3);
-        // MMA2: D2 = W^T A^T
-        if (!ptx::mbar_wait(&bars[kWReady], ph, status, kTimeout)) break;
-        trace(0, i, 4);
-        ptx::tc_fence_after_sync();
-#pragma unroll
-        for (int ks = 0; ks < 4; ++ks) {
-          const uint64_t d = ptx::smem_desc_sw128(aa + ks * 32, 16, 1024);
-          ptx::mma_ts(tmem + kColD2, tmem + kColD1 + ks * 8, d, id_n64, ks > 0);
-        }
-        ptx::mma_commit(&bars[kD2Done]);
-        trace(0, i, 5);
         // MMA3: S^T += V'^T K   (B = K tile read MN-major: 64-column halves are 16 KiB apart)
-        if (!ptx::mbar_wait(&bars[kVdReady], ph, status, kTimeout)) break;
+        if (!(ok = ptx::mbar_spin(&bars[kVdReady], ph, status, kTimeout))) break;
+        if (!(ok = ptx::mbar_spin(&bars[kSScaled], ph, status, kTimeout))) break;
         trace(0, i, 6);
         ptx::tc_fence_after_sync();
 #pragma unroll
-        for (int ks = 0; ks < 4; ++ks) {
-          const uint64_t d = ptx::smem_desc_sw128(kq + ks * 2048, 16384, 1024);
-          ptx::mma_ts(tmem + kColS, tmem + kColD2 + 32 + ks * 8, d, id_mn128, true);
-        }
+        for (int ks = 0; ks < 4; ++ks)
+          ptx::mma_ts(tmem + kColS, tmem + kColD2 + 32 + ks * 8, kmn + ks * (2048 >> 4), id_mn128, true);
         ptx::mma_commit(&bars[kSDone]);
         trace(0, i, 7);
-        if (!kStateOnly) {
-          // MMA4: D4 = Vd^T Pg^T
-          if (!ptx::mbar_wait(&bars[kPgReady], ph, status, kTimeout)) break;
-          if (i > 0 && !ptx::mbar_wait(&bars[kD4Free], prev, status, kTimeout)) break;
-          ptx::tc_fence_after_sync();
+        ptx::mma_commit(&bars[kEmpty0 + s]);  // every MMA that reads this stage has been issued and tracked
+      }
+      // MMA4 of the last chunk
+      if (ok && !kStateOnly && nproc > 0) {
+        const int j = nproc - 1;
+        if (ptx::mbar_spin(&bars[kPgReady], j & 1, status, kTimeout) &&
+            (j == 0 || ptx::mbar_spin(&bars[kD4Free], (j - 1) & 1, status, kTimeout)))
+          issue_mma4(j);
+      }
+    }
+  } else if (warp >= 10) {
+    // =========================================================== aux warps 10, 11: operand tiles
+    // (a) Ab = A diag(beta), in place in the stage's A tile (B operand of MMAu and MMA2);
+    // (b) Pg = s * G .* P from D0 rows 64..127 (TMEM quadrants 2, 3 = warps 10, 11) into a swizzled tile.
+    const int r = tid - 320;  // 0..63: row of A / row c of P
+    const uint32_t tm = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
+    // per-warp private copy of the chunk's cumulative gates (two chunks deep) so that the stage can be
+    // released right after the A tile is scaled, long before Pg of that chunk is produced
+    float* my_g = aux_g + (warp - 10) * 128;
+    auto scale_a_tile = [&](int s, int chunk_parity) {
+      const Gates* gs = gates_of(s);
+      my_g[chunk_parity * 64 + lane] = gs->g[lane];
+      my_g[chunk_parity * 64 + 32 + lane] = gs->g[32 + lane];
+      uint8_t* at = stage_ptr(s) + kStageA;
 #pragma unroll
-          for (int ks = 0; ks < 4; ++ks) {
-            const uint64_t d = ptx::smem_desc_sw128(pg_addr + ks * 32, 16, 1024);
-            ptx::mma_ts(tmem + kColD4, tmem + kColD2 + ks * 8, d, id_n64, ks > 0);
+      for (int c16 = 0; c16 < 8; ++c16) {
+        uint4* ptr = reinterpret_cast<uint4*>(at + ptx::sw128_offset(r, c16));
+        uint4 raw = *ptr;
+        const float4 b0 = *reinterpret_cast<const float4*>(&gs->beta[c16 * 8]);
+        const float4 b1 = *reinterpret_cast<const float4*>(&gs->beta[c16 * 8 + 4]);
+        const T* e = reinterpret_cast<const T*>(&raw);
+        raw = make_uint4(pack2<T>(Cvt<T>::to_f32(e[0]) * b0.x, Cvt<T>::to_f32(e[1]) * b0.y),
+                         pack2<T>(Cvt<T>::to_f32(e[2]) * b0.z, Cvt<T>::to_f32(e[3]) * b0.w),
+                         pack2<T>(Cvt<T>::to_f32(e[4]) * b1.x, Cvt<T>::to_f32(e[5]) * b1.y),
+                         pack2<T>(Cvt<T>::to_f32(e[6]) * b1.z, Cvt<T>::to_f32(e[7]) * b1.w));
+        *ptr = raw;
+      }
+      ptx::fence_proxy_async_smem();
+      // one barrier per stage: the aux warps run one chunk ahead, and a waiter must never fall two
+      // phases behind a barrier
+      warp_arrive(&bars[kAbReady0 + s], lane);
+      warp_arrive(&bars[kEmpty0 + s], lane);  // aux no longer touches stage s
+    };
+    bool ok = true;
+    if (nproc > 0) {
+      ok = ptx::mbar_wait_warp(&bars[kFull0], 0, status, kTimeout);
+      if (ok) scale_a_tile(0, 0);
+    }
+    for (int i = 0; ok && i < nproc; ++i) {
+      const int s = i & 1, ph = i & 1;
+      const float* gsg = my_g + (i & 1) * 64;
+      // the A tile of the NEXT chunk first: MMAu of that chunk waits for it early
+      if (i + 1 < nproc) {
+        if (!(ok = ptx::mbar_wait_warp(&bars[kFull0 + (s ^ 1)], ((i + 1) >> 1) & 1, status, kTimeout))) break;
+        scale_a_tile(s ^ 1, (i + 1) & 1);
+      }
+      if (!kStateOnly) {
+        if (tid == 320) trace(2, i, 8);
+        if (!(ok = ptx::mbar_wait_warp(&bars[kPDone], ph, status, kTimeout))) break;
+        // MMA4 of the previous chunk must have finished reading the Pg tile
+        if (i > 0 && !(ok = ptx::mbar_wait_warp(&bars[kD4Done], (i - 1) & 1, status, kTimeout))) break;
+        ptx::tc_fence_after_sync();
+        if (tid == 320) trace(2, i, 9);
+        const int c = r;
+        const float gc = gsg[c];
+        uint8_t* pg = smem + kOffPg;
+#pragma unroll
+        for (int db = 0; db < 64; db += 32) {
+          uint32_t pr[32];
+          ptx::tmem_ld32(tm + kColD0 + db, pr);
+          ptx::tmem_wait_ld();
+          if (db == 32) {
+            ptx::tc_fence_before_sync();
+            warp_arrive(&bars[kPFree], lane);
           }
-          ptx::mma_commit(&bars[kD4Done]);
-          trace(0, i, 8);
+          // branch-free: every lane evaluates all 32 entries, the causal mask is a select
+#pragma unroll
+          for (int j8 = 0; j8 < 32; j8 += 8) {
+            const float4 ga = *reinterpret_cast<const float4*>(&gsg[db + j8]);
+            const float4 gb = *reinterpret_cast<const float4*>(&gsg[db + j8 + 4]);
+            const float gd[8] = {ga.x, ga.y, ga.z, ga.w, gb.x, gb.y, gb.z, gb.w};
+            float x[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const float e = __expf(fminf(gc - gd[j], 0.f));
+              const float val = p.scale * e * __uint_as_float(pr[j8 + j]);
+              x[j] = (db + j8 + j <= c) ? val : 0.f;
+            }
+            *reinterpret_cast<uint4*>(pg + ptx::sw128_offset(c, (db + j8) >> 3)) =
+                make_uint4(pack2<T>(x[0], x[1]), pack2<T>(x[2], x[3]), pack2<T>(x[4], x[5]), pack2<T>(x[6], x[7]));
+          }
         }
-        ptx::mma_commit(&bars[kEmpty0 + s]);  // every MMA that reads this stage has completed
+        ptx::fence_proxy_async_smem();
+        warp_arrive(&bars[kPgReady], lane);
+        if (tid == 320) trace(2, i, 10);
       }
     }
   } else {
@@ -334,9 +501,65 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       ptx::tmem_wait_st();
       ptx::tc_fence_before_sync();
       warp_arrive(&bars[kSbfReady], lane);
+      warp_arrive(&bars[kSScaled], lane);
     }
 
     float qs[64];  // side warpgroup: s * gamma_c * (Q S0)^T row, kept from D1 until the epilogue
+
+    // Output epilogue of chunk j (side warpgroup): O^T = s gamma .* (Q S0)^T (kept in qs) + D4, transposed
+    // through a shared-memory tile and written with one TMA store (row-masked stores for a ragged tail).
+    auto epilogue = [&](int j, int valid_j, int t0_j) -> bool {
+        if (!(ptx::mbar_wait_warp(&bars[kD4Done], j & 1, status, kTimeout))) return false;
+        ptx::tc_fence_after_sync();
+        if (tid == 128) trace(2, j, 6);
+        T* so = reinterpret_cast<T*>(smem + kOffO + (j & 1) * 16384);
+        // Two output tiles alternate: tile (j & 1) was last used by the TMA store of chunk j - 2, which
+        // must have finished reading it.  Only mbarriers (bounded waits), never a CTA / named barrier.
+        if (j >= 2) {
+          if (tid == 128) {
+            asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+            ptx::mbar_arrive(&bars[kOFree]);
+          }
+          if (!(ptx::mbar_wait_warp(&bars[kOFree], j & 1, status, kTimeout))) return false;
+        }
+#pragma unroll
+        for (int cb = 0; cb < 64; cb += 32) {
+          uint32_t r[32];
+          ptx::tmem_ld32(tm + kColD4 + cb, r);
+          ptx::tmem_wait_ld();
+#pragma unroll
+          for (int e = 0; e < 32; ++e) so[(cb + e) * kHeadDim + v] = Cvt<T>::from_f32(qs[cb + e] + __uint_as_float(r[e]));
+        }
+        ptx::tc_fence_before_sync();
+        warp_arrive(&bars[kD4Free], lane);
+        if (tid == 192) trace(2, j, 11);
+        if (tid == 128) trace(2, j, 12);
+        ptx::fence_proxy_async_smem();
+        warp_arrive(&bars[kOReady], lane);
+        if (valid_j == kChunk) {
+          if (warp == 4) {  // only the issuing warp waits for the tile to be complete
+            if (!(ptx::mbar_wait_warp(&bars[kOReady], j & 1, status, kTimeout))) return false;
+            if (tid == 128) {
+              ptx::tma_store_3d(&tm_o, so, 0, hv, t0_j);
+              ptx::tma_store_commit();
+            }
+          }
+        } else {
+          if (!(ptx::mbar_wait_warp(&bars[kOReady], j & 1, status, kTimeout))) return false;
+          // ragged tail (always the last chunk of a sequence): row-masked 16-byte stores
+          T* ob = static_cast<T*>(p.o);
+          const int tl = tid - 128;  // 16 threads per row (8 elements each), 8 rows per pass
+          for (int r0 = 0; r0 < valid_j; r0 += 8) {
+            const int row = r0 + (tl >> 4);
+            if (row < valid_j) {
+              const uint4 x = *reinterpret_cast<const uint4*>(so + row * kHeadDim + (tl & 15) * 8);
+              *reinterpret_cast<uint4*>(ob + (static_cast<int64_t>(t0_j + row) * p.num_v_heads + hv) * kHeadDim + (tl & 15) * 8) = x;
+            }
+          }
+        }
+      return true;
+    };
+    int prev_valid = 0, prev_t0 = 0;
 
     for (int i = 0; alive && i < nproc; ++i) {
       const int s = i & 1, ph = i & 1;
@@ -347,13 +570,14 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       if (!alive) break;
       if (tid == 128) trace(2, i, 0);
       const int valid = gs->valid;
+      // the previous chunk's output first: its MMA4 was issued right after this chunk's MMA1
+      if (!kStateOnly && wg == 1 && i > 0 && !(alive = epilogue(i - 1, prev_valid, prev_t0))) break;
 
       if (wg == 0) {
-        // ---------------- chain: W = beta .* (V - gamma .* U)
+        // ---------------- chain: W = -gamma .* U   (the V part of Vd is already in D2 from MMAu)
         if (!(alive = ptx::mbar_wait_warp(&bars[kD1Done], ph, status, kTimeout))) break;
         ptx::tc_fence_after_sync();
         if (tid == 0) trace(1, i, 0);
-        const T* vt = reinterpret_cast<const T*>(stage_ptr(s) + kStageV);
 #pragma unroll
         for (int cb = 0; cb < 64; cb += 32) {
           uint32_t u[32], w[16];
@@ -361,18 +585,9 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           ptx::tmem_wait_ld();
 #pragma unroll
           for (int j = 0; j < 32; j += 4) {
-            const int c = cb + j;
-            const float4 b4 = *reinterpret_cast<const float4*>(&gs->beta[c]);
-            const float4 g4 = *reinterpret_cast<const float4*>(&gs->gamma[c]);
-            float vv[4];
-#pragma unroll
-            for (int e = 0; e < 4; ++e) vv[e] = p.zero_v ? 0.f : Cvt<T>::to_f32(vt[(c + e) * kHeadDim + v]);
-            const float w0 = b4.x * (vv[0] - g4.x * __uint_as_float(u[j]));
-            const float w1 = b4.y * (vv[1] - g4.y * __uint_as_float(u[j + 1]));
-            const float w2 = b4.z * (vv[2] - g4.z * __uint_as_float(u[j + 2]));
-            const float w3 = b4.w * (vv[3] - g4.w * __uint_as_float(u[j + 3]));
-            w[j >> 1] = pack2<T>(w0, w1);
-            w[(j >> 1) + 1] = pack2<T>(w2, w3);
+            const float4 g4 = *reinterpret_cast<const float4*>(&gs->gamma[cb + j]);
+            w[j >> 1] = pack2<T>(-g4.x * __uint_as_float(u[j]), -g4.y * __uint_as_float(u[j + 1]));
+            w[(j >> 1) + 1] = pack2<T>(-g4.z * __uint_as_float(u[j + 2]), -g4.w * __uint_as_float(u[j + 3]));
           }
           ptx::tmem_st16(tm + kColD1 + cb / 2, w);
         }
@@ -411,8 +626,17 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             vp[16 + (j >> 1) + 1] = pack2<T>(b2 * r1.z, b3 * r1.w);
           }
           if (tid == 0) trace(1, i, 7);
-          ptx::tmem_st32(tm + kColD2, vd);
+          // V' (A operand of MMA3, on the chain) stays in tensor memory; Vd (A operand of the deferred
+          // MMA4) goes to a swizzled shared-memory tile so that D2 is free for the next chunk at once
           ptx::tmem_st32(tm + kColD2 + 32, vp);
+          if (!kStateOnly) {
+            uint8_t* vt = smem + kOffVd + (i & 1) * 16384;
+#pragma unroll
+            for (int c16 = 0; c16 < 8; ++c16)
+              *reinterpret_cast<uint4*>(vt + ptx::sw128_offset(v, c16)) =
+                  make_uint4(vd[c16 * 4], vd[c16 * 4 + 1], vd[c16 * 4 + 2], vd[c16 * 4 + 3]);
+            ptx::fence_proxy_async_smem();
+          }
           if (tid == 0) trace(1, i, 8);
           if (vn != nullptr) {
             T* dst = vn + (static_cast<int64_t>(t0) * p.num_v_heads + hv) * kHeadDim + v;
@@ -429,46 +653,7 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         warp_arrive(&bars[kVdReady], lane);
         if (tid == 0) trace(1, i, 3);
       } else {
-        // ---------------- side: Pg = s * G .* P  (P rows live in TMEM lanes 64..127 -> warps 6, 7)
         if (!kStateOnly) {
-          if ((warp & 3) >= 2) {
-            if (tid == 192) trace(2, i, 8);
-            if (!(alive = ptx::mbar_wait_warp(&bars[kPDone], ph, status, kTimeout))) break;
-            ptx::tc_fence_after_sync();
-            if (tid == 192) trace(2, i, 9);
-            const int c = v - 64;
-            const float gc = gs->g[c];
-            uint8_t* pg = smem + kOffPg;
-#pragma unroll
-            for (int db = 0; db < 64; db += 32) {
-              uint32_t pr[32];
-              ptx::tmem_ld32(tm + kColD0 + db, pr);
-              ptx::tmem_wait_ld();
-              if (db == 32) {
-                ptx::tc_fence_before_sync();
-                warp_arrive(&bars[kPFree], lane);
-              }
-              // branch-free: every lane evaluates all 32 entries, the causal mask is a select
-#pragma unroll
-              for (int j8 = 0; j8 < 32; j8 += 8) {
-                const float4 ga = *reinterpret_cast<const float4*>(&gs->g[db + j8]);
-                const float4 gb = *reinterpret_cast<const float4*>(&gs->g[db + j8 + 4]);
-                const float gd[8] = {ga.x, ga.y, ga.z, ga.w, gb.x, gb.y, gb.z, gb.w};
-                float x[8];
-#pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                  const float e = __expf(fminf(gc - gd[j], 0.f));
-                  const float val = p.scale * e * __uint_as_float(pr[j8 + j]);
-                  x[j] = (db + j8 + j <= c) ? val : 0.f;
-                }
-                *reinterpret_cast<uint4*>(pg + ptx::sw128_offset(c, (db + j8) >> 3)) =
-                    make_uint4(pack2<T>(x[0], x[1]), pack2<T>(x[2], x[3]), pack2<T>(x[4], x[5]), pack2<T>(x[6], x[7]));
-              }
-            }
-            ptx::fence_proxy_async_smem();
-            warp_arrive(&bars[kPgReady], lane);
-            if (tid == 192) trace(2, i, 10);
-          }
           // ---------------- side: keep s * gamma_c * (Q S0)^T
           if (tid == 128) trace(2, i, 1);
           if (!(alive = ptx::mbar_wait_warp(&bars[kD1Done], ph, status, kTimeout))) break;
@@ -506,14 +691,14 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         egl_next = gates_of(s ^ 1)->egl;
       }
       T* hout = static_cast<T*>(p.h);
+      if (last) {
+        if (p.final_state != nullptr && out_row >= 0) {
+          float* fs = p.final_state + (static_cast<int64_t>(out_row) * p.num_v_heads + hv) * kHeadDim * kHeadDim;
 #pragma unroll
-      for (int kb = 0; kb < 64; kb += 32) {
-        uint32_t sf[32], sb[16];
-        ptx::tmem_ld32(tm + kColS + col_half + kb, sf);
-        ptx::tmem_wait_ld();
-        if (last) {
-          if (p.final_state != nullptr && out_row >= 0) {
-            float* fs = p.final_state + (static_cast<int64_t>(out_row) * p.num_v_heads + hv) * kHeadDim * kHeadDim;
+          for (int kb = 0; kb < 64; kb += 32) {
+            uint32_t sf[32];
+            ptx::tmem_ld32(tm + kColS + col_half + kb, sf);
+            ptx::tmem_wait_ld();
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
               const int k = col_half + kb + j;
@@ -521,15 +706,17 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
               else fs[k * kHeadDim + v] = __uint_as_float(sf[j]);
             }
           }
-        } else {
+        }
+      } else {
+        // (a) critical: bf16 copy of the new state -> MMA1 of the next chunk may start
 #pragma unroll
-          for (int j = 0; j < 32; j += 2) {
-            sb[j >> 1] = pack2<T>(__uint_as_float(sf[j]), __uint_as_float(sf[j + 1]));
-            sf[j] = __float_as_uint(__uint_as_float(sf[j]) * egl_next);
-            sf[j + 1] = __float_as_uint(__uint_as_float(sf[j + 1]) * egl_next);
-          }
+        for (int kb = 0; kb < 64; kb += 32) {
+          uint32_t sf[32], sb[16];
+          ptx::tmem_ld32(tm + kColS + col_half + kb, sf);
+          ptx::tmem_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 32; j += 2) sb[j >> 1] = pack2<T>(__uint_as_float(sf[j]), __uint_as_float(sf[j + 1]));
           ptx::tmem_st16(tm + kColSbf + (col_half + kb) / 2, sb);
-          ptx::tmem_st32(tm + kColS + col_half + kb, sf);
           if (hout != nullptr) {
             // h[chunk + 1] = state entering the next chunk, [K][V] layout
             T* hp = hout + ((chunk_base + chunk + 1) * p.num_v_heads + hv) * kHeadDim * kHeadDim;
@@ -538,67 +725,35 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             for (int j = 0; j < 32; ++j) hp[(col_half + kb + j) * kHeadDim + v] = sbh[j];
           }
         }
-      }
-      if (!last) {
         ptx::tmem_wait_st();
         ptx::tc_fence_before_sync();
         warp_arrive(&bars[kSbfReady], lane);
         if (tid == 0) trace(1, i, 5);
         if (tid == 128) trace(2, i, 5);
         if (tid == 192) trace(2, i, 13);
-      }
-
-      // ---------------- side: output epilogue
-      if (!kStateOnly && wg == 1) {
-        if (!(alive = ptx::mbar_wait_warp(&bars[kD4Done], ph, status, kTimeout))) break;
-        ptx::tc_fence_after_sync();
-        if (tid == 128) trace(2, i, 6);
-        T* so = reinterpret_cast<T*>(smem + kOffO);
-        // The tile is reused every chunk: the previous chunk's TMA store must have finished reading it.
-        // Only mbarriers (bounded waits) are used here, never a CTA or named barrier.
-        if (i > 0) {
-          if (tid == 128) {
-            ptx::tma_store_wait_read();
-            ptx::mbar_arrive(&bars[kOFree]);
-          }
-          if (!(alive = ptx::mbar_wait_warp(&bars[kOFree], (i - 1) & 1, status, kTimeout))) break;
-        }
+        // (b) off the critical path: decay of the fp32 state for the next chunk (needed by MMA3 only)
 #pragma unroll
-        for (int cb = 0; cb < 64; cb += 32) {
-          uint32_t r[32];
-          ptx::tmem_ld32(tm + kColD4 + cb, r);
+        for (int kb = 0; kb < 64; kb += 32) {
+          uint32_t sf[32];
+          ptx::tmem_ld32(tm + kColS + col_half + kb, sf);
           ptx::tmem_wait_ld();
 #pragma unroll
-          for (int j = 0; j < 32; ++j) so[(cb + j) * kHeadDim + v] = Cvt<T>::from_f32(qs[cb + j] + __uint_as_float(r[j]));
+          for (int j = 0; j < 32; ++j) sf[j] = __float_as_uint(__uint_as_float(sf[j]) * egl_next);
+          ptx::tmem_st32(tm + kColS + col_half + kb, sf);
         }
+        ptx::tmem_wait_st();
         ptx::tc_fence_before_sync();
-        warp_arrive(&bars[kD4Free], lane);
-        if (tid == 192) trace(2, i, 11);
-        if (tid == 128) trace(2, i, 12);
-        ptx::fence_proxy_async_smem();
-        warp_arrive(&bars[kOReady], lane);
-        if (!(alive = ptx::mbar_wait_warp(&bars[kOReady], ph, status, kTimeout))) break;
-        if (valid == kChunk) {
-          if (tid == 128) {
-            ptx::tma_store_3d(&tm_o, so, 0, hv, t0);
-            ptx::tma_store_commit();
-          }
-        } else {
-          // ragged tail (always the last chunk of a sequence): row-masked 16-byte stores
-          T* ob = static_cast<T*>(p.o);
-          const int tl = tid - 128;  // 16 threads per row (8 elements each), 8 rows per pass
-          for (int r0 = 0; r0 < valid; r0 += 8) {
-            const int row = r0 + (tl >> 4);
-            if (row < valid) {
-              const uint4 x = *reinterpret_cast<const uint4*>(so + row * kHeadDim + (tl & 15) * 8);
-              *reinterpret_cast<uint4*>(ob + (static_cast<int64_t>(t0 + row) * p.num_v_heads + hv) * kHeadDim + (tl & 15) * 8) = x;
-            }
-          }
-        }
+        warp_arrive(&bars[kSScaled], lane);
       }
-      if (tid == 128) trace(2, i, 7);
-      warp_arrive(&bars[kEmpty0 + s], lane);  // this warp no longer reads stage s
+
+      // The stage is released BEFORE the epilogue (which only needs registers and the Vd/Pg tiles), so the
+      // producer can refill it while MMA4 / the output store of this chunk are still in flight.
+      warp_arrive(&bars[kEmpty0 + s], lane);
+
+      prev_valid = valid;
+      prev_t0 = t0;
     }
+    if (!kStateOnly && wg == 1 && alive && nproc > 0) alive = epilogue(nproc - 1, prev_valid, prev_t0);
     if (!kStateOnly && tid == 128) ptx::tma_store_wait_all();
     // h[first chunk] = initial state
     if (p.h != nullptr && nproc > 0 && wg == 0) {
@@ -628,7 +783,7 @@ int launch_chunk_fwd(const FwdParams& p, const void* q, const void* k, const voi
   int rc;
   if ((rc = make_tmap_3d(&tm_k, k, total_tokens, p.num_k_heads, kHeadDim, 64, 64, true, is_bf16)) != QLA_OK) return rc;
   if ((rc = make_tmap_3d(&tm_q, state_only ? k : q, total_tokens, p.num_k_heads, kHeadDim, 64, 64, true, is_bf16)) != QLA_OK) return rc;
-  if ((rc = make_tmap_3d(&tm_v, v, total_tokens, p.num_v_heads, kHeadDim, 64, 128, false, is_bf16)) != QLA_OK) return rc;
+  if ((rc = make_tmap_3d(&tm_v, v, total_tokens, p.num_v_heads, kHeadDim, 64, 64, true, is_bf16)) != QLA_OK) return rc;
   if ((rc = make_tmap_3d(&tm_a, A, total_tokens, p.num_v_heads, 64, 64, 64, true, is_bf16)) != QLA_OK) return rc;
   if ((rc = make_tmap_3d(&tm_o, state_only ? v : p.o, total_tokens, p.num_v_heads, kHeadDim, 64, 128, false, is_bf16)) != QLA_OK) return rc;
   const unsigned grid = static_cast<unsigned>(p.num_seqs) * p.num_v_heads;

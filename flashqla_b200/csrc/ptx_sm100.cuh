@@ -70,6 +70,31 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* s
   return false;
 }
 
+// Low-latency variant for a single latency-critical thread (the MMA issuer): polls with
+// mbarrier.test_wait, which never suspends the thread, so the wake-up is not delayed by the
+// hardware's try_wait back-off.  Still bounded.
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred P;\n"
+      "mbarrier.test_wait.parity.shared::cta.b64 P, [%1], %2;\n"
+      "selp.b32 %0, 1, 0, P;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_spin(uint64_t* bar, uint32_t parity, int* status, int code) {
+  for (uint32_t i = 0; i < (kSpinLimit << 4); ++i) {
+    if (mbar_test_wait(bar, parity)) return true;
+    if ((i & 16383u) == 16383u && status != nullptr && *reinterpret_cast<volatile int*>(status) != 0) return false;
+  }
+  if (status != nullptr) atomicCAS(status, 0, code);
+  return false;
+}
+
 // Same wait executed by a converged warp; the verdict is made warp-uniform so that no lane leaves a
 // loop alone (later __syncwarp / .sync.aligned instructions need the whole warp).
 __device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, int* status, int code) {
@@ -100,6 +125,13 @@ __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* m, uin
       "[%0], [%1, {%3, %4, %5}], [%2];"
       ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z)
       : "memory");
+}
+// Bring a box into L2 only (no shared-memory destination, no completion tracking).
+__device__ __forceinline__ void tma_prefetch_l2_3d(const CUtensorMap* m, int x, int y, int z) {
+  asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];" ::"l"(
+                   reinterpret_cast<uint64_t>(m)),
+               "r"(x), "r"(y), "r"(z)
+               : "memory");
 }
 __device__ __forceinline__ void tma_store_3d(const CUtensorMap* m, const void* src, int x, int y, int z) {
   asm volatile(
