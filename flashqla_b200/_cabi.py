@@ -62,6 +62,20 @@ class QlaChunkFwdArgs(C.Structure):
     ]
 
 
+class QlaChunkBwdArgs(C.Structure):
+    _fields_ = [
+        ("batch", C.c_int32), ("seq_len", C.c_int32), ("num_seqs", C.c_int32),
+        ("num_k_heads", C.c_int32), ("num_v_heads", C.c_int32), ("qkv_dtype", C.c_int32),
+        ("beta_dtype", C.c_int32), ("flags", C.c_int32), ("scale", C.c_float),
+        ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("g_cumsum", C.c_void_p),
+        ("beta", C.c_void_p), ("A", C.c_void_p), ("h", C.c_void_p), ("v_new", C.c_void_p),
+        ("d_o", C.c_void_p), ("dht", C.c_void_p), ("cu_seqlens", C.c_void_p),
+        ("dq", C.c_void_p), ("dk", C.c_void_p), ("dv", C.c_void_p), ("dbeta", C.c_void_p),
+        ("dg", C.c_void_p), ("dh0", C.c_void_p), ("workspace", C.c_void_p),
+        ("workspace_bytes", C.c_size_t), ("status", C.c_void_p),
+    ]
+
+
 class QlaCpPlanArgs(C.Structure):
     _fields_ = [
         ("num_segments", C.c_int32), ("num_v_heads", C.c_int32), ("threshold", C.c_float),
@@ -82,6 +96,8 @@ EXPORTS = {
     "qla_recurrent_update": (C.c_int, [C.POINTER(QlaRecurrentArgs), C.c_void_p]),
     "qla_chunk_fwd_workspace_bytes": (C.c_size_t, [C.POINTER(QlaChunkFwdArgs)]),
     "qla_chunk_fwd": (C.c_int, [C.POINTER(QlaChunkFwdArgs), C.c_void_p]),
+    "qla_chunk_bwd_workspace_bytes": (C.c_size_t, [C.POINTER(QlaChunkBwdArgs)]),
+    "qla_chunk_bwd": (C.c_int, [C.POINTER(QlaChunkBwdArgs), C.c_void_p]),
     "qla_cp_plan": (C.c_int, [C.POINTER(QlaCpPlanArgs), C.c_void_p]),
     "qla_cp_chain": (C.c_int, [C.POINTER(QlaCpChainArgs), C.c_void_p]),
     "qla_set_trace_buffer": (C.c_int, [C.c_void_p, C.c_size_t]),

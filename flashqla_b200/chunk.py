@@ -163,6 +163,114 @@ def chunk_gated_delta_rule_fwd(
     return g_cumsum, A, o, h, final_state
 
 
+def chunk_gated_delta_rule_bwd(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    g: torch.Tensor,
+    beta: torch.Tensor,
+    A: torch.Tensor,
+    do: torch.Tensor,
+    dht: Optional[torch.Tensor] = None,
+    scale: Optional[float] = None,
+    initial_state: Optional[torch.Tensor] = None,
+    cu_seqlens: Optional[torch.Tensor] = None,
+    h: Optional[torch.Tensor] = None,
+    v_new: Optional[torch.Tensor] = None,
+    transpose_state_layout: bool = False,
+):
+    """Raw backward.  ``g`` is the chunk-local cumulative gate and ``A`` the WY matrix returned by
+    ``chunk_gated_delta_rule_fwd``; ``h`` / ``v_new`` are the forward's optional outputs and are
+    recomputed by a state-only scan when missing.  Returns ``(dq, dk, dv, db, dg, dh0 | None)`` with
+    ``dg`` w.r.t. the raw per-token gate and ``dh0`` present iff ``initial_state`` is given (the
+    oracle's convention, tests/ref_gdr.py:378)."""
+    B, T, Hk, Hv, N = _check_common(q, k, v, g, beta, initial_state, cu_seqlens, transpose_state_layout)
+    dev = q.device
+    q, k, v, beta, A, do = (x if x.is_contiguous() else x.contiguous() for x in (q, k, v, beta, A, do))
+    g_cumsum = g.to(torch.float32)
+    g_cumsum = g_cumsum if g_cumsum.is_contiguous() else g_cumsum.contiguous()
+    if do.dtype != q.dtype:
+        do = do.to(q.dtype)
+    if scale is None:
+        scale = q.shape[-1] ** -0.5
+    h0 = None
+    if initial_state is not None:
+        h0 = initial_state.to(torch.float32).contiguous()
+    if dht is not None:
+        dht = dht.to(torch.float32).contiguous()
+    cu = None
+    lens = None
+    if cu_seqlens is not None:
+        cu = cu_seqlens.to(device=dev, dtype=torch.int32).contiguous()
+        lens = host_seqlens(cu_seqlens)
+    flags = _cabi.CHUNK_TRANSPOSE_STATE if transpose_state_layout else 0
+    if h is None or v_new is None:
+        n_chunks = B * ((T + CHUNK - 1) // CHUNK) if lens is None else sum((n + CHUNK - 1) // CHUNK for n in lens)
+        h = torch.empty(n_chunks, Hv, 128, 128, dtype=q.dtype, device=dev)
+        v_new = torch.empty_like(v)
+        _launch_fwd(None, k, v, None, beta, h0, cu, g_cumsum, A, None, h, v_new, None, scale,
+                    flags=flags | _cabi.CHUNK_STATE_ONLY | _cabi.CHUNK_SKIP_PREPARE)
+    h = h if h.is_contiguous() else h.contiguous()
+    v_new = v_new if v_new.is_contiguous() else v_new.contiguous()
+
+    dq = torch.empty_like(q)
+    dk = torch.empty_like(k)
+    dv = torch.empty_like(v)
+    db = torch.empty(B, T, Hv, dtype=torch.float32, device=dev)
+    dg = torch.empty(B, T, Hv, dtype=torch.float32, device=dev)
+    dh0 = torch.empty(N, Hv, 128, 128, dtype=torch.float32, device=dev) if initial_state is not None else None
+    Bk, Tk = (1, B * T) if cu is not None else (B, T)
+    args = _cabi.QlaChunkBwdArgs(
+        batch=Bk, seq_len=Tk, num_seqs=N, num_k_heads=Hk, num_v_heads=Hv, qkv_dtype=_cabi.dtype_code(q.dtype),
+        beta_dtype=_cabi.dtype_code(beta.dtype), flags=flags, scale=float(scale),
+        q=_cabi.ptr(q), k=_cabi.ptr(k), v=_cabi.ptr(v), g_cumsum=_cabi.ptr(g_cumsum), beta=_cabi.ptr(beta),
+        A=_cabi.ptr(A), h=_cabi.ptr(h), v_new=_cabi.ptr(v_new), d_o=_cabi.ptr(do), dht=_cabi.ptr(dht),
+        cu_seqlens=_cabi.ptr(cu), dq=_cabi.ptr(dq), dk=_cabi.ptr(dk), dv=_cabi.ptr(dv), dbeta=_cabi.ptr(db),
+        dg=_cabi.ptr(dg), dh0=_cabi.ptr(dh0), workspace=None, workspace_bytes=0,
+        status=_cabi.ptr(device_status(dev)))
+    lib = _cabi.lib()
+    ws_bytes = lib.qla_chunk_bwd_workspace_bytes(args)
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
+    args.workspace, args.workspace_bytes = ws.data_ptr(), ws_bytes
+    with torch.cuda.device(dev):
+        code = lib.qla_chunk_bwd(args, _cabi.current_stream(dev))
+    _cabi.check(code, "qla_chunk_bwd")
+    return dq, dk, dv, db, dg, dh0
+
+
+class ChunkGatedDeltaRuleFunction(torch.autograd.Function):
+    """Autograd wrapper (reference: chunk/__init__.py:185-290).  The forward keeps ``h`` and ``v_new``
+    so that the backward does not have to recompute the chunk states."""
+
+    @staticmethod
+    @torch.amp.custom_fwd(device_type="cuda")
+    def forward(ctx, q, k, v, g, beta, scale, initial_state, output_final_state, cu_seqlens,
+                transpose_state_layout):
+        need_grad = any(t is not None and t.requires_grad for t in (q, k, v, g, beta, initial_state))
+        out = chunk_gated_delta_rule_fwd(
+            q, k, v, g, beta, scale=scale, initial_state=initial_state, cu_seqlens=cu_seqlens,
+            output_final_state=output_final_state, output_h=need_grad, output_v_new=need_grad,
+            transpose_state_layout=transpose_state_layout)
+        g_cumsum, A, o, h, final_state = out[:5]
+        v_new = out[5] if need_grad else None
+        ctx.save_for_backward(q, k, v, g_cumsum, beta, A, initial_state, cu_seqlens, h, v_new)
+        ctx.scale = scale
+        ctx.transpose_state_layout = transpose_state_layout
+        ctx.g_dtype, ctx.beta_dtype = g.dtype, beta.dtype
+        return o.to(q.dtype), final_state
+
+    @staticmethod
+    @torch.amp.custom_bwd(device_type="cuda")
+    def backward(ctx, do, dht):
+        q, k, v, g_cumsum, beta, A, initial_state, cu_seqlens, h, v_new = ctx.saved_tensors
+        dq, dk, dv, db, dg, dh0 = chunk_gated_delta_rule_bwd(
+            q, k, v, g_cumsum, beta, A, do, dht=dht, scale=ctx.scale, initial_state=initial_state,
+            cu_seqlens=cu_seqlens, h=h, v_new=v_new, transpose_state_layout=ctx.transpose_state_layout)
+        if dh0 is not None and initial_state is not None:
+            dh0 = dh0.to(initial_state.dtype)
+        return (dq, dk, dv, dg.to(ctx.g_dtype), db.to(ctx.beta_dtype), None, dh0, None, None, None)
+
+
 @torch.compiler.disable
 def chunk_gated_delta_rule(
     q: torch.Tensor,
@@ -178,11 +286,19 @@ def chunk_gated_delta_rule(
     head_first: bool = False,
     transpose_state_layout: bool = False,
 ):
-    """Forward-only entry for now: ``(o, final_state | None)`` (reference: chunk/__init__.py:294-350)."""
+    """``(o, final_state | None)`` with gradients for q, k, v, g, beta and initial_state
+    (reference: chunk/__init__.py:294-350)."""
     assert not head_first, "head_first=True is not supported"
+    assert q.dtype == k.dtype == v.dtype
+    assert q.dtype != torch.float32, "ChunkGatedDeltaRuleFunction does not support float32. Please use bfloat16."
+    if cu_seqlens is not None and q.shape[0] != 1:
+        raise ValueError(
+            f"The batch size is expected to be 1 rather than {q.shape[0]} when using `cu_seqlens`."
+            "Please flatten variable-length inputs before processing.")
+    if scale is None:
+        scale = k.shape[-1] ** -0.5
     if use_qk_l2norm_in_kernel:
         q, k = l2norm(q), l2norm(k)
-    _, _, o, _, final_state = chunk_gated_delta_rule_fwd(
-        q, k, v, g, beta, scale=scale, initial_state=initial_state, cu_seqlens=cu_seqlens,
-        output_final_state=output_final_state, transpose_state_layout=transpose_state_layout)
-    return o.to(q.dtype), final_state
+    o, final_state = ChunkGatedDeltaRuleFunction.apply(
+        q, k, v, g, beta, scale, initial_state, output_final_state, cu_seqlens, transpose_state_layout)
+    return o, final_state

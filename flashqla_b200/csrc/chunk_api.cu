@@ -100,3 +100,70 @@ extern "C" QLA_API int qla_chunk_fwd(const QlaChunkFwdArgs* args, void* stream_)
   const void* v = a.v ? a.v : a.k;  // never dereferenced with QLA_CHUNK_ZERO_V, only used for the tensor map
   return launch_chunk_fwd(fp, a.q, a.k, v, a.A, total_tokens, is_bf16, state_only, stream);
 }
+
+namespace qla {
+namespace {
+struct BwdWorkspace {
+  size_t tables, dh, du, total;
+  int chunks_upper;
+};
+BwdWorkspace bwd_workspace(const QlaChunkBwdArgs& a) {
+  BwdWorkspace w{};
+  const int64_t nt = static_cast<int64_t>(a.batch) * a.seq_len;
+  const bool varlen = a.cu_seqlens != nullptr;
+  w.chunks_upper = varlen ? static_cast<int>(nt / kChunk + a.num_seqs) : a.batch * ((a.seq_len + kChunk - 1) / kChunk);
+  w.tables = varlen ? 2 * table_bytes(a.num_seqs) : 0;
+  w.dh = ((static_cast<size_t>(w.chunks_upper) * a.num_v_heads * kHeadDim * kHeadDim * 2) + 15) & ~size_t(15);
+  w.du = ((static_cast<size_t>(nt) * a.num_v_heads * kHeadDim * 2) + 15) & ~size_t(15);
+  w.total = w.tables + w.dh + w.du;
+  return w;
+}
+}  // namespace
+}  // namespace qla
+
+extern "C" QLA_API size_t qla_chunk_bwd_workspace_bytes(const QlaChunkBwdArgs* a) {
+  if (a == nullptr || a->batch <= 0 || a->num_seqs <= 0 || a->num_v_heads <= 0) return 0;
+  return qla::bwd_workspace(*a).total;
+}
+
+extern "C" QLA_API int qla_chunk_bwd(const QlaChunkBwdArgs* args, void* stream_) {
+  using namespace qla;
+  QLA_CHECK_ARG(args != nullptr, "args is NULL");
+  const QlaChunkBwdArgs& a = *args;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  QLA_CHECK_ARG(a.batch > 0 && a.seq_len >= 0 && a.num_seqs > 0, "batch, seq_len, num_seqs must be positive");
+  QLA_CHECK_ARG(a.num_k_heads > 0 && a.num_v_heads > 0 && a.num_v_heads % a.num_k_heads == 0,
+                "num_v_heads must be a multiple of num_k_heads");
+  QLA_CHECK_SUPPORTED(a.qkv_dtype == QLA_DT_BF16 || a.qkv_dtype == QLA_DT_F16, "q, k, v must be bf16 or fp16");
+  const bool varlen = a.cu_seqlens != nullptr;
+  QLA_CHECK_ARG(!varlen || a.batch == 1, "with cu_seqlens the batch size must be 1");
+  QLA_CHECK_ARG(varlen || a.num_seqs == a.batch, "num_seqs must equal batch without cu_seqlens");
+  QLA_CHECK_ARG(a.q && a.k && a.v && a.g_cumsum && a.beta && a.A && a.d_o, "NULL input tensor");
+  QLA_CHECK_SUPPORTED(a.h && a.v_new, "h and v_new from the forward are required");
+  QLA_CHECK_ARG(a.dq && a.dk && a.dv && a.dbeta && a.dg, "NULL output tensor");
+  const int64_t total_tokens = static_cast<int64_t>(a.batch) * a.seq_len;
+  if (total_tokens == 0) return QLA_OK;
+  const BwdWorkspace w = bwd_workspace(a);
+  if (a.workspace == nullptr || a.workspace_bytes < w.total) {
+    set_last_error("workspace of %zu bytes required, %zu given", w.total, a.workspace_bytes);
+    return QLA_ERR_WORKSPACE;
+  }
+  QLA_CHECK_ARG((reinterpret_cast<uintptr_t>(a.workspace) & 15u) == 0, "workspace must be 16-byte aligned");
+  uint8_t* ws = static_cast<uint8_t*>(a.workspace);
+  int32_t* chunk_offsets = nullptr;
+  if (varlen) {
+    int32_t* pair_offsets = reinterpret_cast<int32_t*>(ws);
+    chunk_offsets = reinterpret_cast<int32_t*>(ws + table_bytes(a.num_seqs));
+    int rc = launch_chunk_tables(a.cu_seqlens, a.num_seqs, pair_offsets, chunk_offsets, stream);
+    if (rc != QLA_OK) return rc;
+  }
+  BwdParams p{};
+  p.q = a.q; p.k = a.k; p.v = a.v; p.v_new = a.v_new; p.d_o = a.d_o; p.A = a.A; p.h = a.h;
+  p.g_cumsum = a.g_cumsum; p.beta = a.beta; p.dht = a.dht; p.cu_seqlens = a.cu_seqlens;
+  p.chunk_offsets = chunk_offsets; p.dh = ws + w.tables; p.du = ws + w.tables + w.dh;
+  p.dq = a.dq; p.dk = a.dk; p.dv = a.dv; p.dbeta = a.dbeta; p.dg = a.dg; p.dh0 = a.dh0;
+  p.num_seqs = a.num_seqs; p.seq_len = a.seq_len; p.num_k_heads = a.num_k_heads; p.num_v_heads = a.num_v_heads;
+  p.beta_dtype = a.beta_dtype; p.transpose_state = (a.flags & QLA_CHUNK_TRANSPOSE_STATE) ? 1 : 0;
+  p.scale = a.scale;
+  return launch_chunk_bwd(p, w.chunks_upper, a.qkv_dtype == QLA_DT_BF16, stream);
+}

@@ -39,6 +39,35 @@ struct FwdParams {
   long long* trace;             // optional phase trace (see qla_set_trace_buffer), NULL in normal use
 };
 
+struct BwdParams {
+  const void* q;                // [NT, Hk, 128]
+  const void* k;
+  const void* v;                // [NT, Hv, 128]
+  const void* v_new;            // [NT, Hv, 128] saved by the forward
+  const void* d_o;              // [NT, Hv, 128]
+  const void* A;                // [NT, Hv, 64]
+  const void* h;                // [chunks, Hv, 128, 128] state entering every chunk, saved by the forward
+  const float* g_cumsum;        // [NT, Hv]
+  const void* beta;             // [NT, Hv]
+  const float* dht;             // [N, Hv, 128, 128] or NULL
+  const int32_t* cu_seqlens;
+  const int32_t* chunk_offsets;
+  void* dh;                     // workspace [chunks, Hv, 128, 128]: gradient of the state leaving every chunk
+  void* du;                     // workspace [NT, Hv, 128]: gradient of v_new
+  void* dq;                     // [NT, Hk, 128]
+  void* dk;
+  void* dv;                     // [NT, Hv, 128]
+  float* dbeta;                 // [NT, Hv]
+  float* dg;                    // [NT, Hv] w.r.t. the raw per-token gate
+  float* dh0;                   // [N, Hv, 128, 128] or NULL
+  int num_seqs, seq_len, num_k_heads, num_v_heads;
+  int beta_dtype;
+  int transpose_state;
+  float scale;
+};
+
+int launch_chunk_bwd(const BwdParams& p, int total_chunks_upper, bool is_bf16, cudaStream_t stream);
+
 // Trace layout: [role 0..2][chunk 4..7][16 events] clock64 stamps of CTA 0.
 constexpr int kTraceRoles = 3, kTraceChunks = 4, kTraceEvents = 16, kTraceFirstChunk = 4;
 long long* current_trace_buffer();

@@ -156,6 +156,52 @@ QLA_API size_t qla_chunk_fwd_workspace_bytes(const QlaChunkFwdArgs* args);
 QLA_API int qla_chunk_fwd(const QlaChunkFwdArgs* args, void* stream);
 
 /*
+ * Chunked backward: dq, dk, dv, dbeta, dg (w.r.t. the raw gate) and dh0.
+ * Replaces chunk_gated_delta_rule_bwd, flash_qla/ops/gated_delta_rule/chunk/__init__.py:89-182
+ * (fused_gdr_bwd chunk/hopper/fused_bwd.py:898, the decomposed stages chunk/blackwell/bwd_sm12x.py:768-780,
+ * group_reduce_vector ops/utils/group_reduce.py:60, reverse chunk_local_cumsum ops/utils/cumsum.py:134).
+ * g_cumsum, A, h and v_new are the tensors qla_chunk_fwd produced for the same inputs (h with one entry
+ * per chunk: the state entering it; v_new = the "new values" of every token).  dq / dk come out already
+ * summed over the v-heads that share a k-head; dg is already mapped back from cumulative to per-token
+ * gates.  dh0 is written iff the pointer is non-NULL.
+ * Workspace: qla_chunk_bwd_workspace_bytes(args) bytes, 16-byte aligned.
+ */
+typedef struct QlaChunkBwdArgs {
+  int32_t batch;
+  int32_t seq_len;
+  int32_t num_seqs;
+  int32_t num_k_heads;
+  int32_t num_v_heads;
+  int32_t qkv_dtype;   /* q, k, v, A, h, v_new, do, dq, dk, dv                                  */
+  int32_t beta_dtype;
+  int32_t flags;       /* QLA_CHUNK_TRANSPOSE_STATE applies to dht and dh0                       */
+  float scale;
+  const void* q;
+  const void* k;
+  const void* v;
+  const float* g_cumsum;
+  const void* beta;
+  const void* A;
+  const void* h;
+  const void* v_new;
+  const void* d_o;          /* gradient of o                                                     */
+  const float* dht;         /* gradient of the final state or NULL                               */
+  const int32_t* cu_seqlens;
+  void* dq;
+  void* dk;
+  void* dv;
+  float* dbeta;
+  float* dg;
+  float* dh0;               /* or NULL                                                           */
+  void* workspace;
+  size_t workspace_bytes;
+  int32_t* status;
+} QlaChunkBwdArgs;
+
+QLA_API size_t qla_chunk_bwd_workspace_bytes(const QlaChunkBwdArgs* args);
+QLA_API int qla_chunk_bwd(const QlaChunkBwdArgs* args, void* stream);
+
+/*
  * Intra-card context parallelism (long sequences, few heads): helpers around qla_chunk_fwd.
  * Replaces intra_card_cp_preprocess, flash_qla/ops/gated_delta_rule/chunk/cp_context.py:117-176
  * (get_warmup_chunks chunk/hopper/cp_fwd.py:66, correct_initial_states chunk/hopper/cp_fwd.py:253;
