@@ -10,10 +10,12 @@ namespace qla {
 
 namespace {
 long long* g_trace = nullptr;
+long long g_trace_count = 0;
 size_t table_bytes(int num_seqs) { return ((static_cast<size_t>(num_seqs) + 1) * sizeof(int32_t) + 15) & ~size_t(15); }
 }  // namespace
 
 long long* current_trace_buffer() { return g_trace; }
+long long current_trace_count() { return g_trace_count; }
 
 }  // namespace qla
 
@@ -24,6 +26,7 @@ extern "C" QLA_API int qla_set_trace_buffer(long long* device_buffer, size_t cou
     return QLA_ERR_INVALID_ARG;
   }
   g_trace = device_buffer;
+  g_trace_count = device_buffer ? static_cast<long long>(count) : 0;
   return QLA_OK;
 }
 
@@ -97,6 +100,7 @@ extern "C" QLA_API int qla_chunk_fwd(const QlaChunkFwdArgs* args, void* stream_)
   fp.zero_v = (a.flags & QLA_CHUNK_ZERO_V) ? 1 : 0;
   fp.scale = a.scale;
   fp.trace = current_trace_buffer();
+  fp.trace_count = current_trace_count();
   const void* v = a.v ? a.v : a.k;  // never dereferenced with QLA_CHUNK_ZERO_V, only used for the tensor map
   return launch_chunk_fwd(fp, a.q, a.k, v, a.A, total_tokens, is_bf16, state_only, stream);
 }

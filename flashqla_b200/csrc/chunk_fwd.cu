@@ -36,8 +36,8 @@ namespace {
 constexpr uint32_t kColS = 0;      // fp32 state S^T, 128 columns
 constexpr uint32_t kColSbf = 128;  // bf16 copy of S^T (A operand of MMA1), 64 columns
 constexpr uint32_t kColD1 = 192;   // U^T (192..255, overwritten by W bf16 at 192..223) | (Q S)^T (256..319)
-constexpr uint32_t kColD2 = 320;   // Vd^T; columns 352..383 are overwritten by V' bf16 (A operand of MMA3)
-constexpr uint32_t kColD4 = 384;   // Vd^T Pg^T
+constexpr uint32_t kColD2 = 320;   // Vd^T; columns 320..351 are overwritten in place by V' bf16 (A operand of MMA3)
+constexpr uint32_t kColD4 = 384;   // output accumulator: s gamma .* (Q S0)^T, then += Vd^T Pg^T
 constexpr uint32_t kColD0 = 448;   // [K;Q] K^T
 
 // ---- shared-memory map (offsets from a 1024-byte aligned base)
@@ -88,7 +88,7 @@ __device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
   return *reinterpret_cast<uint32_t*>(&x);
 }
 
-template <typename T, bool kStateOnly>
+template <typename T, bool kStateOnly, bool kTrace>
 __global__ void __launch_bounds__(kThreads, 1)
 chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                  const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_a,
@@ -162,11 +162,25 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   constexpr int kTimeout = kStatusBarrierTimeout;
 
   // phase trace: leaders of CTA 0 stamp clock64() for chunks kTraceFirstChunk.. (off when p.trace is NULL)
-  const bool tracing = p.trace != nullptr && blockIdx.x == 0;
+  // the traced CTA is chosen by the host through the last slot of the phase region (0 by default)
+  const bool tracing = kTrace && p.trace != nullptr &&
+                       static_cast<long long>(blockIdx.x) == p.trace[kTraceRoles * kTraceChunks * kTraceEvents - 1];
   auto trace = [&](int role, int i, int ev) {
-    if (tracing && i >= kTraceFirstChunk && i < kTraceFirstChunk + kTraceChunks)
+    if (kTrace && tracing && i >= kTraceFirstChunk && i < kTraceFirstChunk + kTraceChunks)
       p.trace[(role * kTraceChunks + (i - kTraceFirstChunk)) * kTraceEvents + ev] = clock64();
   };
+
+  // per-CTA residency record (start, end in ns, SM id) after the phase trace, when the buffer is large enough
+  const long long cta_slot = kTraceRoles * kTraceChunks * kTraceEvents + 3ll * blockIdx.x;
+  const bool cta_trace = kTrace && p.trace != nullptr && cta_slot + 3 <= p.trace_count;
+  if (cta_trace && tid == 0) {
+    unsigned long long t;
+    unsigned sm;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    asm volatile("mov.u32 %0, %smid;" : "=r"(sm));
+    p.trace[cta_slot] = static_cast<long long>(t);
+    p.trace[cta_slot + 2] = sm;
+  }
 
   auto stage_ptr = [&](int s) { return smem + s * kStageBytes; };
   auto gates_of = [&](int s) { return reinterpret_cast<Gates*>(stage_ptr(s) + kStageGate); };
@@ -275,13 +289,14 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       // chain computes, and MMA1 of the next chunk is never queued behind them.
       const uint64_t d_vd0 = ptx::smem_desc_sw128(ptx::smem_u32(smem + kOffVd), 16, 1024);
       const uint64_t d_vd1 = ptx::smem_desc_sw128(ptx::smem_u32(smem + kOffVd + 16384), 16, 1024);
-      // MMA4 of chunk j: D4 = Vd^T Pg^T, both operands from shared memory (Vd tile j & 1)
+      // MMA4 of chunk j: D4 += Vd^T Pg^T on top of s gamma .* (Q S0)^T which the side warpgroup stored
+      // there; both operands from shared memory (Vd tile j & 1)
       auto issue_mma4 = [&](int j) {
         const uint64_t dv = (j & 1) ? d_vd1 : d_vd0;
         ptx::tc_fence_after_sync();
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks)
-          ptx::mma_ss(tmem + kColD4, dv + ks * (32 >> 4), d_pg + ks * (32 >> 4), id_n64, ks > 0);
+          ptx::mma_ss(tmem + kColD4, dv + ks * (32 >> 4), d_pg + ks * (32 >> 4), id_n64, true);
         ptx::mma_commit(&bars[kD4Done]);
       };
       bool ok = true;
@@ -351,7 +366,7 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         ptx::tc_fence_after_sync();
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks)
-          ptx::mma_ts(tmem + kColS, tmem + kColD2 + 32 + ks * 8, kmn + ks * (2048 >> 4), id_mn128, true);
+          ptx::mma_ts(tmem + kColS, tmem + kColD2 + ks * 8, kmn + ks * (2048 >> 4), id_mn128, true);
         ptx::mma_commit(&bars[kSDone]);
         trace(0, i, 7);
         ptx::mma_commit(&bars[kEmpty0 + s]);  // every MMA that reads this stage has been issued and tracked
@@ -359,7 +374,9 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       // MMA4 of the last chunk
       if (ok && !kStateOnly && nproc > 0) {
         const int j = nproc - 1;
-        if (ptx::mbar_spin(&bars[kPgReady], j & 1, status, kTimeout) &&
+        // D1Free of the last chunk also says that its (Q S0)^T part has been stored into D4
+        if (ptx::mbar_spin(&bars[kD1Free], j & 1, status, kTimeout) &&
+            ptx::mbar_spin(&bars[kPgReady], j & 1, status, kTimeout) &&
             (j == 0 || ptx::mbar_spin(&bars[kD4Free], (j - 1) & 1, status, kTimeout)))
           issue_mma4(j);
       }
@@ -378,7 +395,7 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       my_g[chunk_parity * 64 + lane] = gs->g[lane];
       my_g[chunk_parity * 64 + 32 + lane] = gs->g[32 + lane];
       uint8_t* at = stage_ptr(s) + kStageA;
-#pragma unroll
+#pragma unroll 1
       for (int c16 = 0; c16 < 8; ++c16) {
         uint4* ptr = reinterpret_cast<uint4*>(at + ptx::sw128_offset(r, c16));
         uint4 raw = *ptr;
@@ -420,18 +437,20 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         const int c = r;
         const float gc = gsg[c];
         uint8_t* pg = smem + kOffPg;
-#pragma unroll
-        for (int db = 0; db < 64; db += 32) {
-          uint32_t pr[32];
-          ptx::tmem_ld32(tm + kColD0 + db, pr);
+        // loops over 16-column groups are kept rolled: the per-chunk code of all roles has to stay
+        // resident in the instruction cache
+#pragma unroll 1
+        for (int db = 0; db < 64; db += 16) {
+          uint32_t pr[16];
+          ptx::tmem_ld16(tm + kColD0 + db, pr);
           ptx::tmem_wait_ld();
-          if (db == 32) {
+          if (db == 48) {
             ptx::tc_fence_before_sync();
             warp_arrive(&bars[kPFree], lane);
           }
-          // branch-free: every lane evaluates all 32 entries, the causal mask is a select
+          // branch-free: every lane evaluates all entries, the causal mask is a select
 #pragma unroll
-          for (int j8 = 0; j8 < 32; j8 += 8) {
+          for (int j8 = 0; j8 < 16; j8 += 8) {
             const float4 ga = *reinterpret_cast<const float4*>(&gsg[db + j8]);
             const float4 gb = *reinterpret_cast<const float4*>(&gsg[db + j8 + 4]);
             const float gd[8] = {ga.x, ga.y, ga.z, ga.w, gb.x, gb.y, gb.z, gb.w};
@@ -453,49 +472,52 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     }
   } else {
     // =========================================================== compute warpgroups
+    // All loops over TMEM columns run in rolled groups of 16 columns (#pragma unroll 1): with four
+    // roles executing different code every chunk, fully unrolled 64-column bodies overflow the
+    // instruction cache and every SM stalls on instruction fetch.
     const int wg = warp >> 2;              // 0 = chain, 1 = side
     const int v = tid & 127;               // TMEM lane = state column
-    const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
-    const uint32_t tm = tmem + lane_base;
+    const uint32_t tm = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
     const int col_half = wg * 64;          // this warpgroup converts state columns [col_half, col_half + 64)
     bool alive = true;
+    // element (k, v) of a state tensor sits at k * st_k + v * st_v
+    const int st_k = p.transpose_state ? 1 : kHeadDim, st_v = p.transpose_state ? kHeadDim : 1;
+    float* fs_out = (p.final_state != nullptr && out_row >= 0)
+                        ? p.final_state + (static_cast<int64_t>(out_row) * p.num_v_heads + hv) * kHeadDim * kHeadDim
+                        : nullptr;
+    const float* h0p = (!p.init_identity && p.h0 != nullptr)
+                           ? p.h0 + (static_cast<int64_t>(seq) * p.num_v_heads + hv) * kHeadDim * kHeadDim
+                           : nullptr;
 
-    // ---- initial state: S = exp(gL_0) * S_init (fp32) and its bf16 copy
+    // ---- initial state: S = exp(gL_0) * S_init (fp32) and its 16-bit copy
     {
       float egl0 = 1.f;
       if (nproc > 0) {
         alive = ptx::mbar_wait_warp(&bars[kFull0], 0, status, kTimeout);
         egl0 = gates_of(0)->egl;
       }
-      const float* h0p = nullptr;
-      if (!p.init_identity && p.h0 != nullptr)
-        h0p = p.h0 + (static_cast<int64_t>(seq) * p.num_v_heads + hv) * kHeadDim * kHeadDim;
+#pragma unroll 1
+      for (int kb = 0; kb < 64; kb += 16) {
+        float x[16];
+        uint32_t sf[16], sb[8];
 #pragma unroll
-      for (int kb = 0; kb < 64; kb += 32) {
-        float x[32];
-        uint32_t sf[32], sb[16];
-#pragma unroll
-        for (int j = 0; j < 32; ++j) {
+        for (int j = 0; j < 16; ++j) {
           const int k = col_half + kb + j;
           x[j] = 0.f;
           if (p.init_identity) x[j] = (k == v) ? 1.f : 0.f;
-          else if (h0p != nullptr) x[j] = p.transpose_state ? h0p[v * kHeadDim + k] : h0p[k * kHeadDim + v];
+          else if (h0p != nullptr) x[j] = h0p[k * st_k + v * st_v];
         }
 #pragma unroll
-        for (int j = 0; j < 32; j += 2) {
+        for (int j = 0; j < 16; j += 2) {
           sf[j] = __float_as_uint(x[j] * egl0);
           sf[j + 1] = __float_as_uint(x[j + 1] * egl0);
           sb[j >> 1] = pack2<T>(x[j], x[j + 1]);
         }
-        ptx::tmem_st32(tm + kColS + col_half + kb, sf);
-        ptx::tmem_st16(tm + kColSbf + (col_half + kb) / 2, sb);
-        if (nproc == 0 && p.final_state != nullptr && out_row >= 0) {
-          float* fs = p.final_state + (static_cast<int64_t>(out_row) * p.num_v_heads + hv) * kHeadDim * kHeadDim;
+        ptx::tmem_st16(tm + kColS + col_half + kb, sf);
+        ptx::tmem_st8(tm + kColSbf + (col_half + kb) / 2, sb);
+        if (nproc == 0 && fs_out != nullptr) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const int k = col_half + kb + j;
-            if (p.transpose_state) fs[v * kHeadDim + k] = x[j]; else fs[k * kHeadDim + v] = x[j];
-          }
+          for (int j = 0; j < 16; ++j) fs_out[(col_half + kb + j) * st_k + v * st_v] = x[j];
         }
       }
       ptx::tmem_wait_st();
@@ -504,59 +526,57 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       warp_arrive(&bars[kSScaled], lane);
     }
 
-    float qs[64];  // side warpgroup: s * gamma_c * (Q S0)^T row, kept from D1 until the epilogue
-
-    // Output epilogue of chunk j (side warpgroup): O^T = s gamma .* (Q S0)^T (kept in qs) + D4, transposed
-    // through a shared-memory tile and written with one TMA store (row-masked stores for a ragged tail).
+    // Output epilogue of chunk j (side warpgroup): D4 holds O^T = s gamma .* (Q S0)^T + Vd^T Pg^T; it is
+    // transposed through a shared-memory tile and written with one TMA store (row-masked stores for a
+    // ragged tail).
     auto epilogue = [&](int j, int valid_j, int t0_j) -> bool {
-        if (!(ptx::mbar_wait_warp(&bars[kD4Done], j & 1, status, kTimeout))) return false;
-        ptx::tc_fence_after_sync();
-        if (tid == 128) trace(2, j, 6);
-        T* so = reinterpret_cast<T*>(smem + kOffO + (j & 1) * 16384);
-        // Two output tiles alternate: tile (j & 1) was last used by the TMA store of chunk j - 2, which
-        // must have finished reading it.  Only mbarriers (bounded waits), never a CTA / named barrier.
-        if (j >= 2) {
+      if (!ptx::mbar_wait_warp(&bars[kD4Done], j & 1, status, kTimeout)) return false;
+      ptx::tc_fence_after_sync();
+      if (tid == 128) trace(2, j, 6);
+      T* so = reinterpret_cast<T*>(smem + kOffO + (j & 1) * 16384);
+      // Two output tiles alternate: tile (j & 1) was last used by the TMA store of chunk j - 2, which
+      // must have finished reading it.  Only mbarriers (bounded waits), never a CTA / named barrier.
+      if (j >= 2) {
+        if (tid == 128) {
+          asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+          ptx::mbar_arrive(&bars[kOFree]);
+        }
+        if (!ptx::mbar_wait_warp(&bars[kOFree], j & 1, status, kTimeout)) return false;
+      }
+#pragma unroll 1
+      for (int cb = 0; cb < 64; cb += 16) {
+        uint32_t r[16];
+        ptx::tmem_ld16(tm + kColD4 + cb, r);
+        ptx::tmem_wait_ld();
+#pragma unroll
+        for (int e = 0; e < 16; ++e) so[(cb + e) * kHeadDim + v] = Cvt<T>::from_f32(__uint_as_float(r[e]));
+      }
+      ptx::tc_fence_before_sync();
+      warp_arrive(&bars[kD4Free], lane);
+      if (tid == 128) trace(2, j, 12);
+      ptx::fence_proxy_async_smem();
+      warp_arrive(&bars[kOReady], lane);
+      if (valid_j == kChunk) {
+        if (warp == 4) {  // only the issuing warp waits for the tile to be complete
+          if (!ptx::mbar_wait_warp(&bars[kOReady], j & 1, status, kTimeout)) return false;
           if (tid == 128) {
-            asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
-            ptx::mbar_arrive(&bars[kOFree]);
-          }
-          if (!(ptx::mbar_wait_warp(&bars[kOFree], j & 1, status, kTimeout))) return false;
-        }
-#pragma unroll
-        for (int cb = 0; cb < 64; cb += 32) {
-          uint32_t r[32];
-          ptx::tmem_ld32(tm + kColD4 + cb, r);
-          ptx::tmem_wait_ld();
-#pragma unroll
-          for (int e = 0; e < 32; ++e) so[(cb + e) * kHeadDim + v] = Cvt<T>::from_f32(qs[cb + e] + __uint_as_float(r[e]));
-        }
-        ptx::tc_fence_before_sync();
-        warp_arrive(&bars[kD4Free], lane);
-        if (tid == 192) trace(2, j, 11);
-        if (tid == 128) trace(2, j, 12);
-        ptx::fence_proxy_async_smem();
-        warp_arrive(&bars[kOReady], lane);
-        if (valid_j == kChunk) {
-          if (warp == 4) {  // only the issuing warp waits for the tile to be complete
-            if (!(ptx::mbar_wait_warp(&bars[kOReady], j & 1, status, kTimeout))) return false;
-            if (tid == 128) {
-              ptx::tma_store_3d(&tm_o, so, 0, hv, t0_j);
-              ptx::tma_store_commit();
-            }
-          }
-        } else {
-          if (!(ptx::mbar_wait_warp(&bars[kOReady], j & 1, status, kTimeout))) return false;
-          // ragged tail (always the last chunk of a sequence): row-masked 16-byte stores
-          T* ob = static_cast<T*>(p.o);
-          const int tl = tid - 128;  // 16 threads per row (8 elements each), 8 rows per pass
-          for (int r0 = 0; r0 < valid_j; r0 += 8) {
-            const int row = r0 + (tl >> 4);
-            if (row < valid_j) {
-              const uint4 x = *reinterpret_cast<const uint4*>(so + row * kHeadDim + (tl & 15) * 8);
-              *reinterpret_cast<uint4*>(ob + (static_cast<int64_t>(t0_j + row) * p.num_v_heads + hv) * kHeadDim + (tl & 15) * 8) = x;
-            }
+            ptx::tma_store_3d(&tm_o, so, 0, hv, t0_j);
+            ptx::tma_store_commit();
           }
         }
+      } else {
+        if (!ptx::mbar_wait_warp(&bars[kOReady], j & 1, status, kTimeout)) return false;
+        // ragged tail (always the last chunk of a sequence): row-masked 16-byte stores
+        T* ob = static_cast<T*>(p.o);
+        const int tl = tid - 128;  // 16 threads per row (8 elements each), 8 rows per pass
+        for (int r0 = 0; r0 < valid_j; r0 += 8) {
+          const int row = r0 + (tl >> 4);
+          if (row < valid_j) {
+            const uint4 x = *reinterpret_cast<const uint4*>(so + row * kHeadDim + (tl & 15) * 8);
+            *reinterpret_cast<uint4*>(ob + (static_cast<int64_t>(t0_j + row) * p.num_v_heads + hv) * kHeadDim + (tl & 15) * 8) = x;
+          }
+        }
+      }
       return true;
     };
     int prev_valid = 0, prev_t0 = 0;
@@ -578,105 +598,89 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         if (!(alive = ptx::mbar_wait_warp(&bars[kD1Done], ph, status, kTimeout))) break;
         ptx::tc_fence_after_sync();
         if (tid == 0) trace(1, i, 0);
-#pragma unroll
-        for (int cb = 0; cb < 64; cb += 32) {
-          uint32_t u[32], w[16];
-          ptx::tmem_ld32(tm + kColD1 + cb, u);
+#pragma unroll 1
+        for (int cb = 0; cb < 64; cb += 16) {
+          uint32_t u[16], w[8];
+          ptx::tmem_ld16(tm + kColD1 + cb, u);
           ptx::tmem_wait_ld();
 #pragma unroll
-          for (int j = 0; j < 32; j += 4) {
+          for (int j = 0; j < 16; j += 4) {
             const float4 g4 = *reinterpret_cast<const float4*>(&gs->gamma[cb + j]);
             w[j >> 1] = pack2<T>(-g4.x * __uint_as_float(u[j]), -g4.y * __uint_as_float(u[j + 1]));
             w[(j >> 1) + 1] = pack2<T>(-g4.z * __uint_as_float(u[j + 2]), -g4.w * __uint_as_float(u[j + 3]));
           }
-          ptx::tmem_st16(tm + kColD1 + cb / 2, w);
+          ptx::tmem_st8(tm + kColD1 + cb / 2, w);  // in place: columns cb/2 .. cb/2+7 were already read
         }
         ptx::tmem_wait_st();
         ptx::tc_fence_before_sync();
         warp_arrive(&bars[kWReady], lane);
         if (tid == 0) trace(1, i, 1);
 
-        // ---------------- chain: Vd, V' = rho .* Vd
+        // ---------------- chain: Vd (to the shared-memory tile of MMA4, and v_new) and V' = rho .* Vd
         if (!(alive = ptx::mbar_wait_warp(&bars[kD2Done], ph, status, kTimeout))) break;
         ptx::tc_fence_after_sync();
         if (tid == 0) trace(1, i, 2);
         T* vn = static_cast<T*>(p.v_new);
-        {
-          // both halves of Vd^T are read before the bf16 operands overwrite the same columns
-          uint32_t d0[32], d1[32], vd[32], vp[32];
-          ptx::tmem_ld32(tm + kColD2, d0);
-          ptx::tmem_ld32(tm + kColD2 + 32, d1);
+        T* vn_dst = vn ? vn + (static_cast<int64_t>(t0) * p.num_v_heads + hv) * kHeadDim + v : nullptr;
+        const int64_t vn_stride = static_cast<int64_t>(p.num_v_heads) * kHeadDim;
+        uint8_t* vt = smem + kOffVd + (i & 1) * 16384;
+#pragma unroll 1
+        for (int cb = 0; cb < 64; cb += 16) {
+          uint32_t d[16], vd[8], vp[8];
+          ptx::tmem_ld16(tm + kColD2 + cb, d);
           ptx::tmem_wait_ld();
-          if (tid == 0) trace(1, i, 6);
 #pragma unroll
-          for (int j = 0; j < 32; j += 4) {
-            const float4 r0 = *reinterpret_cast<const float4*>(&gs->rho[j]);
-            const float4 r1 = *reinterpret_cast<const float4*>(&gs->rho[32 + j]);
-            const float a0 = __uint_as_float(d0[j]), a1 = __uint_as_float(d0[j + 1]);
-            const float a2 = __uint_as_float(d0[j + 2]), a3 = __uint_as_float(d0[j + 3]);
-            const float b0 = __uint_as_float(d1[j]), b1 = __uint_as_float(d1[j + 1]);
-            const float b2 = __uint_as_float(d1[j + 2]), b3 = __uint_as_float(d1[j + 3]);
+          for (int j = 0; j < 16; j += 4) {
+            const float4 r4 = *reinterpret_cast<const float4*>(&gs->rho[cb + j]);
+            const float a0 = __uint_as_float(d[j]), a1 = __uint_as_float(d[j + 1]);
+            const float a2 = __uint_as_float(d[j + 2]), a3 = __uint_as_float(d[j + 3]);
             vd[j >> 1] = pack2<T>(a0, a1);
             vd[(j >> 1) + 1] = pack2<T>(a2, a3);
-            vd[16 + (j >> 1)] = pack2<T>(b0, b1);
-            vd[16 + (j >> 1) + 1] = pack2<T>(b2, b3);
-            vp[j >> 1] = pack2<T>(a0 * r0.x, a1 * r0.y);
-            vp[(j >> 1) + 1] = pack2<T>(a2 * r0.z, a3 * r0.w);
-            vp[16 + (j >> 1)] = pack2<T>(b0 * r1.x, b1 * r1.y);
-            vp[16 + (j >> 1) + 1] = pack2<T>(b2 * r1.z, b3 * r1.w);
+            vp[j >> 1] = pack2<T>(a0 * r4.x, a1 * r4.y);
+            vp[(j >> 1) + 1] = pack2<T>(a2 * r4.z, a3 * r4.w);
           }
-          if (tid == 0) trace(1, i, 7);
-          // V' (A operand of MMA3, on the chain) stays in tensor memory; Vd (A operand of the deferred
-          // MMA4) goes to a swizzled shared-memory tile so that D2 is free for the next chunk at once
-          ptx::tmem_st32(tm + kColD2 + 32, vp);
+          ptx::tmem_st8(tm + kColD2 + cb / 2, vp);  // V' in place (A operand of MMA3, on the chain)
           if (!kStateOnly) {
-            uint8_t* vt = smem + kOffVd + (i & 1) * 16384;
-#pragma unroll
-            for (int c16 = 0; c16 < 8; ++c16)
-              *reinterpret_cast<uint4*>(vt + ptx::sw128_offset(v, c16)) =
-                  make_uint4(vd[c16 * 4], vd[c16 * 4 + 1], vd[c16 * 4 + 2], vd[c16 * 4 + 3]);
-            ptx::fence_proxy_async_smem();
+            *reinterpret_cast<uint4*>(vt + ptx::sw128_offset(v, cb >> 3)) = make_uint4(vd[0], vd[1], vd[2], vd[3]);
+            *reinterpret_cast<uint4*>(vt + ptx::sw128_offset(v, (cb >> 3) + 1)) = make_uint4(vd[4], vd[5], vd[6], vd[7]);
           }
-          if (tid == 0) trace(1, i, 8);
-          if (vn != nullptr) {
-            T* dst = vn + (static_cast<int64_t>(t0) * p.num_v_heads + hv) * kHeadDim + v;
-            const int64_t stride = static_cast<int64_t>(p.num_v_heads) * kHeadDim;
+          if (vn_dst != nullptr) {
             const T* vdt = reinterpret_cast<const T*>(vd);
 #pragma unroll
-            for (int j = 0; j < 64; ++j)
-              if (j < valid) dst[j * stride] = vdt[j];
+            for (int j = 0; j < 16; ++j)
+              if (cb + j < valid) vn_dst[(cb + j) * vn_stride] = vdt[j];
           }
         }
+        if (!kStateOnly) ptx::fence_proxy_async_smem();
         ptx::tmem_wait_st();
-        if (tid == 0) trace(1, i, 9);
         ptx::tc_fence_before_sync();
         warp_arrive(&bars[kVdReady], lane);
         if (tid == 0) trace(1, i, 3);
-      } else {
-        if (!kStateOnly) {
-          // ---------------- side: keep s * gamma_c * (Q S0)^T
-          if (tid == 128) trace(2, i, 1);
-          if (!(alive = ptx::mbar_wait_warp(&bars[kD1Done], ph, status, kTimeout))) break;
-          ptx::tc_fence_after_sync();
-          if (tid == 128) trace(2, i, 2);
+      } else if (!kStateOnly) {
+        // ---------------- side: D4 <- s gamma .* (Q S0)^T; MMA4 accumulates Vd^T Pg^T on top later
+        if (tid == 128) trace(2, i, 1);
+        if (!(alive = ptx::mbar_wait_warp(&bars[kD1Done], ph, status, kTimeout))) break;
+        ptx::tc_fence_after_sync();
+        if (tid == 128) trace(2, i, 2);
+#pragma unroll 1
+        for (int cb = 0; cb < 64; cb += 16) {
+          uint32_t r[16];
+          ptx::tmem_ld16(tm + kColD1 + 64 + cb, r);
+          ptx::tmem_wait_ld();
 #pragma unroll
-          for (int cb = 0; cb < 64; cb += 32) {
-            uint32_t r[32];
-            ptx::tmem_ld32(tm + kColD1 + 64 + cb, r);
-            ptx::tmem_wait_ld();
-#pragma unroll
-            for (int j = 0; j < 32; j += 4) {
-              const float4 g4 = *reinterpret_cast<const float4*>(&gs->gamma[cb + j]);
-              qs[cb + j] = p.scale * g4.x * __uint_as_float(r[j]);
-              qs[cb + j + 1] = p.scale * g4.y * __uint_as_float(r[j + 1]);
-              qs[cb + j + 2] = p.scale * g4.z * __uint_as_float(r[j + 2]);
-              qs[cb + j + 3] = p.scale * g4.w * __uint_as_float(r[j + 3]);
-            }
+          for (int j = 0; j < 16; j += 4) {
+            const float4 g4 = *reinterpret_cast<const float4*>(&gs->gamma[cb + j]);
+            r[j] = __float_as_uint(p.scale * g4.x * __uint_as_float(r[j]));
+            r[j + 1] = __float_as_uint(p.scale * g4.y * __uint_as_float(r[j + 1]));
+            r[j + 2] = __float_as_uint(p.scale * g4.z * __uint_as_float(r[j + 2]));
+            r[j + 3] = __float_as_uint(p.scale * g4.w * __uint_as_float(r[j + 3]));
           }
-          ptx::tc_fence_before_sync();
-          warp_arrive(&bars[kD1Free], lane);
-          if (tid == 128) trace(2, i, 3);
+          ptx::tmem_st16(tm + kColD4 + cb, r);
         }
+        ptx::tmem_wait_st();
+        ptx::tc_fence_before_sync();
+        warp_arrive(&bars[kD1Free], lane);
+        if (tid == 128) trace(2, i, 3);
       }
 
       // ---------------- both: state convert after MMA3 (this warpgroup's 64 columns)
@@ -685,44 +689,36 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       if (tid == 0) trace(1, i, 4);
       if (tid == 128) trace(2, i, 4);
       const bool last = (i + 1 == nproc);
-      float egl_next = 1.f;
-      if (!last) {
-        if (!(alive = ptx::mbar_wait_warp(&bars[kFull0 + (s ^ 1)], ((i + 1) >> 1) & 1, status, kTimeout))) break;
-        egl_next = gates_of(s ^ 1)->egl;
-      }
-      T* hout = static_cast<T*>(p.h);
       if (last) {
-        if (p.final_state != nullptr && out_row >= 0) {
-          float* fs = p.final_state + (static_cast<int64_t>(out_row) * p.num_v_heads + hv) * kHeadDim * kHeadDim;
-#pragma unroll
-          for (int kb = 0; kb < 64; kb += 32) {
-            uint32_t sf[32];
-            ptx::tmem_ld32(tm + kColS + col_half + kb, sf);
+        if (fs_out != nullptr) {
+#pragma unroll 1
+          for (int kb = 0; kb < 64; kb += 16) {
+            uint32_t sf[16];
+            ptx::tmem_ld16(tm + kColS + col_half + kb, sf);
             ptx::tmem_wait_ld();
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              const int k = col_half + kb + j;
-              if (p.transpose_state) fs[v * kHeadDim + k] = __uint_as_float(sf[j]);
-              else fs[k * kHeadDim + v] = __uint_as_float(sf[j]);
-            }
+            for (int j = 0; j < 16; ++j) fs_out[(col_half + kb + j) * st_k + v * st_v] = __uint_as_float(sf[j]);
           }
         }
       } else {
-        // (a) critical: bf16 copy of the new state -> MMA1 of the next chunk may start
-#pragma unroll
-        for (int kb = 0; kb < 64; kb += 32) {
-          uint32_t sf[32], sb[16];
-          ptx::tmem_ld32(tm + kColS + col_half + kb, sf);
+        if (!(alive = ptx::mbar_wait_warp(&bars[kFull0 + (s ^ 1)], ((i + 1) >> 1) & 1, status, kTimeout))) break;
+        const float egl_next = gates_of(s ^ 1)->egl;
+        T* hp = p.h ? static_cast<T*>(p.h) + ((chunk_base + chunk + 1) * p.num_v_heads + hv) * kHeadDim * kHeadDim + v
+                    : nullptr;
+        // (a) critical: 16-bit copy of the new state -> MMA1 of the next chunk may start
+#pragma unroll 1
+        for (int kb = 0; kb < 64; kb += 16) {
+          uint32_t sf[16], sb[8];
+          ptx::tmem_ld16(tm + kColS + col_half + kb, sf);
           ptx::tmem_wait_ld();
 #pragma unroll
-          for (int j = 0; j < 32; j += 2) sb[j >> 1] = pack2<T>(__uint_as_float(sf[j]), __uint_as_float(sf[j + 1]));
-          ptx::tmem_st16(tm + kColSbf + (col_half + kb) / 2, sb);
-          if (hout != nullptr) {
+          for (int j = 0; j < 16; j += 2) sb[j >> 1] = pack2<T>(__uint_as_float(sf[j]), __uint_as_float(sf[j + 1]));
+          ptx::tmem_st8(tm + kColSbf + (col_half + kb) / 2, sb);
+          if (hp != nullptr) {
             // h[chunk + 1] = state entering the next chunk, [K][V] layout
-            T* hp = hout + ((chunk_base + chunk + 1) * p.num_v_heads + hv) * kHeadDim * kHeadDim;
             const T* sbh = reinterpret_cast<const T*>(sb);
 #pragma unroll
-            for (int j = 0; j < 32; ++j) hp[(col_half + kb + j) * kHeadDim + v] = sbh[j];
+            for (int j = 0; j < 16; ++j) hp[(col_half + kb + j) * kHeadDim] = sbh[j];
           }
         }
         ptx::tmem_wait_st();
@@ -730,26 +726,23 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         warp_arrive(&bars[kSbfReady], lane);
         if (tid == 0) trace(1, i, 5);
         if (tid == 128) trace(2, i, 5);
-        if (tid == 192) trace(2, i, 13);
         // (b) off the critical path: decay of the fp32 state for the next chunk (needed by MMA3 only)
-#pragma unroll
-        for (int kb = 0; kb < 64; kb += 32) {
-          uint32_t sf[32];
-          ptx::tmem_ld32(tm + kColS + col_half + kb, sf);
+#pragma unroll 1
+        for (int kb = 0; kb < 64; kb += 16) {
+          uint32_t sf[16];
+          ptx::tmem_ld16(tm + kColS + col_half + kb, sf);
           ptx::tmem_wait_ld();
 #pragma unroll
-          for (int j = 0; j < 32; ++j) sf[j] = __float_as_uint(__uint_as_float(sf[j]) * egl_next);
-          ptx::tmem_st32(tm + kColS + col_half + kb, sf);
+          for (int j = 0; j < 16; ++j) sf[j] = __float_as_uint(__uint_as_float(sf[j]) * egl_next);
+          ptx::tmem_st16(tm + kColS + col_half + kb, sf);
         }
         ptx::tmem_wait_st();
         ptx::tc_fence_before_sync();
         warp_arrive(&bars[kSScaled], lane);
       }
-
-      // The stage is released BEFORE the epilogue (which only needs registers and the Vd/Pg tiles), so the
-      // producer can refill it while MMA4 / the output store of this chunk are still in flight.
+      // The stage is released here: what follows for this chunk (MMA4, output store) only needs the
+      // Vd / Pg tiles and tensor memory, so the producer can refill the stage already.
       warp_arrive(&bars[kEmpty0 + s], lane);
-
       prev_valid = valid;
       prev_t0 = t0;
     }
@@ -758,13 +751,11 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     // h[first chunk] = initial state
     if (p.h != nullptr && nproc > 0 && wg == 0) {
       T* hp = static_cast<T*>(p.h) + ((chunk_base + first_chunk) * p.num_v_heads + hv) * kHeadDim * kHeadDim;
-      const float* h0p = (!p.init_identity && p.h0 != nullptr)
-                             ? p.h0 + (static_cast<int64_t>(seq) * p.num_v_heads + hv) * kHeadDim * kHeadDim
-                             : nullptr;
+#pragma unroll 4
       for (int k = 0; k < kHeadDim; ++k) {
         float x = 0.f;
         if (p.init_identity) x = (k == v) ? 1.f : 0.f;
-        else if (h0p != nullptr) x = p.transpose_state ? h0p[v * kHeadDim + k] : h0p[k * kHeadDim + v];
+        else if (h0p != nullptr) x = h0p[k * st_k + v * st_v];
         hp[k * kHeadDim + v] = Cvt<T>::from_f32(x);
       }
     }
@@ -773,6 +764,11 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   ptx::tc_fence_before_sync();
   __syncthreads();
   if (warp == 8) ptx::tmem_dealloc(tmem, 512);
+  if (cta_trace && tid == 0) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    p.trace[cta_slot + 1] = static_cast<long long>(t);
+  }
 }
 
 }  // namespace
@@ -787,16 +783,23 @@ int launch_chunk_fwd(const FwdParams& p, const void* q, const void* k, const voi
   if ((rc = make_tmap_3d(&tm_a, A, total_tokens, p.num_v_heads, 64, 64, 64, true, is_bf16)) != QLA_OK) return rc;
   if ((rc = make_tmap_3d(&tm_o, state_only ? v : p.o, total_tokens, p.num_v_heads, kHeadDim, 64, 128, false, is_bf16)) != QLA_OK) return rc;
   const unsigned grid = static_cast<unsigned>(p.num_seqs) * p.num_v_heads;
-#define QLA_LAUNCH_FWD(T, SO)                                                                              \
+#define QLA_LAUNCH_FWD(T, SO, TR)                                                                          \
   do {                                                                                                     \
-    QLA_CHECK_CUDA(cudaFuncSetAttribute(chunk_fwd_kernel<T, SO>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+    QLA_CHECK_CUDA(cudaFuncSetAttribute(chunk_fwd_kernel<T, SO, TR>,                                       \
+                                        cudaFuncAttributeMaxDynamicSharedMemorySize,                       \
                                         static_cast<int>(kSmemBytes)));                                    \
-    chunk_fwd_kernel<T, SO><<<grid, kThreads, kSmemBytes, stream>>>(tm_q, tm_k, tm_v, tm_a, tm_o, p);      \
+    chunk_fwd_kernel<T, SO, TR><<<grid, kThreads, kSmemBytes, stream>>>(tm_q, tm_k, tm_v, tm_a, tm_o, p);  \
   } while (0)
+  // the traced variant is a separate instantiation so that normal launches carry no tracing code
+  const bool traced = p.trace != nullptr;
   if (is_bf16) {
-    if (state_only) QLA_LAUNCH_FWD(__nv_bfloat16, true); else QLA_LAUNCH_FWD(__nv_bfloat16, false);
+    if (traced) { if (state_only) QLA_LAUNCH_FWD(__nv_bfloat16, true, true); else QLA_LAUNCH_FWD(__nv_bfloat16, false, true); }
+    else if (state_only) QLA_LAUNCH_FWD(__nv_bfloat16, true, false);
+    else QLA_LAUNCH_FWD(__nv_bfloat16, false, false);
   } else {
-    if (state_only) QLA_LAUNCH_FWD(__half, true); else QLA_LAUNCH_FWD(__half, false);
+    if (traced) { if (state_only) QLA_LAUNCH_FWD(__half, true, true); else QLA_LAUNCH_FWD(__half, false, true); }
+    else if (state_only) QLA_LAUNCH_FWD(__half, true, false);
+    else QLA_LAUNCH_FWD(__half, false, false);
   }
 #undef QLA_LAUNCH_FWD
   QLA_CHECK_CUDA(cudaGetLastError());

@@ -37,6 +37,7 @@ struct FwdParams {
   int zero_v;                   // treat V as 0
   float scale;
   long long* trace;             // optional phase trace (see qla_set_trace_buffer), NULL in normal use
+  long long trace_count;        // capacity of `trace` in entries
 };
 
 struct BwdParams {
@@ -71,6 +72,7 @@ int launch_chunk_bwd(const BwdParams& p, int total_chunks_upper, bool is_bf16, c
 // Trace layout: [role 0..2][chunk 4..7][16 events] clock64 stamps of CTA 0.
 constexpr int kTraceRoles = 3, kTraceChunks = 4, kTraceEvents = 16, kTraceFirstChunk = 4;
 long long* current_trace_buffer();
+long long current_trace_count();
 
 int launch_chunk_tables(const int32_t* cu, int n, int32_t* pair_offsets, int32_t* chunk_offsets,
                         cudaStream_t stream);

@@ -59,8 +59,11 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // Bounded wait: gives up after `kSpinLimit` polls (each try_wait itself blocks for a
 // hardware-defined interval), records the failure in *status and returns false so that the
 // caller can leave its loop.  A healthy kernel never gets near the limit.
+// The first poll is inlined (the barrier has usually completed already); the polling loop is a single
+// non-inlined copy: there are dozens of call sites and the per-chunk code of the chunk kernels has to
+// fit the instruction cache.
 constexpr uint32_t kSpinLimit = 1u << 20;
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int code) {
+static __device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, int* status, int code) {
   for (uint32_t i = 0; i < kSpinLimit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((i & 1023u) == 1023u && status != nullptr && *reinterpret_cast<volatile int*>(status) != 0)
@@ -68,6 +71,10 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* s
   }
   if (status != nullptr) atomicCAS(status, 0, code);
   return false;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  return mbar_wait_slow(bar, parity, status, code);
 }
 
 // Low-latency variant for a single latency-critical thread (the MMA issuer): polls with
@@ -86,13 +93,17 @@ __device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-__device__ __forceinline__ bool mbar_spin(uint64_t* bar, uint32_t parity, int* status, int code) {
+static __device__ __noinline__ bool mbar_spin_slow(uint64_t* bar, uint32_t parity, int* status, int code) {
   for (uint32_t i = 0; i < (kSpinLimit << 4); ++i) {
     if (mbar_test_wait(bar, parity)) return true;
     if ((i & 16383u) == 16383u && status != nullptr && *reinterpret_cast<volatile int*>(status) != 0) return false;
   }
   if (status != nullptr) atomicCAS(status, 0, code);
   return false;
+}
+__device__ __forceinline__ bool mbar_spin(uint64_t* bar, uint32_t parity, int* status, int code) {
+  if (mbar_test_wait(bar, parity)) return true;
+  return mbar_spin_slow(bar, parity, status, code);
 }
 
 // Same wait executed by a converged warp; the verdict is made warp-uniform so that no lane leaves a
@@ -183,6 +194,11 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
         "=r"(r[30]), "=r"(r[31])
       : "r"(taddr)
       : "memory");
+}
+__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t (&r)[8]) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"r"(taddr),
+               "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+               : "memory");
 }
 __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
   asm volatile(

@@ -247,7 +247,8 @@ QLA_API int qla_cp_chain(const QlaCpChainArgs* args, void* stream);
  * Tracing (no counterpart in the reference, whose profiling is torch.profiler around whole kernels,
  * flash_qla/utils/profiler.py:8-25): when a device buffer of at least 192 int64 is registered, CTA 0 of
  * every later chunk-scan launch stamps clock64() at its phase boundaries for chunks 4..7, laid out as
- * [role: 0 MMA issuer, 1 chain warpgroup, 2 side warpgroup][chunk][16 events].  NULL switches it off.
+ * [role: 0 MMA issuer, 1 chain warpgroup, 2 side warpgroup][chunk][16 events].  If the buffer holds
+ * 192 + 3 * CTAs entries, every CTA also records (start ns, end ns, SM id) there.  NULL switches it off.
  */
 QLA_API int qla_set_trace_buffer(long long* device_buffer, size_t count);
 
