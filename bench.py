@@ -170,7 +170,10 @@ def run_prefill(args, rank, world, device, varlen=False):
         return fq.chunk_gated_delta_rule_fwd(dev["q"], dev["k"], dev["v"], dev["g"], dev["beta"],
                                              initial_state=h0, cu_seqlens=cu_dev, output_final_state=True)
 
-    launches_per_step = fq.chunk.launches_per_forward(varlen=cu is not None)
+    from flashqla_b200 import cp as _cp
+    plan_lens = my_lens if varlen else [T]
+    use_cp = _cp.get_plan(plan_lens, Hv, device).use_cp
+    launches_per_step = fq.chunk.launches_per_forward(varlen=cu is not None, use_cp=use_cp)
     with ClockSampler(torch.cuda.current_device() if device.index is None else device.index) as cs:
         ms = timed(step, args.steps, args.warmup, world, device)
     fq.check_device_status()
@@ -212,6 +215,7 @@ def run_prefill(args, rank, world, device, varlen=False):
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_step, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": workload, "sharding": f"v-heads/{world}" if not varlen else f"sequences/{world}",
+                   "context_parallel": use_cp,
                    "l2": "inputs (>= 0.8 GB per step) exceed the 126 MB L2; no flush needed",
                    "tokens": total_tokens},
         "clocks": cs.summary(),
