@@ -96,6 +96,7 @@ EXPORTS = {
     "qla_recurrent_update": (C.c_int, [C.POINTER(QlaRecurrentArgs), C.c_void_p]),
     "qla_chunk_fwd_workspace_bytes": (C.c_size_t, [C.POINTER(QlaChunkFwdArgs)]),
     "qla_chunk_fwd": (C.c_int, [C.POINTER(QlaChunkFwdArgs), C.c_void_p]),
+    "qla_chunk_fwd_noalloc": (C.c_int, [C.POINTER(QlaChunkFwdArgs), C.c_void_p]),
     "qla_chunk_bwd_workspace_bytes": (C.c_size_t, [C.POINTER(QlaChunkBwdArgs)]),
     "qla_chunk_bwd": (C.c_int, [C.POINTER(QlaChunkBwdArgs), C.c_void_p]),
     "qla_cp_plan": (C.c_int, [C.POINTER(QlaCpPlanArgs), C.c_void_p]),

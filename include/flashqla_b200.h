@@ -156,6 +156,19 @@ QLA_API size_t qla_chunk_fwd_workspace_bytes(const QlaChunkFwdArgs* args);
 QLA_API int qla_chunk_fwd(const QlaChunkFwdArgs* args, void* stream);
 
 /*
+ * qla_chunk_fwd for callers that cannot allocate device memory.  No counterpart in the reference (its
+ * Python layer allocates freely through torch).  Meant for hosts that reserve the whole GPU at start-up
+ * and forbid cudaMalloc afterwards: the chunk tables qla_chunk_fwd would put into a caller-provided
+ * workspace live in a fixed device array inside the library (about 32 KiB per GPU, kept until exit).
+ * args->workspace / workspace_bytes are ignored.  Calls with cu_seqlens and more than
+ * QLA_NOALLOC_MAX_SEQS sequences are rejected with QLA_ERR_INVALID_ARG.  All calls on one GPU share the
+ * array: calls that can overlap on the GPU race.  The first call on each GPU resolves the array's device
+ * address and should be made before any stream capture.  No cudaMalloc / cudaFree inside.
+ */
+#define QLA_NOALLOC_MAX_SEQS 4096
+QLA_API int qla_chunk_fwd_noalloc(const QlaChunkFwdArgs* args, void* stream);
+
+/*
  * Chunked backward: dq, dk, dv, dbeta, dg (w.r.t. the raw gate) and dh0.
  * Replaces chunk_gated_delta_rule_bwd, flash_qla/ops/gated_delta_rule/chunk/__init__.py:89-182
  * (fused_gdr_bwd chunk/hopper/fused_bwd.py:898, the decomposed stages chunk/blackwell/bwd_sm12x.py:768-780,
