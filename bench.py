@@ -180,9 +180,8 @@ def run_prefill(args, rank, world, device, varlen=False):
 
     # ---- dominant kernel alone (the chunk scan), for the roofline entry
     g_cs, A, o, _, fs = step()
-    def scan_only():
-        fq.chunk.forward_scan_only(dev["q"], dev["k"], dev["v"], dev["beta"], g_cs, A, o, fs, initial_state=h0,
-                                   cu_seqlens=cu_dev)
+    scan_only = fq.chunk.make_scan_only(dev["q"], dev["k"], dev["v"], dev["beta"], g_cs, A, o, fs,
+                                        initial_state=h0, cu_seqlens=cu_dev)
     ms_scan = timed(scan_only, args.steps, args.warmup, world, device) / args.steps
 
     # ---- end to end through the public API with host buffers
@@ -336,7 +335,7 @@ def main():
     else:
         line = run_recurrent(args, rank, world, device, verify=args.workload == "verify")
     if rank == 0:
-        if not args.no_cpu_baseline and args.workload == "prefill_fwd":
+        if not args.no_cpu_baseline and args.workload == "prefill_fwd" and world == 1:
             tps, sec = cpu_prefill_sample(args.cpu_sample_tokens)
             line["cpu_baseline"] = {
                 "value": tps, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",

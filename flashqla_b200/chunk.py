@@ -82,13 +82,38 @@ def launches_per_forward(varlen: bool, use_cp: bool = False) -> int:
     return 3 if varlen else 2
 
 
+def make_scan_only(q, k, v, beta, g_cumsum, A, o, final_state, initial_state=None, cu_seqlens=None,
+                   scale=None, auto_cp=True):
+    """Return a callable that launches only the chunk scan (the dominant kernel) exactly as a forward
+    call with these arguments would: over context-parallel segments when the planner chooses them
+    (segment initial states are computed once, here), else over whole sequences.  ``g_cumsum`` and ``A``
+    come from an earlier forward.  Used to time that kernel by itself."""
+    dev = k.device
+    B, T, Hv = k.shape[0], k.shape[1], beta.shape[2]
+    scale = q.shape[-1] ** -0.5 if scale is None else scale
+    cu = None if cu_seqlens is None else cu_seqlens.to(device=dev, dtype=torch.int32).contiguous()
+    lens = host_seqlens(cu_seqlens) if cu_seqlens is not None else [T] * B
+    plan = cp.get_plan(lens, Hv, dev) if auto_cp else None
+    if plan is not None and plan.use_cp:
+        cp_h0 = cp.segment_initial_states(plan, k, v, beta, g_cumsum, A, initial_state, scale, _launch_fwd)
+
+        def run():
+            _launch_fwd(q, k, v, None, beta, cp_h0, plan.dev["cu"], g_cumsum, A, o, None, None, final_state,
+                        scale, flags=_cabi.CHUNK_SKIP_PREPARE, seq_map=plan.dev["seg_raw"],
+                        num_seqs=len(plan.seg_next))
+        return run
+
+    def run():
+        _launch_fwd(q, k, v, None, beta, initial_state, cu, g_cumsum, A, o, None, None, final_state, scale,
+                    flags=_cabi.CHUNK_SKIP_PREPARE)
+    return run
+
+
 def forward_scan_only(q, k, v, beta, g_cumsum, A, o, final_state, initial_state=None, cu_seqlens=None,
                       scale=None):
-    """Launch only the chunk scan (the dominant kernel) with ``g_cumsum`` and ``A`` from an earlier
-    forward; used to time that kernel by itself."""
-    cu = None if cu_seqlens is None else cu_seqlens.to(torch.int32)
-    _launch_fwd(q, k, v, None, beta, initial_state, cu, g_cumsum, A, o, None, None, final_state,
-                q.shape[-1] ** -0.5 if scale is None else scale, flags=_cabi.CHUNK_SKIP_PREPARE)
+    """Launch the chunk scan once over whole sequences (no context parallelism)."""
+    make_scan_only(q, k, v, beta, g_cumsum, A, o, final_state, initial_state, cu_seqlens, scale,
+                   auto_cp=False)()
 
 
 def chunk_gated_delta_rule_fwd(

@@ -9,9 +9,11 @@
 // v-heads that share it, so K is fetched once per group.  K K^T for both chunks is a single
 // tcgen05.mma (M = N = K = 128, operands straight from the TMA-written 128B-swizzled tile,
 // accumulator in tensor memory); thread t then owns row t of the product (TMEM lane t) and keeps its
-// chunk's 64 columns in registers for every v-head.  The triangular inverse runs on CUDA cores in
-// fp32: L goes to shared memory and thread `col` computes column `col` of the inverse by forward
-// substitution with the L entries broadcast from shared memory.
+// chunk's 64 columns in registers for every v-head.  The inverse of the unit-lower-triangular I + L is
+// blocked: the four 16 x 16 diagonal blocks by fp32 forward substitution (one thread per column), then
+// X21 = -X22 (L21 X11) at block size 16 and again at block size 32 with mma.sync m16n8k8 products on
+// fp32 shared-memory tiles, each operand split into two TF32 parts (3xTF32) so that the inverse keeps
+// fp32-level accuracy before it is rounded to the 16-bit output.
 #include "chunk_params.cuh"
 
 namespace qla {
@@ -20,26 +22,66 @@ namespace qla {
 namespace {
 
 constexpr int kLStride = 68;  // floats per L row: 16-byte aligned rows, conflict-free float4 stores
+constexpr int kXStride = 68;  // the two 64 x 68 fp32 X tiles (34 816 B) overlay the dead 32 KiB K tile
+constexpr int kTStride = 40;  // 32 columns + 8: conflict-free fragment loads
 
-template <int BASE>
-__device__ __forceinline__ void solve_column(const float* __restrict__ L, int col, float (&X)[64]) {
-  // X = column `col` of (I + L)^-1 restricted to rows >= BASE (rows < BASE are zero for col >= BASE).
+__device__ __forceinline__ uint32_t to_tf32(float x) {
+  uint32_t r;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+  return r;
+}
+__device__ __forceinline__ void mma_tf32(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+      "{%0, %1, %2, %3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+// One warp: C[16 x 8*NT] = A[16 x K] * B[K x 8*NT] on fp32 shared-memory tiles (row-major, strides in
+// floats).  A points at the first of the 16 rows, B at row 0 / first column of the K x N block.
+template <int NT>
+__device__ __forceinline__ void warp_gemm_tf32(float (&acc)[NT][4], const float* A, int lda, const float* B,
+                                               int ldb, int K) {
+  const int lane = threadIdx.x & 31, g = lane >> 2, c = lane & 3;
 #pragma unroll
-  for (int i = 0; i < 64; ++i) X[i] = (i == col) ? 1.f : 0.f;
+  for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-  for (int i = BASE + 1; i < 64; ++i) {
-    float acc0 = 0.f, acc1 = 0.f;
-    const float* row = L + i * kLStride;
+    for (int e = 0; e < 4; ++e) acc[nt][e] = 0.f;
+#pragma unroll 1
+  for (int k0 = 0; k0 < K; k0 += 8) {
+    // 3xTF32: x = hi + lo with hi = tf32(x), lo = tf32(x - hi); hi*hi + hi*lo + lo*hi keeps the products
+    // at fp32-level accuracy (the dropped lo*lo term is ~2^-22 relative)
+    const float af[4] = {A[g * lda + k0 + c], A[(g + 8) * lda + k0 + c], A[g * lda + k0 + c + 4],
+                         A[(g + 8) * lda + k0 + c + 4]};
+    uint32_t ah[4], al[4];
 #pragma unroll
-    for (int j4 = BASE; j4 < i; j4 += 4) {
-      const float4 l = *reinterpret_cast<const float4*>(row + j4);
-      acc0 = fmaf(l.x, X[j4], acc0);
-      if (j4 + 1 < i) acc1 = fmaf(l.y, X[j4 + 1], acc1);
-      if (j4 + 2 < i) acc0 = fmaf(l.z, X[j4 + 2], acc0);
-      if (j4 + 3 < i) acc1 = fmaf(l.w, X[j4 + 3], acc1);
+    for (int e = 0; e < 4; ++e) {
+      ah[e] = to_tf32(af[e]);
+      al[e] = to_tf32(af[e] - __uint_as_float(ah[e]));
     }
-    X[i] -= acc0 + acc1;
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      const float bf0 = B[(k0 + c) * ldb + nt * 8 + g], bf1 = B[(k0 + c + 4) * ldb + nt * 8 + g];
+      const uint32_t bh0 = to_tf32(bf0), bh1 = to_tf32(bf1);
+      const uint32_t bl0 = to_tf32(bf0 - __uint_as_float(bh0)), bl1 = to_tf32(bf1 - __uint_as_float(bh1));
+      mma_tf32(acc[nt], al, bh0, bh1);
+      mma_tf32(acc[nt], ah, bl0, bl1);
+      mma_tf32(acc[nt], ah, bh0, bh1);
+    }
   }
+}
+// Store a warp's 16 x 8*NT accumulator tile, negated or not, to a row-major fp32 tile.
+template <int NT>
+__device__ __forceinline__ void store_tile(float* D, int ldd, const float (&acc)[NT][4], float sign) {
+  const int lane = threadIdx.x & 31, g = lane >> 2, c = lane & 3;
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) {
+    *reinterpret_cast<float2*>(D + g * ldd + nt * 8 + 2 * c) = make_float2(sign * acc[nt][0], sign * acc[nt][1]);
+    *reinterpret_cast<float2*>(D + (g + 8) * ldd + nt * 8 + 2 * c) = make_float2(sign * acc[nt][2], sign * acc[nt][3]);
+  }
+}
+__device__ __forceinline__ void pair_sync(int ci) {  // the two warps that own one chunk
+  asm volatile("bar.sync %0, 64;" ::"r"(ci + 1) : "memory");
 }
 
 template <typename T>
@@ -73,7 +115,9 @@ __global__ void __launch_bounds__(128) kkt_solve_kernel(const __grid_constant__ 
 
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* sK = smem_raw + ((1024u - (ptx::smem_u32(smem_raw) & 1023u)) & 1023u);
-  float* sL = reinterpret_cast<float*>(sK + 32768);  // [2][64][kLStride]
+  float* sL = reinterpret_cast<float*>(sK + 2 * 64 * kXStride * sizeof(float));  // [2][64][kLStride]
+  float* sX = reinterpret_cast<float*>(sK);          // [2][64][kXStride]: the K tile is dead once K K^T is in TMEM
+  float* sT = sL + 2 * 64 * kLStride;                // [2][32][kTStride] products L21 X11
   __shared__ __align__(16) float s_g[128];
   __shared__ float s_part[4];
   __shared__ uint64_t bar_tma, bar_mma;
@@ -173,14 +217,69 @@ __global__ void __launch_bounds__(128) kkt_solve_kernel(const __grid_constant__ 
     }
     __syncthreads();
 
-    float X[64];
-    if (warp & 1) solve_column<32>(Lc, c, X); else solve_column<0>(Lc, c, X);
-
-    const int64_t row_tok0 = static_cast<int64_t>(tok0) + ci * 64;
+    // ---- blocked inverse of I + L for this chunk (64 threads = warps 2 ci, 2 ci + 1)
+    float* Xc = sX + ci * 64 * kXStride;
+    float* Tc = sT + ci * 32 * kTStride;
+    const int wl = warp & 1;  // warp within the chunk
+    {
+      // zero the tile, then the four 16 x 16 diagonal blocks: thread = (block, column)
+#pragma unroll 1
+      for (int j4 = 0; j4 < kXStride; j4 += 4) *reinterpret_cast<float4*>(Xc + c * kXStride + j4) = make_float4(0.f, 0.f, 0.f, 0.f);
+      pair_sync(ci);
+      const int b0 = (c >> 4) * 16, cc = c & 15;
+      float x[16];
 #pragma unroll
-    for (int i = 0; i < 64; ++i) {
-      if (row_tok0 + i < seq_end)
-        Ab[((row_tok0 + i) * p.num_v_heads + hv) * 64 + c] = Cvt<T>::from_f32(X[i]);
+      for (int i = 0; i < 16; ++i) {
+        float acc = (i == cc) ? 1.f : 0.f;
+#pragma unroll
+        for (int j = 0; j < i; ++j) acc -= Lc[(b0 + i) * kLStride + b0 + j] * x[j];
+        x[i] = acc;
+      }
+#pragma unroll
+      for (int i = 0; i < 16; ++i) Xc[(b0 + i) * kXStride + b0 + cc] = x[i];
+    }
+    pair_sync(ci);
+    {
+      // block size 16: X[R, C] = -X[R, R] (L[R, C] X[C, C]) for (R, C) = (16, 0) and (48, 32); one per warp
+      const int C0 = 32 * wl, R0 = C0 + 16;
+      float acc[2][4];
+      warp_gemm_tf32<2>(acc, Lc + R0 * kLStride + C0, kLStride, Xc + C0 * kXStride + C0, kXStride, 16);
+      float* Tw = Tc + wl * 16 * kTStride;
+      store_tile<2>(Tw, kTStride, acc, 1.f);
+      __syncwarp();
+      warp_gemm_tf32<2>(acc, Xc + R0 * kXStride + R0, kXStride, Tw, kTStride, 16);
+      store_tile<2>(Xc + R0 * kXStride + C0, kXStride, acc, -1.f);
+    }
+    pair_sync(ci);
+    {
+      // block size 32: X[32:64, 0:32] = -X[32:64, 32:64] (L[32:64, 0:32] X[0:32, 0:32]); 16 rows per warp
+      const int R0 = 32 + 16 * wl;
+      float acc[4][4];
+      warp_gemm_tf32<4>(acc, Lc + R0 * kLStride, kLStride, Xc, kXStride, 32);
+      store_tile<4>(Tc + wl * 16 * kTStride, kTStride, acc, 1.f);
+      pair_sync(ci);
+      warp_gemm_tf32<4>(acc, Xc + R0 * kXStride + 32, kXStride, Tc, kTStride, 32);
+      store_tile<4>(Xc + R0 * kXStride, kXStride, acc, -1.f);
+    }
+    pair_sync(ci);
+    {
+      // A rows to global: eight lanes write one 128-byte row, 8 rows per pass of the 64 threads
+      const int64_t row_tok0 = static_cast<int64_t>(tok0) + ci * 64;
+      const int j8 = (c & 7) * 8;
+#pragma unroll 1
+      for (int pass = 0; pass < 8; ++pass) {
+        const int row = pass * 8 + (c >> 3);
+        if (row_tok0 + row < seq_end) {
+          const float4 lo = *reinterpret_cast<const float4*>(Xc + row * kXStride + j8);
+          const float4 hi = *reinterpret_cast<const float4*>(Xc + row * kXStride + j8 + 4);
+          const float xv[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+          T out[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) out[e] = Cvt<T>::from_f32((j8 + e <= row) ? xv[e] : 0.f);
+          *reinterpret_cast<uint4*>(Ab + ((row_tok0 + row) * p.num_v_heads + hv) * 64 + j8) =
+              *reinterpret_cast<const uint4*>(out);
+        }
+      }
     }
     __syncthreads();  // s_g / sL are rewritten for the next head
   }
@@ -220,7 +319,9 @@ int launch_kkt_solve(const KktParams& p, const void* k, int64_t total_tokens, in
   CUtensorMap tm_k;
   int rc = make_tmap_3d(&tm_k, k, total_tokens, p.num_k_heads, kHeadDim, 128, 64, true, is_bf16);
   if (rc != QLA_OK) return rc;
-  const size_t smem = 1024 + 32768 + 2 * 64 * kLStride * sizeof(float);
+  // K tile (32 KiB, later the two X tiles: 2 * 64 * 68 * 4 = 34 816 B, hence the larger of the two) + L + T
+  const size_t smem = 1024 + 2 * 64 * kXStride * sizeof(float) + 2 * 64 * kLStride * sizeof(float) +
+                      2 * 32 * kTStride * sizeof(float);
   dim3 grid(pairs_upper, p.num_k_heads);
   if (is_bf16) {
     QLA_CHECK_CUDA(cudaFuncSetAttribute(kkt_solve_kernel<__nv_bfloat16>,
