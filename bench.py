@@ -272,6 +272,50 @@ def run_recurrent(args, rank, world, device, verify: bool):
     }
 
 
+def run_train(args, rank, world, device):
+    """Config 3: forward (saving h and v_new) + backward, B=4, T=8192, Hk=Hv=32, batch rows sharded."""
+    import flashqla_b200 as fq
+    from flashqla_b200.sharding import batch_shard
+    B_all, T, H = 4, args.tokens if args.tokens != 32768 else 8192, 32
+    rows = batch_shard(B_all, world, rank)
+    B = rows.stop - rows.start
+    gen = torch.Generator(device=device).manual_seed(3 + rank)
+    rn = lambda *s: torch.randn(*s, generator=gen, device=device)
+    q = torch.nn.functional.normalize(rn(B, T, H, K), dim=-1).bfloat16()
+    k = torch.nn.functional.normalize(rn(B, T, H, K), dim=-1).bfloat16()
+    v = rn(B, T, H, V).bfloat16()
+    g = torch.nn.functional.logsigmoid(rn(B, T, H))
+    beta = torch.sigmoid(rn(B, T, H))
+    h0 = 0.1 * rn(B, H, K, V)
+    do = rn(B, T, H, V).bfloat16()
+    dht = 0.1 * rn(B, H, K, V)
+
+    def step():
+        g_cs, A, o, h, fs, vn = fq.chunk_gated_delta_rule_fwd(q, k, v, g, beta, initial_state=h0, output_h=True,
+                                                              output_v_new=True)
+        return fq.chunk_gated_delta_rule_bwd(q, k, v, g_cs, beta, A, do, dht=dht, initial_state=h0, h=h, v_new=vn)
+
+    with ClockSampler(device.index or 0) as cs:
+        ms = timed(step, args.steps, args.warmup, world, device)
+    fq.check_device_status()
+    per_step = ms / args.steps
+    tokens = B_all * T
+    flops = tokens * H * (163840 + 409600)
+    pk = peaks()
+    return {
+        "metric": "gdn_train_fwd_bwd_tokens_per_s", "value": tokens / (per_step * 1e-3), "unit": "tokens/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_step,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"train_fwd_bwd_B{B_all}_T{T}_Hk{H}_Hv{H}_K128_V128_chunk64", "sharding": f"batch/{world}",
+                   "l2": "inputs (>= 1 GB per step) exceed the 126 MB L2; no flush needed", "tokens": tokens},
+        "clocks": cs.summary(), "gpu_launches": 4 * args.steps,
+        "roofline": {"kernel": "fwd+bwd (all kernels)", "bound": "tensor", "achieved": flops / world / (per_step * 1e-3) / 1e12,
+                     "peak": pk["tf_sus"], "unit": "TFLOP/s",
+                     "frac": flops / world / (per_step * 1e-3) / 1e12 / pk["tf_sus"], "peak_source": pk["src"],
+                     "traffic": None},
+    }
+
+
 # ------------------------------------------------------------------------------------ CPU arms
 def cpu_prefill_sample(tokens_sample: int, repeats: int = 2):
     """Oracle forward on the first `tokens_sample` tokens of the default workload, all host threads."""
@@ -292,7 +336,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="prefill_fwd", choices=["prefill_fwd", "varlen", "decode", "verify"])
+    ap.add_argument("--workload", default="prefill_fwd", choices=["prefill_fwd", "varlen", "decode", "verify", "train"])
     ap.add_argument("--tokens", type=int, default=32768)
     ap.add_argument("--bf16-scratch", action="store_true")
     ap.add_argument("--cpu-sample-tokens", type=int, default=4096)
@@ -332,6 +376,8 @@ def main():
         line = run_prefill(args, rank, world, device)
     elif args.workload == "varlen":
         line = run_prefill(args, rank, world, device, varlen=True)
+    elif args.workload == "train":
+        line = run_train(args, rank, world, device)
     else:
         line = run_recurrent(args, rank, world, device, verify=args.workload == "verify")
     if rank == 0:
