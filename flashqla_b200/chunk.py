@@ -45,9 +45,14 @@ def _check_common(q, k, v, g, beta, initial_state, cu_seqlens, transpose_state_l
 
 
 def _launch_fwd(q, k, v, g, beta, h0, cu, g_cumsum, A, o, h, v_new, final_state, scale, flags=0,
-                seq_map=None, chunk_limit=None, num_seqs=None):
-    """Fill ``QlaChunkFwdArgs`` from tensors and call ``qla_chunk_fwd`` on the current stream."""
+                seq_map=None, chunk_limit=None, num_seqs=None, w=None):
+    """Fill ``QlaChunkFwdArgs`` from tensors and call ``qla_chunk_fwd`` on the current stream.  ``w`` is
+    the per-chunk operand ``-(A diag(beta e^g) K)`` that the preparation step writes and the scan reads;
+    it is allocated here when the call does both."""
     dev = k.device
+    if w is None:
+        assert not flags & _cabi.CHUNK_SKIP_PREPARE, "a scan without preparation needs the prepared w"
+        w = new_w(k, beta)
     B, T, Hk = k.shape[0], k.shape[1], k.shape[2]
     Hv = beta.shape[2]
     if cu is not None:  # packed view: [B, T, ...] is contiguous, i.e. [1, B*T, ...]
@@ -60,7 +65,7 @@ def _launch_fwd(q, k, v, g, beta, h0, cu, g_cumsum, A, o, h, v_new, final_state,
         beta_dtype=_cabi.dtype_code(beta.dtype), flags=flags, max_chunks_per_seq=0, scale=float(scale),
         q=_cabi.ptr(q), k=_cabi.ptr(k), v=_cabi.ptr(v), g=_cabi.ptr(g), beta=_cabi.ptr(beta),
         h0=_cabi.ptr(h0), cu_seqlens=_cabi.ptr(cu), seq_map=_cabi.ptr(seq_map),
-        chunk_limit=_cabi.ptr(chunk_limit), g_cumsum=_cabi.ptr(g_cumsum), A=_cabi.ptr(A), o=_cabi.ptr(o),
+        chunk_limit=_cabi.ptr(chunk_limit), g_cumsum=_cabi.ptr(g_cumsum), A=_cabi.ptr(A), w=_cabi.ptr(w), o=_cabi.ptr(o),
         h=_cabi.ptr(h), v_new=_cabi.ptr(v_new), final_state=_cabi.ptr(final_state), workspace=None,
         workspace_bytes=0, status=_cabi.ptr(status))
     lib = _cabi.lib()
@@ -71,6 +76,19 @@ def _launch_fwd(q, k, v, g, beta, h0, cu, g_cumsum, A, o, h, v_new, final_state,
     with torch.cuda.device(dev):
         code = lib.qla_chunk_fwd(args, _cabi.current_stream(dev))
     _cabi.check(code, "qla_chunk_fwd")
+
+
+def new_w(k, beta):
+    """Uninitialised ``[B, T, Hv, 128]`` buffer for the operand ``w`` of ``_launch_fwd``."""
+    return torch.empty(k.shape[0], k.shape[1], beta.shape[2], 128, dtype=k.dtype, device=k.device)
+
+
+def rebuild_w(k, beta, g_cumsum, A, cu):
+    """``w`` from a saved ``g_cumsum`` / ``A`` pair (one preparation launch, no scan)."""
+    w = new_w(k, beta)
+    _launch_fwd(None, k, None, None, beta, None, cu, g_cumsum, A, None, None, None, None, 1.0,
+                flags=_cabi.CHUNK_PREPARE_ONLY | _cabi.CHUNK_A_GIVEN, w=w)
+    return w
 
 
 def launches_per_forward(varlen: bool, use_cp: bool = False) -> int:
@@ -94,18 +112,19 @@ def make_scan_only(q, k, v, beta, g_cumsum, A, o, final_state, initial_state=Non
     cu = None if cu_seqlens is None else cu_seqlens.to(device=dev, dtype=torch.int32).contiguous()
     lens = host_seqlens(cu_seqlens) if cu_seqlens is not None else [T] * B
     plan = cp.get_plan(lens, Hv, dev) if auto_cp else None
+    w = rebuild_w(k, beta, g_cumsum, A, cu)
     if plan is not None and plan.use_cp:
-        cp_h0 = cp.segment_initial_states(plan, k, v, beta, g_cumsum, A, initial_state, scale, _launch_fwd)
+        cp_h0 = cp.segment_initial_states(plan, k, v, beta, g_cumsum, A, w, initial_state, scale, _launch_fwd)
 
         def run():
             _launch_fwd(q, k, v, None, beta, cp_h0, plan.dev["cu"], g_cumsum, A, o, None, None, final_state,
                         scale, flags=_cabi.CHUNK_SKIP_PREPARE, seq_map=plan.dev["seg_raw"],
-                        num_seqs=len(plan.seg_next))
+                        num_seqs=len(plan.seg_next), w=w)
         return run
 
     def run():
         _launch_fwd(q, k, v, None, beta, initial_state, cu, g_cumsum, A, o, None, None, final_state, scale,
-                    flags=_cabi.CHUNK_SKIP_PREPARE)
+                    flags=_cabi.CHUNK_SKIP_PREPARE, w=w)
     return run
 
 
@@ -169,15 +188,17 @@ def chunk_gated_delta_rule_fwd(
     if plan is not None and plan.use_cp:
         # g_cumsum and A on the original sequences, then per-segment initial states, then the scan
         # over segments (segments are whole chunks, so chunk numbering is unchanged)
+        w = new_w(k, beta)
         _launch_fwd(None, k, None, g, beta, None, cu, g_cumsum, A, None, None, None, None, scale,
-                    flags=_cabi.CHUNK_PREPARE_ONLY)
+                    flags=_cabi.CHUNK_PREPARE_ONLY, w=w)
         h0_kv = h0.transpose(-1, -2) if (h0 is not None and transpose_state_layout) else h0
-        cp_h0 = cp.segment_initial_states(plan, k, v, beta, g_cumsum, A, h0_kv, scale, _launch_fwd)
+        cp_h0 = cp.segment_initial_states(plan, k, v, beta, g_cumsum, A, w, h0_kv, scale, _launch_fwd)
         fs = final_state
         if transpose_state_layout and final_state is not None:
             fs = torch.empty_like(final_state)
         _launch_fwd(q, k, v, None, beta, cp_h0, plan.dev["cu"], g_cumsum, A, o, h, v_new, fs, scale,
-                    flags=_cabi.CHUNK_SKIP_PREPARE, seq_map=plan.dev["seg_raw"], num_seqs=len(plan.seg_next))
+                    flags=_cabi.CHUNK_SKIP_PREPARE, seq_map=plan.dev["seg_raw"], num_seqs=len(plan.seg_next),
+                    w=w)
         if fs is not final_state:
             final_state.copy_(fs.transpose(-1, -2))
     else:
@@ -234,7 +255,7 @@ def chunk_gated_delta_rule_bwd(
         h = torch.empty(n_chunks, Hv, 128, 128, dtype=q.dtype, device=dev)
         v_new = torch.empty_like(v)
         _launch_fwd(None, k, v, None, beta, h0, cu, g_cumsum, A, None, h, v_new, None, scale,
-                    flags=flags | _cabi.CHUNK_STATE_ONLY | _cabi.CHUNK_SKIP_PREPARE)
+                    flags=flags | _cabi.CHUNK_STATE_ONLY | _cabi.CHUNK_A_GIVEN)
     h = h if h.is_contiguous() else h.contiguous()
     v_new = v_new if v_new.is_contiguous() else v_new.contiguous()
 

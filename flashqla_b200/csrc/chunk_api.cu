@@ -1,5 +1,5 @@
 // C-ABI entry points of the chunked prefill path: argument checks, workspace carving, launch order
-//   [chunk tables] -> kkt_solve (g_cumsum, A) -> chunk forward scan.
+//   [chunk tables] -> kkt_solve (g_cumsum, A, w) -> chunk forward scan.
 // Mirrors the launch sequence of chunk_gated_delta_rule_fwd,
 // flash_qla/ops/gated_delta_rule/chunk/__init__.py:23-86.
 #include "chunk_params.cuh"
@@ -49,9 +49,12 @@ extern "C" QLA_API int qla_chunk_fwd(const QlaChunkFwdArgs* args, void* stream_)
   QLA_CHECK_ARG(varlen || a.num_seqs == a.batch, "num_seqs must equal batch without cu_seqlens");
   const bool state_only = (a.flags & QLA_CHUNK_STATE_ONLY) != 0;
   const bool skip_prepare = (a.flags & QLA_CHUNK_SKIP_PREPARE) != 0;
-  QLA_CHECK_ARG(a.k && a.beta && a.g_cumsum && a.A && a.status, "k, beta, g_cumsum, A, status are required");
+  QLA_CHECK_ARG(a.k && a.beta && a.g_cumsum && a.A && a.w && a.status,
+                "k, beta, g_cumsum, A, w, status are required");
   QLA_CHECK_ARG((a.flags & (QLA_CHUNK_ZERO_V | QLA_CHUNK_PREPARE_ONLY)) || a.v, "v is required");
-  QLA_CHECK_ARG(skip_prepare || a.g, "g is required");
+  const bool a_given = (a.flags & QLA_CHUNK_A_GIVEN) != 0;
+  QLA_CHECK_ARG(skip_prepare || a_given || a.g, "g is required");
+  QLA_CHECK_ARG(!(skip_prepare && a_given), "QLA_CHUNK_SKIP_PREPARE and QLA_CHUNK_A_GIVEN exclude each other");
   QLA_CHECK_ARG(state_only || (a.flags & QLA_CHUNK_PREPARE_ONLY) || (a.q && a.o),
                 "q and o are required unless QLA_CHUNK_STATE_ONLY");
   QLA_CHECK_SUPPORTED(!(a.flags & QLA_CHUNK_QK_L2NORM), "in-kernel q/k L2 norm is not available");
@@ -77,10 +80,11 @@ extern "C" QLA_API int qla_chunk_fwd(const QlaChunkFwdArgs* args, void* stream_)
 
   if (!skip_prepare) {
     KktParams kp{};
-    kp.g = a.g; kp.beta = a.beta; kp.g_cumsum = a.g_cumsum; kp.A = a.A;
+    kp.g = a_given ? static_cast<const void*>(a.g_cumsum) : a.g; kp.beta = a.beta; kp.g_cumsum = a.g_cumsum;
+    kp.A = a.A; kp.A_in = a_given ? a.A : nullptr; kp.w = a.w;
     kp.cu_seqlens = a.cu_seqlens; kp.pair_offsets = pair_offsets; kp.status = a.status;
     kp.num_seqs = a.num_seqs; kp.seq_len = a.seq_len; kp.num_k_heads = a.num_k_heads; kp.num_v_heads = a.num_v_heads;
-    kp.gate_dtype = a.gate_dtype; kp.beta_dtype = a.beta_dtype;
+    kp.gate_dtype = a_given ? QLA_DT_F32 : a.gate_dtype; kp.beta_dtype = a.beta_dtype;
     const int pairs_upper = varlen ? static_cast<int>(total_tokens / 128 + a.num_seqs)
                                    : a.batch * ((a.seq_len + 127) / 128);
     int rc = launch_kkt_solve(kp, a.k, total_tokens, pairs_upper, is_bf16, stream);
@@ -102,7 +106,7 @@ extern "C" QLA_API int qla_chunk_fwd(const QlaChunkFwdArgs* args, void* stream_)
   fp.trace = current_trace_buffer();
   fp.trace_count = current_trace_count();
   const void* v = a.v ? a.v : a.k;  // never dereferenced with QLA_CHUNK_ZERO_V, only used for the tensor map
-  return launch_chunk_fwd(fp, a.q, a.k, v, a.A, total_tokens, is_bf16, state_only, stream);
+  return launch_chunk_fwd(fp, a.q, a.k, v, a.A, a.w, total_tokens, is_bf16, state_only, stream);
 }
 
 namespace qla {

@@ -5,26 +5,29 @@
 // (chunk/hopper/prepare_h.py:13-556); math as in tests/ref_gdr.py:107-260.
 //
 // Per chunk (S0 = state entering the chunk, g = chunk-local cumulative gate, gL its last value):
-//   U  = K S0                  W  = beta .* (V - exp(g) .* U)        Vd = A W          (= "v_new")
+//   Vd = A diag(beta) (V - exp(g) .* (K S0)) = Ab V - Wt S0           (= "v_new")
+//        Ab = A diag(beta),  Wt = A diag(beta exp(g)) K  (both state independent; Wt comes, negated,
+//        from the preparation kernel)
 //   O  = s exp(g) .* (Q S0) + (s G .* Q K^T) Vd                      G[c,d] = exp(g_c - g_d), c >= d
 //   S1 = exp(gL) S0 + K^T (exp(gL - g) .* Vd)
 //
 // Everything is computed TRANSPOSED so that each tcgen05.mma has M = 128 (the V dimension on the 128
 // TMEM lanes) and every dependent operand can stay in tensor memory:
 //   MMA0  D0[128,64]  = [K;Q] K^T          (SS)  rows 64..127 are P = Q K^T; state independent
-//   MMAu  D2[128,64]  = V^T Ab^T           (SS)  Ab = A diag(beta); state independent part of Vd^T
-//   MMA1  D1[128,128] = S0^T_bf16 [K;Q]^T  (TS)  columns 0..63 = U^T, 64..127 = (Q S0)^T
-//   MMA2  D2[128,64] += W^T Ab^T           (TS)  W = -exp(g) .* U, so D2 = Vd^T = (Ab (V - exp(g) .* U))^T
+//   MMAu  D2[128,64]  = V^T Ab^T           (SS)  state independent part of Vd^T
+//   MMA2  D2[128,64] += S0^T_bf16 (-Wt)^T  (TS)  D2 = Vd^T; the only product between two state updates
+//                                                besides MMA3
+//   MMAq  Dq[128,64]  = S0^T_bf16 Q^T      (TS)  (Q S0)^T for the output, off the chain
 //   MMA3  S^T[128,128] += V'^T K           (TS, B operand MN-major straight from the K tile)
-//   MMA4  D4[128,64]  = Vd^T Pg^T          (SS)  Pg = s G .* P and Vd^T are swizzled smem tiles; off the chain
-// Thread v of a compute warpgroup owns TMEM lane v = column v of the state: it reads U^T/Vd^T rows
+//   MMA4  D4[128,64] += Vd^T Pg^T          (SS)  Pg = s G .* P and Vd^T are swizzled smem tiles; off the chain
+// Thread v of a compute warpgroup owns TMEM lane v = column v of the state: it reads Vd^T rows
 // with tcgen05.ld, applies the gates, and writes the bf16 operand of the next MMA back with
 // tcgen05.st.  The fp32 state never leaves tensor memory between chunks.
 //
-// Warp roles (384 threads): warps 0-3 "chain" (W, Vd, state convert of columns 0..63), warps 4-7 "side"
+// Warp roles (384 threads): warps 0-3 "chain" (Vd, state convert of columns 0..63), warps 4-7 "side"
 // (output epilogue, state convert of columns 64..127), warp 8 TMA producer + gate vectors, warp 9 MMA
-// issuer, warps 10-11 "aux" (operand tiles A diag(beta) and Pg).  Two smem stages of {K,Q,V,A,gates}; all waits are bounded mbarrier waits that raise a
-// status word instead of hanging.
+// issuer, warps 10-11 "aux" (operand tiles A diag(beta) and Pg).  Two smem stages of {K,Q,V,A,Wt,gates};
+// all waits are bounded mbarrier waits that raise a status word instead of hanging.
 #include "chunk_params.cuh"
 
 namespace qla {
@@ -35,17 +38,18 @@ namespace {
 // ---- tensor-memory column map (512 columns)
 constexpr uint32_t kColS = 0;      // fp32 state S^T, 128 columns
 constexpr uint32_t kColSbf = 128;  // bf16 copy of S^T (A operand of MMA1), 64 columns
-constexpr uint32_t kColD1 = 192;   // U^T (192..255, overwritten by W bf16 at 192..223) | (Q S)^T (256..319)
-constexpr uint32_t kColD2 = 320;   // Vd^T; columns 320..351 are overwritten in place by V' bf16 (A operand of MMA3)
-constexpr uint32_t kColD4 = 384;   // output accumulator: s gamma .* (Q S0)^T, then += Vd^T Pg^T
-constexpr uint32_t kColD0 = 448;   // [K;Q] K^T
+constexpr uint32_t kColD2 = 192;   // Vd^T; columns 192..223 are overwritten in place by V' bf16 (A operand of MMA3)
+constexpr uint32_t kColDq = 256;   // (Q S0)^T
+constexpr uint32_t kColD4 = 320;   // output accumulator: s gamma .* (Q S0)^T, then += Vd^T Pg^T
+constexpr uint32_t kColD0 = 384;   // [K;Q] K^T
 
 // ---- shared-memory map (offsets from a 1024-byte aligned base)
 constexpr uint32_t kStageKQ = 0;         // 32 KiB: half 0 [K rows | Q rows] (16 KiB), half 1 (16 KiB); SW128
 constexpr uint32_t kStageV = 32768;      // 16 KiB: V tile as two [64][64] halves (columns 0..63 | 64..127), SW128
 constexpr uint32_t kStageA = 49152;      // 8 KiB: A tile [64][64], SW128; scaled in place to A diag(beta)
-constexpr uint32_t kStageGate = 57344;   // 1 KiB + : g[64], gamma[64], rho[64], beta[64], egl
-constexpr uint32_t kStageBytes = 59392;  // 58 KiB, multiple of 1024
+constexpr uint32_t kStageW = 57344;      // 16 KiB: -Wt tile as two [64][64] halves (columns 0..63 | 64..127), SW128
+constexpr uint32_t kStageGate = 73728;   // 1 KiB + : g[64], gamma[64], rho[64], beta[64], egl
+constexpr uint32_t kStageBytes = 75776;  // 74 KiB, multiple of 1024
 constexpr uint32_t kOffPg = 2 * kStageBytes;         // 8 KiB Pg tile, SW128
 constexpr uint32_t kOffO = kOffPg + 8192;            // 2 x 16 KiB output tiles [64][128]
 constexpr uint32_t kOffVd = kOffO + 2 * 16384;       // 2 x 16 KiB Vd^T tiles [128 v][64 d], SW128 (A of MMA4)
@@ -62,7 +66,7 @@ struct Gates {
 
 enum Bar {
   kFull0 = 0, kFull1, kEmpty0, kEmpty1,
-  kPDone, kPFree, kPgReady, kD1Done, kD1Free, kWReady, kD2Done, kVdReady, kSDone, kSbfReady, kSScaled, kAbReady0, kAbReady1, kD4Done, kD4Free, kOFree, kOReady,
+  kPDone, kPFree, kPgReady, kDqDone, kQsStored, kD2Done, kVdReady, kSDone, kSbfReady, kSScaled, kAbReady0, kAbReady1, kD4Done, kOFree, kOReady,
   kNumBars
 };
 
@@ -92,7 +96,8 @@ template <typename T, bool kStateOnly, bool kTrace>
 __global__ void __launch_bounds__(kThreads, 1)
 chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                  const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_a,
-                 const __grid_constant__ CUtensorMap tm_o, const FwdParams p) {
+                 const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_o,
+                 const FwdParams p) {
   constexpr uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? ptx::kFmtBF16 : ptx::kFmtF16;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int hv = blockIdx.x % p.num_v_heads;
@@ -134,9 +139,8 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     ptx::mbar_init(&bars[kPDone], 1);
     ptx::mbar_init(&bars[kPFree], 2);
     ptx::mbar_init(&bars[kPgReady], 2);
-    ptx::mbar_init(&bars[kD1Done], 1);
-    ptx::mbar_init(&bars[kD1Free], 4);
-    ptx::mbar_init(&bars[kWReady], 4);
+    ptx::mbar_init(&bars[kDqDone], 1);
+    ptx::mbar_init(&bars[kQsStored], 4);
     ptx::mbar_init(&bars[kD2Done], 1);
     ptx::mbar_init(&bars[kVdReady], 4);
     ptx::mbar_init(&bars[kSDone], 1);
@@ -145,7 +149,6 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     ptx::mbar_init(&bars[kAbReady0], 2);
     ptx::mbar_init(&bars[kAbReady1], 2);
     ptx::mbar_init(&bars[kD4Done], 1);
-    ptx::mbar_init(&bars[kD4Free], 4);
     ptx::mbar_init(&bars[kOFree], 1);
     ptx::mbar_init(&bars[kOReady], 4);
     ptx::fence_mbar_init();
@@ -204,6 +207,8 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         ptx::tma_prefetch_l2_3d(&tm_v, 64, hv, pt0);
       }
       ptx::tma_prefetch_l2_3d(&tm_a, 0, hv, pt0);
+      ptx::tma_prefetch_l2_3d(&tm_w, 0, hv, pt0);
+      ptx::tma_prefetch_l2_3d(&tm_w, 64, hv, pt0);
     };
     if (lane == 0)
       for (int j = 2; j < kPrefetchAhead && j < nproc; ++j) prefetch_chunk(j);
@@ -226,12 +231,12 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         gcv[r] = okc ? p.g_cumsum[tok * p.num_v_heads + hv] : gl;
         bcv[r] = okc ? load_scalar(p.beta, p.beta_dtype, tok * p.num_v_heads + hv) : 0.f;
       }
-      if (use > 0 && !ptx::mbar_wait_warp(&bars[kEmpty0 + s], (use - 1) & 1, status, kTimeout)) break;
+      if (use > 0 && !ptx::mbar_wait_warp(&bars[kEmpty0 + s], (use - 1) & 1, status, kTimeout | ((kEmpty0 + s) << 8))) break;
       if (lane == 0) trace(0, i, 10);
       uint8_t* st = stage_ptr(s);
       if (lane == 0) {
         if (i + kPrefetchAhead < nproc) prefetch_chunk(i + kPrefetchAhead);
-        uint32_t bytes = 16384 + 8192;  // K + A
+        uint32_t bytes = 16384 + 8192 + 16384;  // K + A + Wt
         if (!kStateOnly) bytes += 16384;  // Q
         if (!p.zero_v) bytes += 16384;    // V
         ptx::mbar_expect_tx(&bars[kFull0 + s], bytes);
@@ -246,6 +251,8 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           ptx::tma_load_3d(st + kStageV + 8192, &tm_v, &bars[kFull0 + s], 64, hv, t0);
         }
         ptx::tma_load_3d(st + kStageA, &tm_a, &bars[kFull0 + s], 0, hv, t0);
+        ptx::tma_load_3d(st + kStageW, &tm_w, &bars[kFull0 + s], 0, hv, t0);
+        ptx::tma_load_3d(st + kStageW + 8192, &tm_w, &bars[kFull0 + s], 64, hv, t0);
       }
       Gates* gs = gates_of(s);
 #pragma unroll
@@ -268,27 +275,53 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   } else if (warp == 9) {
     // =========================================================== MMA issuer (one thread)
     if (lane == 0) {
-      const uint32_t id_n128 = ptx::mma_idesc(128, 128, fmt, ptx::kMajorK, ptx::kMajorK);
       const uint32_t id_n64 = ptx::mma_idesc(128, 64, fmt, ptx::kMajorK, ptx::kMajorK);
       const uint32_t id_mn128 = ptx::mma_idesc(128, 128, fmt, ptx::kMajorK, ptx::kMajorMN);
       const uint32_t id_u = ptx::mma_idesc(128, 64, fmt, ptx::kMajorMN, ptx::kMajorK);
       // Descriptors are built once; inside the loop an operand step is one 64-bit add of
       // (byte offset >> 4) so that the single issuing thread spends its cycles on tcgen05.mma only.
-      uint64_t d_kq[2], d_kmn[2], d_a[2], d_v[2];
+      uint64_t d_kq[2], d_kmn[2], d_a[2], d_v[2], d_w[2];
 #pragma unroll
       for (int s = 0; s < 2; ++s) {
         d_kq[s] = ptx::smem_desc_sw128(ptx::smem_u32(stage_ptr(s) + kStageKQ), 16, 1024);      // K-major rows
         d_kmn[s] = ptx::smem_desc_sw128(ptx::smem_u32(stage_ptr(s) + kStageKQ), 16384, 1024);  // K tile, MN-major
         d_a[s] = ptx::smem_desc_sw128(ptx::smem_u32(stage_ptr(s) + kStageA), 16, 1024);
         d_v[s] = ptx::smem_desc_sw128(ptx::smem_u32(stage_ptr(s) + kStageV), 8192, 1024);      // V tile, MN-major
+        d_w[s] = ptx::smem_desc_sw128(ptx::smem_u32(stage_ptr(s) + kStageW), 16, 1024);
       }
       const uint64_t d_pg = ptx::smem_desc_sw128(ptx::smem_u32(smem + kOffPg), 16, 1024);
-      // Issue order (software pipelined): the state-dependent MMAs 1 -> 2 -> 3 of a chunk are separated
-      // by ALU phases of the chain warpgroup; the state-independent ones (MMA4 of the previous chunk,
-      // MMAu and MMA0 of this chunk) are issued into those gaps so the tensor pipe executes them while the
-      // chain computes, and MMA1 of the next chunk is never queued behind them.
       const uint64_t d_vd0 = ptx::smem_desc_sw128(ptx::smem_u32(smem + kOffVd), 16, 1024);
       const uint64_t d_vd1 = ptx::smem_desc_sw128(ptx::smem_u32(smem + kOffVd + 16384), 16, 1024);
+      // Issue order (software pipelined).  Between two state updates only MMA2 -> (chain warpgroup: Vd)
+      // -> MMA3 -> (both warpgroups: 16-bit state copy) are serial.  Everything else is issued in the
+      // tail of a chunk, behind MMA3, so that the tensor pipe executes it while the state is converted:
+      // MMAu and MMA0 of the NEXT chunk (state independent) and MMA4 of this chunk.
+      // MMAu of chunk j: D2 = V^T (A diag(beta))^T.  A operand = V tile read MN-major (two 64-column halves
+      // 8 KiB apart), B operand = the A tile after the aux warps scaled its columns by beta in place.
+      auto issue_u = [&](int j) -> bool {
+        const int s = j & 1;
+        if (!ptx::mbar_spin(&bars[kFull0 + s], (j >> 1) & 1, status, kTimeout | ((kFull0 + s) << 8))) return false;
+        if (!ptx::mbar_spin(&bars[kAbReady0 + s], (j >> 1) & 1, status, kTimeout | ((kAbReady0 + s) << 8))) return false;
+        if (!p.zero_v) {
+          const uint64_t vv = s ? d_v[1] : d_v[0], aa = s ? d_a[1] : d_a[0];
+          ptx::tc_fence_after_sync();
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks)
+            ptx::mma_ss(tmem + kColD2, vv + ks * (2048 >> 4), aa + ks * (32 >> 4), id_u, ks > 0);
+        }
+        return true;
+      };
+      // MMA0 of chunk j: D0 = [K;Q] K^T (A = 128 rows, B = first 64 rows of the tile)
+      auto issue_p = [&](int j) {
+        const uint64_t kq = (j & 1) ? d_kq[1] : d_kq[0];
+        ptx::tc_fence_after_sync();
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          const uint64_t d = kq + ((ks >> 2) * (16384 >> 4) + (ks & 3) * (32 >> 4));
+          ptx::mma_ss(tmem + kColD0, d, d, id_n64, ks > 0);
+        }
+        ptx::mma_commit(&bars[kPDone]);
+      };
       // MMA4 of chunk j: D4 += Vd^T Pg^T on top of s gamma .* (Q S0)^T which the side warpgroup stored
       // there; both operands from shared memory (Vd tile j & 1)
       auto issue_mma4 = [&](int j) {
@@ -300,90 +333,62 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         ptx::mma_commit(&bars[kD4Done]);
       };
       bool ok = true;
+      if (nproc > 0) {
+        ok = issue_u(0);
+        if (ok && !kStateOnly) issue_p(0);
+      }
       for (int i = 0; ok && i < nproc; ++i) {
-        const int s = i & 1, ph = i & 1, prev = (i - 1) & 1;
+        const int s = i & 1, ph = i & 1;
         // selects instead of dynamic indexing keep the descriptors in registers
-        const uint64_t kq = s ? d_kq[1] : d_kq[0], kmn = s ? d_kmn[1] : d_kmn[0];
-        const uint64_t aa = s ? d_a[1] : d_a[0], vv = s ? d_v[1] : d_v[0];
-        if (!(ok = ptx::mbar_spin(&bars[kFull0 + s], (i >> 1) & 1, status, kTimeout))) break;
+        const uint64_t kq = s ? d_kq[1] : d_kq[0], kmn = s ? d_kmn[1] : d_kmn[0], ww = s ? d_w[1] : d_w[0];
         trace(0, i, 0);
-        // MMA1: D1 = S0^T_bf16 * [K;Q]^T
-        if (!(ok = ptx::mbar_spin(&bars[kSbfReady], ph, status, kTimeout))) break;
-        if (!kStateOnly && i > 0 && !(ok = ptx::mbar_spin(&bars[kD1Free], prev, status, kTimeout))) break;
+        // MMA2: D2 += S0^T_bf16 (-Wt)^T  (B = the Wt tile, two 64-column halves 8 KiB apart)
+        if (!(ok = ptx::mbar_spin(&bars[kSbfReady], ph, status, kTimeout | ((kSbfReady) << 8)))) break;
         trace(0, i, 2);
         ptx::tc_fence_after_sync();
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
-          const uint64_t d = kq + ((ks >> 2) * (16384 >> 4) + (ks & 3) * (32 >> 4));
-          ptx::mma_ts(tmem + kColD1, tmem + kColSbf + ks * 8, d, kStateOnly ? id_n64 : id_n128, ks > 0);
-        }
-        ptx::mma_commit(&bars[kD1Done]);
-        trace(0, i, 3);
-        // gap 1 (chain computes W): MMA4 of the previous chunk (its Pg tile was produced during that chunk's
-        // second half), so that the side warpgroup can finish that chunk's output while the chain works
-        if (!kStateOnly && i > 0) {
-          if (!(ok = ptx::mbar_spin(&bars[kPgReady], prev, status, kTimeout))) break;
-          if (i > 1 && !(ok = ptx::mbar_spin(&bars[kD4Free], i & 1, status, kTimeout))) break;
-          issue_mma4(i - 1);
-          trace(0, i, 8);
-        }
-        // MMAu: D2 = V^T (A diag(beta))^T.  A operand = V tile read MN-major (two 64-column halves 8 KiB
-        // apart), B operand = the A tile after the aux warps scaled its columns by beta in place.  D2 is
-        // free: MMA3 of the previous chunk (its last reader) precedes this in the tensor pipe.
-        if (!(ok = ptx::mbar_spin(&bars[kAbReady0 + s], (i >> 1) & 1, status, kTimeout))) break;
-        if (!p.zero_v) {
-          ptx::tc_fence_after_sync();
-#pragma unroll
-          for (int ks = 0; ks < 4; ++ks)
-            ptx::mma_ss(tmem + kColD2, vv + ks * (2048 >> 4), aa + ks * (32 >> 4), id_u, ks > 0);
-        }
-        // MMA2: D2 += W^T Ab^T
-        if (!(ok = ptx::mbar_spin(&bars[kWReady], ph, status, kTimeout))) break;
-        trace(0, i, 4);
-        ptx::tc_fence_after_sync();
-#pragma unroll
-        for (int ks = 0; ks < 4; ++ks)
-          ptx::mma_ts(tmem + kColD2, tmem + kColD1 + ks * 8, aa + ks * (32 >> 4), id_n64, ks > 0 || !p.zero_v);
+        for (int ks = 0; ks < 8; ++ks)
+          ptx::mma_ts(tmem + kColD2, tmem + kColSbf + ks * 8, ww + ((ks >> 2) * (8192 >> 4) + (ks & 3) * (32 >> 4)),
+                      id_n64, ks > 0 || !p.zero_v);
         ptx::mma_commit(&bars[kD2Done]);
-        trace(0, i, 5);
-        // gap 2 (chain computes Vd): MMA0: D0 = [K;Q] K^T (A = 128 rows, B = first 64 rows of the tile),
-        // 
+        trace(0, i, 3);
+        // MMAq: Dq = S0^T_bf16 Q^T  (Q rows sit 8 KiB into each half of the stacked [K;Q] tile).  Dq is
+        // free: the side warpgroup read the previous chunk's before MMA4 of that chunk was issued.
         if (!kStateOnly) {
-          if (i > 0 && !(ok = ptx::mbar_spin(&bars[kPFree], prev, status, kTimeout))) break;
-          ptx::tc_fence_after_sync();
 #pragma unroll
-          for (int ks = 0; ks < 8; ++ks) {
-            const uint64_t d = kq + ((ks >> 2) * (16384 >> 4) + (ks & 3) * (32 >> 4));
-            ptx::mma_ss(tmem + kColD0, d, d, id_n64, ks > 0);
-          }
-          ptx::mma_commit(&bars[kPDone]);
-          trace(0, i, 1);
+          for (int ks = 0; ks < 8; ++ks)
+            ptx::mma_ts(tmem + kColDq, tmem + kColSbf + ks * 8,
+                        kq + ((8192 >> 4) + (ks >> 2) * (16384 >> 4) + (ks & 3) * (32 >> 4)), id_n64, ks > 0);
+          ptx::mma_commit(&bars[kDqDone]);
         }
         // MMA3: S^T += V'^T K   (B = K tile read MN-major: 64-column halves are 16 KiB apart)
-        if (!(ok = ptx::mbar_spin(&bars[kVdReady], ph, status, kTimeout))) break;
-        if (!(ok = ptx::mbar_spin(&bars[kSScaled], ph, status, kTimeout))) break;
+        if (!(ok = ptx::mbar_spin(&bars[kVdReady], ph, status, kTimeout | ((kVdReady) << 8)))) break;
+        if (!(ok = ptx::mbar_spin(&bars[kSScaled], ph, status, kTimeout | ((kSScaled) << 8)))) break;
         trace(0, i, 6);
         ptx::tc_fence_after_sync();
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks)
           ptx::mma_ts(tmem + kColS, tmem + kColD2 + ks * 8, kmn + ks * (2048 >> 4), id_mn128, true);
         ptx::mma_commit(&bars[kSDone]);
-        trace(0, i, 7);
         ptx::mma_commit(&bars[kEmpty0 + s]);  // every MMA that reads this stage has been issued and tracked
-      }
-      // MMA4 of the last chunk
-      if (ok && !kStateOnly && nproc > 0) {
-        const int j = nproc - 1;
-        // D1Free of the last chunk also says that its (Q S0)^T part has been stored into D4
-        if (ptx::mbar_spin(&bars[kD1Free], j & 1, status, kTimeout) &&
-            ptx::mbar_spin(&bars[kPgReady], j & 1, status, kTimeout) &&
-            (j == 0 || ptx::mbar_spin(&bars[kD4Free], (j - 1) & 1, status, kTimeout)))
-          issue_mma4(j);
+        trace(0, i, 7);
+        // tail: D2 is free again (the chain read Vd before VdReady, MMA3 precedes in the pipe)
+        if (i + 1 < nproc && !(ok = issue_u(i + 1))) break;
+        if (!kStateOnly) {
+          if (!(ok = ptx::mbar_spin(&bars[kPgReady], ph, status, kTimeout | ((kPgReady) << 8)))) break;
+          if (!(ok = ptx::mbar_spin(&bars[kQsStored], ph, status, kTimeout | ((kQsStored) << 8)))) break;
+          issue_mma4(i);
+          if (i + 1 < nproc) {
+            if (!(ok = ptx::mbar_spin(&bars[kPFree], ph, status, kTimeout | ((kPFree) << 8)))) break;
+            issue_p(i + 1);
+          }
+        }
+        trace(0, i, 8);
       }
     }
   } else if (warp >= 10) {
     // =========================================================== aux warps 10, 11: operand tiles
-    // (a) Ab = A diag(beta), in place in the stage's A tile (B operand of MMAu and MMA2);
+    // (a) Ab = A diag(beta), in place in the stage's A tile (B operand of MMAu);
     // (b) Pg = s * G .* P from D0 rows 64..127 (TMEM quadrants 2, 3 = warps 10, 11) into a swizzled tile.
     const int r = tid - 320;  // 0..63: row of A / row c of P
     const uint32_t tm = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
@@ -416,22 +421,22 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     };
     bool ok = true;
     if (nproc > 0) {
-      ok = ptx::mbar_wait_warp(&bars[kFull0], 0, status, kTimeout);
+      ok = ptx::mbar_wait_warp(&bars[kFull0], 0, status, kTimeout | ((kFull0) << 8));
       if (ok) scale_a_tile(0, 0);
     }
     for (int i = 0; ok && i < nproc; ++i) {
       const int s = i & 1, ph = i & 1;
       const float* gsg = my_g + (i & 1) * 64;
-      // the A tile of the NEXT chunk first: MMAu of that chunk waits for it early
+      // the A tile of the NEXT chunk first: MMAu of that chunk is issued in the tail of this one
       if (i + 1 < nproc) {
-        if (!(ok = ptx::mbar_wait_warp(&bars[kFull0 + (s ^ 1)], ((i + 1) >> 1) & 1, status, kTimeout))) break;
+        if (!(ok = ptx::mbar_wait_warp(&bars[kFull0 + (s ^ 1)], ((i + 1) >> 1) & 1, status, kTimeout | ((kFull0 + (s ^ 1)) << 8)))) break;
         scale_a_tile(s ^ 1, (i + 1) & 1);
       }
       if (!kStateOnly) {
         if (tid == 320) trace(2, i, 8);
-        if (!(ok = ptx::mbar_wait_warp(&bars[kPDone], ph, status, kTimeout))) break;
+        if (!(ok = ptx::mbar_wait_warp(&bars[kPDone], ph, status, kTimeout | ((kPDone) << 8)))) break;
         // MMA4 of the previous chunk must have finished reading the Pg tile
-        if (i > 0 && !(ok = ptx::mbar_wait_warp(&bars[kD4Done], (i - 1) & 1, status, kTimeout))) break;
+        if (i > 0 && !(ok = ptx::mbar_wait_warp(&bars[kD4Done], (i - 1) & 1, status, kTimeout | ((kD4Done) << 8)))) break;
         ptx::tc_fence_after_sync();
         if (tid == 320) trace(2, i, 9);
         const int c = r;
@@ -493,7 +498,7 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     {
       float egl0 = 1.f;
       if (nproc > 0) {
-        alive = ptx::mbar_wait_warp(&bars[kFull0], 0, status, kTimeout);
+        alive = ptx::mbar_wait_warp(&bars[kFull0], 0, status, kTimeout | ((kFull0) << 8));
         egl0 = gates_of(0)->egl;
       }
 #pragma unroll 1
@@ -530,7 +535,7 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     // transposed through a shared-memory tile and written with one TMA store (row-masked stores for a
     // ragged tail).
     auto epilogue = [&](int j, int valid_j, int t0_j) -> bool {
-      if (!ptx::mbar_wait_warp(&bars[kD4Done], j & 1, status, kTimeout)) return false;
+      if (!ptx::mbar_wait_warp(&bars[kD4Done], j & 1, status, kTimeout | ((kD4Done) << 8))) return false;
       ptx::tc_fence_after_sync();
       if (tid == 128) trace(2, j, 6);
       T* so = reinterpret_cast<T*>(smem + kOffO + (j & 1) * 16384);
@@ -541,7 +546,7 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
           ptx::mbar_arrive(&bars[kOFree]);
         }
-        if (!ptx::mbar_wait_warp(&bars[kOFree], j & 1, status, kTimeout)) return false;
+        if (!ptx::mbar_wait_warp(&bars[kOFree], j & 1, status, kTimeout | ((kOFree) << 8))) return false;
       }
 #pragma unroll 1
       for (int cb = 0; cb < 64; cb += 16) {
@@ -552,20 +557,19 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         for (int e = 0; e < 16; ++e) so[(cb + e) * kHeadDim + v] = Cvt<T>::from_f32(__uint_as_float(r[e]));
       }
       ptx::tc_fence_before_sync();
-      warp_arrive(&bars[kD4Free], lane);
       if (tid == 128) trace(2, j, 12);
       ptx::fence_proxy_async_smem();
       warp_arrive(&bars[kOReady], lane);
       if (valid_j == kChunk) {
         if (warp == 4) {  // only the issuing warp waits for the tile to be complete
-          if (!ptx::mbar_wait_warp(&bars[kOReady], j & 1, status, kTimeout)) return false;
+          if (!ptx::mbar_wait_warp(&bars[kOReady], j & 1, status, kTimeout | ((kOReady) << 8))) return false;
           if (tid == 128) {
             ptx::tma_store_3d(&tm_o, so, 0, hv, t0_j);
             ptx::tma_store_commit();
           }
         }
       } else {
-        if (!ptx::mbar_wait_warp(&bars[kOReady], j & 1, status, kTimeout)) return false;
+        if (!ptx::mbar_wait_warp(&bars[kOReady], j & 1, status, kTimeout | ((kOReady) << 8))) return false;
         // ragged tail (always the last chunk of a sequence): row-masked 16-byte stores
         T* ob = static_cast<T*>(p.o);
         const int tl = tid - 128;  // 16 threads per row (8 elements each), 8 rows per pass
@@ -586,7 +590,7 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       const int chunk = first_chunk + i;
       const int t0 = seq_start + chunk * kChunk;
       const Gates* gs = gates_of(s);
-      if (i > 0) alive = ptx::mbar_wait_warp(&bars[kFull0 + s], (i >> 1) & 1, status, kTimeout);
+      if (i > 0) alive = ptx::mbar_wait_warp(&bars[kFull0 + s], (i >> 1) & 1, status, kTimeout | ((kFull0 + s) << 8));
       if (!alive) break;
       if (tid == 128) trace(2, i, 0);
       const int valid = gs->valid;
@@ -594,30 +598,8 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       if (!kStateOnly && wg == 1 && i > 0 && !(alive = epilogue(i - 1, prev_valid, prev_t0))) break;
 
       if (wg == 0) {
-        // ---------------- chain: W = -gamma .* U   (the V part of Vd is already in D2 from MMAu)
-        if (!(alive = ptx::mbar_wait_warp(&bars[kD1Done], ph, status, kTimeout))) break;
-        ptx::tc_fence_after_sync();
-        if (tid == 0) trace(1, i, 0);
-#pragma unroll 1
-        for (int cb = 0; cb < 64; cb += 16) {
-          uint32_t u[16], w[8];
-          ptx::tmem_ld16(tm + kColD1 + cb, u);
-          ptx::tmem_wait_ld();
-#pragma unroll
-          for (int j = 0; j < 16; j += 4) {
-            const float4 g4 = *reinterpret_cast<const float4*>(&gs->gamma[cb + j]);
-            w[j >> 1] = pack2<T>(-g4.x * __uint_as_float(u[j]), -g4.y * __uint_as_float(u[j + 1]));
-            w[(j >> 1) + 1] = pack2<T>(-g4.z * __uint_as_float(u[j + 2]), -g4.w * __uint_as_float(u[j + 3]));
-          }
-          ptx::tmem_st8(tm + kColD1 + cb / 2, w);  // in place: columns cb/2 .. cb/2+7 were already read
-        }
-        ptx::tmem_wait_st();
-        ptx::tc_fence_before_sync();
-        warp_arrive(&bars[kWReady], lane);
-        if (tid == 0) trace(1, i, 1);
-
         // ---------------- chain: Vd (to the shared-memory tile of MMA4, and v_new) and V' = rho .* Vd
-        if (!(alive = ptx::mbar_wait_warp(&bars[kD2Done], ph, status, kTimeout))) break;
+        if (!(alive = ptx::mbar_wait_warp(&bars[kD2Done], ph, status, kTimeout | ((kD2Done) << 8)))) break;
         ptx::tc_fence_after_sync();
         if (tid == 0) trace(1, i, 2);
         T* vn = static_cast<T*>(p.v_new);
@@ -659,13 +641,13 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       } else if (!kStateOnly) {
         // ---------------- side: D4 <- s gamma .* (Q S0)^T; MMA4 accumulates Vd^T Pg^T on top later
         if (tid == 128) trace(2, i, 1);
-        if (!(alive = ptx::mbar_wait_warp(&bars[kD1Done], ph, status, kTimeout))) break;
+        if (!(alive = ptx::mbar_wait_warp(&bars[kDqDone], ph, status, kTimeout | ((kDqDone) << 8)))) break;
         ptx::tc_fence_after_sync();
         if (tid == 128) trace(2, i, 2);
 #pragma unroll 1
         for (int cb = 0; cb < 64; cb += 16) {
           uint32_t r[16];
-          ptx::tmem_ld16(tm + kColD1 + 64 + cb, r);
+          ptx::tmem_ld16(tm + kColDq + cb, r);
           ptx::tmem_wait_ld();
 #pragma unroll
           for (int j = 0; j < 16; j += 4) {
@@ -679,12 +661,12 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         }
         ptx::tmem_wait_st();
         ptx::tc_fence_before_sync();
-        warp_arrive(&bars[kD1Free], lane);
+        warp_arrive(&bars[kQsStored], lane);
         if (tid == 128) trace(2, i, 3);
       }
 
       // ---------------- both: state convert after MMA3 (this warpgroup's 64 columns)
-      if (!(alive = ptx::mbar_wait_warp(&bars[kSDone], ph, status, kTimeout))) break;
+      if (!(alive = ptx::mbar_wait_warp(&bars[kSDone], ph, status, kTimeout | ((kSDone) << 8)))) break;
       ptx::tc_fence_after_sync();
       if (tid == 0) trace(1, i, 4);
       if (tid == 128) trace(2, i, 4);
@@ -701,7 +683,7 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           }
         }
       } else {
-        if (!(alive = ptx::mbar_wait_warp(&bars[kFull0 + (s ^ 1)], ((i + 1) >> 1) & 1, status, kTimeout))) break;
+        if (!(alive = ptx::mbar_wait_warp(&bars[kFull0 + (s ^ 1)], ((i + 1) >> 1) & 1, status, kTimeout | ((kFull0 + (s ^ 1)) << 8)))) break;
         const float egl_next = gates_of(s ^ 1)->egl;
         T* hp = p.h ? static_cast<T*>(p.h) + ((chunk_base + chunk + 1) * p.num_v_heads + hv) * kHeadDim * kHeadDim + v
                     : nullptr;
@@ -774,13 +756,14 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 }  // namespace
 
 int launch_chunk_fwd(const FwdParams& p, const void* q, const void* k, const void* v, const void* A,
-                     int64_t total_tokens, bool is_bf16, bool state_only, cudaStream_t stream) {
-  CUtensorMap tm_q, tm_k, tm_v, tm_a, tm_o;
+                     const void* w, int64_t total_tokens, bool is_bf16, bool state_only, cudaStream_t stream) {
+  CUtensorMap tm_q, tm_k, tm_v, tm_a, tm_w, tm_o;
   int rc;
   if ((rc = make_tmap_3d(&tm_k, k, total_tokens, p.num_k_heads, kHeadDim, 64, 64, true, is_bf16)) != QLA_OK) return rc;
   if ((rc = make_tmap_3d(&tm_q, state_only ? k : q, total_tokens, p.num_k_heads, kHeadDim, 64, 64, true, is_bf16)) != QLA_OK) return rc;
   if ((rc = make_tmap_3d(&tm_v, v, total_tokens, p.num_v_heads, kHeadDim, 64, 64, true, is_bf16)) != QLA_OK) return rc;
   if ((rc = make_tmap_3d(&tm_a, A, total_tokens, p.num_v_heads, 64, 64, 64, true, is_bf16)) != QLA_OK) return rc;
+  if ((rc = make_tmap_3d(&tm_w, w, total_tokens, p.num_v_heads, kHeadDim, 64, 64, true, is_bf16)) != QLA_OK) return rc;
   if ((rc = make_tmap_3d(&tm_o, state_only ? v : p.o, total_tokens, p.num_v_heads, kHeadDim, 64, 128, false, is_bf16)) != QLA_OK) return rc;
   const unsigned grid = static_cast<unsigned>(p.num_seqs) * p.num_v_heads;
 #define QLA_LAUNCH_FWD(T, SO, TR)                                                                          \
@@ -788,7 +771,7 @@ int launch_chunk_fwd(const FwdParams& p, const void* q, const void* k, const voi
     QLA_CHECK_CUDA(cudaFuncSetAttribute(chunk_fwd_kernel<T, SO, TR>,                                       \
                                         cudaFuncAttributeMaxDynamicSharedMemorySize,                       \
                                         static_cast<int>(kSmemBytes)));                                    \
-    chunk_fwd_kernel<T, SO, TR><<<grid, kThreads, kSmemBytes, stream>>>(tm_q, tm_k, tm_v, tm_a, tm_o, p);  \
+    chunk_fwd_kernel<T, SO, TR><<<grid, kThreads, kSmemBytes, stream>>>(tm_q, tm_k, tm_v, tm_a, tm_w, tm_o, p);  \
   } while (0)
   // the traced variant is a separate instantiation so that normal launches carry no tracing code
   const bool traced = p.trace != nullptr;

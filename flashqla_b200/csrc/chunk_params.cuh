@@ -8,8 +8,10 @@ namespace qla {
 struct KktParams {
   const void* g;
   const void* beta;
-  float* g_cumsum;
-  void* A;
+  float* g_cumsum;              // out; in when A_in is given
+  void* A;                      // out (unused when A_in is given)
+  const void* A_in;             // optional: A from an earlier call -> only w is produced
+  void* w;                      // out: -(A diag(beta gamma) K), [NT, Hv, 128]
   const int32_t* cu_seqlens;    // NULL: equal-length batch of `seq_len` tokens
   const int32_t* pair_offsets;  // [num_seqs + 1] exclusive scan of ceil(len / 128), varlen only
   int* status;
@@ -79,6 +81,6 @@ int launch_chunk_tables(const int32_t* cu, int n, int32_t* pair_offsets, int32_t
 int launch_kkt_solve(const KktParams& p, const void* k, int64_t total_tokens, int pairs_upper, bool is_bf16,
                      cudaStream_t stream);
 int launch_chunk_fwd(const FwdParams& p, const void* q, const void* k, const void* v, const void* A,
-                     int64_t total_tokens, bool is_bf16, bool state_only, cudaStream_t stream);
+                     const void* w, int64_t total_tokens, bool is_bf16, bool state_only, cudaStream_t stream);
 
 }  // namespace qla

@@ -9,7 +9,11 @@
 // v-heads that share it, so K is fetched once per group.  K K^T for both chunks is a single
 // tcgen05.mma (M = N = K = 128, operands straight from the TMA-written 128B-swizzled tile,
 // accumulator in tensor memory); thread t then owns row t of the product (TMEM lane t) and keeps its
-// chunk's 64 columns in registers for every v-head.  The inverse of the unit-lower-triangular I + L is
+// chunk's 64 columns in registers for every v-head.  It also produces, per v-head, the chunk operand
+//   Wt = A diag(beta gamma) K      (the "w" of tests/ref_gdr.py:107-147, stored negated)
+// that lets the scan kernel form Vd = A diag(beta) V - Wt S0 with a single state-dependent product:
+// a second tcgen05.mma (block-diagonal [Aw_0 0; 0 Aw_1] times the K tile read MN-major) leaves row t of
+// Wt in TMEM lane t, which thread t writes to global memory as one contiguous 256-byte row.  The inverse of the unit-lower-triangular I + L is
 // blocked: the four 16 x 16 diagonal blocks by fp32 forward substitution (one thread per column), then
 // X21 = -X22 (L21 X11) at block size 16 and again at block size 32 with mma.sync m16n8k8 products on
 // fp32 shared-memory tiles, each operand split into two TF32 parts (3xTF32) so that the inverse keeps
@@ -22,7 +26,7 @@ namespace qla {
 namespace {
 
 constexpr int kLStride = 68;  // floats per L row: 16-byte aligned rows, conflict-free float4 stores
-constexpr int kXStride = 68;  // the two 64 x 68 fp32 X tiles (34 816 B) overlay the dead 32 KiB K tile
+constexpr int kXStride = 68;  // two 64 x 68 fp32 X tiles = 34 816 B, so the L area after them stays 1 KiB aligned
 constexpr int kTStride = 40;  // 32 columns + 8: conflict-free fragment loads
 
 __device__ __forceinline__ uint32_t to_tf32(float x) {
@@ -115,9 +119,11 @@ __global__ void __launch_bounds__(128) kkt_solve_kernel(const __grid_constant__ 
 
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* sK = smem_raw + ((1024u - (ptx::smem_u32(smem_raw) & 1023u)) & 1023u);
-  float* sL = reinterpret_cast<float*>(sK + 2 * 64 * kXStride * sizeof(float));  // [2][64][kLStride]
-  float* sX = reinterpret_cast<float*>(sK);          // [2][64][kXStride]: the K tile is dead once K K^T is in TMEM
+  float* sX = reinterpret_cast<float*>(sK + 32768);                                       // [2][64][kXStride]
+  float* sL = reinterpret_cast<float*>(sK + 32768 + 2 * 64 * kXStride * sizeof(float));  // [2][64][kLStride]
+  uint8_t* sAw = reinterpret_cast<uint8_t*>(sL);     // 32 KiB block-diagonal Aw tile (SW128), overlays L once solved
   float* sT = sL + 2 * 64 * kLStride;                // [2][32][kTStride] products L21 X11
+  __shared__ __align__(16) float s_bg[128];          // beta * gamma per token
   __shared__ __align__(16) float s_g[128];
   __shared__ float s_part[4];
   __shared__ uint64_t bar_tma, bar_mma;
@@ -129,7 +135,7 @@ __global__ void __launch_bounds__(128) kkt_solve_kernel(const __grid_constant__ 
     ptx::fence_mbar_init();
   }
   if (warp == 0) {
-    ptx::tmem_alloc(&tmem_base_s, 128);
+    ptx::tmem_alloc(&tmem_base_s, 256);
     ptx::tmem_relinquish();
   }
   ptx::tc_fence_before_sync();
@@ -178,6 +184,7 @@ __global__ void __launch_bounds__(128) kkt_solve_kernel(const __grid_constant__ 
   float* Lc = sL + ci * 64 * kLStride;
   T* Ab = static_cast<T*>(p.A);
 
+  int mma_uses = 0;  // completed phases of bar_mma after the first (K K^T)
   for (int hv = hk * group; ok && hv < (hk + 1) * group; ++hv) {
     float gv = 0.f, bv = 0.f;
     if (valid) {
@@ -194,8 +201,10 @@ __global__ void __launch_bounds__(128) kkt_solve_kernel(const __grid_constant__ 
     if (lane == 31) s_part[warp] = gcs;
     __syncthreads();
     if (warp & 1) gcs += s_part[warp - 1];
-    if (valid) p.g_cumsum[tok * p.num_v_heads + hv] = gcs;
+    if (p.A_in != nullptr) gcs = valid ? p.g_cumsum[tok * p.num_v_heads + hv] : 0.f;  // gates are cumulative already
+    else if (valid) p.g_cumsum[tok * p.num_v_heads + hv] = gcs;
     s_g[tid] = gcs;
+    s_bg[tid] = bv * __expf(gcs);
     __syncthreads();
 
     // L[c][d] = beta_c * exp(g_c - g_d) * (k_c . k_d) for d < c
@@ -217,8 +226,20 @@ __global__ void __launch_bounds__(128) kkt_solve_kernel(const __grid_constant__ 
     }
     __syncthreads();
 
-    // ---- blocked inverse of I + L for this chunk (64 threads = warps 2 ci, 2 ci + 1)
     float* Xc = sX + ci * 64 * kXStride;
+    if (p.A_in != nullptr) {
+      // A comes from an earlier call: row c of this chunk straight into the X tile
+      const T* arow = static_cast<const T*>(p.A_in) + ((static_cast<int64_t>(tok0) + tid) * p.num_v_heads + hv) * 64;
+#pragma unroll 1
+      for (int j = 0; j < 64; j += 8) {
+        uint4 raw = valid ? *reinterpret_cast<const uint4*>(arow + j) : make_uint4(0, 0, 0, 0);
+        const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+        for (int x = 0; x < 8; ++x) Xc[c * kXStride + j + x] = Cvt<T>::to_f32(e[x]);
+      }
+      pair_sync(ci);
+    } else {
+    // ---- blocked inverse of I + L for this chunk (64 threads = warps 2 ci, 2 ci + 1)
     float* Tc = sT + ci * 32 * kTStride;
     const int wl = warp & 1;  // warp within the chunk
     {
@@ -281,12 +302,74 @@ __global__ void __launch_bounds__(128) kkt_solve_kernel(const __grid_constant__ 
         }
       }
     }
+    }  // A_in
+    // ---- Wt = A diag(beta gamma) K for both chunks with one tcgen05.mma: build the block-diagonal
+    // operand [Aw_0 0; 0 Aw_1] (16-bit, K-major, 128B swizzle) over the L area, which is dead now
+    __syncthreads();
+    {
+      const float* xr = Xc + c * kXStride;
+      uint8_t* own = sAw + ci * 16384 + 0;        // half `ci` holds this chunk's 64 columns
+      uint8_t* other = sAw + (ci ^ 1) * 16384;
+      const float* bg = s_bg + ci * 64;
+#pragma unroll 1
+      for (int c16 = 0; c16 < 8; ++c16) {
+        const float4 x0 = *reinterpret_cast<const float4*>(xr + c16 * 8);
+        const float4 x1 = *reinterpret_cast<const float4*>(xr + c16 * 8 + 4);
+        const float4 b0 = *reinterpret_cast<const float4*>(bg + c16 * 8);
+        const float4 b1 = *reinterpret_cast<const float4*>(bg + c16 * 8 + 4);
+        const float xv[8] = {x0.x * b0.x, x0.y * b0.y, x0.z * b0.z, x0.w * b0.w, x1.x * b1.x, x1.y * b1.y, x1.z * b1.z, x1.w * b1.w};
+        T out[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) out[e] = Cvt<T>::from_f32((c16 * 8 + e <= c && valid) ? xv[e] : 0.f);
+        const uint32_t off = ptx::sw128_offset(tid, c16);  // row = token within the pair
+        *reinterpret_cast<uint4*>(own + off) = *reinterpret_cast<const uint4*>(out);
+        *reinterpret_cast<uint4*>(other + off) = make_uint4(0, 0, 0, 0);
+      }
+    }
+    ptx::fence_proxy_async_smem();
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    if (tid == 0) {
+      ptx::tc_fence_after_sync();
+      constexpr uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? ptx::kFmtBF16 : ptx::kFmtF16;
+      const uint32_t idesc = ptx::mma_idesc(128, 128, fmt, ptx::kMajorK, ptx::kMajorMN);
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks) {
+        const uint64_t da = ptx::smem_desc_sw128(ptx::smem_u32(sAw) + (ks >> 2) * 16384 + (ks & 3) * 32, 16, 1024);
+        const uint64_t db = ptx::smem_desc_sw128(ptx::smem_u32(sK) + ks * 2048, 16384, 1024);
+        ptx::mma_ss(tmem + 128, da, db, idesc, ks > 0);
+      }
+      ptx::mma_commit(&bar_mma);
+    }
+    ++mma_uses;
+    const bool ok2 = __syncthreads_and(ptx::mbar_wait(&bar_mma, mma_uses & 1, p.status, kStatusBarrierTimeout)) != 0;
+    ptx::tc_fence_after_sync();
+    if (ok2) {
+      // row `tid` of -Wt: 128 values -> one contiguous 256-byte row of w.  tcgen05.ld is warp-collective:
+      // every lane runs the loop, only lanes with a valid token store.
+      T* wrow = static_cast<T*>(p.w) + (tok * p.num_v_heads + hv) * kHeadDim;
+      const uint32_t taddr = tmem + (static_cast<uint32_t>(warp * 32) << 16) + 128;
+#pragma unroll 1
+      for (int kb = 0; kb < 128; kb += 16) {
+        uint32_t r[16];
+        ptx::tmem_ld16(taddr + kb, r);
+        ptx::tmem_wait_ld();
+        T out[16];
+#pragma unroll
+        for (int e = 0; e < 16; ++e) out[e] = Cvt<T>::from_f32(-__uint_as_float(r[e]));
+        if (valid) {
+          *reinterpret_cast<uint4*>(wrow + kb) = *reinterpret_cast<const uint4*>(out);
+          *reinterpret_cast<uint4*>(wrow + kb + 8) = *reinterpret_cast<const uint4*>(out + 8);
+        }
+      }
+    }
+    ptx::tc_fence_before_sync();
     __syncthreads();  // s_g / sL are rewritten for the next head
   }
 
   ptx::tc_fence_before_sync();
   __syncthreads();
-  if (warp == 0) ptx::tmem_dealloc(tmem, 128);
+  if (warp == 0) ptx::tmem_dealloc(tmem, 256);
 }
 
 // pair_offsets[n] = sum_{m<n} ceil(len_m / 128), chunk_offsets[n] = sum_{m<n} ceil(len_m / 64).
@@ -319,8 +402,8 @@ int launch_kkt_solve(const KktParams& p, const void* k, int64_t total_tokens, in
   CUtensorMap tm_k;
   int rc = make_tmap_3d(&tm_k, k, total_tokens, p.num_k_heads, kHeadDim, 128, 64, true, is_bf16);
   if (rc != QLA_OK) return rc;
-  // K tile (32 KiB, later the two X tiles: 2 * 64 * 68 * 4 = 34 816 B, hence the larger of the two) + L + T
-  const size_t smem = 1024 + 2 * 64 * kXStride * sizeof(float) + 2 * 64 * kLStride * sizeof(float) +
+  // K tile 32 KiB + X tiles + L tiles (later the Aw tile) + T
+  const size_t smem = 1024 + 32768 + 2 * 64 * kXStride * sizeof(float) + 2 * 64 * kLStride * sizeof(float) +
                       2 * 32 * kTStride * sizeof(float);
   dim3 grid(pairs_upper, p.num_k_heads);
   if (is_bf16) {

@@ -56,20 +56,35 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Bounded wait: gives up after `kSpinLimit` polls (each try_wait itself blocks for a
-// hardware-defined interval), records the failure in *status and returns false so that the
-// caller can leave its loop.  A healthy kernel never gets near the limit.
+// Bounded wait: gives up after `kSpinLimit` polls or `kWaitLimitNs` of wall time, whichever comes
+// first (each try_wait itself blocks for a hardware-defined interval, so the poll count alone does not
+// bound the time), records the failure in *status and returns false so that the caller can leave its
+// loop.  A healthy kernel never gets near the limit.  The recorded word is
+//   code | parity << 16 | warp << 20      (callers put the barrier's index into bits 8..15 of `code`).
 // The first poll is inlined (the barrier has usually completed already); the polling loop is a single
 // non-inlined copy: there are dozens of call sites and the per-chunk code of the chunk kernels has to
 // fit the instruction cache.
 constexpr uint32_t kSpinLimit = 1u << 20;
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ void record_wait_failure(int* status, int code, uint32_t parity) {
+  if (status != nullptr) atomicCAS(status, 0, code | static_cast<int>(parity << 16) | static_cast<int>((threadIdx.x >> 5) << 20));
+}
 static __device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, int* status, int code) {
+  const unsigned long long t0 = global_timer_ns();
   for (uint32_t i = 0; i < kSpinLimit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((i & 1023u) == 1023u && status != nullptr && *reinterpret_cast<volatile int*>(status) != 0)
-      return false;  // another role already failed: do not keep the SM busy
+    if ((i & 63u) == 63u) {
+      if (status != nullptr && *reinterpret_cast<volatile int*>(status) != 0)
+        return false;  // another role already failed: do not keep the SM busy
+      if (global_timer_ns() - t0 > kWaitLimitNs) break;
+    }
   }
-  if (status != nullptr) atomicCAS(status, 0, code);
+  record_wait_failure(status, code, parity);
   return false;
 }
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int code) {
@@ -94,11 +109,15 @@ __device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 static __device__ __noinline__ bool mbar_spin_slow(uint64_t* bar, uint32_t parity, int* status, int code) {
+  const unsigned long long t0 = global_timer_ns();
   for (uint32_t i = 0; i < (kSpinLimit << 4); ++i) {
     if (mbar_test_wait(bar, parity)) return true;
-    if ((i & 16383u) == 16383u && status != nullptr && *reinterpret_cast<volatile int*>(status) != 0) return false;
+    if ((i & 4095u) == 4095u) {
+      if (status != nullptr && *reinterpret_cast<volatile int*>(status) != 0) return false;
+      if (global_timer_ns() - t0 > kWaitLimitNs) break;
+    }
   }
-  if (status != nullptr) atomicCAS(status, 0, code);
+  record_wait_failure(status, code, parity);
   return false;
 }
 __device__ __forceinline__ bool mbar_spin(uint64_t* bar, uint32_t parity, int* status, int code) {

@@ -44,7 +44,9 @@ def check_device_status(device=None) -> None:
         if code != 0:
             st.zero_()
             names = {1: "a bounded barrier wait timed out", 2: "an index was out of range"}
-            raise QlaError(f"device {idx} reported status {code}: {names.get(code, 'unknown')}")
+            # low byte: what happened; the rest says where (barrier index << 8 | parity << 16 | warp << 20)
+            raise QlaError(f"device {idx} reported status {code & 0xFF} (detail {code >> 8:#x}): "
+                           f"{names.get(code & 0xFF, 'unknown')}")
 
 
 def host_seqlens(cu_seqlens: torch.Tensor) -> List[int]:

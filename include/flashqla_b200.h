@@ -99,11 +99,13 @@ enum { /* flags of QlaChunkFwdArgs / QlaChunkBwdArgs */
   QLA_CHUNK_TRANSPOSE_STATE = 1, /* states are [N,Hv,V,K] instead of [N,Hv,K,V]            */
   QLA_CHUNK_STATE_ONLY = 2,      /* skip q / o: only h, v_new and the final state           */
   QLA_CHUNK_QK_L2NORM = 4,       /* normalise q and k rows inside the kernels (reserved)    */
-  QLA_CHUNK_SKIP_PREPARE = 8,    /* g_cumsum and A are inputs (computed by an earlier call) */
+  QLA_CHUNK_SKIP_PREPARE = 8,    /* g_cumsum, A and w are inputs (from an earlier call)     */
   QLA_CHUNK_INIT_IDENTITY = 16,  /* start every sequence from S = I instead of h0          */
   QLA_CHUNK_ZERO_V = 32,         /* treat v as zero (with INIT_IDENTITY: the K x K transition
                                     matrix of the chunks, used by context parallelism)      */
-  QLA_CHUNK_PREPARE_ONLY = 64    /* compute g_cumsum and A only; no scan                     */
+  QLA_CHUNK_PREPARE_ONLY = 64,   /* compute g_cumsum, A and w only; no scan                  */
+  QLA_CHUNK_A_GIVEN = 128        /* g_cumsum and A are inputs, w is rebuilt from them (the
+                                    backward's recomputation of h / v_new)                  */
 };
 
 /*
@@ -143,6 +145,8 @@ typedef struct QlaChunkFwdArgs {
                                  of each (sequence, head), starting from a zero state        */
   float* g_cumsum;     /* out; in with QLA_CHUNK_SKIP_PREPARE                                */
   void* A;             /* out; in with QLA_CHUNK_SKIP_PREPARE                                */
+  void* w;             /* [B,T,Hv,K] in the q/k/v dtype: -(A diag(beta e^g) K), the state-dependent
+                          operand of every chunk; out, in with QLA_CHUNK_SKIP_PREPARE        */
   void* o;             /* out, NULL with QLA_CHUNK_STATE_ONLY                                */
   void* h;             /* out or NULL                                                        */
   void* v_new;         /* out or NULL                                                        */

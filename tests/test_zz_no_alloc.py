@@ -25,14 +25,15 @@ def _args(_cabi, t, out, cu, n_seqs, status):
         beta_dtype=_cabi.dtype_code(beta.dtype), flags=0, max_chunks_per_seq=0, scale=128 ** -0.5,
         q=q.data_ptr(), k=k.data_ptr(), v=v.data_ptr(), g=g.data_ptr(), beta=beta.data_ptr(),
         h0=h0.data_ptr(), cu_seqlens=cu.data_ptr(), seq_map=None, chunk_limit=None,
-        g_cumsum=out["g_cumsum"].data_ptr(), A=out["A"].data_ptr(), o=out["o"].data_ptr(), h=None, v_new=None,
+        g_cumsum=out["g_cumsum"].data_ptr(), A=out["A"].data_ptr(), w=out["w"].data_ptr(), o=out["o"].data_ptr(), h=None, v_new=None,
         final_state=out["fs"].data_ptr(), workspace=None, workspace_bytes=0, status=status.data_ptr())
 
 
 def _outputs(t, n_seqs):
     v = t["v"]
     return dict(g_cumsum=torch.zeros(v.shape[:3], dtype=torch.float32, device=v.device),
-                A=torch.zeros(*v.shape[:3], 64, dtype=v.dtype, device=v.device), o=torch.zeros_like(v),
+                A=torch.zeros(*v.shape[:3], 64, dtype=v.dtype, device=v.device), w=torch.zeros_like(v),
+                o=torch.zeros_like(v),
                 fs=torch.zeros(n_seqs, v.shape[2], 128, 128, dtype=torch.float32, device=v.device))
 
 
