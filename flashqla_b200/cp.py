@@ -6,9 +6,12 @@ planner's constants are re-derived for B200 (148 SMs, one resident chunk-scan CT
 
 * CP is used when the (sequence, v-head) chains alone cannot fill the machine:
   ``chains < 2 * SMs`` and some sequence is long enough to be cut.
-* The segment length aims at ``CTAS_PER_SM`` segment-CTAs per SM, so that dynamic CTA scheduling
-  evens out the tail, with a floor of ``MIN_SEG_CHUNKS`` chunks to keep the warm-up pass (a few
-  trailing chunks per segment, state only) a small fraction of the work.
+* The segment length minimises an estimate of the makespan.  One scan CTA is resident per SM and CTAs
+  are handed to SMs as they free up, so the main scan takes ``ceil(CTAs / SMs)`` rounds of one segment
+  each; the warm-up pass costs another ``WARMUP_CHUNKS`` state-only chunks per round.  What matters
+  is therefore how close ``CTAs / SMs`` comes to an integer from below, not how small the segments are
+  (19 segments x 32 heads = 4.1 rounds is far worse than 9 x 32 = 1.95 rounds).  Floor of
+  ``MIN_SEG_CHUNKS`` chunks per segment.
 
 Everything that depends on tensor VALUES (warm-up lengths, fallback heads) is decided on the device
 (``qla_cp_plan``); the host plan depends on the sequence LENGTHS only, so a cached plan never needs a
@@ -24,8 +27,9 @@ import torch
 from . import _cabi
 
 CHUNK = 64
-CTAS_PER_SM = 4
 MIN_SEG_CHUNKS = 8
+WARMUP_CHUNKS = 10        # typical length of the warm-up pass (chunks until the decay passes the threshold)
+WARMUP_COST = 0.6         # cost of a state-only chunk relative to a full one
 WARMUP_THRESHOLD = -10.0  # exp(-10) ~ 4.5e-5: what a dropped prefix may contribute (cp_fwd.py:29-61)
 
 
@@ -47,11 +51,19 @@ def plan_segments(lens: Sequence[int], num_v_heads: int, num_sms: int = 148) -> 
     """Decide whether to cut sequences and where.  Pure function of lengths, head count, SM count."""
     chunks = [(n + CHUNK - 1) // CHUNK for n in lens]
     chains = len(lens) * num_v_heads
-    total = sum(chunks) * num_v_heads
     if not chunks or chains >= 2 * num_sms or max(chunks) < 2 * MIN_SEG_CHUNKS:
         return CpPlan(use_cp=False)
-    seg = max(MIN_SEG_CHUNKS, -(-total // (CTAS_PER_SM * num_sms)))
-    if max(chunks) <= seg:
+    best, seg = None, 0
+    for cand in range(MIN_SEG_CHUNKS, max(chunks)):
+        ctas = sum(-(-c // cand) for c in chunks) * num_v_heads
+        rounds = -(-ctas // num_sms)
+        # the last segment of a sequence may be shorter; the longest one sets the round time
+        longest = max(min(c, cand) for c in chunks)
+        cost = rounds * (longest + WARMUP_COST * min(WARMUP_CHUNKS, longest))
+        if best is None or cost < best:
+            best, seg = cost, cand
+    uncut = -(-chains // num_sms) * max(chunks)
+    if best is None or best >= uncut:
         return CpPlan(use_cp=False)
     cu, seg_next, seg_raw, raw_first = [0], [], [], [0]
     start = 0

@@ -58,6 +58,7 @@ extern "C" QLA_API int qla_chunk_fwd(const QlaChunkFwdArgs* args, void* stream_)
   QLA_CHECK_ARG(state_only || (a.flags & QLA_CHUNK_PREPARE_ONLY) || (a.q && a.o),
                 "q and o are required unless QLA_CHUNK_STATE_ONLY");
   QLA_CHECK_SUPPORTED(!(a.flags & QLA_CHUNK_QK_L2NORM), "in-kernel q/k L2 norm is not available");
+  QLA_CHECK_SUPPORTED(!(a.flags & QLA_CHUNK_ZERO_V) || state_only, "QLA_CHUNK_ZERO_V needs QLA_CHUNK_STATE_ONLY");
   const int64_t total_tokens = static_cast<int64_t>(a.batch) * a.seq_len;
   if (total_tokens == 0) return QLA_OK;
   QLA_CHECK_ARG(total_tokens < (int64_t(1) << 31), "too many tokens");

@@ -143,6 +143,22 @@ __global__ void __launch_bounds__(128) kkt_solve_kernel(const __grid_constant__ 
   ptx::tc_fence_after_sync();
   const uint32_t tmem = tmem_base_s;
 
+  // gate / beta of the first v-head are requested before anything waits, those of the next head at the
+  // top of every head iteration: their global-memory latency hides behind the work in between
+  const int64_t tok = static_cast<int64_t>(tok0) + tid;
+  const bool valid = tok < seq_end;
+  float gv_n = 0.f, bv_n = 0.f, gin_n = 0.f;
+  auto fetch_gates = [&](int hv) {
+    gv_n = bv_n = gin_n = 0.f;
+    if (valid && hv < (hk + 1) * group) {
+      const int64_t idx = tok * p.num_v_heads + hv;
+      bv_n = load_scalar(p.beta, p.beta_dtype, idx);
+      if (p.A_in != nullptr) gin_n = p.g_cumsum[idx];
+      else gv_n = load_scalar(p.g, p.gate_dtype, idx);
+    }
+  };
+  fetch_gates(hk * group);
+
   if (tid == 0) {
     ptx::mbar_expect_tx(&bar_tma, 32768);
     ptx::tma_load_3d(sK, &tm_k, &bar_tma, 0, hk, tok0);           // columns 0..63 of 128 tokens
@@ -179,18 +195,13 @@ __global__ void __launch_bounds__(128) kkt_solve_kernel(const __grid_constant__ 
     for (int j = 0; j < 32; ++j) kk[32 + j] = __uint_as_float(r[j]);
   }
 
-  const int64_t tok = static_cast<int64_t>(tok0) + tid;
-  const bool valid = tok < seq_end;
   float* Lc = sL + ci * 64 * kLStride;
   T* Ab = static_cast<T*>(p.A);
 
   int mma_uses = 0;  // completed phases of bar_mma after the first (K K^T)
   for (int hv = hk * group; ok && hv < (hk + 1) * group; ++hv) {
-    float gv = 0.f, bv = 0.f;
-    if (valid) {
-      gv = load_scalar(p.g, p.gate_dtype, tok * p.num_v_heads + hv);
-      bv = load_scalar(p.beta, p.beta_dtype, tok * p.num_v_heads + hv);
-    }
+    const float gv = gv_n, bv = bv_n, gin = gin_n;
+    fetch_gates(hv + 1);
     // inclusive scan over the 64 tokens of the chunk (two warps)
     float gcs = gv;
 #pragma unroll
@@ -201,7 +212,7 @@ __global__ void __launch_bounds__(128) kkt_solve_kernel(const __grid_constant__ 
     if (lane == 31) s_part[warp] = gcs;
     __syncthreads();
     if (warp & 1) gcs += s_part[warp - 1];
-    if (p.A_in != nullptr) gcs = valid ? p.g_cumsum[tok * p.num_v_heads + hv] : 0.f;  // gates are cumulative already
+    if (p.A_in != nullptr) gcs = gin;  // gates are cumulative already
     else if (valid) p.g_cumsum[tok * p.num_v_heads + hv] = gcs;
     s_g[tid] = gcs;
     s_bg[tid] = bv * __expf(gcs);

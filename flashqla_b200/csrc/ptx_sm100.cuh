@@ -131,6 +131,18 @@ __device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, i
   return __all_sync(0xffffffffu, mbar_wait(bar, parity, status, code)) != 0;
 }
 
+// Wait executed by a CONVERGED warp, verdict warp-uniform.  The first poll is inline and not voted on:
+// the lanes of a converged warp execute the try_wait as one instruction on one barrier word and see the
+// same answer, so either all of them return here or all of them enter the (non-inlined) polling loop,
+// whose vote makes the verdict uniform even at the edge of the time limit.
+static __device__ __noinline__ bool mbar_wait_warp_slow(uint64_t* bar, uint32_t parity, int* status, int code) {
+  return __all_sync(__activemask(), mbar_wait_slow(bar, parity, status, code)) != 0;
+}
+__device__ __forceinline__ bool mbar_wait_warp_call(uint64_t* bar, uint32_t parity, int* status, int code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  return mbar_wait_warp_slow(bar, parity, status, code);
+}
+
 // ------------------------------------------------------------------------------ fences
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -296,6 +308,80 @@ __device__ __forceinline__ void mma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
                    smem_u32(bar))
                : "memory");
+}
+
+// ---- whole products issued by a CONVERGED warp.
+// A tcgen05.mma is issued by one thread, but when that thread sits in a divergent branch every operand
+// lives in per-thread registers and has to be moved to uniform registers one by one: measured ~55-68
+// cycles of issue per instruction, more than the tensor pipe needs for N <= 128.  Issued from a
+// converged warp with the leader picked by elect.sync INSIDE the asm block, the operand arithmetic stays
+// on the uniform datapath and the cost drops to the pipe's own (34 cycles at N = 64, 68 at N = 128).
+// Descriptor steps are 32-bit adds on the low word (the 14-bit address field never carries).
+// All steps are in units of 16 bytes.  `JUMP` replaces `STEP` between k-steps 3 and 4 (the second
+// 64-element half of a 128-wide operand).
+#define QLA_UMMA_SS_STEP(SA, SB)                                                                     \
+  "add.u32 alo, alo, " SA "; add.u32 blo, blo, " SB "; mov.b64 da, {alo, ahi}; mov.b64 db, {blo, bhi};\n" \
+  "@e tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, t;\n"
+#define QLA_UMMA_SS_HEAD                                                                              \
+  "{\n.reg .pred p, t, e;\n.reg .b32 alo, ahi, blo, bhi;\n.reg .b64 da, db;\n"                         \
+  "elect.sync _|e, 0xffffffff;\nsetp.ne.b32 p, %4, 0;\nsetp.eq.b32 t, 0, 0;\n"                         \
+  "mov.b64 {alo, ahi}, %1;\nmov.b64 {blo, bhi}, %2;\n"                                                 \
+  "@e tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+// D[tmem] (+)= A[smem] B[smem], K = 64 (four instructions).
+template <int A_STEP, int B_STEP>
+__device__ __forceinline__ void umma_ss_k64(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                            bool accumulate) {
+  asm volatile(QLA_UMMA_SS_HEAD QLA_UMMA_SS_STEP("%5", "%6") QLA_UMMA_SS_STEP("%5", "%6") QLA_UMMA_SS_STEP("%5", "%6") "}\n"
+               ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(static_cast<uint32_t>(accumulate)),
+                 "n"(A_STEP), "n"(B_STEP)
+               : "memory");
+}
+// D[tmem] (+)= A[smem] B[smem], K = 128 (eight instructions).
+template <int A_STEP, int A_JUMP, int B_STEP, int B_JUMP>
+__device__ __forceinline__ void umma_ss_k128(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                             bool accumulate) {
+  asm volatile(QLA_UMMA_SS_HEAD QLA_UMMA_SS_STEP("%5", "%6") QLA_UMMA_SS_STEP("%5", "%6") QLA_UMMA_SS_STEP("%5", "%6")
+               QLA_UMMA_SS_STEP("%7", "%8") QLA_UMMA_SS_STEP("%5", "%6") QLA_UMMA_SS_STEP("%5", "%6") QLA_UMMA_SS_STEP("%5", "%6") "}\n"
+               ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(static_cast<uint32_t>(accumulate)),
+                 "n"(A_STEP), "n"(B_STEP), "n"(A_JUMP), "n"(B_JUMP)
+               : "memory");
+}
+#undef QLA_UMMA_SS_STEP
+#undef QLA_UMMA_SS_HEAD
+#define QLA_UMMA_TS_STEP(SB)                                                                         \
+  "add.u32 aa, aa, 8; add.u32 blo, blo, " SB "; mov.b64 db, {blo, bhi};\n"                             \
+  "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [aa], db, %3, t;\n"
+#define QLA_UMMA_TS_HEAD                                                                              \
+  "{\n.reg .pred p, t, e;\n.reg .b32 aa, blo, bhi;\n.reg .b64 db;\n"                                   \
+  "elect.sync _|e, 0xffffffff;\nsetp.ne.b32 p, %4, 0;\nsetp.eq.b32 t, 0, 0;\n"                         \
+  "mov.b32 aa, %1;\nmov.b64 {blo, bhi}, %2;\n"                                                         \
+  "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n"
+// D[tmem] (+)= A[tmem] B[smem], K = 64: A advances 8 TMEM columns (16 values of 16 bits) per instruction.
+template <int B_STEP>
+__device__ __forceinline__ void umma_ts_k64(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                            bool accumulate) {
+  asm volatile(QLA_UMMA_TS_HEAD QLA_UMMA_TS_STEP("%5") QLA_UMMA_TS_STEP("%5") QLA_UMMA_TS_STEP("%5") "}\n"
+               ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(static_cast<uint32_t>(accumulate)), "n"(B_STEP)
+               : "memory");
+}
+// D[tmem] (+)= A[tmem] B[smem], K = 128.
+template <int B_STEP, int B_JUMP>
+__device__ __forceinline__ void umma_ts_k128(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                             bool accumulate) {
+  asm volatile(QLA_UMMA_TS_HEAD QLA_UMMA_TS_STEP("%5") QLA_UMMA_TS_STEP("%5") QLA_UMMA_TS_STEP("%5") QLA_UMMA_TS_STEP("%6")
+               QLA_UMMA_TS_STEP("%5") QLA_UMMA_TS_STEP("%5") QLA_UMMA_TS_STEP("%5") "}\n"
+               ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(static_cast<uint32_t>(accumulate)), "n"(B_STEP),
+                 "n"(B_JUMP)
+               : "memory");
+}
+#undef QLA_UMMA_TS_STEP
+#undef QLA_UMMA_TS_HEAD
+// tcgen05.commit from a converged warp (same elected lane as the umma_* helpers).
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile(
+      "{\n.reg .pred e;\nelect.sync _|e, 0xffffffff;\n"
+      "@e tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n}\n" ::"r"(smem_u32(bar))
+      : "memory");
 }
 
 // Byte offset of element (row, 16-byte chunk `c16`) inside a 128B-swizzled tile whose rows are
