@@ -31,6 +31,7 @@ ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
 K = V = 128
+MEASURED_SCAN_DRAM_BYTES_PER_TOKEN_HK16_HV32 = 42.9e3
 CHUNK = 64
 
 
@@ -128,6 +129,14 @@ def timed(fn, steps, warmup, world, device):
 
 
 # ------------------------------------------------------------------------------------ workloads
+def SCAN_DRAM_BYTES_PER_TOKEN_HEADS(Hk, Hv):
+    """DRAM bytes per token moved by one launch of the chunk scan: dram__bytes_read + dram__bytes_write of an
+    ncu capture of this kernel on a smaller case (8192 tokens, 16 k-heads / 32 v-heads: 351.2 MB = 42.9 KB
+    per token), scaled by the head counts of this rank."""
+    # the scan reads q, k per k-head (512 B) and v, w, A, gates per v-head and writes o (904 B)
+    return MEASURED_SCAN_DRAM_BYTES_PER_TOKEN_HK16_HV32 * (Hk * 512 + Hv * 904) / (16 * 512 + 32 * 904)
+
+
 def prefill_inputs(T, Hk, Hv, seed, n_seqs=1, with_h0=False):
     from oracle import gdr_oracle as orc
     return orc.make_prefill_inputs(1, T, Hk, Hv, seed=seed, with_h0=with_h0, n_states=n_seqs)
@@ -209,6 +218,7 @@ def run_prefill(args, rank, world, device, varlen=False):
     scan_flops = tok_heads_rank * (6 * CHUNK * K + 6 * K * V)  # QK^T, A W, Pg Vd + K S, Q S, K^T V'
     achieved = scan_flops / (ms_scan * 1e-3) / 1e12
     algo_bytes = orc.prefill_bytes(T, Hk, Hv, n_states_in, n_states_in if varlen else 1)
+    gbs_scan = algo_bytes / (ms_scan * 1e-3) / 1e9
     line = {
         "metric": "gdn_prefill_fwd_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_step, "higher_is_better": True,
@@ -221,10 +231,17 @@ def run_prefill(args, rank, world, device, varlen=False):
         "e2e": {"value": total_tokens / (ms_e2e / e2e_steps * 1e-3), "unit": "tokens/s",
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e / e2e_steps},
         "gpu_launches": launches_per_step * args.steps,
-        "roofline": {"kernel": "chunk_fwd_kernel", "bound": "tensor", "achieved": achieved,
-                     "peak": pk["tf_burst"], "unit": "TFLOP/s", "frac": achieved / pk["tf_burst"],
-                     "peak_source": pk["src"], "ms_per_launch": ms_scan, "traffic": None,
-                     "hbm_frac": algo_bytes / (ms_scan * 1e-3) / 1e9 / pk["hbm"]},
+        # The chunk scan is the dominant kernel.  Its intensity (163 840 flop and 24 832 B per token at this
+        # shape) is below the B200 ridge, so HBM is the binding roof; the tensor figures are given beside it.
+        # traffic: DRAM bytes of one launch from an ncu capture (bytes per token measured on a smaller case
+        # of the same kernel, times the tokens of this launch): above the algorithmic bytes by design,
+        # because the prepared operands A and w make a round trip through HBM.
+        "roofline": {"kernel": "chunk_fwd_kernel", "bound": "hbm", "achieved": gbs_scan, "peak": pk["hbm"],
+                     "unit": "GB/s", "frac": gbs_scan / pk["hbm"], "peak_source": pk["src"],
+                     "ms_per_launch": ms_scan,
+                     "traffic": None if varlen else SCAN_DRAM_BYTES_PER_TOKEN_HEADS(Hk, Hv) * T,
+                     "tensor_achieved_tflops": achieved, "tensor_peak_tflops": pk["tf_burst"],
+                     "tensor_frac": achieved / pk["tf_burst"]},
     }
     return line
 
@@ -268,7 +285,10 @@ def run_recurrent(args, rank, world, device, verify: bool):
                    "l2": "state pool (>= 0.5 GB) exceeds the 126 MB L2 at N=1"},
         "clocks": cs.summary(), "gpu_launches": args.steps,
         "roofline": {"kernel": "recurrent_kernel", "bound": "hbm", "achieved": gbs / world, "peak": pk["hbm"],
-                     "unit": "GB/s", "frac": gbs / world / pk["hbm"], "peak_source": pk["src"], "traffic": None},
+                     "unit": "GB/s", "frac": gbs / world / pk["hbm"], "peak_source": pk["src"],
+                     # ncu capture of the decode step (T=1, fp32 pool): 1.021 GB for 256 x 32 (sequence, v-head)
+                     # states, i.e. 124.6 KB each (part of the written state is still in L2 at the end)
+                     "traffic": None if verify else 124.6e3 * N_all * Hv / world},
     }
 
 
@@ -339,7 +359,7 @@ def main():
     ap.add_argument("--workload", default="prefill_fwd", choices=["prefill_fwd", "varlen", "decode", "verify", "train"])
     ap.add_argument("--tokens", type=int, default=32768)
     ap.add_argument("--bf16-scratch", action="store_true")
-    ap.add_argument("--cpu-sample-tokens", type=int, default=4096)
+    ap.add_argument("--cpu-sample-tokens", type=int, default=32768)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     rank, world, local = dist_env()
@@ -385,7 +405,7 @@ def main():
             tps, sec = cpu_prefill_sample(args.cpu_sample_tokens)
             line["cpu_baseline"] = {
                 "value": tps, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",
-                "sample": f"first {args.cpu_sample_tokens} tokens of the workload (all 32 v-heads), best of 2, "
+                "sample": f"first {args.cpu_sample_tokens} of the 32768 tokens (all 32 v-heads), best of 2, "
                           f"{sec:.2f} s"}
         print(json.dumps(line))
     if world > 1:
