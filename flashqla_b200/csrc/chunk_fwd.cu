@@ -57,7 +57,7 @@ constexpr uint32_t kOffVd = kOffO + 16384;           // 2 x 16 KiB Vd^T tiles [1
 constexpr uint32_t kSmemBytes = kOffVd + 2 * 16384 + 1024;
 
 struct alignas(16) Gates {
-  float g[64];
+  float g2[64];      // g * log2(e): the aux warps form exp(g_c - g_d) as ex2 of a difference
   float sgamma[64];  // scale * exp(g)
   float rho[64];
   float beta[64];
@@ -256,7 +256,7 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         const int c = lane + 32 * r;
         const bool ok = c < valid;
         const float gc = gcv[r], bc = bcv[r];
-        gs->g[c] = gc;
+        gs->g2[c] = gc * 1.4426950408889634f;
         gs->sgamma[c] = p.scale * __expf(gc);
         gs->rho[c] = ok ? __expf(gl - gc) : 0.f;
         gs->beta[c] = bc;
@@ -372,6 +372,7 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     const uint32_t tm = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
     // per-warp private copy of the chunk's cumulative gates (two chunks deep)
     float* my_g = aux_g + (warp - 10) * 128;
+    const float log2_scale = __log2f(p.scale);
     bool ok = true;
 #pragma unroll 1
     for (int i = -1; ok && i < nproc; ++i) {
@@ -380,8 +381,8 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         const int j = i + 1, sj = j & 1;
         if (!(ok = wait(kFull0 + sj, (j >> 1) & 1))) break;
         const Gates* gs = gates_of(j);
-        my_g[sj * 64 + lane] = gs->g[lane];
-        my_g[sj * 64 + 32 + lane] = gs->g[32 + lane];
+        my_g[sj * 64 + lane] = gs->g2[lane];
+        my_g[sj * 64 + 32 + lane] = gs->g2[32 + lane];
         uint8_t* at = stage_ptr(sj) + kStageA;
 #pragma unroll 1
         for (int c16 = 0; c16 < 8; ++c16) {
@@ -410,7 +411,9 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         ptx::tc_fence_after_sync();
         if (tid == 320) trace(2, i, 9);
         const int c = r;
-        const float gc = gsg[c];
+        // s * exp(g_c - g_d) = 2^((g2_c + log2 s) - g2_d); above the diagonal the exponent may overflow, the
+        // select below discards those entries
+        const float gc = gsg[c] + log2_scale;
         // Pg tile i & 1 was last read by MMA4 of chunk i - 2; the wait for that is at the end of the previous
         // iteration
         uint8_t* pg = smem + kOffPg + ph * 8192;
@@ -428,8 +431,7 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             float x[8];
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
-              const float e = __expf(fminf(gc - gd[j], 0.f));
-              const float val = p.scale * e * __uint_as_float(pr[j8 + j]);
+              const float val = ptx::ex2(gc - gd[j]) * __uint_as_float(pr[j8 + j]);
               x[j] = (db + j8 + j <= c) ? val : 0.f;
             }
             *reinterpret_cast<uint4*>(pg + ptx::sw128_offset(c, (db + j8) >> 3)) =

@@ -12,8 +12,9 @@
 // chunk's 64 columns in registers for every v-head.  It also produces, per v-head, the chunk operand
 //   Wt = A diag(beta gamma) K      (the "w" of tests/ref_gdr.py:107-147, stored negated)
 // that lets the scan kernel form Vd = A diag(beta) V - Wt S0 with a single state-dependent product:
-// a second tcgen05.mma (block-diagonal [Aw_0 0; 0 Aw_1] times the K tile read MN-major) leaves row t of
-// Wt in TMEM lane t, which thread t writes to global memory as one contiguous 256-byte row.  The inverse of the unit-lower-triangular I + L is
+// one more tcgen05.mma per chunk (the [128][64] tile of -A diag(beta gamma) rows times that chunk's K rows read
+// MN-major) leaves row t of Wt in TMEM lane t, which thread t writes to global memory as one contiguous
+// 256-byte row.  The inverse of the unit-lower-triangular I + L is
 // blocked: the four 16 x 16 diagonal blocks by fp32 forward substitution (one thread per column), then
 // X21 = -X22 (L21 X11) at block size 16 and again at block size 32 with mma.sync m16n8k8 products on
 // fp32 shared-memory tiles, each operand split into two TF32 parts (3xTF32) so that the inverse keeps
@@ -84,12 +85,25 @@ __device__ __forceinline__ void store_tile(float* D, int ldd, const float (&acc)
     *reinterpret_cast<float2*>(D + (g + 8) * ldd + nt * 8 + 2 * c) = make_float2(sign * acc[nt][2], sign * acc[nt][3]);
   }
 }
+template <typename T>
+__device__ __forceinline__ uint32_t pack2(float a, float b);
+template <>
+__device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, float b) {
+  __nv_bfloat162 x = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&x);
+}
+template <>
+__device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
+  __half2 x = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&x);
+}
 __device__ __forceinline__ void pair_sync(int ci) {  // the two warps that own one chunk
   asm volatile("bar.sync %0, 64;" ::"r"(ci + 1) : "memory");
 }
 
 template <typename T>
 __global__ void __launch_bounds__(128) kkt_solve_kernel(const __grid_constant__ CUtensorMap tm_k,
+                                                        const __grid_constant__ CUtensorMap tm_a,
                                                         const KktParams p) {
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int hk = blockIdx.y;
@@ -121,9 +135,10 @@ __global__ void __launch_bounds__(128) kkt_solve_kernel(const __grid_constant__ 
   uint8_t* sK = smem_raw + ((1024u - (ptx::smem_u32(smem_raw) & 1023u)) & 1023u);
   float* sX = reinterpret_cast<float*>(sK + 32768);                                       // [2][64][kXStride]
   float* sL = reinterpret_cast<float*>(sK + 32768 + 2 * 64 * kXStride * sizeof(float));  // [2][64][kLStride]
-  uint8_t* sAw = reinterpret_cast<uint8_t*>(sL);     // 32 KiB block-diagonal Aw tile (SW128), overlays L once solved
+  uint8_t* sAw = reinterpret_cast<uint8_t*>(sL);     // 16 KiB [128 tokens][64] tile -A diag(beta gamma) (SW128), overlays L once solved
+  uint8_t* sAst = sAw + 16384;                       // 16 KiB [128 tokens][64] staging tile of A for the TMA store (SW128)
   float* sT = sL + 2 * 64 * kLStride;                // [2][32][kTStride] products L21 X11
-  __shared__ __align__(16) float s_bg[128];          // beta * gamma per token
+  __shared__ __align__(16) float s_bg[128];          // -beta * gamma per token
   __shared__ __align__(16) float s_g[128];
   __shared__ float s_part[4];
   __shared__ uint64_t bar_tma, bar_mma;
@@ -159,21 +174,23 @@ __global__ void __launch_bounds__(128) kkt_solve_kernel(const __grid_constant__ 
   };
   fetch_gates(hk * group);
 
-  if (tid == 0) {
-    ptx::mbar_expect_tx(&bar_tma, 32768);
-    ptx::tma_load_3d(sK, &tm_k, &bar_tma, 0, hk, tok0);           // columns 0..63 of 128 tokens
-    ptx::tma_load_3d(sK + 16384, &tm_k, &bar_tma, 64, hk, tok0);  // columns 64..127
-    bool ok = ptx::mbar_wait(&bar_tma, 0, p.status, kStatusBarrierTimeout);
-    if (ok) {
-      constexpr uint32_t fmt = sizeof(T) == 2 && std::is_same<T, __nv_bfloat16>::value ? ptx::kFmtBF16 : ptx::kFmtF16;
-      const uint32_t idesc = ptx::mma_idesc(128, 128, fmt, ptx::kMajorK, ptx::kMajorK);
-#pragma unroll
-      for (int ks = 0; ks < 8; ++ks) {
-        const uint64_t d = ptx::smem_desc_sw128(ptx::smem_u32(sK) + (ks >> 2) * 16384 + (ks & 3) * 32, 16, 1024);
-        ptx::mma_ss(tmem, d, d, idesc, ks > 0);
-      }
+  constexpr uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? ptx::kFmtBF16 : ptx::kFmtF16;
+  // Products are issued by warp 0 as a converged warp (one elected lane inside ptx::umma_*): operand
+  // arithmetic then stays on the uniform datapath and an instruction costs its time on the tensor pipe.
+  if (warp == 0) {
+    if (lane == 0) {
+      ptx::mbar_expect_tx(&bar_tma, 32768);
+      ptx::tma_load_3d(sK, &tm_k, &bar_tma, 0, hk, tok0);           // columns 0..63 of 128 tokens
+      ptx::tma_load_3d(sK + 16384, &tm_k, &bar_tma, 64, hk, tok0);  // columns 64..127
     }
-    ptx::mma_commit(&bar_mma);
+    __syncwarp();
+    const bool got = __all_sync(0xffffffffu, ptx::mbar_wait(&bar_tma, 0, p.status, kStatusBarrierTimeout));
+    if (got) {
+      const uint64_t d = ptx::smem_desc_sw128(ptx::smem_u32(sK), 16, 1024);
+      ptx::umma_ss_k128<2, 1024 - 6, 2, 1024 - 6>(tmem, d, d, ptx::mma_idesc(128, 128, fmt, ptx::kMajorK, ptx::kMajorK),
+                                                  false);
+    }
+    ptx::umma_commit(&bar_mma);
   }
   // every thread reaches this point; the AND makes the decision CTA-uniform so that the barriers
   // inside the head loop are never reached by only part of the CTA
@@ -214,21 +231,23 @@ __global__ void __launch_bounds__(128) kkt_solve_kernel(const __grid_constant__ 
     if (warp & 1) gcs += s_part[warp - 1];
     if (p.A_in != nullptr) gcs = gin;  // gates are cumulative already
     else if (valid) p.g_cumsum[tok * p.num_v_heads + hv] = gcs;
-    s_g[tid] = gcs;
-    s_bg[tid] = bv * __expf(gcs);
+    const float gc2 = gcs * 1.4426950408889634f;  // exponents are formed in the log2 domain: one FADD + ex2 each
+    s_g[tid] = gc2;
+    s_bg[tid] = -bv * ptx::ex2(gc2);
     __syncthreads();
 
     // L[c][d] = beta_c * exp(g_c - g_d) * (k_c . k_d) for d < c
     const float* gch = s_g + ci * 64;
-    // branch-free (the causal mask is a select): a data-dependent branch per entry would diverge
+    // branch-free (the causal mask is a select, so an overflowing exponent above the diagonal is harmless):
+    // a data-dependent branch per entry would diverge
 #pragma unroll
     for (int d4 = 0; d4 < 64; d4 += 4) {
       const float4 g4 = *reinterpret_cast<const float4*>(gch + d4);
       float4 l;
-      l.x = bv * __expf(fminf(gcs - g4.x, 0.f)) * kk[d4 + 0];
-      l.y = bv * __expf(fminf(gcs - g4.y, 0.f)) * kk[d4 + 1];
-      l.z = bv * __expf(fminf(gcs - g4.z, 0.f)) * kk[d4 + 2];
-      l.w = bv * __expf(fminf(gcs - g4.w, 0.f)) * kk[d4 + 3];
+      l.x = bv * ptx::ex2(gc2 - g4.x) * kk[d4 + 0];
+      l.y = bv * ptx::ex2(gc2 - g4.y) * kk[d4 + 1];
+      l.z = bv * ptx::ex2(gc2 - g4.z) * kk[d4 + 2];
+      l.w = bv * ptx::ex2(gc2 - g4.w) * kk[d4 + 3];
       l.x = (d4 + 0 < c) ? l.x : 0.f;
       l.y = (d4 + 1 < c) ? l.y : 0.f;
       l.z = (d4 + 2 < c) ? l.z : 0.f;
@@ -294,86 +313,78 @@ __global__ void __launch_bounds__(128) kkt_solve_kernel(const __grid_constant__ 
       store_tile<4>(Xc + R0 * kXStride, kXStride, acc, -1.f);
     }
     pair_sync(ci);
-    {
-      // A rows to global: eight lanes write one 128-byte row, 8 rows per pass of the 64 threads
-      const int64_t row_tok0 = static_cast<int64_t>(tok0) + ci * 64;
-      const int j8 = (c & 7) * 8;
-#pragma unroll 1
-      for (int pass = 0; pass < 8; ++pass) {
-        const int row = pass * 8 + (c >> 3);
-        if (row_tok0 + row < seq_end) {
-          const float4 lo = *reinterpret_cast<const float4*>(Xc + row * kXStride + j8);
-          const float4 hi = *reinterpret_cast<const float4*>(Xc + row * kXStride + j8 + 4);
-          const float xv[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
-          T out[8];
-#pragma unroll
-          for (int e = 0; e < 8; ++e) out[e] = Cvt<T>::from_f32((j8 + e <= row) ? xv[e] : 0.f);
-          *reinterpret_cast<uint4*>(Ab + ((row_tok0 + row) * p.num_v_heads + hv) * 64 + j8) =
-              *reinterpret_cast<const uint4*>(out);
-        }
-      }
-    }
     }  // A_in
-    // ---- Wt = A diag(beta gamma) K for both chunks with one tcgen05.mma: build the block-diagonal
-    // operand [Aw_0 0; 0 Aw_1] (16-bit, K-major, 128B swizzle) over the L area, which is dead now
+    // ---- w = -A diag(beta gamma) K.  Row t of the [128][64] tile holds -A[t][:] .* (beta gamma) of t's own
+    // chunk; one tcgen05.mma per chunk multiplies the WHOLE tile with that chunk's 64 K rows (read MN-major),
+    // so rows 0..63 of the first product and rows 64..127 of the second are the wanted ones and no zero
+    // padding is needed.  The same pass writes A itself (16-bit) into a staging tile for one TMA store.
+    // The upper triangle of X is exactly zero (zero-filled tile, forward substitution yields exact zeros),
+    // and rows / columns of tokens past the sequence end carry beta = 0, so no mask is applied here.
     __syncthreads();
+    const bool full_pair = tok0 + 128 <= seq_end;
     {
       const float* xr = Xc + c * kXStride;
-      uint8_t* own = sAw + ci * 16384 + 0;        // half `ci` holds this chunk's 64 columns
-      uint8_t* other = sAw + (ci ^ 1) * 16384;
       const float* bg = s_bg + ci * 64;
+      T* arow = Ab + (tok * p.num_v_heads + hv) * 64;
 #pragma unroll 1
       for (int c16 = 0; c16 < 8; ++c16) {
         const float4 x0 = *reinterpret_cast<const float4*>(xr + c16 * 8);
         const float4 x1 = *reinterpret_cast<const float4*>(xr + c16 * 8 + 4);
         const float4 b0 = *reinterpret_cast<const float4*>(bg + c16 * 8);
         const float4 b1 = *reinterpret_cast<const float4*>(bg + c16 * 8 + 4);
-        const float xv[8] = {x0.x * b0.x, x0.y * b0.y, x0.z * b0.z, x0.w * b0.w, x1.x * b1.x, x1.y * b1.y, x1.z * b1.z, x1.w * b1.w};
-        T out[8];
-#pragma unroll
-        for (int e = 0; e < 8; ++e) out[e] = Cvt<T>::from_f32((c16 * 8 + e <= c && valid) ? xv[e] : 0.f);
         const uint32_t off = ptx::sw128_offset(tid, c16);  // row = token within the pair
-        *reinterpret_cast<uint4*>(own + off) = *reinterpret_cast<const uint4*>(out);
-        *reinterpret_cast<uint4*>(other + off) = make_uint4(0, 0, 0, 0);
+        *reinterpret_cast<uint4*>(sAw + off) =
+            make_uint4(pack2<T>(x0.x * b0.x, x0.y * b0.y), pack2<T>(x0.z * b0.z, x0.w * b0.w),
+                       pack2<T>(x1.x * b1.x, x1.y * b1.y), pack2<T>(x1.z * b1.z, x1.w * b1.w));
+        if (p.A_in == nullptr) {
+          const uint4 av = make_uint4(pack2<T>(x0.x, x0.y), pack2<T>(x0.z, x0.w), pack2<T>(x1.x, x1.y), pack2<T>(x1.z, x1.w));
+          if (full_pair) *reinterpret_cast<uint4*>(sAst + off) = av;
+          else if (valid) *reinterpret_cast<uint4*>(arow + c16 * 8) = av;  // ragged tail: the next sequence owns the rest
+        }
       }
     }
     ptx::fence_proxy_async_smem();
     ptx::tc_fence_before_sync();
     __syncthreads();
-    if (tid == 0) {
-      ptx::tc_fence_after_sync();
-      constexpr uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? ptx::kFmtBF16 : ptx::kFmtF16;
-      const uint32_t idesc = ptx::mma_idesc(128, 128, fmt, ptx::kMajorK, ptx::kMajorMN);
-#pragma unroll
-      for (int ks = 0; ks < 8; ++ks) {
-        const uint64_t da = ptx::smem_desc_sw128(ptx::smem_u32(sAw) + (ks >> 2) * 16384 + (ks & 3) * 32, 16, 1024);
-        const uint64_t db = ptx::smem_desc_sw128(ptx::smem_u32(sK) + ks * 2048, 16384, 1024);
-        ptx::mma_ss(tmem + 128, da, db, idesc, ks > 0);
+    if (warp == 0) {
+      if (lane == 0 && p.A_in == nullptr && full_pair) {
+        ptx::tma_store_3d(&tm_a, sAst, 0, hv, tok0);
+        ptx::tma_store_commit();
       }
-      ptx::mma_commit(&bar_mma);
+      __syncwarp();
+      ptx::tc_fence_after_sync();
+      const uint32_t idesc = ptx::mma_idesc(128, 128, fmt, ptx::kMajorK, ptx::kMajorMN);
+      const uint64_t da = ptx::smem_desc_sw128(ptx::smem_u32(sAw), 16, 1024);
+      const uint64_t db = ptx::smem_desc_sw128(ptx::smem_u32(sK), 16384, 1024);
+      ptx::umma_ss_k64<2, 128>(tmem, da, db, idesc, false);                       // chunk 0: K rows 0..63
+      ptx::umma_ss_k64<2, 128>(tmem + 128, da, db + (8192 >> 4), idesc, false);   // chunk 1: K rows 64..127
+      ptx::umma_commit(&bar_mma);
     }
     ++mma_uses;
     const bool ok2 = __syncthreads_and(ptx::mbar_wait(&bar_mma, mma_uses & 1, p.status, kStatusBarrierTimeout)) != 0;
     ptx::tc_fence_after_sync();
     if (ok2) {
-      // row `tid` of -Wt: 128 values -> one contiguous 256-byte row of w.  tcgen05.ld is warp-collective:
+      // row `tid` of w: 128 values -> one contiguous 256-byte row.  tcgen05.ld is warp-collective:
       // every lane runs the loop, only lanes with a valid token store.
       T* wrow = static_cast<T*>(p.w) + (tok * p.num_v_heads + hv) * kHeadDim;
-      const uint32_t taddr = tmem + (static_cast<uint32_t>(warp * 32) << 16) + 128;
+      const uint32_t taddr = tmem + (static_cast<uint32_t>(warp * 32) << 16) + ci * 128;
 #pragma unroll 1
-      for (int kb = 0; kb < 128; kb += 16) {
-        uint32_t r[16];
-        ptx::tmem_ld16(taddr + kb, r);
+      for (int kb = 0; kb < 128; kb += 32) {
+        uint32_t r[32];
+        ptx::tmem_ld32(taddr + kb, r);
         ptx::tmem_wait_ld();
-        T out[16];
-#pragma unroll
-        for (int e = 0; e < 16; ++e) out[e] = Cvt<T>::from_f32(-__uint_as_float(r[e]));
         if (valid) {
-          *reinterpret_cast<uint4*>(wrow + kb) = *reinterpret_cast<const uint4*>(out);
-          *reinterpret_cast<uint4*>(wrow + kb + 8) = *reinterpret_cast<const uint4*>(out + 8);
+#pragma unroll
+          for (int e = 0; e < 32; e += 8)
+            *reinterpret_cast<uint4*>(wrow + kb + e) =
+                make_uint4(pack2<T>(__uint_as_float(r[e]), __uint_as_float(r[e + 1])),
+                           pack2<T>(__uint_as_float(r[e + 2]), __uint_as_float(r[e + 3])),
+                           pack2<T>(__uint_as_float(r[e + 4]), __uint_as_float(r[e + 5])),
+                           pack2<T>(__uint_as_float(r[e + 6]), __uint_as_float(r[e + 7])));
         }
       }
     }
+    if (tid == 0) ptx::tma_store_wait_read();  // the staging tile is overwritten by the next head's L
     ptx::tc_fence_before_sync();
     __syncthreads();  // s_g / sL are rewritten for the next head
   }
@@ -410,8 +421,11 @@ int launch_chunk_tables(const int32_t* cu, int n, int32_t* pair_offsets, int32_t
 
 int launch_kkt_solve(const KktParams& p, const void* k, int64_t total_tokens, int pairs_upper, bool is_bf16,
                      cudaStream_t stream) {
-  CUtensorMap tm_k;
+  CUtensorMap tm_k, tm_a;
   int rc = make_tmap_3d(&tm_k, k, total_tokens, p.num_k_heads, kHeadDim, 128, 64, true, is_bf16);
+  if (rc != QLA_OK) return rc;
+  // A leaves through a [128 tokens][64] staging tile; in rebuild mode (A given) the map is made but unused
+  rc = make_tmap_3d(&tm_a, p.A, total_tokens, p.num_v_heads, 64, 128, 64, true, is_bf16);
   if (rc != QLA_OK) return rc;
   // K tile 32 KiB + X tiles + L tiles (later the Aw tile) + T
   const size_t smem = 1024 + 32768 + 2 * 64 * kXStride * sizeof(float) + 2 * 64 * kLStride * sizeof(float) +
@@ -420,11 +434,11 @@ int launch_kkt_solve(const KktParams& p, const void* k, int64_t total_tokens, in
   if (is_bf16) {
     QLA_CHECK_CUDA(cudaFuncSetAttribute(kkt_solve_kernel<__nv_bfloat16>,
                                         cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-    kkt_solve_kernel<__nv_bfloat16><<<grid, 128, smem, stream>>>(tm_k, p);
+    kkt_solve_kernel<__nv_bfloat16><<<grid, 128, smem, stream>>>(tm_k, tm_a, p);
   } else {
     QLA_CHECK_CUDA(cudaFuncSetAttribute(kkt_solve_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                         static_cast<int>(smem)));
-    kkt_solve_kernel<__half><<<grid, 128, smem, stream>>>(tm_k, p);
+    kkt_solve_kernel<__half><<<grid, 128, smem, stream>>>(tm_k, tm_a, p);
   }
   QLA_CHECK_CUDA(cudaGetLastError());
   return QLA_OK;

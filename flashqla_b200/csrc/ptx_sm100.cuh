@@ -143,6 +143,12 @@ __device__ __forceinline__ bool mbar_wait_warp_call(uint64_t* bar, uint32_t pari
   return mbar_wait_warp_slow(bar, parity, status, code);
 }
 
+__device__ __forceinline__ float ex2(float x) {  // 2^x, approximate (the MUFU behind __expf)
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 // ------------------------------------------------------------------------------ fences
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
