@@ -52,7 +52,7 @@ __device__ __forceinline__ void warp_gemm_tf32(float (&acc)[NT][4], const float*
   for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
     for (int e = 0; e < 4; ++e) acc[nt][e] = 0.f;
-#pragma unroll 1
+#pragma unroll 2
   for (int k0 = 0; k0 < K; k0 += 8) {
     // 3xTF32: x = hi + lo with hi = tf32(x), lo = tf32(x - hi); hi*hi + hi*lo + lo*hi keeps the products
     // at fp32-level accuracy (the dropped lo*lo term is ~2^-22 relative)
