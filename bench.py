@@ -200,6 +200,11 @@ def run_prefill(args, rank, world, device, varlen=False):
     d2h = o_host.numel() * o_host.element_size() + fs_host.numel() * fs_host.element_size()
 
     def e2e_step():
+        if not varlen:
+            # one sequence in pinned host memory: copies and compute overlap piece by piece
+            fq.chunk_gated_delta_rule_fwd_host(host["q"], host["k"], host["v"], host["g"], host["beta"],
+                                               out=o_host, final_state_out=fs_host, device=device)
+            return
         d = {n: t.to(device, non_blocking=True) for n, t in host.items()}
         _, _, oo, _, ff = fq.chunk_gated_delta_rule_fwd(d["q"], d["k"], d["v"], d["g"], d["beta"],
                                                         initial_state=d.get("h0"), cu_seqlens=cu_dev,

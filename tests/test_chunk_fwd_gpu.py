@@ -183,3 +183,23 @@ def test_cp_varlen_mixed_lengths(fq):
     ref = orc.chunk_gdr_fwd_varlen(inp["q"], inp["k"], inp["v"], inp["g"], inp["beta"], cu, h0=inp["h0"])
     _check("o", o, ref["o"])
     _check("final_state", fs, ref["final_state"])
+
+
+def test_host_streaming_forward_matches_oracle(fq):
+    """Pinned host tensors in, pinned host results out, copies overlapped with compute piece by piece
+    (pieces of whole chunks with the state carried across): same tolerances as the device forward, and
+    close to the single-call device result."""
+    inp = orc.make_prefill_inputs(1, 1000, 2, 4, seed=31, with_h0=True)
+    host = {n: t.pin_memory() for n, t in inp.items()}
+    o, fs = fq.chunk_gated_delta_rule_fwd_host(host["q"], host["k"], host["v"], host["g"], host["beta"],
+                                               initial_state=host["h0"], piece_tokens=256)
+    fq.check_device_status()
+    ref = orc.chunk_gdr_fwd(inp["q"], inp["k"], inp["v"], inp["g"], inp["beta"], h0=inp["h0"])
+    _check("o", o, ref["o"])
+    _check("final_state", fs[0], ref["final_state"][0])
+    c = _cuda(inp)
+    _, _, o_dev, _, fs_dev = fq.chunk_gated_delta_rule_fwd(c["q"], c["k"], c["v"], c["g"], c["beta"],
+                                                           initial_state=c["h0"])
+    assert orc.rel_rms(o.float(), o_dev.float().cpu()) <= 2e-3
+    with pytest.raises(ValueError):
+        fq.chunk_gated_delta_rule_fwd_host(host["q"].repeat(2, 1, 1, 1), host["k"], host["v"], host["g"], host["beta"])
