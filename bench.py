@@ -175,9 +175,21 @@ def run_prefill(args, rank, world, device, varlen=False):
     h0 = dev.get("h0")
     torch.cuda.synchronize(device)
 
-    def step():
+    def eager_step():
         return fq.chunk_gated_delta_rule_fwd(dev["q"], dev["k"], dev["v"], dev["g"], dev["beta"],
                                              initial_state=h0, cu_seqlens=cu_dev, output_final_state=True)
+
+    # The timed step replays a CUDA graph of the same public call on the same buffers (what a serving loop
+    # with static buffers does): after sharding over several GPUs the host would otherwise need longer to
+    # issue the nine launches of a call than a GPU needs to run them.  --eager times the plain call.
+    step, launch_mode = eager_step, "eager"
+    if not args.eager:
+        try:
+            step = fq.GraphedForward(dev["q"], dev["k"], dev["v"], dev["g"], dev["beta"], initial_state=h0,
+                                     cu_seqlens=cu_dev, output_final_state=True)
+            launch_mode = "cuda_graph"
+        except Exception as exc:  # capture is an optimisation, never a requirement
+            launch_mode = f"eager (graph capture failed: {type(exc).__name__})"
 
     from flashqla_b200 import cp as _cp
     plan_lens = my_lens if varlen else [T]
@@ -229,7 +241,7 @@ def run_prefill(args, rank, world, device, varlen=False):
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_step, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": workload, "sharding": f"v-heads/{world}" if not varlen else f"sequences/{world}",
-                   "context_parallel": use_cp,
+                   "context_parallel": use_cp, "launch": launch_mode,
                    "l2": "inputs (>= 0.8 GB per step) exceed the 126 MB L2; no flush needed",
                    "tokens": total_tokens},
         "clocks": cs.summary(),
@@ -366,6 +378,7 @@ def main():
     ap.add_argument("--bf16-scratch", action="store_true")
     ap.add_argument("--cpu-sample-tokens", type=int, default=32768)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--eager", action="store_true", help="time plain calls instead of CUDA-graph replays")
     args = ap.parse_args()
     rank, world, local = dist_env()
     args.warmup = max(args.warmup, 3)

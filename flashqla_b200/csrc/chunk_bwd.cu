@@ -649,10 +649,8 @@ int launch_chunk_bwd(const BwdParams& p, int total_chunks_upper, bool is_bf16, c
   dim3 chunk_grid(total_chunks_upper, p.num_k_heads);
 #define QLA_LAUNCH_BWD(T)                                                                                  \
   do {                                                                                                     \
-    QLA_CHECK_CUDA(cudaFuncSetAttribute(bwd_scan_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,   \
-                                        static_cast<int>(kScanSmem)));                                     \
-    QLA_CHECK_CUDA(cudaFuncSetAttribute(bwd_chunk_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,  \
-                                        static_cast<int>(kChunkSmem)));                                    \
+    { const int rc_ = ensure_dynamic_smem<bwd_scan_kernel<T>>(kScanSmem); if (rc_ != QLA_OK) return rc_; }       \
+    { const int rc_ = ensure_dynamic_smem<bwd_chunk_kernel<T>>(kChunkSmem); if (rc_ != QLA_OK) return rc_; }     \
     bwd_scan_kernel<T><<<scan_grid, kBwdThreads, kScanSmem, stream>>>(p);                                  \
     QLA_CHECK_CUDA(cudaGetLastError());                                                                    \
     bwd_chunk_kernel<T><<<chunk_grid, kBwdThreads, kChunkSmem, stream>>>(p);                               \

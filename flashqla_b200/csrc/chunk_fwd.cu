@@ -739,9 +739,7 @@ int launch_chunk_fwd(const FwdParams& p, const void* q, const void* k, const voi
   const unsigned grid = static_cast<unsigned>(p.num_seqs) * p.num_v_heads;
 #define QLA_LAUNCH_FWD(T, SO, AUX, TR)                                                                          \
   do {                                                                                                          \
-    QLA_CHECK_CUDA(cudaFuncSetAttribute(chunk_fwd_kernel<T, SO, AUX, TR>,                                       \
-                                        cudaFuncAttributeMaxDynamicSharedMemorySize,                            \
-                                        static_cast<int>(kSmemBytes)));                                         \
+    { const int rc_ = ensure_dynamic_smem<chunk_fwd_kernel<T, SO, AUX, TR>>(kSmemBytes); if (rc_ != QLA_OK) return rc_; }  \
     chunk_fwd_kernel<T, SO, AUX, TR><<<grid, kThreads, kSmemBytes, stream>>>(tm_q, tm_k, tm_v, tm_a, tm_w, tm_o, p); \
   } while (0)
 #define QLA_DISPATCH_FWD(T)                                                                  \

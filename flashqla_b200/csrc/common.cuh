@@ -49,6 +49,20 @@ void set_last_error(const char* fmt, ...);
     }                                                                                     \
   } while (0)
 
+// Raise the dynamic shared-memory limit of kernel `Fn` once per device instead of on every launch (the
+// attribute belongs to the function in that device's context).  `Fn` is a template argument so that every
+// kernel instantiation has its own flags.
+template <auto Fn>
+inline int ensure_dynamic_smem(size_t bytes) {
+  static bool done[64] = {};
+  int dev = 0;
+  QLA_CHECK_CUDA(cudaGetDevice(&dev));
+  if (dev >= 0 && dev < 64 && done[dev]) return QLA_OK;
+  QLA_CHECK_CUDA(cudaFuncSetAttribute(Fn, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes)));
+  if (dev >= 0 && dev < 64) done[dev] = true;
+  return QLA_OK;
+}
+
 // Load one scalar of a runtime dtype (gates, biases: tiny tensors whose dtype varies by caller).
 __device__ __forceinline__ float load_scalar(const void* p, int dtype, int64_t i) {
   if (dtype == QLA_DT_F32) return static_cast<const float*>(p)[i];

@@ -432,12 +432,10 @@ int launch_kkt_solve(const KktParams& p, const void* k, int64_t total_tokens, in
                       2 * 32 * kTStride * sizeof(float);
   dim3 grid(pairs_upper, p.num_k_heads);
   if (is_bf16) {
-    QLA_CHECK_CUDA(cudaFuncSetAttribute(kkt_solve_kernel<__nv_bfloat16>,
-                                        cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    if ((rc = ensure_dynamic_smem<kkt_solve_kernel<__nv_bfloat16>>(smem)) != QLA_OK) return rc;
     kkt_solve_kernel<__nv_bfloat16><<<grid, 128, smem, stream>>>(tm_k, tm_a, p);
   } else {
-    QLA_CHECK_CUDA(cudaFuncSetAttribute(kkt_solve_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        static_cast<int>(smem)));
+    if ((rc = ensure_dynamic_smem<kkt_solve_kernel<__half>>(smem)) != QLA_OK) return rc;
     kkt_solve_kernel<__half><<<grid, 128, smem, stream>>>(tm_k, tm_a, p);
   }
   QLA_CHECK_CUDA(cudaGetLastError());

@@ -203,3 +203,18 @@ def test_host_streaming_forward_matches_oracle(fq):
     assert orc.rel_rms(o.float(), o_dev.float().cpu()) <= 2e-3
     with pytest.raises(ValueError):
         fq.chunk_gated_delta_rule_fwd_host(host["q"].repeat(2, 1, 1, 1), host["k"], host["v"], host["g"], host["beta"])
+
+
+def test_graphed_forward_replays_bitwise(fq):
+    """A captured forward (context-parallel path: nine launches) replays to the same bits as the eager call,
+    also after the inputs were changed in place."""
+    inp = orc.make_prefill_inputs(1, 2048, 2, 4, seed=41)
+    c = _cuda(inp)
+    gf = fq.GraphedForward(c["q"], c["k"], c["v"], c["g"], c["beta"])
+    for round_ in range(2):
+        eager = fq.chunk_gated_delta_rule_fwd(c["q"], c["k"], c["v"], c["g"], c["beta"])
+        out = gf()
+        torch.cuda.synchronize()
+        fq.check_device_status()
+        assert torch.equal(out[2], eager[2]) and torch.equal(out[4], eager[4])
+        c["v"].mul_(0.5)  # new inputs, same buffers
