@@ -18,7 +18,7 @@ _DTYPES = {torch.float32: QLA_DT_F32, torch.bfloat16: QLA_DT_BF16, torch.float16
 
 REC_QK_L2NORM, REC_DISABLE_STATE_UPDATE, REC_A_IS_LOG_DECAY, REC_B_IS_BETA = 1, 2, 4, 8
 CHUNK_TRANSPOSE_STATE, CHUNK_STATE_ONLY, CHUNK_QK_L2NORM, CHUNK_SKIP_PREPARE = 1, 2, 4, 8
-CHUNK_INIT_IDENTITY, CHUNK_ZERO_V, CHUNK_PREPARE_ONLY, CHUNK_A_GIVEN = 16, 32, 64, 128
+CHUNK_INIT_IDENTITY, CHUNK_ZERO_V, CHUNK_PREPARE_ONLY, CHUNK_A_GIVEN, CHUNK_TABLES_READY = 16, 32, 64, 128, 256
 
 
 class QlaError(RuntimeError):

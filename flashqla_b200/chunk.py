@@ -45,10 +45,12 @@ def _check_common(q, k, v, g, beta, initial_state, cu_seqlens, transpose_state_l
 
 
 def _launch_fwd(q, k, v, g, beta, h0, cu, g_cumsum, A, o, h, v_new, final_state, scale, flags=0,
-                seq_map=None, chunk_limit=None, num_seqs=None, w=None):
+                seq_map=None, chunk_limit=None, num_seqs=None, w=None, tables=None):
     """Fill ``QlaChunkFwdArgs`` from tensors and call ``qla_chunk_fwd`` on the current stream.  ``w`` is
     the per-chunk operand ``-(A diag(beta e^g) K)`` that the preparation step writes and the scan reads;
-    it is allocated here when the call does both."""
+    it is allocated here when the call does both.  ``tables`` is an optional dict that keeps the chunk-table
+    workspace of a fixed ``cu`` (the segments of a context-parallel plan) across calls: the first call
+    fills it, later ones skip the table launch."""
     dev = k.device
     if w is None:
         assert not flags & _cabi.CHUNK_SKIP_PREPARE, "a scan without preparation needs the prepared w"
@@ -69,10 +71,17 @@ def _launch_fwd(q, k, v, g, beta, h0, cu, g_cumsum, A, o, h, v_new, final_state,
         h=_cabi.ptr(h), v_new=_cabi.ptr(v_new), final_state=_cabi.ptr(final_state), workspace=None,
         workspace_bytes=0, status=_cabi.ptr(status))
     lib = _cabi.lib()
-    ws_bytes = lib.qla_chunk_fwd_workspace_bytes(args)
-    if ws_bytes:
-        ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
-        args.workspace, args.workspace_bytes = ws.data_ptr(), ws_bytes
+    if tables is not None and "ws" in tables:
+        ws = tables["ws"]
+        args.workspace, args.workspace_bytes = ws.data_ptr(), ws.numel()
+        args.flags = flags | _cabi.CHUNK_TABLES_READY
+    else:
+        ws_bytes = lib.qla_chunk_fwd_workspace_bytes(args)
+        if ws_bytes:
+            ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
+            args.workspace, args.workspace_bytes = ws.data_ptr(), ws_bytes
+            if tables is not None:
+                tables["ws"] = ws  # filled by this call, in stream order before any later reader
     with torch.cuda.device(dev):
         code = lib.qla_chunk_fwd(args, _cabi.current_stream(dev))
     _cabi.check(code, "qla_chunk_fwd")
@@ -93,10 +102,10 @@ def rebuild_w(k, beta, g_cumsum, A, cu):
 
 def launches_per_forward(varlen: bool, use_cp: bool = False) -> int:
     """Kernels of this library one forward call launches.  Plain: [chunk tables] + kkt_solve + chunk
-    scan.  With context parallelism: [tables] + kkt_solve, plan, tables + warm-up scan, tables + transition
-    scan, chain, tables + main scan."""
+    scan.  With context parallelism: [tables] + kkt_solve, plan, warm-up scan, transition scan, chain, main
+    scan (the chunk tables of the plan's segments are computed by the first call with that plan only)."""
     if use_cp:
-        return (2 if varlen else 1) + 1 + 2 + 2 + 1 + 2
+        return (2 if varlen else 1) + 1 + 1 + 1 + 1 + 1
     return 3 if varlen else 2
 
 
@@ -119,7 +128,7 @@ def make_scan_only(q, k, v, beta, g_cumsum, A, o, final_state, initial_state=Non
         def run():
             _launch_fwd(q, k, v, None, beta, cp_h0, plan.dev["cu"], g_cumsum, A, o, None, None, final_state,
                         scale, flags=_cabi.CHUNK_SKIP_PREPARE, seq_map=plan.dev["seg_raw"],
-                        num_seqs=len(plan.seg_next), w=w)
+                        num_seqs=len(plan.seg_next), w=w, tables=plan.tables)
         return run
 
     def run():
@@ -198,7 +207,7 @@ def chunk_gated_delta_rule_fwd(
             fs = torch.empty_like(final_state)
         _launch_fwd(q, k, v, None, beta, cp_h0, plan.dev["cu"], g_cumsum, A, o, h, v_new, fs, scale,
                     flags=_cabi.CHUNK_SKIP_PREPARE, seq_map=plan.dev["seg_raw"], num_seqs=len(plan.seg_next),
-                    w=w)
+                    w=w, tables=plan.tables)
         if fs is not final_state:
             final_state.copy_(fs.transpose(-1, -2))
     else:

@@ -42,6 +42,7 @@ class CpPlan:
     seg_raw: Optional[List[int]] = None      # raw sequence of a segment that ENDS it, else -1
     raw_first: Optional[List[int]] = None    # first segment of every raw sequence, len = n_raw + 1
     dev: Optional[Dict[str, torch.Tensor]] = None
+    tables: Optional[Dict[str, torch.Tensor]] = None  # chunk-table workspace of `cu`, filled by the first launch
 
 
 _PLAN_CACHE: Dict[Tuple, CpPlan] = {}
@@ -87,6 +88,7 @@ def get_plan(lens: Sequence[int], num_v_heads: int, device: torch.device) -> CpP
         sms = torch.cuda.get_device_properties(device).multi_processor_count
         plan = plan_segments(lens, num_v_heads, sms)
         if plan.use_cp:
+            plan.tables = {}
             i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=device)
             n_seg = len(plan.seg_next)
             plan.dev = dict(
@@ -96,9 +98,12 @@ def get_plan(lens: Sequence[int], num_v_heads: int, device: torch.device) -> CpP
                 warm_map=i32([s if s >= 0 else -1 for s in plan.seg_next]),
                 identity=i32(list(range(n_seg))),
                 first_rows=torch.tensor(plan.raw_first[:-1], dtype=torch.int64, device=device))
-        if len(_PLAN_CACHE) >= 256:
-            _PLAN_CACHE.pop(next(iter(_PLAN_CACHE)))
-        _PLAN_CACHE[key] = plan
+        # Plans are never evicted: captured CUDA graphs and in-flight launches keep using a plan's device
+        # tensors.  Past 256 distinct shapes new plans are simply not cached (and do not keep their tables).
+        if len(_PLAN_CACHE) < 256:
+            _PLAN_CACHE[key] = plan
+        else:
+            plan.tables = None
     return plan
 
 
@@ -127,12 +132,12 @@ def segment_initial_states(plan: CpPlan, k, v, beta, g_cumsum, A, w, h0, scale, 
     flags = _cabi.CHUNK_STATE_ONLY | _cabi.CHUNK_SKIP_PREPARE
     # segment-end states from the trailing `warm_limit` chunks, written straight into the successor's row
     launch_fwd(None, k, v, None, beta, None, d["cu"], g_cumsum, A, None, None, None, cp_h0, scale,
-               flags=flags, seq_map=d["warm_map"], chunk_limit=warm_limit, num_seqs=n_seg, w=w)
+               flags=flags, seq_map=d["warm_map"], chunk_limit=warm_limit, num_seqs=n_seg, w=w, tables=plan.tables)
     # transition matrices of the (segment, head) pairs that never decayed below the threshold
     M = torch.empty(n_seg, Hv, 128, 128, dtype=torch.float32, device=dev)
     launch_fwd(None, k, None, None, beta, None, d["cu"], g_cumsum, A, None, None, None, M, scale,
                flags=flags | _cabi.CHUNK_INIT_IDENTITY | _cabi.CHUNK_ZERO_V, seq_map=d["identity"],
-               chunk_limit=m_limit, num_seqs=n_seg, w=w)
+               chunk_limit=m_limit, num_seqs=n_seg, w=w, tables=plan.tables)
     ca = _cabi.QlaCpChainArgs(num_raw_seqs=len(plan.raw_first) - 1, num_v_heads=Hv, h0=cp_h0.data_ptr(),
                               M=M.data_ptr(), m_limit=m_limit.data_ptr(), raw_first_seg=d["raw_first"].data_ptr())
     with torch.cuda.device(dev):

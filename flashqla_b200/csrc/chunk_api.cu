@@ -75,8 +75,10 @@ extern "C" QLA_API int qla_chunk_fwd(const QlaChunkFwdArgs* args, void* stream_)
     QLA_CHECK_ARG((reinterpret_cast<uintptr_t>(a.workspace) & 15u) == 0, "workspace must be 16-byte aligned");
     pair_offsets = static_cast<int32_t*>(a.workspace);
     chunk_offsets = reinterpret_cast<int32_t*>(static_cast<uint8_t*>(a.workspace) + table_bytes(a.num_seqs));
-    int rc = launch_chunk_tables(a.cu_seqlens, a.num_seqs, pair_offsets, chunk_offsets, stream);
-    if (rc != QLA_OK) return rc;
+    if (!(a.flags & QLA_CHUNK_TABLES_READY)) {
+      int rc = launch_chunk_tables(a.cu_seqlens, a.num_seqs, pair_offsets, chunk_offsets, stream);
+      if (rc != QLA_OK) return rc;
+    }
   }
 
   if (!skip_prepare) {

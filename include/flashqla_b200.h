@@ -104,8 +104,11 @@ enum { /* flags of QlaChunkFwdArgs / QlaChunkBwdArgs */
   QLA_CHUNK_ZERO_V = 32,         /* treat v as zero (with INIT_IDENTITY: the K x K transition
                                     matrix of the chunks, used by context parallelism)      */
   QLA_CHUNK_PREPARE_ONLY = 64,   /* compute g_cumsum, A and w only; no scan                  */
-  QLA_CHUNK_A_GIVEN = 128        /* g_cumsum and A are inputs, w is rebuilt from them (the
+  QLA_CHUNK_A_GIVEN = 128,       /* g_cumsum and A are inputs, w is rebuilt from them (the
                                     backward's recomputation of h / v_new)                  */
+  QLA_CHUNK_TABLES_READY = 256   /* the workspace already holds the chunk tables of these
+                                    cu_seqlens (an earlier call with the same cu_seqlens,
+                                    num_seqs and workspace filled it): no table launch      */
 };
 
 /*
