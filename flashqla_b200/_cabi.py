@@ -56,8 +56,8 @@ class QlaChunkFwdArgs(C.Structure):
         ("max_chunks_per_seq", C.c_int32), ("scale", C.c_float),
         ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("g", C.c_void_p),
         ("beta", C.c_void_p), ("h0", C.c_void_p), ("cu_seqlens", C.c_void_p),
-        ("seq_map", C.c_void_p), ("chunk_limit", C.c_void_p), ("g_cumsum", C.c_void_p), ("A", C.c_void_p), ("w", C.c_void_p),
-        ("o", C.c_void_p), ("h", C.c_void_p), ("v_new", C.c_void_p), ("final_state", C.c_void_p),
+        ("seq_map", C.c_void_p), ("seq_order", C.c_void_p), ("chunk_limit", C.c_void_p), ("g_cumsum", C.c_void_p), ("A", C.c_void_p), ("w", C.c_void_p),
+        ("qk_rnorm", C.c_void_p), ("o", C.c_void_p), ("h", C.c_void_p), ("v_new", C.c_void_p), ("final_state", C.c_void_p),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("status", C.c_void_p),
     ]
 

@@ -12,7 +12,7 @@ from typing import Optional
 import torch
 
 from . import _cabi, cp
-from .utils import device_status, host_seqlens, l2norm
+from .utils import device_status, host_seqlens, l2norm, longest_first_order
 
 CHUNK = 64
 
@@ -45,12 +45,13 @@ def _check_common(q, k, v, g, beta, initial_state, cu_seqlens, transpose_state_l
 
 
 def _launch_fwd(q, k, v, g, beta, h0, cu, g_cumsum, A, o, h, v_new, final_state, scale, flags=0,
-                seq_map=None, chunk_limit=None, num_seqs=None, w=None, tables=None):
+                seq_map=None, chunk_limit=None, num_seqs=None, w=None, tables=None, seq_order=None, rnorm=None):
     """Fill ``QlaChunkFwdArgs`` from tensors and call ``qla_chunk_fwd`` on the current stream.  ``w`` is
     the per-chunk operand ``-(A diag(beta e^g) K)`` that the preparation step writes and the scan reads;
     it is allocated here when the call does both.  ``tables`` is an optional dict that keeps the chunk-table
     workspace of a fixed ``cu`` (the segments of a context-parallel plan) across calls: the first call
-    fills it, later ones skip the table launch."""
+    fills it, later ones skip the table launch.  ``rnorm`` ``[B,T,Hk,2]`` switches the in-kernel q / k L2
+    norm on: the preparation step writes the reciprocal row norms there, the scan reads them."""
     dev = k.device
     if w is None:
         assert not flags & _cabi.CHUNK_SKIP_PREPARE, "a scan without preparation needs the prepared w"
@@ -61,13 +62,15 @@ def _launch_fwd(q, k, v, g, beta, h0, cu, g_cumsum, A, o, h, v_new, final_state,
         B, T = 1, B * T
     N = num_seqs if num_seqs is not None else (cu.numel() - 1 if cu is not None else B)
     status = device_status(dev)
+    if rnorm is not None:
+        flags |= _cabi.CHUNK_QK_L2NORM
     args = _cabi.QlaChunkFwdArgs(
         batch=B, seq_len=T, num_seqs=N, num_k_heads=Hk, num_v_heads=Hv,
         qkv_dtype=_cabi.dtype_code(k.dtype), gate_dtype=0 if g is None else _cabi.dtype_code(g.dtype),
         beta_dtype=_cabi.dtype_code(beta.dtype), flags=flags, max_chunks_per_seq=0, scale=float(scale),
         q=_cabi.ptr(q), k=_cabi.ptr(k), v=_cabi.ptr(v), g=_cabi.ptr(g), beta=_cabi.ptr(beta),
-        h0=_cabi.ptr(h0), cu_seqlens=_cabi.ptr(cu), seq_map=_cabi.ptr(seq_map),
-        chunk_limit=_cabi.ptr(chunk_limit), g_cumsum=_cabi.ptr(g_cumsum), A=_cabi.ptr(A), w=_cabi.ptr(w), o=_cabi.ptr(o),
+        h0=_cabi.ptr(h0), cu_seqlens=_cabi.ptr(cu), seq_map=_cabi.ptr(seq_map), seq_order=_cabi.ptr(seq_order),
+        chunk_limit=_cabi.ptr(chunk_limit), g_cumsum=_cabi.ptr(g_cumsum), A=_cabi.ptr(A), w=_cabi.ptr(w), qk_rnorm=_cabi.ptr(rnorm), o=_cabi.ptr(o),
         h=_cabi.ptr(h), v_new=_cabi.ptr(v_new), final_state=_cabi.ptr(final_state), workspace=None,
         workspace_bytes=0, status=_cabi.ptr(status))
     lib = _cabi.lib()
@@ -158,11 +161,14 @@ def chunk_gated_delta_rule_fwd(
     auto_cp: bool = True,
     output_v_new: bool = False,
     transpose_state_layout: bool = False,
+    use_qk_l2norm_in_kernel: bool = False,
 ):
     """Raw forward.  ``g`` is the per-token log decay; returns
     ``(g_cumsum, A, o, h | None, final_state | None[, v_new])`` where ``g_cumsum`` is the chunk-local
     cumulative gate and ``A`` the gated WY matrix ``[B,T,Hv,64]``, both in the form the backward
-    expects."""
+    expects.  ``use_qk_l2norm_in_kernel`` (an addition to the reference's raw forward): q and k are used as
+    ``x * rsqrt(sum(x^2) + 1e-6)`` per row, with the factors folded into the kernels instead of a pass over q
+    and k; ``A`` and ``h`` are then those of the normalised inputs."""
     B, T, Hk, Hv, N = _check_common(q, k, v, g, beta, initial_state, cu_seqlens, transpose_state_layout)
     dev = q.device
     if not q.is_cuda:
@@ -191,6 +197,7 @@ def chunk_gated_delta_rule_fwd(
         h_shape = (1, n_chunks, Hv, 128, 128)
     h = torch.empty(h_shape, dtype=q.dtype, device=dev) if output_h else None
     v_new = torch.empty_like(v) if output_v_new else None
+    rnorm = torch.empty(B, T, Hk, 2, dtype=torch.float32, device=dev) if use_qk_l2norm_in_kernel else None
     final_state = torch.empty(N, Hv, 128, 128, dtype=torch.float32, device=dev) if output_final_state else None
 
     plan = cp.get_plan(lens if lens is not None else [T] * B, Hv, dev) if auto_cp else None
@@ -198,21 +205,23 @@ def chunk_gated_delta_rule_fwd(
         # g_cumsum and A on the original sequences, then per-segment initial states, then the scan
         # over segments (segments are whole chunks, so chunk numbering is unchanged)
         w = new_w(k, beta)
-        _launch_fwd(None, k, None, g, beta, None, cu, g_cumsum, A, None, None, None, None, scale,
-                    flags=_cabi.CHUNK_PREPARE_ONLY, w=w)
+        _launch_fwd(q if rnorm is not None else None, k, None, g, beta, None, cu, g_cumsum, A, None, None, None, None,
+                    scale, flags=_cabi.CHUNK_PREPARE_ONLY, w=w, rnorm=rnorm)
         h0_kv = h0.transpose(-1, -2) if (h0 is not None and transpose_state_layout) else h0
-        cp_h0 = cp.segment_initial_states(plan, k, v, beta, g_cumsum, A, w, h0_kv, scale, _launch_fwd)
+        cp_h0 = cp.segment_initial_states(plan, k, v, beta, g_cumsum, A, w, h0_kv, scale, _launch_fwd, rnorm=rnorm)
         fs = final_state
         if transpose_state_layout and final_state is not None:
             fs = torch.empty_like(final_state)
         _launch_fwd(q, k, v, None, beta, cp_h0, plan.dev["cu"], g_cumsum, A, o, h, v_new, fs, scale,
                     flags=_cabi.CHUNK_SKIP_PREPARE, seq_map=plan.dev["seg_raw"], num_seqs=len(plan.seg_next),
-                    w=w, tables=plan.tables)
+                    w=w, tables=plan.tables, rnorm=rnorm)
         if fs is not final_state:
             final_state.copy_(fs.transpose(-1, -2))
     else:
+        # packed batches of unequal lengths: the longest sequences are handed to the GPU first
+        order = longest_first_order(cu_seqlens, dev) if cu_seqlens is not None else None
         _launch_fwd(q, k, v, g, beta, h0, cu, g_cumsum, A, o, h, v_new, final_state, scale,
-                    flags=_cabi.CHUNK_TRANSPOSE_STATE if transpose_state_layout else 0)
+                    flags=_cabi.CHUNK_TRANSPOSE_STATE if transpose_state_layout else 0, seq_order=order, rnorm=rnorm)
     if output_v_new:
         return g_cumsum, A, o, h, final_state, v_new
     return g_cumsum, A, o, h, final_state
@@ -353,6 +362,15 @@ def chunk_gated_delta_rule(
     if scale is None:
         scale = k.shape[-1] ** -0.5
     if use_qk_l2norm_in_kernel:
+        needs_grad = torch.is_grad_enabled() and any(
+            t is not None and t.requires_grad for t in (q, k, v, g, beta, initial_state))
+        if not needs_grad:
+            # inference: the normalisation is folded into the kernels (no pass over q and k)
+            out = chunk_gated_delta_rule_fwd(q, k, v, g, beta, scale=scale, initial_state=initial_state,
+                                             cu_seqlens=cu_seqlens, output_final_state=output_final_state,
+                                             transpose_state_layout=transpose_state_layout,
+                                             use_qk_l2norm_in_kernel=True)
+            return out[2].to(q.dtype), out[4]
         q, k = l2norm(q), l2norm(k)
     o, final_state = ChunkGatedDeltaRuleFunction.apply(
         q, k, v, g, beta, scale, initial_state, output_final_state, cu_seqlens, transpose_state_layout)

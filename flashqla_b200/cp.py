@@ -107,7 +107,7 @@ def get_plan(lens: Sequence[int], num_v_heads: int, device: torch.device) -> CpP
     return plan
 
 
-def segment_initial_states(plan: CpPlan, k, v, beta, g_cumsum, A, w, h0, scale, launch_fwd):
+def segment_initial_states(plan: CpPlan, k, v, beta, g_cumsum, A, w, h0, scale, launch_fwd, rnorm=None):
     """Run plan -> warm-up -> transition matrices -> chaining.  Returns ``cp_h0`` fp32
     ``[n_seg, Hv, 128, 128]``: the state every segment starts from.  ``launch_fwd`` is
     ``chunk._launch_fwd``; ``w`` is the prepared chunk operand that goes with ``A``."""
@@ -132,12 +132,12 @@ def segment_initial_states(plan: CpPlan, k, v, beta, g_cumsum, A, w, h0, scale, 
     flags = _cabi.CHUNK_STATE_ONLY | _cabi.CHUNK_SKIP_PREPARE
     # segment-end states from the trailing `warm_limit` chunks, written straight into the successor's row
     launch_fwd(None, k, v, None, beta, None, d["cu"], g_cumsum, A, None, None, None, cp_h0, scale,
-               flags=flags, seq_map=d["warm_map"], chunk_limit=warm_limit, num_seqs=n_seg, w=w, tables=plan.tables)
+               flags=flags, seq_map=d["warm_map"], chunk_limit=warm_limit, num_seqs=n_seg, w=w, tables=plan.tables, rnorm=rnorm)
     # transition matrices of the (segment, head) pairs that never decayed below the threshold
     M = torch.empty(n_seg, Hv, 128, 128, dtype=torch.float32, device=dev)
     launch_fwd(None, k, None, None, beta, None, d["cu"], g_cumsum, A, None, None, None, M, scale,
                flags=flags | _cabi.CHUNK_INIT_IDENTITY | _cabi.CHUNK_ZERO_V, seq_map=d["identity"],
-               chunk_limit=m_limit, num_seqs=n_seg, w=w, tables=plan.tables)
+               chunk_limit=m_limit, num_seqs=n_seg, w=w, tables=plan.tables, rnorm=rnorm)
     ca = _cabi.QlaCpChainArgs(num_raw_seqs=len(plan.raw_first) - 1, num_v_heads=Hv, h0=cp_h0.data_ptr(),
                               M=M.data_ptr(), m_limit=m_limit.data_ptr(), raw_first_seg=d["raw_first"].data_ptr())
     with torch.cuda.device(dev):

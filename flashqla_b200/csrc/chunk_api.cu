@@ -57,7 +57,10 @@ extern "C" QLA_API int qla_chunk_fwd(const QlaChunkFwdArgs* args, void* stream_)
   QLA_CHECK_ARG(!(skip_prepare && a_given), "QLA_CHUNK_SKIP_PREPARE and QLA_CHUNK_A_GIVEN exclude each other");
   QLA_CHECK_ARG(state_only || (a.flags & QLA_CHUNK_PREPARE_ONLY) || (a.q && a.o),
                 "q and o are required unless QLA_CHUNK_STATE_ONLY");
-  QLA_CHECK_SUPPORTED(!(a.flags & QLA_CHUNK_QK_L2NORM), "in-kernel q/k L2 norm is not available");
+  const bool l2norm = (a.flags & QLA_CHUNK_QK_L2NORM) != 0;
+  QLA_CHECK_ARG(!l2norm || a.qk_rnorm, "QLA_CHUNK_QK_L2NORM needs the qk_rnorm buffer");
+  QLA_CHECK_ARG(!l2norm || skip_prepare || a.q, "QLA_CHUNK_QK_L2NORM needs q in the preparation step");
+  QLA_CHECK_SUPPORTED(!l2norm || !(a.flags & QLA_CHUNK_A_GIVEN), "QLA_CHUNK_QK_L2NORM with QLA_CHUNK_A_GIVEN");
   QLA_CHECK_SUPPORTED(!(a.flags & QLA_CHUNK_ZERO_V) || state_only, "QLA_CHUNK_ZERO_V needs QLA_CHUNK_STATE_ONLY");
   const int64_t total_tokens = static_cast<int64_t>(a.batch) * a.seq_len;
   if (total_tokens == 0) return QLA_OK;
@@ -85,12 +88,13 @@ extern "C" QLA_API int qla_chunk_fwd(const QlaChunkFwdArgs* args, void* stream_)
     KktParams kp{};
     kp.g = a_given ? static_cast<const void*>(a.g_cumsum) : a.g; kp.beta = a.beta; kp.g_cumsum = a.g_cumsum;
     kp.A = a.A; kp.A_in = a_given ? a.A : nullptr; kp.w = a.w;
+    kp.rnorm = l2norm ? a.qk_rnorm : nullptr; kp.norm_eps = 1e-6f;
     kp.cu_seqlens = a.cu_seqlens; kp.pair_offsets = pair_offsets; kp.status = a.status;
     kp.num_seqs = a.num_seqs; kp.seq_len = a.seq_len; kp.num_k_heads = a.num_k_heads; kp.num_v_heads = a.num_v_heads;
     kp.gate_dtype = a_given ? QLA_DT_F32 : a.gate_dtype; kp.beta_dtype = a.beta_dtype;
     const int pairs_upper = varlen ? static_cast<int>(total_tokens / 128 + a.num_seqs)
                                    : a.batch * ((a.seq_len + 127) / 128);
-    int rc = launch_kkt_solve(kp, a.k, total_tokens, pairs_upper, is_bf16, stream);
+    int rc = launch_kkt_solve(kp, a.k, a.q, total_tokens, pairs_upper, is_bf16, stream);
     if (rc != QLA_OK) return rc;
   }
 
@@ -98,7 +102,8 @@ extern "C" QLA_API int qla_chunk_fwd(const QlaChunkFwdArgs* args, void* stream_)
 
   FwdParams fp{};
   fp.g_cumsum = a.g_cumsum; fp.beta = a.beta; fp.h0 = static_cast<const float*>(a.h0);
-  fp.cu_seqlens = a.cu_seqlens; fp.seq_map = a.seq_map; fp.chunk_offsets = chunk_offsets;
+  fp.cu_seqlens = a.cu_seqlens; fp.seq_map = a.seq_map; fp.seq_order = a.seq_order;
+  fp.rnorm = l2norm ? a.qk_rnorm : nullptr; fp.chunk_offsets = chunk_offsets;
   fp.chunk_limit = a.chunk_limit; fp.o = a.o; fp.v_new = a.v_new; fp.h = a.h; fp.final_state = a.final_state;
   fp.status = a.status; fp.num_seqs = a.num_seqs; fp.seq_len = a.seq_len;
   fp.num_k_heads = a.num_k_heads; fp.num_v_heads = a.num_v_heads; fp.beta_dtype = a.beta_dtype;

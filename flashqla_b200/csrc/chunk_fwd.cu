@@ -57,8 +57,11 @@ constexpr uint32_t kOffVd = kOffO + 16384;           // 2 x 16 KiB Vd^T tiles [1
 constexpr uint32_t kSmemBytes = kOffVd + 2 * 16384 + 1024;
 
 struct alignas(16) Gates {
-  float g2[64];      // g * log2(e): the aux warps form exp(g_c - g_d) as ex2 of a difference
-  float sgamma[64];  // scale * exp(g)
+  // g * log2(e) in the two roles it plays for the aux warps, which form s exp(g_c - g_d) r_q[c] r_k[d] as
+  // ex2(g2row[c] + log2 s - g2col[d]); r_q, r_k = 1 / |q_t|, 1 / |k_t| with in-kernel L2 norm, else 1
+  float g2row[64];   // g log2(e) + log2 r_q
+  float g2col[64];   // g log2(e) - log2 r_k
+  float sgamma[64];  // scale * exp(g) * r_q
   float rho[64];
   float beta[64];
   float egl;
@@ -110,7 +113,8 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   constexpr uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? ptx::kFmtBF16 : ptx::kFmtF16;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int hv = blockIdx.x % p.num_v_heads;
-  const int seq = blockIdx.x / p.num_v_heads;
+  const int slot = blockIdx.x / p.num_v_heads;
+  const int seq = p.seq_order ? p.seq_order[slot] : slot;  // CTAs start in grid order: the caller's order of sequences
   const int hk = hv / (p.num_v_heads / p.num_k_heads);
 
   int seq_start, seq_end;
@@ -138,7 +142,7 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   uint8_t* smem = smem_raw + ((1024u - (ptx::smem_u32(smem_raw) & 1023u)) & 1023u);
   __shared__ uint64_t bars[kNumBars];
   __shared__ uint32_t tmem_base_s;
-  __shared__ __align__(16) float aux_g[2 * 2 * 64];  // [aux warp][chunk parity][64] cumulative gates
+  __shared__ __align__(16) float aux_g[2 * 2 * 128];  // [aux warp][chunk parity][row | column][64] cumulative gates
   // Gate vectors live in their own ring (indexed by chunk, not by stage): the compute warpgroups read
   // them long after the stage's tiles were consumed, and the stage must not wait for that.  Slot reuse
   // needs no barrier: chunk i + 2 is only loaded after MMA3 of chunk i was issued, which needs both
@@ -224,6 +228,7 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       const int64_t last_tok = static_cast<int64_t>(t0) + valid - 1;
       const float gl = p.g_cumsum[last_tok * p.num_v_heads + hv];
       float gcv[2], bcv[2];
+      float2 rn[2];  // (1 / |q|, 1 / |k|)
 #pragma unroll
       for (int r = 0; r < 2; ++r) {
         const int c = lane + 32 * r;
@@ -231,6 +236,8 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         const int64_t tok = static_cast<int64_t>(t0) + c;
         gcv[r] = okc ? p.g_cumsum[tok * p.num_v_heads + hv] : gl;
         bcv[r] = okc ? load_scalar(p.beta, p.beta_dtype, tok * p.num_v_heads + hv) : 0.f;
+        rn[r] = (okc && p.rnorm != nullptr) ? *reinterpret_cast<const float2*>(p.rnorm + (tok * p.num_k_heads + hk) * 2)
+                                           : make_float2(1.f, 1.f);
       }
       if (use > 0 && !wait(kEmpty0 + s, (use - 1) & 1)) break;
       if (lane == 0) trace(0, i, 10);
@@ -256,9 +263,11 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         const int c = lane + 32 * r;
         const bool ok = c < valid;
         const float gc = gcv[r], bc = bcv[r];
-        gs->g2[c] = gc * 1.4426950408889634f;
-        gs->sgamma[c] = p.scale * __expf(gc);
-        gs->rho[c] = ok ? __expf(gl - gc) : 0.f;
+        const float g2 = gc * 1.4426950408889634f;
+        gs->g2row[c] = g2 + __log2f(rn[r].x);
+        gs->g2col[c] = g2 - __log2f(rn[r].y);
+        gs->sgamma[c] = p.scale * __expf(gc) * rn[r].x;
+        gs->rho[c] = ok ? __expf(gl - gc) * rn[r].y : 0.f;
         gs->beta[c] = bc;
       }
       if (lane == 0) {
@@ -371,7 +380,7 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     const int r = tid - 320;  // 0..63: row of A / row c of P
     const uint32_t tm = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
     // per-warp private copy of the chunk's cumulative gates (two chunks deep)
-    float* my_g = aux_g + (warp - 10) * 128;
+    float* my_g = aux_g + (warp - 10) * 256;
     const float log2_scale = __log2f(p.scale);
     bool ok = true;
 #pragma unroll 1
@@ -381,8 +390,10 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         const int j = i + 1, sj = j & 1;
         if (!(ok = wait(kFull0 + sj, (j >> 1) & 1))) break;
         const Gates* gs = gates_of(j);
-        my_g[sj * 64 + lane] = gs->g2[lane];
-        my_g[sj * 64 + 32 + lane] = gs->g2[32 + lane];
+        my_g[sj * 128 + lane] = gs->g2row[lane];
+        my_g[sj * 128 + 32 + lane] = gs->g2row[32 + lane];
+        my_g[sj * 128 + 64 + lane] = gs->g2col[lane];
+        my_g[sj * 128 + 96 + lane] = gs->g2col[32 + lane];
         uint8_t* at = stage_ptr(sj) + kStageA;
 #pragma unroll 1
         for (int c16 = 0; c16 < 8; ++c16) {
@@ -405,7 +416,7 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       }
       if (!kStateOnly && i >= 0) {
         const int ph = i & 1;
-        const float* gsg = my_g + ph * 64;
+        const float* gsg = my_g + ph * 128;
         if (tid == 320) trace(2, i, 8);
         if (!(ok = wait(kPDone0 + ph, (i >> 1) & 1))) break;
         ptx::tc_fence_after_sync();
@@ -414,6 +425,7 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         // s * exp(g_c - g_d) = 2^((g2_c + log2 s) - g2_d); above the diagonal the exponent may overflow, the
         // select below discards those entries
         const float gc = gsg[c] + log2_scale;
+        const float* gcol = gsg + 64;
         // Pg tile i & 1 was last read by MMA4 of chunk i - 2; the wait for that is at the end of the previous
         // iteration
         uint8_t* pg = smem + kOffPg + ph * 8192;
@@ -425,8 +437,8 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           // branch-free: every lane evaluates all entries, the causal mask is a select
 #pragma unroll
           for (int j8 = 0; j8 < 16; j8 += 8) {
-            const float4 ga = *reinterpret_cast<const float4*>(&gsg[db + j8]);
-            const float4 gb = *reinterpret_cast<const float4*>(&gsg[db + j8 + 4]);
+            const float4 ga = *reinterpret_cast<const float4*>(&gcol[db + j8]);
+            const float4 gb = *reinterpret_cast<const float4*>(&gcol[db + j8 + 4]);
             const float gd[8] = {ga.x, ga.y, ga.z, ga.w, gb.x, gb.y, gb.z, gb.w};
             float x[8];
 #pragma unroll

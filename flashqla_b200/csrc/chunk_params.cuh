@@ -12,6 +12,8 @@ struct KktParams {
   void* A;                      // out (unused when A_in is given)
   const void* A_in;             // optional: A from an earlier call -> only w is produced
   void* w;                      // out: -(A diag(beta gamma) K), [NT, Hv, 128]
+  float* rnorm;                 // out or NULL: [NT, Hk, 2] = 1/|q_t|, 1/|k_t| (in-kernel q/k L2 norm)
+  float norm_eps;               // added to the squared norm
   const int32_t* cu_seqlens;    // NULL: equal-length batch of `seq_len` tokens
   const int32_t* pair_offsets;  // [num_seqs + 1] exclusive scan of ceil(len / 128), varlen only
   int* status;
@@ -25,6 +27,8 @@ struct FwdParams {
   const float* h0;              // [n_h0, Hv, 128, 128] or NULL
   const int32_t* cu_seqlens;    // [num_seqs + 1] or NULL (equal-length batch)
   const int32_t* seq_map;       // [num_seqs] row of final_state (< 0: none) or NULL (identity)
+  const int32_t* seq_order;     // [num_seqs] launch order (permutation) or NULL
+  const float* rnorm;           // [NT, Hk, 2] = 1/|q_t|, 1/|k_t| or NULL (q, k used as they are)
   const int32_t* chunk_offsets; // [num_seqs + 1] first chunk index of each sequence (varlen h output)
   const int32_t* chunk_limit;   // [num_seqs, Hv] optional: only the LAST chunk_limit chunks are processed
   void* o;                      // [NT, Hv, 128]
@@ -78,8 +82,8 @@ long long current_trace_count();
 
 int launch_chunk_tables(const int32_t* cu, int n, int32_t* pair_offsets, int32_t* chunk_offsets,
                         cudaStream_t stream);
-int launch_kkt_solve(const KktParams& p, const void* k, int64_t total_tokens, int pairs_upper, bool is_bf16,
-                     cudaStream_t stream);
+int launch_kkt_solve(const KktParams& p, const void* k, const void* q, int64_t total_tokens, int pairs_upper,
+                     bool is_bf16, cudaStream_t stream);
 int launch_chunk_fwd(const FwdParams& p, const void* q, const void* k, const void* v, const void* A,
                      const void* w, int64_t total_tokens, bool is_bf16, bool state_only, cudaStream_t stream);
 

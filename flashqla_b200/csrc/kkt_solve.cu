@@ -103,6 +103,7 @@ __device__ __forceinline__ void pair_sync(int ci) {  // the two warps that own o
 
 template <typename T>
 __global__ void __launch_bounds__(128) kkt_solve_kernel(const __grid_constant__ CUtensorMap tm_k,
+                                                        const __grid_constant__ CUtensorMap tm_q,
                                                         const __grid_constant__ CUtensorMap tm_a,
                                                         const KktParams p) {
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -140,6 +141,7 @@ __global__ void __launch_bounds__(128) kkt_solve_kernel(const __grid_constant__ 
   float* sT = sL + 2 * 64 * kLStride;                // [2][32][kTStride] products L21 X11
   __shared__ __align__(16) float s_bg[128];          // -beta * gamma per token
   __shared__ __align__(16) float s_g[128];
+  __shared__ __align__(16) float s_rk[128];          // 1 / |k_t| per token (in-kernel q/k L2 norm), else unused
   __shared__ float s_part[4];
   __shared__ uint64_t bar_tma, bar_mma;
   __shared__ uint32_t tmem_base_s;
@@ -179,9 +181,13 @@ __global__ void __launch_bounds__(128) kkt_solve_kernel(const __grid_constant__ 
   // arithmetic then stays on the uniform datapath and an instruction costs its time on the tensor pipe.
   if (warp == 0) {
     if (lane == 0) {
-      ptx::mbar_expect_tx(&bar_tma, 32768);
+      ptx::mbar_expect_tx(&bar_tma, p.rnorm != nullptr ? 65536 : 32768);
       ptx::tma_load_3d(sK, &tm_k, &bar_tma, 0, hk, tok0);           // columns 0..63 of 128 tokens
       ptx::tma_load_3d(sK + 16384, &tm_k, &bar_tma, 64, hk, tok0);  // columns 64..127
+      if (p.rnorm != nullptr) {  // the Q tile visits the (still unused) X area, only for its row norms
+        ptx::tma_load_3d(sK + 32768, &tm_q, &bar_tma, 0, hk, tok0);
+        ptx::tma_load_3d(sK + 32768 + 16384, &tm_q, &bar_tma, 64, hk, tok0);
+      }
     }
     __syncwarp();
     const bool got = __all_sync(0xffffffffu, ptx::mbar_wait(&bar_tma, 0, p.status, kStatusBarrierTimeout));
@@ -192,8 +198,40 @@ __global__ void __launch_bounds__(128) kkt_solve_kernel(const __grid_constant__ 
     }
     ptx::umma_commit(&bar_mma);
   }
+  // In-kernel L2 norm of q and k (reference: l2norm before the kernels, flash_qla/utils/math.py:14-21 via
+  // chunk/__init__.py:332-334): thread t computes 1/sqrt(|row t|^2 + eps) of its K and Q rows while the
+  // product runs.  Everything downstream uses the RAW tiles and folds the factors in: K K^T[c][d] r_c r_d
+  // here, r_k into beta gamma for w; the scan folds r_k into rho, r_q into s gamma and both into Pg.
+  float rk_c = 1.f;
+  if (p.rnorm != nullptr) {
+    const bool got = ptx::mbar_wait(&bar_tma, 0, p.status, kStatusBarrierTimeout);
+    float sk = 0.f, sq = 0.f;
+    if (got) {
+#pragma unroll 1
+      for (int h = 0; h < 2; ++h)
+#pragma unroll 2
+        for (int c16 = 0; c16 < 8; ++c16) {
+          const uint32_t off = h * 16384 + ptx::sw128_offset(tid, c16);
+          const uint4 kv = *reinterpret_cast<const uint4*>(sK + off);
+          const uint4 qv = *reinterpret_cast<const uint4*>(sK + 32768 + off);
+          const T* ke = reinterpret_cast<const T*>(&kv);
+          const T* qe = reinterpret_cast<const T*>(&qv);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const float a = Cvt<T>::to_f32(ke[e]), b = Cvt<T>::to_f32(qe[e]);
+            sk += a * a;
+            sq += b * b;
+          }
+        }
+    }
+    rk_c = rsqrtf(sk + p.norm_eps);
+    const float rq_c = rsqrtf(sq + p.norm_eps);
+    s_rk[tid] = rk_c;
+    if (valid) *reinterpret_cast<float2*>(p.rnorm + (tok * p.num_k_heads + hk) * 2) = make_float2(rq_c, rk_c);
+  }
   // every thread reaches this point; the AND makes the decision CTA-uniform so that the barriers
-  // inside the head loop are never reached by only part of the CTA
+  // inside the head loop are never reached by only part of the CTA (it also orders s_rk and the last reads
+  // of the Q tile before the head loop reuses that memory)
   const bool ok = __syncthreads_and(ptx::mbar_wait(&bar_mma, 0, p.status, kStatusBarrierTimeout)) != 0;
   ptx::tc_fence_after_sync();
 
@@ -210,6 +248,11 @@ __global__ void __launch_bounds__(128) kkt_solve_kernel(const __grid_constant__ 
     ptx::tmem_wait_ld();
 #pragma unroll
     for (int j = 0; j < 32; ++j) kk[32 + j] = __uint_as_float(r[j]);
+    if (p.rnorm != nullptr) {
+      const float* rkc = s_rk + ci * 64;
+#pragma unroll
+      for (int j = 0; j < 64; ++j) kk[j] *= rk_c * rkc[j];
+    }
   }
 
   float* Lc = sL + ci * 64 * kLStride;
@@ -233,7 +276,7 @@ __global__ void __launch_bounds__(128) kkt_solve_kernel(const __grid_constant__ 
     else if (valid) p.g_cumsum[tok * p.num_v_heads + hv] = gcs;
     const float gc2 = gcs * 1.4426950408889634f;  // exponents are formed in the log2 domain: one FADD + ex2 each
     s_g[tid] = gc2;
-    s_bg[tid] = -bv * ptx::ex2(gc2);
+    s_bg[tid] = -bv * ptx::ex2(gc2) * rk_c;
     __syncthreads();
 
     // L[c][d] = beta_c * exp(g_c - g_d) * (k_c . k_d) for d < c
@@ -419,10 +462,13 @@ int launch_chunk_tables(const int32_t* cu, int n, int32_t* pair_offsets, int32_t
   return QLA_OK;
 }
 
-int launch_kkt_solve(const KktParams& p, const void* k, int64_t total_tokens, int pairs_upper, bool is_bf16,
-                     cudaStream_t stream) {
-  CUtensorMap tm_k, tm_a;
+int launch_kkt_solve(const KktParams& p, const void* k, const void* q, int64_t total_tokens, int pairs_upper,
+                     bool is_bf16, cudaStream_t stream) {
+  CUtensorMap tm_k, tm_q, tm_a;
   int rc = make_tmap_3d(&tm_k, k, total_tokens, p.num_k_heads, kHeadDim, 128, 64, true, is_bf16);
+  if (rc != QLA_OK) return rc;
+  // q is only read for the in-kernel L2 norm (p.rnorm set); otherwise the map is made over k and unused
+  rc = make_tmap_3d(&tm_q, p.rnorm != nullptr ? q : k, total_tokens, p.num_k_heads, kHeadDim, 128, 64, true, is_bf16);
   if (rc != QLA_OK) return rc;
   // A leaves through a [128 tokens][64] staging tile; in rebuild mode (A given) the map is made but unused
   rc = make_tmap_3d(&tm_a, p.A, total_tokens, p.num_v_heads, 64, 128, 64, true, is_bf16);
@@ -433,10 +479,10 @@ int launch_kkt_solve(const KktParams& p, const void* k, int64_t total_tokens, in
   dim3 grid(pairs_upper, p.num_k_heads);
   if (is_bf16) {
     if ((rc = ensure_dynamic_smem<kkt_solve_kernel<__nv_bfloat16>>(smem)) != QLA_OK) return rc;
-    kkt_solve_kernel<__nv_bfloat16><<<grid, 128, smem, stream>>>(tm_k, tm_a, p);
+    kkt_solve_kernel<__nv_bfloat16><<<grid, 128, smem, stream>>>(tm_k, tm_q, tm_a, p);
   } else {
     if ((rc = ensure_dynamic_smem<kkt_solve_kernel<__half>>(smem)) != QLA_OK) return rc;
-    kkt_solve_kernel<__half><<<grid, 128, smem, stream>>>(tm_k, tm_a, p);
+    kkt_solve_kernel<__half><<<grid, 128, smem, stream>>>(tm_k, tm_q, tm_a, p);
   }
   QLA_CHECK_CUDA(cudaGetLastError());
   return QLA_OK;

@@ -6,13 +6,14 @@ are seen).
 """
 from __future__ import annotations
 
-from typing import Dict, List, Tuple
+from typing import Optional, Dict, List, Tuple
 
 import torch
 
 _STATUS: Dict[int, torch.Tensor] = {}
 _SEQLEN_CACHE: Dict[Tuple, List[int]] = {}
 _SEQLEN_CACHE_MAX = 256
+_ORDER_CACHE: Dict[Tuple, Optional[torch.Tensor]] = {}
 
 
 def l2norm(x: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
@@ -63,3 +64,22 @@ def host_seqlens(cu_seqlens: torch.Tensor) -> List[int]:
             _SEQLEN_CACHE.pop(next(iter(_SEQLEN_CACHE)))
         _SEQLEN_CACHE[key] = lens
     return lens
+
+
+def longest_first_order(cu_seqlens: torch.Tensor, device: torch.device) -> Optional[torch.Tensor]:
+    """Int32 permutation on ``device`` that lists the sequences of ``cu_seqlens`` longest first, or ``None``
+    when that changes nothing (one sequence, equal lengths).  The chunk scan hands sequences to the GPU in
+    this order, so the longest chains start first instead of forming the tail.  Cached like
+    ``host_seqlens``; entries are never evicted (launches in flight and captured graphs use the tensor), past
+    the cache limit the permutation is simply rebuilt per call."""
+    key = (cu_seqlens.data_ptr(), cu_seqlens.numel(), str(cu_seqlens.device), cu_seqlens._version, str(device))
+    if key in _ORDER_CACHE:
+        return _ORDER_CACHE[key]
+    lens = host_seqlens(cu_seqlens)
+    order = None
+    if len(lens) > 1 and min(lens) != max(lens):
+        idx = sorted(range(len(lens)), key=lambda i: -lens[i])
+        order = torch.tensor(idx, dtype=torch.int32, device=device)
+    if len(_ORDER_CACHE) < _SEQLEN_CACHE_MAX:
+        _ORDER_CACHE[key] = order
+    return order

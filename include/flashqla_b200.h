@@ -98,7 +98,8 @@ QLA_API int qla_recurrent_update(const QlaRecurrentArgs* args, void* stream);
 enum { /* flags of QlaChunkFwdArgs / QlaChunkBwdArgs */
   QLA_CHUNK_TRANSPOSE_STATE = 1, /* states are [N,Hv,V,K] instead of [N,Hv,K,V]            */
   QLA_CHUNK_STATE_ONLY = 2,      /* skip q / o: only h, v_new and the final state           */
-  QLA_CHUNK_QK_L2NORM = 4,       /* normalise q and k rows inside the kernels (reserved)    */
+  QLA_CHUNK_QK_L2NORM = 4,       /* use q / |q| and k / |k| (rows, eps 1e-6) without a pass
+                                    over q and k: needs qk_rnorm                            */
   QLA_CHUNK_SKIP_PREPARE = 8,    /* g_cumsum, A and w are inputs (from an earlier call)     */
   QLA_CHUNK_INIT_IDENTITY = 16,  /* start every sequence from S = I instead of h0          */
   QLA_CHUNK_ZERO_V = 32,         /* treat v as zero (with INIT_IDENTITY: the K x K transition
@@ -144,12 +145,17 @@ typedef struct QlaChunkFwdArgs {
   const void* h0;      /* NULL = zero                                                        */
   const int32_t* cu_seqlens;
   const int32_t* seq_map;
+  const int32_t* seq_order;   /* device int32 [N] or NULL: the order in which sequences are handed to the
+                                 GPU (a permutation of 0..N-1); longest first shortens the tail of
+                                 batches with very different lengths                          */
   const int32_t* chunk_limit; /* device int32 [N,Hv] or NULL: run only the last chunk_limit chunks
                                  of each (sequence, head), starting from a zero state        */
   float* g_cumsum;     /* out; in with QLA_CHUNK_SKIP_PREPARE                                */
   void* A;             /* out; in with QLA_CHUNK_SKIP_PREPARE                                */
   void* w;             /* [B,T,Hv,K] in the q/k/v dtype: -(A diag(beta e^g) K), the state-dependent
                           operand of every chunk; out, in with QLA_CHUNK_SKIP_PREPARE        */
+  float* qk_rnorm;     /* [B,T,Hk,2] fp32, only with QLA_CHUNK_QK_L2NORM: 1/|q_t|, 1/|k_t|; written by
+                          the preparation step, read by the scan (in with QLA_CHUNK_SKIP_PREPARE) */
   void* o;             /* out, NULL with QLA_CHUNK_STATE_ONLY                                */
   void* h;             /* out or NULL                                                        */
   void* v_new;         /* out or NULL                                                        */

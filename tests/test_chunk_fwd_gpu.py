@@ -218,3 +218,35 @@ def test_graphed_forward_replays_bitwise(fq):
         fq.check_device_status()
         assert torch.equal(out[2], eager[2]) and torch.equal(out[4], eager[4])
         c["v"].mul_(0.5)  # new inputs, same buffers
+
+
+@pytest.mark.parametrize("T,use_cp", [(300, False), (4096, True)])
+def test_in_kernel_qk_l2norm(fq, T, use_cp):
+    """``use_qk_l2norm_in_kernel``: un-normalised q, k in, the row norms folded into the kernels.  Oracle: the
+    reference's order of operations, l2norm (fp32, eps 1e-6, rounded back to the input dtype) then the op
+    (flash_qla/ops/gated_delta_rule/chunk/__init__.py:332-334)."""
+    from flashqla_b200 import cp
+    inp = orc.make_prefill_inputs(1, T, 2, 4, seed=51, with_h0=True)
+    gen = torch.Generator().manual_seed(52)
+    # rows of very different lengths
+    inp["q"] = (inp["q"].float() * (0.2 + 3.0 * torch.rand(1, T, 2, 1, generator=gen))).to(inp["q"].dtype)
+    inp["k"] = (inp["k"].float() * (0.2 + 3.0 * torch.rand(1, T, 2, 1, generator=gen))).to(inp["k"].dtype)
+    assert cp.plan_segments([T], 4, 148).use_cp == use_cp
+    c = _cuda(inp)
+    g_cs, A, o, h, fs = fq.chunk_gated_delta_rule_fwd(c["q"], c["k"], c["v"], c["g"], c["beta"],
+                                                      initial_state=c["h0"], use_qk_l2norm_in_kernel=True)
+    fq.check_device_status()
+    qn, kn = orc.l2norm(inp["q"].float()).to(inp["q"].dtype), orc.l2norm(inp["k"].float()).to(inp["k"].dtype)
+    ref = orc.chunk_gdr_fwd(qn, kn, inp["v"], inp["g"], inp["beta"], h0=inp["h0"])
+    _check("o", o, ref["o"])
+    _check("final_state", fs, ref["final_state"])
+    assert orc.rel_rms(A.float().cpu(), ref["A"]) < 5e-3
+    # the public op takes this path when no gradient is asked for, and agrees with its autograd path
+    with torch.no_grad():
+        o_pub, fs_pub = fq.chunk_gated_delta_rule(c["q"], c["k"], c["v"], c["g"], c["beta"], initial_state=c["h0"],
+                                                  output_final_state=True, use_qk_l2norm_in_kernel=True)
+    assert torch.equal(o_pub, o)
+    qg = c["q"].clone().requires_grad_(True)
+    o_ag, _ = fq.chunk_gated_delta_rule(qg, c["k"], c["v"], c["g"], c["beta"], initial_state=c["h0"],
+                                        output_final_state=True, use_qk_l2norm_in_kernel=True)
+    assert orc.rel_rms(o_ag.detach().float().cpu(), o.float().cpu()) <= 4e-3
