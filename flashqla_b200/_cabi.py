@@ -76,6 +76,14 @@ class QlaChunkBwdArgs(C.Structure):
     ]
 
 
+class QlaStateCommitArgs(C.Structure):
+    _fields_ = [
+        ("num_seqs", C.c_int32), ("num_v_heads", C.c_int32), ("inter_dtype", C.c_int32), ("inter_steps", C.c_int32),
+        ("inter_slots", C.c_int64), ("state_slots", C.c_int64), ("inter", C.c_void_p), ("accepted", C.c_void_p),
+        ("state_indices", C.c_void_p), ("inter_indices", C.c_void_p), ("state", C.c_void_p), ("status", C.c_void_p),
+    ]
+
+
 class QlaCpPlanArgs(C.Structure):
     _fields_ = [
         ("num_segments", C.c_int32), ("num_v_heads", C.c_int32), ("threshold", C.c_float),
@@ -94,6 +102,7 @@ class QlaCpChainArgs(C.Structure):
 # Every symbol include/flashqla_b200.h declares; tests check that the built library exports each.
 EXPORTS = {
     "qla_recurrent_update": (C.c_int, [C.POINTER(QlaRecurrentArgs), C.c_void_p]),
+    "qla_state_commit": (C.c_int, [C.POINTER(QlaStateCommitArgs), C.c_void_p]),
     "qla_chunk_fwd_workspace_bytes": (C.c_size_t, [C.POINTER(QlaChunkFwdArgs)]),
     "qla_chunk_fwd": (C.c_int, [C.POINTER(QlaChunkFwdArgs), C.c_void_p]),
     "qla_chunk_fwd_noalloc": (C.c_int, [C.POINTER(QlaChunkFwdArgs), C.c_void_p]),

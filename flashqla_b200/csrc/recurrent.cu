@@ -258,6 +258,59 @@ int launch_recurrent(const QlaRecurrentArgs& a, int rows, cudaStream_t stream) {
 }  // namespace
 }  // namespace qla
 
+namespace qla {
+namespace {
+// One CTA per (sequence, v-head): 128 x 128 values = 64 KiB of fp32 state, 128-bit accesses.
+template <typename InterT>
+__global__ void __launch_bounds__(256) state_commit_kernel(const QlaStateCommitArgs a) {
+  const int n = blockIdx.x, hv = blockIdx.y;
+  const int acc = a.accepted[n];
+  if (acc <= 0) return;
+  const int64_t sslot = a.state_indices ? a.state_indices[n] : n;
+  const int64_t islot = a.inter_indices ? a.inter_indices[n] : n;
+  if (acc > a.inter_steps || sslot < 0 || sslot >= a.state_slots || islot < 0 || islot >= a.inter_slots) {
+    if (a.status != nullptr && threadIdx.x == 0) atomicCAS(a.status, 0, kStatusBadIndex);
+    return;
+  }
+  constexpr int kElems = kHeadDim * kHeadDim;
+  const InterT* src = static_cast<const InterT*>(a.inter) +
+                      ((islot * a.inter_steps + (acc - 1)) * a.num_v_heads + hv) * static_cast<int64_t>(kElems);
+  float* dst = a.state + (sslot * a.num_v_heads + hv) * static_cast<int64_t>(kElems);
+  for (int i = threadIdx.x * 8; i < kElems; i += 256 * 8) {
+    float x[8];
+    if (sizeof(InterT) == 4) {
+      const float4 lo = *reinterpret_cast<const float4*>(src + i), hi = *reinterpret_cast<const float4*>(src + i + 4);
+      x[0] = lo.x; x[1] = lo.y; x[2] = lo.z; x[3] = lo.w; x[4] = hi.x; x[5] = hi.y; x[6] = hi.z; x[7] = hi.w;
+    } else {
+      const uint4 raw = *reinterpret_cast<const uint4*>(src + i);
+      const InterT* e = reinterpret_cast<const InterT*>(&raw);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) x[j] = Cvt<InterT>::to_f32(e[j]);
+    }
+    *reinterpret_cast<float4*>(dst + i) = make_float4(x[0], x[1], x[2], x[3]);
+    *reinterpret_cast<float4*>(dst + i + 4) = make_float4(x[4], x[5], x[6], x[7]);
+  }
+}
+}  // namespace
+}  // namespace qla
+
+extern "C" QLA_API int qla_state_commit(const QlaStateCommitArgs* args, void* stream) {
+  using namespace qla;
+  QLA_CHECK_ARG(args != nullptr, "args is NULL");
+  const QlaStateCommitArgs& a = *args;
+  QLA_CHECK_ARG(a.num_seqs >= 0 && a.num_v_heads > 0, "bad sizes");
+  if (a.num_seqs == 0) return QLA_OK;
+  QLA_CHECK_ARG(a.inter && a.accepted && a.state, "NULL tensor pointer");
+  QLA_CHECK_ARG(a.inter_slots > 0 && a.inter_steps > 0 && a.state_slots > 0, "extents must be positive");
+  QLA_CHECK_SUPPORTED(a.inter_dtype == QLA_DT_F32 || a.inter_dtype == QLA_DT_BF16,
+                      "intermediate_states_buffer must be fp32 or bf16");
+  dim3 grid(a.num_seqs, a.num_v_heads);
+  if (a.inter_dtype == QLA_DT_F32) state_commit_kernel<float><<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(a);
+  else state_commit_kernel<__nv_bfloat16><<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(a);
+  QLA_CHECK_CUDA(cudaGetLastError());
+  return QLA_OK;
+}
+
 extern "C" QLA_API int qla_recurrent_update(const QlaRecurrentArgs* args, void* stream) {
   using namespace qla;
   QLA_CHECK_ARG(args != nullptr, "args is NULL");

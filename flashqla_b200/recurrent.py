@@ -178,3 +178,40 @@ def fused_sigmoid_gating_delta_rule_update(
 
 
 flashqla_recurrent_gdn_update = fused_sigmoid_gating_delta_rule_update
+
+
+def commit_verified_state(
+    initial_state_source: torch.Tensor,
+    intermediate_states_buffer: torch.Tensor,
+    num_accepted: torch.Tensor,
+    initial_state_indices: Optional[torch.Tensor] = None,
+    intermediate_state_indices: Optional[torch.Tensor] = None,
+) -> None:
+    """After a verify step (``disable_state_update=True`` with ``intermediate_states_buffer``): write the state
+    that follows the last ACCEPTED draft token of every sequence back into the pool, in place,
+    ``state[initial_state_indices[n]] = intermediate[intermediate_state_indices[n], num_accepted[n] - 1]``;
+    ``num_accepted[n] == 0`` leaves a sequence's state as it was.  Argument names follow
+    ``fused_sigmoid_gating_delta_rule_update``; the reference leaves this step to its caller."""
+    state, inter = initial_state_source, intermediate_states_buffer
+    if inter.dim() != 5 or tuple(inter.shape[3:]) != (128, 128):
+        raise ValueError("intermediate_states_buffer must be [slots, steps, HV, 128, 128]")
+    Hv = inter.shape[2]
+    if not state.is_contiguous() or not inter.is_contiguous():
+        raise ValueError("the state pool and intermediate_states_buffer must be contiguous")
+    if state.dtype != torch.float32 or state.numel() % (Hv * 128 * 128) != 0:
+        raise ValueError("initial_state_source must be a float32 pool of [HV, 128, 128] states")
+    if inter.dtype not in (torch.float32, torch.bfloat16):
+        raise NotImplementedError("intermediate_states_buffer must be float32 or bfloat16")
+    dev = state.device
+    acc = _i32(num_accepted, dev)
+    sidx = _i32(initial_state_indices, dev)
+    cidx = _i32(intermediate_state_indices, dev)
+    from .utils import device_status
+    args = _cabi.QlaStateCommitArgs(
+        num_seqs=acc.numel(), num_v_heads=Hv, inter_dtype=_cabi.dtype_code(inter.dtype), inter_steps=inter.shape[1],
+        inter_slots=inter.shape[0], state_slots=state.numel() // (Hv * 128 * 128), inter=_cabi.ptr(inter),
+        accepted=_cabi.ptr(acc), state_indices=_cabi.ptr(sidx), inter_indices=_cabi.ptr(cidx),
+        state=_cabi.ptr(state), status=_cabi.ptr(device_status(dev)))
+    with torch.cuda.device(dev):
+        code = _cabi.lib().qla_state_commit(args, _cabi.current_stream(dev))
+    _cabi.check(code, "qla_state_commit")

@@ -95,6 +95,29 @@ typedef struct QlaRecurrentArgs {
 
 QLA_API int qla_recurrent_update(const QlaRecurrentArgs* args, void* stream);
 
+/* Commit of accepted draft tokens after a speculative-decoding verify step.  The reference's verify
+ * convention leaves the state pool untouched (disable_state_update) and caches the state after every draft
+ * token in intermediate_states_buffer (recurrent_fused.py:5912-5925); writing the accepted one back is left
+ * to the serving framework there.  For every sequence n with accepted[n] > 0:
+ *   state[state_indices[n]] = fp32(inter[inter_indices[n], accepted[n] - 1])      (all heads, V x K)
+ * accepted[n] == 0 keeps the old state.  Slots outside their pools raise the device status word.      */
+typedef struct QlaStateCommitArgs {
+  int32_t num_seqs;        /* N                                                               */
+  int32_t num_v_heads;     /* Hv                                                              */
+  int32_t inter_dtype;     /* QLA_DT_F32 | QLA_DT_BF16                                        */
+  int32_t inter_steps;     /* second extent of inter                                          */
+  int64_t inter_slots;     /* first extent of inter                                           */
+  int64_t state_slots;     /* first extent of state                                           */
+  const void* inter;       /* [inter_slots, inter_steps, Hv, 128, 128]                        */
+  const int32_t* accepted; /* [N] number of accepted tokens, 0 .. inter_steps                 */
+  const int32_t* state_indices; /* [N] or NULL (identity)                                     */
+  const int32_t* inter_indices; /* [N] or NULL (identity)                                     */
+  float* state;            /* [state_slots, Hv, 128, 128] fp32, updated in place              */
+  int32_t* status;         /* device int32 status word or NULL                                */
+} QlaStateCommitArgs;
+
+QLA_API int qla_state_commit(const QlaStateCommitArgs* args, void* stream);
+
 enum { /* flags of QlaChunkFwdArgs / QlaChunkBwdArgs */
   QLA_CHUNK_TRANSPOSE_STATE = 1, /* states are [N,Hv,V,K] instead of [N,Hv,K,V]            */
   QLA_CHUNK_STATE_ONLY = 2,      /* skip q / o: only h, v_new and the final state           */

@@ -178,3 +178,42 @@ def test_python_api_errors_on_gpu(fq):
         fq.fused_sigmoid_gating_delta_rule_update(hv, ab[:, :2], hv, q, q, v, ab, st)
     with pytest.raises(ValueError, match="K=V=128"):
         fq.fused_sigmoid_gating_delta_rule_update(hv, ab, hv, q[..., :64], q[..., :64], v, ab, st)
+
+
+@pytest.mark.parametrize("scratch_dtype", [torch.float32, torch.bfloat16])
+def test_commit_verified_state(scratch_dtype):
+    """Verify (T=4, cached, pool untouched) followed by the commit of the accepted prefix equals running the
+    accepted tokens through the decode path: the pool ends up with the state after token num_accepted - 1."""
+    import flashqla_b200 as fq
+    from oracle import gdr_oracle as orc
+    N, T, Hk, Hv = 5, 4, 2, 4
+    gen = torch.Generator().manual_seed(61)
+    rn = lambda *s: torch.randn(*s, generator=gen)
+    q = orc.l2norm(rn(1, N * T, Hk, 128)).bfloat16().cuda()
+    k = orc.l2norm(rn(1, N * T, Hk, 128)).bfloat16().cuda()
+    v = rn(1, N * T, Hv, 128).bfloat16().cuda()
+    g = torch.nn.functional.logsigmoid(rn(1, N * T, Hv)).cuda()
+    beta = torch.sigmoid(rn(1, N * T, Hv)).cuda()
+    pool = (0.1 * rn(8, Hv, 128, 128)).cuda()
+    slots = torch.tensor([6, 0, 3, 7, 2], dtype=torch.int32, device="cuda")
+    inter = torch.zeros(N, T, Hv, 128, 128, dtype=scratch_dtype, device="cuda")
+    before = pool.clone()
+    fq.fused_sigmoid_gating_delta_rule_update(None, g, None, q, k, v, beta, pool, initial_state_indices=slots,
+                                              use_qk_l2norm_in_kernel=False, a_is_log_decay=True, b_is_beta=True,
+                                              assume_regular=True, disable_state_update=True,
+                                              intermediate_states_buffer=inter)
+    assert torch.equal(pool, before)
+    accepted = torch.tensor([4, 0, 1, 3, 2], dtype=torch.int32, device="cuda")
+    fq.commit_verified_state(pool, inter, accepted, initial_state_indices=slots)
+    fq.check_device_status()
+    for n in range(N):
+        s, a = int(slots[n]), int(accepted[n])
+        want = before[s] if a == 0 else inter[n, a - 1].float()
+        assert torch.equal(pool[s], want), f"sequence {n}"
+    untouched = [i for i in range(8) if i not in slots.tolist()]
+    assert torch.equal(pool[untouched], before[untouched])
+    # out-of-range slot: reported through the status word, nothing written
+    bad = torch.tensor([99, 0, 3, 7, 2], dtype=torch.int32, device="cuda")
+    fq.commit_verified_state(pool, inter, accepted, initial_state_indices=bad)
+    with pytest.raises(Exception):
+        fq.check_device_status()
