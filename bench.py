@@ -228,6 +228,20 @@ def run_prefill(args, rank, world, device, varlen=False):
     ms_e2e = timed(e2e_step, e2e_steps, 2, world, device)
     fq.check_device_status()
 
+    # ---- optional same-box bar: FLA's Triton kernels (the reference's own comparison baseline) on these inputs
+    same_box = None
+    if args.compare_fla:
+        try:
+            from fla.ops.gated_delta_rule import chunk_gated_delta_rule as fla_gdr
+            cu64 = None if cu_dev is None else cu_dev.long()
+            fla_step = lambda: fla_gdr(dev["q"], dev["k"], dev["v"], dev["g"], dev["beta"], scale=K ** -0.5,
+                                       initial_state=h0, output_final_state=True, cu_seqlens=cu64)
+            ms_fla = timed(fla_step, args.steps, args.warmup, world, device) / args.steps
+            same_box = {"impl": "fla %s (Triton)" % __import__("fla").__version__, "ms_per_step": ms_fla,
+                        "tokens_per_s": total_tokens / (ms_fla * 1e-3)}
+        except Exception as exc:
+            same_box = {"impl": "fla", "unavailable": f"{type(exc).__name__}: {str(exc)[:120]}"}
+
     pk = peaks()
     per_step = ms / args.steps
     value = total_tokens / (per_step * 1e-3)
@@ -260,6 +274,8 @@ def run_prefill(args, rank, world, device, varlen=False):
                      "tensor_achieved_tflops": achieved, "tensor_peak_tflops": pk["tf_burst"],
                      "tensor_frac": achieved / pk["tf_burst"]},
     }
+    if same_box is not None:
+        line["same_box"] = same_box
     return line
 
 
@@ -379,6 +395,8 @@ def main():
     ap.add_argument("--cpu-sample-tokens", type=int, default=32768)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--eager", action="store_true", help="time plain calls instead of CUDA-graph replays")
+    ap.add_argument("--compare-fla", action="store_true",
+                    help="also time FLA's Triton forward on the same inputs (adds a same_box entry)")
     args = ap.parse_args()
     rank, world, local = dist_env()
     args.warmup = max(args.warmup, 3)
