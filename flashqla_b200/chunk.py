@@ -310,7 +310,8 @@ class ChunkGatedDeltaRuleFunction(torch.autograd.Function):
     @torch.amp.custom_fwd(device_type="cuda")
     def forward(ctx, q, k, v, g, beta, scale, initial_state, output_final_state, cu_seqlens,
                 transpose_state_layout):
-        need_grad = any(t is not None and t.requires_grad for t in (q, k, v, g, beta, initial_state))
+        # h and v_new are only kept when a backward can follow (False for every input under torch.no_grad())
+        need_grad = any(ctx.needs_input_grad)
         out = chunk_gated_delta_rule_fwd(
             q, k, v, g, beta, scale=scale, initial_state=initial_state, cu_seqlens=cu_seqlens,
             output_final_state=output_final_state, output_h=need_grad, output_v_new=need_grad,

@@ -301,7 +301,15 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       const uint64_t d_vd = ptx::smem_desc_sw128(ptx::smem_u32(smem + kOffVd), 16, 1024);
       constexpr int kHalfWQ = (16384 >> 4) - 3 * 2;  // from k-step 3 to k-step 4 of the stacked tile
       constexpr int kHalfK = (8192 >> 4) - 3 * 2;
-      bool ok = true;
+      // The CTA owns all 512 columns, so the allocation starts at column 0 of lane 0: tensor-memory
+      // addresses are compile-time constants here (checked once; a value loaded from shared memory would
+      // have to be moved to a uniform register for every instruction).  Barrier addresses for the commits
+      // that the product blocks issue themselves.
+      constexpr uint32_t tmem0 = 0;
+      const uint32_t bar0 = ptx::smem_u32(&bars[0]);
+      auto bar_addr = [&](int b) { return bar0 + 8u * static_cast<uint32_t>(b); };
+      bool ok = tmem == tmem0;
+      if (!ok) ptx::record_wait_failure(status, kStatusBadTmemBase, 0);
 #pragma unroll 1
       for (int i = -1; ok && i <= nproc; ++i) {
         const int ph = i & 1, prev = (i - 1) & 1;
@@ -315,8 +323,8 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           if (!(ok = wait(kSbfReady, ph))) break;
           if (lane == 0) trace(0, i, 2);
           ptx::tc_fence_after_sync();
-          ptx::umma_ts_k128<2, kHalfWQ>(tmem + kColD2, tmem + kColSbf, d_wq + so, id_n64, kStateOnly ? !p.zero_v : true);
-          ptx::umma_commit(&bars[kD2Done]);
+          ptx::umma_ts_k128<2, kHalfWQ>(tmem0 + kColD2, tmem0 + kColSbf, d_wq + so, id_n64,
+                                        kStateOnly ? !p.zero_v : true, bar_addr(kD2Done));
           if (lane == 0) trace(0, i, 3);
         }
         // gap 1 (the chain computes V'): MMAq(i): Dq = S0^T_bf16 Q^T (Q rows sit 8 KiB into each half of the
@@ -329,15 +337,14 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             if (!(ok = wait(kQsStored, prev))) break;
           }
           if (cur) {
-            ptx::umma_ts_k128<2, kHalfWQ>(tmem + kColDq, tmem + kColSbf, d_wq + so + (8192 >> 4), id_n64, false);
-            ptx::umma_commit(&bars[kDqDone]);
+            ptx::umma_ts_k128<2, kHalfWQ>(tmem0 + kColDq, tmem0 + kColSbf, d_wq + so + (8192 >> 4), id_n64, false,
+                                          bar_addr(kDqDone));
           }
           if (i > 0) {
             if (!(ok = wait(kPgReady, prev))) break;
             ptx::tc_fence_after_sync();
-            ptx::umma_ss_k64<2, 2>(tmem + kColD4, d_vd + static_cast<uint64_t>(prev * (16384 >> 4)),
-                                   d_pg + static_cast<uint64_t>(prev * (8192 >> 4)), id_n64, true);
-            ptx::umma_commit(&bars[kD4Done]);
+            ptx::umma_ss_k64<2, 2>(tmem0 + kColD4, d_vd + static_cast<uint64_t>(prev * (16384 >> 4)),
+                                   d_pg + static_cast<uint64_t>(prev * (8192 >> 4)), id_n64, true, bar_addr(kD4Done));
           }
         }
         if (cur) {
@@ -347,9 +354,9 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           if (!(ok = wait(kSScaled, ph))) break;
           if (lane == 0) trace(0, i, 6);
           ptx::tc_fence_after_sync();
-          ptx::umma_ts_k64<128>(tmem + kColS, tmem + kColD2, d_kmn + so, id_mn128, true);
-          ptx::umma_commit(&bars[kSDone]);
-          ptx::umma_commit(&bars[kEmpty0 + (i & 1)]);  // every MMA that reads this stage has been issued and tracked
+          // (second commit: every MMA that reads this stage has been issued and tracked)
+          ptx::umma_ts_k64<128>(tmem0 + kColS, tmem0 + kColD2, d_kmn + so, id_mn128, true, bar_addr(kSDone),
+                                bar_addr(kEmpty0 + (i & 1)));
           if (lane == 0) trace(0, i, 7);
         }
         // gap 2 (both warpgroups convert the state): the state-independent products of the next chunk.
@@ -363,11 +370,10 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           if (!(ok = wait(kFull0 + sj, (j >> 1) & 1))) break;
           if (!(ok = wait(kAbReady0 + sj, (j >> 1) & 1))) break;
           ptx::tc_fence_after_sync();
-          if (!p.zero_v) ptx::umma_ss_k64<128, 2>(tmem + kColD2, d_v + sn, d_a + sn, id_u, false);
-          if (!kStateOnly) {
-            ptx::umma_ss_k128<2, kHalfWQ, 2, kHalfK>(tmem + kColD0 + sj * 64, d_wq + sn, d_k + sn, id_n64, false);
-            ptx::umma_commit(&bars[kPDone0 + sj]);  // one barrier per parity: the aux warps may lag a chunk
-          }
+          if (!p.zero_v) ptx::umma_ss_k64<128, 2>(tmem0 + kColD2, d_v + sn, d_a + sn, id_u, false);
+          if (!kStateOnly)  // (one PDone barrier per parity: the aux warps may lag a chunk)
+            ptx::umma_ss_k128<2, kHalfWQ, 2, kHalfK>(tmem0 + kColD0 + sj * 64, d_wq + sn, d_k + sn, id_n64, false,
+                                                     bar_addr(kPDone0 + sj));
         }
         if (cur && lane == 0) trace(0, i, 8);
       }

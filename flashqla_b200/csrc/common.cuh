@@ -19,6 +19,7 @@ enum DeviceStatus : int {
   kStatusOk = 0,
   kStatusBarrierTimeout = 1,  // a bounded mbarrier wait gave up
   kStatusBadIndex = 2,        // an index tensor pointed outside its buffer
+  kStatusBadTmemBase = 3,     // a full tensor-memory allocation did not start at column 0
 };
 
 void set_last_error(const char* fmt, ...);

@@ -324,32 +324,40 @@ __device__ __forceinline__ void mma_commit(uint64_t* bar) {
 // on the uniform datapath and the cost drops to the pipe's own (34 cycles at N = 64, 68 at N = 128).
 // Descriptor steps are 32-bit adds on the low word (the 14-bit address field never carries).
 // All steps are in units of 16 bytes.  `JUMP` replaces `STEP` between k-steps 3 and 4 (the second
-// 64-element half of a 128-wide operand).
+// 64-element half of a 128-wide operand).  Every block ends with up to two tcgen05.commit on the
+// barriers whose shared-memory addresses are passed in (0 = none), so that a product and its completion
+// signal cost one leader election.
+#define QLA_UMMA_COMMITS(B1, B2)                                                                      \
+  "setp.ne.b32 c1, " B1 ", 0;\nsetp.ne.b32 c2, " B2 ", 0;\nand.pred c1, c1, e;\nand.pred c2, c2, e;\n"   \
+  "@c1 tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [" B1 "];\n"              \
+  "@c2 tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [" B2 "];\n"
 #define QLA_UMMA_SS_STEP(SA, SB)                                                                     \
   "add.u32 alo, alo, " SA "; add.u32 blo, blo, " SB "; mov.b64 da, {alo, ahi}; mov.b64 db, {blo, bhi};\n" \
   "@e tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, t;\n"
 #define QLA_UMMA_SS_HEAD                                                                              \
-  "{\n.reg .pred p, t, e;\n.reg .b32 alo, ahi, blo, bhi;\n.reg .b64 da, db;\n"                         \
+  "{\n.reg .pred p, t, e, c1, c2;\n.reg .b32 alo, ahi, blo, bhi;\n.reg .b64 da, db;\n"                         \
   "elect.sync _|e, 0xffffffff;\nsetp.ne.b32 p, %4, 0;\nsetp.eq.b32 t, 0, 0;\n"                         \
   "mov.b64 {alo, ahi}, %1;\nmov.b64 {blo, bhi}, %2;\n"                                                 \
   "@e tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
 // D[tmem] (+)= A[smem] B[smem], K = 64 (four instructions).
 template <int A_STEP, int B_STEP>
 __device__ __forceinline__ void umma_ss_k64(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                            bool accumulate) {
-  asm volatile(QLA_UMMA_SS_HEAD QLA_UMMA_SS_STEP("%5", "%6") QLA_UMMA_SS_STEP("%5", "%6") QLA_UMMA_SS_STEP("%5", "%6") "}\n"
+                                            bool accumulate, uint32_t commit1 = 0, uint32_t commit2 = 0) {
+  asm volatile(QLA_UMMA_SS_HEAD QLA_UMMA_SS_STEP("%5", "%6") QLA_UMMA_SS_STEP("%5", "%6") QLA_UMMA_SS_STEP("%5", "%6")
+               QLA_UMMA_COMMITS("%7", "%8") "}\n"
                ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(static_cast<uint32_t>(accumulate)),
-                 "n"(A_STEP), "n"(B_STEP)
+                 "n"(A_STEP), "n"(B_STEP), "r"(commit1), "r"(commit2)
                : "memory");
 }
 // D[tmem] (+)= A[smem] B[smem], K = 128 (eight instructions).
 template <int A_STEP, int A_JUMP, int B_STEP, int B_JUMP>
 __device__ __forceinline__ void umma_ss_k128(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                             bool accumulate) {
+                                             bool accumulate, uint32_t commit1 = 0, uint32_t commit2 = 0) {
   asm volatile(QLA_UMMA_SS_HEAD QLA_UMMA_SS_STEP("%5", "%6") QLA_UMMA_SS_STEP("%5", "%6") QLA_UMMA_SS_STEP("%5", "%6")
-               QLA_UMMA_SS_STEP("%7", "%8") QLA_UMMA_SS_STEP("%5", "%6") QLA_UMMA_SS_STEP("%5", "%6") QLA_UMMA_SS_STEP("%5", "%6") "}\n"
+               QLA_UMMA_SS_STEP("%7", "%8") QLA_UMMA_SS_STEP("%5", "%6") QLA_UMMA_SS_STEP("%5", "%6") QLA_UMMA_SS_STEP("%5", "%6")
+               QLA_UMMA_COMMITS("%9", "%10") "}\n"
                ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(static_cast<uint32_t>(accumulate)),
-                 "n"(A_STEP), "n"(B_STEP), "n"(A_JUMP), "n"(B_JUMP)
+                 "n"(A_STEP), "n"(B_STEP), "n"(A_JUMP), "n"(B_JUMP), "r"(commit1), "r"(commit2)
                : "memory");
 }
 #undef QLA_UMMA_SS_STEP
@@ -358,30 +366,34 @@ __device__ __forceinline__ void umma_ss_k128(uint32_t d_tmem, uint64_t a_desc, u
   "add.u32 aa, aa, 8; add.u32 blo, blo, " SB "; mov.b64 db, {blo, bhi};\n"                             \
   "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [aa], db, %3, t;\n"
 #define QLA_UMMA_TS_HEAD                                                                              \
-  "{\n.reg .pred p, t, e;\n.reg .b32 aa, blo, bhi;\n.reg .b64 db;\n"                                   \
+  "{\n.reg .pred p, t, e, c1, c2;\n.reg .b32 aa, blo, bhi;\n.reg .b64 db;\n"                                   \
   "elect.sync _|e, 0xffffffff;\nsetp.ne.b32 p, %4, 0;\nsetp.eq.b32 t, 0, 0;\n"                         \
   "mov.b32 aa, %1;\nmov.b64 {blo, bhi}, %2;\n"                                                         \
   "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n"
 // D[tmem] (+)= A[tmem] B[smem], K = 64: A advances 8 TMEM columns (16 values of 16 bits) per instruction.
 template <int B_STEP>
 __device__ __forceinline__ void umma_ts_k64(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
-                                            bool accumulate) {
-  asm volatile(QLA_UMMA_TS_HEAD QLA_UMMA_TS_STEP("%5") QLA_UMMA_TS_STEP("%5") QLA_UMMA_TS_STEP("%5") "}\n"
-               ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(static_cast<uint32_t>(accumulate)), "n"(B_STEP)
+                                            bool accumulate, uint32_t commit1 = 0, uint32_t commit2 = 0) {
+  asm volatile(QLA_UMMA_TS_HEAD QLA_UMMA_TS_STEP("%5") QLA_UMMA_TS_STEP("%5") QLA_UMMA_TS_STEP("%5")
+               QLA_UMMA_COMMITS("%6", "%7") "}\n"
+               ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(static_cast<uint32_t>(accumulate)), "n"(B_STEP),
+                 "r"(commit1), "r"(commit2)
                : "memory");
 }
 // D[tmem] (+)= A[tmem] B[smem], K = 128.
 template <int B_STEP, int B_JUMP>
 __device__ __forceinline__ void umma_ts_k128(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
-                                             bool accumulate) {
+                                             bool accumulate, uint32_t commit1 = 0, uint32_t commit2 = 0) {
   asm volatile(QLA_UMMA_TS_HEAD QLA_UMMA_TS_STEP("%5") QLA_UMMA_TS_STEP("%5") QLA_UMMA_TS_STEP("%5") QLA_UMMA_TS_STEP("%6")
-               QLA_UMMA_TS_STEP("%5") QLA_UMMA_TS_STEP("%5") QLA_UMMA_TS_STEP("%5") "}\n"
+               QLA_UMMA_TS_STEP("%5") QLA_UMMA_TS_STEP("%5") QLA_UMMA_TS_STEP("%5")
+               QLA_UMMA_COMMITS("%7", "%8") "}\n"
                ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(static_cast<uint32_t>(accumulate)), "n"(B_STEP),
-                 "n"(B_JUMP)
+                 "n"(B_JUMP), "r"(commit1), "r"(commit2)
                : "memory");
 }
 #undef QLA_UMMA_TS_STEP
 #undef QLA_UMMA_TS_HEAD
+#undef QLA_UMMA_COMMITS
 // tcgen05.commit from a converged warp (same elected lane as the umma_* helpers).
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile(

@@ -44,7 +44,8 @@ def check_device_status(device=None) -> None:
         code = int(st.item())
         if code != 0:
             st.zero_()
-            names = {1: "a bounded barrier wait timed out", 2: "an index was out of range"}
+            names = {1: "a bounded barrier wait timed out", 2: "an index was out of range",
+                     3: "tensor memory was not allocated at column 0"}
             # low byte: what happened; the rest says where (barrier index << 8 | parity << 16 | warp << 20)
             raise QlaError(f"device {idx} reported status {code & 0xFF} (detail {code >> 8:#x}): "
                            f"{names.get(code & 0xFF, 'unknown')}")

@@ -58,7 +58,9 @@ def recurrent_cases(ref_root: Path):
 
 
 def main():
-    ref_root = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        sys.exit("usage: make_golden.py <path of the reference checkout>")
+    ref_root = Path(sys.argv[1])
     sys.path[:0] = [str(ref_root), str(ref_root / "tests")]
     import ref_gdr as ref
 
