@@ -13,8 +13,8 @@
 //   Wt = A diag(beta gamma) K      (the "w" of tests/ref_gdr.py:107-147, stored negated)
 // that lets the scan kernel form Vd = A diag(beta) V - Wt S0 with a single state-dependent product:
 // one more tcgen05.mma per chunk (the [128][64] tile of -A diag(beta gamma) rows times that chunk's K rows read
-// MN-major) leaves row t of Wt in TMEM lane t, which thread t writes to global memory as one contiguous
-// 256-byte row.  The inverse of the unit-lower-triangular I + L is
+// MN-major) leaves row t of Wt in TMEM lane t; the rows leave through a swizzled staging tile and TMA stores
+// (row by row for a ragged tail).  The inverse of the unit-lower-triangular I + L is
 // blocked: the four 16 x 16 diagonal blocks by fp32 forward substitution (one thread per column), then
 // X21 = -X22 (L21 X11) at block size 16 and again at block size 32 with mma.sync m16n8k8 products on
 // fp32 shared-memory tiles, each operand split into two TF32 parts (3xTF32) so that the inverse keeps
@@ -44,7 +44,8 @@ __device__ __forceinline__ void mma_tf32(float (&c)[4], const uint32_t (&a)[4], 
 }
 // One warp: C[16 x 8*NT] = A[16 x K] * B[K x 8*NT] on fp32 shared-memory tiles (row-major, strides in
 // floats).  A points at the first of the 16 rows, B at row 0 / first column of the K x N block.
-template <int NT>
+// kLowerB: B is lower triangular (B[k][n] = 0 for n > k), so column tile nt starts at k0 = 8 nt.
+template <int NT, bool kLowerB = false>
 __device__ __forceinline__ void warp_gemm_tf32(float (&acc)[NT][4], const float* A, int lda, const float* B,
                                                int ldb, int K) {
   const int lane = threadIdx.x & 31, g = lane >> 2, c = lane & 3;
@@ -66,6 +67,7 @@ __device__ __forceinline__ void warp_gemm_tf32(float (&acc)[NT][4], const float*
     }
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
+      if (kLowerB && nt * 8 > k0) continue;
       const float bf0 = B[(k0 + c) * ldb + nt * 8 + g], bf1 = B[(k0 + c + 4) * ldb + nt * 8 + g];
       const uint32_t bh0 = to_tf32(bf0), bh1 = to_tf32(bf1);
       const uint32_t bl0 = to_tf32(bf0 - __uint_as_float(bh0)), bl1 = to_tf32(bf1 - __uint_as_float(bh1));
@@ -105,6 +107,7 @@ template <typename T>
 __global__ void __launch_bounds__(128) kkt_solve_kernel(const __grid_constant__ CUtensorMap tm_k,
                                                         const __grid_constant__ CUtensorMap tm_q,
                                                         const __grid_constant__ CUtensorMap tm_a,
+                                                        const __grid_constant__ CUtensorMap tm_w,
                                                         const KktParams p) {
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int hk = blockIdx.y;
@@ -138,6 +141,7 @@ __global__ void __launch_bounds__(128) kkt_solve_kernel(const __grid_constant__ 
   float* sL = reinterpret_cast<float*>(sK + 32768 + 2 * 64 * kXStride * sizeof(float));  // [2][64][kLStride]
   uint8_t* sAw = reinterpret_cast<uint8_t*>(sL);     // 16 KiB [128 tokens][64] tile -A diag(beta gamma) (SW128), overlays L once solved
   uint8_t* sAst = sAw + 16384;                       // 16 KiB [128 tokens][64] staging tile of A for the TMA store (SW128)
+  uint8_t* sW = sAw;                                 // 32 KiB staging tile of w (two [128][64] halves, SW128), once both are consumed
   float* sT = sL + 2 * 64 * kLStride;                // [2][32][kTStride] products L21 X11
   __shared__ __align__(16) float s_bg[128];          // -beta * gamma per token
   __shared__ __align__(16) float s_g[128];
@@ -257,8 +261,17 @@ __global__ void __launch_bounds__(128) kkt_solve_kernel(const __grid_constant__ 
 
   float* Lc = sL + ci * 64 * kLStride;
   T* Ab = static_cast<T*>(p.A);
+  // The inverse only ever writes the lower block triangle of the X tiles (diagonal blocks in full), so the
+  // zeros above it are written once per CTA, not once per head.  The first barrier of the head loop orders
+  // them before any other thread's writes.
+  if (ok && p.A_in == nullptr) {
+    float* xrow = sX + tid * kXStride;
+#pragma unroll 1
+    for (int j4 = 0; j4 < kXStride; j4 += 4) *reinterpret_cast<float4*>(xrow + j4) = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
 
   int mma_uses = 0;  // completed phases of bar_mma after the first (K K^T)
+  bool w_store_pending = false;
   for (int hv = hk * group; ok && hv < (hk + 1) * group; ++hv) {
     const float gv = gv_n, bv = bv_n, gin = gin_n;
     fetch_gates(hv + 1);
@@ -277,14 +290,18 @@ __global__ void __launch_bounds__(128) kkt_solve_kernel(const __grid_constant__ 
     const float gc2 = gcs * 1.4426950408889634f;  // exponents are formed in the log2 domain: one FADD + ex2 each
     s_g[tid] = gc2;
     s_bg[tid] = -bv * ptx::ex2(gc2) * rk_c;
+    // the previous head's w tile lies where L is built next: its store must have read it by now
+    if (tid == 0 && w_store_pending) ptx::tma_store_wait_read();
     __syncthreads();
 
     // L[c][d] = beta_c * exp(g_c - g_d) * (k_c . k_d) for d < c
     const float* gch = s_g + ci * 64;
     // branch-free (the causal mask is a select, so an overflowing exponent above the diagonal is harmless):
     // a data-dependent branch per entry would diverge
+    // Only the lower block triangle of L is ever read, so the warp that owns rows 0..31 stops at column 32.
 #pragma unroll
     for (int d4 = 0; d4 < 64; d4 += 4) {
+      if (d4 >= 32 && (warp & 1) == 0) break;
       const float4 g4 = *reinterpret_cast<const float4*>(gch + d4);
       float4 l;
       l.x = bv * ptx::ex2(gc2 - g4.x) * kk[d4 + 0];
@@ -316,10 +333,7 @@ __global__ void __launch_bounds__(128) kkt_solve_kernel(const __grid_constant__ 
     float* Tc = sT + ci * 32 * kTStride;
     const int wl = warp & 1;  // warp within the chunk
     {
-      // zero the tile, then the four 16 x 16 diagonal blocks: thread = (block, column)
-#pragma unroll 1
-      for (int j4 = 0; j4 < kXStride; j4 += 4) *reinterpret_cast<float4*>(Xc + c * kXStride + j4) = make_float4(0.f, 0.f, 0.f, 0.f);
-      pair_sync(ci);
+      // the four 16 x 16 diagonal blocks: thread = (block, column)
       const int b0 = (c >> 4) * 16, cc = c & 15;
       float x[16];
 #pragma unroll
@@ -337,7 +351,7 @@ __global__ void __launch_bounds__(128) kkt_solve_kernel(const __grid_constant__ 
       // block size 16: X[R, C] = -X[R, R] (L[R, C] X[C, C]) for (R, C) = (16, 0) and (48, 32); one per warp
       const int C0 = 32 * wl, R0 = C0 + 16;
       float acc[2][4];
-      warp_gemm_tf32<2>(acc, Lc + R0 * kLStride + C0, kLStride, Xc + C0 * kXStride + C0, kXStride, 16);
+      warp_gemm_tf32<2, true>(acc, Lc + R0 * kLStride + C0, kLStride, Xc + C0 * kXStride + C0, kXStride, 16);
       float* Tw = Tc + wl * 16 * kTStride;
       store_tile<2>(Tw, kTStride, acc, 1.f);
       __syncwarp();
@@ -349,10 +363,12 @@ __global__ void __launch_bounds__(128) kkt_solve_kernel(const __grid_constant__ 
       // block size 32: X[32:64, 0:32] = -X[32:64, 32:64] (L[32:64, 0:32] X[0:32, 0:32]); 16 rows per warp
       const int R0 = 32 + 16 * wl;
       float acc[4][4];
-      warp_gemm_tf32<4>(acc, Lc + R0 * kLStride, kLStride, Xc, kXStride, 32);
+      // X[0:32, 0:32] is lower triangular: column tile nt has nothing above row 8 nt.  X[32:64, 32:64] is too:
+      // its rows 0..15 (warp 0) end at column 15.
+      warp_gemm_tf32<4, true>(acc, Lc + R0 * kLStride, kLStride, Xc, kXStride, 32);
       store_tile<4>(Tc + wl * 16 * kTStride, kTStride, acc, 1.f);
       pair_sync(ci);
-      warp_gemm_tf32<4>(acc, Xc + R0 * kXStride + 32, kXStride, Tc, kTStride, 32);
+      warp_gemm_tf32<4>(acc, Xc + R0 * kXStride + 32, kXStride, Tc, kTStride, 16 * (wl + 1));
       store_tile<4>(Xc + R0 * kXStride, kXStride, acc, -1.f);
     }
     pair_sync(ci);
@@ -361,7 +377,7 @@ __global__ void __launch_bounds__(128) kkt_solve_kernel(const __grid_constant__ 
     // chunk; one tcgen05.mma per chunk multiplies the WHOLE tile with that chunk's 64 K rows (read MN-major),
     // so rows 0..63 of the first product and rows 64..127 of the second are the wanted ones and no zero
     // padding is needed.  The same pass writes A itself (16-bit) into a staging tile for one TMA store.
-    // The upper triangle of X is exactly zero (zero-filled tile, forward substitution yields exact zeros),
+    // The upper triangle of X is exactly zero (zeroed once per CTA and never written; forward substitution yields exact zeros inside the diagonal blocks),
     // and rows / columns of tokens past the sequence end carry beta = 0, so no mask is applied here.
     __syncthreads();
     const bool full_pair = tok0 + 128 <= seq_end;
@@ -369,7 +385,7 @@ __global__ void __launch_bounds__(128) kkt_solve_kernel(const __grid_constant__ 
       const float* xr = Xc + c * kXStride;
       const float* bg = s_bg + ci * 64;
       T* arow = Ab + (tok * p.num_v_heads + hv) * 64;
-#pragma unroll 1
+#pragma unroll 2
       for (int c16 = 0; c16 < 8; ++c16) {
         const float4 x0 = *reinterpret_cast<const float4*>(xr + c16 * 8);
         const float4 x1 = *reinterpret_cast<const float4*>(xr + c16 * 8 + 4);
@@ -402,13 +418,18 @@ __global__ void __launch_bounds__(128) kkt_solve_kernel(const __grid_constant__ 
       ptx::umma_ss_k64<2, 128>(tmem, da, db, idesc, false);                       // chunk 0: K rows 0..63
       ptx::umma_ss_k64<2, 128>(tmem + 128, da, db + (8192 >> 4), idesc, false);   // chunk 1: K rows 64..127
       ptx::umma_commit(&bar_mma);
+      // the w rows are staged where the A tile sits: its store has to have read it before anybody passes
+      // the barrier below
+      if (lane == 0) ptx::tma_store_wait_read();
+      __syncwarp();
     }
     ++mma_uses;
     const bool ok2 = __syncthreads_and(ptx::mbar_wait(&bar_mma, mma_uses & 1, p.status, kStatusBarrierTimeout)) != 0;
     ptx::tc_fence_after_sync();
     if (ok2) {
-      // row `tid` of w: 128 values -> one contiguous 256-byte row.  tcgen05.ld is warp-collective:
-      // every lane runs the loop, only lanes with a valid token store.
+      // Row `tid` of w: 128 values.  A full pair goes through a swizzled staging tile and two TMA stores
+      // (whole 128-byte lines per token row); a ragged tail is written row by row, only by lanes with a valid
+      // token.  tcgen05.ld is warp-collective: every lane runs the loop.
       T* wrow = static_cast<T*>(p.w) + (tok * p.num_v_heads + hv) * kHeadDim;
       const uint32_t taddr = tmem + (static_cast<uint32_t>(warp * 32) << 16) + ci * 128;
 #pragma unroll 1
@@ -416,21 +437,29 @@ __global__ void __launch_bounds__(128) kkt_solve_kernel(const __grid_constant__ 
         uint32_t r[32];
         ptx::tmem_ld32(taddr + kb, r);
         ptx::tmem_wait_ld();
-        if (valid) {
+        uint8_t* half = sW + (kb >> 6) * 16384;
 #pragma unroll
-          for (int e = 0; e < 32; e += 8)
-            *reinterpret_cast<uint4*>(wrow + kb + e) =
-                make_uint4(pack2<T>(__uint_as_float(r[e]), __uint_as_float(r[e + 1])),
-                           pack2<T>(__uint_as_float(r[e + 2]), __uint_as_float(r[e + 3])),
-                           pack2<T>(__uint_as_float(r[e + 4]), __uint_as_float(r[e + 5])),
-                           pack2<T>(__uint_as_float(r[e + 6]), __uint_as_float(r[e + 7])));
+        for (int e = 0; e < 32; e += 8) {
+          const uint4 val = make_uint4(pack2<T>(__uint_as_float(r[e]), __uint_as_float(r[e + 1])),
+                                       pack2<T>(__uint_as_float(r[e + 2]), __uint_as_float(r[e + 3])),
+                                       pack2<T>(__uint_as_float(r[e + 4]), __uint_as_float(r[e + 5])),
+                                       pack2<T>(__uint_as_float(r[e + 6]), __uint_as_float(r[e + 7])));
+          if (full_pair) *reinterpret_cast<uint4*>(half + ptx::sw128_offset(tid, ((kb & 63) + e) >> 3)) = val;
+          else if (valid) *reinterpret_cast<uint4*>(wrow + kb + e) = val;
         }
       }
     }
-    if (tid == 0) ptx::tma_store_wait_read();  // the staging tile is overwritten by the next head's L
+    ptx::fence_proxy_async_smem();
     ptx::tc_fence_before_sync();
-    __syncthreads();  // s_g / sL are rewritten for the next head
+    __syncthreads();  // s_g / s_bg are rewritten for the next head; the w tile is complete
+    if (tid == 0 && ok2 && full_pair) {
+      ptx::tma_store_3d(&tm_w, sW, 0, hv, tok0);
+      ptx::tma_store_3d(&tm_w, sW + 16384, 64, hv, tok0);
+      ptx::tma_store_commit();
+    }
+    w_store_pending = true;
   }
+  if (tid == 0) ptx::tma_store_wait_read();  // shared memory stays allocated until the last store has read it
 
   ptx::tc_fence_before_sync();
   __syncthreads();
@@ -464,7 +493,7 @@ int launch_chunk_tables(const int32_t* cu, int n, int32_t* pair_offsets, int32_t
 
 int launch_kkt_solve(const KktParams& p, const void* k, const void* q, int64_t total_tokens, int pairs_upper,
                      bool is_bf16, cudaStream_t stream) {
-  CUtensorMap tm_k, tm_q, tm_a;
+  CUtensorMap tm_k, tm_q, tm_a, tm_w;
   int rc = make_tmap_3d(&tm_k, k, total_tokens, p.num_k_heads, kHeadDim, 128, 64, true, is_bf16);
   if (rc != QLA_OK) return rc;
   // q is only read for the in-kernel L2 norm (p.rnorm set); otherwise the map is made over k and unused
@@ -473,16 +502,19 @@ int launch_kkt_solve(const KktParams& p, const void* k, const void* q, int64_t t
   // A leaves through a [128 tokens][64] staging tile; in rebuild mode (A given) the map is made but unused
   rc = make_tmap_3d(&tm_a, p.A, total_tokens, p.num_v_heads, 64, 128, 64, true, is_bf16);
   if (rc != QLA_OK) return rc;
+  // w leaves through two [128 tokens][64] staging tiles per (pair, head)
+  rc = make_tmap_3d(&tm_w, p.w, total_tokens, p.num_v_heads, kHeadDim, 128, 64, true, is_bf16);
+  if (rc != QLA_OK) return rc;
   // K tile 32 KiB + X tiles + L tiles (later the Aw tile) + T
   const size_t smem = 1024 + 32768 + 2 * 64 * kXStride * sizeof(float) + 2 * 64 * kLStride * sizeof(float) +
                       2 * 32 * kTStride * sizeof(float);
   dim3 grid(pairs_upper, p.num_k_heads);
   if (is_bf16) {
     if ((rc = ensure_dynamic_smem<kkt_solve_kernel<__nv_bfloat16>>(smem)) != QLA_OK) return rc;
-    kkt_solve_kernel<__nv_bfloat16><<<grid, 128, smem, stream>>>(tm_k, tm_q, tm_a, p);
+    kkt_solve_kernel<__nv_bfloat16><<<grid, 128, smem, stream>>>(tm_k, tm_q, tm_a, tm_w, p);
   } else {
     if ((rc = ensure_dynamic_smem<kkt_solve_kernel<__half>>(smem)) != QLA_OK) return rc;
-    kkt_solve_kernel<__half><<<grid, 128, smem, stream>>>(tm_k, tm_q, tm_a, p);
+    kkt_solve_kernel<__half><<<grid, 128, smem, stream>>>(tm_k, tm_q, tm_a, tm_w, p);
   }
   QLA_CHECK_CUDA(cudaGetLastError());
   return QLA_OK;
