@@ -17,8 +17,8 @@
 // (row by row for a ragged tail).  The inverse of the unit-lower-triangular I + L is
 // blocked: the four 16 x 16 diagonal blocks by fp32 forward substitution (one thread per column), then
 // X21 = -X22 (L21 X11) at block size 16 and again at block size 32 with mma.sync m16n8k8 products on
-// fp32 shared-memory tiles, each operand split into two TF32 parts (3xTF32) so that the inverse keeps
-// fp32-level accuracy before it is rounded to the 16-bit output.
+// fp32 shared-memory tiles; at block size 16 each operand is split into two TF32 parts (3xTF32), at block
+// size 32 the products are plain TF32 (see kSplit32).
 #include "chunk_params.cuh"
 
 namespace qla {
@@ -28,6 +28,12 @@ namespace {
 
 constexpr int kLStride = 68;  // floats per L row: 16-byte aligned rows, conflict-free float4 stores
 constexpr int kXStride = 68;  // two 64 x 68 fp32 X tiles = 34 816 B, so the L area after them stays 1 KiB aligned
+// Product precision of the blocked inverse.  Block size 16 keeps 3xTF32; block size 32 uses single TF32
+// products like the reference's fp32-tile gemm there (chunk/hopper/kkt_solve.py:181-183): against an fp64
+// inverse the error of that block is 1.70e-3 relative rms instead of 1.68e-3 (the 16-bit rounding of A
+// dominates both), and o / final state do not move in the fourth digit.
+constexpr bool kSplit32 = false;
+constexpr bool kSplit16 = true;
 constexpr int kTStride = 40;  // 32 columns + 8: conflict-free fragment loads
 
 __device__ __forceinline__ uint32_t to_tf32(float x) {
@@ -45,7 +51,8 @@ __device__ __forceinline__ void mma_tf32(float (&c)[4], const uint32_t (&a)[4], 
 // One warp: C[16 x 8*NT] = A[16 x K] * B[K x 8*NT] on fp32 shared-memory tiles (row-major, strides in
 // floats).  A points at the first of the 16 rows, B at row 0 / first column of the K x N block.
 // kLowerB: B is lower triangular (B[k][n] = 0 for n > k), so column tile nt starts at k0 = 8 nt.
-template <int NT, bool kLowerB = false>
+// kSplit: 3xTF32 (fp32-level products); otherwise one TF32 product per term.
+template <int NT, bool kLowerB = false, bool kSplit = true>
 __device__ __forceinline__ void warp_gemm_tf32(float (&acc)[NT][4], const float* A, int lda, const float* B,
                                                int ldb, int K) {
   const int lane = threadIdx.x & 31, g = lane >> 2, c = lane & 3;
@@ -63,16 +70,18 @@ __device__ __forceinline__ void warp_gemm_tf32(float (&acc)[NT][4], const float*
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
       ah[e] = to_tf32(af[e]);
-      al[e] = to_tf32(af[e] - __uint_as_float(ah[e]));
+      if (kSplit) al[e] = to_tf32(af[e] - __uint_as_float(ah[e]));
     }
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
       if (kLowerB && nt * 8 > k0) continue;
       const float bf0 = B[(k0 + c) * ldb + nt * 8 + g], bf1 = B[(k0 + c + 4) * ldb + nt * 8 + g];
       const uint32_t bh0 = to_tf32(bf0), bh1 = to_tf32(bf1);
-      const uint32_t bl0 = to_tf32(bf0 - __uint_as_float(bh0)), bl1 = to_tf32(bf1 - __uint_as_float(bh1));
-      mma_tf32(acc[nt], al, bh0, bh1);
-      mma_tf32(acc[nt], ah, bl0, bl1);
+      if (kSplit) {
+        const uint32_t bl0 = to_tf32(bf0 - __uint_as_float(bh0)), bl1 = to_tf32(bf1 - __uint_as_float(bh1));
+        mma_tf32(acc[nt], al, bh0, bh1);
+        mma_tf32(acc[nt], ah, bl0, bl1);
+      }
       mma_tf32(acc[nt], ah, bh0, bh1);
     }
   }
@@ -351,11 +360,11 @@ __global__ void __launch_bounds__(128) kkt_solve_kernel(const __grid_constant__ 
       // block size 16: X[R, C] = -X[R, R] (L[R, C] X[C, C]) for (R, C) = (16, 0) and (48, 32); one per warp
       const int C0 = 32 * wl, R0 = C0 + 16;
       float acc[2][4];
-      warp_gemm_tf32<2, true>(acc, Lc + R0 * kLStride + C0, kLStride, Xc + C0 * kXStride + C0, kXStride, 16);
+      warp_gemm_tf32<2, true, kSplit16>(acc, Lc + R0 * kLStride + C0, kLStride, Xc + C0 * kXStride + C0, kXStride, 16);
       float* Tw = Tc + wl * 16 * kTStride;
       store_tile<2>(Tw, kTStride, acc, 1.f);
       __syncwarp();
-      warp_gemm_tf32<2>(acc, Xc + R0 * kXStride + R0, kXStride, Tw, kTStride, 16);
+      warp_gemm_tf32<2, false, kSplit16>(acc, Xc + R0 * kXStride + R0, kXStride, Tw, kTStride, 16);
       store_tile<2>(Xc + R0 * kXStride + C0, kXStride, acc, -1.f);
     }
     pair_sync(ci);
@@ -365,10 +374,10 @@ __global__ void __launch_bounds__(128) kkt_solve_kernel(const __grid_constant__ 
       float acc[4][4];
       // X[0:32, 0:32] is lower triangular: column tile nt has nothing above row 8 nt.  X[32:64, 32:64] is too:
       // its rows 0..15 (warp 0) end at column 15.
-      warp_gemm_tf32<4, true>(acc, Lc + R0 * kLStride, kLStride, Xc, kXStride, 32);
+      warp_gemm_tf32<4, true, kSplit32>(acc, Lc + R0 * kLStride, kLStride, Xc, kXStride, 32);
       store_tile<4>(Tc + wl * 16 * kTStride, kTStride, acc, 1.f);
       pair_sync(ci);
-      warp_gemm_tf32<4>(acc, Xc + R0 * kXStride + 32, kXStride, Tc, kTStride, 16 * (wl + 1));
+      warp_gemm_tf32<4, false, kSplit32>(acc, Xc + R0 * kXStride + 32, kXStride, Tc, kTStride, 16 * (wl + 1));
       store_tile<4>(Xc + R0 * kXStride, kXStride, acc, -1.f);
     }
     pair_sync(ci);
