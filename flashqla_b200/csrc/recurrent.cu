@@ -12,6 +12,7 @@
 // rows in registers for the whole call (R*16 floats); the K-reductions (S.k and S.q) are three
 // xor-shuffles over the eight lanes of a row.  A CTA of 128 threads covers 16*R rows.
 #include "common.cuh"
+#include "mma_sync.cuh"
 
 namespace qla {
 namespace {
@@ -60,18 +61,71 @@ __device__ __forceinline__ float group8_sum(float x) {
   return x;
 }
 
+#ifndef QLA_REC_STAGES
+#define QLA_REC_STAGES 2
+#endif
+constexpr int kRecStages = QLA_REC_STAGES;  // state tiles staged per CTA: the current one and kRecStages - 1 ahead
+
 template <typename T, typename InterT, int R>
-__global__ void __launch_bounds__(128) recurrent_kernel(const QlaRecurrentArgs p) {
+__global__ void __launch_bounds__(128) recurrent_kernel(const QlaRecurrentArgs p, const int64_t total_items) {
   constexpr int D = kHeadDim;
   constexpr int BV = 16 * R;
   constexpr int kTiles = D / BV;
-  const int tile = blockIdx.x % kTiles;
-  const int nh = blockIdx.x / kTiles;
-  const int h = nh % p.num_v_heads;
-  const int n = nh / p.num_v_heads;
-  const int hk = h / (p.num_v_heads / p.num_k_heads);
+  // [kRecStages][R * 4 pieces][128 threads] float4: every thread stages exactly the 16-byte pieces it owns, so
+  // no barrier is needed between the copy and its use
+  extern __shared__ __align__(16) float4 s_stage[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int sub = lane & 7, grp = lane >> 3;
+  const int col0 = sub * 4;  // first owned column of j = 0; j-th is col0 + 32 j
+
+  auto pool_slot = [&](int n) -> int64_t {
+    int64_t sidx = p.state_indices ? p.state_indices[n] : n;
+    return sidx >= p.state_slots ? -1 : sidx;  // never touch memory outside the pool
+  };
+  // The state tile of an item is requested one item ahead (cp.async, L2 only): the copy of the next tile is
+  // in flight while this one is computed and written back, which keeps reads queued at the memory the whole
+  // time instead of only at the start of every CTA.
+  auto prefetch = [&](int64_t item, int stage) {
+    const int tile = static_cast<int>(item % kTiles);
+    const int64_t nh = item / kTiles;
+    const int h = static_cast<int>(nh % p.num_v_heads), n = static_cast<int>(nh / p.num_v_heads);
+    const int64_t sidx = pool_slot(n);
+    if (sidx < 0) return;
+    const int row0 = tile * BV + warp * 4 + grp;
+    const float* sp = static_cast<const float*>(p.state) + ((sidx * p.num_v_heads + h) * D + row0) * D + col0;
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        mm::cp_async16(&s_stage[(stage * R * 4 + r * 4 + j) * 128 + threadIdx.x], sp + (r * 16) * D + j * 32, true);
+  };
+
+  const T* qb = static_cast<const T*>(p.q);
+  const T* kb = static_cast<const T*>(p.k);
+  const T* vb = static_cast<const T*>(p.v);
+  T* ob = static_cast<T*>(p.o);
+  InterT* ib = static_cast<InterT*>(p.inter);
+  const bool l2norm = (p.flags & QLA_REC_QK_L2NORM) != 0;
+
+  int64_t item = blockIdx.x;
+#pragma unroll
+  for (int a = 0; a < kRecStages - 1; ++a) {
+    if (item + a * static_cast<int64_t>(gridDim.x) < total_items) prefetch(item + a * static_cast<int64_t>(gridDim.x), a);
+    mm::cp_async_commit();
+  }
+  for (int it = 0; item < total_items; item += gridDim.x, ++it) {
+  {
+    const int64_t ahead = item + (kRecStages - 1) * static_cast<int64_t>(gridDim.x);
+    if (ahead < total_items) prefetch(ahead, (it + kRecStages - 1) % kRecStages);
+    mm::cp_async_commit();
+  }
+  mm::cp_async_wait<kRecStages - 1>();  // all but the newest kRecStages - 1 groups: this item's tile has landed
+
+  const int tile = static_cast<int>(item % kTiles);
+  const int64_t nh = item / kTiles;
+  const int h = static_cast<int>(nh % p.num_v_heads);
+  const int n = static_cast<int>(nh / p.num_v_heads);
+  const int hk = h / (p.num_v_heads / p.num_k_heads);
 
   int t0, len;
   if (p.tokens_per_seq > 0) {
@@ -81,8 +135,7 @@ __global__ void __launch_bounds__(128) recurrent_kernel(const QlaRecurrentArgs p
     t0 = p.cu_seqlens[n];
     len = p.cu_seqlens[n + 1] - t0;
   }
-  int64_t sidx = p.state_indices ? p.state_indices[n] : n;
-  if (sidx >= p.state_slots) sidx = -1;  // never touch memory outside the pool
+  const int64_t sidx = pool_slot(n);
   int64_t cidx = -1;
   if (p.inter != nullptr) {
     cidx = p.inter_indices ? p.inter_indices[n] : n;
@@ -90,15 +143,16 @@ __global__ void __launch_bounds__(128) recurrent_kernel(const QlaRecurrentArgs p
   }
 
   const int row0 = tile * BV + warp * 4 + grp;  // row of r = 0; r-th row is row0 + 16 r
-  const int col0 = sub * 4;                     // first owned column of j = 0; j-th is col0 + 32 j
 
   float S[R][4][4];
   if (sidx >= 0) {
-    const float* sp = static_cast<const float*>(p.state) + ((sidx * p.num_v_heads + h) * D + row0) * D + col0;
 #pragma unroll
     for (int r = 0; r < R; ++r)
 #pragma unroll
-      for (int j = 0; j < 4; ++j) load4<float>(sp + (r * 16) * D + j * 32, S[r][j]);
+      for (int j = 0; j < 4; ++j) {
+        const float4 x = s_stage[((it % kRecStages) * R * 4 + r * 4 + j) * 128 + threadIdx.x];
+        S[r][j][0] = x.x; S[r][j][1] = x.y; S[r][j][2] = x.z; S[r][j][3] = x.w;
+      }
   } else {
 #pragma unroll
     for (int r = 0; r < R; ++r)
@@ -108,12 +162,6 @@ __global__ void __launch_bounds__(128) recurrent_kernel(const QlaRecurrentArgs p
         for (int i = 0; i < 4; ++i) S[r][j][i] = 0.f;
   }
 
-  const T* qb = static_cast<const T*>(p.q);
-  const T* kb = static_cast<const T*>(p.k);
-  const T* vb = static_cast<const T*>(p.v);
-  T* ob = static_cast<T*>(p.o);
-  InterT* ib = static_cast<InterT*>(p.inter);
-  const bool l2norm = (p.flags & QLA_REC_QK_L2NORM) != 0;
   float a_coef = 0.f, dt_b = 0.f;
   if (!(p.flags & QLA_REC_A_IS_LOG_DECAY)) {
     a_coef = -expf(load_scalar(p.A_log, p.a_log_dtype, h));
@@ -241,18 +289,47 @@ __global__ void __launch_bounds__(128) recurrent_kernel(const QlaRecurrentArgs p
 #pragma unroll
       for (int j = 0; j < 4; ++j) store4(sp + (r * 16) * D + j * 32, S[r][j]);
   }
+  }  // items
+}
+
+// Resident CTAs of `Fn` on the current device (SMs x CTAs per SM), looked up once per device.
+template <auto Fn>
+int resident_ctas(size_t smem, int* out) {
+  static int cached[64] = {};
+  int dev = 0;
+  QLA_CHECK_CUDA(cudaGetDevice(&dev));
+  if (dev >= 0 && dev < 64 && cached[dev] > 0) {
+    *out = cached[dev];
+    return QLA_OK;
+  }
+  int sms = 0, per_sm = 0;
+  QLA_CHECK_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  QLA_CHECK_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, Fn, 128, smem));
+  *out = sms * (per_sm > 0 ? per_sm : 1);
+  if (dev >= 0 && dev < 64) cached[dev] = *out;
+  return QLA_OK;
+}
+
+template <typename T, typename InterT, int R>
+int launch_recurrent_rows(const QlaRecurrentArgs& a, cudaStream_t stream) {
+  const int64_t items = static_cast<int64_t>(a.num_seqs) * a.num_v_heads * (kHeadDim / (16 * R));
+  constexpr size_t smem = kRecStages * R * 4 * 128 * sizeof(float4);
+  int resident = 0;
+  int rc = ensure_dynamic_smem<recurrent_kernel<T, InterT, R>>(smem);
+  if (rc != QLA_OK) return rc;
+  rc = resident_ctas<recurrent_kernel<T, InterT, R>>(smem, &resident);
+  if (rc != QLA_OK) return rc;
+  // one CTA per item while they all fit at once; otherwise as many CTAs as are resident, each walking the
+  // items with stride gridDim.x
+  const unsigned grid = static_cast<unsigned>(items < resident ? items : resident);
+  recurrent_kernel<T, InterT, R><<<grid, 128, smem, stream>>>(a, items);
+  QLA_CHECK_CUDA(cudaGetLastError());
+  return QLA_OK;
 }
 
 template <typename T, typename InterT>
 int launch_recurrent(const QlaRecurrentArgs& a, int rows, cudaStream_t stream) {
-  const int64_t heads = static_cast<int64_t>(a.num_seqs) * a.num_v_heads;
-  if (rows == 16) {
-    recurrent_kernel<T, InterT, 1><<<static_cast<unsigned>(heads * 8), 128, 0, stream>>>(a);
-  } else {
-    recurrent_kernel<T, InterT, 2><<<static_cast<unsigned>(heads * 4), 128, 0, stream>>>(a);
-  }
-  QLA_CHECK_CUDA(cudaGetLastError());
-  return QLA_OK;
+  return rows == 16 ? launch_recurrent_rows<T, InterT, 1>(a, stream) : launch_recurrent_rows<T, InterT, 2>(a, stream);
 }
 
 }  // namespace
