@@ -128,6 +128,28 @@ def test_state_index_modes(fq, mode):
     assert orc.max_abs(state.cpu(), ref_state) <= STATE_TOL
 
 
+@pytest.mark.parametrize("rows", [16, 32])
+def test_more_items_than_resident_ctas(fq, rows):
+    """Enough (sequence, head, row tile) items that every CTA walks several of them, so the staged copy of the
+    next state tile alternates its buffers; shuffled pool slots with some sequences on the zero state (-1,
+    nothing staged for them, no write-back)."""
+    N, T, Hk, Hv, slots = 96, 2, 2, 8, 100
+    d = _inputs(N, T, Hk, Hv, seed=21, slots=slots)
+    gen = torch.Generator().manual_seed(5)
+    idx = torch.randperm(slots, generator=gen)[:N].int()
+    idx[::7] = -1
+    c = _cuda(d)
+    state = c["state"].clone()
+    o = fq.fused_sigmoid_gating_delta_rule_update(
+        c["A_log"], c["a"], c["dt_bias"], c["q"], c["k"], c["v"], c["b"], state,
+        initial_state_indices=idx.cuda(), block_dv=rows)
+    ref_state = d["state"].clone()
+    o_ref = orc.recurrent_update_ref(d["A_log"], d["a"], d["dt_bias"], d["q"], d["k"], d["v"], d["b"],
+                                     ref_state, state_indices=idx)
+    assert orc.max_abs(o.float().cpu(), o_ref) <= O_TOL
+    assert orc.max_abs(state.cpu(), ref_state) <= STATE_TOL
+
+
 def test_ragged_cu_seqlens_and_tree(fq):
     lens = [3, 1, 5, 2]
     N, Hk, Hv = len(lens), 2, 4
