@@ -36,6 +36,20 @@ __device__ __forceinline__ void load4<__half>(const __half* p, float (&out)[4]) 
   float2 a = __half22float2(lo), b = __half22float2(hi);
   out[0] = a.x; out[1] = a.y; out[2] = b.x; out[3] = b.y;
 }
+template <typename T>
+__device__ __forceinline__ void unpack4(uint2 raw, float (&out)[4]);
+template <>
+__device__ __forceinline__ void unpack4<__nv_bfloat16>(uint2 raw, float (&out)[4]) {
+  float2 a = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&raw.x));
+  float2 b = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&raw.y));
+  out[0] = a.x; out[1] = a.y; out[2] = b.x; out[3] = b.y;
+}
+template <>
+__device__ __forceinline__ void unpack4<__half>(uint2 raw, float (&out)[4]) {
+  float2 a = __half22float2(*reinterpret_cast<__half2*>(&raw.x));
+  float2 b = __half22float2(*reinterpret_cast<__half2*>(&raw.y));
+  out[0] = a.x; out[1] = a.y; out[2] = b.x; out[3] = b.y;
+}
 template <>
 __device__ __forceinline__ void load4<float>(const float* p, float (&out)[4]) {
   float4 raw = *reinterpret_cast<const float4*>(p);
@@ -168,6 +182,26 @@ __global__ void __launch_bounds__(128) recurrent_kernel(const QlaRecurrentArgs p
     dt_b = load_scalar(p.dt_bias, p.dt_bias_dtype, h);
   }
 
+  // Inputs of a step (q, k row pieces, v, gate, beta) are requested one step ahead, so that with several draft
+  // tokens their global-memory latency overlaps the previous step's arithmetic instead of heading every step.
+  uint2 q_raw[4], k_raw[4];
+  T v_raw[R];
+  float a_in = 0.f, b_in = 0.f;
+  auto fetch_inputs = [&](int64_t t) {
+    const T* qp = qb + (t * p.num_k_heads + hk) * D + col0;
+    const T* kp = kb + (t * p.num_k_heads + hk) * D + col0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      q_raw[j] = *reinterpret_cast<const uint2*>(qp + j * 32);
+      k_raw[j] = *reinterpret_cast<const uint2*>(kp + j * 32);
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r) v_raw[r] = vb[(t * p.num_v_heads + h) * D + row0 + 16 * r];
+    a_in = load_scalar(p.a, p.a_dtype, t * p.num_v_heads + h);
+    b_in = load_scalar(p.b, p.a_dtype, t * p.num_v_heads + h);
+  };
+  if (len > 0) fetch_inputs(t0);
+
   for (int step = 0; step < len; ++step) {
     const int64_t t = t0 + step;
 
@@ -184,19 +218,16 @@ __global__ void __launch_bounds__(128) recurrent_kernel(const QlaRecurrentArgs p
     }
 
     float qv[4][4], kv[4][4];
-    {
-      const T* qp = qb + (t * p.num_k_heads + hk) * D + col0;
-      const T* kp = kb + (t * p.num_k_heads + hk) * D + col0;
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        load4<T>(qp + j * 32, qv[j]);
-        load4<T>(kp + j * 32, kv[j]);
-      }
+    for (int j = 0; j < 4; ++j) {
+      unpack4<T>(q_raw[j], qv[j]);
+      unpack4<T>(k_raw[j], kv[j]);
     }
     float vrow[R];
 #pragma unroll
-    for (int r = 0; r < R; ++r)
-      vrow[r] = Cvt<T>::to_f32(vb[(t * p.num_v_heads + h) * D + row0 + 16 * r]);
+    for (int r = 0; r < R; ++r) vrow[r] = Cvt<T>::to_f32(v_raw[r]);
+    const float a_raw = a_in, b_raw = b_in;
+    if (step + 1 < len) fetch_inputs(t + 1);
 
     float qs = p.scale, ks = 1.f;
     if (l2norm) {
@@ -221,8 +252,6 @@ __global__ void __launch_bounds__(128) recurrent_kernel(const QlaRecurrentArgs p
         kv[j][i] *= ks;
       }
 
-    const float a_raw = load_scalar(p.a, p.a_dtype, t * p.num_v_heads + h);
-    const float b_raw = load_scalar(p.b, p.a_dtype, t * p.num_v_heads + h);
     float g;
     if (p.flags & QLA_REC_A_IS_LOG_DECAY) {
       g = a_raw;
