@@ -98,3 +98,47 @@ def test_two_rank_head_sharding_reproduces_single_rank():
         assert p.exitcode == 0
     err, tmax = out.get()
     assert err < 1e-5 and tmax == 2.0
+
+
+def _sp_rank_main(rank, world, port, out):
+    """Sequence-parallel carry with the oracle standing in for the kernels: every rank summarises its slice
+    as (end state from zero, transition matrix), one all_gather, fold, then the slice with its incoming state."""
+    from flashqla_b200.seq_parallel import fold_incoming_state
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    Hv, K, T = 2, 64, 64 * 2 * world
+    inp = orc.make_prefill_inputs(1, T, 1, Hv, K=K, V=K, seed=9, with_h0=True, dtype=torch.float32, gate_div=4.0)
+    sl = slice(rank * T // world, (rank + 1) * T // world)
+    mine = {n: inp[n][:, sl] for n in ("q", "k", "v", "g", "beta")}
+    run = lambda v, h0: orc.chunk_gdr_fwd(mine["q"], mine["k"], v, mine["g"], mine["beta"], h0=h0, dtype=torch.float64)
+    H = run(mine["v"], None)["final_state"][0]
+    M = run(torch.zeros_like(mine["v"]), torch.eye(K).expand(1, Hv, K, K))["final_state"][0]
+    summary = torch.stack((H, M)).float()
+    gathered = [torch.empty_like(summary) for _ in range(world)]
+    dist.all_gather(gathered, summary)
+    incoming = fold_incoming_state(torch.stack(gathered), rank, inp["h0"])
+    res = run(mine["v"], incoming[None].double())
+    full = orc.chunk_gdr_fwd(inp["q"], inp["k"], inp["v"], inp["g"], inp["beta"], h0=inp["h0"], dtype=torch.float64)
+    err = float((res["o"] - full["o"][:, sl]).abs().max())
+    if rank == world - 1:
+        err = max(err, float((res["final_state"] - full["final_state"]).abs().max()))
+    t = torch.tensor([err])
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        out.put(float(t.item()))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_sequence_parallel_carry_reproduces_single_rank(world):
+    ctx = mp.get_context("spawn")
+    out = ctx.SimpleQueue()
+    port = _free_port()
+    procs = [ctx.Process(target=_sp_rank_main, args=(r, world, port, out)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(180)
+        assert p.exitcode == 0
+    assert out.get() < 1e-5
