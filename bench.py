@@ -279,6 +279,35 @@ def run_prefill(args, rank, world, device, varlen=False):
     return line
 
 
+def run_prefill_sp(args, rank, world, device):
+    """Config 1 with the TOKENS of the one sequence spread over the ranks (all heads on every rank) and the
+    chunk-boundary states carried by one all-gather per call: the optional sequence-parallel mode.  The
+    default multi-GPU prefill line shards heads instead, which needs no exchange."""
+    import flashqla_b200 as fq
+    Hk, Hv, T = 16, 32, args.tokens
+    per = (T // world // 64) * 64
+    lo = rank * per
+    hi = T if rank == world - 1 else lo + per
+    inp = prefill_inputs(T, Hk, Hv, seed=1)
+    c = {n: t[:, lo:hi].contiguous().to(device) for n, t in inp.items()}
+
+    def step():
+        fq.chunk_gated_delta_rule_fwd_sp(c["q"], c["k"], c["v"], c["g"], c["beta"])
+
+    with ClockSampler(device.index) as clocks:
+        ms = timed(step, args.steps, args.warmup, world, device)
+    ms_step = ms / args.steps
+    tps = T / (ms_step * 1e-3)
+    return {
+        "metric": "gdn_prefill_fwd_tokens_per_s", "value": tps, "unit": "tokens/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"prefill_fwd_B1_T{T}_Hk16_Hv32_K128_V128_chunk64", "sharding": f"tokens/{world}",
+                   "exchange": f"one all_gather of {2 * Hv * 65536} B per rank", "launch": "eager",
+                   "l2": "inputs exceed the 126 MB L2; no flush needed", "tokens": T},
+        "clocks": clocks.summary(), "gpu_launches": args.steps * 7}
+
+
 def run_recurrent(args, rank, world, device, verify: bool):
     import flashqla_b200 as fq
     from oracle import gdr_oracle as orc
@@ -389,7 +418,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="prefill_fwd", choices=["prefill_fwd", "varlen", "decode", "verify", "train"])
+    ap.add_argument("--workload", default="prefill_fwd", choices=["prefill_fwd", "prefill_sp", "varlen", "decode", "verify", "train"])
     ap.add_argument("--tokens", type=int, default=32768)
     ap.add_argument("--bf16-scratch", action="store_true")
     ap.add_argument("--cpu-sample-tokens", type=int, default=32768)
@@ -430,6 +459,8 @@ def main():
         dist.init_process_group("nccl", device_id=device)
     if args.workload == "prefill_fwd":
         line = run_prefill(args, rank, world, device)
+    elif args.workload == "prefill_sp":
+        line = run_prefill_sp(args, rank, world, device)
     elif args.workload == "varlen":
         line = run_prefill(args, rank, world, device, varlen=True)
     elif args.workload == "train":

@@ -62,3 +62,47 @@ def test_slice_must_be_whole_chunks():
     c = {n: t.cuda() for n, t in inp.items()}
     with pytest.raises(ValueError):
         sp.slice_summary(c["q"], c["k"], c["v"], c["g"], c["beta"])
+
+
+def _nccl_rank(rank, world, port, out):
+    import os
+    import torch.distributed as dist
+    import flashqla_b200 as fq
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    T, Hk, Hv = 4096, 2, 4
+    inp = orc.make_prefill_inputs(1, T, Hk, Hv, seed=33, with_h0=True)
+    sl = slice(rank * T // world, (rank + 1) * T // world)
+    c = {n: (t[:, sl] if n != "h0" else t).cuda() for n, t in inp.items()}
+    o, fs = fq.chunk_gated_delta_rule_fwd_sp(c["q"], c["k"], c["v"], c["g"], c["beta"], initial_state=c["h0"],
+                                             broadcast_final_state=True)
+    ref = orc.chunk_gdr_fwd(inp["q"], inp["k"], inp["v"], inp["g"], inp["beta"], h0=inp["h0"], dtype=torch.float64)
+    err = torch.tensor([orc.rel_rms(o.float().cpu(), ref["o"][:, sl]),
+                        orc.rel_rms(fs.float().cpu(), ref["final_state"])], device="cuda")
+    dist.all_reduce(err, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        out.put(err.cpu().tolist())
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_two_gpus_nccl_all_gather():
+    """The real collective: needs two GPUs, skipped on a single-GPU box."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import socket
+    import torch.multiprocessing as mp
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    out = ctx.SimpleQueue()
+    procs = [ctx.Process(target=_nccl_rank, args=(r, 2, port, out)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(300)
+        assert p.exitcode == 0
+    e_o, e_fs = out.get()
+    assert e_o <= RMS_TOL and e_fs <= RMS_TOL
