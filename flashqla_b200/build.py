@@ -52,6 +52,9 @@ def is_current() -> bool:
 def build(force: bool = False, verbose: bool = False) -> Path:
     """Compile every ``csrc/*.cu`` and link the shared library.  Returns its path."""
     if not force and is_current():
+        from .manifest import MANIFEST_NAME, write_manifest
+        if not (LIB_DIR / MANIFEST_NAME).exists():
+            write_manifest(LIB_DIR)
         return LIB_PATH
     LIB_DIR.mkdir(exist_ok=True)
     nvcc = _nvcc()
@@ -78,6 +81,8 @@ def build(force: bool = False, verbose: bool = False) -> Path:
             "arch=compute_100a,code=sm_100a", "-lcudart"]
     subprocess.run(link, check=True)
     STAMP.write_text(_digest())
+    from .manifest import write_manifest  # JSON description of the exports beside the library
+    write_manifest(LIB_DIR)
     return LIB_PATH
 
 

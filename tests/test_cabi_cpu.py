@@ -63,3 +63,26 @@ def test_python_api_rejects_bad_inputs():
     q = torch.zeros(1, 4, 1, 128, dtype=torch.bfloat16)
     with pytest.raises(ValueError, match="CUDA"):
         fq.fused_sigmoid_gating_delta_rule_update(None, None, None, q, q, q, None, None)
+
+
+def test_manifest_describes_the_header(built_lib):
+    """The JSON manifest written beside the library lists every exported function and every argument
+    structure with the header's field order, and its offsets are those of the ctypes mirrors."""
+    import json
+    from flashqla_b200 import _cabi, manifest
+    path = built_lib.parent / manifest.MANIFEST_NAME
+    assert path.exists(), "the build writes the manifest"
+    m = json.loads(path.read_text())
+    header = (ROOT / "include" / "flashqla_b200.h").read_text()
+    assert m["abi_version"] == int(re.search(r"#define QLA_ABI_VERSION (\d+)", header).group(1))
+    assert set(m["exports"]) == set(_cabi.EXPORTS)
+    for name, desc in m["structs"].items():
+        body = re.search(r"typedef struct %s \{(.*?)\} %s;" % (name, name), header, re.S).group(1)
+        body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
+        assert [f["name"] for f in desc["fields"]] == re.findall(r"(\w+)\s*;", body), name
+        cls = getattr(_cabi, name)
+        assert desc["size"] == ctypes.sizeof(cls)
+        assert all(f["offset"] == getattr(cls, f["name"]).offset for f in desc["fields"])
+    for flag, value in m["flags"].items():
+        c_name = "QLA_" + flag
+        assert re.search(r"%s\s*=\s*%d\b|#define %s\s+%d\b" % (c_name, value, c_name, value), header), c_name
