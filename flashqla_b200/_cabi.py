@@ -19,6 +19,7 @@ _DTYPES = {torch.float32: QLA_DT_F32, torch.bfloat16: QLA_DT_BF16, torch.float16
 REC_QK_L2NORM, REC_DISABLE_STATE_UPDATE, REC_A_IS_LOG_DECAY, REC_B_IS_BETA = 1, 2, 4, 8
 CHUNK_TRANSPOSE_STATE, CHUNK_STATE_ONLY, CHUNK_QK_L2NORM, CHUNK_SKIP_PREPARE = 1, 2, 4, 8
 CHUNK_INIT_IDENTITY, CHUNK_ZERO_V, CHUNK_PREPARE_ONLY, CHUNK_A_GIVEN, CHUNK_TABLES_READY = 16, 32, 64, 128, 256
+CHUNK_GATE_ACT, CHUNK_BETA_LOGIT = 512, 1024
 
 
 class QlaError(RuntimeError):
@@ -57,7 +58,7 @@ class QlaChunkFwdArgs(C.Structure):
         ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("g", C.c_void_p),
         ("beta", C.c_void_p), ("h0", C.c_void_p), ("cu_seqlens", C.c_void_p),
         ("seq_map", C.c_void_p), ("seq_order", C.c_void_p), ("chunk_limit", C.c_void_p), ("g_cumsum", C.c_void_p), ("A", C.c_void_p), ("w", C.c_void_p),
-        ("qk_rnorm", C.c_void_p), ("o", C.c_void_p), ("h", C.c_void_p), ("v_new", C.c_void_p), ("final_state", C.c_void_p),
+        ("qk_rnorm", C.c_void_p), ("A_log", C.c_void_p), ("dt_bias", C.c_void_p), ("beta_out", C.c_void_p), ("o", C.c_void_p), ("h", C.c_void_p), ("v_new", C.c_void_p), ("final_state", C.c_void_p),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("status", C.c_void_p),
     ]
 

@@ -45,7 +45,8 @@ def _check_common(q, k, v, g, beta, initial_state, cu_seqlens, transpose_state_l
 
 
 def _launch_fwd(q, k, v, g, beta, h0, cu, g_cumsum, A, o, h, v_new, final_state, scale, flags=0,
-                seq_map=None, chunk_limit=None, num_seqs=None, w=None, tables=None, seq_order=None, rnorm=None):
+                seq_map=None, chunk_limit=None, num_seqs=None, w=None, tables=None, seq_order=None, rnorm=None,
+                A_log=None, dt_bias=None, beta_out=None):
     """Fill ``QlaChunkFwdArgs`` from tensors and call ``qla_chunk_fwd`` on the current stream.  ``w`` is
     the per-chunk operand ``-(A diag(beta e^g) K)`` that the preparation step writes and the scan reads;
     it is allocated here when the call does both.  ``tables`` is an optional dict that keeps the chunk-table
@@ -64,13 +65,18 @@ def _launch_fwd(q, k, v, g, beta, h0, cu, g_cumsum, A, o, h, v_new, final_state,
     status = device_status(dev)
     if rnorm is not None:
         flags |= _cabi.CHUNK_QK_L2NORM
+    if A_log is not None:
+        flags |= _cabi.CHUNK_GATE_ACT
+    if beta_out is not None:
+        flags |= _cabi.CHUNK_BETA_LOGIT
     args = _cabi.QlaChunkFwdArgs(
         batch=B, seq_len=T, num_seqs=N, num_k_heads=Hk, num_v_heads=Hv,
         qkv_dtype=_cabi.dtype_code(k.dtype), gate_dtype=0 if g is None else _cabi.dtype_code(g.dtype),
         beta_dtype=_cabi.dtype_code(beta.dtype), flags=flags, max_chunks_per_seq=0, scale=float(scale),
         q=_cabi.ptr(q), k=_cabi.ptr(k), v=_cabi.ptr(v), g=_cabi.ptr(g), beta=_cabi.ptr(beta),
         h0=_cabi.ptr(h0), cu_seqlens=_cabi.ptr(cu), seq_map=_cabi.ptr(seq_map), seq_order=_cabi.ptr(seq_order),
-        chunk_limit=_cabi.ptr(chunk_limit), g_cumsum=_cabi.ptr(g_cumsum), A=_cabi.ptr(A), w=_cabi.ptr(w), qk_rnorm=_cabi.ptr(rnorm), o=_cabi.ptr(o),
+        chunk_limit=_cabi.ptr(chunk_limit), g_cumsum=_cabi.ptr(g_cumsum), A=_cabi.ptr(A), w=_cabi.ptr(w), qk_rnorm=_cabi.ptr(rnorm),
+        A_log=_cabi.ptr(A_log), dt_bias=_cabi.ptr(dt_bias), beta_out=_cabi.ptr(beta_out), o=_cabi.ptr(o),
         h=_cabi.ptr(h), v_new=_cabi.ptr(v_new), final_state=_cabi.ptr(final_state), workspace=None,
         workspace_bytes=0, status=_cabi.ptr(status))
     lib = _cabi.lib()
@@ -162,14 +168,22 @@ def chunk_gated_delta_rule_fwd(
     output_v_new: bool = False,
     transpose_state_layout: bool = False,
     use_qk_l2norm_in_kernel: bool = False,
+    A_log: Optional[torch.Tensor] = None,
+    dt_bias: Optional[torch.Tensor] = None,
+    beta_is_logit: bool = False,
 ):
     """Raw forward.  ``g`` is the per-token log decay; returns
     ``(g_cumsum, A, o, h | None, final_state | None[, v_new])`` where ``g_cumsum`` is the chunk-local
     cumulative gate and ``A`` the gated WY matrix ``[B,T,Hv,64]``, both in the form the backward
     expects.  ``use_qk_l2norm_in_kernel`` (an addition to the reference's raw forward): q and k are used as
     ``x * rsqrt(sum(x^2) + 1e-6)`` per row, with the factors folded into the kernels instead of a pass over q
-    and k; ``A`` and ``h`` are then those of the normalised inputs."""
+    and k; ``A`` and ``h`` are then those of the normalised inputs.  Two more additions fold the layer's gate
+    activations into the preparation kernel (the recurrent op always had them): with ``A_log`` / ``dt_bias``
+    ``[Hv]`` the argument ``g`` is the raw gate input ``a`` and ``g = -exp(A_log) * softplus(a + dt_bias)``
+    is used; with ``beta_is_logit`` the argument ``beta`` holds logits and ``sigmoid(beta)`` is used."""
     B, T, Hk, Hv, N = _check_common(q, k, v, g, beta, initial_state, cu_seqlens, transpose_state_layout)
+    if (A_log is None) != (dt_bias is None):
+        raise ValueError("A_log and dt_bias go together")
     dev = q.device
     if not q.is_cuda:
         raise ValueError("flashqla_b200 requires CUDA tensors")
@@ -199,6 +213,13 @@ def chunk_gated_delta_rule_fwd(
     v_new = torch.empty_like(v) if output_v_new else None
     rnorm = torch.empty(B, T, Hk, 2, dtype=torch.float32, device=dev) if use_qk_l2norm_in_kernel else None
     final_state = torch.empty(N, Hv, 128, 128, dtype=torch.float32, device=dev) if output_final_state else None
+    act = {}
+    if A_log is not None:
+        act.update(A_log=A_log.to(device=dev, dtype=torch.float32).contiguous(),
+                   dt_bias=dt_bias.to(device=dev, dtype=torch.float32).contiguous())
+    beta_act = torch.empty(B, T, Hv, dtype=torch.float32, device=dev) if beta_is_logit else None
+    if beta_act is not None:
+        act.update(beta_out=beta_act)
 
     plan = cp.get_plan(lens if lens is not None else [T] * B, Hv, dev) if auto_cp else None
     if plan is not None and plan.use_cp:
@@ -206,7 +227,9 @@ def chunk_gated_delta_rule_fwd(
         # over segments (segments are whole chunks, so chunk numbering is unchanged)
         w = new_w(k, beta)
         _launch_fwd(q if rnorm is not None else None, k, None, g, beta, None, cu, g_cumsum, A, None, None, None, None,
-                    scale, flags=_cabi.CHUNK_PREPARE_ONLY, w=w, rnorm=rnorm)
+                    scale, flags=_cabi.CHUNK_PREPARE_ONLY, w=w, rnorm=rnorm, **act)
+        if beta_act is not None:
+            beta = beta_act  # every later stage reads the activated values
         h0_kv = h0.transpose(-1, -2) if (h0 is not None and transpose_state_layout) else h0
         cp_h0 = cp.segment_initial_states(plan, k, v, beta, g_cumsum, A, w, h0_kv, scale, _launch_fwd, rnorm=rnorm)
         fs = final_state
@@ -221,7 +244,8 @@ def chunk_gated_delta_rule_fwd(
         # packed batches of unequal lengths: the longest sequences are handed to the GPU first
         order = longest_first_order(cu_seqlens, dev) if cu_seqlens is not None else None
         _launch_fwd(q, k, v, g, beta, h0, cu, g_cumsum, A, o, h, v_new, final_state, scale,
-                    flags=_cabi.CHUNK_TRANSPOSE_STATE if transpose_state_layout else 0, seq_order=order, rnorm=rnorm)
+                    flags=_cabi.CHUNK_TRANSPOSE_STATE if transpose_state_layout else 0, seq_order=order, rnorm=rnorm,
+                    **act)
     if output_v_new:
         return g_cumsum, A, o, h, final_state, v_new
     return g_cumsum, A, o, h, final_state
@@ -350,9 +374,17 @@ def chunk_gated_delta_rule(
     cu_seqlens: Optional[torch.Tensor] = None,
     head_first: bool = False,
     transpose_state_layout: bool = False,
+    use_gate_in_kernel: bool = False,
+    A_log: Optional[torch.Tensor] = None,
+    dt_bias: Optional[torch.Tensor] = None,
+    use_beta_sigmoid_in_kernel: bool = False,
 ):
     """``(o, final_state | None)`` with gradients for q, k, v, g, beta and initial_state
-    (reference: chunk/__init__.py:294-350)."""
+    (reference: chunk/__init__.py:294-350).  Additions after the reference's surface: with
+    ``use_gate_in_kernel`` the argument ``g`` is the raw gate input and
+    ``g = -exp(A_log) * softplus(g + dt_bias)`` (``A_log``, ``dt_bias`` ``[Hv]``) is applied here; with
+    ``use_beta_sigmoid_in_kernel`` the argument ``beta`` holds logits.  Without gradients both are folded into
+    the preparation kernel; with gradients they are torch operations in front of the op."""
     assert not head_first, "head_first=True is not supported"
     assert q.dtype == k.dtype == v.dtype
     assert q.dtype != torch.float32, "ChunkGatedDeltaRuleFunction does not support float32. Please use bfloat16."
@@ -362,17 +394,27 @@ def chunk_gated_delta_rule(
             "Please flatten variable-length inputs before processing.")
     if scale is None:
         scale = k.shape[-1] ** -0.5
-    if use_qk_l2norm_in_kernel:
+    if use_gate_in_kernel and (A_log is None or dt_bias is None):
+        raise ValueError("use_gate_in_kernel needs A_log and dt_bias")
+    if use_qk_l2norm_in_kernel or use_gate_in_kernel or use_beta_sigmoid_in_kernel:
         needs_grad = torch.is_grad_enabled() and any(
-            t is not None and t.requires_grad for t in (q, k, v, g, beta, initial_state))
+            t is not None and t.requires_grad for t in (q, k, v, g, beta, initial_state, A_log, dt_bias))
         if not needs_grad:
-            # inference: the normalisation is folded into the kernels (no pass over q and k)
+            # inference: normalisation and activations are folded into the kernels (no extra passes)
             out = chunk_gated_delta_rule_fwd(q, k, v, g, beta, scale=scale, initial_state=initial_state,
                                              cu_seqlens=cu_seqlens, output_final_state=output_final_state,
                                              transpose_state_layout=transpose_state_layout,
-                                             use_qk_l2norm_in_kernel=True)
+                                             use_qk_l2norm_in_kernel=use_qk_l2norm_in_kernel,
+                                             A_log=A_log if use_gate_in_kernel else None,
+                                             dt_bias=dt_bias if use_gate_in_kernel else None,
+                                             beta_is_logit=use_beta_sigmoid_in_kernel)
             return out[2].to(q.dtype), out[4]
-        q, k = l2norm(q), l2norm(k)
+        if use_qk_l2norm_in_kernel:
+            q, k = l2norm(q), l2norm(k)
+        if use_gate_in_kernel:
+            g = -torch.exp(A_log.float()) * torch.nn.functional.softplus(g.float() + dt_bias.float())
+        if use_beta_sigmoid_in_kernel:
+            beta = torch.sigmoid(beta.float())
     o, final_state = ChunkGatedDeltaRuleFunction.apply(
         q, k, v, g, beta, scale, initial_state, output_final_state, cu_seqlens, transpose_state_layout)
     return o, final_state

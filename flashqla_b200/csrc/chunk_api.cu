@@ -62,6 +62,11 @@ extern "C" QLA_API int qla_chunk_fwd(const QlaChunkFwdArgs* args, void* stream_)
   QLA_CHECK_ARG(!l2norm || skip_prepare || a.q, "QLA_CHUNK_QK_L2NORM needs q in the preparation step");
   QLA_CHECK_SUPPORTED(!l2norm || !(a.flags & QLA_CHUNK_A_GIVEN), "QLA_CHUNK_QK_L2NORM with QLA_CHUNK_A_GIVEN");
   QLA_CHECK_SUPPORTED(!(a.flags & QLA_CHUNK_ZERO_V) || state_only, "QLA_CHUNK_ZERO_V needs QLA_CHUNK_STATE_ONLY");
+  const bool gate_act = (a.flags & QLA_CHUNK_GATE_ACT) != 0, beta_logit = (a.flags & QLA_CHUNK_BETA_LOGIT) != 0;
+  QLA_CHECK_ARG(!gate_act || (a.A_log && a.dt_bias), "QLA_CHUNK_GATE_ACT needs A_log and dt_bias");
+  QLA_CHECK_ARG(!beta_logit || a.beta_out, "QLA_CHUNK_BETA_LOGIT needs the beta_out buffer");
+  QLA_CHECK_ARG(!(gate_act || beta_logit) || !(skip_prepare || a_given),
+                "gate / beta activation belongs to the preparation step: not with SKIP_PREPARE or A_GIVEN");
   const int64_t total_tokens = static_cast<int64_t>(a.batch) * a.seq_len;
   if (total_tokens == 0) return QLA_OK;
   QLA_CHECK_ARG(total_tokens < (int64_t(1) << 31), "too many tokens");
@@ -89,6 +94,8 @@ extern "C" QLA_API int qla_chunk_fwd(const QlaChunkFwdArgs* args, void* stream_)
     kp.g = a_given ? static_cast<const void*>(a.g_cumsum) : a.g; kp.beta = a.beta; kp.g_cumsum = a.g_cumsum;
     kp.A = a.A; kp.A_in = a_given ? a.A : nullptr; kp.w = a.w;
     kp.rnorm = l2norm ? a.qk_rnorm : nullptr; kp.norm_eps = 1e-6f;
+    kp.A_log = gate_act ? a.A_log : nullptr; kp.dt_bias = gate_act ? a.dt_bias : nullptr;
+    kp.beta_out = beta_logit ? a.beta_out : nullptr;
     kp.cu_seqlens = a.cu_seqlens; kp.pair_offsets = pair_offsets; kp.status = a.status;
     kp.num_seqs = a.num_seqs; kp.seq_len = a.seq_len; kp.num_k_heads = a.num_k_heads; kp.num_v_heads = a.num_v_heads;
     kp.gate_dtype = a_given ? QLA_DT_F32 : a.gate_dtype; kp.beta_dtype = a.beta_dtype;
@@ -111,6 +118,10 @@ extern "C" QLA_API int qla_chunk_fwd(const QlaChunkFwdArgs* args, void* stream_)
   fp.init_identity = (a.flags & QLA_CHUNK_INIT_IDENTITY) ? 1 : 0;
   fp.zero_v = (a.flags & QLA_CHUNK_ZERO_V) ? 1 : 0;
   fp.scale = a.scale;
+  if (beta_logit) {  // the scan reads the activated values the preparation step just wrote
+    fp.beta = a.beta_out;
+    fp.beta_dtype = QLA_DT_F32;
+  }
   fp.trace = current_trace_buffer();
   fp.trace_count = current_trace_count();
   const void* v = a.v ? a.v : a.k;  // never dereferenced with QLA_CHUNK_ZERO_V, only used for the tensor map

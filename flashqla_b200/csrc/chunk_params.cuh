@@ -14,6 +14,9 @@ struct KktParams {
   void* w;                      // out: -(A diag(beta gamma) K), [NT, Hv, 128]
   float* rnorm;                 // out or NULL: [NT, Hk, 2] = 1/|q_t|, 1/|k_t| (in-kernel q/k L2 norm)
   float norm_eps;               // added to the squared norm
+  const float* A_log;           // [Hv] or NULL: g = -exp(A_log[h]) * softplus(raw gate + dt_bias[h])
+  const float* dt_bias;         // [Hv], with A_log
+  float* beta_out;              // [NT, Hv] or NULL: beta holds logits, sigmoid(beta) is used and written here
   const int32_t* cu_seqlens;    // NULL: equal-length batch of `seq_len` tokens
   const int32_t* pair_offsets;  // [num_seqs + 1] exclusive scan of ceil(len / 128), varlen only
   int* status;

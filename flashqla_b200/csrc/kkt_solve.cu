@@ -183,8 +183,16 @@ __global__ void __launch_bounds__(128) kkt_solve_kernel(const __grid_constant__ 
     if (valid && hv < (hk + 1) * group) {
       const int64_t idx = tok * p.num_v_heads + hv;
       bv_n = load_scalar(p.beta, p.beta_dtype, idx);
+      if (p.beta_out != nullptr) {  // logits in: the activated value is what every later stage reads
+        bv_n = 1.f / (1.f + __expf(-bv_n));
+        p.beta_out[idx] = bv_n;
+      }
       if (p.A_in != nullptr) gin_n = p.g_cumsum[idx];
       else gv_n = load_scalar(p.g, p.gate_dtype, idx);
+      if (p.A_log != nullptr) {  // gate activation of the layer (recurrent op: recurrent_fused.py:346-487)
+        const float x = gv_n + p.dt_bias[hv];
+        gv_n = -expf(p.A_log[hv]) * (x <= 20.f ? log1pf(expf(x)) : x);
+      }
     }
   };
   fetch_gates(hk * group);

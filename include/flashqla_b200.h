@@ -130,9 +130,14 @@ enum { /* flags of QlaChunkFwdArgs / QlaChunkBwdArgs */
   QLA_CHUNK_PREPARE_ONLY = 64,   /* compute g_cumsum, A and w only; no scan                  */
   QLA_CHUNK_A_GIVEN = 128,       /* g_cumsum and A are inputs, w is rebuilt from them (the
                                     backward's recomputation of h / v_new)                  */
-  QLA_CHUNK_TABLES_READY = 256   /* the workspace already holds the chunk tables of these
+  QLA_CHUNK_TABLES_READY = 256,  /* the workspace already holds the chunk tables of these
                                     cu_seqlens (an earlier call with the same cu_seqlens,
                                     num_seqs and workspace filled it): no table launch      */
+  QLA_CHUNK_GATE_ACT = 512,      /* g holds the raw gate input a: the preparation step uses
+                                    g = -exp(A_log[h]) * softplus(a + dt_bias[h]) (softplus
+                                    with beta 1, threshold 20, as the recurrent op)          */
+  QLA_CHUNK_BETA_LOGIT = 1024    /* beta holds logits: the preparation step uses sigmoid(beta)
+                                    and writes it to beta_out, which the scan reads           */
 };
 
 /*
@@ -179,6 +184,10 @@ typedef struct QlaChunkFwdArgs {
                           operand of every chunk; out, in with QLA_CHUNK_SKIP_PREPARE        */
   float* qk_rnorm;     /* [B,T,Hk,2] fp32, only with QLA_CHUNK_QK_L2NORM: 1/|q_t|, 1/|k_t|; written by
                           the preparation step, read by the scan (in with QLA_CHUNK_SKIP_PREPARE) */
+  const float* A_log;  /* [Hv] fp32, only with QLA_CHUNK_GATE_ACT                            */
+  const float* dt_bias;/* [Hv] fp32, only with QLA_CHUNK_GATE_ACT                            */
+  float* beta_out;     /* [B,T,Hv] fp32 out, only with QLA_CHUNK_BETA_LOGIT: sigmoid(beta); pass it as
+                          `beta` (fp32) to later QLA_CHUNK_SKIP_PREPARE calls                 */
   void* o;             /* out, NULL with QLA_CHUNK_STATE_ONLY                                */
   void* h;             /* out or NULL                                                        */
   void* v_new;         /* out or NULL                                                        */

@@ -279,3 +279,36 @@ def test_error_not_worse_than_fla(fq, gate_div, zero_gate):
     for name, mine, theirs, r in (("o", o, o_f, ref["o"]), ("final_state", fs, fs_f, ref["final_state"])):
         e_mine, e_fla = orc.max_abs(mine.float().cpu(), r), orc.max_abs(theirs.float().cpu(), r)
         assert e_mine <= 1.1 * e_fla + 1e-4, f"{name}: max_abs {e_mine:.3e} vs FLA {e_fla:.3e}"
+
+
+@pytest.mark.parametrize("T,Hk,Hv,varlen", [(1024, 2, 4, False), (300, 1, 2, False), (700, 2, 2, True)])
+def test_gate_and_beta_activation_in_kernel(T, Hk, Hv, varlen):
+    """Raw gate input and beta logits activated inside the preparation kernel against the same call on
+    activated inputs (identical arithmetic downstream) and against the oracle; with and without context
+    parallelism (T = 1024 with few heads is cut into segments), ragged tail, packed sequences."""
+    import flashqla_b200 as fq
+    inp = orc.make_prefill_inputs(1, T, Hk, Hv, seed=41)
+    gen = torch.Generator().manual_seed(7)
+    a_raw = torch.randn(1, T, Hv, generator=gen)
+    b_raw = torch.randn(1, T, Hv, generator=gen)
+    A_log = -0.5 + torch.rand(Hv, generator=gen)
+    dt_bias = 0.3 * torch.randn(Hv, generator=gen)
+    g = -torch.exp(A_log) * torch.nn.functional.softplus(a_raw + dt_bias)
+    beta = torch.sigmoid(b_raw)
+    cu = torch.tensor([0, 130, 450, T], dtype=torch.int32) if varlen else None
+    c = {n: t.cuda() for n, t in inp.items()}
+    kw = dict(cu_seqlens=None if cu is None else cu.cuda())
+    _, _, o_ref, _, fs_ref = fq.chunk_gated_delta_rule_fwd(c["q"], c["k"], c["v"], g.cuda(), beta.cuda(), **kw)
+    _, _, o, _, fs = fq.chunk_gated_delta_rule_fwd(c["q"], c["k"], c["v"], a_raw.cuda(), b_raw.cuda(),
+                                                   A_log=A_log.cuda(), dt_bias=dt_bias.cuda(), beta_is_logit=True, **kw)
+    # same kernels, same operands up to the rounding of the activations (expf / log1pf on device vs torch)
+    assert orc.rel_rms(o.float().cpu(), o_ref.float().cpu()) <= 1e-3
+    assert orc.rel_rms(fs.cpu(), fs_ref.cpu()) <= 1e-3
+    if cu is None:
+        ref = orc.chunk_gdr_fwd(inp["q"], inp["k"], inp["v"], g, beta, dtype=torch.float64)
+        assert orc.rel_rms(o.float().cpu(), ref["o"]) <= 5e-3
+        assert orc.rel_rms(fs.float().cpu(), ref["final_state"]) <= 5e-3
+    o2, fs2 = fq.chunk_gated_delta_rule(c["q"], c["k"], c["v"], a_raw.cuda(), b_raw.cuda(), output_final_state=True,
+                                        use_gate_in_kernel=True, A_log=A_log.cuda(), dt_bias=dt_bias.cuda(),
+                                        use_beta_sigmoid_in_kernel=True, **kw)
+    assert torch.equal(o2, o.to(o2.dtype)) and torch.equal(fs2, fs)
