@@ -239,3 +239,32 @@ def test_commit_verified_state(scratch_dtype):
     fq.commit_verified_state(pool, inter, accepted, initial_state_indices=bad)
     with pytest.raises(Exception):
         fq.check_device_status()
+
+
+def test_prefill_then_decode_through_the_pool(fq):
+    """Prefill writes the final states into pool slots (one sequence without a slot), a second prefill call
+    continues from the pool, then the recurrent op decodes one more token from the same slots: o of that token
+    and the pool must be those of the per-token recurrence over all tokens."""
+    N, Hk, Hv, T1, T2, slots = 3, 2, 4, 128, 64, 6
+    inp = orc.make_prefill_inputs(N, T1 + T2 + 1, Hk, Hv, seed=51)
+    c = {n: t.cuda() for n, t in inp.items()}
+    idx = torch.tensor([4, -1, 1], dtype=torch.int32)
+    pool = torch.full((slots, Hv, 128, 128), 7.0, device="cuda")
+    part = lambda a, b: [c[n][:, a:b].contiguous() for n in ("q", "k", "v", "g", "beta")]
+    o1, _ = fq.prefill_into_state_pool(*part(0, T1), pool, idx.cuda())
+    o2, _ = fq.prefill_into_state_pool(*part(T1, T1 + T2), pool, idx.cuda(), continue_from_pool=True)
+    assert float((pool[[0, 2, 3, 5]] - 7.0).abs().max()) == 0.0  # untouched slots
+    # one decode token per sequence from the pool (packed [1, N, ...] layout of the recurrent op)
+    t = T1 + T2
+    tok = lambda n: c[n][:, t].unsqueeze(0).contiguous()
+    o3 = fq.fused_sigmoid_gating_delta_rule_update(
+        None, tok("g"), None, tok("q"), tok("k"), tok("v"), tok("beta"), pool, initial_state_indices=idx.cuda(),
+        use_qk_l2norm_in_kernel=False, a_is_log_decay=True, b_is_beta=True, assume_regular=True)
+    ref = orc.naive_recurrent_gdr(inp["q"], inp["k"], inp["v"], inp["g"], inp["beta"], dtype=torch.float64)
+    o_ref, s_ref = ref[0], ref[1]
+    keep = [0, 2]  # sequence 1 has no slot: its second prefill and its decode start from zero
+    assert orc.rel_rms(o1.float().cpu(), o_ref[:, :T1]) <= 5e-3
+    assert orc.rel_rms(o2.float().cpu()[keep], o_ref[keep, T1:t]) <= 5e-3
+    assert orc.rel_rms(o3.float().cpu()[0, keep], o_ref[keep, t]) <= 5e-3
+    # pool layout is [V, K]; the oracle's state is [K, V]
+    assert orc.rel_rms(pool[[4, 1]].cpu(), s_ref[keep].transpose(-1, -2).float()) <= 5e-3
