@@ -95,3 +95,22 @@ def test_verify_equals_successive_decodes():
         assert orc.max_abs(o_t[0].float(), o_v[:, t].float()) <= 3e-3
         assert orc.max_abs(inter[:, t], pool_d) <= 1e-4
     assert orc.max_abs(pool_v, pool_d) <= 1e-4
+
+
+def test_backward_is_linear_in_do_at_config3():
+    """Config 3 (4 x 8192 tokens, 32 heads): for fixed inputs every gradient is linear in the output gradient."""
+    import flashqla_b200 as fq
+    B, T3, H = 4, 8192, 32
+    gen = torch.Generator(device="cuda").manual_seed(3)
+    rn = lambda *s: torch.randn(*s, generator=gen, device="cuda")
+    unit = lambda x: x * torch.rsqrt((x * x).sum(-1, keepdim=True) + 1e-6)
+    q, k = unit(rn(B, T3, H, 128)).bfloat16(), unit(rn(B, T3, H, 128)).bfloat16()
+    v = rn(B, T3, H, 128).bfloat16()
+    g, beta = torch.nn.functional.logsigmoid(rn(B, T3, H)), torch.sigmoid(rn(B, T3, H))
+    g_cs, A, o, h, fs, v_new = fq.chunk_gated_delta_rule_fwd(q, k, v, g, beta, output_h=True, output_v_new=True)
+    do1, do2 = rn(B, T3, H, 128).bfloat16(), rn(B, T3, H, 128).bfloat16()
+    run = lambda do: fq.chunk_gated_delta_rule_bwd(q, k, v, g_cs, beta, A, do, h=h, v_new=v_new)[:5]
+    ga, gb = run(do1), run(do2)
+    gc = run((do1.float() + do2.float()).bfloat16())
+    for name, a, b, c in zip(("dq", "dk", "dv", "dbeta", "dg"), ga, gb, gc):
+        assert orc.rel_rms(a.float() + b.float(), c.float()) <= 2e-2, name
