@@ -268,3 +268,28 @@ def test_prefill_then_decode_through_the_pool(fq):
     assert orc.rel_rms(o3.float().cpu()[0, keep], o_ref[keep, t]) <= 5e-3
     # pool layout is [V, K]; the oracle's state is [K, V]
     assert orc.rel_rms(pool[[4, 1]].cpu(), s_ref[keep].transpose(-1, -2).float()) <= 5e-3
+
+
+def test_decode_step_in_a_cuda_graph(fq):
+    """A decode step captured in a CUDA graph (how serving loops launch it; the reference skips its autotune
+    under capture, recurrent_fused.py:234) replays with the same result as a plain call."""
+    N, Hk, Hv = 8, 2, 4
+    d = _inputs(N, 1, Hk, Hv, seed=61)
+    c = _cuda(d)
+    kw = dict(use_qk_l2norm_in_kernel=True)
+    ref_state = c["state"].clone()
+    o_ref = fq.fused_sigmoid_gating_delta_rule_update(c["A_log"], c["a"], c["dt_bias"], c["q"], c["k"], c["v"],
+                                                      c["b"], ref_state, **kw)
+    state = c["state"].clone()
+    graph = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            o = fq.fused_sigmoid_gating_delta_rule_update(c["A_log"], c["a"], c["dt_bias"], c["q"], c["k"], c["v"],
+                                                          c["b"], state, **kw)
+    torch.cuda.current_stream().wait_stream(side)
+    state.copy_(c["state"])  # capture does not run the kernel; replay on the initial pool
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(o, o_ref) and torch.equal(state, ref_state)
