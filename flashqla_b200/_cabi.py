@@ -46,6 +46,7 @@ class QlaRecurrentArgs(C.Structure):
         ("k", C.c_void_p), ("v", C.c_void_p), ("b", C.c_void_p), ("state", C.c_void_p),
         ("state_indices", C.c_void_p), ("cu_seqlens", C.c_void_p), ("inter", C.c_void_p),
         ("inter_indices", C.c_void_p), ("parents", C.c_void_p), ("o", C.c_void_p),
+        ("status", C.c_void_p), ("state_dtype", C.c_int32), ("parents_steps", C.c_int32),
     ]
 
 
@@ -82,6 +83,7 @@ class QlaStateCommitArgs(C.Structure):
         ("num_seqs", C.c_int32), ("num_v_heads", C.c_int32), ("inter_dtype", C.c_int32), ("inter_steps", C.c_int32),
         ("inter_slots", C.c_int64), ("state_slots", C.c_int64), ("inter", C.c_void_p), ("accepted", C.c_void_p),
         ("state_indices", C.c_void_p), ("inter_indices", C.c_void_p), ("state", C.c_void_p), ("status", C.c_void_p),
+        ("state_dtype", C.c_int32), ("reserved", C.c_int32),
     ]
 
 

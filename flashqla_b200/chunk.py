@@ -49,9 +49,9 @@ def _launch_fwd(q, k, v, g, beta, h0, cu, g_cumsum, A, o, h, v_new, final_state,
                 A_log=None, dt_bias=None, beta_out=None):
     """Fill ``QlaChunkFwdArgs`` from tensors and call ``qla_chunk_fwd`` on the current stream.  ``w`` is
     the per-chunk operand ``-(A diag(beta e^g) K)`` that the preparation step writes and the scan reads;
-    it is allocated here when the call does both.  ``tables`` is an optional dict that keeps the chunk-table
-    workspace of a fixed ``cu`` (the segments of a context-parallel plan) across calls: the first call
-    fills it, later ones skip the table launch.  ``rnorm`` ``[B,T,Hk,2]`` switches the in-kernel q / k L2
+    it is allocated here when the call does both.  ``tables`` is an optional dict holding the ready-made
+    chunk-table workspace of a fixed ``cu`` (``chunk_tables_workspace``: the segments of a context-parallel
+    plan); calls that get it skip the table launch.  ``rnorm`` ``[B,T,Hk,2]`` switches the in-kernel q / k L2
     norm on: the preparation step writes the reciprocal row norms there, the scan reads them."""
     dev = k.device
     if w is None:
@@ -89,11 +89,26 @@ def _launch_fwd(q, k, v, g, beta, h0, cu, g_cumsum, A, o, h, v_new, final_state,
         if ws_bytes:
             ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
             args.workspace, args.workspace_bytes = ws.data_ptr(), ws_bytes
-            if tables is not None:
-                tables["ws"] = ws  # filled by this call, in stream order before any later reader
     with torch.cuda.device(dev):
         code = lib.qla_chunk_fwd(args, _cabi.current_stream(dev))
     _cabi.check(code, "qla_chunk_fwd")
+
+
+def chunk_tables_workspace(cu: list, device) -> dict:
+    """The workspace ``qla_chunk_fwd`` keeps its chunk tables in, computed on the host for boundaries known
+    there: ``[n + 1]`` int32 exclusive scans of ``ceil(len / 128)`` and of ``ceil(len / 64)``, each padded to
+    16 bytes.  The upload is a blocking copy, so the tables are complete before any stream can use them."""
+    n = len(cu) - 1
+    padded = ((n + 1) * 4 + 15) // 16 * 4
+    pair, chunk = [0], [0]
+    for i in range(n):
+        length = cu[i + 1] - cu[i]
+        pair.append(pair[-1] + (length + 127) // 128)
+        chunk.append(chunk[-1] + (length + CHUNK - 1) // CHUNK)
+    host = torch.zeros(2 * padded, dtype=torch.int32)
+    host[:n + 1] = torch.tensor(pair, dtype=torch.int32)
+    host[padded:padded + n + 1] = torch.tensor(chunk, dtype=torch.int32)
+    return {"ws": host.to(device).view(torch.uint8)}
 
 
 def new_w(k, beta):
@@ -112,7 +127,7 @@ def rebuild_w(k, beta, g_cumsum, A, cu):
 def launches_per_forward(varlen: bool, use_cp: bool = False) -> int:
     """Kernels of this library one forward call launches.  Plain: [chunk tables] + kkt_solve + chunk
     scan.  With context parallelism: [tables] + kkt_solve, plan, warm-up scan, transition scan, chain, main
-    scan (the chunk tables of the plan's segments are computed by the first call with that plan only)."""
+    scan (the chunk tables of the plan's segments are built on the host together with the plan)."""
     if use_cp:
         return (2 if varlen else 1) + 1 + 1 + 1 + 1 + 1
     return 3 if varlen else 2
@@ -198,7 +213,7 @@ def chunk_gated_delta_rule_fwd(
     lens = None
     if cu_seqlens is not None:
         cu = cu_seqlens.to(device=dev, dtype=torch.int32).contiguous()
-        lens = host_seqlens(cu_seqlens)
+        lens = host_seqlens(cu_seqlens, total_tokens=B * T)
 
     g_cumsum = torch.empty(B, T, Hv, dtype=torch.float32, device=dev)
     A = torch.empty(B, T, Hv, CHUNK, dtype=q.dtype, device=dev)
@@ -290,7 +305,7 @@ def chunk_gated_delta_rule_bwd(
     lens = None
     if cu_seqlens is not None:
         cu = cu_seqlens.to(device=dev, dtype=torch.int32).contiguous()
-        lens = host_seqlens(cu_seqlens)
+        lens = host_seqlens(cu_seqlens, total_tokens=B * T)
     flags = _cabi.CHUNK_TRANSPOSE_STATE if transpose_state_layout else 0
     if h is None or v_new is None:
         n_chunks = B * ((T + CHUNK - 1) // CHUNK) if lens is None else sum((n + CHUNK - 1) // CHUNK for n in lens)
@@ -333,9 +348,11 @@ class ChunkGatedDeltaRuleFunction(torch.autograd.Function):
     @staticmethod
     @torch.amp.custom_fwd(device_type="cuda")
     def forward(ctx, q, k, v, g, beta, scale, initial_state, output_final_state, cu_seqlens,
-                transpose_state_layout):
-        # h and v_new are only kept when a backward can follow (False for every input under torch.no_grad())
-        need_grad = any(ctx.needs_input_grad)
+                transpose_state_layout, keep_for_backward=True):
+        # h and v_new are only kept when a backward can follow.  needs_input_grad reflects requires_grad of the
+        # inputs even under torch.no_grad(), and grad mode is always off inside forward(), so the caller
+        # passes whether gradients were enabled at the call.
+        need_grad = keep_for_backward and any(ctx.needs_input_grad)
         out = chunk_gated_delta_rule_fwd(
             q, k, v, g, beta, scale=scale, initial_state=initial_state, cu_seqlens=cu_seqlens,
             output_final_state=output_final_state, output_h=need_grad, output_v_new=need_grad,
@@ -357,7 +374,7 @@ class ChunkGatedDeltaRuleFunction(torch.autograd.Function):
             cu_seqlens=cu_seqlens, h=h, v_new=v_new, transpose_state_layout=ctx.transpose_state_layout)
         if dh0 is not None and initial_state is not None:
             dh0 = dh0.to(initial_state.dtype)
-        return (dq, dk, dv, dg.to(ctx.g_dtype), db.to(ctx.beta_dtype), None, dh0, None, None, None)
+        return (dq, dk, dv, dg.to(ctx.g_dtype), db.to(ctx.beta_dtype), None, dh0, None, None, None, None)
 
 
 @torch.compiler.disable
@@ -416,5 +433,6 @@ def chunk_gated_delta_rule(
         if use_beta_sigmoid_in_kernel:
             beta = torch.sigmoid(beta.float())
     o, final_state = ChunkGatedDeltaRuleFunction.apply(
-        q, k, v, g, beta, scale, initial_state, output_final_state, cu_seqlens, transpose_state_layout)
+        q, k, v, g, beta, scale, initial_state, output_final_state, cu_seqlens, transpose_state_layout,
+        torch.is_grad_enabled())
     return o, final_state

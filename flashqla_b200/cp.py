@@ -42,7 +42,7 @@ class CpPlan:
     seg_raw: Optional[List[int]] = None      # raw sequence of a segment that ENDS it, else -1
     raw_first: Optional[List[int]] = None    # first segment of every raw sequence, len = n_raw + 1
     dev: Optional[Dict[str, torch.Tensor]] = None
-    tables: Optional[Dict[str, torch.Tensor]] = None  # chunk-table workspace of `cu`, filled by the first launch
+    tables: Optional[Dict[str, torch.Tensor]] = None  # chunk-table workspace of `cu`, built with the plan
 
 
 _PLAN_CACHE: Dict[Tuple, CpPlan] = {}
@@ -88,7 +88,8 @@ def get_plan(lens: Sequence[int], num_v_heads: int, device: torch.device) -> CpP
         sms = torch.cuda.get_device_properties(device).multi_processor_count
         plan = plan_segments(lens, num_v_heads, sms)
         if plan.use_cp:
-            plan.tables = {}
+            from .chunk import chunk_tables_workspace
+            plan.tables = chunk_tables_workspace(plan.cu, device)
             i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=device)
             n_seg = len(plan.seg_next)
             plan.dev = dict(
@@ -99,11 +100,9 @@ def get_plan(lens: Sequence[int], num_v_heads: int, device: torch.device) -> CpP
                 identity=i32(list(range(n_seg))),
                 first_rows=torch.tensor(plan.raw_first[:-1], dtype=torch.int64, device=device))
         # Plans are never evicted: captured CUDA graphs and in-flight launches keep using a plan's device
-        # tensors.  Past 256 distinct shapes new plans are simply not cached (and do not keep their tables).
+        # tensors.  Past 256 distinct shapes new plans are simply not cached.
         if len(_PLAN_CACHE) < 256:
             _PLAN_CACHE[key] = plan
-        else:
-            plan.tables = None
     return plan
 
 

@@ -14,9 +14,11 @@
 //   * every call on a GPU uses the same array, so two calls that may overlap on the GPU (different
 //     streams) race on it - serialise them;
 //   * the tables are rewritten completely by each call before they are read, nothing in the array has
-//     to be cleared between calls;
-//   * the first call on each GPU looks the array's device address up (cudaGetSymbolAddress); make that
-//     first call outside of any stream capture.
+//     to be cleared between calls; for the same reason QLA_CHUNK_TABLES_READY is ignored here (another
+//     call may have rewritten the shared array since the caller last filled it);
+//   * the first call on each GPU looks the array's device address up (cudaGetSymbolAddress) and, like
+//     qla_chunk_fwd, raises the dynamic shared-memory limit of the kernels it launches
+//     (cudaFuncSetAttribute); make that first call outside of any stream capture.
 // It calls no cudaMalloc / cudaFree and no allocating library routine; inputs, outputs and the status
 // word are still the caller's.
 #include <mutex>
@@ -72,5 +74,6 @@ extern "C" QLA_API int qla_chunk_fwd_noalloc(const QlaChunkFwdArgs* args, void* 
   QlaChunkFwdArgs a = *args;
   a.workspace = scratch;
   a.workspace_bytes = kScratchBytes;
+  a.flags &= ~QLA_CHUNK_TABLES_READY;  // the shared array may hold another call's tables
   return qla_chunk_fwd(&a, stream);
 }

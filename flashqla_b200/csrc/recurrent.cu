@@ -68,6 +68,15 @@ __device__ __forceinline__ void store4(__nv_bfloat16* p, const float (&x)[4]) {
   *reinterpret_cast<uint2*>(p) = raw;
 }
 
+__device__ __forceinline__ uint2 pack4(const float (&x)[4]) {
+  __nv_bfloat162 lo = __floats2bfloat162_rn(x[0], x[1]);
+  __nv_bfloat162 hi = __floats2bfloat162_rn(x[2], x[3]);
+  uint2 raw;
+  raw.x = *reinterpret_cast<uint32_t*>(&lo);
+  raw.y = *reinterpret_cast<uint32_t*>(&hi);
+  return raw;
+}
+
 __device__ __forceinline__ float group8_sum(float x) {
   x += __shfl_xor_sync(0xffffffffu, x, 1);
   x += __shfl_xor_sync(0xffffffffu, x, 2);
@@ -80,21 +89,48 @@ __device__ __forceinline__ float group8_sum(float x) {
 #endif
 constexpr int kRecStages = QLA_REC_STAGES;  // state tiles staged per CTA: the current one and kRecStages - 1 ahead
 
-template <typename T, typename InterT, int R>
+// One 16-byte (fp32 pool) or 8-byte (16-bit pool) piece of a state row: the four values a lane owns.
+template <typename StateT>
+struct StatePiece;
+template <>
+struct StatePiece<float> {
+  using Raw = float4;
+  static __device__ __forceinline__ void copy_async(Raw* dst, const float* src) { mm::cp_async16(dst, src, true); }
+  static __device__ __forceinline__ void unpack(const Raw& x, float (&out)[4]) {
+    out[0] = x.x; out[1] = x.y; out[2] = x.z; out[3] = x.w;
+  }
+};
+template <>
+struct StatePiece<__nv_bfloat16> {
+  using Raw = uint2;
+  static __device__ __forceinline__ void copy_async(Raw* dst, const __nv_bfloat16* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(mm::smem_addr(dst)), "l"(src) : "memory");
+  }
+  static __device__ __forceinline__ void unpack(const Raw& x, float (&out)[4]) { unpack4<__nv_bfloat16>(x, out); }
+};
+
+template <typename T, typename InterT, typename StateT, int R>
 __global__ void __launch_bounds__(128) recurrent_kernel(const QlaRecurrentArgs p, const int64_t total_items) {
   constexpr int D = kHeadDim;
   constexpr int BV = 16 * R;
   constexpr int kTiles = D / BV;
   // [kRecStages][R * 4 pieces][128 threads] float4: every thread stages exactly the 16-byte pieces it owns, so
   // no barrier is needed between the copy and its use
-  extern __shared__ __align__(16) float4 s_stage[];
+  using Piece = StatePiece<StateT>;
+  extern __shared__ __align__(16) uint8_t s_stage_raw[];
+  typename Piece::Raw* s_stage = reinterpret_cast<typename Piece::Raw*>(s_stage_raw);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int sub = lane & 7, grp = lane >> 3;
   const int col0 = sub * 4;  // first owned column of j = 0; j-th is col0 + 32 j
 
+  // A slot outside the pool is never touched: the sequence runs from a zero state without write-back, and
+  // the status word says that an index was bad.
+  auto bad_index = [&]() {
+    if (p.status != nullptr && threadIdx.x == 0) atomicCAS(p.status, 0, kStatusBadIndex);
+  };
   auto pool_slot = [&](int n) -> int64_t {
     int64_t sidx = p.state_indices ? p.state_indices[n] : n;
-    return sidx >= p.state_slots ? -1 : sidx;  // never touch memory outside the pool
+    return sidx >= p.state_slots ? -1 : sidx;
   };
   // The state tile of an item is requested one item ahead (cp.async, L2 only): the copy of the next tile is
   // in flight while this one is computed and written back, which keeps reads queued at the memory the whole
@@ -106,12 +142,12 @@ __global__ void __launch_bounds__(128) recurrent_kernel(const QlaRecurrentArgs p
     const int64_t sidx = pool_slot(n);
     if (sidx < 0) return;
     const int row0 = tile * BV + warp * 4 + grp;
-    const float* sp = static_cast<const float*>(p.state) + ((sidx * p.num_v_heads + h) * D + row0) * D + col0;
+    const StateT* sp = static_cast<const StateT*>(p.state) + ((sidx * p.num_v_heads + h) * D + row0) * D + col0;
 #pragma unroll
     for (int r = 0; r < R; ++r)
 #pragma unroll
       for (int j = 0; j < 4; ++j)
-        mm::cp_async16(&s_stage[(stage * R * 4 + r * 4 + j) * 128 + threadIdx.x], sp + (r * 16) * D + j * 32, true);
+        Piece::copy_async(&s_stage[(stage * R * 4 + r * 4 + j) * 128 + threadIdx.x], sp + (r * 16) * D + j * 32);
   };
 
   const T* qb = static_cast<const T*>(p.q);
@@ -148,12 +184,22 @@ __global__ void __launch_bounds__(128) recurrent_kernel(const QlaRecurrentArgs p
   } else {
     t0 = p.cu_seqlens[n];
     len = p.cu_seqlens[n + 1] - t0;
+    // boundaries that leave the token range would read q / k / v and write o out of bounds
+    if (t0 < 0 || len < 0 || t0 > p.total_tokens || len > p.total_tokens - t0) {
+      bad_index();
+      t0 = max(0, min(t0, p.total_tokens));
+      len = max(0, min(len, p.total_tokens - t0));
+    }
   }
   const int64_t sidx = pool_slot(n);
+  if (p.state_indices != nullptr && p.state_indices[n] >= p.state_slots) bad_index();
   int64_t cidx = -1;
   if (p.inter != nullptr) {
     cidx = p.inter_indices ? p.inter_indices[n] : n;
-    if (cidx >= p.inter_slots) cidx = -1;
+    if (cidx >= p.inter_slots) {
+      bad_index();
+      cidx = -1;
+    }
   }
 
   const int row0 = tile * BV + warp * 4 + grp;  // row of r = 0; r-th row is row0 + 16 r
@@ -164,8 +210,7 @@ __global__ void __launch_bounds__(128) recurrent_kernel(const QlaRecurrentArgs p
     for (int r = 0; r < R; ++r)
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        const float4 x = s_stage[((it % kRecStages) * R * 4 + r * 4 + j) * 128 + threadIdx.x];
-        S[r][j][0] = x.x; S[r][j][1] = x.y; S[r][j][2] = x.z; S[r][j][3] = x.w;
+        Piece::unpack(s_stage[((it % kRecStages) * R * 4 + r * 4 + j) * 128 + threadIdx.x], S[r][j]);
       }
   } else {
 #pragma unroll
@@ -206,7 +251,9 @@ __global__ void __launch_bounds__(128) recurrent_kernel(const QlaRecurrentArgs p
     const int64_t t = t0 + step;
 
     if (p.parents != nullptr && step > 0 && cidx >= 0) {
-      const int par = p.parents[static_cast<int64_t>(n) * p.parents_stride + step];
+      if (step >= p.parents_steps) bad_index();  // the parents table is narrower than this sequence
+      const int par = step < p.parents_steps ? p.parents[static_cast<int64_t>(n) * p.parents_stride + step] : step - 1;
+      if (par != step - 1 && (par < 0 || par >= p.inter_steps)) bad_index();
       if (par != step - 1 && par >= 0 && par < p.inter_steps) {
         const InterT* src =
             ib + (((cidx * p.inter_steps + par) * p.num_v_heads + h) * D + row0) * D + col0;
@@ -304,15 +351,35 @@ __global__ void __launch_bounds__(128) recurrent_kernel(const QlaRecurrentArgs p
 
     if (cidx >= 0 && step < p.inter_steps) {
       InterT* dst = ib + (((cidx * p.inter_steps + step) * p.num_v_heads + h) * D + row0) * D + col0;
+      if constexpr (sizeof(InterT) == 2) {
+        // 16-bit scratch: a lane's four values are only 8 bytes.  Neighbouring lanes (sub, sub ^ 1) own adjacent
+        // column groups, so they swap one packed piece each and every lane writes 16 bytes: the even lane
+        // columns [4 sub, 4 sub + 8) of piece j, the odd lane the same eight columns of piece j + 1.
+        const bool odd = (sub & 1) != 0;
+        InterT* dst16 = dst - (odd ? 4 : 0);
 #pragma unroll
-      for (int r = 0; r < R; ++r)
+        for (int r = 0; r < R; ++r)
 #pragma unroll
-        for (int j = 0; j < 4; ++j) store4(dst + (r * 16) * D + j * 32, S[r][j]);
+          for (int j = 0; j < 4; j += 2) {
+            const uint2 p0 = pack4(S[r][j]), p1 = pack4(S[r][j + 1]);
+            const uint2 send = odd ? p0 : p1;
+            uint2 recv;
+            recv.x = __shfl_xor_sync(0xffffffffu, send.x, 1);
+            recv.y = __shfl_xor_sync(0xffffffffu, send.y, 1);
+            const uint4 out = odd ? make_uint4(recv.x, recv.y, p1.x, p1.y) : make_uint4(p0.x, p0.y, recv.x, recv.y);
+            *reinterpret_cast<uint4*>(dst16 + (r * 16) * D + (j + (odd ? 1 : 0)) * 32) = out;
+          }
+      } else {
+#pragma unroll
+        for (int r = 0; r < R; ++r)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) store4(dst + (r * 16) * D + j * 32, S[r][j]);
+      }
     }
   }
 
   if (!(p.flags & QLA_REC_DISABLE_STATE_UPDATE) && sidx >= 0) {
-    float* sp = static_cast<float*>(p.state) + ((sidx * p.num_v_heads + h) * D + row0) * D + col0;
+    StateT* sp = static_cast<StateT*>(p.state) + ((sidx * p.num_v_heads + h) * D + row0) * D + col0;
 #pragma unroll
     for (int r = 0; r < R; ++r)
 #pragma unroll
@@ -339,26 +406,30 @@ int resident_ctas(size_t smem, int* out) {
   return QLA_OK;
 }
 
-template <typename T, typename InterT, int R>
+template <typename T, typename InterT, typename StateT, int R>
 int launch_recurrent_rows(const QlaRecurrentArgs& a, cudaStream_t stream) {
   const int64_t items = static_cast<int64_t>(a.num_seqs) * a.num_v_heads * (kHeadDim / (16 * R));
-  constexpr size_t smem = kRecStages * R * 4 * 128 * sizeof(float4);
+  constexpr size_t smem = kRecStages * R * 4 * 128 * sizeof(typename StatePiece<StateT>::Raw);
   int resident = 0;
-  int rc = ensure_dynamic_smem<recurrent_kernel<T, InterT, R>>(smem);
+  int rc = ensure_dynamic_smem<recurrent_kernel<T, InterT, StateT, R>>(smem);
   if (rc != QLA_OK) return rc;
-  rc = resident_ctas<recurrent_kernel<T, InterT, R>>(smem, &resident);
+  rc = resident_ctas<recurrent_kernel<T, InterT, StateT, R>>(smem, &resident);
   if (rc != QLA_OK) return rc;
   // one CTA per item while they all fit at once; otherwise as many CTAs as are resident, each walking the
   // items with stride gridDim.x
   const unsigned grid = static_cast<unsigned>(items < resident ? items : resident);
-  recurrent_kernel<T, InterT, R><<<grid, 128, smem, stream>>>(a, items);
+  recurrent_kernel<T, InterT, StateT, R><<<grid, 128, smem, stream>>>(a, items);
   QLA_CHECK_CUDA(cudaGetLastError());
   return QLA_OK;
 }
 
 template <typename T, typename InterT>
 int launch_recurrent(const QlaRecurrentArgs& a, int rows, cudaStream_t stream) {
-  return rows == 16 ? launch_recurrent_rows<T, InterT, 1>(a, stream) : launch_recurrent_rows<T, InterT, 2>(a, stream);
+  if (a.state_dtype == QLA_DT_BF16)
+    return rows == 16 ? launch_recurrent_rows<T, InterT, __nv_bfloat16, 1>(a, stream)
+                      : launch_recurrent_rows<T, InterT, __nv_bfloat16, 2>(a, stream);
+  return rows == 16 ? launch_recurrent_rows<T, InterT, float, 1>(a, stream)
+                    : launch_recurrent_rows<T, InterT, float, 2>(a, stream);
 }
 
 }  // namespace
@@ -381,7 +452,9 @@ __global__ void __launch_bounds__(256) state_commit_kernel(const QlaStateCommitA
   constexpr int kElems = kHeadDim * kHeadDim;
   const InterT* src = static_cast<const InterT*>(a.inter) +
                       ((islot * a.inter_steps + (acc - 1)) * a.num_v_heads + hv) * static_cast<int64_t>(kElems);
-  float* dst = a.state + (sslot * a.num_v_heads + hv) * static_cast<int64_t>(kElems);
+  const int64_t dst_off = (sslot * a.num_v_heads + hv) * static_cast<int64_t>(kElems);
+  float* dst = static_cast<float*>(a.state) + dst_off;
+  __nv_bfloat16* dst16 = static_cast<__nv_bfloat16*>(a.state) + dst_off;
   for (int i = threadIdx.x * 8; i < kElems; i += 256 * 8) {
     float x[8];
     if (sizeof(InterT) == 4) {
@@ -393,8 +466,14 @@ __global__ void __launch_bounds__(256) state_commit_kernel(const QlaStateCommitA
 #pragma unroll
       for (int j = 0; j < 8; ++j) x[j] = Cvt<InterT>::to_f32(e[j]);
     }
-    *reinterpret_cast<float4*>(dst + i) = make_float4(x[0], x[1], x[2], x[3]);
-    *reinterpret_cast<float4*>(dst + i + 4) = make_float4(x[4], x[5], x[6], x[7]);
+    if (a.state_dtype == QLA_DT_BF16) {
+      const float lo[4] = {x[0], x[1], x[2], x[3]}, hi[4] = {x[4], x[5], x[6], x[7]};
+      store4(dst16 + i, lo);
+      store4(dst16 + i + 4, hi);
+    } else {
+      *reinterpret_cast<float4*>(dst + i) = make_float4(x[0], x[1], x[2], x[3]);
+      *reinterpret_cast<float4*>(dst + i + 4) = make_float4(x[4], x[5], x[6], x[7]);
+    }
   }
 }
 }  // namespace
@@ -410,6 +489,7 @@ extern "C" QLA_API int qla_state_commit(const QlaStateCommitArgs* args, void* st
   QLA_CHECK_ARG(a.inter_slots > 0 && a.inter_steps > 0 && a.state_slots > 0, "extents must be positive");
   QLA_CHECK_SUPPORTED(a.inter_dtype == QLA_DT_F32 || a.inter_dtype == QLA_DT_BF16,
                       "intermediate_states_buffer must be fp32 or bf16");
+  QLA_CHECK_SUPPORTED(a.state_dtype == QLA_DT_F32 || a.state_dtype == QLA_DT_BF16, "the state pool must be fp32 or bf16");
   dim3 grid(a.num_seqs, a.num_v_heads);
   if (a.inter_dtype == QLA_DT_F32) state_commit_kernel<float><<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(a);
   else state_commit_kernel<__nv_bfloat16><<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(a);
@@ -436,6 +516,11 @@ extern "C" QLA_API int qla_recurrent_update(const QlaRecurrentArgs* args, void* 
   QLA_CHECK_SUPPORTED(a.qkv_dtype == QLA_DT_BF16 || a.qkv_dtype == QLA_DT_F16,
                       "q, k, v must be bf16 or fp16");
   QLA_CHECK_ARG(a.state_slots > 0, "state_slots must be positive");
+  QLA_CHECK_SUPPORTED(a.state_dtype == QLA_DT_F32 || a.state_dtype == QLA_DT_BF16,
+                      "initial_state_source must be fp32 or bf16");
+  QLA_CHECK_ARG(a.parents == nullptr || a.parents_steps > 0, "parents_steps (second extent of parents) must be positive");
+  QLA_CHECK_ARG(a.parents == nullptr || a.tokens_per_seq <= a.parents_steps,
+                "retrieve_parent_token has fewer columns than tokens per sequence");
   if (a.inter != nullptr) {
     QLA_CHECK_ARG(a.inter_slots > 0 && a.inter_steps > 0, "inter extents must be positive");
     QLA_CHECK_SUPPORTED(a.inter_dtype == QLA_DT_F32 || a.inter_dtype == QLA_DT_BF16,

@@ -51,7 +51,7 @@ def describe() -> dict:
                for name, (res, args) in _cabi.EXPORTS.items()}
     flags = {n: getattr(_cabi, n) for n in dir(_cabi) if n.startswith(("CHUNK_", "REC_")) and isinstance(getattr(_cabi, n), int)}
     return {
-        "abi_version": 1,
+        "abi_version": 2,
         "library": _cabi.lib_path().name,
         "arch": "sm_100a",
         "stream_argument": "cudaStream_t passed as void*",

@@ -12,6 +12,7 @@ from typing import Optional
 import torch
 
 from . import _cabi
+from .utils import device_status
 
 
 def _state_view(state: torch.Tensor, Hv: int, K: int, V: int) -> torch.Tensor:
@@ -61,7 +62,9 @@ def fused_sigmoid_gating_delta_rule_update(
     b_is_beta: bool = False,
     a_is_log_decay: bool = False,
 ) -> torch.Tensor:
-    """One GDN step per token, state ``[slots, Hv, V, K]`` fp32 updated in place; returns ``o``.
+    """One GDN step per token, state ``[slots, Hv, V, K]`` (fp32, or bf16 as an addition to the reference)
+    updated in place; returns ``o``.  Out-of-range slots, parents or cu_seqlens boundaries never touch memory and
+    are reported through ``check_device_status()``.
 
     ``g = a`` if ``a_is_log_decay`` else ``-exp(A_log) * softplus(a + dt_bias)``; ``beta = b`` if
     ``b_is_beta`` else ``sigmoid(b)``.  Unlike the reference, both flags are honoured on every
@@ -96,8 +99,9 @@ def fused_sigmoid_gating_delta_rule_update(
         A_log, dt_bias = A_log.contiguous(), dt_bias.contiguous()
 
     state = _state_view(initial_state_source, Hv, K, V)
-    if state.dtype != torch.float32:
-        raise NotImplementedError("initial_state_source must be float32")
+    if state.dtype not in (torch.float32, torch.bfloat16):
+        # the reference's pools are float32 (recurrent_fused.py:6292); bfloat16 pools are an addition
+        raise NotImplementedError("initial_state_source must be float32 or bfloat16")
     dev = q.device
     cu = _i32(cu_seqlens, dev)
     sidx = _i32(initial_state_indices, dev)
@@ -148,6 +152,8 @@ def fused_sigmoid_gating_delta_rule_update(
             raise ValueError("retrieve_parent_token requires intermediate_states_buffer")
         if parents.dim() != 2 or parents.shape[0] != N:
             raise ValueError("retrieve_parent_token first dimension must equal num_sequences")
+        if tokens_per_seq > parents.shape[1]:
+            raise ValueError("retrieve_parent_token has fewer columns than tokens per sequence")
 
     o = torch.empty_like(v)
     flags = ((_cabi.REC_QK_L2NORM if use_qk_l2norm_in_kernel else 0)
@@ -170,7 +176,9 @@ def fused_sigmoid_gating_delta_rule_update(
         dt_bias=None if a_is_log_decay else _cabi.ptr(dt_bias),
         q=_cabi.ptr(q), k=_cabi.ptr(k), v=_cabi.ptr(v), b=_cabi.ptr(b), state=_cabi.ptr(state),
         state_indices=_cabi.ptr(sidx), cu_seqlens=_cabi.ptr(cu), inter=_cabi.ptr(inter),
-        inter_indices=_cabi.ptr(cidx), parents=_cabi.ptr(parents), o=_cabi.ptr(o))
+        inter_indices=_cabi.ptr(cidx), parents=_cabi.ptr(parents), o=_cabi.ptr(o),
+        status=_cabi.ptr(device_status(dev)), state_dtype=_cabi.dtype_code(state.dtype),
+        parents_steps=0 if parents is None else parents.shape[1])
     with torch.cuda.device(dev):
         code = _cabi.lib().qla_recurrent_update(args, _cabi.current_stream(dev))
     _cabi.check(code, "qla_recurrent_update")
@@ -198,20 +206,19 @@ def commit_verified_state(
     Hv = inter.shape[2]
     if not state.is_contiguous() or not inter.is_contiguous():
         raise ValueError("the state pool and intermediate_states_buffer must be contiguous")
-    if state.dtype != torch.float32 or state.numel() % (Hv * 128 * 128) != 0:
-        raise ValueError("initial_state_source must be a float32 pool of [HV, 128, 128] states")
+    if state.dtype not in (torch.float32, torch.bfloat16) or state.numel() % (Hv * 128 * 128) != 0:
+        raise ValueError("initial_state_source must be a float32 or bfloat16 pool of [HV, 128, 128] states")
     if inter.dtype not in (torch.float32, torch.bfloat16):
         raise NotImplementedError("intermediate_states_buffer must be float32 or bfloat16")
     dev = state.device
     acc = _i32(num_accepted, dev)
     sidx = _i32(initial_state_indices, dev)
     cidx = _i32(intermediate_state_indices, dev)
-    from .utils import device_status
     args = _cabi.QlaStateCommitArgs(
         num_seqs=acc.numel(), num_v_heads=Hv, inter_dtype=_cabi.dtype_code(inter.dtype), inter_steps=inter.shape[1],
         inter_slots=inter.shape[0], state_slots=state.numel() // (Hv * 128 * 128), inter=_cabi.ptr(inter),
         accepted=_cabi.ptr(acc), state_indices=_cabi.ptr(sidx), inter_indices=_cabi.ptr(cidx),
-        state=_cabi.ptr(state), status=_cabi.ptr(device_status(dev)))
+        state=_cabi.ptr(state), status=_cabi.ptr(device_status(dev)), state_dtype=_cabi.dtype_code(state.dtype))
     with torch.cuda.device(dev):
         code = _cabi.lib().qla_state_commit(args, _cabi.current_stream(dev))
     _cabi.check(code, "qla_state_commit")

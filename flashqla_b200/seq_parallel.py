@@ -31,7 +31,7 @@ from typing import Callable, Dict, Optional, Tuple
 import torch
 
 from . import _cabi, cp
-from .chunk import CHUNK, _launch_fwd, new_w
+from .chunk import CHUNK, _launch_fwd, chunk_tables_workspace, new_w
 
 _SP_PLANS: Dict[Tuple, "SpPlan"] = {}
 
@@ -60,7 +60,7 @@ def _sp_plan(tokens: int, num_v_heads: int, device: torch.device) -> SpPlan:
             identity=i32(list(range(n_seg))),
             raw_first=i32([0, n_seg + 1]),
             # the main scan writes the state behind the last segment into row 0 of its final-state output
-            seg_raw=i32([-1] * (n_seg - 1) + [0])), {})
+            seg_raw=i32([-1] * (n_seg - 1) + [0])), chunk_tables_workspace(cu, device))
         if len(_SP_PLANS) < 256:
             _SP_PLANS[key] = plan
     return plan

@@ -23,7 +23,7 @@
 extern "C" {
 #endif
 
-#define QLA_ABI_VERSION 1
+#define QLA_ABI_VERSION 2
 
 #if defined(QLA_BUILDING_LIB)
 #define QLA_API __attribute__((visibility("default")))
@@ -55,7 +55,10 @@ enum { /* flags of QlaRecurrentArgs */
  *   flash_qla/ops/gated_delta_rule/recurrent_fused.py:6287-7534 (dispatcher) and the kernels
  *   :290-487 (ragged), :4003-4256 (decode), :5656-5944 (verify), :5952-6249 (tree verify).
  * Layouts (all contiguous): q,k [NT,Hk,128]; v,o [NT,Hv,128]; a,b [NT,Hv]; A_log,dt_bias [Hv];
- * state [slots,Hv,128(V),128(K)] fp32, updated in place; inter [slots,inter_steps,Hv,128,128].
+ * state [slots,Hv,128(V),128(K)] fp32 or bf16 (state_dtype), updated in place;
+ * inter [slots,inter_steps,Hv,128,128].  Index tensors are checked on the device: a slot outside its pool,
+ * cu_seqlens boundaries outside [0, total_tokens] or a parent outside the cached steps never touch memory
+ * (the sequence is treated as padding / the access is skipped) and raise the status word.
  */
 typedef struct QlaRecurrentArgs {
   int32_t num_seqs;        /* N                                                              */
@@ -89,8 +92,11 @@ typedef struct QlaRecurrentArgs {
   const int32_t* cu_seqlens;    /* [N+1] or NULL                                             */
   void* inter;                  /* intermediate_states_buffer or NULL                        */
   const int32_t* inter_indices; /* [N] or NULL (identity)                                    */
-  const int32_t* parents;       /* retrieve_parent_token [N,steps] or NULL                   */
+  const int32_t* parents;       /* retrieve_parent_token [N,parents_steps] or NULL           */
   void* o;
+  int32_t* status;              /* device int32 status word or NULL (see qla_chunk_fwd)      */
+  int32_t state_dtype;          /* QLA_DT_F32 | QLA_DT_BF16: element type of the state pool  */
+  int32_t parents_steps;        /* second extent of parents (0 when parents == NULL)         */
 } QlaRecurrentArgs;
 
 QLA_API int qla_recurrent_update(const QlaRecurrentArgs* args, void* stream);
@@ -112,8 +118,10 @@ typedef struct QlaStateCommitArgs {
   const int32_t* accepted; /* [N] number of accepted tokens, 0 .. inter_steps                 */
   const int32_t* state_indices; /* [N] or NULL (identity)                                     */
   const int32_t* inter_indices; /* [N] or NULL (identity)                                     */
-  float* state;            /* [state_slots, Hv, 128, 128] fp32, updated in place              */
+  void* state;             /* [state_slots, Hv, 128, 128] fp32 or bf16, updated in place      */
   int32_t* status;         /* device int32 status word or NULL                                */
+  int32_t state_dtype;     /* QLA_DT_F32 | QLA_DT_BF16                                        */
+  int32_t reserved;
 } QlaStateCommitArgs;
 
 QLA_API int qla_state_commit(const QlaStateCommitArgs* args, void* stream);
@@ -207,8 +215,10 @@ QLA_API int qla_chunk_fwd(const QlaChunkFwdArgs* args, void* stream);
  * workspace live in a fixed device array inside the library (about 32 KiB per GPU, kept until exit).
  * args->workspace / workspace_bytes are ignored.  Calls with cu_seqlens and more than
  * QLA_NOALLOC_MAX_SEQS sequences are rejected with QLA_ERR_INVALID_ARG.  All calls on one GPU share the
- * array: calls that can overlap on the GPU race.  The first call on each GPU resolves the array's device
- * address and should be made before any stream capture.  No cudaMalloc / cudaFree inside.
+ * array: calls that can overlap on the GPU race.  QLA_CHUNK_TABLES_READY has no meaning with a shared
+ * array (another call may have rewritten it) and is ignored: every call recomputes the tables.  The first
+ * call on each GPU resolves the array's device address and sets the kernels' shared-memory attribute
+ * (cudaFuncSetAttribute), so it should be made before any stream capture.  No cudaMalloc / cudaFree inside.
  */
 #define QLA_NOALLOC_MAX_SEQS 4096
 QLA_API int qla_chunk_fwd_noalloc(const QlaChunkFwdArgs* args, void* stream);

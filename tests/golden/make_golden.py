@@ -1,6 +1,6 @@
 """Generate the golden fixtures in this directory from the reference's own CPU code.
 
-Run once, in a container that has the reference checkout (it cannot travel to the GPU box):
+Run once, where a checkout of the reference is at hand (the tests only need the stored fixtures):
 
     python tests/golden/make_golden.py /path/to/FlashQLA
 

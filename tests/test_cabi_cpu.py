@@ -18,7 +18,7 @@ def built_lib():
 def test_library_builds_and_loads(built_lib):
     from flashqla_b200 import _cabi
     lib = _cabi.lib()
-    assert lib.qla_abi_version() == 1
+    assert lib.qla_abi_version() == 2
     assert lib.qla_status_string(0) == b"ok"
     assert lib.qla_status_string(-1) == b"invalid argument"
 

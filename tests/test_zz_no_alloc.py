@@ -4,8 +4,9 @@
 cudaMalloc on the request path (for instance a serving process whose pools fill the card); it keeps the
 chunk tables of packed (cu_seqlens) batches in a fixed array inside the library.  The test drives it
 through the C ABI with ctypes on two consecutive calls and compares with `qla_chunk_fwd` (bitwise: both
-run the same kernels on the same inputs).  Collected last on purpose: a run that stops at the first
-failure has then already executed every other test.
+run the same kernels on the same inputs).  A call with a different number of sequences runs in between,
+so the second call finds another batch's tables in the shared array, and the device's free memory is
+compared before and after to see that nothing was allocated.
 """
 import ctypes as C
 
@@ -54,15 +55,34 @@ def test_noalloc_forward_matches_regular_entry_point():
     a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
     assert lib.qla_chunk_fwd(a, stream) == 0, lib.qla_last_error()
 
-    # the entry point under test, twice in a row (the second call reuses the shared array)
+    # another packed batch (different number of sequences, so its tables sit at other offsets of the array)
+    lens2 = [70, 500]
+    cu2 = torch.tensor([0, 70, 570], dtype=torch.int32, device="cuda")
+    inp2 = orc.make_prefill_inputs(1, sum(lens2), 2, 4, seed=78, with_h0=True, n_states=len(lens2))
+    t2 = {n: x.cuda() for n, x in inp2.items()}
+    out2 = _outputs(t2, len(lens2))
+
+    # the entry point under test, twice in a row (the second call reuses the shared array, which the call
+    # in between has overwritten); the flag that would skip the table launch must not be honoured
+    outs = [_outputs(t, len(lens)) for _ in range(2)]
+    torch.cuda.synchronize()
+    free_before, allocated_before = torch.cuda.mem_get_info()[0], torch.cuda.memory_allocated()
     for call in range(2):
-        got = _outputs(t, len(lens))
+        got = outs[call]
         b = _args(_cabi, t, got, cu, len(lens), status)
+        if call == 1:
+            b.flags |= _cabi.CHUNK_TABLES_READY
         assert lib.qla_chunk_fwd_noalloc(b, stream) == 0, lib.qla_last_error()
+        if call == 0:
+            assert lib.qla_chunk_fwd_noalloc(_args(_cabi, t2, out2, cu2, len(lens2), status), stream) == 0
         torch.cuda.synchronize()
         assert int(status.item()) == 0
         for name in ref:
             assert torch.equal(got[name], ref[name]), f"call {call}: {name} differs"
+    assert torch.cuda.memory_allocated() == allocated_before
+    assert torch.cuda.mem_get_info()[0] >= free_before, "device memory was allocated during the calls"
+    ref2 = orc.chunk_gdr_fwd_varlen(inp2["q"], inp2["k"], inp2["v"], inp2["g"], inp2["beta"], cu2.cpu(), h0=inp2["h0"])
+    assert orc.rel_rms(out2["o"].float().cpu(), ref2["o"]) <= 5e-3
     # and against the oracle, with the tolerance of the forward tests
     o_ref = orc.chunk_gdr_fwd_varlen(inp["q"], inp["k"], inp["v"], inp["g"], inp["beta"], cu.cpu(), h0=inp["h0"])
     assert orc.rel_rms(got["o"].float().cpu(), o_ref["o"]) <= 5e-3
