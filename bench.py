@@ -357,7 +357,7 @@ def run_recurrent(args, rank, world, device, verify: bool):
         return fq.fused_sigmoid_gating_delta_rule_update(
             None, g, None, q, k, v, beta, pools[calls[0] % copies], use_qk_l2norm_in_kernel=False,
             a_is_log_decay=True, b_is_beta=True, assume_regular=True, disable_state_update=verify,
-            intermediate_states_buffer=inter)
+            intermediate_states_buffer=inter, block_dv=args.block_dv)
 
     with ClockSampler(device.index or 0) as cs:
         ms = timed(step, args.steps, args.warmup, world, device)
@@ -451,6 +451,7 @@ def main():
     ap.add_argument("--workload", default="prefill_fwd", choices=["prefill_fwd", "prefill_sp", "varlen", "decode", "verify", "train"])
     ap.add_argument("--tokens", type=int, default=32768)
     ap.add_argument("--bf16-scratch", action="store_true")
+    ap.add_argument("--block-dv", type=int, default=None, help="recurrent workloads: rows of V per CTA (16 or 32)")
     ap.add_argument("--cpu-sample-tokens", type=int, default=32768)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--eager", action="store_true", help="time plain calls instead of CUDA-graph replays")

@@ -141,7 +141,7 @@ BwdWorkspace bwd_workspace(const QlaChunkBwdArgs& a) {
   w.chunks_upper = varlen ? static_cast<int>(nt / kChunk + a.num_seqs) : a.batch * ((a.seq_len + kChunk - 1) / kChunk);
   w.tables = varlen ? 2 * table_bytes(a.num_seqs) : 0;
   w.dh = ((static_cast<size_t>(w.chunks_upper) * a.num_v_heads * kHeadDim * kHeadDim * 2) + 15) & ~size_t(15);
-  w.du = ((static_cast<size_t>(nt) * a.num_v_heads * kHeadDim * 2) + 15) & ~size_t(15);
+  w.du = ((static_cast<size_t>(w.chunks_upper) * a.num_v_heads * kHeadDim * kChunk * 2) + 15) & ~size_t(15);
   w.total = w.tables + w.dh + w.du;
   return w;
 }
@@ -191,6 +191,6 @@ extern "C" QLA_API int qla_chunk_bwd(const QlaChunkBwdArgs* args, void* stream_)
   p.dq = a.dq; p.dk = a.dk; p.dv = a.dv; p.dbeta = a.dbeta; p.dg = a.dg; p.dh0 = a.dh0;
   p.num_seqs = a.num_seqs; p.seq_len = a.seq_len; p.num_k_heads = a.num_k_heads; p.num_v_heads = a.num_v_heads;
   p.beta_dtype = a.beta_dtype; p.transpose_state = (a.flags & QLA_CHUNK_TRANSPOSE_STATE) ? 1 : 0;
-  p.scale = a.scale;
-  return launch_chunk_bwd(p, w.chunks_upper, a.qkv_dtype == QLA_DT_BF16, stream);
+  p.scale = a.scale; p.status = a.status;
+  return launch_chunk_bwd(p, total_tokens, w.chunks_upper, a.qkv_dtype == QLA_DT_BF16, stream);
 }

@@ -3,17 +3,15 @@
 // math is the decomposed form of tests/ref_gdr.py:263-557 / chunk/blackwell/bwd_sm12x.py (dv_local,
 // reverse state scan, dq/dk/dw/dg, WY backward), regrouped into two kernels:
 //
-//  bwd_scan_kernel   one CTA per (sequence, v-head), chunks in reverse order, dS (fp32, K x V) resident in
-//                    mma accumulators:   du = Pg^T dO + rho .* (K dS)        (Pg = s G .* Q K^T)
-//                                        x  = A^T du
-//                                        dS <- exp(gL) dS + (s gamma .* Q)^T dO - (beta gamma .* K)^T x
-//                    writes du, the state gradient entering every chunk (dh) and dh0.
+//  bwd_scan_kernel   (chunk_bwd_scan.cu) one CTA per (sequence, v-head), chunks in reverse order, dS resident
+//                    in tensor memory; writes du^T [chunk][Hv][128 v][64 tokens], the state gradient
+//                    leaving every chunk dh^T [chunk][Hv][128 v][128 k] and dh0.
 //  bwd_chunk_kernel  one CTA per (chunk, k-head), looping over the v-heads of the GQA group so that dq and
 //                    dk leave already reduced over the group: every remaining product of the chunk
 //                    (dq, dk, dw, dA, the triangular-inverse backward, dbeta, dg with its chunk-local
 //                    reverse cumulative sum).
 //
-// Both kernels run their many small products (64 x 64 x 128, 64 x 128 x 64, ...) with mma.sync on padded
+// This kernel runs its many small products (64 x 64 x 128, 64 x 128 x 64, ...) with mma.sync on padded
 // shared-memory tiles; rows beyond the end of a sequence are zero-filled on load, which makes every
 // contraction over the chunk dimension ignore them.
 #include "chunk_params.cuh"
@@ -54,213 +52,6 @@ __device__ __forceinline__ ChunkCoord locate_chunk(int chunk, const int32_t* cu,
   return c;
 }
 
-// ============================================================================== reverse scan
-template <typename T>
-__global__ void __launch_bounds__(kBwdThreads, 1) bwd_scan_kernel(const BwdParams p) {
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int g = lane >> 2, c4 = lane & 3;
-  const int hv = blockIdx.x % p.num_v_heads;
-  const int seq = blockIdx.x / p.num_v_heads;
-  const int hk = hv / (p.num_v_heads / p.num_k_heads);
-  int seq_start, seq_end;
-  if (p.cu_seqlens != nullptr) {
-    seq_start = p.cu_seqlens[seq];
-    seq_end = p.cu_seqlens[seq + 1];
-  } else {
-    seq_start = seq * p.seq_len;
-    seq_end = seq_start + p.seq_len;
-  }
-  const int nchunks = (seq_end - seq_start + kChunk - 1) / kChunk;
-  const int64_t chunk_base =
-      p.chunk_offsets ? p.chunk_offsets[seq] : static_cast<int64_t>(seq) * ((p.seq_len + kChunk - 1) / kChunk);
-
-  extern __shared__ __align__(16) uint8_t smem_raw[];
-  T* sK = reinterpret_cast<T*>(smem_raw);           // [2][64][LD]
-  T* sQ = sK + 2 * 64 * LD;                         // [2][64][LD]
-  T* sdO = sQ + 2 * 64 * LD;                        // [2][64][LD]
-  T* sA = sdO + 2 * 64 * LD;                        // [2][64][LS]
-  T* sS = sA + 2 * 64 * LS;                         // [128][LD]  bf16 copy of dS
-  T* sP = sS + 128 * LD;                            // [64][LS]   Pg
-  T* sDu = sP + 64 * LS;                            // [64][LD]   du
-  T* sX = sDu + 64 * LD;                            // [64][LD]   -(beta gamma) .* x
-  float* sG = reinterpret_cast<float*>(sX + 64 * LD);  // [2][64] cumulative gates
-  float* sB = sG + 128;                                // [2][64] beta
-
-  const T* qg = static_cast<const T*>(p.q);
-  const T* kg = static_cast<const T*>(p.k);
-  const T* dog = static_cast<const T*>(p.d_o);
-  const T* ag = static_cast<const T*>(p.A);
-  const int64_t qk_stride = static_cast<int64_t>(p.num_k_heads) * kHeadDim;
-  const int64_t v_stride = static_cast<int64_t>(p.num_v_heads) * kHeadDim;
-  const int64_t a_stride = static_cast<int64_t>(p.num_v_heads) * kChunk;
-
-  auto issue_loads = [&](int chunk, int buf) {
-    const int t0 = seq_start + chunk * kChunk;
-    const int valid = min(kChunk, seq_end - t0);
-    mm::load_tile_async<T, 64, 128, kBwdThreads>(sK + buf * 64 * LD, LD, kg + (static_cast<int64_t>(t0) * p.num_k_heads + hk) * kHeadDim, qk_stride, valid);
-    mm::load_tile_async<T, 64, 128, kBwdThreads>(sQ + buf * 64 * LD, LD, qg + (static_cast<int64_t>(t0) * p.num_k_heads + hk) * kHeadDim, qk_stride, valid);
-    mm::load_tile_async<T, 64, 128, kBwdThreads>(sdO + buf * 64 * LD, LD, dog + (static_cast<int64_t>(t0) * p.num_v_heads + hv) * kHeadDim, v_stride, valid);
-    mm::load_tile_async<T, 64, 64, kBwdThreads>(sA + buf * 64 * LS, LS, ag + (static_cast<int64_t>(t0) * p.num_v_heads + hv) * kChunk, a_stride, valid);
-    if (tid < 64) {
-      const int64_t last = static_cast<int64_t>(t0) + valid - 1;
-      const bool ok = tid < valid;
-      const int64_t tok = ok ? static_cast<int64_t>(t0) + tid : last;
-      sG[buf * 64 + tid] = p.g_cumsum[tok * p.num_v_heads + hv];
-      sB[buf * 64 + tid] = ok ? load_scalar(p.beta, p.beta_dtype, tok * p.num_v_heads + hv) : 0.f;
-    }
-    mm::cp_async_commit();
-  };
-
-  // dS accumulators: warp w owns rows k = 16 w .. 16 w + 15, all 128 columns v
-  float accS[16][4];
-  {
-    const float* dht = p.dht ? p.dht + (static_cast<int64_t>(seq) * p.num_v_heads + hv) * kHeadDim * kHeadDim : nullptr;
-#pragma unroll
-    for (int nt = 0; nt < 16; ++nt)
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int k = warp * 16 + g + (e >> 1) * 8, v = nt * 8 + 2 * c4 + (e & 1);
-        accS[nt][e] = dht ? (p.transpose_state ? dht[v * kHeadDim + k] : dht[k * kHeadDim + v]) : 0.f;
-      }
-  }
-
-  if (nchunks > 0) issue_loads(nchunks - 1, (nchunks - 1) & 1);
-  const int mt = warp & 3, nh = warp >> 2;
-  T* dh_out = static_cast<T*>(p.dh);
-  T* du_out = static_cast<T*>(p.du);
-
-  for (int chunk = nchunks - 1; chunk >= 0; --chunk) {
-    const int buf = chunk & 1;
-    const int t0 = seq_start + chunk * kChunk;
-    const int valid = min(kChunk, seq_end - t0);
-    const T* bK = sK + buf * 64 * LD;
-    T* bQ = sQ + buf * 64 * LD;
-    const T* bdO = sdO + buf * 64 * LD;
-    const T* bA = sA + buf * 64 * LS;
-    const float* gs = sG + buf * 64;
-    const float* bs = sB + buf * 64;
-
-    // bf16 copy of dS for this chunk's K dS product, and dh[chunk] for the per-chunk kernel
-    {
-      T* hp = dh_out + ((chunk_base + chunk) * p.num_v_heads + hv) * kHeadDim * kHeadDim;
-#pragma unroll
-      for (int nt = 0; nt < 16; ++nt) {
-        const int v = nt * 8 + 2 * c4;
-        const uint32_t lo = mm::pack_pair<T>(accS[nt][0], accS[nt][1]);
-        const uint32_t hi = mm::pack_pair<T>(accS[nt][2], accS[nt][3]);
-        *reinterpret_cast<uint32_t*>(sS + (warp * 16 + g) * LD + v) = lo;
-        *reinterpret_cast<uint32_t*>(sS + (warp * 16 + g + 8) * LD + v) = hi;
-        *reinterpret_cast<uint32_t*>(hp + (warp * 16 + g) * kHeadDim + v) = lo;
-        *reinterpret_cast<uint32_t*>(hp + (warp * 16 + g + 8) * kHeadDim + v) = hi;
-      }
-    }
-    if (chunk > 0) issue_loads(chunk - 1, buf ^ 1);
-    if (chunk > 0) mm::cp_async_wait<1>(); else mm::cp_async_wait<0>();
-    __syncthreads();
-
-    const float gl = gs[valid - 1];
-    const float g_r0 = gs[mt * 16 + g], g_r1 = gs[mt * 16 + g + 8];
-
-    // ---- step 1: Pg = s * G .* (Q K^T), rows 16 mt.., columns 32 nh..
-    {
-      float acc[4][4];
-      mm::zero_acc(acc);
-      mm::warp_gemm<T, 4, false, false>(acc, bQ + mt * 16 * LD, LD, bK + nh * 32 * LD, LD, 128);
-#pragma unroll
-      for (int nt = 0; nt < 4; ++nt)
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int row = mt * 16 + g + (e >> 1) * 8, col = nh * 32 + nt * 8 + 2 * c4 + (e & 1);
-          const float gr = (e >> 1) ? g_r1 : g_r0;
-          const float w = p.scale * __expf(fminf(gr - gs[col], 0.f));
-          acc[nt][e] = (col <= row) ? acc[nt][e] * w : 0.f;
-        }
-      mm::store_acc<T, 4>(sP + mt * 16 * LS + nh * 32, LS, acc);
-    }
-    __syncthreads();
-
-    // Q is no longer needed unscaled: scale its rows by s * gamma in place (operand of step 5)
-    for (int i = tid; i < 64 * 16; i += kBwdThreads) {
-      const int r = i >> 4, c8 = (i & 15) * 8;
-      const float f = p.scale * __expf(gs[r]);
-      uint4 raw = *reinterpret_cast<uint4*>(bQ + r * LD + c8);
-      T* e = reinterpret_cast<T*>(&raw);
-#pragma unroll
-      for (int x = 0; x < 8; ++x) e[x] = Cvt<T>::from_f32(Cvt<T>::to_f32(e[x]) * f);
-      *reinterpret_cast<uint4*>(bQ + r * LD + c8) = raw;
-    }
-
-    // ---- steps 2 + 3: du = rho .* (K dS) + Pg^T dO     rows 16 mt.., columns 64 nh..
-    {
-      float acc[8][4];
-      mm::zero_acc(acc);
-      mm::warp_gemm<T, 8, false, true>(acc, bK + mt * 16 * LD, LD, sS + nh * 64, LD, 128);
-      const float rho0 = (mt * 16 + g < valid) ? __expf(gl - g_r0) : 0.f;
-      const float rho1 = (mt * 16 + g + 8 < valid) ? __expf(gl - g_r1) : 0.f;
-#pragma unroll
-      for (int nt = 0; nt < 8; ++nt) {
-        acc[nt][0] *= rho0; acc[nt][1] *= rho0;
-        acc[nt][2] *= rho1; acc[nt][3] *= rho1;
-      }
-      mm::warp_gemm<T, 8, true, true>(acc, sP + mt * 16, LS, bdO + nh * 64, LD, 64);
-      mm::store_acc<T, 8>(sDu + mt * 16 * LD + nh * 64, LD, acc);
-      // du to global (rows of this sequence only)
-#pragma unroll
-      for (int nt = 0; nt < 8; ++nt) {
-        const int col = nh * 64 + nt * 8 + 2 * c4;
-        const int r0 = mt * 16 + g, r1 = r0 + 8;
-        if (r0 < valid)
-          *reinterpret_cast<uint32_t*>(du_out + (static_cast<int64_t>(t0 + r0) * p.num_v_heads + hv) * kHeadDim + col) =
-              mm::pack_pair<T>(acc[nt][0], acc[nt][1]);
-        if (r1 < valid)
-          *reinterpret_cast<uint32_t*>(du_out + (static_cast<int64_t>(t0 + r1) * p.num_v_heads + hv) * kHeadDim + col) =
-              mm::pack_pair<T>(acc[nt][2], acc[nt][3]);
-      }
-    }
-    __syncthreads();
-
-    // ---- step 4: x = A^T du, stored as -(beta gamma) .* x
-    {
-      float acc[8][4];
-      mm::zero_acc(acc);
-      mm::warp_gemm<T, 8, true, true>(acc, bA + mt * 16, LS, sDu + nh * 64, LD, 64);
-      const float f0 = -bs[mt * 16 + g] * __expf(g_r0), f1 = -bs[mt * 16 + g + 8] * __expf(g_r1);
-#pragma unroll
-      for (int nt = 0; nt < 8; ++nt) {
-        acc[nt][0] *= f0; acc[nt][1] *= f0;
-        acc[nt][2] *= f1; acc[nt][3] *= f1;
-      }
-      mm::store_acc<T, 8>(sX + mt * 16 * LD + nh * 64, LD, acc);
-    }
-    __syncthreads();
-
-    // ---- step 5: dS <- exp(gL) dS + (s gamma .* Q)^T dO + K^T (-(beta gamma) .* x)
-    {
-      const float egl = __expf(gl);
-#pragma unroll
-      for (int nt = 0; nt < 16; ++nt)
-#pragma unroll
-        for (int e = 0; e < 4; ++e) accS[nt][e] *= egl;
-      mm::warp_gemm<T, 16, true, true>(accS, bQ + warp * 16, LD, bdO, LD, 64);
-      mm::warp_gemm<T, 16, true, true>(accS, bK + warp * 16, LD, sX, LD, 64);
-    }
-    __syncthreads();  // the tiles of this buffer and sS / sDu / sX are rewritten next iteration
-  }
-
-  if (p.dh0 != nullptr) {
-    float* out = p.dh0 + (static_cast<int64_t>(seq) * p.num_v_heads + hv) * kHeadDim * kHeadDim;
-#pragma unroll
-    for (int nt = 0; nt < 16; ++nt)
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int k = warp * 16 + g + (e >> 1) * 8, v = nt * 8 + 2 * c4 + (e & 1);
-        if (p.transpose_state) out[v * kHeadDim + k] = accS[nt][e]; else out[k * kHeadDim + v] = accS[nt][e];
-      }
-  }
-}
-
-constexpr size_t kScanSmem = (2 * 3 * 64 * LD + 2 * 64 * LS + 128 * LD + 64 * LS + 2 * 64 * LD) * 2 + 2 * 128 * sizeof(float);
-
 // ============================================================================== per-chunk kernel
 // Row sums over the columns a warp owns, reduced over the four lanes that share a row.
 __device__ __forceinline__ float quad_sum(float x) {
@@ -295,8 +86,8 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_chunk_kernel(const BwdPara
   T* sV = sK + 64 * LD;
   T* sVn = sV + 64 * LD;
   T* sdO = sVn + 64 * LD;
-  T* sDu = sdO + 64 * LD;
-  T* sDw = sDu + 64 * LD;
+  T* sDu = sdO + 64 * LD;       // du^T [128 v][LS]
+  T* sDw = sDu + 128 * LS;
   T* sA = sDw + 64 * LD;        // [64][LS]
   T* sH = sA + 64 * LS;         // [128][LD]
   T* sDh = sH + 128 * LD;       // [128][LD]
@@ -331,7 +122,8 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_chunk_kernel(const BwdPara
       mm::load_tile_async<T, 64, 128, kBwdThreads>(sV, LD, static_cast<const T*>(p.v) + vo, v_stride, valid);
       mm::load_tile_async<T, 64, 128, kBwdThreads>(sVn, LD, static_cast<const T*>(p.v_new) + vo, v_stride, valid);
       mm::load_tile_async<T, 64, 128, kBwdThreads>(sdO, LD, static_cast<const T*>(p.d_o) + vo, v_stride, valid);
-      mm::load_tile_async<T, 64, 128, kBwdThreads>(sDu, LD, static_cast<const T*>(p.du) + vo, v_stride, valid);
+      mm::load_tile_async<T, 128, 64, kBwdThreads>(
+          sDu, LS, static_cast<const T*>(p.du) + (chunk_global * p.num_v_heads + hv) * kHeadDim * kChunk, kChunk, 128);
       mm::load_tile_async<T, 64, 64, kBwdThreads>(sA, LS, static_cast<const T*>(p.A) + (static_cast<int64_t>(t0) * p.num_v_heads + hv) * kChunk, a_stride, valid);
       const int64_t ho = (chunk_global * p.num_v_heads + hv) * kHeadDim * kHeadDim;
       mm::load_tile_async<T, 128, 128, kBwdThreads>(sH, LD, static_cast<const T*>(p.h) + ho, kHeadDim, 128);
@@ -393,7 +185,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_chunk_kernel(const BwdPara
         for (int e = 0; e < 4; ++e) dq_acc[nt][e] += acc[nt][e];
       // dk += rho .* (v_new dh^T);  dg -= k . that;  dg_last += sum of the same
       mm::zero_acc(acc);
-      mm::warp_gemm<T, 8, false, false>(acc, sVn + mt * 16 * LD, LD, sDh + nh * 64 * LD, LD, 128);
+      mm::warp_gemm<T, 8, false, true>(acc, sVn + mt * 16 * LD, LD, sDh + nh * 64, LD, 128);  // dh stored [v][k]
 #pragma unroll
       for (int nt = 0; nt < 8; ++nt) { acc[nt][0] *= rho0; acc[nt][1] *= rho0; acc[nt][2] *= rho1; acc[nt][3] *= rho1; }
       dot_rows(acc, sK, s0, s1);
@@ -405,7 +197,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_chunk_kernel(const BwdPara
         for (int e = 0; e < 4; ++e) dk_acc[nt][e] += acc[nt][e];
       // dw = -du h^T
       mm::zero_acc(acc);
-      mm::warp_gemm<T, 8, false, false>(acc, sDu + mt * 16 * LD, LD, sH + nh * 64 * LD, LD, 128);
+      mm::warp_gemm<T, 8, true, false>(acc, sDu + mt * 16, LS, sH + nh * 64 * LD, LD, 128);
 #pragma unroll
       for (int nt = 0; nt < 8; ++nt)
 #pragma unroll
@@ -416,10 +208,9 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_chunk_kernel(const BwdPara
       for (int i = tid; i < 128 * 64; i += kBwdThreads) {
         const int r = i >> 6, c2 = (i & 63) * 2;
         const uint32_t a = *reinterpret_cast<const uint32_t*>(sH + r * LD + c2);
-        const uint32_t b = *reinterpret_cast<const uint32_t*>(sDh + r * LD + c2);
         const T* ea = reinterpret_cast<const T*>(&a);
-        const T* eb = reinterpret_cast<const T*>(&b);
-        hd += Cvt<T>::to_f32(ea[0]) * Cvt<T>::to_f32(eb[0]) + Cvt<T>::to_f32(ea[1]) * Cvt<T>::to_f32(eb[1]);
+        hd += Cvt<T>::to_f32(ea[0]) * Cvt<T>::to_f32(sDh[c2 * LD + r]) +
+              Cvt<T>::to_f32(ea[1]) * Cvt<T>::to_f32(sDh[(c2 + 1) * LD + r]);
       }
       dg_last += __expf(gl) * hd;
     }
@@ -460,7 +251,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_chunk_kernel(const BwdPara
       mm::zero_acc(a1);
       mm::zero_acc(a2);
       mm::warp_gemm<T, 4, false, false>(a1, sDw + mt * 16 * LD, LD, sK + nh * 32 * LD, LD, 128);
-      mm::warp_gemm<T, 4, false, false>(a2, sDu + mt * 16 * LD, LD, sV + nh * 32 * LD, LD, 128);
+      mm::warp_gemm<T, 4, true, false>(a2, sDu + mt * 16, LS, sV + nh * 32 * LD, LD, 128);
 #pragma unroll
       for (int nt = 0; nt < 4; ++nt)
 #pragma unroll
@@ -489,7 +280,7 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_chunk_kernel(const BwdPara
       }
       // x = A^T du: dv = beta .* x ; dbeta += x . v
       mm::zero_acc(acc);
-      mm::warp_gemm<T, 8, true, true>(acc, sA + mt * 16, LS, sDu + nh * 64, LD, 64);
+      mm::warp_gemm<T, 8, true, false>(acc, sA + mt * 16, LS, sDu + nh * 64 * LS, LS, 64);
       dot_rows(acc, sV, s0, s1);
       db_row[0] += s0; db_row[1] += s1;
       T* dvg = static_cast<T*>(p.dv);
@@ -640,23 +431,22 @@ __global__ void __launch_bounds__(kBwdThreads, 1) bwd_chunk_kernel(const BwdPara
   }
 }
 
-constexpr size_t kChunkSmem = (7 * 64 * LD + 64 * LS + 2 * 128 * LD) * 2 + (64 + 64 + 256 + 8) * sizeof(float);
+constexpr size_t kChunkSmem = (6 * 64 * LD + 128 * LS + 64 * LS + 2 * 128 * LD) * 2 + (64 + 64 + 256 + 8) * sizeof(float);
 
 }  // namespace
 
-int launch_chunk_bwd(const BwdParams& p, int total_chunks_upper, bool is_bf16, cudaStream_t stream) {
-  const unsigned scan_grid = static_cast<unsigned>(p.num_seqs) * p.num_v_heads;
+int launch_chunk_bwd(const BwdParams& p, int64_t total_tokens, int total_chunks_upper, bool is_bf16,
+                     cudaStream_t stream) {
+  int rc = launch_bwd_scan(p, total_tokens, is_bf16, stream);
+  if (rc != QLA_OK) return rc;
   dim3 chunk_grid(total_chunks_upper, p.num_k_heads);
-#define QLA_LAUNCH_BWD(T)                                                                                  \
-  do {                                                                                                     \
-    { const int rc_ = ensure_dynamic_smem<bwd_scan_kernel<T>>(kScanSmem); if (rc_ != QLA_OK) return rc_; }       \
-    { const int rc_ = ensure_dynamic_smem<bwd_chunk_kernel<T>>(kChunkSmem); if (rc_ != QLA_OK) return rc_; }     \
-    bwd_scan_kernel<T><<<scan_grid, kBwdThreads, kScanSmem, stream>>>(p);                                  \
-    QLA_CHECK_CUDA(cudaGetLastError());                                                                    \
-    bwd_chunk_kernel<T><<<chunk_grid, kBwdThreads, kChunkSmem, stream>>>(p);                               \
-  } while (0)
-  if (is_bf16) QLA_LAUNCH_BWD(__nv_bfloat16); else QLA_LAUNCH_BWD(__half);
-#undef QLA_LAUNCH_BWD
+  if (is_bf16) {
+    if ((rc = ensure_dynamic_smem<bwd_chunk_kernel<__nv_bfloat16>>(kChunkSmem)) != QLA_OK) return rc;
+    bwd_chunk_kernel<__nv_bfloat16><<<chunk_grid, kBwdThreads, kChunkSmem, stream>>>(p);
+  } else {
+    if ((rc = ensure_dynamic_smem<bwd_chunk_kernel<__half>>(kChunkSmem)) != QLA_OK) return rc;
+    bwd_chunk_kernel<__half><<<chunk_grid, kBwdThreads, kChunkSmem, stream>>>(p);
+  }
   QLA_CHECK_CUDA(cudaGetLastError());
   return QLA_OK;
 }

@@ -1,0 +1,545 @@
+// Chunked gated-delta-rule backward, part 1: the reverse scan over the chunks of one (sequence, v-head)
+// with the gradient of the recurrent state resident in tensor memory.
+// Reference: the reverse loop of fused_gdr_bwd (flash_qla/ops/gated_delta_rule/chunk/hopper/fused_bwd.py:287-361:
+// dS update; :388-432: du and the product with A^T); math as in tests/ref_gdr.py:263-557.
+//
+// Per chunk, walking from the last chunk to the first (dS1 = gradient of the state leaving the chunk):
+//   du  = Pg^T dO + rho .* (K dS1)                      Pg = s G .* (Q K^T), G[c,d] = exp(g_c - g_d), c >= d
+//   X   = -(beta gamma) .* (A^T du)
+//   dS0 = exp(gL) dS1 + (s gamma .* Q)^T dO + K^T X      -> dS1 of the chunk before; the last one is dh0
+// du and the bf16 copy of every dS1 ("dh") go to the workspace the per-chunk kernel reads.
+//
+// The kernel mirrors the forward scan (chunk_fwd.cu): everything is computed TRANSPOSED so that each
+// tcgen05.mma has M = 128 (the V dimension on the 128 TMEM lanes) and dependent operands stay in tensor memory:
+//   MMA0  D0[128,64]  = [K;Q] K^T            (SS)  rows 64..127 are P = Q K^T; state independent
+//   MMAu  Du0[128,64] = dO^T Pg              (SS)  A = dO tile read MN-major, B = Pg tile read MN-major
+//   MMA2  D2[128,64]  = dS1^T_bf16 K^T       (TS)  chain
+//   MMAx  Dx[128,64]  = du^T_bf16 (A diag(-beta gamma))      (TS, B = A tile read MN-major)  chain
+//   MMAq  dS^T[128,128] += dO^T (s gamma .* Q)              (SS, both operands MN-major)  off the chain
+//   MMA3  dS^T[128,128] += X^T_bf16 K                      (TS, B = K tile read MN-major)  chain
+// Thread v of a compute warpgroup owns TMEM lane v (column v of dS): it forms du = Du0 + rho .* D2, writes
+// the 16-bit operand of the next product back with tcgen05.st and its 128 bytes of du^T to the workspace.
+// Warp roles (384 threads): warps 0-7 compute (both warpgroups take half of the token columns of every
+// chain phase and half of the state columns of the state conversion), warp 8 TMA producer + gate vectors,
+// warp 9 MMA issuer, warps 10-11 operand tiles (A diag(-beta gamma) in place, Pg, s gamma .* Q in place).
+// Every wait is a bounded mbarrier wait that raises the status word instead of hanging.
+#include "chunk_params.cuh"
+
+namespace qla {
+namespace {
+
+// ---- tensor-memory column map (512 columns)
+constexpr uint32_t kColS = 0;       // fp32 dS^T, 128 columns
+constexpr uint32_t kColSbf = 128;   // 16-bit copy of dS^T (A operand of MMA2), 64 columns
+constexpr uint32_t kColD2 = 192;    // (K dS1)^T
+constexpr uint32_t kColDu0 = 256;   // (Pg^T dO)^T; the same columns hold Dx once du has been formed
+constexpr uint32_t kColDu16 = 320;  // 16-bit du^T (A operand of MMAx), 32 columns
+constexpr uint32_t kColX16 = 352;   // 16-bit X^T (A operand of MMA3), 32 columns
+constexpr uint32_t kColD0 = 384;    // [K;Q] K^T, two buffers of 64 columns (chunk parity)
+
+// ---- shared-memory map (offsets from a 1024-byte aligned base)
+constexpr uint32_t kStageKQ = 0;         // 32 KiB: half h (columns 64h..) = [K rows 8 KiB | Q rows 8 KiB]; SW128
+constexpr uint32_t kStageDO = 32768;     // 16 KiB: dO tile as two [64][64] halves, SW128
+constexpr uint32_t kStageA = 49152;      // 8 KiB: A tile [64][64], SW128; columns scaled in place
+constexpr uint32_t kStageBytes = 57344;  // 56 KiB
+constexpr uint32_t kOffPg = 2 * kStageBytes;  // 2 x 8 KiB Pg tiles [c][d], SW128 (chunk parity)
+constexpr uint32_t kSmemBytes = kOffPg + 2 * 8192 + 1024;
+
+struct alignas(16) Gates {
+  float g2[64];    // g log2(e)
+  float rho[64];   // exp(gL - g), 0 on padded rows
+  float sgam[64];  // scale * exp(g), 0 on padded rows
+  float nbg[64];   // -beta * exp(g), 0 on padded rows
+  float egl;
+  int valid;
+  int pad[2];
+};
+constexpr int kGateRing = 4;
+
+enum Bar {
+  kFull0 = 0, kFull1, kEmpty0, kEmpty1, kPDone0, kPDone1, kAbReady0, kAbReady1,
+  kPgReady, kQsReady, kD2Done, kDu0Done, kDuReady, kDxDone, kXReady, kSDone, kSbfReady, kSScaled,
+  kNumBars
+};
+constexpr int kThreads = 384;
+
+__device__ __forceinline__ void warp_arrive(uint64_t* bar, int lane) {
+  __syncwarp();
+  if (lane == 0) ptx::mbar_arrive(bar);
+}
+
+template <typename T>
+__device__ __forceinline__ uint32_t pack2(float a, float b);
+template <>
+__device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, float b) {
+  __nv_bfloat162 x = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&x);
+}
+template <>
+__device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
+  __half2 x = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&x);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads, 1)
+bwd_scan_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                const __grid_constant__ CUtensorMap tm_do, const __grid_constant__ CUtensorMap tm_a,
+                const BwdParams p) {
+  constexpr uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? ptx::kFmtBF16 : ptx::kFmtF16;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int hv = blockIdx.x % p.num_v_heads;
+  const int seq = blockIdx.x / p.num_v_heads;
+  const int hk = hv / (p.num_v_heads / p.num_k_heads);
+  int seq_start, seq_end;
+  if (p.cu_seqlens != nullptr) {
+    seq_start = p.cu_seqlens[seq];
+    seq_end = p.cu_seqlens[seq + 1];
+  } else {
+    seq_start = seq * p.seq_len;
+    seq_end = seq_start + p.seq_len;
+  }
+  const int nproc = (seq_end - seq_start + kChunk - 1) / kChunk;  // iteration i handles chunk nproc - 1 - i
+  const int64_t chunk_base =
+      p.chunk_offsets ? p.chunk_offsets[seq] : static_cast<int64_t>(seq) * ((p.seq_len + kChunk - 1) / kChunk);
+
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = smem_raw + ((1024u - (ptx::smem_u32(smem_raw) & 1023u)) & 1023u);
+  __shared__ uint64_t bars[kNumBars];
+  __shared__ uint32_t tmem_base_s;
+  __shared__ __align__(16) float aux_g[2 * 2 * 64];  // [aux warp][chunk parity][64] cumulative gates (log2 domain)
+  __shared__ Gates gate_ring[kGateRing];
+
+  if (tid == 0) {
+#pragma unroll 1
+    for (int b = 0; b < kNumBars; ++b) {
+      int count = 1;  // commits: kPDone*, kD2Done, kDu0Done, kDxDone, kSDone
+      if (b == kFull0 || b == kFull1) count = 33;
+      else if (b == kEmpty0 || b == kEmpty1) count = 3;
+      else if (b == kAbReady0 || b == kAbReady1 || b == kPgReady || b == kQsReady) count = 2;
+      else if (b == kDuReady || b == kXReady || b == kSbfReady || b == kSScaled) count = 8;
+      ptx::mbar_init(&bars[b], count);
+    }
+    ptx::fence_mbar_init();
+  }
+  if (warp == 8) {
+    ptx::tmem_alloc(&tmem_base_s, 512);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  ptx::tc_fence_after_sync();
+  const uint32_t tmem = tmem_base_s;
+  int* status = p.status;
+  auto wait = [&](int b, uint32_t parity) {
+    return ptx::mbar_wait_warp_call(&bars[b], parity, status, kStatusBarrierTimeout | ((b + 64) << 8));  // + 64: the backward scan
+  };
+  auto stage_ptr = [&](int s) { return smem + s * kStageBytes; };
+  auto gates_of = [&](int i) { return &gate_ring[i & (kGateRing - 1)]; };
+  auto chunk_of = [&](int i) { return nproc - 1 - i; };
+
+  if (warp == 8) {
+    // =========================================================== producer: TMA + gate vectors
+    constexpr int kPrefetchAhead = 4;
+    for (int i = 2 - kPrefetchAhead; i < nproc; ++i) {
+      if (lane == 0 && i + kPrefetchAhead < nproc) {
+        const int pt0 = seq_start + chunk_of(i + kPrefetchAhead) * kChunk;
+#pragma unroll 1
+        for (int x = 0; x < 128; x += 64) {
+          ptx::tma_prefetch_l2_3d(&tm_k, x, hk, pt0);
+          ptx::tma_prefetch_l2_3d(&tm_q, x, hk, pt0);
+          ptx::tma_prefetch_l2_3d(&tm_do, x, hv, pt0);
+        }
+        ptx::tma_prefetch_l2_3d(&tm_a, 0, hv, pt0);
+      }
+      if (i < 0) continue;
+      const int s = i & 1, use = i >> 1;
+      const int t0 = seq_start + chunk_of(i) * kChunk;
+      const int valid = min(kChunk, seq_end - t0);
+      const int64_t last_tok = static_cast<int64_t>(t0) + valid - 1;
+      const float gl = p.g_cumsum[last_tok * p.num_v_heads + hv];
+      float gcv[2], bcv[2];
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        const int c = lane + 32 * r;
+        const bool okc = c < valid;
+        const int64_t tok = static_cast<int64_t>(t0) + c;
+        gcv[r] = okc ? p.g_cumsum[tok * p.num_v_heads + hv] : gl;
+        bcv[r] = okc ? load_scalar(p.beta, p.beta_dtype, tok * p.num_v_heads + hv) : 0.f;
+      }
+      if (use > 0 && !wait(kEmpty0 + s, (use - 1) & 1)) break;
+      uint8_t* st = stage_ptr(s);
+      if (lane == 0) {
+        uint64_t* full = &bars[kFull0 + s];
+        ptx::mbar_expect_tx(full, kStageBytes);
+#pragma unroll 1
+        for (int h = 0; h < 2; ++h) {
+          ptx::tma_load_3d(st + kStageKQ + h * 16384, &tm_k, full, h * 64, hk, t0);
+          ptx::tma_load_3d(st + kStageKQ + h * 16384 + 8192, &tm_q, full, h * 64, hk, t0);
+          ptx::tma_load_3d(st + kStageDO + h * 8192, &tm_do, full, h * 64, hv, t0);
+        }
+        ptx::tma_load_3d(st + kStageA, &tm_a, full, 0, hv, t0);
+      }
+      Gates* gs = gates_of(i);
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        const int c = lane + 32 * r;
+        const bool ok = c < valid;
+        const float gc = gcv[r];
+        const float eg = __expf(gc);
+        gs->g2[c] = gc * 1.4426950408889634f;
+        gs->rho[c] = ok ? __expf(gl - gc) : 0.f;
+        gs->sgam[c] = ok ? p.scale * eg : 0.f;
+        gs->nbg[c] = -bcv[r] * eg;  // beta = 0 on padded rows
+      }
+      if (lane == 0) {
+        gs->egl = __expf(gl);
+        gs->valid = valid;
+      }
+      ptx::mbar_arrive(&bars[kFull0 + s]);
+    }
+  } else if (warp == 9) {
+    // =========================================================== MMA issuer (whole warp, converged)
+    const uint32_t id_n64 = ptx::mma_idesc(128, 64, fmt, ptx::kMajorK, ptx::kMajorK);        // MMA0, MMA2
+    const uint32_t id_u = ptx::mma_idesc(128, 64, fmt, ptx::kMajorMN, ptx::kMajorMN);       // MMAu
+    const uint32_t id_x = ptx::mma_idesc(128, 64, fmt, ptx::kMajorK, ptx::kMajorMN);        // MMAx
+    const uint32_t id_s = ptx::mma_idesc(128, 128, fmt, ptx::kMajorK, ptx::kMajorMN);       // MMA3
+    const uint32_t id_q = ptx::mma_idesc(128, 128, fmt, ptx::kMajorMN, ptx::kMajorMN);      // MMAq
+    // descriptors of stage 0; stage 1 is kStageBytes further
+    const uint64_t d_kq = ptx::smem_desc_sw128(ptx::smem_u32(smem + kStageKQ), 16, 1024);           // [K;Q] 128 rows, K-major
+    const uint64_t d_kmn = ptx::smem_desc_sw128(ptx::smem_u32(smem + kStageKQ), 16384, 1024);       // K rows, MN-major
+    const uint64_t d_qmn = ptx::smem_desc_sw128(ptx::smem_u32(smem + kStageKQ + 8192), 16384, 1024);  // Q rows, MN-major
+    const uint64_t d_do = ptx::smem_desc_sw128(ptx::smem_u32(smem + kStageDO), 8192, 1024);         // dO, MN-major
+    const uint64_t d_a = ptx::smem_desc_sw128(ptx::smem_u32(smem + kStageA), 8192, 1024);           // A tile, MN-major
+    const uint64_t d_pg = ptx::smem_desc_sw128(ptx::smem_u32(smem + kOffPg), 8192, 1024);           // Pg, MN-major
+    constexpr int kHalf = (16384 >> 4) - 3 * 2;  // from k-step 3 to k-step 4: the second 64-column half
+    constexpr uint32_t tmem0 = 0;
+    const uint32_t bar0 = ptx::smem_u32(&bars[0]);
+    auto bar_addr = [&](int b) { return bar0 + 8u * static_cast<uint32_t>(b); };
+    bool ok = tmem == tmem0;
+    if (!ok) ptx::record_wait_failure(status, kStatusBadTmemBase, 0);
+    auto issue_mma0 = [&](int j) {  // D0[j & 1] = [K;Q] K^T of chunk j
+      const uint64_t sn = static_cast<uint64_t>((j & 1) * (kStageBytes >> 4));
+      ptx::tc_fence_after_sync();
+      ptx::umma_ss_k128<2, kHalf, 2, kHalf>(tmem0 + kColD0 + (j & 1) * 64, d_kq + sn, d_kq + sn, id_n64, false,
+                                            bar_addr(kPDone0 + (j & 1)));
+    };
+    bool p0_issued = false;  // MMA0 of the next chunk already issued in gap 1
+#pragma unroll 1
+    for (int i = -1; ok && i < nproc; ++i) {
+      const int ph = i & 1;
+      const uint64_t so = static_cast<uint64_t>((i & 1) * (kStageBytes >> 4));
+      if (i >= 0) {
+        // MMA2: D2 = dS1^T_bf16 K^T
+        if (!(ok = wait(kSbfReady, ph))) break;
+        ptx::tc_fence_after_sync();
+        ptx::umma_ts_k128<2, kHalf>(tmem0 + kColD2, tmem0 + kColSbf, d_kq + so, id_n64, false, bar_addr(kD2Done));
+        // gap 1 (the compute warps form du): MMAq, off the chain, and - when its tiles have landed - MMA0 of
+        // the next chunk, so that Pg of that chunk is ready long before its MMAu
+        if (!(ok = wait(kQsReady, ph))) break;
+        if (!(ok = wait(kSScaled, ph))) break;
+        ptx::tc_fence_after_sync();
+        ptx::umma_ss_k64<128, 128>(tmem0 + kColS, d_do + so, d_qmn + so, id_q, true);
+        p0_issued = false;
+        if (i + 1 < nproc) {
+          const int j = i + 1;
+          const bool landed =
+              __all_sync(0xffffffffu, ptx::mbar_test_wait(&bars[kFull0 + (j & 1)], (j >> 1) & 1)) != 0;
+          if (landed) {
+            issue_mma0(j);
+            p0_issued = true;
+          }
+        }
+        // MMAx: Dx = du^T_bf16 (A diag(-beta gamma))
+        if (!(ok = wait(kAbReady0 + ph, (i >> 1) & 1))) break;
+        if (!(ok = wait(kDuReady, ph))) break;
+        ptx::tc_fence_after_sync();
+        ptx::umma_ts_k64<128>(tmem0 + kColDu0, tmem0 + kColDu16, d_a + so, id_x, false, bar_addr(kDxDone));
+        // MMA3: dS^T += X^T_bf16 K; its completion also releases the stage
+        if (!(ok = wait(kXReady, ph))) break;
+        ptx::tc_fence_after_sync();
+        ptx::umma_ts_k64<128>(tmem0 + kColS, tmem0 + kColX16, d_kmn + so, id_s, true, bar_addr(kSDone),
+                              bar_addr(kEmpty0 + ph));
+      }
+      // gap 2 (the compute warps convert the state): the state-independent products of the next chunk
+      if (i + 1 < nproc) {
+        const int j = i + 1;
+        const uint64_t sn = static_cast<uint64_t>((j & 1) * (kStageBytes >> 4));
+        if (!p0_issued) {
+          if (!(ok = wait(kFull0 + (j & 1), (j >> 1) & 1))) break;
+          issue_mma0(j);
+        }
+        // MMAu: Du0 = dO^T Pg (the compute warps read Dx of this chunk before XReady, MMA3 precedes in the pipe)
+        if (!(ok = wait(kPgReady, j & 1))) break;
+        ptx::tc_fence_after_sync();
+        ptx::umma_ss_k64<128, 128>(tmem0 + kColDu0, d_do + sn, d_pg + static_cast<uint64_t>((j & 1) * (8192 >> 4)),
+                                   id_u, false, bar_addr(kDu0Done));
+      }
+    }
+  } else if (warp >= 10) {
+    // =========================================================== aux warps 10, 11: operand tiles
+    const int r = tid - 320;  // 0..63: row of the A / Pg / Q tiles
+    const uint32_t tm = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
+    float* my_g = aux_g + (warp - 10) * 128;
+    const float log2_scale = __log2f(p.scale);
+    bool ok = true;
+#pragma unroll 1
+    for (int j = 0; ok && j < nproc; ++j) {
+      const int sj = j & 1;
+      if (!(ok = wait(kFull0 + sj, (j >> 1) & 1))) break;
+      const Gates* gs = gates_of(j);
+      my_g[sj * 64 + lane] = gs->g2[lane];
+      my_g[sj * 64 + 32 + lane] = gs->g2[32 + lane];
+      const int valid = gs->valid;
+      // (a) A diag(-beta gamma): column d of the A tile times nbg[d], in place
+      uint8_t* at = stage_ptr(sj) + kStageA;
+#pragma unroll 1
+      for (int c16 = 0; c16 < 8; ++c16) {
+        uint4* ptr = reinterpret_cast<uint4*>(at + ptx::sw128_offset(r, c16));
+        uint4 raw = *ptr;
+        const float4 b0 = *reinterpret_cast<const float4*>(&gs->nbg[c16 * 8]);
+        const float4 b1 = *reinterpret_cast<const float4*>(&gs->nbg[c16 * 8 + 4]);
+        const T* e = reinterpret_cast<const T*>(&raw);
+        raw = make_uint4(pack2<T>(Cvt<T>::to_f32(e[0]) * b0.x, Cvt<T>::to_f32(e[1]) * b0.y),
+                         pack2<T>(Cvt<T>::to_f32(e[2]) * b0.z, Cvt<T>::to_f32(e[3]) * b0.w),
+                         pack2<T>(Cvt<T>::to_f32(e[4]) * b1.x, Cvt<T>::to_f32(e[5]) * b1.y),
+                         pack2<T>(Cvt<T>::to_f32(e[6]) * b1.z, Cvt<T>::to_f32(e[7]) * b1.w));
+        *ptr = raw;
+      }
+      ptx::fence_proxy_async_smem();
+      warp_arrive(&bars[kAbReady0 + sj], lane);
+      // (b) Pg = s G .* P from D0 rows 64..127 (TMEM quadrants 2, 3), rows beyond the sequence end zeroed.
+      // The Pg tile of this parity was last read by MMAu two chunks ago, which precedes this chunk's MMA0 in
+      // the tensor pipe and therefore has completed when PDone fires.
+      if (!(ok = wait(kPDone0 + sj, (j >> 1) & 1))) break;
+      ptx::tc_fence_after_sync();
+      const float* gsg = my_g + sj * 64;
+      const int c = r;
+      const float gc = gsg[c] + log2_scale;
+      uint8_t* pg = smem + kOffPg + sj * 8192;
+#pragma unroll 1
+      for (int db = 0; db < 64; db += 16) {
+        uint32_t pr[16];
+        ptx::tmem_ld16(tm + kColD0 + sj * 64 + db, pr);
+        ptx::tmem_wait_ld();
+#pragma unroll
+        for (int j8 = 0; j8 < 16; j8 += 8) {
+          const float4 ga = *reinterpret_cast<const float4*>(&gsg[db + j8]);
+          const float4 gb = *reinterpret_cast<const float4*>(&gsg[db + j8 + 4]);
+          const float gd[8] = {ga.x, ga.y, ga.z, ga.w, gb.x, gb.y, gb.z, gb.w};
+          float x[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const float val = ptx::ex2(gc - gd[e]) * __uint_as_float(pr[j8 + e]);
+            x[e] = (db + j8 + e <= c && c < valid) ? val : 0.f;
+          }
+          *reinterpret_cast<uint4*>(pg + ptx::sw128_offset(c, (db + j8) >> 3)) =
+              make_uint4(pack2<T>(x[0], x[1]), pack2<T>(x[2], x[3]), pack2<T>(x[4], x[5]), pack2<T>(x[6], x[7]));
+        }
+      }
+      ptx::fence_proxy_async_smem();
+      ptx::tc_fence_before_sync();
+      warp_arrive(&bars[kPgReady], lane);
+      // (c) Q rows times s gamma (0 beyond the sequence end), in place: MMA0 has read the raw tile
+      const float f = gs->sgam[r];
+#pragma unroll 1
+      for (int h = 0; h < 2; ++h) {
+        uint8_t* qt = stage_ptr(sj) + kStageKQ + h * 16384 + 8192;
+#pragma unroll 2
+        for (int c16 = 0; c16 < 8; ++c16) {
+          uint4* ptr = reinterpret_cast<uint4*>(qt + ptx::sw128_offset(r, c16));
+          uint4 raw = *ptr;
+          const T* e = reinterpret_cast<const T*>(&raw);
+          raw = make_uint4(pack2<T>(Cvt<T>::to_f32(e[0]) * f, Cvt<T>::to_f32(e[1]) * f),
+                           pack2<T>(Cvt<T>::to_f32(e[2]) * f, Cvt<T>::to_f32(e[3]) * f),
+                           pack2<T>(Cvt<T>::to_f32(e[4]) * f, Cvt<T>::to_f32(e[5]) * f),
+                           pack2<T>(Cvt<T>::to_f32(e[6]) * f, Cvt<T>::to_f32(e[7]) * f));
+          *ptr = raw;
+        }
+      }
+      ptx::fence_proxy_async_smem();
+      warp_arrive(&bars[kQsReady], lane);
+      warp_arrive(&bars[kEmpty0 + sj], lane);  // aux no longer touches stage sj
+    }
+  } else {
+    // =========================================================== compute warpgroups
+    const int wg = warp >> 2;   // token columns [32 wg, 32 wg + 32) of the chain phases, state columns [64 wg, ..)
+    const int v = tid & 127;    // TMEM lane = column v of dS
+    const uint32_t tm = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
+    const int col_half = wg * 64;
+    bool alive = true;
+    const int st_k = p.transpose_state ? 1 : kHeadDim, st_v = p.transpose_state ? kHeadDim : 1;
+    const float* dhtp = p.dht != nullptr ? p.dht + (static_cast<int64_t>(seq) * p.num_v_heads + hv) * kHeadDim * kHeadDim
+                                         : nullptr;
+    float* dh0p = p.dh0 != nullptr ? p.dh0 + (static_cast<int64_t>(seq) * p.num_v_heads + hv) * kHeadDim * kHeadDim
+                                   : nullptr;
+    T* dh_ws = static_cast<T*>(p.dh);  // [chunk][Hv][128 v][128 k]
+    T* du_ws = static_cast<T*>(p.du);  // [chunk][Hv][128 v][64 tokens]
+    auto dh_row = [&](int chunk) {
+      return dh_ws + (((chunk_base + chunk) * p.num_v_heads + hv) * kHeadDim + v) * kHeadDim;
+    };
+
+    // ---- initial state: dS = exp(gL) * dht (fp32), its 16-bit copy, and dh of the last chunk
+    {
+      float egl0 = 1.f;
+      if (nproc > 0) {
+        alive = wait(kFull0, 0);
+        egl0 = gates_of(0)->egl;
+      }
+      T* hp = nproc > 0 ? dh_row(nproc - 1) : nullptr;
+#pragma unroll 1
+      for (int kb = 0; kb < 64; kb += 16) {
+        float x[16];
+        uint32_t sf[16], sb[8];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const int k = col_half + kb + j;
+          x[j] = dhtp != nullptr ? dhtp[k * st_k + v * st_v] : 0.f;
+        }
+#pragma unroll
+        for (int j = 0; j < 16; j += 2) {
+          sf[j] = __float_as_uint(x[j] * egl0);
+          sf[j + 1] = __float_as_uint(x[j + 1] * egl0);
+          sb[j >> 1] = pack2<T>(x[j], x[j + 1]);
+        }
+        ptx::tmem_st16(tm + kColS + col_half + kb, sf);
+        ptx::tmem_st8(tm + kColSbf + (col_half + kb) / 2, sb);
+        if (hp != nullptr) {
+          *reinterpret_cast<uint4*>(hp + col_half + kb) = make_uint4(sb[0], sb[1], sb[2], sb[3]);
+          *reinterpret_cast<uint4*>(hp + col_half + kb + 8) = make_uint4(sb[4], sb[5], sb[6], sb[7]);
+        }
+        if (nproc == 0 && dh0p != nullptr) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) dh0p[(col_half + kb + j) * st_k + v * st_v] = x[j];
+        }
+      }
+      ptx::tmem_wait_st();
+      ptx::tc_fence_before_sync();
+      warp_arrive(&bars[kSbfReady], lane);
+      warp_arrive(&bars[kSScaled], lane);
+    }
+
+#pragma unroll 1
+    for (int i = 0; alive && i < nproc; ++i) {
+      const int ph = i & 1;
+      const int chunk = chunk_of(i);
+      const Gates* gs = gates_of(i);
+      // ---------------- du^T = Du0 + rho .* D2 for this warpgroup's 32 tokens: 16-bit copy into tensor memory
+      // (A operand of MMAx) and to the workspace
+      if (!(alive = wait(kD2Done, ph))) break;
+      if (!(alive = wait(kDu0Done, ph))) break;
+      ptx::tc_fence_after_sync();
+      {
+        uint32_t d2[32], u0[32], pk[16];
+        ptx::tmem_ld32(tm + kColD2 + 32 * wg, d2);
+        ptx::tmem_ld32(tm + kColDu0 + 32 * wg, u0);
+        ptx::tmem_wait_ld();
+#pragma unroll
+        for (int j = 0; j < 32; j += 4) {
+          const float4 r4 = *reinterpret_cast<const float4*>(&gs->rho[32 * wg + j]);
+          pk[j >> 1] = pack2<T>(fmaf(__uint_as_float(d2[j]), r4.x, __uint_as_float(u0[j])),
+                                fmaf(__uint_as_float(d2[j + 1]), r4.y, __uint_as_float(u0[j + 1])));
+          pk[(j >> 1) + 1] = pack2<T>(fmaf(__uint_as_float(d2[j + 2]), r4.z, __uint_as_float(u0[j + 2])),
+                                      fmaf(__uint_as_float(d2[j + 3]), r4.w, __uint_as_float(u0[j + 3])));
+        }
+        ptx::tmem_st16(tm + kColDu16 + 16 * wg, pk);
+        ptx::tmem_wait_st();
+        ptx::tc_fence_before_sync();
+        warp_arrive(&bars[kDuReady], lane);
+        T* dup = du_ws + (((chunk_base + chunk) * p.num_v_heads + hv) * kHeadDim + v) * kChunk + 32 * wg;
+#pragma unroll
+        for (int j = 0; j < 16; j += 4)
+          *reinterpret_cast<uint4*>(dup + 2 * j) = make_uint4(pk[j], pk[j + 1], pk[j + 2], pk[j + 3]);
+      }
+      // ---------------- X^T: 16-bit copy of Dx into tensor memory (A operand of MMA3)
+      if (!(alive = wait(kDxDone, ph))) break;
+      ptx::tc_fence_after_sync();
+      {
+        uint32_t x[32], pk[16];
+        ptx::tmem_ld32(tm + kColDu0 + 32 * wg, x);
+        ptx::tmem_wait_ld();
+#pragma unroll
+        for (int j = 0; j < 32; j += 2) pk[j >> 1] = pack2<T>(__uint_as_float(x[j]), __uint_as_float(x[j + 1]));
+        ptx::tmem_st16(tm + kColX16 + 16 * wg, pk);
+        ptx::tmem_wait_st();
+        ptx::tc_fence_before_sync();
+        warp_arrive(&bars[kXReady], lane);
+      }
+      // ---------------- state conversion after MMA3 (this warpgroup's 64 columns)
+      if (!(alive = wait(kSDone, ph))) break;
+      ptx::tc_fence_after_sync();
+      if (i + 1 == nproc) {
+        if (dh0p != nullptr) {
+#pragma unroll 1
+          for (int kb = 0; kb < 64; kb += 16) {
+            uint32_t sf[16];
+            ptx::tmem_ld16(tm + kColS + col_half + kb, sf);
+            ptx::tmem_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 16; ++j) dh0p[(col_half + kb + j) * st_k + v * st_v] = __uint_as_float(sf[j]);
+          }
+        }
+      } else {
+        T* hp = dh_row(chunk - 1);
+        // (a) critical: 16-bit copy of the new state -> MMA2 of the next chunk may start; the same values are dh
+#pragma unroll 1
+        for (int h = 0; h < 2; ++h) {
+          uint32_t sf[32], sb[16];
+          ptx::tmem_ld32(tm + kColS + col_half + 32 * h, sf);
+          ptx::tmem_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 32; j += 2) sb[j >> 1] = pack2<T>(__uint_as_float(sf[j]), __uint_as_float(sf[j + 1]));
+          ptx::tmem_st16(tm + kColSbf + col_half / 2 + 16 * h, sb);
+#pragma unroll
+          for (int j = 0; j < 16; j += 4)
+            *reinterpret_cast<uint4*>(hp + col_half + 32 * h + 2 * j) = make_uint4(sb[j], sb[j + 1], sb[j + 2], sb[j + 3]);
+        }
+        ptx::tmem_wait_st();
+        ptx::tc_fence_before_sync();
+        warp_arrive(&bars[kSbfReady], lane);
+        // (b) off the critical path: decay of the fp32 state for the next chunk (needed by MMAq / MMA3 only)
+        if (!(alive = wait(kFull0 + ((i + 1) & 1), ((i + 1) >> 1) & 1))) break;
+        const float egl_next = gates_of(i + 1)->egl;
+#pragma unroll 1
+        for (int h = 0; h < 2; ++h) {
+          uint32_t sf[32];
+          ptx::tmem_ld32(tm + kColS + col_half + 32 * h, sf);
+          ptx::tmem_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) sf[j] = __float_as_uint(__uint_as_float(sf[j]) * egl_next);
+          ptx::tmem_st32(tm + kColS + col_half + 32 * h, sf);
+        }
+        ptx::tmem_wait_st();
+        ptx::tc_fence_before_sync();
+        warp_arrive(&bars[kSScaled], lane);
+      }
+    }
+  }
+
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 8) ptx::tmem_dealloc(tmem, 512);
+}
+
+}  // namespace
+
+int launch_bwd_scan(const BwdParams& p, int64_t total_tokens, bool is_bf16, cudaStream_t stream) {
+  CUtensorMap tm_q, tm_k, tm_do, tm_a;
+  int rc;
+  if ((rc = make_tmap_3d(&tm_k, p.k, total_tokens, p.num_k_heads, kHeadDim, 64, 64, true, is_bf16)) != QLA_OK) return rc;
+  if ((rc = make_tmap_3d(&tm_q, p.q, total_tokens, p.num_k_heads, kHeadDim, 64, 64, true, is_bf16)) != QLA_OK) return rc;
+  if ((rc = make_tmap_3d(&tm_do, p.d_o, total_tokens, p.num_v_heads, kHeadDim, 64, 64, true, is_bf16)) != QLA_OK) return rc;
+  if ((rc = make_tmap_3d(&tm_a, p.A, total_tokens, p.num_v_heads, 64, 64, 64, true, is_bf16)) != QLA_OK) return rc;
+  const unsigned grid = static_cast<unsigned>(p.num_seqs) * p.num_v_heads;
+  if (is_bf16) {
+    if ((rc = ensure_dynamic_smem<bwd_scan_kernel<__nv_bfloat16>>(kSmemBytes)) != QLA_OK) return rc;
+    bwd_scan_kernel<__nv_bfloat16><<<grid, kThreads, kSmemBytes, stream>>>(tm_q, tm_k, tm_do, tm_a, p);
+  } else {
+    if ((rc = ensure_dynamic_smem<bwd_scan_kernel<__half>>(kSmemBytes)) != QLA_OK) return rc;
+    bwd_scan_kernel<__half><<<grid, kThreads, kSmemBytes, stream>>>(tm_q, tm_k, tm_do, tm_a, p);
+  }
+  QLA_CHECK_CUDA(cudaGetLastError());
+  return QLA_OK;
+}
+
+}  // namespace qla

@@ -62,21 +62,24 @@ struct BwdParams {
   const float* dht;             // [N, Hv, 128, 128] or NULL
   const int32_t* cu_seqlens;
   const int32_t* chunk_offsets;
-  void* dh;                     // workspace [chunks, Hv, 128, 128]: gradient of the state leaving every chunk
-  void* du;                     // workspace [NT, Hv, 128]: gradient of v_new
+  void* dh;                     // workspace [chunks, Hv, 128 v, 128 k]: gradient of the state leaving every chunk
+  void* du;                     // workspace [chunks, Hv, 128 v, 64 tokens]: gradient of v_new, transposed per chunk
   void* dq;                     // [NT, Hk, 128]
   void* dk;
   void* dv;                     // [NT, Hv, 128]
   float* dbeta;                 // [NT, Hv]
   float* dg;                    // [NT, Hv] w.r.t. the raw per-token gate
   float* dh0;                   // [N, Hv, 128, 128] or NULL
+  int* status;
   int num_seqs, seq_len, num_k_heads, num_v_heads;
   int beta_dtype;
   int transpose_state;
   float scale;
 };
 
-int launch_chunk_bwd(const BwdParams& p, int total_chunks_upper, bool is_bf16, cudaStream_t stream);
+int launch_bwd_scan(const BwdParams& p, int64_t total_tokens, bool is_bf16, cudaStream_t stream);
+int launch_chunk_bwd(const BwdParams& p, int64_t total_tokens, int total_chunks_upper, bool is_bf16,
+                     cudaStream_t stream);
 
 // Trace layout: [role 0..2][chunk 4..7][16 events] clock64 stamps of CTA 0.
 constexpr int kTraceRoles = 3, kTraceChunks = 4, kTraceEvents = 16, kTraceFirstChunk = 4;

@@ -68,15 +68,6 @@ __device__ __forceinline__ void store4(__nv_bfloat16* p, const float (&x)[4]) {
   *reinterpret_cast<uint2*>(p) = raw;
 }
 
-__device__ __forceinline__ uint2 pack4(const float (&x)[4]) {
-  __nv_bfloat162 lo = __floats2bfloat162_rn(x[0], x[1]);
-  __nv_bfloat162 hi = __floats2bfloat162_rn(x[2], x[3]);
-  uint2 raw;
-  raw.x = *reinterpret_cast<uint32_t*>(&lo);
-  raw.y = *reinterpret_cast<uint32_t*>(&hi);
-  return raw;
-}
-
 __device__ __forceinline__ float group8_sum(float x) {
   x += __shfl_xor_sync(0xffffffffu, x, 1);
   x += __shfl_xor_sync(0xffffffffu, x, 2);
@@ -311,18 +302,19 @@ __global__ void __launch_bounds__(128) recurrent_kernel(const QlaRecurrentArgs p
     const float decay = expf(g);
     const float beta = (p.flags & QLA_REC_B_IS_BETA) ? b_raw : 1.f / (1.f + expf(-b_raw));
 
+    // four partial sums per row (one per owned piece): the dependent chain of a row is 4 deep instead of 16
     float dot[R];
 #pragma unroll
     for (int r = 0; r < R; ++r) {
-      float acc = 0.f;
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int j = 0; j < 4; ++j)
+      for (int i = 0; i < 4; ++i)
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
+        for (int j = 0; j < 4; ++j) {
           S[r][j][i] *= decay;
-          acc = fmaf(S[r][j][i], kv[j][i], acc);
+          acc[j] = fmaf(S[r][j][i], kv[j][i], acc[j]);
         }
-      dot[r] = acc;
+      dot[r] = (acc[0] + acc[1]) + (acc[2] + acc[3]);
     }
 #pragma unroll
     for (int r = 0; r < R; ++r) dot[r] = group8_sum(dot[r]);
@@ -331,15 +323,15 @@ __global__ void __launch_bounds__(128) recurrent_kernel(const QlaRecurrentArgs p
 #pragma unroll
     for (int r = 0; r < R; ++r) {
       const float delta = (vrow[r] - dot[r]) * beta;
-      float acc = 0.f;
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int j = 0; j < 4; ++j)
+      for (int i = 0; i < 4; ++i)
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
+        for (int j = 0; j < 4; ++j) {
           S[r][j][i] = fmaf(kv[j][i], delta, S[r][j][i]);
-          acc = fmaf(S[r][j][i], qv[j][i], acc);
+          acc[j] = fmaf(S[r][j][i], qv[j][i], acc[j]);
         }
-      out[r] = acc;
+      out[r] = (acc[0] + acc[1]) + (acc[2] + acc[3]);
     }
 #pragma unroll
     for (int r = 0; r < R; ++r) out[r] = group8_sum(out[r]);
@@ -351,30 +343,10 @@ __global__ void __launch_bounds__(128) recurrent_kernel(const QlaRecurrentArgs p
 
     if (cidx >= 0 && step < p.inter_steps) {
       InterT* dst = ib + (((cidx * p.inter_steps + step) * p.num_v_heads + h) * D + row0) * D + col0;
-      if constexpr (sizeof(InterT) == 2) {
-        // 16-bit scratch: a lane's four values are only 8 bytes.  Neighbouring lanes (sub, sub ^ 1) own adjacent
-        // column groups, so they swap one packed piece each and every lane writes 16 bytes: the even lane
-        // columns [4 sub, 4 sub + 8) of piece j, the odd lane the same eight columns of piece j + 1.
-        const bool odd = (sub & 1) != 0;
-        InterT* dst16 = dst - (odd ? 4 : 0);
 #pragma unroll
-        for (int r = 0; r < R; ++r)
+      for (int r = 0; r < R; ++r)
 #pragma unroll
-          for (int j = 0; j < 4; j += 2) {
-            const uint2 p0 = pack4(S[r][j]), p1 = pack4(S[r][j + 1]);
-            const uint2 send = odd ? p0 : p1;
-            uint2 recv;
-            recv.x = __shfl_xor_sync(0xffffffffu, send.x, 1);
-            recv.y = __shfl_xor_sync(0xffffffffu, send.y, 1);
-            const uint4 out = odd ? make_uint4(recv.x, recv.y, p1.x, p1.y) : make_uint4(p0.x, p0.y, recv.x, recv.y);
-            *reinterpret_cast<uint4*>(dst16 + (r * 16) * D + (j + (odd ? 1 : 0)) * 32) = out;
-          }
-      } else {
-#pragma unroll
-        for (int r = 0; r < R; ++r)
-#pragma unroll
-          for (int j = 0; j < 4; ++j) store4(dst + (r * 16) * D + j * 32, S[r][j]);
-      }
+        for (int j = 0; j < 4; ++j) store4(dst + (r * 16) * D + j * 32, S[r][j]);
     }
   }
 
