@@ -192,5 +192,6 @@ extern "C" QLA_API int qla_chunk_bwd(const QlaChunkBwdArgs* args, void* stream_)
   p.num_seqs = a.num_seqs; p.seq_len = a.seq_len; p.num_k_heads = a.num_k_heads; p.num_v_heads = a.num_v_heads;
   p.beta_dtype = a.beta_dtype; p.transpose_state = (a.flags & QLA_CHUNK_TRANSPOSE_STATE) ? 1 : 0;
   p.scale = a.scale; p.status = a.status;
+  p.trace = current_trace_buffer();
   return launch_chunk_bwd(p, total_tokens, w.chunks_upper, a.qkv_dtype == QLA_DT_BF16, stream);
 }

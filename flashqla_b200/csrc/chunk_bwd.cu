@@ -1,28 +1,70 @@
-// Chunked gated-delta-rule backward for sm_100a.
+// Chunked gated-delta-rule backward for sm_100a, part 2: everything that is local to one chunk.
 // Reference: chunk_gated_delta_rule_bwd (flash_qla/ops/gated_delta_rule/chunk/__init__.py:89-182); the
 // math is the decomposed form of tests/ref_gdr.py:263-557 / chunk/blackwell/bwd_sm12x.py (dv_local,
-// reverse state scan, dq/dk/dw/dg, WY backward), regrouped into two kernels:
+// dq/dk/dw/dg, WY backward), the fused original is chunk/hopper/fused_bwd.py:388-882.
 //
+// The backward is two kernels:
 //  bwd_scan_kernel   (chunk_bwd_scan.cu) one CTA per (sequence, v-head), chunks in reverse order, dS resident
 //                    in tensor memory; writes du^T [chunk][Hv][128 v][64 tokens], the state gradient
 //                    leaving every chunk dh^T [chunk][Hv][128 v][128 k] and dh0.
-//  bwd_chunk_kernel  one CTA per (chunk, k-head), looping over the v-heads of the GQA group so that dq and
-//                    dk leave already reduced over the group: every remaining product of the chunk
-//                    (dq, dk, dw, dA, the triangular-inverse backward, dbeta, dg with its chunk-local
-//                    reverse cumulative sum).
+//  bwd_chunk_kernel  (this file) persistent CTAs walk the (chunk, k-head) items and loop over the v-heads of the
+//                    GQA group, so that dq and dk leave already reduced over the group: the sixteen remaining
+//                    products of a chunk, the triangular-inverse backward, dbeta, and dg with its chunk-local
+//                    reverse cumulative sum.
 //
-// This kernel runs its many small products (64 x 64 x 128, 64 x 128 x 64, ...) with mma.sync on padded
-// shared-memory tiles; rows beyond the end of a sequence are zero-filled on load, which makes every
-// contraction over the chunk dimension ignore them.
+// Every product is a tcgen05.mma with M = 64 (the 64 tokens of the chunk; such an accumulator occupies 16
+// lanes of each 32-lane partition of tensor memory, so two accumulators share a column range: "bank" 0 at
+// lane offset 0, bank 1 at lane offset 16), operands are TMA-written or thread-written 128B-swizzled
+// shared-memory tiles read K-major or MN-major as the product needs, so no tile is ever transposed.
+// Accumulators are read back as 16 x 256 bit fragments, which hand warp w = (mt, nh) rows 16 mt .. 16 mt + 15
+// and one half of the columns in the mma.sync accumulator layout: thread 4 g + c holds rows g, g + 8 and
+// column pairs 8 nt + 2 c.  dq / dk accumulate in registers over the heads of the group.
+//
+//   level 0 (inputs only)   T1 = dO h^T   T2 = v_new dh^T   dw- = du h^T   x = A^T du   dO v_new^T   Q K^T
+//                           du V^T   K K^T
+//   level 1 (ds, dw)        ds K    ds^T Q    A^T dw    dw K^T
+//   level 2 (dA)            M1 = A^T dA
+//   level 3 (M1)            M1 A^T
+//   level 4 (dL)            dL K    (beta dL)^T K
+// Warp roles (320 threads): warps 0-7 epilogues, warp 8 TMA producer + gate vectors, warp 9 MMA issuer.  The
+// tiles only level 0 reads (dO, v_new, V, du, h, dh: 128 KiB) are refilled for the next head while levels 1-4
+// run.  Rows beyond the end of a sequence hold the next sequence's tokens (TMA does not know about sequences);
+// they never contribute because du, beta, rho and the ds rows of such tokens are exactly zero.
 #include "chunk_params.cuh"
-#include "mma_sync.cuh"
 
 namespace qla {
 namespace {
 
-constexpr int kBwdThreads = 256;
-constexpr int LD = 136;  // padded row stride (elements) of [*][128] tiles: conflict-free ldmatrix
-constexpr int LS = 72;   // padded row stride of [*][64] tiles
+constexpr int kThreads = 320;
+
+// ---- shared-memory map (offsets from a 1024-byte aligned base; every tile 128B-swizzled)
+constexpr uint32_t kOffQ = 0;        // [64][128] as two [64][64] halves
+constexpr uint32_t kOffK = 16384;
+constexpr uint32_t kOffA = 32768;    // [64][64]
+constexpr uint32_t kOffDO = 40960;
+constexpr uint32_t kOffVn = 57344;
+constexpr uint32_t kOffV = 73728;
+constexpr uint32_t kOffDu = 90112;   // du^T [128 v][64 tokens]
+constexpr uint32_t kOffH = 106496;   // h [128 k][128 v] as two [128][64] halves
+constexpr uint32_t kOffDh = 139264;  // dh^T [128 v][128 k] as two [128][64] halves
+constexpr uint32_t kOffDw = 172032;  // dw [64][128], written by the epilogue
+constexpr uint32_t kOffX = 188416;   // [64][64]: ds, then M1, then beta .* dL
+constexpr uint32_t kOffY = 196608;   // [64][64]: dA, then dL
+constexpr uint32_t kSmemBytes = 204800 + 1024;
+constexpr uint32_t kEarlyBytes = 3 * 16384 + 16384 + 2 * 32768;  // dO, v_new, V, du^T, h, dh^T
+
+// ---- tensor-memory columns; bank 1 = the same columns at lane offset 16
+constexpr uint32_t kBank1 = 16u << 16;
+constexpr uint32_t kColT = 0;      // T1 | T2           later M1 (0..63), M1 A^T (64..127)
+constexpr uint32_t kColW = 128;    // dw- | x           later A^T dw (bank 0); dL K | (beta dL)^T K
+constexpr uint32_t kColP = 256;    // dO v_new^T | Q K^T    later dw K^T (bank 0)
+constexpr uint32_t kColR = 320;    // du V^T | K K^T
+constexpr uint32_t kColQ = 384;    // ds K | ds^T Q
+
+enum Bar {
+  kEarlyFull = 0, kLateFull, kEarlyFree, kLateFree, kC45, kC3, kCB, kCT, kL1Ready, kCL1, kDaReady, kC12, kM1Ready,
+  kC13, kDlReady, kC4, kNumBars
+};
 
 struct ChunkCoord {
   int seq, seq_start, seq_end, local_chunk;
@@ -52,386 +94,641 @@ __device__ __forceinline__ ChunkCoord locate_chunk(int chunk, const int32_t* cu,
   return c;
 }
 
-// ============================================================================== per-chunk kernel
-// Row sums over the columns a warp owns, reduced over the four lanes that share a row.
-__device__ __forceinline__ float quad_sum(float x) {
+__device__ __forceinline__ float quad_sum(float x) {  // over the four lanes that share a row
   x += __shfl_xor_sync(0xffffffffu, x, 1);
   x += __shfl_xor_sync(0xffffffffu, x, 2);
   return x;
 }
-// Column sums over the 16 rows a warp owns, reduced over the eight lanes that share a column pair.
-__device__ __forceinline__ float oct_sum(float x) {
+__device__ __forceinline__ float oct_sum(float x) {  // over the eight lanes that share a column pair
   x += __shfl_xor_sync(0xffffffffu, x, 4);
   x += __shfl_xor_sync(0xffffffffu, x, 8);
   x += __shfl_xor_sync(0xffffffffu, x, 16);
   return x;
 }
+__device__ __forceinline__ void compute_sync() {  // the eight epilogue warps
+  asm volatile("bar.sync 1, 256;" ::: "memory");
+}
+__device__ __forceinline__ void warp_arrive(uint64_t* bar, int lane) {
+  __syncwarp();
+  if (lane == 0) ptx::mbar_arrive(bar);
+}
 
 template <typename T>
-__global__ void __launch_bounds__(kBwdThreads, 1) bwd_chunk_kernel(const BwdParams p) {
+__device__ __forceinline__ uint32_t pack2(float a, float b);
+template <>
+__device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, float b) {
+  __nv_bfloat162 x = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&x);
+}
+template <>
+__device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
+  __half2 x = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&x);
+}
+template <typename T>
+__device__ __forceinline__ float2 unpack2(uint32_t raw) {
+  const T* e = reinterpret_cast<const T*>(&raw);
+  return make_float2(Cvt<T>::to_f32(e[0]), Cvt<T>::to_f32(e[1]));
+}
+
+// Two 16-bit elements (row, col), (row, col + 1) of a [rows][128] tile stored as two 64-column halves
+// `half_bytes` apart; col is even.
+__device__ __forceinline__ uint32_t ld_pair(const uint8_t* tile, uint32_t half_bytes, int row, int col) {
+  return *reinterpret_cast<const uint32_t*>(tile + (col >> 6) * half_bytes + ptx::sw128_offset(row, (col & 63) >> 3) +
+                                            (col & 7) * 2);
+}
+__device__ __forceinline__ void st_pair(uint8_t* tile, uint32_t half_bytes, int row, int col, uint32_t v) {
+  *reinterpret_cast<uint32_t*>(tile + (col >> 6) * half_bytes + ptx::sw128_offset(row, (col & 63) >> 3) + (col & 7) * 2) = v;
+}
+
+// kTrace: a separate instantiation whose CTA 0 stamps clock64() at the phase boundaries of its fourth step into
+// the buffer registered with qla_set_trace_buffer (events 0..19 epilogue warp 0, 20..31 the MMA issuer).
+template <typename T, bool kTrace>
+__global__ void __launch_bounds__(kThreads, 1)
+bwd_chunk_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                 const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_vn,
+                 const __grid_constant__ CUtensorMap tm_do, const __grid_constant__ CUtensorMap tm_a,
+                 const __grid_constant__ CUtensorMap tm_h, const __grid_constant__ CUtensorMap tm_dh,
+                 const __grid_constant__ CUtensorMap tm_du, const BwdParams p, const int total_items) {
+  constexpr uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? ptx::kFmtBF16 : ptx::kFmtF16;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int g = lane >> 2, c4 = lane & 3;
-  const int mt = warp & 3, nh = warp >> 2;
-  const int hk = blockIdx.y;
   const int group = p.num_v_heads / p.num_k_heads;
-  if (p.cu_seqlens != nullptr && static_cast<int>(blockIdx.x) >= p.chunk_offsets[p.num_seqs]) return;
-  const ChunkCoord cc = locate_chunk(blockIdx.x, p.cu_seqlens, p.chunk_offsets, p.num_seqs, p.seq_len);
-  const int t0 = cc.seq_start + cc.local_chunk * kChunk;
-  const int valid = min(kChunk, cc.seq_end - t0);
-  const int64_t chunk_global = blockIdx.x;
+  const int real_chunks = p.cu_seqlens != nullptr ? p.chunk_offsets[p.num_seqs] : 0x7fffffff;
 
-  extern __shared__ __align__(16) uint8_t smem_raw[];
-  T* sQ = reinterpret_cast<T*>(smem_raw);  // [64][LD]
-  T* sK = sQ + 64 * LD;
-  T* sV = sK + 64 * LD;
-  T* sVn = sV + 64 * LD;
-  T* sdO = sVn + 64 * LD;
-  T* sDu = sdO + 64 * LD;       // du^T [128 v][LS]
-  T* sDw = sDu + 128 * LS;
-  T* sA = sDw + 64 * LD;        // [64][LS]
-  T* sH = sA + 64 * LS;         // [128][LD]
-  T* sDh = sH + 128 * LD;       // [128][LD]
-  // 64 x 64 temporaries reuse the h / dh area once those are consumed
-  T* sDs = sH;                  // ds            [64][LS]
-  T* sDA = sDs + 64 * LS;       // masked dA
-  T* sM1 = sDA + 64 * LS;       // A^T dA
-  T* sDL = sM1 + 64 * LS;       // dL
-  T* sDLb = sDL + 64 * LS;      // beta .* dL
-  float* sG = reinterpret_cast<float*>(sDh + 128 * LD);  // [64]
-  float* sB = sG + 64;                                   // [64]
-  float* red = sB + 64;                                  // [4][64] cross-warp partials
-  float* red2 = red + 256;                               // [8] scalar partials
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = smem_raw + ((1024u - (ptx::smem_u32(smem_raw) & 1023u)) & 1023u);
+  __shared__ uint64_t bars[kNumBars];
+  __shared__ uint32_t tmem_base_s;
+  __shared__ __align__(16) float sG[2][64];  // cumulative gates of the step (parity), padded rows = last valid
+  __shared__ __align__(16) float sB[2][64];  // beta, 0 on padded rows
+  __shared__ float red[256];
+  __shared__ float red2[8];
 
-  const int64_t qk_stride = static_cast<int64_t>(p.num_k_heads) * kHeadDim;
-  const int64_t v_stride = static_cast<int64_t>(p.num_v_heads) * kHeadDim;
-  const int64_t a_stride = static_cast<int64_t>(p.num_v_heads) * kChunk;
-  const T* qg = static_cast<const T*>(p.q) + (static_cast<int64_t>(t0) * p.num_k_heads + hk) * kHeadDim;
-  const T* kg = static_cast<const T*>(p.k) + (static_cast<int64_t>(t0) * p.num_k_heads + hk) * kHeadDim;
-  mm::load_tile_async<T, 64, 128, kBwdThreads>(sQ, LD, qg, qk_stride, valid);
-  mm::load_tile_async<T, 64, 128, kBwdThreads>(sK, LD, kg, qk_stride, valid);
-  mm::cp_async_commit();
+  if (tid == 0) {
+#pragma unroll 1
+    for (int b = 0; b < kNumBars; ++b) {
+      int count = 1;  // tcgen05.commit, or the producer's expect_tx arrival
+      if (b == kEarlyFull) count = 33;
+      else if (b == kEarlyFree || b == kLateFree) count = 9;
+      else if (b == kL1Ready || b == kDaReady || b == kM1Ready || b == kDlReady) count = 8;
+      ptx::mbar_init(&bars[b], count);
+    }
+    ptx::fence_mbar_init();
+  }
+  if (warp == 8) {
+    ptx::tmem_alloc(&tmem_base_s, 512);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  ptx::tc_fence_after_sync();
+  const uint32_t tmem = tmem_base_s;
+  int* status = p.status;
+  auto wait = [&](int b, uint32_t parity) {  // (+ 128 in the recorded barrier index: this kernel)
+    return ptx::mbar_wait_warp_call(&bars[b], parity, status, kStatusBarrierTimeout | ((b + 128) << 8));
+  };
+  auto trace = [&](int step, int ev) {
+    if (kTrace && p.trace != nullptr && blockIdx.x == 0 && step == 3 && lane == 0) p.trace[ev] = clock64();
+  };
 
-  float dq_acc[8][4], dk_acc[8][4];  // rows 16 mt.., columns 64 nh.. ; summed over the v-heads of the group
-  mm::zero_acc(dq_acc);
-  mm::zero_acc(dk_acc);
-
-  for (int hv = hk * group; hv < (hk + 1) * group; ++hv) {
-    __syncthreads();  // previous head's shared-memory readers are done
-    {
-      const int64_t vo = (static_cast<int64_t>(t0) * p.num_v_heads + hv) * kHeadDim;
-      mm::load_tile_async<T, 64, 128, kBwdThreads>(sV, LD, static_cast<const T*>(p.v) + vo, v_stride, valid);
-      mm::load_tile_async<T, 64, 128, kBwdThreads>(sVn, LD, static_cast<const T*>(p.v_new) + vo, v_stride, valid);
-      mm::load_tile_async<T, 64, 128, kBwdThreads>(sdO, LD, static_cast<const T*>(p.d_o) + vo, v_stride, valid);
-      mm::load_tile_async<T, 128, 64, kBwdThreads>(
-          sDu, LS, static_cast<const T*>(p.du) + (chunk_global * p.num_v_heads + hv) * kHeadDim * kChunk, kChunk, 128);
-      mm::load_tile_async<T, 64, 64, kBwdThreads>(sA, LS, static_cast<const T*>(p.A) + (static_cast<int64_t>(t0) * p.num_v_heads + hv) * kChunk, a_stride, valid);
-      const int64_t ho = (chunk_global * p.num_v_heads + hv) * kHeadDim * kHeadDim;
-      mm::load_tile_async<T, 128, 128, kBwdThreads>(sH, LD, static_cast<const T*>(p.h) + ho, kHeadDim, 128);
-      mm::load_tile_async<T, 128, 128, kBwdThreads>(sDh, LD, static_cast<const T*>(p.dh) + ho, kHeadDim, 128);
-      mm::cp_async_commit();
-      if (tid < 64) {
-        const int64_t last = static_cast<int64_t>(t0) + valid - 1;
-        const bool ok = tid < valid;
-        const int64_t tok = ok ? static_cast<int64_t>(t0) + tid : last;
-        sG[tid] = p.g_cumsum[tok * p.num_v_heads + hv];
-        sB[tid] = ok ? load_scalar(p.beta, p.beta_dtype, tok * p.num_v_heads + hv) : 0.f;
+  if (warp == 8) {
+    // =========================================================== producer: TMA + gate vectors
+    int step = 0;
+    bool ok = true;
+    for (int item = blockIdx.x; ok && item < total_items; item += gridDim.x) {
+      const int chunk = item / p.num_k_heads, hk = item % p.num_k_heads;
+      if (chunk >= real_chunks) continue;
+      const ChunkCoord cc = locate_chunk(chunk, p.cu_seqlens, p.chunk_offsets, p.num_seqs, p.seq_len);
+      const int t0 = cc.seq_start + cc.local_chunk * kChunk;
+      const int valid = min(kChunk, cc.seq_end - t0);
+      for (int hv = hk * group; ok && hv < (hk + 1) * group; ++hv, ++step) {
+        const int ph = step & 1;
+        // gates of this head into the step's parity slot (its previous reader finished two steps ago)
+        const int64_t last_tok = static_cast<int64_t>(t0) + valid - 1;
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+          const int c = lane + 32 * r;
+          const bool okc = c < valid;
+          const int64_t tok = okc ? static_cast<int64_t>(t0) + c : last_tok;
+          sG[ph][c] = p.g_cumsum[tok * p.num_v_heads + hv];
+          sB[ph][c] = okc ? load_scalar(p.beta, p.beta_dtype, tok * p.num_v_heads + hv) : 0.f;
+        }
+        if (step > 0 && !(ok = wait(kEarlyFree, (step - 1) & 1))) break;
+        if (lane == 0) {
+          uint64_t* full = &bars[kEarlyFull];
+          ptx::mbar_expect_tx(full, kEarlyBytes);
+          const int row = (chunk * p.num_v_heads + hv) * kHeadDim;  // row of the [chunks * Hv * 128, width] views
+#pragma unroll 1
+          for (int h = 0; h < 2; ++h) {
+            ptx::tma_load_3d(smem + kOffDO + h * 8192, &tm_do, full, h * 64, hv, t0);
+            ptx::tma_load_3d(smem + kOffVn + h * 8192, &tm_vn, full, h * 64, hv, t0);
+            ptx::tma_load_3d(smem + kOffV + h * 8192, &tm_v, full, h * 64, hv, t0);
+            ptx::tma_load_3d(smem + kOffH + h * 16384, &tm_h, full, h * 64, 0, row);
+            ptx::tma_load_3d(smem + kOffDh + h * 16384, &tm_dh, full, h * 64, 0, row);
+          }
+          ptx::tma_load_3d(smem + kOffDu, &tm_du, full, 0, 0, row);
+        }
+        ptx::mbar_arrive(&bars[kEarlyFull]);  // 32 arrivals (gates written) + the expect_tx arrival
+        if (step > 0 && !(ok = wait(kLateFree, (step - 1) & 1))) break;
+        if (lane == 0) {
+          uint64_t* full = &bars[kLateFull];
+          const bool first_head = hv == hk * group;
+          ptx::mbar_expect_tx(full, first_head ? 8192 + 32768 : 8192);
+          ptx::tma_load_3d(smem + kOffA, &tm_a, full, 0, hv, t0);
+          if (first_head) {
+#pragma unroll 1
+            for (int h = 0; h < 2; ++h) {
+              ptx::tma_load_3d(smem + kOffQ + h * 8192, &tm_q, full, h * 64, hk, t0);
+              ptx::tma_load_3d(smem + kOffK + h * 8192, &tm_k, full, h * 64, hk, t0);
+            }
+          }
+        }
       }
     }
-    mm::cp_async_wait<0>();
-    __syncthreads();
-
-    const int r0 = mt * 16 + g, r1 = r0 + 8;  // the two rows this thread owns in every 64-row product
-    const float gl = sG[valid - 1];
-    const float g0 = sG[r0], g1 = sG[r1];
-    const float gam0 = __expf(g0), gam1 = __expf(g1);
-    const float rho0 = (r0 < valid) ? __expf(gl - g0) : 0.f, rho1 = (r1 < valid) ? __expf(gl - g1) : 0.f;
-    const float be0 = sB[r0], be1 = sB[r1];
-    float dg_row[2] = {0.f, 0.f}, db_row[2] = {0.f, 0.f};
-    float dg_col[4][2];  // columns 32 nh + 8 nt + 2 c4 + {0, 1} of the 64 x 64 products
+  } else if (warp == 9) {
+    // =========================================================== MMA issuer (whole warp, converged)
+    using ptx::kMajorK;
+    using ptx::kMajorMN;
+    auto desc = [&](uint32_t off, uint32_t lbo) { return ptx::smem_desc_sw128(ptx::smem_u32(smem + off), lbo, 1024); };
+    const uint64_t d_q = desc(kOffQ, 16), d_k = desc(kOffK, 16), d_a = desc(kOffA, 16), d_do = desc(kOffDO, 16);
+    const uint64_t d_vn = desc(kOffVn, 16), d_v = desc(kOffV, 16), d_du = desc(kOffDu, 16), d_h = desc(kOffH, 16);
+    const uint64_t d_dw = desc(kOffDw, 16), d_x = desc(kOffX, 16), d_y = desc(kOffY, 16);
+    // the same tiles read MN-major (leading-dimension offset = distance of the two 64-wide halves)
+    const uint64_t m_q = desc(kOffQ, 8192), m_k = desc(kOffK, 8192), m_a = desc(kOffA, 8192), m_du = desc(kOffDu, 8192);
+    const uint64_t m_dh = desc(kOffDh, 16384), m_dw = desc(kOffDw, 8192), m_x = desc(kOffX, 8192), m_y = desc(kOffY, 8192);
+    constexpr int kJ8 = (8192 >> 4) - 6, kJ16 = (16384 >> 4) - 6;  // to the second 64-column half of a K-major tile
+    const uint32_t i_kk64 = ptx::mma_idesc(64, 64, fmt, kMajorK, kMajorK), i_mk64 = ptx::mma_idesc(64, 64, fmt, kMajorMN, kMajorK);
+    const uint32_t i_mm64 = ptx::mma_idesc(64, 64, fmt, kMajorMN, kMajorMN);
+    const uint32_t i_kk = ptx::mma_idesc(64, 128, fmt, kMajorK, kMajorK), i_km = ptx::mma_idesc(64, 128, fmt, kMajorK, kMajorMN);
+    const uint32_t i_mk = ptx::mma_idesc(64, 128, fmt, kMajorMN, kMajorK), i_mm = ptx::mma_idesc(64, 128, fmt, kMajorMN, kMajorMN);
+    constexpr uint32_t t0c = 0;  // the CTA owns all 512 columns: the allocation starts at column 0
+    const uint32_t bar0 = ptx::smem_u32(&bars[0]);
+    auto ba = [&](int b) { return bar0 + 8u * static_cast<uint32_t>(b); };
+    bool ok = tmem == t0c;
+    if (!ok) ptx::record_wait_failure(status, kStatusBadTmemBase, 0);
+    int step = 0;
+    for (int item = blockIdx.x; ok && item < total_items; item += gridDim.x) {
+      if (item / p.num_k_heads >= real_chunks) continue;
+      for (int hh = 0; ok && hh < group; ++hh, ++step) {
+        const uint32_t ph = step & 1;
+        if (!(ok = wait(kEarlyFull, ph))) break;
+        trace(step, 30);
+        if (!(ok = wait(kLateFull, ph))) break;
+        ptx::tc_fence_after_sync();
+        trace(step, 20);
+        // ---- level 0
+        ptx::umma_ss_k128<2, kJ8, 2, kJ8>(t0c + kColP, d_do, d_vn, i_kk64, false);                      // dO v_new^T
+        ptx::umma_ss_k128<2, kJ8, 2, kJ8>(t0c + kColP + kBank1, d_q, d_k, i_kk64, false, ba(kC45));     // Q K^T
+        ptx::umma_ss_k128<128, 128, 2, kJ16>(t0c + kColW, m_du, d_h, i_mk, false, ba(kC3));             // du h^T
+        ptx::umma_ss_k64<128, 2>(t0c + kColW + kBank1, m_a, d_du, i_mk, false);                         // x = A^T du
+        ptx::umma_ss_k128<128, 128, 2, kJ8>(t0c + kColR, m_du, d_v, i_mk64, false);                     // du V^T
+        ptx::umma_ss_k128<2, kJ8, 2, kJ8>(t0c + kColR + kBank1, d_k, d_k, i_kk64, false, ba(kCB));      // K K^T
+        ptx::umma_ss_k128<2, kJ8, 2, kJ16>(t0c + kColT, d_do, d_h, i_kk, false);                        // T1 = dO h^T
+        ptx::umma_ss_k128<2, kJ8, 128, 128>(t0c + kColT + kBank1, d_vn, m_dh, i_km, false, ba(kCT), ba(kEarlyFree));  // T2
+        trace(step, 21);
+        // ---- level 1
+        if (!(ok = wait(kL1Ready, ph))) break;
+        ptx::tc_fence_after_sync();
+        trace(step, 22);
+        ptx::umma_ss_k64<2, 128>(t0c + kColQ, d_x, m_k, i_km, false);                                   // ds K
+        ptx::umma_ss_k64<128, 128>(t0c + kColQ + kBank1, m_x, m_q, i_mm, false);                        // ds^T Q
+        ptx::umma_ss_k64<128, 128>(t0c + kColW, m_a, m_dw, i_mm, false);                                // y = A^T dw
+        ptx::umma_ss_k128<2, kJ8, 2, kJ8>(t0c + kColP, d_dw, d_k, i_kk64, false, ba(kCL1));             // dw K^T
+        trace(step, 23);
+        // ---- level 2
+        if (!(ok = wait(kDaReady, ph))) break;
+        ptx::tc_fence_after_sync();
+        trace(step, 24);
+        ptx::umma_ss_k64<128, 128>(t0c + kColT, m_a, m_y, i_mm64, false, ba(kC12));                     // M1 = A^T dA
+        trace(step, 25);
+        // ---- level 3
+        if (!(ok = wait(kM1Ready, ph))) break;
+        ptx::tc_fence_after_sync();
+        trace(step, 26);
+        ptx::umma_ss_k64<2, 2>(t0c + kColT + 64, d_x, d_a, i_kk64, false, ba(kC13));                    // M1 A^T
+        trace(step, 27);
+        // ---- level 4
+        if (!(ok = wait(kDlReady, ph))) break;
+        ptx::tc_fence_after_sync();
+        trace(step, 28);
+        ptx::umma_ss_k64<2, 128>(t0c + kColW, d_y, m_k, i_km, false);                                   // z = dL K
+        ptx::umma_ss_k64<128, 128>(t0c + kColW + kBank1, m_x, m_k, i_mm, false, ba(kC4), ba(kLateFree));  // (beta dL)^T K
+        trace(step, 29);
+      }
+    }
+  } else {
+    // =========================================================== epilogue warps
+    const int g = lane >> 2, c4 = lane & 3;
+    const int mt = warp & 3, nh = warp >> 2;
+    const int r0 = mt * 16 + g, r1 = r0 + 8;  // the two rows this thread owns in every fragment
+    const uint32_t tq = tmem + (static_cast<uint32_t>(mt * 32) << 16);  // bank 0 of this warp's partition
+    uint8_t* sQ = smem + kOffQ;
+    uint8_t* sK = smem + kOffK;
+    uint8_t* sV = smem + kOffV;
+    auto frag8 = [&](uint32_t col, float (&acc)[8][4]) {  // 16 rows x 64 columns starting at col
+      uint32_t r[32];
+      ptx::tmem_ld_frag8(tq + col, r);
+      ptx::tmem_wait_ld();
 #pragma unroll
-    for (int nt = 0; nt < 4; ++nt) dg_col[nt][0] = dg_col[nt][1] = 0.f;
-    float dg_last = 0.f;
-
-    // helper: sum over this thread's columns of acc .* M[rows r0 / r1][64 nh + ...]
-    auto dot_rows = [&](const float (&acc)[8][4], const T* M, float& s0, float& s1) {
+      for (int j = 0; j < 32; ++j) acc[j >> 2][j & 3] = __uint_as_float(r[j]);
+    };
+    auto frag4 = [&](uint32_t col, float (&acc)[4][4]) {  // 16 rows x 32 columns
+      uint32_t r[16];
+      ptx::tmem_ld_frag4(tq + col, r);
+      ptx::tmem_wait_ld();
+#pragma unroll
+      for (int j = 0; j < 16; ++j) acc[j >> 2][j & 3] = __uint_as_float(r[j]);
+    };
+    // sum over this thread's columns of acc .* M[rows r0 / r1][64 nh + ...]   (M = a [64][128] tile)
+    auto dot_rows = [&](const float (&acc)[8][4], const uint8_t* M, float& s0, float& s1) {
       s0 = 0.f; s1 = 0.f;
 #pragma unroll
       for (int nt = 0; nt < 8; ++nt) {
         const int col = nh * 64 + nt * 8 + 2 * c4;
-        const uint32_t a = *reinterpret_cast<const uint32_t*>(M + r0 * LD + col);
-        const uint32_t b = *reinterpret_cast<const uint32_t*>(M + r1 * LD + col);
-        const T* ea = reinterpret_cast<const T*>(&a);
-        const T* eb = reinterpret_cast<const T*>(&b);
-        s0 += acc[nt][0] * Cvt<T>::to_f32(ea[0]) + acc[nt][1] * Cvt<T>::to_f32(ea[1]);
-        s1 += acc[nt][2] * Cvt<T>::to_f32(eb[0]) + acc[nt][3] * Cvt<T>::to_f32(eb[1]);
+        const float2 a = unpack2<T>(ld_pair(M, 8192, r0, col)), b = unpack2<T>(ld_pair(M, 8192, r1, col));
+        s0 += acc[nt][0] * a.x + acc[nt][1] * a.y;
+        s1 += acc[nt][2] * b.x + acc[nt][3] * b.y;
       }
-    };  // per-thread partials: every use is linear, the quad reduction happens once at the end
-
-    // ---- phase 1: products with the chunk states h (entering) and dh (gradient of the leaving state)
-    {
-      float acc[8][4];
-      // dq += s gamma .* (dO h^T);  dg += q . that
-      mm::zero_acc(acc);
-      mm::warp_gemm<T, 8, false, false>(acc, sdO + mt * 16 * LD, LD, sH + nh * 64 * LD, LD, 128);
-      const float f0 = p.scale * gam0, f1 = p.scale * gam1;
+    };
+    auto st_frag4 = [&](uint8_t* tile, const float (&acc)[4][4]) {  // [64][64] tile, columns 32 nh ..
 #pragma unroll
-      for (int nt = 0; nt < 8; ++nt) { acc[nt][0] *= f0; acc[nt][1] *= f0; acc[nt][2] *= f1; acc[nt][3] *= f1; }
-      float s0, s1;
-      dot_rows(acc, sQ, s0, s1);
-      dg_row[0] += s0; dg_row[1] += s1;
-#pragma unroll
-      for (int nt = 0; nt < 8; ++nt)
-#pragma unroll
-        for (int e = 0; e < 4; ++e) dq_acc[nt][e] += acc[nt][e];
-      // dk += rho .* (v_new dh^T);  dg -= k . that;  dg_last += sum of the same
-      mm::zero_acc(acc);
-      mm::warp_gemm<T, 8, false, true>(acc, sVn + mt * 16 * LD, LD, sDh + nh * 64, LD, 128);  // dh stored [v][k]
-#pragma unroll
-      for (int nt = 0; nt < 8; ++nt) { acc[nt][0] *= rho0; acc[nt][1] *= rho0; acc[nt][2] *= rho1; acc[nt][3] *= rho1; }
-      dot_rows(acc, sK, s0, s1);
-      dg_row[0] -= s0; dg_row[1] -= s1;
-      dg_last += s0 + s1;
-#pragma unroll
-      for (int nt = 0; nt < 8; ++nt)
-#pragma unroll
-        for (int e = 0; e < 4; ++e) dk_acc[nt][e] += acc[nt][e];
-      // dw = -du h^T
-      mm::zero_acc(acc);
-      mm::warp_gemm<T, 8, true, false>(acc, sDu + mt * 16, LS, sH + nh * 64 * LD, LD, 128);
-#pragma unroll
-      for (int nt = 0; nt < 8; ++nt)
-#pragma unroll
-        for (int e = 0; e < 4; ++e) acc[nt][e] = -acc[nt][e];
-      mm::store_acc<T, 8>(sDw + mt * 16 * LD + nh * 64, LD, acc);
-      // dg_last += exp(gL) * sum(h .* dh)
-      float hd = 0.f;
-      for (int i = tid; i < 128 * 64; i += kBwdThreads) {
-        const int r = i >> 6, c2 = (i & 63) * 2;
-        const uint32_t a = *reinterpret_cast<const uint32_t*>(sH + r * LD + c2);
-        const T* ea = reinterpret_cast<const T*>(&a);
-        hd += Cvt<T>::to_f32(ea[0]) * Cvt<T>::to_f32(sDh[c2 * LD + r]) +
-              Cvt<T>::to_f32(ea[1]) * Cvt<T>::to_f32(sDh[(c2 + 1) * LD + r]);
+      for (int nt = 0; nt < 4; ++nt) {
+        const int col = nh * 32 + nt * 8 + 2 * c4;
+        st_pair(tile, 0, r0, col, pack2<T>(acc[nt][0], acc[nt][1]));
+        st_pair(tile, 0, r1, col, pack2<T>(acc[nt][2], acc[nt][3]));
       }
-      dg_last += __expf(gl) * hd;
-    }
-    __syncthreads();  // sDw complete; sH / sDh may be overwritten by the 64 x 64 temporaries
+    };
 
-    // ---- phase 2: ds = s G .* (dO v_new^T), ds2 = ds .* (Q K^T)       rows 16 mt.., columns 32 nh..
-    {
-      float acc[4][4], pq[4][4];
-      mm::zero_acc(acc);
-      mm::zero_acc(pq);
-      mm::warp_gemm<T, 4, false, false>(acc, sdO + mt * 16 * LD, LD, sVn + nh * 32 * LD, LD, 128);
-      mm::warp_gemm<T, 4, false, false>(pq, sQ + mt * 16 * LD, LD, sK + nh * 32 * LD, LD, 128);
+    int step = 0;
+    bool ok = true;
+    for (int item = blockIdx.x; ok && item < total_items; item += gridDim.x) {
+      const int chunk = item / p.num_k_heads, hk = item % p.num_k_heads;
+      if (chunk >= real_chunks) continue;
+      const ChunkCoord cc = locate_chunk(chunk, p.cu_seqlens, p.chunk_offsets, p.num_seqs, p.seq_len);
+      const int t0 = cc.seq_start + cc.local_chunk * kChunk;
+      const int valid = min(kChunk, cc.seq_end - t0);
+      float dq_acc[8][4], dk_acc[8][4];  // rows r0 / r1, columns 64 nh ..; summed over the v-heads of the group
 #pragma unroll
-      for (int nt = 0; nt < 4; ++nt)
+      for (int nt = 0; nt < 8; ++nt)
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int row = (e >> 1) ? r1 : r0, col = nh * 32 + nt * 8 + 2 * c4 + (e & 1);
-          const float w = p.scale * __expf(fminf(((e >> 1) ? g1 : g0) - sG[col], 0.f));
-          const float ds = (col <= row) ? acc[nt][e] * w : 0.f;
-          acc[nt][e] = ds;
-          const float ds2 = ds * pq[nt][e];
-          dg_row[e >> 1] += ds2;     // per-thread partial, reduced over the quad at the end
-          dg_col[nt][e & 1] -= ds2;  // reduced over the rows at the end
+        for (int e = 0; e < 4; ++e) dq_acc[nt][e] = dk_acc[nt][e] = 0.f;
+
+      for (int hv = hk * group; ok && hv < (hk + 1) * group; ++hv, ++step) {
+        const uint32_t ph = step & 1;
+        if (!(ok = wait(kEarlyFull, ph))) break;
+        if (warp == 0) trace(step, 0);
+        const float* gs = sG[ph];
+        const float* bs = sB[ph];
+        const float gl = gs[valid - 1];
+        const float g0 = gs[r0], g1 = gs[r1];
+        const float gam0 = __expf(g0), gam1 = __expf(g1);
+        const float rho0 = (r0 < valid) ? __expf(gl - g0) : 0.f, rho1 = (r1 < valid) ? __expf(gl - g1) : 0.f;
+        const float be0 = bs[r0], be1 = bs[r1];
+        float dg_row[2] = {0.f, 0.f}, db_row[2] = {0.f, 0.f};
+        float dg_col[4][2];  // columns 32 nh + 8 nt + 2 c4 + {0, 1} of the 64 x 64 products
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt) dg_col[nt][0] = dg_col[nt][1] = 0.f;
+        float dg_last = 0.f;
+
+        // ---- sum(h .* dh) straight from the tiles while level 0 runs: thread = (k, half of v)
+        {
+          const int k = tid & 127, vh = tid >> 7;
+          const uint8_t* hrow = smem + kOffH + vh * 16384 + k * 128;
+          const uint8_t* dcol = smem + kOffDh + (k >> 6) * 16384 + (k & 7) * 2;
+          const int kc = (k & 63) >> 3;
+          float hd = 0.f;
+#pragma unroll 2
+          for (int j = 0; j < 8; ++j) {
+            const uint4 raw = *reinterpret_cast<const uint4*>(hrow + ((j ^ (k & 7)) << 4));
+            const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+            for (int x = 0; x < 8; ++x) {
+              const int v = vh * 64 + j * 8 + x;
+              const T d = *reinterpret_cast<const T*>(dcol + v * 128 + ((kc ^ (v & 7)) << 4));
+              hd += Cvt<T>::to_f32(e[x]) * Cvt<T>::to_f32(d);
+            }
+          }
+          dg_last += __expf(gl) * hd;
         }
-      mm::store_acc<T, 4>(sDs + mt * 16 * LS + nh * 32, LS, acc);
-    }
-    __syncthreads();
-    {
-      // dq += ds K ;  dk += ds^T Q
-      mm::warp_gemm<T, 8, false, true>(dq_acc, sDs + mt * 16 * LS, LS, sK + nh * 64, LD, 64);
-      mm::warp_gemm<T, 8, true, true>(dk_acc, sDs + mt * 16, LS, sQ + nh * 64, LD, 64);
-    }
 
-    // ---- phase 3: WY backward
-    {
-      // dA = (beta gamma)_d (dw K^T) + beta_d (du V^T), strictly lower
-      float a1[4][4], a2[4][4];
-      mm::zero_acc(a1);
-      mm::zero_acc(a2);
-      mm::warp_gemm<T, 4, false, false>(a1, sDw + mt * 16 * LD, LD, sK + nh * 32 * LD, LD, 128);
-      mm::warp_gemm<T, 4, true, false>(a2, sDu + mt * 16, LS, sV + nh * 32 * LD, LD, 128);
+        if (warp == 0) trace(step, 1);
+        // ---- level 0, first pair: ds = s G .* (dO v_new^T) (rows of the sequence only), ds2 = ds .* (Q K^T)
+        if (!(ok = wait(kC45, ph))) break;
+        ptx::tc_fence_after_sync();
+        if (warp == 0) trace(step, 2);
+        {
+          float acc[4][4], pq[4][4];
+          frag4(kColP + 32 * nh, acc);
+          frag4(kColP + kBank1 + 32 * nh, pq);
 #pragma unroll
-      for (int nt = 0; nt < 4; ++nt)
+          for (int nt = 0; nt < 4; ++nt)
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int row = (e >> 1) ? r1 : r0, col = nh * 32 + nt * 8 + 2 * c4 + (e & 1);
-          const float bd = sB[col];
-          const float val = bd * (__expf(sG[col]) * a1[nt][e] + a2[nt][e]);
-          a1[nt][e] = (col < row) ? val : 0.f;
+            for (int e = 0; e < 4; ++e) {
+              const int row = (e >> 1) ? r1 : r0, col = nh * 32 + nt * 8 + 2 * c4 + (e & 1);
+              const float w = p.scale * __expf(fminf(((e >> 1) ? g1 : g0) - gs[col], 0.f));
+              const float ds = (col <= row && row < valid) ? acc[nt][e] * w : 0.f;
+              acc[nt][e] = ds;
+              const float ds2 = ds * pq[nt][e];
+              dg_row[e >> 1] += ds2;
+              dg_col[nt][e & 1] -= ds2;
+            }
+          st_frag4(smem + kOffX, acc);
         }
-      mm::store_acc<T, 4>(sDA + mt * 16 * LS + nh * 32, LS, a1);
-    }
-    {
-      // y = A^T dw: dk += (beta gamma) .* y ; dbeta += gamma * (y . k) ; dg += beta gamma * (y . k)
-      float acc[8][4];
-      mm::zero_acc(acc);
-      mm::warp_gemm<T, 8, true, true>(acc, sA + mt * 16, LS, sDw + nh * 64, LD, 64);
-      float s0, s1;
-      dot_rows(acc, sK, s0, s1);
-      db_row[0] += gam0 * s0; db_row[1] += gam1 * s1;
-      dg_row[0] += be0 * gam0 * s0; dg_row[1] += be1 * gam1 * s1;
-      const float f0 = be0 * gam0, f1 = be1 * gam1;
+        // ---- dw = -du h^T
+        if (warp == 0) trace(step, 3);
+        if (!(ok = wait(kC3, ph))) break;
+        ptx::tc_fence_after_sync();
+        if (warp == 0) trace(step, 4);
+        {
+          float acc[8][4];
+          frag8(kColW + 64 * nh, acc);
 #pragma unroll
-      for (int nt = 0; nt < 8; ++nt) {
-        dk_acc[nt][0] += f0 * acc[nt][0]; dk_acc[nt][1] += f0 * acc[nt][1];
-        dk_acc[nt][2] += f1 * acc[nt][2]; dk_acc[nt][3] += f1 * acc[nt][3];
+          for (int nt = 0; nt < 8; ++nt) {
+            const int col = nh * 64 + nt * 8 + 2 * c4;
+            st_pair(smem + kOffDw, 8192, r0, col, pack2<T>(-acc[nt][0], -acc[nt][1]));
+            st_pair(smem + kOffDw, 8192, r1, col, pack2<T>(-acc[nt][2], -acc[nt][3]));
+          }
+        }
+        ptx::fence_proxy_async_smem();
+        ptx::tc_fence_before_sync();
+        warp_arrive(&bars[kL1Ready], lane);
+        if (warp == 0) trace(step, 5);
+
+        // ---- x = A^T du: dv = beta .* x, dbeta += x . v; a2 = du V^T kept for dA
+        if (!(ok = wait(kCB, ph))) break;
+        ptx::tc_fence_after_sync();
+        if (warp == 0) trace(step, 6);
+        float a2[4][4];
+        {
+          float acc[8][4];
+          frag8(kColW + kBank1 + 64 * nh, acc);
+          float s0, s1;
+          dot_rows(acc, sV, s0, s1);
+          db_row[0] += s0; db_row[1] += s1;
+          T* dvg = static_cast<T*>(p.dv);
+#pragma unroll
+          for (int nt = 0; nt < 8; ++nt) {
+            const int col = nh * 64 + nt * 8 + 2 * c4;
+            if (r0 < valid)
+              *reinterpret_cast<uint32_t*>(dvg + (static_cast<int64_t>(t0 + r0) * p.num_v_heads + hv) * kHeadDim + col) =
+                  pack2<T>(be0 * acc[nt][0], be0 * acc[nt][1]);
+            if (r1 < valid)
+              *reinterpret_cast<uint32_t*>(dvg + (static_cast<int64_t>(t0 + r1) * p.num_v_heads + hv) * kHeadDim + col) =
+                  pack2<T>(be1 * acc[nt][2], be1 * acc[nt][3]);
+          }
+          frag4(kColR + 32 * nh, a2);
+        }
+        // ---- T1 = dO h^T: dq += s gamma .* T1, dg += q . that;  T2 = v_new dh^T: dk += rho .* T2, dg -= k . that
+        if (warp == 0) trace(step, 7);
+        if (!(ok = wait(kCT, ph))) break;
+        if (!(ok = wait(kLateFull, ph))) break;  // Q, K rows are read below (they landed before level 0 was issued)
+        ptx::tc_fence_after_sync();
+        if (warp == 0) trace(step, 8);
+        {
+          float acc[8][4];
+          frag8(kColT + 64 * nh, acc);
+          const float f0 = p.scale * gam0, f1 = p.scale * gam1;
+#pragma unroll
+          for (int nt = 0; nt < 8; ++nt) { acc[nt][0] *= f0; acc[nt][1] *= f0; acc[nt][2] *= f1; acc[nt][3] *= f1; }
+          float s0, s1;
+          dot_rows(acc, sQ, s0, s1);
+          dg_row[0] += s0; dg_row[1] += s1;
+#pragma unroll
+          for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) dq_acc[nt][e] += acc[nt][e];
+          frag8(kColT + kBank1 + 64 * nh, acc);
+#pragma unroll
+          for (int nt = 0; nt < 8; ++nt) { acc[nt][0] *= rho0; acc[nt][1] *= rho0; acc[nt][2] *= rho1; acc[nt][3] *= rho1; }
+          dot_rows(acc, sK, s0, s1);
+          dg_row[0] -= s0; dg_row[1] -= s1;
+          dg_last += s0 + s1;
+#pragma unroll
+          for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) dk_acc[nt][e] += acc[nt][e];
+        }
+        // this warp no longer reads the tiles only level 0 uses (V was the last)
+        ptx::tc_fence_before_sync();
+        warp_arrive(&bars[kEarlyFree], lane);
+        if (warp == 0) trace(step, 9);
+
+        // ---- level 1: dq += ds K, dk += ds^T Q; y = A^T dw; dA from dw K^T and du V^T
+        if (!(ok = wait(kCL1, ph))) break;
+        ptx::tc_fence_after_sync();
+        if (warp == 0) trace(step, 10);
+        {
+          float acc[8][4];
+          frag8(kColQ + 64 * nh, acc);
+#pragma unroll
+          for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) dq_acc[nt][e] += acc[nt][e];
+          frag8(kColQ + kBank1 + 64 * nh, acc);
+#pragma unroll
+          for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) dk_acc[nt][e] += acc[nt][e];
+          // y = A^T dw: dk += (beta gamma) .* y ; dbeta += gamma * (y . k) ; dg += beta gamma * (y . k)
+          frag8(kColW + 64 * nh, acc);
+          float s0, s1;
+          dot_rows(acc, sK, s0, s1);
+          db_row[0] += gam0 * s0; db_row[1] += gam1 * s1;
+          dg_row[0] += be0 * gam0 * s0; dg_row[1] += be1 * gam1 * s1;
+          const float f0 = be0 * gam0, f1 = be1 * gam1;
+#pragma unroll
+          for (int nt = 0; nt < 8; ++nt) {
+            dk_acc[nt][0] += f0 * acc[nt][0]; dk_acc[nt][1] += f0 * acc[nt][1];
+            dk_acc[nt][2] += f1 * acc[nt][2]; dk_acc[nt][3] += f1 * acc[nt][3];
+          }
+        }
+        {
+          // dA = (beta gamma)_d (dw K^T) + beta_d (du V^T), strictly lower
+          float a1[4][4];
+          frag4(kColP + 32 * nh, a1);
+#pragma unroll
+          for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const int row = (e >> 1) ? r1 : r0, col = nh * 32 + nt * 8 + 2 * c4 + (e & 1);
+              const float val = bs[col] * (__expf(gs[col]) * a1[nt][e] + a2[nt][e]);
+              a1[nt][e] = (col < row) ? val : 0.f;
+            }
+          st_frag4(smem + kOffY, a1);
+        }
+        ptx::fence_proxy_async_smem();
+        ptx::tc_fence_before_sync();
+        warp_arrive(&bars[kDaReady], lane);
+        if (warp == 0) trace(step, 11);
+
+        // ---- level 2: M1 = A^T dA as the next operand (the ds tile it overwrites was read by level 1)
+        if (!(ok = wait(kC12, ph))) break;
+        ptx::tc_fence_after_sync();
+        if (warp == 0) trace(step, 12);
+        {
+          float acc[4][4];
+          frag4(kColT + 32 * nh, acc);
+          st_frag4(smem + kOffX, acc);
+        }
+        ptx::fence_proxy_async_smem();
+        ptx::tc_fence_before_sync();
+        warp_arrive(&bars[kM1Ready], lane);
+        if (warp == 0) trace(step, 13);
+
+        // ---- level 3: dL = -(M1 A^T) .* G (strictly lower); t = dL .* (beta_row K K^T): dg += rowsum(t) - colsum(t)
+        if (!(ok = wait(kC13, ph))) break;
+        ptx::tc_fence_after_sync();
+        if (warp == 0) trace(step, 14);
+        {
+          float acc[4][4], kk[4][4], lb[4][4];
+          frag4(kColT + 64 + 32 * nh, acc);
+          frag4(kColR + kBank1 + 32 * nh, kk);
+#pragma unroll
+          for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const int row = (e >> 1) ? r1 : r0, col = nh * 32 + nt * 8 + 2 * c4 + (e & 1);
+              const float w = __expf(fminf(((e >> 1) ? g1 : g0) - gs[col], 0.f));
+              const float dl = (col < row) ? -acc[nt][e] * w : 0.f;
+              const float be = (e >> 1) ? be1 : be0;
+              acc[nt][e] = dl;
+              lb[nt][e] = be * dl;
+              const float t = be * dl * kk[nt][e];
+              dg_row[e >> 1] += t;
+              dg_col[nt][e & 1] -= t;
+            }
+          st_frag4(smem + kOffY, acc);  // dL over dA (level 2 has read it)
+          st_frag4(smem + kOffX, lb);   // beta .* dL over M1 (level 3 has read it)
+        }
+        ptx::fence_proxy_async_smem();
+        ptx::tc_fence_before_sync();
+        warp_arrive(&bars[kDlReady], lane);
+        if (warp == 0) trace(step, 15);
+
+        // ---- level 4: z = dL K: dbeta += z . k ; dk += beta .* z ;  dk += (beta .* dL)^T K
+        if (!(ok = wait(kC4, ph))) break;
+        ptx::tc_fence_after_sync();
+        if (warp == 0) trace(step, 16);
+        {
+          float acc[8][4];
+          frag8(kColW + 64 * nh, acc);
+          float s0, s1;
+          dot_rows(acc, sK, s0, s1);
+          db_row[0] += s0; db_row[1] += s1;
+#pragma unroll
+          for (int nt = 0; nt < 8; ++nt) {
+            dk_acc[nt][0] += be0 * acc[nt][0]; dk_acc[nt][1] += be0 * acc[nt][1];
+            dk_acc[nt][2] += be1 * acc[nt][2]; dk_acc[nt][3] += be1 * acc[nt][3];
+          }
+          frag8(kColW + kBank1 + 64 * nh, acc);
+#pragma unroll
+          for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) dk_acc[nt][e] += acc[nt][e];
+        }
+        // this warp no longer reads Q, K, A or tensor memory of this head
+        ptx::tc_fence_before_sync();
+        warp_arrive(&bars[kLateFree], lane);
+        if (warp == 0) trace(step, 17);
+
+        // ---- reductions: dg (rows + columns + last), dbeta; chunk-local reverse cumulative sum of dg
+        compute_sync();
+        {
+          const float a0 = quad_sum(dg_row[0]), a1 = quad_sum(dg_row[1]);
+          const float b0 = quad_sum(db_row[0]), b1 = quad_sum(db_row[1]);
+          if (c4 == 0) {
+            red[nh * 64 + r0] = a0; red[nh * 64 + r1] = a1;
+            red[128 + nh * 64 + r0] = b0; red[128 + nh * 64 + r1] = b1;
+          }
+          float s = dg_last;
+#pragma unroll
+          for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+          if (lane == 0) red2[warp] = s;
+        }
+        compute_sync();
+        float dg_c = 0.f, db_c = 0.f;
+        if (tid < 64) {
+          dg_c = red[tid] + red[64 + tid];
+          db_c = red[128 + tid] + red[192 + tid];
+          if (tid == valid - 1) {
+            float s = 0.f;
+#pragma unroll
+            for (int w = 0; w < 8; ++w) s += red2[w];
+            dg_c += s;
+          }
+        }
+        compute_sync();
+        {
+#pragma unroll
+          for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+              const float s = oct_sum(dg_col[nt][e]);
+              if (g == 0) red[mt * 64 + nh * 32 + nt * 8 + 2 * c4 + e] = s;
+            }
+        }
+        compute_sync();
+        if (tid < 64) {
+          dg_c += red[tid] + red[64 + tid] + red[128 + tid] + red[192 + tid];
+          if (tid >= valid) dg_c = 0.f;  // rows of the next sequence: they must not enter the suffix sum
+          red2[0] = 0.f;
+        }
+        compute_sync();
+        // suffix sum over the 64 tokens of the chunk (two warps): dg_raw[c] = sum_{c' >= c} dg_cum[c']
+        if (tid < 64) {
+          float s = dg_c;
+#pragma unroll
+          for (int off = 1; off < 32; off <<= 1) {
+            const float n = __shfl_down_sync(0xffffffffu, s, off);
+            if (lane + off < 32) s += n;
+          }
+          if (tid == 32) red2[0] = s;  // total of tokens 32..63
+          __syncwarp();
+          red[tid] = s;
+        }
+        compute_sync();
+        if (tid < 64) {
+          float s = red[tid];
+          if (tid < 32) s += red2[0];
+          if (tid < valid) {
+            p.dg[(static_cast<int64_t>(t0) + tid) * p.num_v_heads + hv] = s;
+            p.dbeta[(static_cast<int64_t>(t0) + tid) * p.num_v_heads + hv] = db_c;
+          }
+        }
+        compute_sync();  // red / red2 are rewritten by the next head
+        if (warp == 0) trace(step, 18);
       }
-      // x = A^T du: dv = beta .* x ; dbeta += x . v
-      mm::zero_acc(acc);
-      mm::warp_gemm<T, 8, true, false>(acc, sA + mt * 16, LS, sDu + nh * 64 * LS, LS, 64);
-      dot_rows(acc, sV, s0, s1);
-      db_row[0] += s0; db_row[1] += s1;
-      T* dvg = static_cast<T*>(p.dv);
+      if (!ok) break;
+
+      // dq, dk of the k-head (already summed over its v-heads)
+      T* dqg = static_cast<T*>(p.dq);
+      T* dkg = static_cast<T*>(p.dk);
 #pragma unroll
       for (int nt = 0; nt < 8; ++nt) {
         const int col = nh * 64 + nt * 8 + 2 * c4;
-        if (r0 < valid)
-          *reinterpret_cast<uint32_t*>(dvg + (static_cast<int64_t>(t0 + r0) * p.num_v_heads + hv) * kHeadDim + col) =
-              mm::pack_pair<T>(be0 * acc[nt][0], be0 * acc[nt][1]);
-        if (r1 < valid)
-          *reinterpret_cast<uint32_t*>(dvg + (static_cast<int64_t>(t0 + r1) * p.num_v_heads + hv) * kHeadDim + col) =
-              mm::pack_pair<T>(be1 * acc[nt][2], be1 * acc[nt][3]);
-      }
-    }
-    __syncthreads();  // sDA complete
-    {
-      float acc[4][4];
-      mm::zero_acc(acc);
-      mm::warp_gemm<T, 4, true, true>(acc, sA + mt * 16, LS, sDA + nh * 32, LS, 64);  // M1 = A^T dA
-      mm::store_acc<T, 4>(sM1 + mt * 16 * LS + nh * 32, LS, acc);
-    }
-    __syncthreads();
-    {
-      // dL = -(M1 A^T) .* G (strictly lower); t = dL .* (beta_row K K^T): dg += rowsum(t) - colsum(t)
-      float acc[4][4], kk[4][4], lb[4][4];
-      mm::zero_acc(acc);
-      mm::zero_acc(kk);
-      mm::warp_gemm<T, 4, false, false>(acc, sM1 + mt * 16 * LS, LS, sA + nh * 32 * LS, LS, 64);
-      mm::warp_gemm<T, 4, false, false>(kk, sK + mt * 16 * LD, LD, sK + nh * 32 * LD, LD, 128);
-#pragma unroll
-      for (int nt = 0; nt < 4; ++nt)
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int row = (e >> 1) ? r1 : r0, col = nh * 32 + nt * 8 + 2 * c4 + (e & 1);
-          const float w = __expf(fminf(((e >> 1) ? g1 : g0) - sG[col], 0.f));
-          const float dl = (col < row) ? -acc[nt][e] * w : 0.f;
-          const float be = (e >> 1) ? be1 : be0;
-          acc[nt][e] = dl;
-          lb[nt][e] = be * dl;
-          const float t = be * dl * kk[nt][e];
-          dg_row[e >> 1] += t;
-          dg_col[nt][e & 1] -= t;
+        if (r0 < valid) {
+          const int64_t o = (static_cast<int64_t>(t0 + r0) * p.num_k_heads + hk) * kHeadDim + col;
+          *reinterpret_cast<uint32_t*>(dqg + o) = pack2<T>(dq_acc[nt][0], dq_acc[nt][1]);
+          *reinterpret_cast<uint32_t*>(dkg + o) = pack2<T>(dk_acc[nt][0], dk_acc[nt][1]);
         }
-      mm::store_acc<T, 4>(sDL + mt * 16 * LS + nh * 32, LS, acc);
-      mm::store_acc<T, 4>(sDLb + mt * 16 * LS + nh * 32, LS, lb);
-    }
-    __syncthreads();
-    {
-      // z = dL K: dbeta += z . k ; dk += beta .* z ;  dk += (beta .* dL)^T K
-      float acc[8][4];
-      mm::zero_acc(acc);
-      mm::warp_gemm<T, 8, false, true>(acc, sDL + mt * 16 * LS, LS, sK + nh * 64, LD, 64);
-      float s0, s1;
-      dot_rows(acc, sK, s0, s1);
-      db_row[0] += s0; db_row[1] += s1;
-#pragma unroll
-      for (int nt = 0; nt < 8; ++nt) {
-        dk_acc[nt][0] += be0 * acc[nt][0]; dk_acc[nt][1] += be0 * acc[nt][1];
-        dk_acc[nt][2] += be1 * acc[nt][2]; dk_acc[nt][3] += be1 * acc[nt][3];
-      }
-      mm::warp_gemm<T, 8, true, true>(dk_acc, sDLb + mt * 16, LS, sK + nh * 64, LD, 64);
-    }
-
-    // ---- reductions: dg (rows + columns + last), dbeta; chunk-local reverse cumulative sum of dg
-    // red[0..1][64]: row partials of the two column halves; red[2..3] reused after a barrier for columns
-    __syncthreads();
-    {
-      const float a0 = quad_sum(dg_row[0]), a1 = quad_sum(dg_row[1]);
-      const float b0 = quad_sum(db_row[0]), b1 = quad_sum(db_row[1]);
-      if (c4 == 0) {
-        red[nh * 64 + r0] = a0; red[nh * 64 + r1] = a1;
-        red[128 + nh * 64 + r0] = b0; red[128 + nh * 64 + r1] = b1;
-      }
-      float s = dg_last;
-#pragma unroll
-      for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
-      if (lane == 0) red2[warp] = s;
-    }
-    __syncthreads();
-    float dg_c = 0.f, db_c = 0.f;
-    if (tid < 64) {
-      dg_c = red[tid] + red[64 + tid];
-      db_c = red[128 + tid] + red[192 + tid];
-      if (tid == valid - 1) {
-        float s = 0.f;
-#pragma unroll
-        for (int w = 0; w < 8; ++w) s += red2[w];
-        dg_c += s;
-      }
-    }
-    __syncthreads();
-    {
-      // column partials: four row-tile warps per column
-#pragma unroll
-      for (int nt = 0; nt < 4; ++nt)
-#pragma unroll
-        for (int e = 0; e < 2; ++e) {
-          const float s = oct_sum(dg_col[nt][e]);
-          if (g == 0) red[mt * 64 + nh * 32 + nt * 8 + 2 * c4 + e] = s;
+        if (r1 < valid) {
+          const int64_t o = (static_cast<int64_t>(t0 + r1) * p.num_k_heads + hk) * kHeadDim + col;
+          *reinterpret_cast<uint32_t*>(dqg + o) = pack2<T>(dq_acc[nt][2], dq_acc[nt][3]);
+          *reinterpret_cast<uint32_t*>(dkg + o) = pack2<T>(dk_acc[nt][2], dk_acc[nt][3]);
         }
-    }
-    __syncthreads();
-    if (tid < 64) {
-      dg_c += red[tid] + red[64 + tid] + red[128 + tid] + red[192 + tid];
-      red2[0] = 0.f;
-    }
-    __syncthreads();
-    // suffix sum over the 64 tokens of the chunk (two warps): dg_raw[c] = sum_{c' >= c} dg_cum[c']
-    if (tid < 64) {
-      float s = dg_c;
-#pragma unroll
-      for (int off = 1; off < 32; off <<= 1) {
-        const float n = __shfl_down_sync(0xffffffffu, s, off);
-        if (lane + off < 32) s += n;
-      }
-      if (tid == 32) red2[0] = s;  // total of tokens 32..63
-      __syncwarp();
-      red[tid] = s;
-    }
-    __syncthreads();
-    if (tid < 64) {
-      float s = red[tid];
-      if (tid < 32) s += red2[0];
-      if (tid < valid) {
-        p.dg[(static_cast<int64_t>(t0) + tid) * p.num_v_heads + hv] = s;
-        p.dbeta[(static_cast<int64_t>(t0) + tid) * p.num_v_heads + hv] = db_c;
       }
     }
   }
 
-  // dq, dk of the k-head (already summed over its v-heads)
-  T* dqg = static_cast<T*>(p.dq);
-  T* dkg = static_cast<T*>(p.dk);
-  const int r0 = mt * 16 + g, r1 = r0 + 8;
-#pragma unroll
-  for (int nt = 0; nt < 8; ++nt) {
-    const int col = nh * 64 + nt * 8 + 2 * c4;
-    if (r0 < valid) {
-      const int64_t o = (static_cast<int64_t>(t0 + r0) * p.num_k_heads + hk) * kHeadDim + col;
-      *reinterpret_cast<uint32_t*>(dqg + o) = mm::pack_pair<T>(dq_acc[nt][0], dq_acc[nt][1]);
-      *reinterpret_cast<uint32_t*>(dkg + o) = mm::pack_pair<T>(dk_acc[nt][0], dk_acc[nt][1]);
-    }
-    if (r1 < valid) {
-      const int64_t o = (static_cast<int64_t>(t0 + r1) * p.num_k_heads + hk) * kHeadDim + col;
-      *reinterpret_cast<uint32_t*>(dqg + o) = mm::pack_pair<T>(dq_acc[nt][2], dq_acc[nt][3]);
-      *reinterpret_cast<uint32_t*>(dkg + o) = mm::pack_pair<T>(dk_acc[nt][2], dk_acc[nt][3]);
-    }
-  }
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 8) ptx::tmem_dealloc(tmem, 512);
 }
 
-constexpr size_t kChunkSmem = (6 * 64 * LD + 128 * LS + 64 * LS + 2 * 128 * LD) * 2 + (64 + 64 + 256 + 8) * sizeof(float);
+// [rows, width] row-major tensor of 16-bit elements seen as a 3-D map with a unit middle extent
+int make_tmap_rows(CUtensorMap* out, const void* base, uint64_t rows, uint64_t width, uint32_t box_rows, bool is_bf16) {
+  return make_tmap_3d(out, base, rows, 1, width, box_rows, 64, true, is_bf16);
+}
 
 }  // namespace
 
@@ -439,14 +736,35 @@ int launch_chunk_bwd(const BwdParams& p, int64_t total_tokens, int total_chunks_
                      cudaStream_t stream) {
   int rc = launch_bwd_scan(p, total_tokens, is_bf16, stream);
   if (rc != QLA_OK) return rc;
-  dim3 chunk_grid(total_chunks_upper, p.num_k_heads);
+  CUtensorMap tm_q, tm_k, tm_v, tm_vn, tm_do, tm_a, tm_h, tm_dh, tm_du;
+  const uint64_t state_rows = static_cast<uint64_t>(total_chunks_upper) * p.num_v_heads * kHeadDim;
+  if ((rc = make_tmap_3d(&tm_q, p.q, total_tokens, p.num_k_heads, kHeadDim, 64, 64, true, is_bf16)) != QLA_OK) return rc;
+  if ((rc = make_tmap_3d(&tm_k, p.k, total_tokens, p.num_k_heads, kHeadDim, 64, 64, true, is_bf16)) != QLA_OK) return rc;
+  if ((rc = make_tmap_3d(&tm_v, p.v, total_tokens, p.num_v_heads, kHeadDim, 64, 64, true, is_bf16)) != QLA_OK) return rc;
+  if ((rc = make_tmap_3d(&tm_vn, p.v_new, total_tokens, p.num_v_heads, kHeadDim, 64, 64, true, is_bf16)) != QLA_OK) return rc;
+  if ((rc = make_tmap_3d(&tm_do, p.d_o, total_tokens, p.num_v_heads, kHeadDim, 64, 64, true, is_bf16)) != QLA_OK) return rc;
+  if ((rc = make_tmap_3d(&tm_a, p.A, total_tokens, p.num_v_heads, 64, 64, 64, true, is_bf16)) != QLA_OK) return rc;
+  if ((rc = make_tmap_rows(&tm_h, p.h, state_rows, kHeadDim, 128, is_bf16)) != QLA_OK) return rc;
+  if ((rc = make_tmap_rows(&tm_dh, p.dh, state_rows, kHeadDim, 128, is_bf16)) != QLA_OK) return rc;
+  if ((rc = make_tmap_rows(&tm_du, p.du, state_rows, kChunk, 128, is_bf16)) != QLA_OK) return rc;
+  const int total_items = total_chunks_upper * p.num_k_heads;
+  int dev = 0, sms = 0;
+  QLA_CHECK_CUDA(cudaGetDevice(&dev));
+  QLA_CHECK_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  const unsigned grid = static_cast<unsigned>(total_items < sms ? total_items : sms);
+#define QLA_LAUNCH_BWD_CHUNK(T, TR)                                                                         \
+  do {                                                                                                     \
+    if ((rc = ensure_dynamic_smem<bwd_chunk_kernel<T, TR>>(kSmemBytes)) != QLA_OK) return rc;              \
+    bwd_chunk_kernel<T, TR><<<grid, kThreads, kSmemBytes, stream>>>(tm_q, tm_k, tm_v, tm_vn, tm_do, tm_a, tm_h, tm_dh, \
+                                                                    tm_du, p, total_items);                \
+  } while (0)
+  const bool traced = p.trace != nullptr;
   if (is_bf16) {
-    if ((rc = ensure_dynamic_smem<bwd_chunk_kernel<__nv_bfloat16>>(kChunkSmem)) != QLA_OK) return rc;
-    bwd_chunk_kernel<__nv_bfloat16><<<chunk_grid, kBwdThreads, kChunkSmem, stream>>>(p);
+    if (traced) QLA_LAUNCH_BWD_CHUNK(__nv_bfloat16, true); else QLA_LAUNCH_BWD_CHUNK(__nv_bfloat16, false);
   } else {
-    if ((rc = ensure_dynamic_smem<bwd_chunk_kernel<__half>>(kChunkSmem)) != QLA_OK) return rc;
-    bwd_chunk_kernel<__half><<<chunk_grid, kBwdThreads, kChunkSmem, stream>>>(p);
+    if (traced) QLA_LAUNCH_BWD_CHUNK(__half, true); else QLA_LAUNCH_BWD_CHUNK(__half, false);
   }
+#undef QLA_LAUNCH_BWD_CHUNK
   QLA_CHECK_CUDA(cudaGetLastError());
   return QLA_OK;
 }

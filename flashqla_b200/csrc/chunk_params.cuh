@@ -71,6 +71,7 @@ struct BwdParams {
   float* dg;                    // [NT, Hv] w.r.t. the raw per-token gate
   float* dh0;                   // [N, Hv, 128, 128] or NULL
   int* status;
+  long long* trace;             // optional phase trace of the per-chunk kernel (see qla_set_trace_buffer), NULL in normal use
   int num_seqs, seq_len, num_k_heads, num_v_heads;
   int beta_dtype;
   int transpose_state;
