@@ -17,7 +17,7 @@
 // lane offset 0, bank 1 at lane offset 16), operands are TMA-written or thread-written 128B-swizzled
 // shared-memory tiles read K-major or MN-major as the product needs, so no tile is ever transposed.
 // Accumulators are read back as 16 x 256 bit fragments, which hand warp w = (mt, nh) rows 16 mt .. 16 mt + 15
-// and one half of the columns in the mma.sync accumulator layout: thread 4 g + c holds rows g, g + 8 and
+// and one quarter of the columns in the mma.sync accumulator layout: thread 4 g + c holds rows g, g + 8 and
 // column pairs 8 nt + 2 c.  dq / dk accumulate in registers over the heads of the group.
 //
 //   level 0 (inputs only)   T1 = dO h^T   T2 = v_new dh^T   dw- = du h^T   x = A^T du   dO v_new^T   Q K^T
@@ -26,7 +26,8 @@
 //   level 2 (dA)            M1 = A^T dA
 //   level 3 (M1)            M1 A^T
 //   level 4 (dL)            dL K    (beta dL)^T K
-// Warp roles (320 threads): warps 0-7 epilogues, warp 8 TMA producer + gate vectors, warp 9 MMA issuer.  The
+// Warp roles (576 threads): warps 0-15 epilogues (warp = row tile mt x column quarter nh), warp 16 TMA producer +
+// gate vectors, warp 17 MMA issuer.  dv, dq and dk leave through shared-memory tiles and TMA stores.  The
 // tiles only level 0 reads (dO, v_new, V, du, h, dh: 128 KiB) are refilled for the next head while levels 1-4
 // run.  Rows beyond the end of a sequence hold the next sequence's tokens (TMA does not know about sequences);
 // they never contribute because du, beta, rho and the ds rows of such tokens are exactly zero.
@@ -35,7 +36,9 @@
 namespace qla {
 namespace {
 
-constexpr int kThreads = 320;
+constexpr int kComputeWarps = 16;
+constexpr int kThreads = 32 * (kComputeWarps + 2);
+constexpr int kRedFloats = 800;  // per parity: dg rows [4][64], dbeta rows [4][64], dg columns [4][64], last [16], carry
 
 // ---- shared-memory map (offsets from a 1024-byte aligned base; every tile 128B-swizzled)
 constexpr uint32_t kOffQ = 0;        // [64][128] as two [64][64] halves
@@ -105,8 +108,8 @@ __device__ __forceinline__ float oct_sum(float x) {  // over the eight lanes tha
   x += __shfl_xor_sync(0xffffffffu, x, 16);
   return x;
 }
-__device__ __forceinline__ void compute_sync() {  // the eight epilogue warps
-  asm volatile("bar.sync 1, 256;" ::: "memory");
+__device__ __forceinline__ void compute_sync() {  // the epilogue warps
+  asm volatile("bar.sync 1, %0;" ::"n"(32 * kComputeWarps) : "memory");
 }
 __device__ __forceinline__ void warp_arrive(uint64_t* bar, int lane) {
   __syncwarp();
@@ -149,7 +152,9 @@ bwd_chunk_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                  const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_vn,
                  const __grid_constant__ CUtensorMap tm_do, const __grid_constant__ CUtensorMap tm_a,
                  const __grid_constant__ CUtensorMap tm_h, const __grid_constant__ CUtensorMap tm_dh,
-                 const __grid_constant__ CUtensorMap tm_du, const BwdParams p, const int total_items) {
+                 const __grid_constant__ CUtensorMap tm_du, const __grid_constant__ CUtensorMap tm_dq,
+                 const __grid_constant__ CUtensorMap tm_dk, const __grid_constant__ CUtensorMap tm_dv, const BwdParams p,
+                 const int total_items) {
   constexpr uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? ptx::kFmtBF16 : ptx::kFmtF16;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int group = p.num_v_heads / p.num_k_heads;
@@ -161,21 +166,20 @@ bwd_chunk_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   __shared__ uint32_t tmem_base_s;
   __shared__ __align__(16) float sG[2][64];  // cumulative gates of the step (parity), padded rows = last valid
   __shared__ __align__(16) float sB[2][64];  // beta, 0 on padded rows
-  __shared__ float red[256];
-  __shared__ float red2[8];
+  __shared__ float red[2 * kRedFloats];
 
   if (tid == 0) {
 #pragma unroll 1
     for (int b = 0; b < kNumBars; ++b) {
       int count = 1;  // tcgen05.commit, or the producer's expect_tx arrival
       if (b == kEarlyFull) count = 33;
-      else if (b == kEarlyFree || b == kLateFree) count = 9;
-      else if (b == kL1Ready || b == kDaReady || b == kM1Ready || b == kDlReady) count = 8;
+      else if (b == kEarlyFree || b == kLateFree) count = kComputeWarps + 1;
+      else if (b == kL1Ready || b == kDaReady || b == kM1Ready || b == kDlReady) count = kComputeWarps;
       ptx::mbar_init(&bars[b], count);
     }
     ptx::fence_mbar_init();
   }
-  if (warp == 8) {
+  if (warp == kComputeWarps) {
     ptx::tmem_alloc(&tmem_base_s, 512);
     ptx::tmem_relinquish();
   }
@@ -191,7 +195,7 @@ bwd_chunk_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     if (kTrace && p.trace != nullptr && blockIdx.x == 0 && step == 3 && lane == 0) p.trace[ev] = clock64();
   };
 
-  if (warp == 8) {
+  if (warp == kComputeWarps) {
     // =========================================================== producer: TMA + gate vectors
     int step = 0;
     bool ok = true;
@@ -229,6 +233,39 @@ bwd_chunk_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           ptx::tma_load_3d(smem + kOffDu, &tm_du, full, 0, 0, row);
         }
         ptx::mbar_arrive(&bars[kEarlyFull]);  // 32 arrivals (gates written) + the expect_tx arrival
+        // the tiles of the NEXT step into L2, so that its demand loads (issued when this step's buffers are
+        // released) find them there
+        if (lane == 0) {
+          int hv2 = hv + 1, item2 = item;
+          if (hv2 == (hk + 1) * group) {
+            item2 = item + gridDim.x;
+            hv2 = (item2 % p.num_k_heads) * group;
+          }
+          const int chunk2 = item2 / p.num_k_heads;
+          if (item2 < total_items && chunk2 < real_chunks) {
+            int t2 = t0;
+            if (item2 != item) {
+              const ChunkCoord c2 = locate_chunk(chunk2, p.cu_seqlens, p.chunk_offsets, p.num_seqs, p.seq_len);
+              t2 = c2.seq_start + c2.local_chunk * kChunk;
+            }
+            const int hk2 = hv2 / group;
+            const int row2 = (chunk2 * p.num_v_heads + hv2) * kHeadDim;
+#pragma unroll 1
+            for (int x = 0; x < 128; x += 64) {
+              ptx::tma_prefetch_l2_3d(&tm_do, x, hv2, t2);
+              ptx::tma_prefetch_l2_3d(&tm_vn, x, hv2, t2);
+              ptx::tma_prefetch_l2_3d(&tm_v, x, hv2, t2);
+              ptx::tma_prefetch_l2_3d(&tm_h, x, 0, row2);
+              ptx::tma_prefetch_l2_3d(&tm_dh, x, 0, row2);
+              if (item2 != item) {
+                ptx::tma_prefetch_l2_3d(&tm_q, x, hk2, t2);
+                ptx::tma_prefetch_l2_3d(&tm_k, x, hk2, t2);
+              }
+            }
+            ptx::tma_prefetch_l2_3d(&tm_du, 0, 0, row2);
+            ptx::tma_prefetch_l2_3d(&tm_a, 0, hv2, t2);
+          }
+        }
         if (step > 0 && !(ok = wait(kLateFree, (step - 1) & 1))) break;
         if (lane == 0) {
           uint64_t* full = &bars[kLateFull];
@@ -245,7 +282,7 @@ bwd_chunk_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         }
       }
     }
-  } else if (warp == 9) {
+  } else if (warp == kComputeWarps + 1) {
     // =========================================================== MMA issuer (whole warp, converged)
     using ptx::kMajorK;
     using ptx::kMajorMN;
@@ -319,43 +356,96 @@ bwd_chunk_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   } else {
     // =========================================================== epilogue warps
     const int g = lane >> 2, c4 = lane & 3;
-    const int mt = warp & 3, nh = warp >> 2;
+    const int mt = warp & 3, nh = warp >> 2;  // rows 16 mt .., column quarter nh
     const int r0 = mt * 16 + g, r1 = r0 + 8;  // the two rows this thread owns in every fragment
     const uint32_t tq = tmem + (static_cast<uint32_t>(mt * 32) << 16);  // bank 0 of this warp's partition
     uint8_t* sQ = smem + kOffQ;
     uint8_t* sK = smem + kOffK;
     uint8_t* sV = smem + kOffV;
-    auto frag8 = [&](uint32_t col, float (&acc)[8][4]) {  // 16 rows x 64 columns starting at col
-      uint32_t r[32];
-      ptx::tmem_ld_frag8(tq + col, r);
-      ptx::tmem_wait_ld();
-#pragma unroll
-      for (int j = 0; j < 32; ++j) acc[j >> 2][j & 3] = __uint_as_float(r[j]);
-    };
-    auto frag4 = [&](uint32_t col, float (&acc)[4][4]) {  // 16 rows x 32 columns
+    // wide fragment: 16 rows x 32 columns (a quarter of a 128-column product); narrow: 16 rows x 16 columns
+    auto wide = [&](uint32_t col, float (&acc)[4][4]) {
       uint32_t r[16];
-      ptx::tmem_ld_frag4(tq + col, r);
+      ptx::tmem_ld_frag4(tq + col + 32 * nh, r);
       ptx::tmem_wait_ld();
 #pragma unroll
       for (int j = 0; j < 16; ++j) acc[j >> 2][j & 3] = __uint_as_float(r[j]);
     };
-    // sum over this thread's columns of acc .* M[rows r0 / r1][64 nh + ...]   (M = a [64][128] tile)
-    auto dot_rows = [&](const float (&acc)[8][4], const uint8_t* M, float& s0, float& s1) {
+    auto wide2 = [&](uint32_t col_a, float (&a)[4][4], uint32_t col_b, float (&b)[4][4]) {  // two loads in flight
+      uint32_t ra[16], rb[16];
+      ptx::tmem_ld_frag4(tq + col_a + 32 * nh, ra);
+      ptx::tmem_ld_frag4(tq + col_b + 32 * nh, rb);
+      ptx::tmem_wait_ld();
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        a[j >> 2][j & 3] = __uint_as_float(ra[j]);
+        b[j >> 2][j & 3] = __uint_as_float(rb[j]);
+      }
+    };
+    auto narrow2 = [&](uint32_t col_a, float (&a)[2][4], uint32_t col_b, float (&b)[2][4]) {
+      uint32_t ra[8], rb[8];
+      ptx::tmem_ld_frag2(tq + col_a + 16 * nh, ra);
+      ptx::tmem_ld_frag2(tq + col_b + 16 * nh, rb);
+      ptx::tmem_wait_ld();
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        a[j >> 2][j & 3] = __uint_as_float(ra[j]);
+        b[j >> 2][j & 3] = __uint_as_float(rb[j]);
+      }
+    };
+    auto narrow = [&](uint32_t col, float (&a)[2][4]) {
+      uint32_t ra[8];
+      ptx::tmem_ld_frag2(tq + col + 16 * nh, ra);
+      ptx::tmem_wait_ld();
+#pragma unroll
+      for (int j = 0; j < 8; ++j) a[j >> 2][j & 3] = __uint_as_float(ra[j]);
+    };
+    // byte offsets of this thread's elements inside 128B-swizzled tiles (r0 & 7 = r1 & 7 = g)
+    const uint32_t row_off0 = r0 * 128 + 4 * c4, row_off1 = r1 * 128 + 4 * c4;
+    auto wide_off = [&](int nt) {  // column 32 nh + 8 nt + 2 c4 of a [64][128] tile (two halves 8192 apart)
+      return static_cast<uint32_t>((nh >> 1) * 8192 + (((((nh & 1) * 4 + nt) ^ g)) << 4));
+    };
+    auto narrow_off = [&](int nt) {  // column 16 nh + 8 nt + 2 c4 of a [64][64] tile
+      return static_cast<uint32_t>(((nh * 2 + nt) ^ g) << 4);
+    };
+    // sum over this thread's columns of acc .* M[rows r0 / r1][32 nh + ...]   (M = a [64][128] tile)
+    auto dot_rows = [&](const float (&acc)[4][4], const uint8_t* M, float& s0, float& s1) {
       s0 = 0.f; s1 = 0.f;
 #pragma unroll
-      for (int nt = 0; nt < 8; ++nt) {
-        const int col = nh * 64 + nt * 8 + 2 * c4;
-        const float2 a = unpack2<T>(ld_pair(M, 8192, r0, col)), b = unpack2<T>(ld_pair(M, 8192, r1, col));
+      for (int nt = 0; nt < 4; ++nt) {
+        const uint32_t o = wide_off(nt);
+        const float2 a = unpack2<T>(*reinterpret_cast<const uint32_t*>(M + row_off0 + o));
+        const float2 b = unpack2<T>(*reinterpret_cast<const uint32_t*>(M + row_off1 + o));
         s0 += acc[nt][0] * a.x + acc[nt][1] * a.y;
         s1 += acc[nt][2] * b.x + acc[nt][3] * b.y;
       }
     };
-    auto st_frag4 = [&](uint8_t* tile, const float (&acc)[4][4]) {  // [64][64] tile, columns 32 nh ..
+    auto st_wide = [&](uint8_t* tile, const float (&acc)[4][4], float f0, float f1) {  // [64][128] tile
+#pragma unroll
+      for (int nt = 0; nt < 4; ++nt) {
+        const uint32_t o = wide_off(nt);
+        *reinterpret_cast<uint32_t*>(tile + row_off0 + o) = pack2<T>(f0 * acc[nt][0], f0 * acc[nt][1]);
+        *reinterpret_cast<uint32_t*>(tile + row_off1 + o) = pack2<T>(f1 * acc[nt][2], f1 * acc[nt][3]);
+      }
+    };
+    auto st_narrow = [&](uint8_t* tile, const float (&acc)[2][4]) {  // [64][64] tile
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt) {
+        const uint32_t o = narrow_off(nt);
+        *reinterpret_cast<uint32_t*>(tile + row_off0 + o) = pack2<T>(acc[nt][0], acc[nt][1]);
+        *reinterpret_cast<uint32_t*>(tile + row_off1 + o) = pack2<T>(acc[nt][2], acc[nt][3]);
+      }
+    };
+    // rows r0 / r1 of a [64][128] result straight to global memory (ragged tail chunks)
+    auto st_global_rows = [&](T* base, int heads, int head, int t0, int valid, const float (&acc)[4][4], float f0, float f1) {
 #pragma unroll
       for (int nt = 0; nt < 4; ++nt) {
         const int col = nh * 32 + nt * 8 + 2 * c4;
-        st_pair(tile, 0, r0, col, pack2<T>(acc[nt][0], acc[nt][1]));
-        st_pair(tile, 0, r1, col, pack2<T>(acc[nt][2], acc[nt][3]));
+        if (r0 < valid)
+          *reinterpret_cast<uint32_t*>(base + (static_cast<int64_t>(t0 + r0) * heads + head) * kHeadDim + col) =
+              pack2<T>(f0 * acc[nt][0], f0 * acc[nt][1]);
+        if (r1 < valid)
+          *reinterpret_cast<uint32_t*>(base + (static_cast<int64_t>(t0 + r1) * heads + head) * kHeadDim + col) =
+              pack2<T>(f1 * acc[nt][2], f1 * acc[nt][3]);
       }
     };
 
@@ -367,9 +457,9 @@ bwd_chunk_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       const ChunkCoord cc = locate_chunk(chunk, p.cu_seqlens, p.chunk_offsets, p.num_seqs, p.seq_len);
       const int t0 = cc.seq_start + cc.local_chunk * kChunk;
       const int valid = min(kChunk, cc.seq_end - t0);
-      float dq_acc[8][4], dk_acc[8][4];  // rows r0 / r1, columns 64 nh ..; summed over the v-heads of the group
+      float dq_acc[4][4], dk_acc[4][4];  // rows r0 / r1, columns 32 nh ..; summed over the v-heads of the group
 #pragma unroll
-      for (int nt = 0; nt < 8; ++nt)
+      for (int nt = 0; nt < 4; ++nt)
 #pragma unroll
         for (int e = 0; e < 4; ++e) dq_acc[nt][e] = dk_acc[nt][e] = 0.f;
 
@@ -385,46 +475,48 @@ bwd_chunk_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         const float rho0 = (r0 < valid) ? __expf(gl - g0) : 0.f, rho1 = (r1 < valid) ? __expf(gl - g1) : 0.f;
         const float be0 = bs[r0], be1 = bs[r1];
         float dg_row[2] = {0.f, 0.f}, db_row[2] = {0.f, 0.f};
-        float dg_col[4][2];  // columns 32 nh + 8 nt + 2 c4 + {0, 1} of the 64 x 64 products
+        float dg_col[2][2];  // columns 16 nh + 8 nt + 2 c4 + {0, 1} of the 64 x 64 products
 #pragma unroll
-        for (int nt = 0; nt < 4; ++nt) dg_col[nt][0] = dg_col[nt][1] = 0.f;
+        for (int nt = 0; nt < 2; ++nt) dg_col[nt][0] = dg_col[nt][1] = 0.f;
         float dg_last = 0.f;
 
-        // ---- sum(h .* dh) straight from the tiles while level 0 runs: thread = (k, half of v)
+        // ---- sum(h .* dh) straight from the tiles while level 0 runs: thread = (k, quarter of v)
         {
-          const int k = tid & 127, vh = tid >> 7;
-          const uint8_t* hrow = smem + kOffH + vh * 16384 + k * 128;
+          const int k = tid & 127, vq = tid >> 7;
+          const uint8_t* hrow = smem + kOffH + (vq >> 1) * 16384 + k * 128;
           const uint8_t* dcol = smem + kOffDh + (k >> 6) * 16384 + (k & 7) * 2;
           const int kc = (k & 63) >> 3;
           float hd = 0.f;
 #pragma unroll 2
-          for (int j = 0; j < 8; ++j) {
+          for (int j = (vq & 1) * 4; j < (vq & 1) * 4 + 4; ++j) {
             const uint4 raw = *reinterpret_cast<const uint4*>(hrow + ((j ^ (k & 7)) << 4));
             const T* e = reinterpret_cast<const T*>(&raw);
 #pragma unroll
             for (int x = 0; x < 8; ++x) {
-              const int v = vh * 64 + j * 8 + x;
+              const int v = (vq >> 1) * 64 + j * 8 + x;
               const T d = *reinterpret_cast<const T*>(dcol + v * 128 + ((kc ^ (v & 7)) << 4));
               hd += Cvt<T>::to_f32(e[x]) * Cvt<T>::to_f32(d);
             }
           }
           dg_last += __expf(gl) * hd;
         }
-
         if (warp == 0) trace(step, 1);
+        // the tiles the previous item's dq / dk left through (dw, ds / dA areas) are rewritten from here on
+        if (tid == 0) ptx::tma_store_wait_read();
+        compute_sync();
+
         // ---- level 0, first pair: ds = s G .* (dO v_new^T) (rows of the sequence only), ds2 = ds .* (Q K^T)
         if (!(ok = wait(kC45, ph))) break;
         ptx::tc_fence_after_sync();
         if (warp == 0) trace(step, 2);
         {
-          float acc[4][4], pq[4][4];
-          frag4(kColP + 32 * nh, acc);
-          frag4(kColP + kBank1 + 32 * nh, pq);
+          float acc[2][4], pq[2][4];
+          narrow2(kColP, acc, kColP + kBank1, pq);
 #pragma unroll
-          for (int nt = 0; nt < 4; ++nt)
+          for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-              const int row = (e >> 1) ? r1 : r0, col = nh * 32 + nt * 8 + 2 * c4 + (e & 1);
+              const int row = (e >> 1) ? r1 : r0, col = nh * 16 + nt * 8 + 2 * c4 + (e & 1);
               const float w = p.scale * __expf(fminf(((e >> 1) ? g1 : g0) - gs[col], 0.f));
               const float ds = (col <= row && row < valid) ? acc[nt][e] * w : 0.f;
               acc[nt][e] = ds;
@@ -432,22 +524,17 @@ bwd_chunk_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
               dg_row[e >> 1] += ds2;
               dg_col[nt][e & 1] -= ds2;
             }
-          st_frag4(smem + kOffX, acc);
+          st_narrow(smem + kOffX, acc);
         }
-        // ---- dw = -du h^T
         if (warp == 0) trace(step, 3);
+        // ---- dw = -du h^T
         if (!(ok = wait(kC3, ph))) break;
         ptx::tc_fence_after_sync();
         if (warp == 0) trace(step, 4);
         {
-          float acc[8][4];
-          frag8(kColW + 64 * nh, acc);
-#pragma unroll
-          for (int nt = 0; nt < 8; ++nt) {
-            const int col = nh * 64 + nt * 8 + 2 * c4;
-            st_pair(smem + kOffDw, 8192, r0, col, pack2<T>(-acc[nt][0], -acc[nt][1]));
-            st_pair(smem + kOffDw, 8192, r1, col, pack2<T>(-acc[nt][2], -acc[nt][3]));
-          }
+          float acc[4][4];
+          wide(kColW, acc);
+          st_wide(smem + kOffDw, acc, -1.f, -1.f);
         }
         ptx::fence_proxy_async_smem();
         ptx::tc_fence_before_sync();
@@ -458,57 +545,60 @@ bwd_chunk_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         if (!(ok = wait(kCB, ph))) break;
         ptx::tc_fence_after_sync();
         if (warp == 0) trace(step, 6);
-        float a2[4][4];
+        float a2[2][4];
         {
-          float acc[8][4];
-          frag8(kColW + kBank1 + 64 * nh, acc);
+          float acc[4][4];
+          wide(kColW + kBank1, acc);
+          narrow(kColR, a2);
           float s0, s1;
           dot_rows(acc, sV, s0, s1);
           db_row[0] += s0; db_row[1] += s1;
-          T* dvg = static_cast<T*>(p.dv);
-#pragma unroll
-          for (int nt = 0; nt < 8; ++nt) {
-            const int col = nh * 64 + nt * 8 + 2 * c4;
-            if (r0 < valid)
-              *reinterpret_cast<uint32_t*>(dvg + (static_cast<int64_t>(t0 + r0) * p.num_v_heads + hv) * kHeadDim + col) =
-                  pack2<T>(be0 * acc[nt][0], be0 * acc[nt][1]);
-            if (r1 < valid)
-              *reinterpret_cast<uint32_t*>(dvg + (static_cast<int64_t>(t0 + r1) * p.num_v_heads + hv) * kHeadDim + col) =
-                  pack2<T>(be1 * acc[nt][2], be1 * acc[nt][3]);
+          if (valid == kChunk) {
+            // through the V tile (level 0 has read it, and so has every warp after the barrier) and one TMA store
+            compute_sync();
+            st_wide(sV, acc, be0, be1);
+            ptx::fence_proxy_async_smem();
+            compute_sync();
+            if (tid == 0) {
+              ptx::tma_store_3d(&tm_dv, sV, 0, hv, t0);
+              ptx::tma_store_3d(&tm_dv, sV + 8192, 64, hv, t0);
+              ptx::tma_store_commit();
+            }
+          } else {
+            st_global_rows(static_cast<T*>(p.dv), p.num_v_heads, hv, t0, valid, acc, be0, be1);
           }
-          frag4(kColR + 32 * nh, a2);
         }
-        // ---- T1 = dO h^T: dq += s gamma .* T1, dg += q . that;  T2 = v_new dh^T: dk += rho .* T2, dg -= k . that
         if (warp == 0) trace(step, 7);
+        // ---- T1 = dO h^T: dq += s gamma .* T1, dg += q . that;  T2 = v_new dh^T: dk += rho .* T2, dg -= k . that
         if (!(ok = wait(kCT, ph))) break;
         if (!(ok = wait(kLateFull, ph))) break;  // Q, K rows are read below (they landed before level 0 was issued)
         ptx::tc_fence_after_sync();
         if (warp == 0) trace(step, 8);
         {
-          float acc[8][4];
-          frag8(kColT + 64 * nh, acc);
+          float acc[4][4], acc2[4][4];
+          wide2(kColT, acc, kColT + kBank1, acc2);
           const float f0 = p.scale * gam0, f1 = p.scale * gam1;
 #pragma unroll
-          for (int nt = 0; nt < 8; ++nt) { acc[nt][0] *= f0; acc[nt][1] *= f0; acc[nt][2] *= f1; acc[nt][3] *= f1; }
+          for (int nt = 0; nt < 4; ++nt) {
+            acc[nt][0] *= f0; acc[nt][1] *= f0; acc[nt][2] *= f1; acc[nt][3] *= f1;
+            acc2[nt][0] *= rho0; acc2[nt][1] *= rho0; acc2[nt][2] *= rho1; acc2[nt][3] *= rho1;
+          }
           float s0, s1;
           dot_rows(acc, sQ, s0, s1);
           dg_row[0] += s0; dg_row[1] += s1;
-#pragma unroll
-          for (int nt = 0; nt < 8; ++nt)
-#pragma unroll
-            for (int e = 0; e < 4; ++e) dq_acc[nt][e] += acc[nt][e];
-          frag8(kColT + kBank1 + 64 * nh, acc);
-#pragma unroll
-          for (int nt = 0; nt < 8; ++nt) { acc[nt][0] *= rho0; acc[nt][1] *= rho0; acc[nt][2] *= rho1; acc[nt][3] *= rho1; }
-          dot_rows(acc, sK, s0, s1);
+          dot_rows(acc2, sK, s0, s1);
           dg_row[0] -= s0; dg_row[1] -= s1;
           dg_last += s0 + s1;
 #pragma unroll
-          for (int nt = 0; nt < 8; ++nt)
+          for (int nt = 0; nt < 4; ++nt)
 #pragma unroll
-            for (int e = 0; e < 4; ++e) dk_acc[nt][e] += acc[nt][e];
+            for (int e = 0; e < 4; ++e) {
+              dq_acc[nt][e] += acc[nt][e];
+              dk_acc[nt][e] += acc2[nt][e];
+            }
         }
-        // this warp no longer reads the tiles only level 0 uses (V was the last)
+        // this warp no longer reads the tiles only level 0 uses; the dv store must have read the V tile
+        if (tid == 0) ptx::tma_store_wait_read();
         ptx::tc_fence_before_sync();
         warp_arrive(&bars[kEarlyFree], lane);
         if (warp == 0) trace(step, 9);
@@ -518,43 +608,39 @@ bwd_chunk_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         ptx::tc_fence_after_sync();
         if (warp == 0) trace(step, 10);
         {
-          float acc[8][4];
-          frag8(kColQ + 64 * nh, acc);
+          float acc[4][4], acc2[4][4];
+          wide2(kColQ, acc, kColQ + kBank1, acc2);
 #pragma unroll
-          for (int nt = 0; nt < 8; ++nt)
+          for (int nt = 0; nt < 4; ++nt)
 #pragma unroll
-            for (int e = 0; e < 4; ++e) dq_acc[nt][e] += acc[nt][e];
-          frag8(kColQ + kBank1 + 64 * nh, acc);
-#pragma unroll
-          for (int nt = 0; nt < 8; ++nt)
-#pragma unroll
-            for (int e = 0; e < 4; ++e) dk_acc[nt][e] += acc[nt][e];
+            for (int e = 0; e < 4; ++e) {
+              dq_acc[nt][e] += acc[nt][e];
+              dk_acc[nt][e] += acc2[nt][e];
+            }
           // y = A^T dw: dk += (beta gamma) .* y ; dbeta += gamma * (y . k) ; dg += beta gamma * (y . k)
-          frag8(kColW + 64 * nh, acc);
+          float a1[2][4];
+          wide(kColW, acc);
+          narrow(kColP, a1);
           float s0, s1;
           dot_rows(acc, sK, s0, s1);
           db_row[0] += gam0 * s0; db_row[1] += gam1 * s1;
           dg_row[0] += be0 * gam0 * s0; dg_row[1] += be1 * gam1 * s1;
           const float f0 = be0 * gam0, f1 = be1 * gam1;
 #pragma unroll
-          for (int nt = 0; nt < 8; ++nt) {
+          for (int nt = 0; nt < 4; ++nt) {
             dk_acc[nt][0] += f0 * acc[nt][0]; dk_acc[nt][1] += f0 * acc[nt][1];
             dk_acc[nt][2] += f1 * acc[nt][2]; dk_acc[nt][3] += f1 * acc[nt][3];
           }
-        }
-        {
           // dA = (beta gamma)_d (dw K^T) + beta_d (du V^T), strictly lower
-          float a1[4][4];
-          frag4(kColP + 32 * nh, a1);
 #pragma unroll
-          for (int nt = 0; nt < 4; ++nt)
+          for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-              const int row = (e >> 1) ? r1 : r0, col = nh * 32 + nt * 8 + 2 * c4 + (e & 1);
+              const int row = (e >> 1) ? r1 : r0, col = nh * 16 + nt * 8 + 2 * c4 + (e & 1);
               const float val = bs[col] * (__expf(gs[col]) * a1[nt][e] + a2[nt][e]);
               a1[nt][e] = (col < row) ? val : 0.f;
             }
-          st_frag4(smem + kOffY, a1);
+          st_narrow(smem + kOffY, a1);
         }
         ptx::fence_proxy_async_smem();
         ptx::tc_fence_before_sync();
@@ -566,9 +652,9 @@ bwd_chunk_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         ptx::tc_fence_after_sync();
         if (warp == 0) trace(step, 12);
         {
-          float acc[4][4];
-          frag4(kColT + 32 * nh, acc);
-          st_frag4(smem + kOffX, acc);
+          float acc[2][4];
+          narrow(kColT, acc);
+          st_narrow(smem + kOffX, acc);
         }
         ptx::fence_proxy_async_smem();
         ptx::tc_fence_before_sync();
@@ -580,14 +666,13 @@ bwd_chunk_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         ptx::tc_fence_after_sync();
         if (warp == 0) trace(step, 14);
         {
-          float acc[4][4], kk[4][4], lb[4][4];
-          frag4(kColT + 64 + 32 * nh, acc);
-          frag4(kColR + kBank1 + 32 * nh, kk);
+          float acc[2][4], kk[2][4], lb[2][4];
+          narrow2(kColT + 64, acc, kColR + kBank1, kk);
 #pragma unroll
-          for (int nt = 0; nt < 4; ++nt)
+          for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-              const int row = (e >> 1) ? r1 : r0, col = nh * 32 + nt * 8 + 2 * c4 + (e & 1);
+              const int row = (e >> 1) ? r1 : r0, col = nh * 16 + nt * 8 + 2 * c4 + (e & 1);
               const float w = __expf(fminf(((e >> 1) ? g1 : g0) - gs[col], 0.f));
               const float dl = (col < row) ? -acc[nt][e] * w : 0.f;
               const float be = (e >> 1) ? be1 : be0;
@@ -597,34 +682,50 @@ bwd_chunk_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
               dg_row[e >> 1] += t;
               dg_col[nt][e & 1] -= t;
             }
-          st_frag4(smem + kOffY, acc);  // dL over dA (level 2 has read it)
-          st_frag4(smem + kOffX, lb);   // beta .* dL over M1 (level 3 has read it)
+          st_narrow(smem + kOffY, acc);  // dL over dA (level 2 has read it)
+          st_narrow(smem + kOffX, lb);   // beta .* dL over M1 (level 3 has read it)
         }
         ptx::fence_proxy_async_smem();
         ptx::tc_fence_before_sync();
         warp_arrive(&bars[kDlReady], lane);
         if (warp == 0) trace(step, 15);
 
+        // ---- partial sums of this head that do not depend on level 4 (they overlap its products)
+        float* rr = red + ph * kRedFloats;
+        {
+          const float a0 = quad_sum(dg_row[0]), a1 = quad_sum(dg_row[1]);
+          if (c4 == 0) {
+            rr[nh * 64 + r0] = a0;
+            rr[nh * 64 + r1] = a1;
+          }
+#pragma unroll
+          for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+              const float s = oct_sum(dg_col[nt][e]);
+              if (g == 0) rr[512 + mt * 64 + nh * 16 + nt * 8 + 2 * c4 + e] = s;
+            }
+          float s = dg_last;
+#pragma unroll
+          for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+          if (lane == 0) rr[768 + warp] = s;
+        }
+
         // ---- level 4: z = dL K: dbeta += z . k ; dk += beta .* z ;  dk += (beta .* dL)^T K
         if (!(ok = wait(kC4, ph))) break;
         ptx::tc_fence_after_sync();
         if (warp == 0) trace(step, 16);
         {
-          float acc[8][4];
-          frag8(kColW + 64 * nh, acc);
+          float acc[4][4], acc2[4][4];
+          wide2(kColW, acc, kColW + kBank1, acc2);
           float s0, s1;
           dot_rows(acc, sK, s0, s1);
           db_row[0] += s0; db_row[1] += s1;
 #pragma unroll
-          for (int nt = 0; nt < 8; ++nt) {
-            dk_acc[nt][0] += be0 * acc[nt][0]; dk_acc[nt][1] += be0 * acc[nt][1];
-            dk_acc[nt][2] += be1 * acc[nt][2]; dk_acc[nt][3] += be1 * acc[nt][3];
+          for (int nt = 0; nt < 4; ++nt) {
+            dk_acc[nt][0] += be0 * acc[nt][0] + acc2[nt][0]; dk_acc[nt][1] += be0 * acc[nt][1] + acc2[nt][1];
+            dk_acc[nt][2] += be1 * acc[nt][2] + acc2[nt][2]; dk_acc[nt][3] += be1 * acc[nt][3] + acc2[nt][3];
           }
-          frag8(kColW + kBank1 + 64 * nh, acc);
-#pragma unroll
-          for (int nt = 0; nt < 8; ++nt)
-#pragma unroll
-            for (int e = 0; e < 4; ++e) dk_acc[nt][e] += acc[nt][e];
         }
         // this warp no longer reads Q, K, A or tensor memory of this head
         ptx::tc_fence_before_sync();
@@ -632,97 +733,72 @@ bwd_chunk_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         if (warp == 0) trace(step, 17);
 
         // ---- reductions: dg (rows + columns + last), dbeta; chunk-local reverse cumulative sum of dg
-        compute_sync();
         {
-          const float a0 = quad_sum(dg_row[0]), a1 = quad_sum(dg_row[1]);
           const float b0 = quad_sum(db_row[0]), b1 = quad_sum(db_row[1]);
           if (c4 == 0) {
-            red[nh * 64 + r0] = a0; red[nh * 64 + r1] = a1;
-            red[128 + nh * 64 + r0] = b0; red[128 + nh * 64 + r1] = b1;
+            rr[256 + nh * 64 + r0] = b0;
+            rr[256 + nh * 64 + r1] = b1;
           }
-          float s = dg_last;
-#pragma unroll
-          for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
-          if (lane == 0) red2[warp] = s;
         }
         compute_sync();
-        float dg_c = 0.f, db_c = 0.f;
         if (tid < 64) {
-          dg_c = red[tid] + red[64 + tid];
-          db_c = red[128 + tid] + red[192 + tid];
+          float dg_c = 0.f, db_c = 0.f;
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            dg_c += rr[q * 64 + tid] + rr[512 + q * 64 + tid];
+            db_c += rr[256 + q * 64 + tid];
+          }
           if (tid == valid - 1) {
             float s = 0.f;
 #pragma unroll
-            for (int w = 0; w < 8; ++w) s += red2[w];
+            for (int w = 0; w < 16; ++w) s += rr[768 + w];
             dg_c += s;
           }
-        }
-        compute_sync();
-        {
-#pragma unroll
-          for (int nt = 0; nt < 4; ++nt)
-#pragma unroll
-            for (int e = 0; e < 2; ++e) {
-              const float s = oct_sum(dg_col[nt][e]);
-              if (g == 0) red[mt * 64 + nh * 32 + nt * 8 + 2 * c4 + e] = s;
-            }
-        }
-        compute_sync();
-        if (tid < 64) {
-          dg_c += red[tid] + red[64 + tid] + red[128 + tid] + red[192 + tid];
           if (tid >= valid) dg_c = 0.f;  // rows of the next sequence: they must not enter the suffix sum
-          red2[0] = 0.f;
-        }
-        compute_sync();
-        // suffix sum over the 64 tokens of the chunk (two warps): dg_raw[c] = sum_{c' >= c} dg_cum[c']
-        if (tid < 64) {
+          // suffix sum over the 64 tokens of the chunk (two warps): dg_raw[c] = sum_{c' >= c} dg_cum[c']
           float s = dg_c;
 #pragma unroll
           for (int off = 1; off < 32; off <<= 1) {
             const float n = __shfl_down_sync(0xffffffffu, s, off);
             if (lane + off < 32) s += n;
           }
-          if (tid == 32) red2[0] = s;  // total of tokens 32..63
-          __syncwarp();
-          red[tid] = s;
-        }
-        compute_sync();
-        if (tid < 64) {
-          float s = red[tid];
-          if (tid < 32) s += red2[0];
+          if (tid == 32) rr[784] = s;  // total of tokens 32..63
+          asm volatile("bar.sync 2, 64;" ::: "memory");
+          if (tid < 32) s += rr[784];
           if (tid < valid) {
             p.dg[(static_cast<int64_t>(t0) + tid) * p.num_v_heads + hv] = s;
             p.dbeta[(static_cast<int64_t>(t0) + tid) * p.num_v_heads + hv] = db_c;
           }
         }
-        compute_sync();  // red / red2 are rewritten by the next head
         if (warp == 0) trace(step, 18);
       }
       if (!ok) break;
 
-      // dq, dk of the k-head (already summed over its v-heads)
-      T* dqg = static_cast<T*>(p.dq);
-      T* dkg = static_cast<T*>(p.dk);
-#pragma unroll
-      for (int nt = 0; nt < 8; ++nt) {
-        const int col = nh * 64 + nt * 8 + 2 * c4;
-        if (r0 < valid) {
-          const int64_t o = (static_cast<int64_t>(t0 + r0) * p.num_k_heads + hk) * kHeadDim + col;
-          *reinterpret_cast<uint32_t*>(dqg + o) = pack2<T>(dq_acc[nt][0], dq_acc[nt][1]);
-          *reinterpret_cast<uint32_t*>(dkg + o) = pack2<T>(dk_acc[nt][0], dk_acc[nt][1]);
+      // dq, dk of the k-head (already summed over its v-heads): through the dw and ds / dA tile areas and TMA
+      // stores when the chunk is complete, row by row for a ragged tail
+      if (valid == kChunk) {
+        st_wide(smem + kOffDw, dq_acc, 1.f, 1.f);
+        st_wide(smem + kOffX, dk_acc, 1.f, 1.f);
+        ptx::fence_proxy_async_smem();
+        compute_sync();
+        if (tid == 0) {
+          ptx::tma_store_3d(&tm_dq, smem + kOffDw, 0, hk, t0);
+          ptx::tma_store_3d(&tm_dq, smem + kOffDw + 8192, 64, hk, t0);
+          ptx::tma_store_3d(&tm_dk, smem + kOffX, 0, hk, t0);
+          ptx::tma_store_3d(&tm_dk, smem + kOffX + 8192, 64, hk, t0);
+          ptx::tma_store_commit();
         }
-        if (r1 < valid) {
-          const int64_t o = (static_cast<int64_t>(t0 + r1) * p.num_k_heads + hk) * kHeadDim + col;
-          *reinterpret_cast<uint32_t*>(dqg + o) = pack2<T>(dq_acc[nt][2], dq_acc[nt][3]);
-          *reinterpret_cast<uint32_t*>(dkg + o) = pack2<T>(dk_acc[nt][2], dk_acc[nt][3]);
-        }
+      } else {
+        st_global_rows(static_cast<T*>(p.dq), p.num_k_heads, hk, t0, valid, dq_acc, 1.f, 1.f);
+        st_global_rows(static_cast<T*>(p.dk), p.num_k_heads, hk, t0, valid, dk_acc, 1.f, 1.f);
       }
     }
+    if (tid == 0) ptx::tma_store_wait_all();
   }
 
   ptx::tc_fence_before_sync();
   __syncthreads();
-  if (warp == 8) ptx::tmem_dealloc(tmem, 512);
+  if (warp == kComputeWarps) ptx::tmem_dealloc(tmem, 512);
 }
 
 // [rows, width] row-major tensor of 16-bit elements seen as a 3-D map with a unit middle extent
@@ -736,7 +812,7 @@ int launch_chunk_bwd(const BwdParams& p, int64_t total_tokens, int total_chunks_
                      cudaStream_t stream) {
   int rc = launch_bwd_scan(p, total_tokens, is_bf16, stream);
   if (rc != QLA_OK) return rc;
-  CUtensorMap tm_q, tm_k, tm_v, tm_vn, tm_do, tm_a, tm_h, tm_dh, tm_du;
+  CUtensorMap tm_q, tm_k, tm_v, tm_vn, tm_do, tm_a, tm_h, tm_dh, tm_du, tm_dq, tm_dk, tm_dv;
   const uint64_t state_rows = static_cast<uint64_t>(total_chunks_upper) * p.num_v_heads * kHeadDim;
   if ((rc = make_tmap_3d(&tm_q, p.q, total_tokens, p.num_k_heads, kHeadDim, 64, 64, true, is_bf16)) != QLA_OK) return rc;
   if ((rc = make_tmap_3d(&tm_k, p.k, total_tokens, p.num_k_heads, kHeadDim, 64, 64, true, is_bf16)) != QLA_OK) return rc;
@@ -747,6 +823,9 @@ int launch_chunk_bwd(const BwdParams& p, int64_t total_tokens, int total_chunks_
   if ((rc = make_tmap_rows(&tm_h, p.h, state_rows, kHeadDim, 128, is_bf16)) != QLA_OK) return rc;
   if ((rc = make_tmap_rows(&tm_dh, p.dh, state_rows, kHeadDim, 128, is_bf16)) != QLA_OK) return rc;
   if ((rc = make_tmap_rows(&tm_du, p.du, state_rows, kChunk, 128, is_bf16)) != QLA_OK) return rc;
+  if ((rc = make_tmap_3d(&tm_dq, p.dq, total_tokens, p.num_k_heads, kHeadDim, 64, 64, true, is_bf16)) != QLA_OK) return rc;
+  if ((rc = make_tmap_3d(&tm_dk, p.dk, total_tokens, p.num_k_heads, kHeadDim, 64, 64, true, is_bf16)) != QLA_OK) return rc;
+  if ((rc = make_tmap_3d(&tm_dv, p.dv, total_tokens, p.num_v_heads, kHeadDim, 64, 64, true, is_bf16)) != QLA_OK) return rc;
   const int total_items = total_chunks_upper * p.num_k_heads;
   int dev = 0, sms = 0;
   QLA_CHECK_CUDA(cudaGetDevice(&dev));
@@ -756,7 +835,7 @@ int launch_chunk_bwd(const BwdParams& p, int64_t total_tokens, int total_chunks_
   do {                                                                                                     \
     if ((rc = ensure_dynamic_smem<bwd_chunk_kernel<T, TR>>(kSmemBytes)) != QLA_OK) return rc;              \
     bwd_chunk_kernel<T, TR><<<grid, kThreads, kSmemBytes, stream>>>(tm_q, tm_k, tm_v, tm_vn, tm_do, tm_a, tm_h, tm_dh, \
-                                                                    tm_du, p, total_items);                \
+                                                                    tm_du, tm_dq, tm_dk, tm_dv, p, total_items); \
   } while (0)
   const bool traced = p.trace != nullptr;
   if (is_bf16) {
