@@ -403,9 +403,10 @@ def run_train(args, rank, world, device):
     dht = 0.1 * rn(B, H, K, V)
 
     def step():
-        g_cs, A, o, h, fs, vn = fq.chunk_gated_delta_rule_fwd(q, k, v, g, beta, initial_state=h0, output_h=True,
-                                                              output_v_new=True)
-        return fq.chunk_gated_delta_rule_bwd(q, k, v, g_cs, beta, A, do, dht=dht, initial_state=h0, h=h, v_new=vn)
+        g_cs, A, o, h, fs, vn, w = fq.chunk_gated_delta_rule_fwd(q, k, v, g, beta, initial_state=h0, output_h=True,
+                                                                 output_v_new=True, output_w=True)
+        return fq.chunk_gated_delta_rule_bwd(q, k, v, g_cs, beta, A, do, dht=dht, initial_state=h0, h=h, v_new=vn,
+                                             w=w)
 
     with ClockSampler(device.index or 0) as cs:
         ms = timed(step, args.steps, args.warmup, world, device)

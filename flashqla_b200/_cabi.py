@@ -71,7 +71,7 @@ class QlaChunkBwdArgs(C.Structure):
         ("beta_dtype", C.c_int32), ("flags", C.c_int32), ("scale", C.c_float),
         ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("g_cumsum", C.c_void_p),
         ("beta", C.c_void_p), ("A", C.c_void_p), ("h", C.c_void_p), ("v_new", C.c_void_p),
-        ("d_o", C.c_void_p), ("dht", C.c_void_p), ("cu_seqlens", C.c_void_p),
+        ("w", C.c_void_p), ("d_o", C.c_void_p), ("dht", C.c_void_p), ("cu_seqlens", C.c_void_p),
         ("dq", C.c_void_p), ("dk", C.c_void_p), ("dv", C.c_void_p), ("dbeta", C.c_void_p),
         ("dg", C.c_void_p), ("dh0", C.c_void_p), ("workspace", C.c_void_p),
         ("workspace_bytes", C.c_size_t), ("status", C.c_void_p),

@@ -186,6 +186,7 @@ def chunk_gated_delta_rule_fwd(
     A_log: Optional[torch.Tensor] = None,
     dt_bias: Optional[torch.Tensor] = None,
     beta_is_logit: bool = False,
+    output_w: bool = False,
 ):
     """Raw forward.  ``g`` is the per-token log decay; returns
     ``(g_cumsum, A, o, h | None, final_state | None[, v_new])`` where ``g_cumsum`` is the chunk-local
@@ -195,7 +196,9 @@ def chunk_gated_delta_rule_fwd(
     and k; ``A`` and ``h`` are then those of the normalised inputs.  Two more additions fold the layer's gate
     activations into the preparation kernel (the recurrent op always had them): with ``A_log`` / ``dt_bias``
     ``[Hv]`` the argument ``g`` is the raw gate input ``a`` and ``g = -exp(A_log) * softplus(a + dt_bias)``
-    is used; with ``beta_is_logit`` the argument ``beta`` holds logits and ``sigmoid(beta)`` is used."""
+    is used; with ``beta_is_logit`` the argument ``beta`` holds logits and ``sigmoid(beta)`` is used.  With
+    ``output_w`` the prepared chunk operand ``w = -(A diag(beta e^g) K)`` ``[B,T,Hv,128]`` is appended to the
+    result; the backward takes it back (``w=``) instead of rebuilding it from ``g_cumsum`` and ``A``."""
     B, T, Hk, Hv, N = _check_common(q, k, v, g, beta, initial_state, cu_seqlens, transpose_state_layout)
     if (A_log is None) != (dt_bias is None):
         raise ValueError("A_log and dt_bias go together")
@@ -237,10 +240,10 @@ def chunk_gated_delta_rule_fwd(
         act.update(beta_out=beta_act)
 
     plan = cp.get_plan(lens if lens is not None else [T] * B, Hv, dev) if auto_cp else None
+    w = new_w(k, beta)
     if plan is not None and plan.use_cp:
         # g_cumsum and A on the original sequences, then per-segment initial states, then the scan
         # over segments (segments are whole chunks, so chunk numbering is unchanged)
-        w = new_w(k, beta)
         _launch_fwd(q if rnorm is not None else None, k, None, g, beta, None, cu, g_cumsum, A, None, None, None, None,
                     scale, flags=_cabi.CHUNK_PREPARE_ONLY, w=w, rnorm=rnorm, **act)
         if beta_act is not None:
@@ -260,10 +263,13 @@ def chunk_gated_delta_rule_fwd(
         order = longest_first_order(cu_seqlens, dev) if cu_seqlens is not None else None
         _launch_fwd(q, k, v, g, beta, h0, cu, g_cumsum, A, o, h, v_new, final_state, scale,
                     flags=_cabi.CHUNK_TRANSPOSE_STATE if transpose_state_layout else 0, seq_order=order, rnorm=rnorm,
-                    **act)
+                    w=w, **act)
+    out = (g_cumsum, A, o, h, final_state)
     if output_v_new:
-        return g_cumsum, A, o, h, final_state, v_new
-    return g_cumsum, A, o, h, final_state
+        out += (v_new,)
+    if output_w:
+        out += (w,)
+    return out
 
 
 def chunk_gated_delta_rule_bwd(
@@ -281,10 +287,11 @@ def chunk_gated_delta_rule_bwd(
     h: Optional[torch.Tensor] = None,
     v_new: Optional[torch.Tensor] = None,
     transpose_state_layout: bool = False,
+    w: Optional[torch.Tensor] = None,
 ):
     """Raw backward.  ``g`` is the chunk-local cumulative gate and ``A`` the WY matrix returned by
-    ``chunk_gated_delta_rule_fwd``; ``h`` / ``v_new`` are the forward's optional outputs and are
-    recomputed by a state-only scan when missing.  Returns ``(dq, dk, dv, db, dg, dh0 | None)`` with
+    ``chunk_gated_delta_rule_fwd``; ``h`` / ``v_new`` / ``w`` are the forward's optional outputs: ``h`` and
+    ``v_new`` are recomputed by a state-only scan when missing, ``w`` by one preparation launch.  Returns ``(dq, dk, dv, db, dg, dh0 | None)`` with
     ``dg`` w.r.t. the raw per-token gate and ``dh0`` present iff ``initial_state`` is given (the
     oracle's convention, tests/ref_gdr.py:378)."""
     B, T, Hk, Hv, N = _check_common(q, k, v, g, beta, initial_state, cu_seqlens, transpose_state_layout)
@@ -311,8 +318,16 @@ def chunk_gated_delta_rule_bwd(
         n_chunks = B * ((T + CHUNK - 1) // CHUNK) if lens is None else sum((n + CHUNK - 1) // CHUNK for n in lens)
         h = torch.empty(n_chunks, Hv, 128, 128, dtype=q.dtype, device=dev)
         v_new = torch.empty_like(v)
-        _launch_fwd(None, k, v, None, beta, h0, cu, g_cumsum, A, None, h, v_new, None, scale,
-                    flags=flags | _cabi.CHUNK_STATE_ONLY | _cabi.CHUNK_A_GIVEN)
+        if w is None:  # the recomputation rebuilds w on its way: keep it
+            w = new_w(k, beta)
+            _launch_fwd(None, k, v, None, beta, h0, cu, g_cumsum, A, None, h, v_new, None, scale,
+                        flags=flags | _cabi.CHUNK_STATE_ONLY | _cabi.CHUNK_A_GIVEN, w=w)
+        else:
+            _launch_fwd(None, k, v, None, beta, h0, cu, g_cumsum, A, None, h, v_new, None, scale,
+                        flags=flags | _cabi.CHUNK_STATE_ONLY | _cabi.CHUNK_SKIP_PREPARE, w=w)
+    if w is None:
+        w = rebuild_w(k, beta, g_cumsum, A, cu)
+    w = w if w.is_contiguous() else w.contiguous()
     h = h if h.is_contiguous() else h.contiguous()
     v_new = v_new if v_new.is_contiguous() else v_new.contiguous()
 
@@ -327,7 +342,7 @@ def chunk_gated_delta_rule_bwd(
         batch=Bk, seq_len=Tk, num_seqs=N, num_k_heads=Hk, num_v_heads=Hv, qkv_dtype=_cabi.dtype_code(q.dtype),
         beta_dtype=_cabi.dtype_code(beta.dtype), flags=flags, scale=float(scale),
         q=_cabi.ptr(q), k=_cabi.ptr(k), v=_cabi.ptr(v), g_cumsum=_cabi.ptr(g_cumsum), beta=_cabi.ptr(beta),
-        A=_cabi.ptr(A), h=_cabi.ptr(h), v_new=_cabi.ptr(v_new), d_o=_cabi.ptr(do), dht=_cabi.ptr(dht),
+        A=_cabi.ptr(A), h=_cabi.ptr(h), v_new=_cabi.ptr(v_new), w=_cabi.ptr(w), d_o=_cabi.ptr(do), dht=_cabi.ptr(dht),
         cu_seqlens=_cabi.ptr(cu), dq=_cabi.ptr(dq), dk=_cabi.ptr(dk), dv=_cabi.ptr(dv), dbeta=_cabi.ptr(db),
         dg=_cabi.ptr(dg), dh0=_cabi.ptr(dh0), workspace=None, workspace_bytes=0,
         status=_cabi.ptr(device_status(dev)))
@@ -342,8 +357,8 @@ def chunk_gated_delta_rule_bwd(
 
 
 class ChunkGatedDeltaRuleFunction(torch.autograd.Function):
-    """Autograd wrapper (reference: chunk/__init__.py:185-290).  The forward keeps ``h`` and ``v_new``
-    so that the backward does not have to recompute the chunk states."""
+    """Autograd wrapper (reference: chunk/__init__.py:185-290).  The forward keeps ``h``, ``v_new`` and the
+    prepared operand ``w`` so that the backward does not have to recompute them."""
 
     @staticmethod
     @torch.amp.custom_fwd(device_type="cuda")
@@ -356,10 +371,10 @@ class ChunkGatedDeltaRuleFunction(torch.autograd.Function):
         out = chunk_gated_delta_rule_fwd(
             q, k, v, g, beta, scale=scale, initial_state=initial_state, cu_seqlens=cu_seqlens,
             output_final_state=output_final_state, output_h=need_grad, output_v_new=need_grad,
-            transpose_state_layout=transpose_state_layout)
+            transpose_state_layout=transpose_state_layout, output_w=need_grad)
         g_cumsum, A, o, h, final_state = out[:5]
-        v_new = out[5] if need_grad else None
-        ctx.save_for_backward(q, k, v, g_cumsum, beta, A, initial_state, cu_seqlens, h, v_new)
+        v_new, w = (out[5], out[6]) if need_grad else (None, None)
+        ctx.save_for_backward(q, k, v, g_cumsum, beta, A, initial_state, cu_seqlens, h, v_new, w)
         ctx.scale = scale
         ctx.transpose_state_layout = transpose_state_layout
         ctx.g_dtype, ctx.beta_dtype = g.dtype, beta.dtype
@@ -368,10 +383,10 @@ class ChunkGatedDeltaRuleFunction(torch.autograd.Function):
     @staticmethod
     @torch.amp.custom_bwd(device_type="cuda")
     def backward(ctx, do, dht):
-        q, k, v, g_cumsum, beta, A, initial_state, cu_seqlens, h, v_new = ctx.saved_tensors
+        q, k, v, g_cumsum, beta, A, initial_state, cu_seqlens, h, v_new, w = ctx.saved_tensors
         dq, dk, dv, db, dg, dh0 = chunk_gated_delta_rule_bwd(
             q, k, v, g_cumsum, beta, A, do, dht=dht, scale=ctx.scale, initial_state=initial_state,
-            cu_seqlens=cu_seqlens, h=h, v_new=v_new, transpose_state_layout=ctx.transpose_state_layout)
+            cu_seqlens=cu_seqlens, h=h, v_new=v_new, transpose_state_layout=ctx.transpose_state_layout, w=w)
         if dh0 is not None and initial_state is not None:
             dh0 = dh0.to(initial_state.dtype)
         return (dq, dk, dv, dg.to(ctx.g_dtype), db.to(ctx.beta_dtype), None, dh0, None, None, None, None)

@@ -166,7 +166,7 @@ extern "C" QLA_API int qla_chunk_bwd(const QlaChunkBwdArgs* args, void* stream_)
   QLA_CHECK_ARG(!varlen || a.batch == 1, "with cu_seqlens the batch size must be 1");
   QLA_CHECK_ARG(varlen || a.num_seqs == a.batch, "num_seqs must equal batch without cu_seqlens");
   QLA_CHECK_ARG(a.q && a.k && a.v && a.g_cumsum && a.beta && a.A && a.d_o, "NULL input tensor");
-  QLA_CHECK_SUPPORTED(a.h && a.v_new, "h and v_new from the forward are required");
+  QLA_CHECK_SUPPORTED(a.h && a.v_new && a.w, "h, v_new and w from the forward are required");
   QLA_CHECK_ARG(a.dq && a.dk && a.dv && a.dbeta && a.dg, "NULL output tensor");
   const int64_t total_tokens = static_cast<int64_t>(a.batch) * a.seq_len;
   if (total_tokens == 0) return QLA_OK;
@@ -185,7 +185,7 @@ extern "C" QLA_API int qla_chunk_bwd(const QlaChunkBwdArgs* args, void* stream_)
     if (rc != QLA_OK) return rc;
   }
   BwdParams p{};
-  p.q = a.q; p.k = a.k; p.v = a.v; p.v_new = a.v_new; p.d_o = a.d_o; p.A = a.A; p.h = a.h;
+  p.q = a.q; p.k = a.k; p.v = a.v; p.v_new = a.v_new; p.d_o = a.d_o; p.A = a.A; p.h = a.h; p.w = a.w;
   p.g_cumsum = a.g_cumsum; p.beta = a.beta; p.dht = a.dht; p.cu_seqlens = a.cu_seqlens;
   p.chunk_offsets = chunk_offsets; p.dh = ws + w.tables; p.du = ws + w.tables + w.dh;
   p.dq = a.dq; p.dk = a.dk; p.dv = a.dv; p.dbeta = a.dbeta; p.dg = a.dg; p.dh0 = a.dh0;

@@ -5,8 +5,10 @@
 //
 // Per chunk, walking from the last chunk to the first (dS1 = gradient of the state leaving the chunk):
 //   du  = Pg^T dO + rho .* (K dS1)                      Pg = s G .* (Q K^T), G[c,d] = exp(g_c - g_d), c >= d
-//   X   = -(beta gamma) .* (A^T du)
-//   dS0 = exp(gL) dS1 + (s gamma .* Q)^T dO + K^T X      -> dS1 of the chunk before; the last one is dh0
+//   dS0 = exp(gL) dS1 + (s gamma .* Q)^T dO + K^T X,    X = -(beta gamma) .* (A^T du)
+//       = exp(gL) dS1 + (s gamma .* Q)^T dO + w^T du     -> dS1 of the chunk before; the last one is dh0
+// with w = -(A diag(beta gamma) K), the operand the forward's preparation kernel produced for its own scan
+// (K^T X = sum_i w_i^T du_i): one product on the serial chain instead of two with a conversion between them.
 // du and the bf16 copy of every dS1 ("dh") go to the workspace the per-chunk kernel reads.
 //
 // The kernel mirrors the forward scan (chunk_fwd.cu): everything is computed TRANSPOSED so that each
@@ -14,14 +16,13 @@
 //   MMA0  D0[128,64]  = [K;Q] K^T            (SS)  rows 64..127 are P = Q K^T; state independent
 //   MMAu  Du0[128,64] = dO^T Pg              (SS)  A = dO tile read MN-major, B = Pg tile read MN-major
 //   MMA2  D2[128,64]  = dS1^T_bf16 K^T       (TS)  chain
-//   MMAx  Dx[128,64]  = du^T_bf16 (A diag(-beta gamma))      (TS, B = A tile read MN-major)  chain
 //   MMAq  dS^T[128,128] += dO^T (s gamma .* Q)              (SS, both operands MN-major)  off the chain
-//   MMA3  dS^T[128,128] += X^T_bf16 K                      (TS, B = K tile read MN-major)  chain
+//   MMA3  dS^T[128,128] += du^T_bf16 w                     (TS, B = w tile read MN-major)  chain
 // Thread v of a compute warpgroup owns TMEM lane v (column v of dS): it forms du = Du0 + rho .* D2, writes
 // the 16-bit operand of the next product back with tcgen05.st and its 128 bytes of du^T to the workspace.
 // Warp roles (384 threads): warps 0-7 compute (both warpgroups take half of the token columns of every
 // chain phase and half of the state columns of the state conversion), warp 8 TMA producer + gate vectors,
-// warp 9 MMA issuer, warps 10-11 operand tiles (A diag(-beta gamma) in place, Pg, s gamma .* Q in place).
+// warp 9 MMA issuer, warps 10-11 operand tiles (Pg, s gamma .* Q in place).
 // Every wait is a bounded mbarrier wait that raises the status word instead of hanging.
 #include "chunk_params.cuh"
 
@@ -32,16 +33,15 @@ namespace {
 constexpr uint32_t kColS = 0;       // fp32 dS^T, 128 columns
 constexpr uint32_t kColSbf = 128;   // 16-bit copy of dS^T (A operand of MMA2), 64 columns
 constexpr uint32_t kColD2 = 192;    // (K dS1)^T
-constexpr uint32_t kColDu0 = 256;   // (Pg^T dO)^T; the same columns hold Dx once du has been formed
-constexpr uint32_t kColDu16 = 320;  // 16-bit du^T (A operand of MMAx), 32 columns
-constexpr uint32_t kColX16 = 352;   // 16-bit X^T (A operand of MMA3), 32 columns
+constexpr uint32_t kColDu0 = 256;   // (Pg^T dO)^T
+constexpr uint32_t kColDu16 = 320;  // 16-bit du^T (A operand of MMA3), 32 columns
 constexpr uint32_t kColD0 = 384;    // [K;Q] K^T, two buffers of 64 columns (chunk parity)
 
 // ---- shared-memory map (offsets from a 1024-byte aligned base)
 constexpr uint32_t kStageKQ = 0;         // 32 KiB: half h (columns 64h..) = [K rows 8 KiB | Q rows 8 KiB]; SW128
 constexpr uint32_t kStageDO = 32768;     // 16 KiB: dO tile as two [64][64] halves, SW128
-constexpr uint32_t kStageA = 49152;      // 8 KiB: A tile [64][64], SW128; columns scaled in place
-constexpr uint32_t kStageBytes = 57344;  // 56 KiB
+constexpr uint32_t kStageW = 49152;      // 16 KiB: w tile as two [64][64] halves, SW128
+constexpr uint32_t kStageBytes = 65536;  // 64 KiB
 constexpr uint32_t kOffPg = 2 * kStageBytes;  // 2 x 8 KiB Pg tiles [c][d], SW128 (chunk parity)
 constexpr uint32_t kSmemBytes = kOffPg + 2 * 8192 + 1024;
 
@@ -49,7 +49,6 @@ struct alignas(16) Gates {
   float g2[64];    // g log2(e)
   float rho[64];   // exp(gL - g), 0 on padded rows
   float sgam[64];  // scale * exp(g), 0 on padded rows
-  float nbg[64];   // -beta * exp(g), 0 on padded rows
   float egl;
   int valid;
   int pad[2];
@@ -57,8 +56,8 @@ struct alignas(16) Gates {
 constexpr int kGateRing = 4;
 
 enum Bar {
-  kFull0 = 0, kFull1, kEmpty0, kEmpty1, kPDone0, kPDone1, kAbReady0, kAbReady1,
-  kPgReady, kQsReady, kD2Done, kDu0Done, kDuReady, kDxDone, kXReady, kSDone, kSbfReady, kSScaled,
+  kFull0 = 0, kFull1, kEmpty0, kEmpty1, kPDone0, kPDone1,
+  kPgReady, kQsReady, kD2Done, kDu0Done, kDuReady, kSDone, kSbfReady, kSScaled,
   kNumBars
 };
 constexpr int kThreads = 384;
@@ -84,7 +83,7 @@ __device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
 template <typename T>
 __global__ void __launch_bounds__(kThreads, 1)
 bwd_scan_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                const __grid_constant__ CUtensorMap tm_do, const __grid_constant__ CUtensorMap tm_a,
+                const __grid_constant__ CUtensorMap tm_do, const __grid_constant__ CUtensorMap tm_w,
                 const BwdParams p) {
   constexpr uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? ptx::kFmtBF16 : ptx::kFmtF16;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -113,11 +112,11 @@ bwd_scan_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   if (tid == 0) {
 #pragma unroll 1
     for (int b = 0; b < kNumBars; ++b) {
-      int count = 1;  // commits: kPDone*, kD2Done, kDu0Done, kDxDone, kSDone
+      int count = 1;  // commits: kPDone*, kD2Done, kDu0Done, kSDone
       if (b == kFull0 || b == kFull1) count = 33;
       else if (b == kEmpty0 || b == kEmpty1) count = 3;
-      else if (b == kAbReady0 || b == kAbReady1 || b == kPgReady || b == kQsReady) count = 2;
-      else if (b == kDuReady || b == kXReady || b == kSbfReady || b == kSScaled) count = 8;
+      else if (b == kPgReady || b == kQsReady) count = 2;
+      else if (b == kDuReady || b == kSbfReady || b == kSScaled) count = 8;
       ptx::mbar_init(&bars[b], count);
     }
     ptx::fence_mbar_init();
@@ -149,8 +148,8 @@ bwd_scan_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           ptx::tma_prefetch_l2_3d(&tm_k, x, hk, pt0);
           ptx::tma_prefetch_l2_3d(&tm_q, x, hk, pt0);
           ptx::tma_prefetch_l2_3d(&tm_do, x, hv, pt0);
+          ptx::tma_prefetch_l2_3d(&tm_w, x, hv, pt0);
         }
-        ptx::tma_prefetch_l2_3d(&tm_a, 0, hv, pt0);
       }
       if (i < 0) continue;
       const int s = i & 1, use = i >> 1;
@@ -158,14 +157,12 @@ bwd_scan_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       const int valid = min(kChunk, seq_end - t0);
       const int64_t last_tok = static_cast<int64_t>(t0) + valid - 1;
       const float gl = p.g_cumsum[last_tok * p.num_v_heads + hv];
-      float gcv[2], bcv[2];
+      float gcv[2];
 #pragma unroll
       for (int r = 0; r < 2; ++r) {
         const int c = lane + 32 * r;
-        const bool okc = c < valid;
         const int64_t tok = static_cast<int64_t>(t0) + c;
-        gcv[r] = okc ? p.g_cumsum[tok * p.num_v_heads + hv] : gl;
-        bcv[r] = okc ? load_scalar(p.beta, p.beta_dtype, tok * p.num_v_heads + hv) : 0.f;
+        gcv[r] = c < valid ? p.g_cumsum[tok * p.num_v_heads + hv] : gl;
       }
       if (use > 0 && !wait(kEmpty0 + s, (use - 1) & 1)) break;
       uint8_t* st = stage_ptr(s);
@@ -177,8 +174,8 @@ bwd_scan_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           ptx::tma_load_3d(st + kStageKQ + h * 16384, &tm_k, full, h * 64, hk, t0);
           ptx::tma_load_3d(st + kStageKQ + h * 16384 + 8192, &tm_q, full, h * 64, hk, t0);
           ptx::tma_load_3d(st + kStageDO + h * 8192, &tm_do, full, h * 64, hv, t0);
+          ptx::tma_load_3d(st + kStageW + h * 8192, &tm_w, full, h * 64, hv, t0);
         }
-        ptx::tma_load_3d(st + kStageA, &tm_a, full, 0, hv, t0);
       }
       Gates* gs = gates_of(i);
 #pragma unroll
@@ -190,7 +187,6 @@ bwd_scan_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         gs->g2[c] = gc * 1.4426950408889634f;
         gs->rho[c] = ok ? __expf(gl - gc) : 0.f;
         gs->sgam[c] = ok ? p.scale * eg : 0.f;
-        gs->nbg[c] = -bcv[r] * eg;  // beta = 0 on padded rows
       }
       if (lane == 0) {
         gs->egl = __expf(gl);
@@ -202,7 +198,6 @@ bwd_scan_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     // =========================================================== MMA issuer (whole warp, converged)
     const uint32_t id_n64 = ptx::mma_idesc(128, 64, fmt, ptx::kMajorK, ptx::kMajorK);        // MMA0, MMA2
     const uint32_t id_u = ptx::mma_idesc(128, 64, fmt, ptx::kMajorMN, ptx::kMajorMN);       // MMAu
-    const uint32_t id_x = ptx::mma_idesc(128, 64, fmt, ptx::kMajorK, ptx::kMajorMN);        // MMAx
     const uint32_t id_s = ptx::mma_idesc(128, 128, fmt, ptx::kMajorK, ptx::kMajorMN);       // MMA3
     const uint32_t id_q = ptx::mma_idesc(128, 128, fmt, ptx::kMajorMN, ptx::kMajorMN);      // MMAq
     // descriptors of stage 0; stage 1 is kStageBytes further
@@ -210,7 +205,7 @@ bwd_scan_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const uint64_t d_kmn = ptx::smem_desc_sw128(ptx::smem_u32(smem + kStageKQ), 16384, 1024);       // K rows, MN-major
     const uint64_t d_qmn = ptx::smem_desc_sw128(ptx::smem_u32(smem + kStageKQ + 8192), 16384, 1024);  // Q rows, MN-major
     const uint64_t d_do = ptx::smem_desc_sw128(ptx::smem_u32(smem + kStageDO), 8192, 1024);         // dO, MN-major
-    const uint64_t d_a = ptx::smem_desc_sw128(ptx::smem_u32(smem + kStageA), 8192, 1024);           // A tile, MN-major
+    const uint64_t d_wmn = ptx::smem_desc_sw128(ptx::smem_u32(smem + kStageW), 8192, 1024);         // w tile, MN-major
     const uint64_t d_pg = ptx::smem_desc_sw128(ptx::smem_u32(smem + kOffPg), 8192, 1024);           // Pg, MN-major
     constexpr int kHalf = (16384 >> 4) - 3 * 2;  // from k-step 3 to k-step 4: the second 64-column half
     constexpr uint32_t tmem0 = 0;
@@ -250,15 +245,10 @@ bwd_scan_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             p0_issued = true;
           }
         }
-        // MMAx: Dx = du^T_bf16 (A diag(-beta gamma))
-        if (!(ok = wait(kAbReady0 + ph, (i >> 1) & 1))) break;
+        // MMA3: dS^T += du^T_bf16 w; its completion also releases the stage
         if (!(ok = wait(kDuReady, ph))) break;
         ptx::tc_fence_after_sync();
-        ptx::umma_ts_k64<128>(tmem0 + kColDu0, tmem0 + kColDu16, d_a + so, id_x, false, bar_addr(kDxDone));
-        // MMA3: dS^T += X^T_bf16 K; its completion also releases the stage
-        if (!(ok = wait(kXReady, ph))) break;
-        ptx::tc_fence_after_sync();
-        ptx::umma_ts_k64<128>(tmem0 + kColS, tmem0 + kColX16, d_kmn + so, id_s, true, bar_addr(kSDone),
+        ptx::umma_ts_k64<128>(tmem0 + kColS, tmem0 + kColDu16, d_wmn + so, id_s, true, bar_addr(kSDone),
                               bar_addr(kEmpty0 + ph));
       }
       // gap 2 (the compute warps convert the state): the state-independent products of the next chunk
@@ -269,7 +259,7 @@ bwd_scan_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           if (!(ok = wait(kFull0 + (j & 1), (j >> 1) & 1))) break;
           issue_mma0(j);
         }
-        // MMAu: Du0 = dO^T Pg (the compute warps read Dx of this chunk before XReady, MMA3 precedes in the pipe)
+        // MMAu: Du0 = dO^T Pg (the compute warps read Du0 of this chunk before DuReady, MMA3 precedes in the pipe)
         if (!(ok = wait(kPgReady, j & 1))) break;
         ptx::tc_fence_after_sync();
         ptx::umma_ss_k64<128, 128>(tmem0 + kColDu0, d_do + sn, d_pg + static_cast<uint64_t>((j & 1) * (8192 >> 4)),
@@ -291,24 +281,7 @@ bwd_scan_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       my_g[sj * 64 + lane] = gs->g2[lane];
       my_g[sj * 64 + 32 + lane] = gs->g2[32 + lane];
       const int valid = gs->valid;
-      // (a) A diag(-beta gamma): column d of the A tile times nbg[d], in place
-      uint8_t* at = stage_ptr(sj) + kStageA;
-#pragma unroll 1
-      for (int c16 = 0; c16 < 8; ++c16) {
-        uint4* ptr = reinterpret_cast<uint4*>(at + ptx::sw128_offset(r, c16));
-        uint4 raw = *ptr;
-        const float4 b0 = *reinterpret_cast<const float4*>(&gs->nbg[c16 * 8]);
-        const float4 b1 = *reinterpret_cast<const float4*>(&gs->nbg[c16 * 8 + 4]);
-        const T* e = reinterpret_cast<const T*>(&raw);
-        raw = make_uint4(pack2<T>(Cvt<T>::to_f32(e[0]) * b0.x, Cvt<T>::to_f32(e[1]) * b0.y),
-                         pack2<T>(Cvt<T>::to_f32(e[2]) * b0.z, Cvt<T>::to_f32(e[3]) * b0.w),
-                         pack2<T>(Cvt<T>::to_f32(e[4]) * b1.x, Cvt<T>::to_f32(e[5]) * b1.y),
-                         pack2<T>(Cvt<T>::to_f32(e[6]) * b1.z, Cvt<T>::to_f32(e[7]) * b1.w));
-        *ptr = raw;
-      }
-      ptx::fence_proxy_async_smem();
-      warp_arrive(&bars[kAbReady0 + sj], lane);
-      // (b) Pg = s G .* P from D0 rows 64..127 (TMEM quadrants 2, 3), rows beyond the sequence end zeroed.
+      // (a) Pg = s G .* P from D0 rows 64..127 (TMEM quadrants 2, 3), rows beyond the sequence end zeroed.
       // The Pg tile of this parity was last read by MMAu two chunks ago, which precedes this chunk's MMA0 in
       // the tensor pipe and therefore has completed when PDone fires.
       if (!(ok = wait(kPDone0 + sj, (j >> 1) & 1))) break;
@@ -340,7 +313,7 @@ bwd_scan_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       ptx::fence_proxy_async_smem();
       ptx::tc_fence_before_sync();
       warp_arrive(&bars[kPgReady], lane);
-      // (c) Q rows times s gamma (0 beyond the sequence end), in place: MMA0 has read the raw tile
+      // (b) Q rows times s gamma (0 beyond the sequence end), in place: MMA0 has read the raw tile
       const float f = gs->sgam[r];
 #pragma unroll 1
       for (int h = 0; h < 2; ++h) {
@@ -425,7 +398,7 @@ bwd_scan_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       const int chunk = chunk_of(i);
       const Gates* gs = gates_of(i);
       // ---------------- du^T = Du0 + rho .* D2 for this warpgroup's 32 tokens: 16-bit copy into tensor memory
-      // (A operand of MMAx) and to the workspace
+      // (A operand of MMA3) and to the workspace
       if (!(alive = wait(kD2Done, ph))) break;
       if (!(alive = wait(kDu0Done, ph))) break;
       ptx::tc_fence_after_sync();
@@ -450,20 +423,6 @@ bwd_scan_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 #pragma unroll
         for (int j = 0; j < 16; j += 4)
           *reinterpret_cast<uint4*>(dup + 2 * j) = make_uint4(pk[j], pk[j + 1], pk[j + 2], pk[j + 3]);
-      }
-      // ---------------- X^T: 16-bit copy of Dx into tensor memory (A operand of MMA3)
-      if (!(alive = wait(kDxDone, ph))) break;
-      ptx::tc_fence_after_sync();
-      {
-        uint32_t x[32], pk[16];
-        ptx::tmem_ld32(tm + kColDu0 + 32 * wg, x);
-        ptx::tmem_wait_ld();
-#pragma unroll
-        for (int j = 0; j < 32; j += 2) pk[j >> 1] = pack2<T>(__uint_as_float(x[j]), __uint_as_float(x[j + 1]));
-        ptx::tmem_st16(tm + kColX16 + 16 * wg, pk);
-        ptx::tmem_wait_st();
-        ptx::tc_fence_before_sync();
-        warp_arrive(&bars[kXReady], lane);
       }
       // ---------------- state conversion after MMA3 (this warpgroup's 64 columns)
       if (!(alive = wait(kSDone, ph))) break;
@@ -524,19 +483,19 @@ bwd_scan_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 }  // namespace
 
 int launch_bwd_scan(const BwdParams& p, int64_t total_tokens, bool is_bf16, cudaStream_t stream) {
-  CUtensorMap tm_q, tm_k, tm_do, tm_a;
+  CUtensorMap tm_q, tm_k, tm_do, tm_w;
   int rc;
   if ((rc = make_tmap_3d(&tm_k, p.k, total_tokens, p.num_k_heads, kHeadDim, 64, 64, true, is_bf16)) != QLA_OK) return rc;
   if ((rc = make_tmap_3d(&tm_q, p.q, total_tokens, p.num_k_heads, kHeadDim, 64, 64, true, is_bf16)) != QLA_OK) return rc;
   if ((rc = make_tmap_3d(&tm_do, p.d_o, total_tokens, p.num_v_heads, kHeadDim, 64, 64, true, is_bf16)) != QLA_OK) return rc;
-  if ((rc = make_tmap_3d(&tm_a, p.A, total_tokens, p.num_v_heads, 64, 64, 64, true, is_bf16)) != QLA_OK) return rc;
+  if ((rc = make_tmap_3d(&tm_w, p.w, total_tokens, p.num_v_heads, kHeadDim, 64, 64, true, is_bf16)) != QLA_OK) return rc;
   const unsigned grid = static_cast<unsigned>(p.num_seqs) * p.num_v_heads;
   if (is_bf16) {
     if ((rc = ensure_dynamic_smem<bwd_scan_kernel<__nv_bfloat16>>(kSmemBytes)) != QLA_OK) return rc;
-    bwd_scan_kernel<__nv_bfloat16><<<grid, kThreads, kSmemBytes, stream>>>(tm_q, tm_k, tm_do, tm_a, p);
+    bwd_scan_kernel<__nv_bfloat16><<<grid, kThreads, kSmemBytes, stream>>>(tm_q, tm_k, tm_do, tm_w, p);
   } else {
     if ((rc = ensure_dynamic_smem<bwd_scan_kernel<__half>>(kSmemBytes)) != QLA_OK) return rc;
-    bwd_scan_kernel<__half><<<grid, kThreads, kSmemBytes, stream>>>(tm_q, tm_k, tm_do, tm_a, p);
+    bwd_scan_kernel<__half><<<grid, kThreads, kSmemBytes, stream>>>(tm_q, tm_k, tm_do, tm_w, p);
   }
   QLA_CHECK_CUDA(cudaGetLastError());
   return QLA_OK;

@@ -56,6 +56,7 @@ struct BwdParams {
   const void* v_new;            // [NT, Hv, 128] saved by the forward
   const void* d_o;              // [NT, Hv, 128]
   const void* A;                // [NT, Hv, 64]
+  const void* w;                // [NT, Hv, 128] -(A diag(beta gamma) K), the forward's prepared operand
   const void* h;                // [chunks, Hv, 128, 128] state entering every chunk, saved by the forward
   const float* g_cumsum;        // [NT, Hv]
   const void* beta;             // [NT, Hv]

@@ -228,8 +228,9 @@ QLA_API int qla_chunk_fwd_noalloc(const QlaChunkFwdArgs* args, void* stream);
  * Replaces chunk_gated_delta_rule_bwd, flash_qla/ops/gated_delta_rule/chunk/__init__.py:89-182
  * (fused_gdr_bwd chunk/hopper/fused_bwd.py:898, the decomposed stages chunk/blackwell/bwd_sm12x.py:768-780,
  * group_reduce_vector ops/utils/group_reduce.py:60, reverse chunk_local_cumsum ops/utils/cumsum.py:134).
- * g_cumsum, A, h and v_new are the tensors qla_chunk_fwd produced for the same inputs (h with one entry
- * per chunk: the state entering it; v_new = the "new values" of every token).  dq / dk come out already
+ * g_cumsum, A, w, h and v_new are the tensors qla_chunk_fwd produced for the same inputs (h with one entry
+ * per chunk: the state entering it; v_new = the "new values" of every token; w = the prepared operand, which
+ * QLA_CHUNK_PREPARE_ONLY | QLA_CHUNK_A_GIVEN rebuilds from g_cumsum and A when it was not kept).  dq / dk come out already
  * summed over the v-heads that share a k-head; dg is already mapped back from cumulative to per-token
  * gates.  dh0 is written iff the pointer is non-NULL.
  * Workspace: qla_chunk_bwd_workspace_bytes(args) bytes, 16-byte aligned.
@@ -252,6 +253,7 @@ typedef struct QlaChunkBwdArgs {
   const void* A;
   const void* h;
   const void* v_new;
+  const void* w;            /* [B,T,Hv,128] as in QlaChunkFwdArgs                               */
   const void* d_o;          /* gradient of o                                                     */
   const float* dht;         /* gradient of the final state or NULL                               */
   const int32_t* cu_seqlens;

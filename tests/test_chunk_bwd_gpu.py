@@ -42,12 +42,12 @@ def _report(got: dict, ref: dict, rms_tol=None):
 def _raw_bwd(fq, c, cu=None, with_h0=True, with_dht=True, saved=True):
     h0 = c.get("h0") if with_h0 else None
     out = fq.chunk_gated_delta_rule_fwd(c["q"], c["k"], c["v"], c["g"], c["beta"], initial_state=h0,
-                                        cu_seqlens=cu, output_h=saved, output_v_new=saved)
+                                        cu_seqlens=cu, output_h=saved, output_v_new=saved, output_w=saved)
     g_cs, A, o, h, fs = out[:5]
-    v_new = out[5] if saved else None
+    v_new, w = (out[5], out[6]) if saved else (None, None)  # not saved: h, v_new and w are recomputed
     res = fq.chunk_gated_delta_rule_bwd(c["q"], c["k"], c["v"], g_cs, c["beta"], A, c["do"],
                                         dht=c["dht"] if with_dht else None, initial_state=h0, cu_seqlens=cu,
-                                        h=h, v_new=v_new)
+                                        h=h, v_new=v_new, w=w)
     fq.check_device_status()
     return dict(zip(GRADS, res))
 
