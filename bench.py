@@ -144,6 +144,23 @@ def timed(fn, steps, warmup, world, device, flush_l2=False):
     return ms
 
 
+MIN_TIMED_SECONDS = 1.0
+MAX_BLOCKS = 400
+
+
+def measure(fn, steps, warmup, world, device, flush_l2=False, min_seconds=None):
+    """Median over repeated blocks of exactly K timed steps (``timed``): the block is repeated until the timed
+    regions add up to at least ``MIN_TIMED_SECONDS`` (at most ``MAX_BLOCKS`` blocks), so that clocks and power
+    have settled and the clock sampler sees the region.  Every rank runs the same number of blocks (the count
+    comes from the first block's max-over-ranks time).  Returns (ms of the median block, number of blocks)."""
+    min_seconds = MIN_TIMED_SECONDS if min_seconds is None else min_seconds
+    first = timed(fn, steps, warmup, world, device, flush_l2=flush_l2)
+    blocks = int(min(MAX_BLOCKS, max(1, -(-min_seconds * 1e3 // max(first, 1e-6)))))
+    times = [first] + [timed(fn, steps, 0, world, device, flush_l2=flush_l2) for _ in range(blocks - 1)]
+    times.sort()
+    return times[len(times) // 2], len(times)
+
+
 # ------------------------------------------------------------------------------------ workloads
 def SCAN_DRAM_BYTES_PER_TOKEN_HEADS(Hk, Hv):
     """DRAM bytes per token moved by one launch of the chunk scan: dram__bytes_read + dram__bytes_write of an
@@ -214,14 +231,14 @@ def run_prefill(args, rank, world, device, varlen=False):
     in_bytes = sum(t.numel() * t.element_size() for t in dev.values())
     flush_l2 = in_bytes < 2 * L2_BYTES  # head shards of 4 and 8 GPUs: the inputs of a rank would fit the L2
     with ClockSampler(torch.cuda.current_device() if device.index is None else device.index) as cs:
-        ms = timed(step, args.steps, args.warmup, world, device, flush_l2=flush_l2)
+        ms, blocks = measure(step, args.steps, args.warmup, world, device, flush_l2=flush_l2)
     fq.check_device_status()
 
     # ---- dominant kernel alone (the chunk scan), for the roofline entry
     g_cs, A, o, _, fs = step()
     scan_only = fq.chunk.make_scan_only(dev["q"], dev["k"], dev["v"], dev["beta"], g_cs, A, o, fs,
                                         initial_state=h0, cu_seqlens=cu_dev)
-    ms_scan = timed(scan_only, args.steps, args.warmup, world, device, flush_l2=flush_l2) / args.steps
+    ms_scan = measure(scan_only, args.steps, args.warmup, world, device, flush_l2=flush_l2, min_seconds=0.2)[0] / args.steps
 
     # ---- end to end through the public API with host buffers
     o_host = torch.empty(o.shape, dtype=o.dtype).pin_memory()
@@ -271,7 +288,7 @@ def run_prefill(args, rank, world, device, varlen=False):
     line = {
         "metric": "gdn_prefill_fwd_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_step, "higher_is_better": True,
-        "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "blocks": blocks,
         "config": {"workload": workload, "sharding": f"v-heads/{world}" if not varlen else f"sequences/{world}",
                    "context_parallel": use_cp, "launch": launch_mode,
                    "l2": (f"inputs of a rank ({in_bytes / 1e6:.0f} MB) exceed the 126 MB L2; no flush needed" if not flush_l2
@@ -281,7 +298,7 @@ def run_prefill(args, rank, world, device, varlen=False):
         "clocks": cs.summary(),
         "e2e": {"value": total_tokens / (ms_e2e / e2e_steps * 1e-3), "unit": "tokens/s",
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e / e2e_steps},
-        "gpu_launches": launches_per_step * args.steps,
+        "gpu_launches": launches_per_step * args.steps * blocks,
         # The chunk scan is the dominant kernel.  Its intensity (163 840 flop and 24 832 B per token at this
         # shape) is below the B200 ridge, so HBM is the binding roof; the tensor figures are given beside it.
         # traffic: DRAM bytes of one launch from an ncu capture (bytes per token measured on a smaller case
@@ -290,6 +307,8 @@ def run_prefill(args, rank, world, device, varlen=False):
         "roofline": {"kernel": "chunk_fwd_kernel", "bound": "hbm", "achieved": gbs_scan, "peak": pk["hbm"],
                      "unit": "GB/s", "frac": gbs_scan / pk["hbm"], "peak_source": pk["src"],
                      "ms_per_launch": ms_scan,
+                     # the same algorithmic bytes over the WHOLE call (preparation + context-parallel passes + scan)
+                     "whole_call_frac": algo_bytes / (per_step * 1e-3) / 1e9 / pk["hbm"],
                      "traffic": None if varlen else SCAN_DRAM_BYTES_PER_TOKEN_HEADS(Hk, Hv) * T,
                      "tensor_achieved_tflops": achieved, "tensor_peak_tflops": pk["tf_burst"],
                      "tensor_frac": achieved / pk["tf_burst"]},
@@ -315,17 +334,17 @@ def run_prefill_sp(args, rank, world, device):
         fq.chunk_gated_delta_rule_fwd_sp(c["q"], c["k"], c["v"], c["g"], c["beta"])
 
     with ClockSampler(device.index) as clocks:
-        ms = timed(step, args.steps, args.warmup, world, device)
+        ms, blocks = measure(step, args.steps, args.warmup, world, device)
     ms_step = ms / args.steps
     tps = T / (ms_step * 1e-3)
     return {
         "metric": "gdn_prefill_fwd_tokens_per_s", "value": tps, "unit": "tokens/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
-        "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "blocks": blocks,
         "config": {"workload": f"prefill_fwd_B1_T{T}_Hk16_Hv32_K128_V128_chunk64", "sharding": f"tokens/{world}",
                    "exchange": f"one all_gather of {2 * Hv * 65536} B per rank", "launch": "eager",
                    "l2": "inputs exceed the 126 MB L2; no flush needed", "tokens": T},
-        "clocks": clocks.summary(), "gpu_launches": args.steps * 7}
+        "clocks": clocks.summary(), "gpu_launches": args.steps * 7 * blocks}
 
 
 def run_recurrent(args, rank, world, device, verify: bool):
@@ -360,22 +379,41 @@ def run_recurrent(args, rank, world, device, verify: bool):
             intermediate_states_buffer=inter, block_dv=args.block_dv)
 
     with ClockSampler(device.index or 0) as cs:
-        ms = timed(step, args.steps, args.warmup, world, device)
+        ms, blocks = measure(step, args.steps, args.warmup, world, device)
     per_step = ms / args.steps
+    same_box = None
+    if args.compare_fla and not verify:
+        # same-box bar: FLA's Triton recurrent kernel on the same inputs (what the reference compares its decode
+        # kernels with); it returns the new states instead of updating the pool in place
+        try:
+            from fla.ops.gated_delta_rule import fused_recurrent_gated_delta_rule as fla_update
+            cu_fla = torch.arange(N + 1, device=device, dtype=torch.long)
+            fla_step = lambda: fla_update(q, k, v, g=g, beta=beta, scale=K ** -0.5, initial_state=pools[0],
+                                          output_final_state=True, use_qk_l2norm_in_kernel=False, cu_seqlens=cu_fla,
+                                          transpose_state_layout=True)
+            ms_fla = measure(fla_step, args.steps, args.warmup, world, device, min_seconds=0.3)[0] / args.steps
+            same_box = {"impl": "fla %s fused_recurrent_gated_delta_rule (Triton)" % __import__("fla").__version__,
+                        "ms_per_step": ms_fla}
+        except Exception as exc:
+            same_box = {"impl": "fla fused_recurrent_gated_delta_rule", "unavailable": f"{type(exc).__name__}: {str(exc)[:160]}"}
     cache_b = 0 if not verify else (2 if args.bf16_scratch else 4)
     nbytes = orc.state_bytes_decode(N, Hv, T=T, Hk=Hk, cache_bytes=cache_b, write_back=not verify)
     gbs = nbytes * world / (per_step * 1e-3) / 1e9
     pk = peaks()
+    if same_box is not None and "ms_per_step" in same_box:
+        same_box["gb_per_s"] = nbytes * world / (same_box["ms_per_step"] * 1e-3) / 1e9
     return {
+        **({"same_box": same_box} if same_box is not None else {}),
         "metric": "gdn_%s_hbm_gb_per_s" % ("verify" if verify else "decode"), "value": gbs, "unit": "GB/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_step,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "blocks": blocks,
         "config": {"workload": f"{'verify_T4' if verify else 'decode_T1'}_N{N_all}_Hk16_Hv32",
                    "scratch": None if not verify else ("bf16" if args.bf16_scratch else "fp32"),
                    "l2": ("state pool (>= 0.5 GB) exceeds the 126 MB L2" if copies == 1 else
                           f"steps rotate over {copies} copies of the rank's pool (>= 0.5 GB together), so no step "
                           "finds its pool in the 126 MB L2")},
-        "clocks": cs.summary(), "gpu_launches": args.steps,
+        "clocks": cs.summary(), "gpu_launches": args.steps * blocks,
         "roofline": {"kernel": "recurrent_kernel", "bound": "hbm", "achieved": gbs / world, "peak": pk["hbm"],
                      "unit": "GB/s", "frac": gbs / world / pk["hbm"], "peak_source": pk["src"],
                      # ncu capture of the decode step (T=1, fp32 pool): 1.021 GB for 256 x 32 (sequence, v-head)
@@ -388,9 +426,16 @@ def run_train(args, rank, world, device):
     """Config 3: forward (saving h and v_new) + backward, B=4, T=8192, Hk=Hv=32, batch rows sharded."""
     import flashqla_b200 as fq
     from flashqla_b200.sharding import batch_shard
-    B_all, T, H = 4, args.tokens if args.tokens != 32768 else 8192, 32
-    rows = batch_shard(B_all, world, rank)
-    B = rows.stop - rows.start
+    B_all, T, H_all = 4, args.tokens if args.tokens != 32768 else 8192, 32
+    if world <= B_all:
+        rows = batch_shard(B_all, world, rank)
+        B, H = rows.stop - rows.start, H_all
+        sharding = f"batch/{world}"
+    else:  # more ranks than batch rows: every row's heads are split as well
+        per_row = world // B_all
+        assert world % B_all == 0 and H_all % per_row == 0
+        B, H = 1, H_all // per_row
+        sharding = f"batch/{B_all} x heads/{per_row}"
     gen = torch.Generator(device=device).manual_seed(3 + rank)
     rn = lambda *s: torch.randn(*s, generator=gen, device=device)
     q = torch.nn.functional.normalize(rn(B, T, H, K), dim=-1).bfloat16()
@@ -409,20 +454,21 @@ def run_train(args, rank, world, device):
                                              w=w)
 
     with ClockSampler(device.index or 0) as cs:
-        ms = timed(step, args.steps, args.warmup, world, device)
+        ms, blocks = measure(step, args.steps, args.warmup, world, device)
     fq.check_device_status()
     per_step = ms / args.steps
     tokens = B_all * T
-    flops = tokens * H * (163840 + 409600)
+    flops = tokens * H_all * (163840 + 409600)
     pk = peaks()
     return {
         "metric": "gdn_train_fwd_bwd_tokens_per_s", "value": tokens / (per_step * 1e-3), "unit": "tokens/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_step,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": f"train_fwd_bwd_B{B_all}_T{T}_Hk{H}_Hv{H}_K128_V128_chunk64", "sharding": f"batch/{world}",
+        "blocks": blocks,
+        "config": {"workload": f"train_fwd_bwd_B{B_all}_T{T}_Hk{H_all}_Hv{H_all}_K128_V128_chunk64", "sharding": sharding,
                    "l2": "inputs (>= 1 GB per step) exceed the 126 MB L2; no flush needed", "tokens": tokens},
-        "clocks": cs.summary(), "gpu_launches": 4 * args.steps,
-        "roofline": {"kernel": "fwd+bwd (all kernels)", "bound": "tensor", "achieved": flops / world / (per_step * 1e-3) / 1e12,
+        "clocks": cs.summary(), "gpu_launches": 4 * args.steps * blocks,
+        "roofline": {"kernel": "fwd+bwd (kkt_solve, chunk scan, bwd_scan, bwd_chunk)", "bound": "tensor", "achieved": flops / world / (per_step * 1e-3) / 1e12,
                      "peak": pk["tf_sus"], "unit": "TFLOP/s",
                      "frac": flops / world / (per_step * 1e-3) / 1e12 / pk["tf_sus"], "peak_source": pk["src"],
                      "traffic": None},
@@ -430,15 +476,41 @@ def run_train(args, rank, world, device):
 
 
 # ------------------------------------------------------------------------------------ CPU arms
-def cpu_prefill_sample(tokens_sample: int, repeats: int = 2):
-    """Oracle forward on the first `tokens_sample` tokens of the default workload, all host threads."""
+def reference_forward():
+    """The CPU forward the reference arm times: the reference's own fp32 PyTorch forward
+    (tests/ref_gdr.py, placed under oracle/_ref/ by oracle/build_ref.py where a checkout of the reference was
+    at hand) when it is there, else the oracle port.  Returns (callable, kind, description)."""
+    from oracle import gdr_oracle as orc
+    ref = ROOT / "oracle" / "_ref" / "ref_gdr.py"
+    if ref.exists():
+        try:
+            import importlib.util
+            spec = importlib.util.spec_from_file_location("_ref_gdr", ref)
+            mod = importlib.util.module_from_spec(spec)
+            spec.loader.exec_module(mod)
+            fwd = mod.chunk_gated_delta_rule_fwd
+
+            def run(inp):
+                return fwd(inp["q"].float(), inp["k"].float(), inp["v"].float(), inp["g"].clone(), inp["beta"],
+                           scale=128 ** -0.5)
+            return run, "reference", "the reference's tests/ref_gdr.py forward (fp32 PyTorch, all host threads)"
+        except Exception:  # missing dependency of the reference's file on this box: the port stands in
+            pass
+    return (lambda inp: orc.chunk_gdr_fwd(inp["q"], inp["k"], inp["v"], inp["g"], inp["beta"]), "port",
+            "fp32 oracle port (oracle/gdr_oracle.py, all host threads)")
+
+
+def cpu_prefill_sample(tokens_sample: int, repeats: int = 2, fn=None):
+    """CPU forward on the first `tokens_sample` tokens of the default workload, all host threads."""
     from oracle import gdr_oracle as orc
     torch.set_num_threads(os.cpu_count() or 1)
     inp = orc.make_prefill_inputs(1, tokens_sample, 16, 32, seed=1)
+    if fn is None:
+        fn = lambda i: orc.chunk_gdr_fwd(i["q"], i["k"], i["v"], i["g"], i["beta"])
     best = float("inf")
     for _ in range(repeats):
         t0 = time.perf_counter()
-        orc.chunk_gdr_fwd(inp["q"], inp["k"], inp["v"], inp["g"], inp["beta"])
+        fn(inp)
         best = min(best, time.perf_counter() - t0)
     return tokens_sample / best, best
 
@@ -455,6 +527,8 @@ def main():
     ap.add_argument("--block-dv", type=int, default=None, help="recurrent workloads: rows of V per CTA (16 or 32)")
     ap.add_argument("--cpu-sample-tokens", type=int, default=32768)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-secondary", action="store_true",
+                    help="default workload only: skip the decode / verify / varlen / train records")
     ap.add_argument("--eager", action="store_true", help="time plain calls instead of CUDA-graph replays")
     ap.add_argument("--compare-fla", action="store_true",
                     help="also time FLA's Triton forward on the same inputs (adds a same_box entry)")
@@ -466,18 +540,19 @@ def main():
         if rank != 0:
             return
         steps = max(1, min(args.steps, 3))
+        ref_fn, kind, what = reference_forward()
         vals = []
-        for _ in range(max(1, min(args.warmup, 1)) + steps):
-            tps, sec = cpu_prefill_sample(args.cpu_sample_tokens, repeats=1)
+        for _ in range(1 + steps):
+            tps, sec = cpu_prefill_sample(args.cpu_sample_tokens, repeats=1, fn=ref_fn)
             vals.append(tps)
         tps = sum(vals[-steps:]) / steps
-        sample = f"first {args.cpu_sample_tokens} tokens of the workload (all 32 v-heads), fp32 oracle port"
+        sample = f"first {args.cpu_sample_tokens} tokens of the workload (all 32 v-heads), {what}"
         print(json.dumps({
             "impl": "reference", "metric": "gdn_prefill_fwd_tokens_per_s", "value": tps, "unit": "tokens/s",
             "n_gpus": args.gpus, "steps": steps, "warmup": 1, "ms_per_step": args.cpu_sample_tokens / tps * 1e3,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": "prefill_fwd_B1_T32768_Hk16_Hv32_K128_V128_chunk64", "tokens": 32768},
-            "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",
+            "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": kind,
                              "sample": sample},
             "e2e": {"value": tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}))
@@ -499,12 +574,43 @@ def main():
         line = run_train(args, rank, world, device)
     else:
         line = run_recurrent(args, rank, world, device, verify=args.workload == "verify")
+    if args.workload == "prefill_fwd" and not args.no_secondary:
+        # the other metrics of the path, measured after the headline's timed region with the same rules; every
+        # rank takes part (the shards are those of the workloads themselves)
+        import copy
+        secondary = []
+        workloads = [("decode", {}), ("verify", {}), ("verify", {"bf16_scratch": True}), ("varlen", {}), ("train", {})]
+        if world > 1:  # the optional sequence-parallel mode: tokens over the ranks, one NCCL all-gather per call
+            workloads.append(("prefill_sp", {}))
+        for wl, extra in workloads:
+            a2 = copy.copy(args)
+            a2.workload, a2.steps, a2.tokens, a2.bf16_scratch = wl, min(args.steps, 20), 32768, False
+            a2.compare_fla = wl == "decode" and world == 1
+            for name, val in extra.items():
+                setattr(a2, name, val)
+            try:
+                if wl == "varlen":
+                    rec = run_prefill(a2, rank, world, device, varlen=True)
+                elif wl == "train":
+                    rec = run_train(a2, rank, world, device)
+                elif wl == "prefill_sp":
+                    rec = run_prefill_sp(a2, rank, world, device)
+                else:
+                    rec = run_recurrent(a2, rank, world, device, verify=wl == "verify")
+                rec = {k: rec[k] for k in ("metric", "value", "unit", "ms_per_step", "steps", "blocks", "config",
+                                           "roofline", "clocks", "gpu_launches", "same_box") if k in rec}
+            except Exception as exc:
+                rec = {"metric": wl, "error": f"{type(exc).__name__}: {str(exc)[:200]}"}
+            secondary.append(rec)
+        line["secondary"] = secondary
+        line["gpu_launches"] += sum(r.get("gpu_launches", 0) for r in secondary)
     if rank == 0:
         if not args.no_cpu_baseline and args.workload == "prefill_fwd" and world == 1:
-            tps, sec = cpu_prefill_sample(args.cpu_sample_tokens)
+            ref_fn, kind, what = reference_forward()
+            tps, sec = cpu_prefill_sample(args.cpu_sample_tokens, fn=ref_fn)
             line["cpu_baseline"] = {
-                "value": tps, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",
-                "sample": f"first {args.cpu_sample_tokens} of the 32768 tokens (all 32 v-heads), best of 2, "
+                "value": tps, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": kind,
+                "sample": f"first {args.cpu_sample_tokens} of the 32768 tokens (all 32 v-heads), {what}, best of 2, "
                           f"{sec:.2f} s"}
         print(json.dumps(line))
     if world > 1:

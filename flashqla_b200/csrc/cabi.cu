@@ -1,7 +1,7 @@
 // Status / error reporting of the C ABI (include/flashqla_b200.h).
 #include <stdarg.h>
 
-#include "common.cuh"
+#include "ptx_sm100.cuh"
 
 namespace qla {
 namespace {
@@ -31,3 +31,30 @@ extern "C" QLA_API const char* qla_status_string(int code) {
 extern "C" QLA_API const char* qla_last_error(void) { return qla::g_last_error; }
 
 extern "C" QLA_API int qla_abi_version(void) { return QLA_ABI_VERSION; }
+
+namespace qla {
+namespace {
+// One warp waits, with the bounded wait every kernel of the library uses, for a barrier phase that nothing
+// will ever complete: the wait gives up after `limit_ns`, records barrier / parity / warp in the status word
+// and the kernel returns normally.
+__global__ void bounded_wait_selftest_kernel(int* status, unsigned long long limit_ns) {
+  __shared__ uint64_t bar;
+  if (threadIdx.x == 0) {
+    ptx::mbar_init(&bar, 1);
+    ptx::fence_mbar_init();
+  }
+  __syncthreads();
+  const bool ok = ptx::mbar_wait_polling(&bar, 0, status, kStatusBarrierTimeout | (255 << 8), limit_ns);
+  if (ok && status != nullptr) atomicCAS(status, 0, kStatusBadIndex);  // cannot happen: nobody arrives
+}
+}  // namespace
+}  // namespace qla
+
+extern "C" QLA_API int qla_selftest_bounded_wait(int32_t* status, uint64_t limit_ns, void* stream) {
+  using namespace qla;
+  QLA_CHECK_ARG(status != nullptr, "status is NULL");
+  QLA_CHECK_ARG(limit_ns > 0 && limit_ns <= 1000000000ull, "limit_ns must be in (0, 1e9]");
+  bounded_wait_selftest_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(status, limit_ns);
+  QLA_CHECK_CUDA(cudaGetLastError());
+  return QLA_OK;
+}

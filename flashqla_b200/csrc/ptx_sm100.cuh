@@ -74,18 +74,23 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
 __device__ __forceinline__ void record_wait_failure(int* status, int code, uint32_t parity) {
   if (status != nullptr) atomicCAS(status, 0, code | static_cast<int>(parity << 16) | static_cast<int>((threadIdx.x >> 5) << 20));
 }
-static __device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, int* status, int code) {
+// The polling loop itself; `limit_ns` is kWaitLimitNs everywhere except in the self-test of this very path.
+__device__ __forceinline__ bool mbar_wait_polling(uint64_t* bar, uint32_t parity, int* status, int code,
+                                                  unsigned long long limit_ns) {
   const unsigned long long t0 = global_timer_ns();
   for (uint32_t i = 0; i < kSpinLimit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((i & 63u) == 63u) {
       if (status != nullptr && *reinterpret_cast<volatile int*>(status) != 0)
         return false;  // another role already failed: do not keep the SM busy
-      if (global_timer_ns() - t0 > kWaitLimitNs) break;
+      if (global_timer_ns() - t0 > limit_ns) break;
     }
   }
   record_wait_failure(status, code, parity);
   return false;
+}
+static __device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, int* status, int code) {
+  return mbar_wait_polling(bar, parity, status, code, kWaitLimitNs);
 }
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int code) {
   if (mbar_try_wait(bar, parity)) return true;

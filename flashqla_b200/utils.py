@@ -152,6 +152,17 @@ def _cache_get(cache: Dict, key: Tuple, cu_seqlens: torch.Tensor):
     return None
 
 
+def selftest_bounded_wait(device=None, limit_ms: float = 20.0) -> None:
+    """Launch the library's self-test kernel whose only wait can never complete: after ``limit_ms`` the bounded
+    wait gives up and records the fault in the device status word, which ``check_device_status`` then raises."""
+    from . import _cabi
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    st = device_status(dev)
+    with torch.cuda.device(dev):
+        code = _cabi.lib().qla_selftest_bounded_wait(st.data_ptr(), int(limit_ms * 1e6), _cabi.current_stream(dev))
+    _cabi.check(code, "qla_selftest_bounded_wait")
+
+
 def host_seqlens(cu_seqlens: torch.Tensor, total_tokens: Optional[int] = None) -> List[int]:
     """Sequence lengths as Python ints.  One device-to-host copy per distinct cu_seqlens tensor and content
     version; later calls with the same tensor object hit the cache.  ``total_tokens`` (the packed token

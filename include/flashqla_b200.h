@@ -322,6 +322,14 @@ QLA_API int qla_cp_chain(const QlaCpChainArgs* args, void* stream);
  */
 QLA_API int qla_set_trace_buffer(long long* device_buffer, size_t count);
 
+/*
+ * Self-test of the fault path (no counterpart in the reference, whose kernels wait without a bound): launches
+ * one warp that waits, with the bounded mbarrier wait every kernel of the library uses, for a barrier nothing
+ * completes.  After limit_ns (at most one second) the wait gives up, writes (1 | 255 << 8 | parity << 16 |
+ * warp << 20) to *status and the kernel returns; the context stays usable.
+ */
+QLA_API int qla_selftest_bounded_wait(int32_t* status, uint64_t limit_ns, void* stream);
+
 QLA_API const char* qla_status_string(int code);
 QLA_API const char* qla_last_error(void);
 QLA_API int qla_abi_version(void);

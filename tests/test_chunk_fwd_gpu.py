@@ -312,3 +312,15 @@ def test_gate_and_beta_activation_in_kernel(T, Hk, Hv, varlen):
                                         use_gate_in_kernel=True, A_log=A_log.cuda(), dt_bias=dt_bias.cuda(),
                                         use_beta_sigmoid_in_kernel=True, **kw)
     assert torch.equal(o2, o.to(o2.dtype)) and torch.equal(fs2, fs)
+
+
+def test_bounded_wait_runs_out_and_reports(fq):
+    """A wait that can never complete gives up after its limit and raises the status word instead of hanging;
+    afterwards the context is still usable (the next forward passes)."""
+    from flashqla_b200 import _cabi, utils
+    fq.check_device_status()
+    utils.selftest_bounded_wait(limit_ms=20.0)
+    with pytest.raises(_cabi.QlaError, match="bounded barrier wait timed out"):
+        fq.check_device_status()
+    fq.check_device_status()  # cleared
+    _run_case(fq, 1, 130, 1, 2, seed=5, with_h0=True)

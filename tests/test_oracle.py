@@ -80,3 +80,24 @@ def test_inverse_gate_roundtrip():
     a, b = orc.inverse_gate(g, beta)
     assert torch.allclose(-torch.nn.functional.softplus(a), g, atol=1e-5)
     assert torch.allclose(torch.sigmoid(b), beta, atol=1e-6)
+
+
+def test_oracle_agrees_with_the_reference_file_when_present():
+    """Where oracle/build_ref.py has placed the reference's own tests/ref_gdr.py under oracle/_ref/, the port and
+    the reference's forward agree on fresh seeded inputs (a tail chunk, GQA, an initial state)."""
+    import importlib.util
+    from pathlib import Path
+    import pytest
+    ref_file = Path(__file__).resolve().parents[1] / "oracle" / "_ref" / "ref_gdr.py"
+    if not ref_file.exists():
+        pytest.skip("no reference checkout was at hand when the library was built")
+    spec = importlib.util.spec_from_file_location("_ref_gdr", ref_file)
+    ref = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(ref)
+    inp = orc.make_prefill_inputs(2, 200, 2, 4, seed=11, dtype=torch.float32, with_h0=True)
+    g_cs, o, A, h, fs = ref.chunk_gated_delta_rule_fwd(inp["q"], inp["k"], inp["v"], inp["g"].clone(), inp["beta"],
+                                                       initial_state=inp["h0"], scale=128 ** -0.5)
+    mine = orc.chunk_gdr_fwd(inp["q"], inp["k"], inp["v"], inp["g"], inp["beta"], h0=inp["h0"])
+    assert orc.max_abs(mine["o"], o) <= 2e-5
+    assert orc.max_abs(mine["final_state"], fs) <= 2e-5
+    assert orc.max_abs(mine["g_cumsum"], g_cs) <= 2e-6
