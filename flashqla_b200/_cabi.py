@@ -19,7 +19,7 @@ _DTYPES = {torch.float32: QLA_DT_F32, torch.bfloat16: QLA_DT_BF16, torch.float16
 REC_QK_L2NORM, REC_DISABLE_STATE_UPDATE, REC_A_IS_LOG_DECAY, REC_B_IS_BETA = 1, 2, 4, 8
 CHUNK_TRANSPOSE_STATE, CHUNK_STATE_ONLY, CHUNK_QK_L2NORM, CHUNK_SKIP_PREPARE = 1, 2, 4, 8
 CHUNK_INIT_IDENTITY, CHUNK_ZERO_V, CHUNK_PREPARE_ONLY, CHUNK_A_GIVEN, CHUNK_TABLES_READY = 16, 32, 64, 128, 256
-CHUNK_GATE_ACT, CHUNK_BETA_LOGIT = 512, 1024
+CHUNK_GATE_ACT, CHUNK_BETA_LOGIT, CHUNK_H0_KV_F32, CHUNK_DUAL_TRANSITION, CHUNK_OUT_GATED_RMSNORM = 512, 1024, 2048, 4096, 8192
 
 
 class QlaError(RuntimeError):
@@ -61,6 +61,9 @@ class QlaChunkFwdArgs(C.Structure):
         ("seq_map", C.c_void_p), ("seq_order", C.c_void_p), ("chunk_limit", C.c_void_p), ("g_cumsum", C.c_void_p), ("A", C.c_void_p), ("w", C.c_void_p),
         ("qk_rnorm", C.c_void_p), ("A_log", C.c_void_p), ("dt_bias", C.c_void_p), ("beta_out", C.c_void_p), ("o", C.c_void_p), ("h", C.c_void_p), ("v_new", C.c_void_p), ("final_state", C.c_void_p),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("status", C.c_void_p),
+        ("h0_map", C.c_void_p), ("state_dtype", C.c_int32), ("reserved", C.c_int32),
+        ("chunk_limit_b", C.c_void_p), ("seq_map_b", C.c_void_p), ("final_state_b", C.c_void_p),
+        ("norm_gate", C.c_void_p), ("norm_weight", C.c_void_p), ("norm_eps", C.c_float), ("reserved2", C.c_int32),
     ]
 
 
@@ -92,6 +95,8 @@ class QlaCpPlanArgs(C.Structure):
         ("num_segments", C.c_int32), ("num_v_heads", C.c_int32), ("threshold", C.c_float),
         ("g_cumsum", C.c_void_p), ("cu_seqlens", C.c_void_p), ("seg_next", C.c_void_p),
         ("warm_limit", C.c_void_p), ("m_limit", C.c_void_p),
+        ("cp_h0", C.c_void_p), ("seg_start_of", C.c_void_p), ("h0", C.c_void_p), ("h0_map", C.c_void_p),
+        ("h0_dtype", C.c_int32), ("h0_transposed", C.c_int32),
     ]
 
 

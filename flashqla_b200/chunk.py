@@ -46,13 +46,16 @@ def _check_common(q, k, v, g, beta, initial_state, cu_seqlens, transpose_state_l
 
 def _launch_fwd(q, k, v, g, beta, h0, cu, g_cumsum, A, o, h, v_new, final_state, scale, flags=0,
                 seq_map=None, chunk_limit=None, num_seqs=None, w=None, tables=None, seq_order=None, rnorm=None,
-                A_log=None, dt_bias=None, beta_out=None):
+                A_log=None, dt_bias=None, beta_out=None, h0_map=None, dual=None, out_norm=None):
     """Fill ``QlaChunkFwdArgs`` from tensors and call ``qla_chunk_fwd`` on the current stream.  ``w`` is
     the per-chunk operand ``-(A diag(beta e^g) K)`` that the preparation step writes and the scan reads;
     it is allocated here when the call does both.  ``tables`` is an optional dict holding the ready-made
     chunk-table workspace of a fixed ``cu`` (``chunk_tables_workspace``: the segments of a context-parallel
     plan); calls that get it skip the table launch.  ``rnorm`` ``[B,T,Hk,2]`` switches the in-kernel q / k L2
-    norm on: the preparation step writes the reciprocal row norms there, the scan reads them."""
+    norm on: the preparation step writes the reciprocal row norms there, the scan reads them.  ``h0_map`` /
+    ``seq_map`` are per-sequence rows of ``h0`` / ``final_state`` (state pools; ``-1`` = zero state / no output);
+    the two share a dtype (fp32 or bf16).  ``dual = (chunk_limit_b, seq_map_b, final_state_b)`` adds the
+    transition-matrix pass of context parallelism to a state-only launch."""
     dev = k.device
     if w is None:
         assert not flags & _cabi.CHUNK_SKIP_PREPARE, "a scan without preparation needs the prepared w"
@@ -69,6 +72,17 @@ def _launch_fwd(q, k, v, g, beta, h0, cu, g_cumsum, A, o, h, v_new, final_state,
         flags |= _cabi.CHUNK_GATE_ACT
     if beta_out is not None:
         flags |= _cabi.CHUNK_BETA_LOGIT
+    state_dtype = torch.float32
+    for st in (final_state, h0 if not flags & _cabi.CHUNK_H0_KV_F32 else None):
+        if st is not None:
+            state_dtype = st.dtype
+    dual_args = {}
+    if out_norm is not None:  # (gate z, weight, eps): the gated RMS norm behind the op as an epilogue of the scan
+        flags |= _cabi.CHUNK_OUT_GATED_RMSNORM
+        dual_args.update(norm_gate=_cabi.ptr(out_norm[0]), norm_weight=_cabi.ptr(out_norm[1]), norm_eps=float(out_norm[2]))
+    if dual is not None:
+        flags |= _cabi.CHUNK_DUAL_TRANSITION
+        dual_args.update(chunk_limit_b=_cabi.ptr(dual[0]), seq_map_b=_cabi.ptr(dual[1]), final_state_b=_cabi.ptr(dual[2]))
     args = _cabi.QlaChunkFwdArgs(
         batch=B, seq_len=T, num_seqs=N, num_k_heads=Hk, num_v_heads=Hv,
         qkv_dtype=_cabi.dtype_code(k.dtype), gate_dtype=0 if g is None else _cabi.dtype_code(g.dtype),
@@ -78,7 +92,8 @@ def _launch_fwd(q, k, v, g, beta, h0, cu, g_cumsum, A, o, h, v_new, final_state,
         chunk_limit=_cabi.ptr(chunk_limit), g_cumsum=_cabi.ptr(g_cumsum), A=_cabi.ptr(A), w=_cabi.ptr(w), qk_rnorm=_cabi.ptr(rnorm),
         A_log=_cabi.ptr(A_log), dt_bias=_cabi.ptr(dt_bias), beta_out=_cabi.ptr(beta_out), o=_cabi.ptr(o),
         h=_cabi.ptr(h), v_new=_cabi.ptr(v_new), final_state=_cabi.ptr(final_state), workspace=None,
-        workspace_bytes=0, status=_cabi.ptr(status))
+        workspace_bytes=0, status=_cabi.ptr(status), h0_map=_cabi.ptr(h0_map),
+        state_dtype=_cabi.dtype_code(state_dtype), **dual_args)
     lib = _cabi.lib()
     if tables is not None and "ws" in tables:
         ws = tables["ws"]
@@ -126,10 +141,11 @@ def rebuild_w(k, beta, g_cumsum, A, cu):
 
 def launches_per_forward(varlen: bool, use_cp: bool = False) -> int:
     """Kernels of this library one forward call launches.  Plain: [chunk tables] + kkt_solve + chunk
-    scan.  With context parallelism: [tables] + kkt_solve, plan, warm-up scan, transition scan, chain, main
-    scan (the chunk tables of the plan's segments are built on the host together with the plan)."""
+    scan.  With context parallelism: [tables] + kkt_solve, plan (+ start states), warm-up / transition scan
+    (one launch), chain, main scan (the chunk tables of the plan's segments are built on the host together
+    with the plan)."""
     if use_cp:
-        return (2 if varlen else 1) + 1 + 1 + 1 + 1 + 1
+        return (2 if varlen else 1) + 1 + 1 + 1 + 1
     return 3 if varlen else 2
 
 
@@ -151,7 +167,7 @@ def make_scan_only(q, k, v, beta, g_cumsum, A, o, final_state, initial_state=Non
 
         def run():
             _launch_fwd(q, k, v, None, beta, cp_h0, plan.dev["cu"], g_cumsum, A, o, None, None, final_state,
-                        scale, flags=_cabi.CHUNK_SKIP_PREPARE, seq_map=plan.dev["seg_raw"],
+                        scale, flags=_cabi.CHUNK_SKIP_PREPARE | _cabi.CHUNK_H0_KV_F32, seq_map=plan.dev["seg_raw"],
                         num_seqs=len(plan.seg_next), w=w, tables=plan.tables)
         return run
 
@@ -187,6 +203,12 @@ def chunk_gated_delta_rule_fwd(
     dt_bias: Optional[torch.Tensor] = None,
     beta_is_logit: bool = False,
     output_w: bool = False,
+    initial_state_indices: Optional[torch.Tensor] = None,
+    final_state_out: Optional[torch.Tensor] = None,
+    final_state_indices: Optional[torch.Tensor] = None,
+    out_norm_gate: Optional[torch.Tensor] = None,
+    out_norm_weight: Optional[torch.Tensor] = None,
+    out_norm_eps: float = 1e-6,
 ):
     """Raw forward.  ``g`` is the per-token log decay; returns
     ``(g_cumsum, A, o, h | None, final_state | None[, v_new])`` where ``g_cumsum`` is the chunk-local
@@ -198,8 +220,22 @@ def chunk_gated_delta_rule_fwd(
     ``[Hv]`` the argument ``g`` is the raw gate input ``a`` and ``g = -exp(A_log) * softplus(a + dt_bias)``
     is used; with ``beta_is_logit`` the argument ``beta`` holds logits and ``sigmoid(beta)`` is used.  With
     ``output_w`` the prepared chunk operand ``w = -(A diag(beta e^g) K)`` ``[B,T,Hv,128]`` is appended to the
-    result; the backward takes it back (``w=``) instead of rebuilding it from ``g_cumsum`` and ``A``."""
-    B, T, Hk, Hv, N = _check_common(q, k, v, g, beta, initial_state, cu_seqlens, transpose_state_layout)
+    result; the backward takes it back (``w=``) instead of rebuilding it from ``g_cumsum`` and ``A``.
+
+    State pools (the slot-indexed initial states of the reference's recurrent op,
+    recurrent_fused.py:6287-6311, for the chunked path): with ``initial_state_indices`` (int ``[N]``)
+    ``initial_state`` is a pool ``[slots, Hv, ...]`` and sequence ``n`` starts from slot
+    ``initial_state_indices[n]`` (``-1``: zero state); with ``final_state_out`` the final states are written
+    into that tensor, sequence ``n`` into row ``final_state_indices[n]`` (``-1``: not written; no indices:
+    row ``n``), and it is what the call returns as final state.  Pools may be fp32 or bf16 (both the same);
+    the kernels index the slots themselves, nothing is gathered or scattered around the call.
+
+    Output norm (the gated RMS norm that follows the op in a GDN layer): with ``out_norm_gate`` ``z``
+    ``[B,T,Hv,128]`` (q/k/v dtype) and ``out_norm_weight`` ``[128]`` the returned ``o`` is
+    ``o * rsqrt(mean(o^2, -1) + out_norm_eps) * weight * silu(z)``, applied to the output tile inside the scan
+    (inference: not together with ``output_h`` / ``output_v_new``)."""
+    B, T, Hk, Hv, N = _check_common(q, k, v, g, beta, None if initial_state_indices is not None else initial_state,
+                                    cu_seqlens, transpose_state_layout)
     if (A_log is None) != (dt_bias is None):
         raise ValueError("A_log and dt_bias go together")
     dev = q.device
@@ -208,10 +244,36 @@ def chunk_gated_delta_rule_fwd(
     q, k, v, g, beta = (x if x.is_contiguous() else x.contiguous() for x in (q, k, v, g, beta))
     if scale is None:
         scale = q.shape[-1] ** -0.5
-    h0 = None
+    pooled = initial_state_indices is not None or final_state_out is not None
+    h0, h0_map, fs_map = None, None, None
     if initial_state is not None:
-        h0 = initial_state.to(torch.float32)
-        h0 = h0 if h0.is_contiguous() else h0.contiguous()
+        if initial_state_indices is not None:
+            if initial_state.dim() != 4 or initial_state.shape[1] != Hv or tuple(initial_state.shape[2:]) != (128, 128):
+                raise ValueError(f"a state pool must be [slots, {Hv}, 128, 128], got {tuple(initial_state.shape)}")
+            if initial_state.dtype not in (torch.float32, torch.bfloat16) or not initial_state.is_contiguous():
+                raise ValueError("a state pool must be a contiguous float32 or bfloat16 tensor")
+            if initial_state_indices.numel() != N:
+                raise ValueError(f"initial_state_indices must have one entry per sequence ({N})")
+            h0 = initial_state
+            h0_map = initial_state_indices.to(device=dev, dtype=torch.int32).contiguous()
+        else:
+            h0 = initial_state if (pooled and initial_state.dtype == torch.bfloat16) else initial_state.to(torch.float32)
+            h0 = h0 if h0.is_contiguous() else h0.contiguous()
+    if final_state_out is not None:
+        if final_state_out.dim() != 4 or final_state_out.shape[1] != Hv or tuple(final_state_out.shape[2:]) != (128, 128):
+            raise ValueError(f"final_state_out must be [rows, {Hv}, 128, 128], got {tuple(final_state_out.shape)}")
+        if final_state_out.dtype not in (torch.float32, torch.bfloat16) or not final_state_out.is_contiguous():
+            raise ValueError("final_state_out must be a contiguous float32 or bfloat16 tensor")
+        if h0 is not None and h0.dtype != final_state_out.dtype:
+            raise ValueError("initial states and final_state_out must share a dtype")
+        if final_state_indices is not None:
+            if final_state_indices.numel() != N:
+                raise ValueError(f"final_state_indices must have one entry per sequence ({N})")
+            fs_map = final_state_indices.to(device=dev, dtype=torch.int32).contiguous()
+        elif final_state_out.shape[0] < N:
+            raise ValueError("final_state_out needs one row per sequence")
+    elif final_state_indices is not None:
+        raise ValueError("final_state_indices needs final_state_out")
     cu = None
     lens = None
     if cu_seqlens is not None:
@@ -230,7 +292,19 @@ def chunk_gated_delta_rule_fwd(
     h = torch.empty(h_shape, dtype=q.dtype, device=dev) if output_h else None
     v_new = torch.empty_like(v) if output_v_new else None
     rnorm = torch.empty(B, T, Hk, 2, dtype=torch.float32, device=dev) if use_qk_l2norm_in_kernel else None
-    final_state = torch.empty(N, Hv, 128, 128, dtype=torch.float32, device=dev) if output_final_state else None
+    out_norm = None
+    if out_norm_gate is not None:
+        if out_norm_weight is None or tuple(out_norm_gate.shape) != tuple(v.shape) or out_norm_gate.dtype != v.dtype:
+            raise ValueError("out_norm_gate must have v's shape and dtype and needs out_norm_weight [128]")
+        if output_h or output_v_new:
+            raise ValueError("the output norm is an inference epilogue: not with output_h / output_v_new")
+        out_norm = (out_norm_gate.contiguous(), out_norm_weight.to(device=dev, dtype=torch.float32).contiguous(),
+                    out_norm_eps)
+    if final_state_out is not None:
+        final_state = final_state_out
+    else:
+        fs_dtype = h0.dtype if (h0 is not None and pooled) else torch.float32
+        final_state = torch.empty(N, Hv, 128, 128, dtype=fs_dtype, device=dev) if output_final_state else None
     act = {}
     if A_log is not None:
         act.update(A_log=A_log.to(device=dev, dtype=torch.float32).contiguous(),
@@ -248,22 +322,22 @@ def chunk_gated_delta_rule_fwd(
                     scale, flags=_cabi.CHUNK_PREPARE_ONLY, w=w, rnorm=rnorm, **act)
         if beta_act is not None:
             beta = beta_act  # every later stage reads the activated values
-        h0_kv = h0.transpose(-1, -2) if (h0 is not None and transpose_state_layout) else h0
-        cp_h0 = cp.segment_initial_states(plan, k, v, beta, g_cumsum, A, w, h0_kv, scale, _launch_fwd, rnorm=rnorm)
-        fs = final_state
-        if transpose_state_layout and final_state is not None:
-            fs = torch.empty_like(final_state)
-        _launch_fwd(q, k, v, None, beta, cp_h0, plan.dev["cu"], g_cumsum, A, o, h, v_new, fs, scale,
-                    flags=_cabi.CHUNK_SKIP_PREPARE, seq_map=plan.dev["seg_raw"], num_seqs=len(plan.seg_next),
-                    w=w, tables=plan.tables, rnorm=rnorm)
-        if fs is not final_state:
-            final_state.copy_(fs.transpose(-1, -2))
+        cp_h0 = cp.segment_initial_states(plan, k, v, beta, g_cumsum, A, w, h0, scale, _launch_fwd, rnorm=rnorm,
+                                          h0_map=h0_map, h0_transposed=transpose_state_layout)
+        seg_rows = plan.dev["seg_raw"]
+        if fs_map is not None:  # segment -> sequence -> row of the caller's pool
+            seg_rows = torch.where(seg_rows >= 0, fs_map[seg_rows.clamp(min=0).long()], seg_rows)
+        _launch_fwd(q, k, v, None, beta, cp_h0, plan.dev["cu"], g_cumsum, A, o, h, v_new, final_state, scale,
+                    flags=_cabi.CHUNK_SKIP_PREPARE | _cabi.CHUNK_H0_KV_F32 |
+                    (_cabi.CHUNK_TRANSPOSE_STATE if transpose_state_layout else 0),
+                    seq_map=seg_rows, num_seqs=len(plan.seg_next), w=w, tables=plan.tables, rnorm=rnorm,
+                    out_norm=out_norm)
     else:
         # packed batches of unequal lengths: the longest sequences are handed to the GPU first
         order = longest_first_order(cu_seqlens, dev) if cu_seqlens is not None else None
         _launch_fwd(q, k, v, g, beta, h0, cu, g_cumsum, A, o, h, v_new, final_state, scale,
                     flags=_cabi.CHUNK_TRANSPOSE_STATE if transpose_state_layout else 0, seq_order=order, rnorm=rnorm,
-                    w=w, **act)
+                    w=w, h0_map=h0_map, seq_map=fs_map, out_norm=out_norm, **act)
     out = (g_cumsum, A, o, h, final_state)
     if output_v_new:
         out += (v_new,)
@@ -392,6 +466,63 @@ class ChunkGatedDeltaRuleFunction(torch.autograd.Function):
         return (dq, dk, dv, dg.to(ctx.g_dtype), db.to(ctx.beta_dtype), None, dh0, None, None, None, None)
 
 
+class ChunkGatedDeltaRuleFusedFunction(torch.autograd.Function):
+    """Autograd wrapper of the forward with the layer's prologue folded into the kernels (q / k L2 norm, gate
+    activation ``g = -exp(A_log) softplus(a + dt_bias)``, ``beta = sigmoid(b)``).  The forward runs the fused
+    kernels (no elementwise pass over q, k, a, b); the backward re-forms the normalised / activated inputs with
+    elementwise torch operations, runs the chunk backward on them and applies the chain rule of the three
+    prologue maps to what comes back.  The reference applies these maps as separate differentiable passes in
+    front of its op (chunk/__init__.py:332-334 for the L2 norm)."""
+
+    @staticmethod
+    @torch.amp.custom_fwd(device_type="cuda")
+    def forward(ctx, q, k, v, g, beta, A_log, dt_bias, scale, initial_state, output_final_state, cu_seqlens,
+                transpose_state_layout, use_l2norm, use_gate, use_beta_sigmoid):
+        out = chunk_gated_delta_rule_fwd(
+            q, k, v, g, beta, scale=scale, initial_state=initial_state, cu_seqlens=cu_seqlens,
+            output_final_state=output_final_state, output_h=True, output_v_new=True, output_w=True,
+            transpose_state_layout=transpose_state_layout, use_qk_l2norm_in_kernel=use_l2norm,
+            A_log=A_log if use_gate else None, dt_bias=dt_bias if use_gate else None, beta_is_logit=use_beta_sigmoid)
+        g_cumsum, A, o, h, final_state, v_new, w = out
+        ctx.save_for_backward(q, k, v, g, beta, A_log, dt_bias, g_cumsum, A, initial_state, cu_seqlens, h, v_new, w)
+        ctx.scale, ctx.transpose_state_layout = scale, transpose_state_layout
+        ctx.flags = (use_l2norm, use_gate, use_beta_sigmoid)
+        return o.to(q.dtype), final_state
+
+    @staticmethod
+    @torch.amp.custom_bwd(device_type="cuda")
+    def backward(ctx, do, dht):
+        q, k, v, g_in, beta_in, A_log, dt_bias, g_cumsum, A, initial_state, cu_seqlens, h, v_new, w = ctx.saved_tensors
+        use_l2norm, use_gate, use_beta_sigmoid = ctx.flags
+        qn, kn = (l2norm(q), l2norm(k)) if use_l2norm else (q, k)
+        beta = torch.sigmoid(beta_in.float()) if use_beta_sigmoid else beta_in
+        dq, dk, dv, db, dg, dh0 = chunk_gated_delta_rule_bwd(
+            qn, kn, v, g_cumsum, beta, A, do, dht=dht, scale=ctx.scale, initial_state=initial_state,
+            cu_seqlens=cu_seqlens, h=h, v_new=v_new, transpose_state_layout=ctx.transpose_state_layout, w=w)
+        if use_l2norm:
+            # x_hat = x r with r = (sum x^2 + eps)^-1/2:  dx = r (dx_hat - x_hat (x_hat . dx_hat))
+            def l2norm_bwd(x, xn, dxn):
+                r = torch.rsqrt(x.float().pow(2).sum(-1, keepdim=True) + 1e-6)
+                xn, dxn = xn.float(), dxn.float()
+                return (r * (dxn - xn * (xn * dxn).sum(-1, keepdim=True))).to(x.dtype)
+            dq, dk = l2norm_bwd(q, qn, dq), l2norm_bwd(k, kn, dk)
+        dA_log = ddt = None
+        if use_gate:
+            x = g_in.float() + dt_bias.float()
+            coef = -torch.exp(A_log.float())
+            gval = coef * torch.nn.functional.softplus(x)  # softplus with beta 1, threshold 20 (the kernel's)
+            da = dg * coef * torch.where(x <= 20.0, torch.sigmoid(x), torch.ones_like(x))
+            dA_log = (dg * gval).sum(dim=(0, 1)).to(A_log.dtype)
+            ddt = da.sum(dim=(0, 1)).to(dt_bias.dtype)
+            dg = da
+        if use_beta_sigmoid:
+            db = db * beta * (1.0 - beta)
+        if dh0 is not None and initial_state is not None:
+            dh0 = dh0.to(initial_state.dtype)
+        return (dq, dk, dv, dg.to(g_in.dtype), db.to(beta_in.dtype), dA_log, ddt, None, dh0, None, None, None, None,
+                None, None)
+
+
 @torch.compiler.disable
 def chunk_gated_delta_rule(
     q: torch.Tensor,
@@ -410,13 +541,19 @@ def chunk_gated_delta_rule(
     A_log: Optional[torch.Tensor] = None,
     dt_bias: Optional[torch.Tensor] = None,
     use_beta_sigmoid_in_kernel: bool = False,
+    output_norm_gate: Optional[torch.Tensor] = None,
+    output_norm_weight: Optional[torch.Tensor] = None,
+    output_norm_eps: float = 1e-6,
 ):
     """``(o, final_state | None)`` with gradients for q, k, v, g, beta and initial_state
     (reference: chunk/__init__.py:294-350).  Additions after the reference's surface: with
     ``use_gate_in_kernel`` the argument ``g`` is the raw gate input and
     ``g = -exp(A_log) * softplus(g + dt_bias)`` (``A_log``, ``dt_bias`` ``[Hv]``) is applied here; with
-    ``use_beta_sigmoid_in_kernel`` the argument ``beta`` holds logits.  Without gradients both are folded into
-    the preparation kernel; with gradients they are torch operations in front of the op."""
+    ``use_beta_sigmoid_in_kernel`` the argument ``beta`` holds logits.  These and ``use_qk_l2norm_in_kernel`` are
+    folded into the forward kernels with and without gradients (gradients also reach ``A_log`` and ``dt_bias``).
+    With ``output_norm_gate`` ``z`` and ``output_norm_weight`` the returned ``o`` has passed the gated RMS norm
+    that follows the op in a GDN layer, ``o * rsqrt(mean(o^2) + eps) * weight * silu(z)``: inside the scan kernel
+    when no gradient is needed, as differentiable torch operations behind the op otherwise."""
     assert not head_first, "head_first=True is not supported"
     assert q.dtype == k.dtype == v.dtype
     assert q.dtype != torch.float32, "ChunkGatedDeltaRuleFunction does not support float32. Please use bfloat16."
@@ -428,26 +565,35 @@ def chunk_gated_delta_rule(
         scale = k.shape[-1] ** -0.5
     if use_gate_in_kernel and (A_log is None or dt_bias is None):
         raise ValueError("use_gate_in_kernel needs A_log and dt_bias")
-    if use_qk_l2norm_in_kernel or use_gate_in_kernel or use_beta_sigmoid_in_kernel:
-        needs_grad = torch.is_grad_enabled() and any(
-            t is not None and t.requires_grad for t in (q, k, v, g, beta, initial_state, A_log, dt_bias))
-        if not needs_grad:
-            # inference: normalisation and activations are folded into the kernels (no extra passes)
-            out = chunk_gated_delta_rule_fwd(q, k, v, g, beta, scale=scale, initial_state=initial_state,
-                                             cu_seqlens=cu_seqlens, output_final_state=output_final_state,
-                                             transpose_state_layout=transpose_state_layout,
-                                             use_qk_l2norm_in_kernel=use_qk_l2norm_in_kernel,
-                                             A_log=A_log if use_gate_in_kernel else None,
-                                             dt_bias=dt_bias if use_gate_in_kernel else None,
-                                             beta_is_logit=use_beta_sigmoid_in_kernel)
-            return out[2].to(q.dtype), out[4]
-        if use_qk_l2norm_in_kernel:
-            q, k = l2norm(q), l2norm(k)
-        if use_gate_in_kernel:
-            g = -torch.exp(A_log.float()) * torch.nn.functional.softplus(g.float() + dt_bias.float())
-        if use_beta_sigmoid_in_kernel:
-            beta = torch.sigmoid(beta.float())
-    o, final_state = ChunkGatedDeltaRuleFunction.apply(
-        q, k, v, g, beta, scale, initial_state, output_final_state, cu_seqlens, transpose_state_layout,
-        torch.is_grad_enabled())
+    if (output_norm_gate is None) != (output_norm_weight is None):
+        raise ValueError("output_norm_gate and output_norm_weight go together")
+    fused = use_qk_l2norm_in_kernel or use_gate_in_kernel or use_beta_sigmoid_in_kernel
+    needs_grad = torch.is_grad_enabled() and any(
+        t is not None and t.requires_grad
+        for t in (q, k, v, g, beta, initial_state, A_log, dt_bias, output_norm_gate, output_norm_weight))
+    if not needs_grad and (fused or output_norm_gate is not None):
+        # inference: normalisation, activations and the output norm are folded into the kernels (no extra passes)
+        out = chunk_gated_delta_rule_fwd(q, k, v, g, beta, scale=scale, initial_state=initial_state,
+                                         cu_seqlens=cu_seqlens, output_final_state=output_final_state,
+                                         transpose_state_layout=transpose_state_layout,
+                                         use_qk_l2norm_in_kernel=use_qk_l2norm_in_kernel,
+                                         A_log=A_log if use_gate_in_kernel else None,
+                                         dt_bias=dt_bias if use_gate_in_kernel else None,
+                                         beta_is_logit=use_beta_sigmoid_in_kernel,
+                                         out_norm_gate=output_norm_gate, out_norm_weight=output_norm_weight,
+                                         out_norm_eps=output_norm_eps)
+        return out[2].to(q.dtype), out[4]
+    if fused:
+        o, final_state = ChunkGatedDeltaRuleFusedFunction.apply(
+            q, k, v, g, beta, A_log if use_gate_in_kernel else None, dt_bias if use_gate_in_kernel else None, scale,
+            initial_state, output_final_state, cu_seqlens, transpose_state_layout, use_qk_l2norm_in_kernel,
+            use_gate_in_kernel, use_beta_sigmoid_in_kernel)
+    else:
+        o, final_state = ChunkGatedDeltaRuleFunction.apply(
+            q, k, v, g, beta, scale, initial_state, output_final_state, cu_seqlens, transpose_state_layout,
+            torch.is_grad_enabled())
+    if output_norm_gate is not None:
+        of, z = o.float(), output_norm_gate.float()
+        o = (of * torch.rsqrt(of.pow(2).mean(-1, keepdim=True) + output_norm_eps) * output_norm_weight.float()
+             * torch.nn.functional.silu(z)).to(o.dtype)
     return o, final_state

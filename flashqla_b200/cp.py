@@ -98,7 +98,8 @@ def get_plan(lens: Sequence[int], num_v_heads: int, device: torch.device) -> CpP
                 # row of cp_h0 a segment's end state is written to by the warm-up pass
                 warm_map=i32([s if s >= 0 else -1 for s in plan.seg_next]),
                 identity=i32(list(range(n_seg))),
-                first_rows=torch.tensor(plan.raw_first[:-1], dtype=torch.int64, device=device))
+                # original sequence a segment starts (-1: it continues one)
+                seg_start_of=i32([plan.raw_first.index(s) if s in plan.raw_first[:-1] else -1 for s in range(n_seg)]))
         # Plans are never evicted: captured CUDA graphs and in-flight launches keep using a plan's device
         # tensors.  Past 256 distinct shapes new plans are simply not cached.
         if len(_PLAN_CACHE) < 256:
@@ -106,10 +107,12 @@ def get_plan(lens: Sequence[int], num_v_heads: int, device: torch.device) -> CpP
     return plan
 
 
-def segment_initial_states(plan: CpPlan, k, v, beta, g_cumsum, A, w, h0, scale, launch_fwd, rnorm=None):
-    """Run plan -> warm-up -> transition matrices -> chaining.  Returns ``cp_h0`` fp32
-    ``[n_seg, Hv, 128, 128]``: the state every segment starts from.  ``launch_fwd`` is
-    ``chunk._launch_fwd``; ``w`` is the prepared chunk operand that goes with ``A``."""
+def segment_initial_states(plan: CpPlan, k, v, beta, g_cumsum, A, w, h0, scale, launch_fwd, rnorm=None,
+                           h0_map=None, h0_transposed=False):
+    """Run plan (+ start states) -> warm-up and transition passes (one launch) -> chaining.  Returns ``cp_h0``
+    fp32 ``[n_seg, Hv, 128(K), 128(V)]``: the state every segment starts from.  ``launch_fwd`` is
+    ``chunk._launch_fwd``; ``w`` is the prepared chunk operand that goes with ``A``; ``h0`` are the caller's
+    initial states (fp32 or bf16, ``[V, K]`` with ``h0_transposed``, rows picked by ``h0_map`` if given)."""
     dev = k.device
     Hv = beta.shape[2]
     d = plan.dev
@@ -118,25 +121,23 @@ def segment_initial_states(plan: CpPlan, k, v, beta, g_cumsum, A, w, h0, scale, 
     stream = _cabi.current_stream(dev)
     warm_limit = torch.empty(n_seg, Hv, dtype=torch.int32, device=dev)
     m_limit = torch.empty(n_seg, Hv, dtype=torch.int32, device=dev)
+    cp_h0 = torch.empty(n_seg, Hv, 128, 128, dtype=torch.float32, device=dev)
     pa = _cabi.QlaCpPlanArgs(num_segments=n_seg, num_v_heads=Hv, threshold=WARMUP_THRESHOLD,
                              g_cumsum=g_cumsum.data_ptr(), cu_seqlens=d["cu"].data_ptr(),
                              seg_next=d["seg_next"].data_ptr(), warm_limit=warm_limit.data_ptr(),
-                             m_limit=m_limit.data_ptr())
+                             m_limit=m_limit.data_ptr(), cp_h0=cp_h0.data_ptr(), seg_start_of=d["seg_start_of"].data_ptr(),
+                             h0=_cabi.ptr(h0), h0_map=_cabi.ptr(h0_map),
+                             h0_dtype=_cabi.dtype_code(h0.dtype) if h0 is not None else 0,
+                             h0_transposed=1 if h0_transposed else 0)
     with torch.cuda.device(dev):
         _cabi.check(lib.qla_cp_plan(pa, stream), "qla_cp_plan")
-
-    cp_h0 = torch.zeros(n_seg, Hv, 128, 128, dtype=torch.float32, device=dev)
-    if h0 is not None:
-        cp_h0.index_copy_(0, d["first_rows"], h0)
-    flags = _cabi.CHUNK_STATE_ONLY | _cabi.CHUNK_SKIP_PREPARE
-    # segment-end states from the trailing `warm_limit` chunks, written straight into the successor's row
-    launch_fwd(None, k, v, None, beta, None, d["cu"], g_cumsum, A, None, None, None, cp_h0, scale,
-               flags=flags, seq_map=d["warm_map"], chunk_limit=warm_limit, num_seqs=n_seg, w=w, tables=plan.tables, rnorm=rnorm)
-    # transition matrices of the (segment, head) pairs that never decayed below the threshold
+    # One launch, two passes: segment-end states from the trailing `warm_limit` chunks, written straight into the
+    # successor's row, and the transition matrices of the (segment, head) pairs that never decayed below the
+    # threshold.
     M = torch.empty(n_seg, Hv, 128, 128, dtype=torch.float32, device=dev)
-    launch_fwd(None, k, None, None, beta, None, d["cu"], g_cumsum, A, None, None, None, M, scale,
-               flags=flags | _cabi.CHUNK_INIT_IDENTITY | _cabi.CHUNK_ZERO_V, seq_map=d["identity"],
-               chunk_limit=m_limit, num_seqs=n_seg, w=w, tables=plan.tables, rnorm=rnorm)
+    launch_fwd(None, k, v, None, beta, None, d["cu"], g_cumsum, A, None, None, None, cp_h0, scale,
+               flags=_cabi.CHUNK_STATE_ONLY | _cabi.CHUNK_SKIP_PREPARE, seq_map=d["warm_map"], chunk_limit=warm_limit,
+               num_seqs=n_seg, w=w, tables=plan.tables, rnorm=rnorm, dual=(m_limit, d["identity"], M))
     ca = _cabi.QlaCpChainArgs(num_raw_seqs=len(plan.raw_first) - 1, num_v_heads=Hv, h0=cp_h0.data_ptr(),
                               M=M.data_ptr(), m_limit=m_limit.data_ptr(), raw_first_seg=d["raw_first"].data_ptr())
     with torch.cuda.device(dev):

@@ -71,6 +71,10 @@ extern "C" QLA_API int qla_chunk_fwd(const QlaChunkFwdArgs* args, void* stream_)
   if (total_tokens == 0) return QLA_OK;
   QLA_CHECK_ARG(total_tokens < (int64_t(1) << 31), "too many tokens");
   const bool is_bf16 = a.qkv_dtype == QLA_DT_BF16;
+  QLA_CHECK_SUPPORTED(a.state_dtype == QLA_DT_F32 || a.state_dtype == QLA_DT_BF16, "states must be fp32 or bf16");
+  QLA_CHECK_ARG(!(a.flags & QLA_CHUNK_DUAL_TRANSITION) ||
+                    (state_only && a.chunk_limit && a.chunk_limit_b && a.seq_map_b && a.final_state_b),
+                "QLA_CHUNK_DUAL_TRANSITION needs QLA_CHUNK_STATE_ONLY, chunk_limit(_b), seq_map_b and final_state_b");
 
   int32_t* pair_offsets = nullptr;
   int32_t* chunk_offsets = nullptr;
@@ -108,7 +112,8 @@ extern "C" QLA_API int qla_chunk_fwd(const QlaChunkFwdArgs* args, void* stream_)
   if (a.flags & QLA_CHUNK_PREPARE_ONLY) return QLA_OK;
 
   FwdParams fp{};
-  fp.g_cumsum = a.g_cumsum; fp.beta = a.beta; fp.h0 = static_cast<const float*>(a.h0);
+  fp.g_cumsum = a.g_cumsum; fp.beta = a.beta; fp.h0 = a.h0; fp.h0_map = a.h0_map;
+  fp.state_dtype = a.state_dtype; fp.h0_kv = (a.flags & QLA_CHUNK_H0_KV_F32) ? 1 : 0;
   fp.cu_seqlens = a.cu_seqlens; fp.seq_map = a.seq_map; fp.seq_order = a.seq_order;
   fp.rnorm = l2norm ? a.qk_rnorm : nullptr; fp.chunk_offsets = chunk_offsets;
   fp.chunk_limit = a.chunk_limit; fp.o = a.o; fp.v_new = a.v_new; fp.h = a.h; fp.final_state = a.final_state;
@@ -117,6 +122,15 @@ extern "C" QLA_API int qla_chunk_fwd(const QlaChunkFwdArgs* args, void* stream_)
   fp.transpose_state = (a.flags & QLA_CHUNK_TRANSPOSE_STATE) ? 1 : 0;
   fp.init_identity = (a.flags & QLA_CHUNK_INIT_IDENTITY) ? 1 : 0;
   fp.zero_v = (a.flags & QLA_CHUNK_ZERO_V) ? 1 : 0;
+  const bool out_norm = (a.flags & QLA_CHUNK_OUT_GATED_RMSNORM) != 0;
+  QLA_CHECK_ARG(!out_norm || (a.norm_gate && a.norm_weight), "QLA_CHUNK_OUT_GATED_RMSNORM needs norm_gate and norm_weight");
+  QLA_CHECK_SUPPORTED(!out_norm || (!state_only && a.h == nullptr && a.v_new == nullptr),
+                      "the output norm is an inference epilogue: not with QLA_CHUNK_STATE_ONLY, h or v_new");
+  QLA_CHECK_SUPPORTED(a.state_dtype != QLA_DT_BF16 || (!state_only && !out_norm && a.h == nullptr && a.v_new == nullptr),
+                      "bf16 states are an inference path: not with QLA_CHUNK_STATE_ONLY, h, v_new or the output norm");
+  fp.norm_gate = out_norm ? a.norm_gate : nullptr; fp.norm_weight = a.norm_weight; fp.norm_eps = a.norm_eps;
+  fp.dual = (a.flags & QLA_CHUNK_DUAL_TRANSITION) ? 1 : 0;
+  fp.chunk_limit_b = a.chunk_limit_b; fp.seq_map_b = a.seq_map_b; fp.final_state_b = a.final_state_b;
   fp.scale = a.scale;
   if (beta_logit) {  // the scan reads the activated values the preparation step just wrote
     fp.beta = a.beta_out;

@@ -73,7 +73,7 @@ constexpr int kGateRing = 4;
 enum Bar {
   kFull0 = 0, kFull1, kEmpty0, kEmpty1,
   kPDone0, kPDone1, kPgReady, kQsStored, kD2Done, kDqDone, kVdReady, kVdTile, kSDone, kSbfReady, kSScaled, kAbReady0, kAbReady1,
-  kD4Done, kOFree, kOReady,
+  kD4Done, kOFree, kOReady, kONormed,
   kNumBars
 };
 
@@ -104,7 +104,12 @@ __device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
 // and chunk in its instruction stream: this kernel is bound by instruction fetch before anything else,
 // and every loop below is shaped for a small per-chunk code footprint (32-column groups, rolled; every
 // product issued from one place; barrier waits as real calls).
-template <typename T, bool kStateOnly, bool kAux, bool kTrace>
+// kNorm: the output tile passes through the gated RMS norm that follows the op in a GDN layer
+// (o <- o * rsqrt(mean_v(o^2) + eps) * weight[v] * silu(z[t, h, v])) before it is stored.
+// kState16: h0 / final_state are bf16 (state pools); its own instantiation, like kNorm: the code of the plain
+// forward must stay small (it is the instruction cache, not the work, that a few extra branches in the
+// unrolled state loops cost: +20 % on the whole scan when they were part of the plain kernel).
+template <typename T, bool kStateOnly, bool kAux, bool kTrace, bool kNorm = false, bool kState16 = false>
 __global__ void __launch_bounds__(kThreads, 1)
 chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                  const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_a,
@@ -112,8 +117,17 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                  const FwdParams p) {
   constexpr uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? ptx::kFmtBF16 : ptx::kFmtF16;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int hv = blockIdx.x % p.num_v_heads;
-  const int slot = blockIdx.x / p.num_v_heads;
+  // A "dual" launch carries two passes over the same sequences in one grid: the CTAs of the second half run
+  // the transition-matrix pass of context parallelism (start from the identity, V treated as zero) with their
+  // own chunk limits and output rows (chunk_limit_b, seq_map_b, final_state_b).
+  const bool pass_b = p.dual && blockIdx.x >= static_cast<unsigned>(p.num_seqs) * p.num_v_heads;
+  const unsigned cta = pass_b ? blockIdx.x - static_cast<unsigned>(p.num_seqs) * p.num_v_heads : blockIdx.x;
+  const bool zero_v = p.zero_v || pass_b, init_identity = p.init_identity || pass_b;
+  const int32_t* chunk_limit = pass_b ? p.chunk_limit_b : p.chunk_limit;
+  const int32_t* seq_map = pass_b ? p.seq_map_b : p.seq_map;
+  void* final_state = pass_b ? p.final_state_b : p.final_state;
+  const int hv = cta % p.num_v_heads;
+  const int slot = cta / p.num_v_heads;
   const int seq = p.seq_order ? p.seq_order[slot] : slot;  // CTAs start in grid order: the caller's order of sequences
   const int hk = hv / (p.num_v_heads / p.num_k_heads);
 
@@ -127,13 +141,13 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   }
   int nchunks = (seq_end - seq_start + kChunk - 1) / kChunk;
   int first_chunk = 0;
-  if (p.chunk_limit != nullptr) {
-    const int lim = p.chunk_limit[seq * p.num_v_heads + hv];
+  if (chunk_limit != nullptr) {
+    const int lim = chunk_limit[seq * p.num_v_heads + hv];
     if (lim <= 0) return;  // nothing asked of this (sequence, head); uniform for the whole CTA
     if (lim < nchunks) first_chunk = nchunks - lim;
   }
   const int nproc = nchunks - first_chunk;
-  const int out_row = p.seq_map ? p.seq_map[seq] : seq;
+  const int out_row = seq_map ? seq_map[seq] : seq;
   const int64_t chunk_base =
       p.chunk_offsets ? p.chunk_offsets[seq] : static_cast<int64_t>(seq) * ((p.seq_len + kChunk - 1) / kChunk);
 
@@ -156,7 +170,7 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       if (b == kFull0 || b == kFull1) count = 33;
       else if (b == kEmpty0 || b == kEmpty1) count = 3;
       else if (b == kPgReady || b == kAbReady0 || b == kAbReady1) count = 2;
-      else if (b == kQsStored || b == kVdReady || b == kVdTile || b == kOReady) count = 4;
+      else if (b == kQsStored || b == kVdReady || b == kVdTile || b == kOReady || b == kONormed) count = 4;
       else if (b == kSbfReady || b == kSScaled) count = 8;
       ptx::mbar_init(&bars[b], count);
     }
@@ -212,7 +226,7 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         for (int x = 0; x < 128; x += 64) {
           ptx::tma_prefetch_l2_3d(&tm_k, x, hk, pt0);
           if (!kStateOnly) ptx::tma_prefetch_l2_3d(&tm_q, x, hk, pt0);
-          if (!p.zero_v) ptx::tma_prefetch_l2_3d(&tm_v, x, hv, pt0);
+          if (!zero_v) ptx::tma_prefetch_l2_3d(&tm_v, x, hv, pt0);
           ptx::tma_prefetch_l2_3d(&tm_w, x, hv, pt0);
         }
         ptx::tma_prefetch_l2_3d(&tm_a, 0, hv, pt0);
@@ -245,7 +259,7 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       if (lane == 0) {
         uint32_t bytes = 16384 + 8192 + 16384;  // K + A + Wt
         if (!kStateOnly) bytes += 16384;  // Q
-        if (!p.zero_v) bytes += 16384;    // V
+        if (!zero_v) bytes += 16384;    // V
         uint64_t* full = &bars[kFull0 + s];
         ptx::mbar_expect_tx(full, bytes);
 #pragma unroll 1
@@ -253,7 +267,7 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           ptx::tma_load_3d(st + kStageWQ + h * 16384, &tm_w, full, h * 64, hv, t0);
           if (!kStateOnly) ptx::tma_load_3d(st + kStageWQ + h * 16384 + 8192, &tm_q, full, h * 64, hk, t0);
           ptx::tma_load_3d(st + kStageK + h * 8192, &tm_k, full, h * 64, hk, t0);
-          if (!p.zero_v) ptx::tma_load_3d(st + kStageV + h * 8192, &tm_v, full, h * 64, hv, t0);
+          if (!zero_v) ptx::tma_load_3d(st + kStageV + h * 8192, &tm_v, full, h * 64, hv, t0);
         }
         ptx::tma_load_3d(st + kStageA, &tm_a, full, 0, hv, t0);
       }
@@ -324,7 +338,7 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           if (lane == 0) trace(0, i, 2);
           ptx::tc_fence_after_sync();
           ptx::umma_ts_k128<2, kHalfWQ>(tmem0 + kColD2, tmem0 + kColSbf, d_wq + so, id_n64,
-                                        kStateOnly ? !p.zero_v : true, bar_addr(kD2Done));
+                                        kStateOnly ? !zero_v : true, bar_addr(kD2Done));
           if (lane == 0) trace(0, i, 3);
         }
         // gap 1 (the chain computes V'): MMAq(i): Dq = S0^T_bf16 Q^T (Q rows sit 8 KiB into each half of the
@@ -370,7 +384,7 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           if (!(ok = wait(kFull0 + sj, (j >> 1) & 1))) break;
           if (!(ok = wait(kAbReady0 + sj, (j >> 1) & 1))) break;
           ptx::tc_fence_after_sync();
-          if (!p.zero_v) ptx::umma_ss_k64<128, 2>(tmem0 + kColD2, d_v + sn, d_a + sn, id_u, false);
+          if (!zero_v) ptx::umma_ss_k64<128, 2>(tmem0 + kColD2, d_v + sn, d_a + sn, id_u, false);
           if (!kStateOnly)  // (one PDone barrier per parity: the aux warps may lag a chunk)
             ptx::umma_ss_k128<2, kHalfWQ, 2, kHalfK>(tmem0 + kColD0 + sj * 64, d_wq + sn, d_k + sn, id_n64, false,
                                                      bar_addr(kPDone0 + sj));
@@ -475,12 +489,26 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     bool alive = true;
     // element (k, v) of a state tensor sits at k * st_k + v * st_v
     const int st_k = p.transpose_state ? 1 : kHeadDim, st_v = p.transpose_state ? kHeadDim : 1;
-    float* fs_out = (p.final_state != nullptr && out_row >= 0)
-                        ? p.final_state + (static_cast<int64_t>(out_row) * p.num_v_heads + hv) * kHeadDim * kHeadDim
-                        : nullptr;
-    const float* h0p = (!p.init_identity && p.h0 != nullptr)
-                           ? p.h0 + (static_cast<int64_t>(seq) * p.num_v_heads + hv) * kHeadDim * kHeadDim
-                           : nullptr;
+    // states are fp32 or bf16 (state pools of the recurrent op); the slot of a sequence comes from h0_map /
+    // seq_map, so that a serving loop can prefill straight from and into its pool
+    constexpr bool st16 = kState16;
+    const int64_t fs_off = (static_cast<int64_t>(out_row) * p.num_v_heads + hv) * kHeadDim * kHeadDim;
+    const bool fs16 = st16 && !pass_b;  // (transition matrices are always fp32)
+    float* fs_out = (final_state != nullptr && out_row >= 0 && !fs16) ? static_cast<float*>(final_state) + fs_off : nullptr;
+    __nv_bfloat16* fs_out16 =
+        (final_state != nullptr && out_row >= 0 && fs16) ? static_cast<__nv_bfloat16*>(final_state) + fs_off : nullptr;
+    const int h0_row = p.h0_map != nullptr ? p.h0_map[seq] : seq;
+    const bool h0_16 = st16 && !p.h0_kv;
+    const int h0_k = (p.transpose_state && !p.h0_kv) ? 1 : kHeadDim, h0_v = (p.transpose_state && !p.h0_kv) ? kHeadDim : 1;
+    const int64_t h0_off = (static_cast<int64_t>(h0_row) * p.num_v_heads + hv) * kHeadDim * kHeadDim;
+    const bool has_h0 = !init_identity && p.h0 != nullptr && h0_row >= 0;
+    const float* h0p = (has_h0 && !h0_16) ? static_cast<const float*>(p.h0) + h0_off : nullptr;
+    const __nv_bfloat16* h0p16 = (has_h0 && h0_16) ? static_cast<const __nv_bfloat16*>(p.h0) + h0_off : nullptr;
+    auto store_final = [&](int k, float x) {
+      if (!kState16 || fs_out != nullptr) fs_out[k * st_k + v * st_v] = x;
+      else if (fs_out16 != nullptr) fs_out16[k * st_k + v * st_v] = __float2bfloat16_rn(x);
+    };
+    const bool write_final = fs_out != nullptr || (kState16 && fs_out16 != nullptr);
     const int64_t vn_stride = static_cast<int64_t>(p.num_v_heads) * kHeadDim;
 
     // ---- initial state: S = exp(gL_0) * S_init (fp32) and its 16-bit copy
@@ -501,8 +529,9 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         for (int j = 0; j < 16; ++j) {
           const int k = col_half + kb + j;
           x[j] = 0.f;
-          if (p.init_identity) x[j] = (k == v) ? 1.f : 0.f;
-          else if (h0p != nullptr) x[j] = h0p[k * st_k + v * st_v];
+          if (init_identity) x[j] = (k == v) ? 1.f : 0.f;
+          else if (h0p != nullptr) x[j] = h0p[k * h0_k + v * h0_v];
+          else if (kState16 && h0p16 != nullptr) x[j] = __bfloat162float(h0p16[k * h0_k + v * h0_v]);
         }
 #pragma unroll
         for (int j = 0; j < 16; j += 2) {
@@ -517,9 +546,9 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 #pragma unroll
           for (int j = 0; j < 16; ++j) hp0[(col_half + kb + j) * kHeadDim] = sbh[j];
         }
-        if (nproc == 0 && fs_out != nullptr) {
+        if (nproc == 0 && write_final) {
 #pragma unroll
-          for (int j = 0; j < 16; ++j) fs_out[(col_half + kb + j) * st_k + v * st_v] = x[j];
+          for (int j = 0; j < 16; ++j) store_final(col_half + kb + j, x[j]);
         }
       }
       ptx::tmem_wait_st();
@@ -622,16 +651,54 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           if (tid == 128) trace(2, j, 12);
           ptx::fence_proxy_async_smem();
           warp_arrive(&bars[kOReady], lane);
+          if (kNorm) {
+            // gated RMS norm of the finished tile, in place: 16 threads per token row (8 values each), 8 rows per pass
+            if (!(alive = wait(kOReady, j & 1))) break;
+            const int tl = tid - 128, c8 = (tl & 15) * 8;
+            const T* zb = static_cast<const T*>(p.norm_gate);
+            const float4 w0 = *reinterpret_cast<const float4*>(p.norm_weight + c8);
+            const float4 w1 = *reinterpret_cast<const float4*>(p.norm_weight + c8 + 4);
+            const float wv[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll 1
+            for (int r8 = 0; r8 < kChunk; r8 += 8) {
+              const int row = r8 + (tl >> 4);
+              uint4* cell = reinterpret_cast<uint4*>(so + row * kHeadDim + c8);
+              uint4 raw = *cell;
+              uint4 zraw = make_uint4(0, 0, 0, 0);
+              if (row < prev_valid)
+                zraw = *reinterpret_cast<const uint4*>(zb + (static_cast<int64_t>(prev_t0 + row) * p.num_v_heads + hv) * kHeadDim + c8);
+              const T* e = reinterpret_cast<const T*>(&raw);
+              const T* ze = reinterpret_cast<const T*>(&zraw);
+              float x[8], ss = 0.f;
+#pragma unroll
+              for (int q8 = 0; q8 < 8; ++q8) {
+                x[q8] = Cvt<T>::to_f32(e[q8]);
+                ss = fmaf(x[q8], x[q8], ss);
+              }
+#pragma unroll
+              for (int off = 1; off < 16; off <<= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+              const float rstd = rsqrtf(ss * (1.f / kHeadDim) + p.norm_eps);
+#pragma unroll
+              for (int q8 = 0; q8 < 8; ++q8) {
+                const float z = Cvt<T>::to_f32(ze[q8]);
+                x[q8] = x[q8] * rstd * wv[q8] * (z / (1.f + __expf(-z)));
+              }
+              *cell = make_uint4(pack2<T>(x[0], x[1]), pack2<T>(x[2], x[3]), pack2<T>(x[4], x[5]), pack2<T>(x[6], x[7]));
+            }
+            ptx::fence_proxy_async_smem();
+            warp_arrive(&bars[kONormed], lane);
+          }
+          constexpr int kTileDone = kNorm ? kONormed : kOReady;
           if (prev_valid == kChunk) {
             if (warp == 4) {  // only the issuing warp waits for the tile to be complete
-              if (!(alive = wait(kOReady, j & 1))) break;
+              if (!(alive = wait(kTileDone, j & 1))) break;
               if (tid == 128) {
                 ptx::tma_store_3d(&tm_o, so, 0, hv, prev_t0);
                 ptx::tma_store_commit();
               }
             }
           } else {
-            if (!(alive = wait(kOReady, j & 1))) break;
+            if (!(alive = wait(kTileDone, j & 1))) break;
             // ragged tail (always the last chunk of a sequence): row-masked 16-byte stores
             T* ob = static_cast<T*>(p.o);
             const int tl = tid - 128;  // 16 threads per row (8 elements each), 8 rows per pass
@@ -679,14 +746,14 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       if (tid == 128) trace(2, i, 4);
       const bool last = (i + 1 == nproc);
       if (last) {
-        if (fs_out != nullptr) {
+        if (write_final) {
 #pragma unroll 1
           for (int kb = 0; kb < 64; kb += 16) {
             uint32_t sf[16];
             ptx::tmem_ld16(tm + kColS + col_half + kb, sf);
             ptx::tmem_wait_ld();
 #pragma unroll
-            for (int j = 0; j < 16; ++j) fs_out[(col_half + kb + j) * st_k + v * st_v] = __uint_as_float(sf[j]);
+            for (int j = 0; j < 16; ++j) store_final(col_half + kb + j, __uint_as_float(sf[j]));
           }
         }
       } else {
@@ -754,15 +821,27 @@ int launch_chunk_fwd(const FwdParams& p, const void* q, const void* k, const voi
   if ((rc = make_tmap_3d(&tm_a, A, total_tokens, p.num_v_heads, 64, 64, 64, true, is_bf16)) != QLA_OK) return rc;
   if ((rc = make_tmap_3d(&tm_w, w, total_tokens, p.num_v_heads, kHeadDim, 64, 64, true, is_bf16)) != QLA_OK) return rc;
   if ((rc = make_tmap_3d(&tm_o, state_only ? v : p.o, total_tokens, p.num_v_heads, kHeadDim, 64, 128, false, is_bf16)) != QLA_OK) return rc;
-  const unsigned grid = static_cast<unsigned>(p.num_seqs) * p.num_v_heads;
+  const unsigned grid = static_cast<unsigned>(p.num_seqs) * p.num_v_heads * (p.dual ? 2 : 1);
 #define QLA_LAUNCH_FWD(T, SO, AUX, TR)                                                                          \
   do {                                                                                                          \
     { const int rc_ = ensure_dynamic_smem<chunk_fwd_kernel<T, SO, AUX, TR>>(kSmemBytes); if (rc_ != QLA_OK) return rc_; }  \
     chunk_fwd_kernel<T, SO, AUX, TR><<<grid, kThreads, kSmemBytes, stream>>>(tm_q, tm_k, tm_v, tm_a, tm_w, tm_o, p); \
   } while (0)
+#define QLA_LAUNCH_FWD_NORM(T)                                                                                   \
+  do {                                                                                                          \
+    { const int rc_ = ensure_dynamic_smem<chunk_fwd_kernel<T, false, false, false, true>>(kSmemBytes); if (rc_ != QLA_OK) return rc_; }  \
+    chunk_fwd_kernel<T, false, false, false, true><<<grid, kThreads, kSmemBytes, stream>>>(tm_q, tm_k, tm_v, tm_a, tm_w, tm_o, p); \
+  } while (0)
+#define QLA_LAUNCH_FWD_ST16(T)                                                                                   \
+  do {                                                                                                          \
+    { const int rc_ = ensure_dynamic_smem<chunk_fwd_kernel<T, false, false, false, false, true>>(kSmemBytes); if (rc_ != QLA_OK) return rc_; }  \
+    chunk_fwd_kernel<T, false, false, false, false, true><<<grid, kThreads, kSmemBytes, stream>>>(tm_q, tm_k, tm_v, tm_a, tm_w, tm_o, p); \
+  } while (0)
 #define QLA_DISPATCH_FWD(T)                                                                  \
   do {                                                                                       \
-    if (traced) QLA_LAUNCH_FWD(T, false, false, true);                                       \
+    if (p.state_dtype == QLA_DT_BF16) QLA_LAUNCH_FWD_ST16(T);                                \
+    else if (p.norm_gate != nullptr) QLA_LAUNCH_FWD_NORM(T);                                 \
+    else if (traced) QLA_LAUNCH_FWD(T, false, false, true);                                  \
     else if (state_only && aux) QLA_LAUNCH_FWD(T, true, true, false);                        \
     else if (state_only) QLA_LAUNCH_FWD(T, true, false, false);                              \
     else if (aux) QLA_LAUNCH_FWD(T, false, true, false);                                     \
@@ -775,6 +854,8 @@ int launch_chunk_fwd(const FwdParams& p, const void* q, const void* k, const voi
   if (is_bf16) QLA_DISPATCH_FWD(__nv_bfloat16);
   else QLA_DISPATCH_FWD(__half);
 #undef QLA_DISPATCH_FWD
+#undef QLA_LAUNCH_FWD_NORM
+#undef QLA_LAUNCH_FWD_ST16
 #undef QLA_LAUNCH_FWD
   QLA_CHECK_CUDA(cudaGetLastError());
   return QLA_OK;

@@ -27,7 +27,8 @@ struct KktParams {
 struct FwdParams {
   const float* g_cumsum;        // [NT, Hv]
   const void* beta;             // [NT, Hv]
-  const float* h0;              // [n_h0, Hv, 128, 128] or NULL
+  const void* h0;               // [n_h0, Hv, 128, 128] (state_dtype) or NULL
+  const int32_t* h0_map;        // [num_seqs] row of h0 a sequence starts from (< 0: zero state) or NULL (identity)
   const int32_t* cu_seqlens;    // [num_seqs + 1] or NULL (equal-length batch)
   const int32_t* seq_map;       // [num_seqs] row of final_state (< 0: none) or NULL (identity)
   const int32_t* seq_order;     // [num_seqs] launch order (permutation) or NULL
@@ -37,13 +38,22 @@ struct FwdParams {
   void* o;                      // [NT, Hv, 128]
   void* v_new;                  // [NT, Hv, 128] or NULL
   void* h;                      // [total_chunks, Hv, 128, 128] bf16/fp16 or NULL
-  float* final_state;           // [n_out, Hv, 128, 128] or NULL
+  const void* norm_gate;        // [NT, Hv, 128] gate z of the output gated RMS norm or NULL (no norm)
+  const float* norm_weight;     // [128] with norm_gate
+  float norm_eps;
+  void* final_state;            // [n_out, Hv, 128, 128] (state_dtype) or NULL
   int* status;
   int num_seqs, seq_len, num_k_heads, num_v_heads;
   int beta_dtype;
-  int transpose_state;          // states stored [V, K] instead of [K, V]
+  int state_dtype;              // QLA_DT_F32 | QLA_DT_BF16: element type of h0 and final_state
+  int transpose_state;          // final_state (and h0, unless h0_kv) stored [V, K] instead of [K, V]
+  int h0_kv;                    // h0 is fp32 [K, V] whatever transpose_state / state_dtype say (context-parallel segments)
   int init_identity;            // start from S = I (ignores h0)
   int zero_v;                   // treat V as 0
+  int dual;                     // second half of the grid = transition-matrix pass (identity start, zero V) with:
+  const int32_t* chunk_limit_b; //   its chunk limits,
+  const int32_t* seq_map_b;     //   its output rows,
+  void* final_state_b;          //   and its fp32 output
   float scale;
   long long* trace;             // optional phase trace (see qla_set_trace_buffer), NULL in normal use
   long long trace_count;        // capacity of `trace` in entries

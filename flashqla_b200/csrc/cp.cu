@@ -14,28 +14,46 @@
 namespace qla {
 namespace {
 
-__global__ void cp_plan_kernel(const float* __restrict__ g_cumsum, const int32_t* __restrict__ cu,
-                               const int32_t* __restrict__ seg_next, int num_heads, float threshold,
-                               int32_t* __restrict__ warm_limit, int32_t* __restrict__ m_limit) {
-  const int seg = blockIdx.x;
-  const int h = threadIdx.x;
-  if (h >= num_heads) return;
-  const int start = cu[seg], end = cu[seg + 1];
-  const int nchunks = (end - start + kChunk - 1) / kChunk;
-  int warm = 0, ml = 0;
-  if (seg_next[seg] >= 0 && nchunks > 0) {
-    float acc = 0.f;
-    bool reached = false;
-    for (int c = nchunks - 1; c >= 0; --c) {
-      const int last = min(end, start + (c + 1) * kChunk) - 1;
-      acc += g_cumsum[static_cast<int64_t>(last) * num_heads + h];
-      ++warm;
-      if (acc < threshold) { reached = true; break; }
+// One CTA per (segment, head): thread 0 walks the chunk-end gates; all threads write the segment's start state.
+__global__ void __launch_bounds__(256) cp_plan_kernel(const QlaCpPlanArgs a) {
+  const int seg = blockIdx.x, h = blockIdx.y;
+  const int num_heads = a.num_v_heads;
+  if (threadIdx.x == 0) {
+    const int start = a.cu_seqlens[seg], end = a.cu_seqlens[seg + 1];
+    const int nchunks = (end - start + kChunk - 1) / kChunk;
+    int warm = 0, ml = 0;
+    if (a.seg_next[seg] >= 0 && nchunks > 0) {
+      float acc = 0.f;
+      bool reached = false;
+      for (int c = nchunks - 1; c >= 0; --c) {
+        const int last = min(end, start + (c + 1) * kChunk) - 1;
+        acc += a.g_cumsum[static_cast<int64_t>(last) * num_heads + h];
+        ++warm;
+        if (acc < a.threshold) { reached = true; break; }
+      }
+      if (!reached) ml = nchunks;  // warm == nchunks here
     }
-    if (!reached) ml = nchunks;  // warm == nchunks here
+    a.warm_limit[seg * num_heads + h] = warm;
+    a.m_limit[seg * num_heads + h] = ml;
   }
-  warm_limit[seg * num_heads + h] = warm;
-  m_limit[seg * num_heads + h] = ml;
+  if (a.cp_h0 == nullptr) return;
+  constexpr int kElems = kHeadDim * kHeadDim;
+  float* dst = a.cp_h0 + (static_cast<int64_t>(seg) * num_heads + h) * kElems;
+  const int raw = a.seg_start_of[seg];
+  int row = -1;
+  if (raw >= 0 && a.h0 != nullptr) row = a.h0_map != nullptr ? a.h0_map[raw] : raw;
+  if (row < 0) {
+    for (int i = threadIdx.x * 4; i < kElems; i += 256 * 4) *reinterpret_cast<float4*>(dst + i) = make_float4(0.f, 0.f, 0.f, 0.f);
+    return;
+  }
+  const int64_t off = (static_cast<int64_t>(row) * num_heads + h) * kElems;
+  const float* s32 = static_cast<const float*>(a.h0) + off;
+  const __nv_bfloat16* s16 = static_cast<const __nv_bfloat16*>(a.h0) + off;
+  for (int i = threadIdx.x; i < kElems; i += 256) {
+    // destination [K][V]; a transposed source is read along its rows by consecutive threads
+    const int di = a.h0_transposed ? (i & (kHeadDim - 1)) * kHeadDim + (i >> 7) : i;
+    dst[di] = a.h0_dtype == QLA_DT_BF16 ? __bfloat162float(s16[i]) : s32[i];
+  }
 }
 
 // One CTA: one (raw sequence, head, 32-column slab of the state).  Thread t owns row k = t of the slab.
@@ -75,10 +93,12 @@ extern "C" QLA_API int qla_cp_plan(const QlaCpPlanArgs* a, void* stream) {
   using namespace qla;
   QLA_CHECK_ARG(a != nullptr && a->g_cumsum && a->cu_seqlens && a->seg_next && a->warm_limit && a->m_limit,
                 "NULL pointer in QlaCpPlanArgs");
-  QLA_CHECK_ARG(a->num_segments > 0 && a->num_v_heads > 0 && a->num_v_heads <= 1024, "bad sizes");
-  const int threads = ((a->num_v_heads + 31) / 32) * 32;
-  cp_plan_kernel<<<a->num_segments, threads, 0, static_cast<cudaStream_t>(stream)>>>(
-      a->g_cumsum, a->cu_seqlens, a->seg_next, a->num_v_heads, a->threshold, a->warm_limit, a->m_limit);
+  QLA_CHECK_ARG(a->num_segments > 0 && a->num_v_heads > 0 && a->num_v_heads <= 65535, "bad sizes");
+  QLA_CHECK_ARG(a->cp_h0 == nullptr || a->seg_start_of != nullptr, "cp_h0 needs seg_start_of");
+  QLA_CHECK_SUPPORTED(a->h0 == nullptr || a->h0_dtype == QLA_DT_F32 || a->h0_dtype == QLA_DT_BF16,
+                      "initial states must be fp32 or bf16");
+  dim3 grid(a->num_segments, a->num_v_heads);
+  cp_plan_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(*a);
   QLA_CHECK_CUDA(cudaGetLastError());
   return QLA_OK;
 }

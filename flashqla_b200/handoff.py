@@ -5,9 +5,10 @@ The chunked forward keeps a sequence's state as ``[N, Hv, K, V]`` (``[N, Hv, V, 
 slot-indexed pool ``[slots, Hv, V, K]`` fp32 that it updates in place
 (``fused_sigmoid_gating_delta_rule_update``, recurrent_fused.py:6287-6311).  A serving loop prefills a batch of
 (new or continued) requests and then decodes them token by token from that pool; the reference leaves the
-gather of the slots before the prefill and the scatter behind it to its caller.  This helper does both around
-one forward call, with the pool's layout and slot conventions: ``-1`` = no slot (zero state in, nothing
-written back).
+gather of the slots before the prefill and the scatter behind it to its caller.  Here the forward kernels take
+the slot indices themselves (``initial_state_indices`` / ``final_state_indices`` of
+``chunk_gated_delta_rule_fwd``), with the pool's layout and slot conventions: ``-1`` = no slot (zero state in,
+nothing written back).
 """
 from __future__ import annotations
 
@@ -34,31 +35,22 @@ def prefill_into_state_pool(
     """Chunked forward of ``N`` sequences whose final states land in ``state_pool[state_indices[n]]``
     (``[slots, Hv, V, K]`` fp32, contiguous, updated in place).  With ``continue_from_pool`` the sequences
     start from the states already in their slots (chunked prefill of a long prompt, prefix reuse), else from
-    zero.  A slot index of ``-1`` starts from zero and writes nothing.  Returns ``(o, final_state)`` with
-    ``final_state`` ``[N, Hv, V, K]`` as written.  ``forward_kwargs`` go to ``chunk_gated_delta_rule_fwd``
+    zero.  A slot index of ``-1`` starts from zero and writes nothing.  The pool may be fp32 or bf16.  Returns
+    ``(o, state_pool)``.  ``forward_kwargs`` go to ``chunk_gated_delta_rule_fwd``
     (``use_qk_l2norm_in_kernel``, ``A_log`` ...)."""
-    if state_pool.dim() != 4 or state_pool.dtype != torch.float32 or not state_pool.is_contiguous():
-        raise ValueError("state_pool must be a contiguous float32 tensor [slots, Hv, V, K]")
+    if state_pool.dim() != 4 or state_pool.dtype not in (torch.float32, torch.bfloat16) or not state_pool.is_contiguous():
+        raise ValueError("state_pool must be a contiguous float32 or bfloat16 tensor [slots, Hv, V, K]")
     Hv = v.shape[2]
     if state_pool.shape[1] != Hv or tuple(state_pool.shape[2:]) != (128, 128):
         raise ValueError(f"state_pool must be [slots, {Hv}, 128, 128], got {tuple(state_pool.shape)}")
     N = q.shape[0] if cu_seqlens is None else cu_seqlens.numel() - 1
-    idx = state_indices.to(device=state_pool.device, dtype=torch.int64)
-    if idx.numel() != N:
-        raise ValueError(f"state_indices must have one entry per sequence ({N}), got {idx.numel()}")
-    has_slot = idx >= 0
-    safe = idx.clamp(min=0)
-    h0 = None
-    if continue_from_pool:
-        h0 = state_pool.index_select(0, safe) * has_slot.view(-1, 1, 1, 1).to(torch.float32)
-    out = chunk_gated_delta_rule_fwd(q, k, v, g, beta, scale=scale, initial_state=h0, cu_seqlens=cu_seqlens,
-                                     output_final_state=True, transpose_state_layout=True, **forward_kwargs)
-    o, final_state = out[2], out[4]
-    # Scatter without a host sync: a row without a slot repeats the write of the first row that has one (same
-    # slot, same data, so the duplicate is harmless); if no row has a slot, slot 0 is rewritten with itself.
-    rows = torch.arange(N, device=idx.device)
-    src = torch.where(has_slot, rows, torch.argmax(has_slot.to(torch.int8)))
-    dst = idx.index_select(0, src).clamp(min=0)
-    data = torch.where(has_slot.any(), final_state.index_select(0, src), state_pool.index_select(0, dst))
-    state_pool.index_copy_(0, dst, data)
-    return o, final_state
+    if state_indices.numel() != N:
+        raise ValueError(f"state_indices must have one entry per sequence ({N}), got {state_indices.numel()}")
+    # The kernels index the pool themselves: a sequence reads its slot when it starts and writes it when it ends
+    # (slots of different sequences must differ), so nothing is gathered or scattered around the call.
+    out = chunk_gated_delta_rule_fwd(
+        q, k, v, g, beta, scale=scale, cu_seqlens=cu_seqlens, output_final_state=True, transpose_state_layout=True,
+        initial_state=state_pool if continue_from_pool else None,
+        initial_state_indices=state_indices if continue_from_pool else None,
+        final_state_out=state_pool, final_state_indices=state_indices, **forward_kwargs)
+    return out[2], state_pool

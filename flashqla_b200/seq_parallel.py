@@ -118,12 +118,11 @@ def slice_summary(q, k, v, g, beta, scale: Optional[float] = None) -> _SliceCont
 
     cp_h0 = torch.zeros(n_seg + 1, Hv, 128, 128, dtype=torch.float32, device=dev)
     flags = _cabi.CHUNK_STATE_ONLY | _cabi.CHUNK_SKIP_PREPARE
-    _launch_fwd(None, k, v, None, beta, None, d["cu"], g_cumsum, A, None, None, None, cp_h0, scale, flags=flags,
-                seq_map=d["seg_next"], chunk_limit=warm_limit, num_seqs=n_seg, w=w, tables=plan.tables)
     M = torch.empty(n_seg, Hv, 128, 128, dtype=torch.float32, device=dev)
-    _launch_fwd(None, k, None, None, beta, None, d["cu"], g_cumsum, A, None, None, None, M, scale,
-                flags=flags | _cabi.CHUNK_INIT_IDENTITY | _cabi.CHUNK_ZERO_V, seq_map=d["identity"],
-                chunk_limit=m_limit, num_seqs=n_seg, w=w, tables=plan.tables)
+    # warm-up pass and transition-matrix pass as one launch
+    _launch_fwd(None, k, v, None, beta, None, d["cu"], g_cumsum, A, None, None, None, cp_h0, scale, flags=flags,
+                seq_map=d["seg_next"], chunk_limit=warm_limit, num_seqs=n_seg, w=w, tables=plan.tables,
+                dual=(m_limit, d["identity"], M))
     prefix = torch.zeros(n_seg + 1, Hv, 128, 128, dtype=torch.float32, device=dev)
     prefix[0] = torch.eye(128, dtype=torch.float32, device=dev)
     for buf in (cp_h0, prefix):

@@ -144,8 +144,19 @@ enum { /* flags of QlaChunkFwdArgs / QlaChunkBwdArgs */
   QLA_CHUNK_GATE_ACT = 512,      /* g holds the raw gate input a: the preparation step uses
                                     g = -exp(A_log[h]) * softplus(a + dt_bias[h]) (softplus
                                     with beta 1, threshold 20, as the recurrent op)          */
-  QLA_CHUNK_BETA_LOGIT = 1024    /* beta holds logits: the preparation step uses sigmoid(beta)
+  QLA_CHUNK_BETA_LOGIT = 1024,   /* beta holds logits: the preparation step uses sigmoid(beta)
                                     and writes it to beta_out, which the scan reads           */
+  QLA_CHUNK_H0_KV_F32 = 2048,    /* h0 is fp32 [N,Hv,K,V] whatever QLA_CHUNK_TRANSPOSE_STATE and
+                                    state_dtype say for final_state (the start states of
+                                    context-parallel segments)                                */
+  QLA_CHUNK_OUT_GATED_RMSNORM = 8192, /* o leaves through the gated RMS norm that follows the op in a GDN
+                                    layer: o * rsqrt(mean_v(o^2) + norm_eps) * norm_weight[v] *
+                                    silu(norm_gate[t,h,v]); inference epilogue (no h / v_new)    */
+  QLA_CHUNK_DUAL_TRANSITION = 4096 /* with QLA_CHUNK_STATE_ONLY: the same launch also runs the
+                                    INIT_IDENTITY | ZERO_V pass of every (sequence, head) with
+                                    chunk_limit_b, writing its K x K result to row seq_map_b[n]
+                                    of final_state_b (fp32): warm-up and transition pass of
+                                    context parallelism as one grid                           */
 };
 
 /*
@@ -157,7 +168,10 @@ enum { /* flags of QlaChunkFwdArgs / QlaChunkBwdArgs */
  * A [B,T,Hv,64]; h [B*NC or total chunks,Hv,128,128] bf16; states fp32 [N,Hv,128,128].
  * With cu_seqlens (device int32 [N+1]) B must be 1 and T is the packed token count.
  * seq_map (device int32 [N], optional) gives for every sequence the row of final_state
- * it writes (< 0: none); NULL = identity.
+ * it writes (< 0: none); NULL = identity.  h0_map (device int32 [N], optional) likewise gives the row of
+ * h0 a sequence starts from (< 0: zero state).  With both maps set to the slot indices of a state pool and
+ * h0 == final_state == the pool ([slots,Hv,V,K] with QLA_CHUNK_TRANSPOSE_STATE; fp32 or bf16, state_dtype)
+ * a batch is prefilled from and into the pool of the recurrent op in place; sequences must not share a slot.
  * Workspace: qla_chunk_fwd_workspace_bytes(args) bytes of device memory, 16-byte aligned;
  * it holds the per-sequence chunk tables when cu_seqlens is given.
  */
@@ -199,10 +213,20 @@ typedef struct QlaChunkFwdArgs {
   void* o;             /* out, NULL with QLA_CHUNK_STATE_ONLY                                */
   void* h;             /* out or NULL                                                        */
   void* v_new;         /* out or NULL                                                        */
-  float* final_state;  /* out or NULL                                                        */
+  void* final_state;   /* out or NULL                                                        */
   void* workspace;
   size_t workspace_bytes;
   int32_t* status;     /* device int32, must be 0 on entry; kernels write a non-zero code on a fault */
+  const int32_t* h0_map; /* device int32 [N] or NULL: row of h0 per sequence, < 0 = zero state        */
+  int32_t state_dtype; /* QLA_DT_F32 | QLA_DT_BF16: element type of h0 and final_state               */
+  int32_t reserved;
+  const int32_t* chunk_limit_b; /* QLA_CHUNK_DUAL_TRANSITION: chunk limits [N,Hv] of the second pass  */
+  const int32_t* seq_map_b;     /* QLA_CHUNK_DUAL_TRANSITION: output rows [N] of the second pass      */
+  float* final_state_b;         /* QLA_CHUNK_DUAL_TRANSITION: fp32 [rows,Hv,128,128] out              */
+  const void* norm_gate;        /* QLA_CHUNK_OUT_GATED_RMSNORM: z [B,T,Hv,128] in the q/k/v dtype     */
+  const float* norm_weight;     /* QLA_CHUNK_OUT_GATED_RMSNORM: fp32 [128]                            */
+  float norm_eps;
+  int32_t reserved2;
 } QlaChunkFwdArgs;
 
 QLA_API size_t qla_chunk_fwd_workspace_bytes(const QlaChunkFwdArgs* args);
@@ -292,6 +316,16 @@ typedef struct QlaCpPlanArgs {
   const int32_t* seg_next;    /* [num_segments]                                                 */
   int32_t* warm_limit;        /* out [num_segments, Hv]                                         */
   int32_t* m_limit;           /* out [num_segments, Hv]                                         */
+  /* optional: start states of the segments, written by the same launch.  seg_start_of[s] = index of the
+   * original sequence segment s starts (< 0: s continues a sequence).  Row s of cp_h0 becomes the caller's
+   * initial state of that sequence (row h0_map[r] of h0, or r; < 0 or h0 == NULL: zero), converted to fp32
+   * [K,V]; rows of continuing segments are zeroed (the warm-up pass adds their state).                    */
+  float* cp_h0;               /* out fp32 [num_segments, Hv, 128, 128] or NULL                  */
+  const int32_t* seg_start_of; /* [num_segments], with cp_h0                                    */
+  const void* h0;             /* caller's initial states or NULL                                */
+  const int32_t* h0_map;      /* [number of original sequences] or NULL                         */
+  int32_t h0_dtype;           /* QLA_DT_F32 | QLA_DT_BF16                                       */
+  int32_t h0_transposed;      /* caller's states are [V,K]                                      */
 } QlaCpPlanArgs;
 
 QLA_API int qla_cp_plan(const QlaCpPlanArgs* args, void* stream);

@@ -241,19 +241,22 @@ def test_commit_verified_state(scratch_dtype):
         fq.check_device_status()
 
 
-def test_prefill_then_decode_through_the_pool(fq):
+@pytest.mark.parametrize("pool_dtype", [torch.float32, torch.bfloat16])
+def test_prefill_then_decode_through_the_pool(fq, pool_dtype):
     """Prefill writes the final states into pool slots (one sequence without a slot), a second prefill call
     continues from the pool, then the recurrent op decodes one more token from the same slots: o of that token
-    and the pool must be those of the per-token recurrence over all tokens."""
+    and the pool must be those of the per-token recurrence over all tokens.  The kernels index the slots
+    themselves; the pool is fp32 or bf16 (then every hand-over rounds the state to 16 bits)."""
     N, Hk, Hv, T1, T2, slots = 3, 2, 4, 128, 64, 6
     inp = orc.make_prefill_inputs(N, T1 + T2 + 1, Hk, Hv, seed=51)
     c = {n: t.cuda() for n, t in inp.items()}
     idx = torch.tensor([4, -1, 1], dtype=torch.int32)
-    pool = torch.full((slots, Hv, 128, 128), 7.0, device="cuda")
+    pool = torch.full((slots, Hv, 128, 128), 7.0, device="cuda", dtype=pool_dtype)
+    tol = 5e-3 if pool_dtype == torch.float32 else 1e-2
     part = lambda a, b: [c[n][:, a:b].contiguous() for n in ("q", "k", "v", "g", "beta")]
     o1, _ = fq.prefill_into_state_pool(*part(0, T1), pool, idx.cuda())
     o2, _ = fq.prefill_into_state_pool(*part(T1, T1 + T2), pool, idx.cuda(), continue_from_pool=True)
-    assert float((pool[[0, 2, 3, 5]] - 7.0).abs().max()) == 0.0  # untouched slots
+    assert float((pool[[0, 2, 3, 5]].float() - 7.0).abs().max()) == 0.0  # untouched slots
     # one decode token per sequence from the pool (packed [1, N, ...] layout of the recurrent op)
     t = T1 + T2
     tok = lambda n: c[n][:, t].unsqueeze(0).contiguous()
@@ -264,10 +267,32 @@ def test_prefill_then_decode_through_the_pool(fq):
     o_ref, s_ref = ref[0], ref[1]
     keep = [0, 2]  # sequence 1 has no slot: its second prefill and its decode start from zero
     assert orc.rel_rms(o1.float().cpu(), o_ref[:, :T1]) <= 5e-3
-    assert orc.rel_rms(o2.float().cpu()[keep], o_ref[keep, T1:t]) <= 5e-3
-    assert orc.rel_rms(o3.float().cpu()[0, keep], o_ref[keep, t]) <= 5e-3
+    assert orc.rel_rms(o2.float().cpu()[keep], o_ref[keep, T1:t]) <= tol
+    assert orc.rel_rms(o3.float().cpu()[0, keep], o_ref[keep, t]) <= tol
     # pool layout is [V, K]; the oracle's state is [K, V]
-    assert orc.rel_rms(pool[[4, 1]].cpu(), s_ref[keep].transpose(-1, -2).float()) <= 5e-3
+    assert orc.rel_rms(pool[[4, 1]].float().cpu(), s_ref[keep].transpose(-1, -2).float()) <= tol
+
+
+def test_pool_prefill_with_context_parallel_segments(fq):
+    """The same slot-indexed prefill when the planner cuts the sequences into segments: the start states come
+    out of the pool inside the plan kernel ([V, K] slots into the [K, V] segment states), the last segment of
+    every sequence writes its slot."""
+    lens = [4096 + 37, 2048]
+    cu = torch.tensor([0, lens[0], lens[0] + lens[1]], dtype=torch.int32)
+    inp = orc.make_prefill_inputs(1, sum(lens), 1, 2, seed=52, with_h0=True, n_states=2)
+    c = {n: t.cuda() for n, t in inp.items()}
+    idx = torch.tensor([3, 0], dtype=torch.int32, device="cuda")
+    pool = torch.zeros(5, 2, 128, 128, device="cuda")
+    pool[3], pool[0] = c["h0"][0].transpose(-1, -2), c["h0"][1].transpose(-1, -2)
+    from flashqla_b200 import cp
+    assert cp.get_plan(lens, 2, torch.device("cuda", 0)).use_cp
+    o, _ = fq.prefill_into_state_pool(c["q"], c["k"], c["v"], c["g"], c["beta"], pool, idx, cu_seqlens=cu.cuda(),
+                                      continue_from_pool=True)
+    fq.check_device_status()
+    ref = orc.chunk_gdr_fwd_varlen(inp["q"], inp["k"], inp["v"], inp["g"], inp["beta"], cu, h0=inp["h0"])
+    assert orc.rel_rms(o.float().cpu(), ref["o"]) <= 5e-3
+    assert orc.rel_rms(pool[[3, 0]].cpu(), ref["final_state"].transpose(-1, -2)) <= 5e-3
+    assert float(pool[[1, 2, 4]].abs().max()) == 0.0
 
 
 def test_decode_step_in_a_cuda_graph(fq):
