@@ -120,6 +120,7 @@ EXPORTS = {
     "qla_cp_chain": (C.c_int, [C.POINTER(QlaCpChainArgs), C.c_void_p]),
     "qla_set_trace_buffer": (C.c_int, [C.c_void_p, C.c_size_t]),
     "qla_selftest_bounded_wait": (C.c_int, [C.c_void_p, C.c_uint64, C.c_void_p]),
+    "qla_kernel_launch_info": (C.c_int, [C.c_char_p, C.POINTER(C.c_int32), C.POINTER(C.c_size_t)]),
     "qla_status_string": (C.c_char_p, [C.c_int]),
     "qla_last_error": (C.c_char_p, []),
     "qla_abi_version": (C.c_int, []),

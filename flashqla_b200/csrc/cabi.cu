@@ -1,6 +1,8 @@
 // Status / error reporting of the C ABI (include/flashqla_b200.h).
 #include <stdarg.h>
 
+#include <string>
+
 #include "ptx_sm100.cuh"
 
 namespace qla {
@@ -56,5 +58,33 @@ extern "C" QLA_API int qla_selftest_bounded_wait(int32_t* status, uint64_t limit
   QLA_CHECK_ARG(limit_ns > 0 && limit_ns <= 1000000000ull, "limit_ns must be in (0, 1e9]");
   bounded_wait_selftest_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(status, limit_ns);
   QLA_CHECK_CUDA(cudaGetLastError());
+  return QLA_OK;
+}
+
+namespace qla {
+void launch_info_chunk_fwd_kernel(int*, size_t*);
+void launch_info_bwd_scan_kernel(int*, size_t*);
+void launch_info_bwd_chunk_kernel(int*, size_t*);
+void launch_info_kkt_solve_kernel(int*, size_t*);
+void launch_info_recurrent_kernel(int*, size_t*);
+}  // namespace qla
+
+extern "C" QLA_API int qla_kernel_launch_info(const char* kernel, int32_t* block_threads, size_t* dynamic_smem_bytes) {
+  using namespace qla;
+  QLA_CHECK_ARG(kernel != nullptr && block_threads != nullptr && dynamic_smem_bytes != nullptr, "NULL argument");
+  int block = 0;
+  size_t smem = 0;
+  const std::string name(kernel);
+  if (name == "chunk_fwd_kernel") launch_info_chunk_fwd_kernel(&block, &smem);
+  else if (name == "bwd_scan_kernel") launch_info_bwd_scan_kernel(&block, &smem);
+  else if (name == "bwd_chunk_kernel") launch_info_bwd_chunk_kernel(&block, &smem);
+  else if (name == "kkt_solve_kernel") launch_info_kkt_solve_kernel(&block, &smem);
+  else if (name == "recurrent_kernel") launch_info_recurrent_kernel(&block, &smem);
+  else {
+    set_last_error("unknown kernel '%s'", kernel);
+    return QLA_ERR_INVALID_ARG;
+  }
+  *block_threads = block;
+  *dynamic_smem_bytes = smem;
   return QLA_OK;
 }

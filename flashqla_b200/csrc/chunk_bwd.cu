@@ -848,4 +848,9 @@ int launch_chunk_bwd(const BwdParams& p, int64_t total_tokens, int total_chunks_
   return QLA_OK;
 }
 
+void launch_info_bwd_chunk_kernel(int* block_threads, size_t* dynamic_smem_bytes) {
+  *block_threads = kThreads;
+  *dynamic_smem_bytes = kSmemBytes;
+}
+
 }  // namespace qla

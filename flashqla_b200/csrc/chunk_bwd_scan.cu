@@ -501,4 +501,9 @@ int launch_bwd_scan(const BwdParams& p, int64_t total_tokens, bool is_bf16, cuda
   return QLA_OK;
 }
 
+void launch_info_bwd_scan_kernel(int* block_threads, size_t* dynamic_smem_bytes) {
+  *block_threads = kThreads;
+  *dynamic_smem_bytes = kSmemBytes;
+}
+
 }  // namespace qla

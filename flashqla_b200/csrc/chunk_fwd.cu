@@ -861,4 +861,9 @@ int launch_chunk_fwd(const FwdParams& p, const void* q, const void* k, const voi
   return QLA_OK;
 }
 
+void launch_info_chunk_fwd_kernel(int* block_threads, size_t* dynamic_smem_bytes) {
+  *block_threads = kThreads;
+  *dynamic_smem_bytes = kSmemBytes;
+}
+
 }  // namespace qla

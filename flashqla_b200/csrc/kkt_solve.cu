@@ -112,6 +112,10 @@ __device__ __forceinline__ void pair_sync(int ci) {  // the two warps that own o
   asm volatile("bar.sync %0, 64;" ::"r"(ci + 1) : "memory");
 }
 
+// K tile 32 KiB + X tiles + L tiles (later the Aw tile) + T
+constexpr size_t kKktSmemBytes = 1024 + 32768 + 2 * 64 * kXStride * sizeof(float) + 2 * 64 * kLStride * sizeof(float) +
+                                 2 * 32 * kTStride * sizeof(float);
+
 template <typename T>
 __global__ void __launch_bounds__(128) kkt_solve_kernel(const __grid_constant__ CUtensorMap tm_k,
                                                         const __grid_constant__ CUtensorMap tm_q,
@@ -522,9 +526,7 @@ int launch_kkt_solve(const KktParams& p, const void* k, const void* q, int64_t t
   // w leaves through two [128 tokens][64] staging tiles per (pair, head)
   rc = make_tmap_3d(&tm_w, p.w, total_tokens, p.num_v_heads, kHeadDim, 128, 64, true, is_bf16);
   if (rc != QLA_OK) return rc;
-  // K tile 32 KiB + X tiles + L tiles (later the Aw tile) + T
-  const size_t smem = 1024 + 32768 + 2 * 64 * kXStride * sizeof(float) + 2 * 64 * kLStride * sizeof(float) +
-                      2 * 32 * kTStride * sizeof(float);
+  const size_t smem = kKktSmemBytes;
   dim3 grid(pairs_upper, p.num_k_heads);
   if (is_bf16) {
     if ((rc = ensure_dynamic_smem<kkt_solve_kernel<__nv_bfloat16>>(smem)) != QLA_OK) return rc;
@@ -535,6 +537,11 @@ int launch_kkt_solve(const KktParams& p, const void* k, const void* q, int64_t t
   }
   QLA_CHECK_CUDA(cudaGetLastError());
   return QLA_OK;
+}
+
+void launch_info_kkt_solve_kernel(int* block_threads, size_t* dynamic_smem_bytes) {
+  *block_threads = 128;
+  *dynamic_smem_bytes = kKktSmemBytes;
 }
 
 }  // namespace qla

@@ -451,6 +451,14 @@ __global__ void __launch_bounds__(256) state_commit_kernel(const QlaStateCommitA
 }  // namespace
 }  // namespace qla
 
+namespace qla {
+// (32-row tiles of an fp32 pool: the largest variant; 16-row tiles and bf16 pools use a half / a quarter)
+void launch_info_recurrent_kernel(int* block_threads, size_t* dynamic_smem_bytes) {
+  *block_threads = 128;
+  *dynamic_smem_bytes = kRecStages * 2 * 4 * 128 * sizeof(float4);
+}
+}  // namespace qla
+
 extern "C" QLA_API int qla_state_commit(const QlaStateCommitArgs* args, void* stream) {
   using namespace qla;
   QLA_CHECK_ARG(args != nullptr, "args is NULL");

@@ -364,6 +364,15 @@ QLA_API int qla_set_trace_buffer(long long* device_buffer, size_t count);
  */
 QLA_API int qla_selftest_bounded_wait(int32_t* status, uint64_t limit_ns, void* stream);
 
+/*
+ * Launch constants of the library's main kernels ("chunk_fwd_kernel", "kkt_solve_kernel", "bwd_scan_kernel",
+ * "bwd_chunk_kernel", "recurrent_kernel"): threads per block and dynamic shared-memory bytes, as compiled.
+ * The manifest written beside the library (and beside the per-kernel cubins) carries the same figures for
+ * launchers that load the cubins without the CUDA runtime, the role of the reference's AOT export
+ * (flash_qla/compile_sm12x_gdn.py:580-669).
+ */
+QLA_API int qla_kernel_launch_info(const char* kernel, int32_t* block_threads, size_t* dynamic_smem_bytes);
+
 QLA_API const char* qla_status_string(int code);
 QLA_API const char* qla_last_error(void);
 QLA_API int qla_abi_version(void);

@@ -86,3 +86,24 @@ def test_manifest_describes_the_header(built_lib):
     for flag, value in m["flags"].items():
         c_name = "QLA_" + flag
         assert re.search(r"%s\s*=\s*%d\b|#define %s\s+%d\b" % (c_name, value, c_name, value), header), c_name
+
+
+def test_manifest_lists_every_kernel_with_its_cubin(built_lib):
+    """The build leaves one cubin per translation unit with kernels; the manifest's kernel entries point at
+    them and carry launch constants that agree with the library's own (qla_kernel_launch_info)."""
+    import json
+    from flashqla_b200 import _cabi, manifest
+    m = json.loads((built_lib.parent / manifest.MANIFEST_NAME).read_text())
+    kernels = m["kernels"]
+    assert kernels, "the build records its kernels"
+    names = {k["kernel_name"] for k in kernels}
+    assert set(manifest.KERNEL_RULES) <= names
+    lib = _cabi.lib()
+    for k in kernels:
+        assert (built_lib.parent / k["cubin"]).exists(), k["cubin"]
+        assert k["registers"] and k["export_name"].startswith("_Z")
+        if k["kernel_name"] in manifest.KERNEL_RULES:
+            block, smem = ctypes.c_int32(), ctypes.c_size_t()
+            assert lib.qla_kernel_launch_info(k["kernel_name"].encode(), ctypes.byref(block), ctypes.byref(smem)) == 0
+            assert block.value == 32 * k["num_warps"] and smem.value == k["shared"], k["kernel_name"]
+    assert lib.qla_kernel_launch_info(b"no_such_kernel", ctypes.byref(block), ctypes.byref(smem)) == -1
