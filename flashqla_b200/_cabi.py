@@ -78,6 +78,9 @@ class QlaChunkBwdArgs(C.Structure):
         ("dq", C.c_void_p), ("dk", C.c_void_p), ("dv", C.c_void_p), ("dbeta", C.c_void_p),
         ("dg", C.c_void_p), ("dh0", C.c_void_p), ("workspace", C.c_void_p),
         ("workspace_bytes", C.c_size_t), ("status", C.c_void_p),
+        ("num_segments", C.c_int32), ("reserved", C.c_int32), ("seg_cu", C.c_void_p), ("seg_dht", C.c_void_p),
+        ("seg_dh0_map", C.c_void_p), ("chunk_limit", C.c_void_p), ("out_map", C.c_void_p),
+        ("chunk_limit_b", C.c_void_p), ("out_map_b", C.c_void_p), ("out_b", C.c_void_p),
     ]
 
 
@@ -96,14 +99,14 @@ class QlaCpPlanArgs(C.Structure):
         ("g_cumsum", C.c_void_p), ("cu_seqlens", C.c_void_p), ("seg_next", C.c_void_p),
         ("warm_limit", C.c_void_p), ("m_limit", C.c_void_p),
         ("cp_h0", C.c_void_p), ("seg_start_of", C.c_void_p), ("h0", C.c_void_p), ("h0_map", C.c_void_p),
-        ("h0_dtype", C.c_int32), ("h0_transposed", C.c_int32),
+        ("h0_dtype", C.c_int32), ("h0_transposed", C.c_int32), ("reverse", C.c_int32), ("reserved", C.c_int32),
     ]
 
 
 class QlaCpChainArgs(C.Structure):
     _fields_ = [
         ("num_raw_seqs", C.c_int32), ("num_v_heads", C.c_int32), ("h0", C.c_void_p), ("M", C.c_void_p),
-        ("m_limit", C.c_void_p), ("raw_first_seg", C.c_void_p),
+        ("m_limit", C.c_void_p), ("raw_first_seg", C.c_void_p), ("reverse", C.c_int32), ("reserved", C.c_int32),
     ]
 
 

@@ -25,6 +25,11 @@ NVCC_FLAGS = [
 ]
 
 
+def _extra_flags() -> list[str]:
+    """Extra nvcc flags for experiments (``QLA_NVCC_EXTRA="-DQLA_REC_REG_PREFETCH=0"``); empty in normal builds."""
+    return os.environ.get("QLA_NVCC_EXTRA", "").split()
+
+
 def _nvcc() -> str:
     for cand in (os.environ.get("NVCC"), shutil.which("nvcc"), "/usr/local/cuda/bin/nvcc"):
         if cand and Path(cand).exists():
@@ -95,7 +100,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     procs = []
     for src in sources():
         obj = LIB_DIR / (src.stem + ".o")
-        cmd = [nvcc, "-Xptxas", "-v", *NVCC_FLAGS, "-c", str(src), "-o", str(obj)]
+        cmd = [nvcc, "-Xptxas", "-v", *NVCC_FLAGS, *_extra_flags(), "-c", str(src), "-o", str(obj)]
         procs.append((src, "obj", subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
         objs.append(obj)
         cubin = CUBIN_DIR / (src.stem + ".sm_100a.cubin")

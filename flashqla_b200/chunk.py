@@ -362,6 +362,7 @@ def chunk_gated_delta_rule_bwd(
     v_new: Optional[torch.Tensor] = None,
     transpose_state_layout: bool = False,
     w: Optional[torch.Tensor] = None,
+    auto_cp: bool = True,
 ):
     """Raw backward.  ``g`` is the chunk-local cumulative gate and ``A`` the WY matrix returned by
     ``chunk_gated_delta_rule_fwd``; ``h`` / ``v_new`` / ``w`` are the forward's optional outputs: ``h`` and
@@ -412,6 +413,13 @@ def chunk_gated_delta_rule_bwd(
     dg = torch.empty(B, T, Hv, dtype=torch.float32, device=dev)
     dh0 = torch.empty(N, Hv, 128, 128, dtype=torch.float32, device=dev) if initial_state is not None else None
     Bk, Tk = (1, B * T) if cu is not None else (B, T)
+    # Long sequences on few heads: the reverse scan is cut into the same segments as the forward's (cp.py)
+    plan = cp.get_plan(lens if lens is not None else [T] * B, Hv, dev) if auto_cp else None
+    seg = {}
+    if plan is not None and plan.use_cp:
+        seg_dht = cp.segment_end_gradients(plan, q, k, do, w, g_cumsum, dht, scale, transposed=transpose_state_layout)
+        seg = dict(num_segments=len(plan.seg_next), seg_cu=_cabi.ptr(plan.dev["cu"]), seg_dht=_cabi.ptr(seg_dht),
+                   seg_dh0_map=_cabi.ptr(plan.dev["seg_start_of"]))
     args = _cabi.QlaChunkBwdArgs(
         batch=Bk, seq_len=Tk, num_seqs=N, num_k_heads=Hk, num_v_heads=Hv, qkv_dtype=_cabi.dtype_code(q.dtype),
         beta_dtype=_cabi.dtype_code(beta.dtype), flags=flags, scale=float(scale),
@@ -419,7 +427,7 @@ def chunk_gated_delta_rule_bwd(
         A=_cabi.ptr(A), h=_cabi.ptr(h), v_new=_cabi.ptr(v_new), w=_cabi.ptr(w), d_o=_cabi.ptr(do), dht=_cabi.ptr(dht),
         cu_seqlens=_cabi.ptr(cu), dq=_cabi.ptr(dq), dk=_cabi.ptr(dk), dv=_cabi.ptr(dv), dbeta=_cabi.ptr(db),
         dg=_cabi.ptr(dg), dh0=_cabi.ptr(dh0), workspace=None, workspace_bytes=0,
-        status=_cabi.ptr(device_status(dev)))
+        status=_cabi.ptr(device_status(dev)), **seg)
     lib = _cabi.lib()
     ws_bytes = lib.qla_chunk_bwd_workspace_bytes(args)
     ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)

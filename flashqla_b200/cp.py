@@ -99,7 +99,9 @@ def get_plan(lens: Sequence[int], num_v_heads: int, device: torch.device) -> CpP
                 warm_map=i32([s if s >= 0 else -1 for s in plan.seg_next]),
                 identity=i32(list(range(n_seg))),
                 # original sequence a segment starts (-1: it continues one)
-                seg_start_of=i32([plan.raw_first.index(s) if s in plan.raw_first[:-1] else -1 for s in range(n_seg)]))
+                seg_start_of=i32([plan.raw_first.index(s) if s in plan.raw_first[:-1] else -1 for s in range(n_seg)]),
+                # predecessor segment (-1: the segment starts a sequence): the backward's "next"
+                seg_prev=i32([-1 if s in plan.raw_first[:-1] else s - 1 for s in range(n_seg)]))
         # Plans are never evicted: captured CUDA graphs and in-flight launches keep using a plan's device
         # tensors.  Past 256 distinct shapes new plans are simply not cached.
         if len(_PLAN_CACHE) < 256:
@@ -143,3 +145,48 @@ def segment_initial_states(plan: CpPlan, k, v, beta, g_cumsum, A, w, h0, scale, 
     with torch.cuda.device(dev):
         _cabi.check(lib.qla_cp_chain(ca, stream), "qla_cp_chain")
     return cp_h0
+
+
+def segment_end_gradients(plan: CpPlan, q, k, do, w, g_cumsum, dht, scale, transposed=False):
+    """The backward's counterpart of :func:`segment_initial_states` (the reference's backward has no context
+    parallelism: its grid is sequences x heads, chunk/hopper/fused_bwd.py:79).  Returns ``seg_dht`` fp32
+    ``[n_seg, Hv, 128(K), 128(V)]``: the state gradient entering every segment from its right end.
+
+    plan (reverse: decay accumulated from a segment's START; rows of the last segments take the caller's ``dht``)
+    -> one launch of the reverse scan in state-only mode over the leading chunks of every segment (zero start,
+    result written to the predecessor's row) together with the transition matrices of the pairs whose decay never
+    passed the threshold -> reverse chaining."""
+    dev = k.device
+    Hv = w.shape[2]
+    Hk = k.shape[2]
+    d = plan.dev
+    n_seg = len(plan.seg_next)
+    lib = _cabi.lib()
+    stream = _cabi.current_stream(dev)
+    warm_limit = torch.empty(n_seg, Hv, dtype=torch.int32, device=dev)
+    m_limit = torch.empty(n_seg, Hv, dtype=torch.int32, device=dev)
+    seg_dht = torch.empty(n_seg, Hv, 128, 128, dtype=torch.float32, device=dev)
+    pa = _cabi.QlaCpPlanArgs(num_segments=n_seg, num_v_heads=Hv, threshold=WARMUP_THRESHOLD,
+                             g_cumsum=g_cumsum.data_ptr(), cu_seqlens=d["cu"].data_ptr(),
+                             seg_next=d["seg_prev"].data_ptr(), warm_limit=warm_limit.data_ptr(),
+                             m_limit=m_limit.data_ptr(), cp_h0=seg_dht.data_ptr(), seg_start_of=d["seg_raw"].data_ptr(),
+                             h0=_cabi.ptr(dht), h0_map=None, h0_dtype=_cabi.QLA_DT_F32,
+                             h0_transposed=1 if transposed else 0, reverse=1)
+    M = torch.empty(n_seg, Hv, 128, 128, dtype=torch.float32, device=dev)
+    total = q.shape[0] * q.shape[1]
+    from .utils import device_status
+    sa = _cabi.QlaChunkBwdArgs(
+        batch=1, seq_len=total, num_seqs=n_seg, num_k_heads=Hk, num_v_heads=Hv, qkv_dtype=_cabi.dtype_code(q.dtype),
+        beta_dtype=_cabi.QLA_DT_F32, flags=_cabi.CHUNK_STATE_ONLY | _cabi.CHUNK_DUAL_TRANSITION, scale=float(scale),
+        q=_cabi.ptr(q), k=_cabi.ptr(k), g_cumsum=_cabi.ptr(g_cumsum), w=_cabi.ptr(w), d_o=_cabi.ptr(do),
+        cu_seqlens=d["cu"].data_ptr(), dh0=seg_dht.data_ptr(), status=_cabi.ptr(device_status(dev)),
+        chunk_limit=warm_limit.data_ptr(), out_map=d["seg_prev"].data_ptr(), chunk_limit_b=m_limit.data_ptr(),
+        out_map_b=d["identity"].data_ptr(), out_b=M.data_ptr())
+    ca = _cabi.QlaCpChainArgs(num_raw_seqs=len(plan.raw_first) - 1, num_v_heads=Hv, h0=seg_dht.data_ptr(),
+                              M=M.data_ptr(), m_limit=m_limit.data_ptr(), raw_first_seg=d["raw_first"].data_ptr(),
+                              reverse=1)
+    with torch.cuda.device(dev):
+        _cabi.check(lib.qla_cp_plan(pa, stream), "qla_cp_plan")
+        _cabi.check(lib.qla_chunk_bwd(sa, stream), "qla_chunk_bwd (state-only)")
+        _cabi.check(lib.qla_cp_chain(ca, stream), "qla_cp_chain")
+    return seg_dht

@@ -156,7 +156,7 @@ BwdWorkspace bwd_workspace(const QlaChunkBwdArgs& a) {
   w.tables = varlen ? 2 * table_bytes(a.num_seqs) : 0;
   w.dh = ((static_cast<size_t>(w.chunks_upper) * a.num_v_heads * kHeadDim * kHeadDim * 2) + 15) & ~size_t(15);
   w.du = ((static_cast<size_t>(w.chunks_upper) * a.num_v_heads * kHeadDim * kChunk * 2) + 15) & ~size_t(15);
-  w.total = w.tables + w.dh + w.du;
+  w.total = w.tables + w.dh + w.du + (a.num_segments > 0 ? 2 * table_bytes(a.num_segments) : 0);
   return w;
 }
 }  // namespace
@@ -177,13 +177,41 @@ extern "C" QLA_API int qla_chunk_bwd(const QlaChunkBwdArgs* args, void* stream_)
                 "num_v_heads must be a multiple of num_k_heads");
   QLA_CHECK_SUPPORTED(a.qkv_dtype == QLA_DT_BF16 || a.qkv_dtype == QLA_DT_F16, "q, k, v must be bf16 or fp16");
   const bool varlen = a.cu_seqlens != nullptr;
+  const bool state_only = (a.flags & QLA_CHUNK_STATE_ONLY) != 0;
   QLA_CHECK_ARG(!varlen || a.batch == 1, "with cu_seqlens the batch size must be 1");
   QLA_CHECK_ARG(varlen || a.num_seqs == a.batch, "num_seqs must equal batch without cu_seqlens");
-  QLA_CHECK_ARG(a.q && a.k && a.v && a.g_cumsum && a.beta && a.A && a.d_o, "NULL input tensor");
-  QLA_CHECK_SUPPORTED(a.h && a.v_new && a.w, "h, v_new and w from the forward are required");
-  QLA_CHECK_ARG(a.dq && a.dk && a.dv && a.dbeta && a.dg, "NULL output tensor");
+  QLA_CHECK_ARG(a.q && a.k && a.g_cumsum && a.d_o && a.w, "NULL input tensor");
   const int64_t total_tokens = static_cast<int64_t>(a.batch) * a.seq_len;
   if (total_tokens == 0) return QLA_OK;
+  const bool is_bf16 = a.qkv_dtype == QLA_DT_BF16;
+
+  BwdParams p{};
+  p.q = a.q; p.k = a.k; p.v = a.v; p.v_new = a.v_new; p.d_o = a.d_o; p.A = a.A; p.h = a.h; p.w = a.w;
+  p.g_cumsum = a.g_cumsum; p.beta = a.beta; p.dht = a.dht; p.cu_seqlens = a.cu_seqlens;
+  p.dq = a.dq; p.dk = a.dk; p.dv = a.dv; p.dbeta = a.dbeta; p.dg = a.dg; p.dh0 = a.dh0;
+  p.num_seqs = a.num_seqs; p.seq_len = a.seq_len; p.num_k_heads = a.num_k_heads; p.num_v_heads = a.num_v_heads;
+  p.beta_dtype = a.beta_dtype; p.transpose_state = (a.flags & QLA_CHUNK_TRANSPOSE_STATE) ? 1 : 0;
+  p.scale = a.scale; p.status = a.status;
+  p.trace = current_trace_buffer();
+
+  if (state_only) {
+    // A state-only pass of the reverse scan (context parallelism): over the first chunk_limit chunks of every
+    // interval, from a zero gradient (or dht), writing only the gradient that leaves the interval on the left
+    // to row out_map[n] of dh0; optionally the transition-matrix pass in the same launch.
+    QLA_CHECK_ARG(a.dh0 != nullptr, "a state-only pass writes dh0");
+    QLA_CHECK_ARG(varlen, "a state-only pass works on intervals given by cu_seqlens");
+    const bool dual = (a.flags & QLA_CHUNK_DUAL_TRANSITION) != 0;
+    QLA_CHECK_ARG(!dual || (a.chunk_limit && a.chunk_limit_b && a.out_map_b && a.out_b),
+                  "QLA_CHUNK_DUAL_TRANSITION needs chunk_limit(_b), out_map_b and out_b");
+    BwdScanMode mode{};
+    mode.chunk_limit = a.chunk_limit; mode.out_map = a.out_map; mode.state_only = 1; mode.dual = dual ? 1 : 0;
+    mode.chunk_limit_b = a.chunk_limit_b; mode.out_map_b = a.out_map_b; mode.out_b = a.out_b;
+    return launch_bwd_scan(p, mode, total_tokens, is_bf16, stream);
+  }
+
+  QLA_CHECK_ARG(a.v && a.beta && a.A, "NULL input tensor");
+  QLA_CHECK_SUPPORTED(a.h && a.v_new, "h and v_new from the forward are required");
+  QLA_CHECK_ARG(a.dq && a.dk && a.dv && a.dbeta && a.dg, "NULL output tensor");
   const BwdWorkspace w = bwd_workspace(a);
   if (a.workspace == nullptr || a.workspace_bytes < w.total) {
     set_last_error("workspace of %zu bytes required, %zu given", w.total, a.workspace_bytes);
@@ -198,14 +226,23 @@ extern "C" QLA_API int qla_chunk_bwd(const QlaChunkBwdArgs* args, void* stream_)
     int rc = launch_chunk_tables(a.cu_seqlens, a.num_seqs, pair_offsets, chunk_offsets, stream);
     if (rc != QLA_OK) return rc;
   }
-  BwdParams p{};
-  p.q = a.q; p.k = a.k; p.v = a.v; p.v_new = a.v_new; p.d_o = a.d_o; p.A = a.A; p.h = a.h; p.w = a.w;
-  p.g_cumsum = a.g_cumsum; p.beta = a.beta; p.dht = a.dht; p.cu_seqlens = a.cu_seqlens;
   p.chunk_offsets = chunk_offsets; p.dh = ws + w.tables; p.du = ws + w.tables + w.dh;
-  p.dq = a.dq; p.dk = a.dk; p.dv = a.dv; p.dbeta = a.dbeta; p.dg = a.dg; p.dh0 = a.dh0;
-  p.num_seqs = a.num_seqs; p.seq_len = a.seq_len; p.num_k_heads = a.num_k_heads; p.num_v_heads = a.num_v_heads;
-  p.beta_dtype = a.beta_dtype; p.transpose_state = (a.flags & QLA_CHUNK_TRANSPOSE_STATE) ? 1 : 0;
-  p.scale = a.scale; p.status = a.status;
-  p.trace = current_trace_buffer();
-  return launch_chunk_bwd(p, total_tokens, w.chunks_upper, a.qkv_dtype == QLA_DT_BF16, stream);
+
+  // reverse scan: over whole sequences, or over the segments of a context-parallel plan (segments are whole
+  // chunks, so the chunk numbering of the workspace is that of the sequences)
+  BwdParams sp = p;
+  BwdScanMode mode{};
+  if (a.num_segments > 0) {
+    QLA_CHECK_ARG(a.seg_cu && a.seg_dht && a.seg_dh0_map, "segments need seg_cu, seg_dht and seg_dh0_map");
+    int32_t* seg_tables = reinterpret_cast<int32_t*>(ws + w.tables + w.dh + w.du);
+    int32_t* seg_chunk_offsets = reinterpret_cast<int32_t*>(ws + w.tables + w.dh + w.du + table_bytes(a.num_segments));
+    int rc = launch_chunk_tables(a.seg_cu, a.num_segments, seg_tables, seg_chunk_offsets, stream);
+    if (rc != QLA_OK) return rc;
+    sp.cu_seqlens = a.seg_cu; sp.num_seqs = a.num_segments; sp.chunk_offsets = seg_chunk_offsets;
+    sp.dht = a.seg_dht; sp.dht_kv = 1;
+    mode.out_map = a.seg_dh0_map;
+  }
+  int rc = launch_bwd_scan(sp, mode, total_tokens, is_bf16, stream);
+  if (rc != QLA_OK) return rc;
+  return launch_chunk_bwd(p, total_tokens, w.chunks_upper, is_bf16, stream);
 }

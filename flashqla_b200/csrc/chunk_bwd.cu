@@ -810,8 +810,7 @@ int make_tmap_rows(CUtensorMap* out, const void* base, uint64_t rows, uint64_t w
 
 int launch_chunk_bwd(const BwdParams& p, int64_t total_tokens, int total_chunks_upper, bool is_bf16,
                      cudaStream_t stream) {
-  int rc = launch_bwd_scan(p, total_tokens, is_bf16, stream);
-  if (rc != QLA_OK) return rc;
+  int rc;
   CUtensorMap tm_q, tm_k, tm_v, tm_vn, tm_do, tm_a, tm_h, tm_dh, tm_du, tm_dq, tm_dk, tm_dv;
   const uint64_t state_rows = static_cast<uint64_t>(total_chunks_upper) * p.num_v_heads * kHeadDim;
   if ((rc = make_tmap_3d(&tm_q, p.q, total_tokens, p.num_k_heads, kHeadDim, 64, 64, true, is_bf16)) != QLA_OK) return rc;

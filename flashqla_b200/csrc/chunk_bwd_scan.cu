@@ -84,11 +84,19 @@ template <typename T>
 __global__ void __launch_bounds__(kThreads, 1)
 bwd_scan_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_do, const __grid_constant__ CUtensorMap tm_w,
-                const BwdParams p) {
+                const BwdParams p, const BwdScanMode mode) {
   constexpr uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? ptx::kFmtBF16 : ptx::kFmtF16;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int hv = blockIdx.x % p.num_v_heads;
-  const int seq = blockIdx.x / p.num_v_heads;
+  // context-parallel passes: the second half of a "dual" grid computes the K x K transition matrix of the reverse
+  // recurrence over an interval's first chunks (identity start, dO treated as zero)
+  const bool pass_b = mode.dual && blockIdx.x >= static_cast<unsigned>(p.num_seqs) * p.num_v_heads;
+  const unsigned cta = pass_b ? blockIdx.x - static_cast<unsigned>(p.num_seqs) * p.num_v_heads : blockIdx.x;
+  const bool zero_do = pass_b, init_identity = pass_b, state_only = mode.state_only || pass_b;
+  const int32_t* chunk_limit = pass_b ? mode.chunk_limit_b : mode.chunk_limit;
+  const int32_t* out_map = pass_b ? mode.out_map_b : mode.out_map;
+  float* out_states = pass_b ? mode.out_b : p.dh0;
+  const int hv = cta % p.num_v_heads;
+  const int seq = cta / p.num_v_heads;
   const int hk = hv / (p.num_v_heads / p.num_k_heads);
   int seq_start, seq_end;
   if (p.cu_seqlens != nullptr) {
@@ -98,7 +106,12 @@ bwd_scan_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     seq_start = seq * p.seq_len;
     seq_end = seq_start + p.seq_len;
   }
-  const int nproc = (seq_end - seq_start + kChunk - 1) / kChunk;  // iteration i handles chunk nproc - 1 - i
+  int nproc = (seq_end - seq_start + kChunk - 1) / kChunk;  // iteration i handles chunk nproc - 1 - i
+  if (chunk_limit != nullptr) {
+    const int lim = chunk_limit[seq * p.num_v_heads + hv];
+    if (lim <= 0) return;  // nothing asked of this (interval, head); uniform for the whole CTA
+    nproc = min(nproc, lim);
+  }
   const int64_t chunk_base =
       p.chunk_offsets ? p.chunk_offsets[seq] : static_cast<int64_t>(seq) * ((p.seq_len + kChunk - 1) / kChunk);
 
@@ -234,7 +247,7 @@ bwd_scan_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         if (!(ok = wait(kQsReady, ph))) break;
         if (!(ok = wait(kSScaled, ph))) break;
         ptx::tc_fence_after_sync();
-        ptx::umma_ss_k64<128, 128>(tmem0 + kColS, d_do + so, d_qmn + so, id_q, true);
+        if (!zero_do) ptx::umma_ss_k64<128, 128>(tmem0 + kColS, d_do + so, d_qmn + so, id_q, true);
         p0_issued = false;
         if (i + 1 < nproc) {
           const int j = i + 1;
@@ -262,8 +275,9 @@ bwd_scan_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         // MMAu: Du0 = dO^T Pg (the compute warps read Du0 of this chunk before DuReady, MMA3 precedes in the pipe)
         if (!(ok = wait(kPgReady, j & 1))) break;
         ptx::tc_fence_after_sync();
-        ptx::umma_ss_k64<128, 128>(tmem0 + kColDu0, d_do + sn, d_pg + static_cast<uint64_t>((j & 1) * (8192 >> 4)),
-                                   id_u, false, bar_addr(kDu0Done));
+        if (!zero_do)
+          ptx::umma_ss_k64<128, 128>(tmem0 + kColDu0, d_do + sn, d_pg + static_cast<uint64_t>((j & 1) * (8192 >> 4)),
+                                     id_u, false, bar_addr(kDu0Done));
       }
     }
   } else if (warp >= 10) {
@@ -342,10 +356,14 @@ bwd_scan_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const int col_half = wg * 64;
     bool alive = true;
     const int st_k = p.transpose_state ? 1 : kHeadDim, st_v = p.transpose_state ? kHeadDim : 1;
-    const float* dhtp = p.dht != nullptr ? p.dht + (static_cast<int64_t>(seq) * p.num_v_heads + hv) * kHeadDim * kHeadDim
-                                         : nullptr;
-    float* dh0p = p.dh0 != nullptr ? p.dh0 + (static_cast<int64_t>(seq) * p.num_v_heads + hv) * kHeadDim * kHeadDim
-                                   : nullptr;
+    const int ht_k = (p.transpose_state && !p.dht_kv) ? 1 : kHeadDim, ht_v = (p.transpose_state && !p.dht_kv) ? kHeadDim : 1;
+    const float* dhtp = (p.dht != nullptr && !init_identity)
+                            ? p.dht + (static_cast<int64_t>(seq) * p.num_v_heads + hv) * kHeadDim * kHeadDim
+                            : nullptr;
+    const int out_row = out_map != nullptr ? out_map[seq] : seq;
+    float* dh0p = (out_states != nullptr && out_row >= 0)
+                      ? out_states + (static_cast<int64_t>(out_row) * p.num_v_heads + hv) * kHeadDim * kHeadDim
+                      : nullptr;
     T* dh_ws = static_cast<T*>(p.dh);  // [chunk][Hv][128 v][128 k]
     T* du_ws = static_cast<T*>(p.du);  // [chunk][Hv][128 v][64 tokens]
     auto dh_row = [&](int chunk) {
@@ -359,7 +377,7 @@ bwd_scan_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         alive = wait(kFull0, 0);
         egl0 = gates_of(0)->egl;
       }
-      T* hp = nproc > 0 ? dh_row(nproc - 1) : nullptr;
+      T* hp = (nproc > 0 && !state_only) ? dh_row(nproc - 1) : nullptr;
 #pragma unroll 1
       for (int kb = 0; kb < 64; kb += 16) {
         float x[16];
@@ -367,7 +385,7 @@ bwd_scan_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
           const int k = col_half + kb + j;
-          x[j] = dhtp != nullptr ? dhtp[k * st_k + v * st_v] : 0.f;
+          x[j] = dhtp != nullptr ? dhtp[k * ht_k + v * ht_v] : ((init_identity && k == v) ? 1.f : 0.f);
         }
 #pragma unroll
         for (int j = 0; j < 16; j += 2) {
@@ -400,12 +418,17 @@ bwd_scan_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       // ---------------- du^T = Du0 + rho .* D2 for this warpgroup's 32 tokens: 16-bit copy into tensor memory
       // (A operand of MMA3) and to the workspace
       if (!(alive = wait(kD2Done, ph))) break;
-      if (!(alive = wait(kDu0Done, ph))) break;
+      if (!zero_do && !(alive = wait(kDu0Done, ph))) break;
       ptx::tc_fence_after_sync();
       {
         uint32_t d2[32], u0[32], pk[16];
         ptx::tmem_ld32(tm + kColD2 + 32 * wg, d2);
-        ptx::tmem_ld32(tm + kColDu0 + 32 * wg, u0);
+        if (!zero_do) {
+          ptx::tmem_ld32(tm + kColDu0 + 32 * wg, u0);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) u0[j] = 0u;
+        }
         ptx::tmem_wait_ld();
 #pragma unroll
         for (int j = 0; j < 32; j += 4) {
@@ -419,10 +442,12 @@ bwd_scan_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         ptx::tmem_wait_st();
         ptx::tc_fence_before_sync();
         warp_arrive(&bars[kDuReady], lane);
-        T* dup = du_ws + (((chunk_base + chunk) * p.num_v_heads + hv) * kHeadDim + v) * kChunk + 32 * wg;
+        if (!state_only) {
+          T* dup = du_ws + (((chunk_base + chunk) * p.num_v_heads + hv) * kHeadDim + v) * kChunk + 32 * wg;
 #pragma unroll
-        for (int j = 0; j < 16; j += 4)
-          *reinterpret_cast<uint4*>(dup + 2 * j) = make_uint4(pk[j], pk[j + 1], pk[j + 2], pk[j + 3]);
+          for (int j = 0; j < 16; j += 4)
+            *reinterpret_cast<uint4*>(dup + 2 * j) = make_uint4(pk[j], pk[j + 1], pk[j + 2], pk[j + 3]);
+        }
       }
       // ---------------- state conversion after MMA3 (this warpgroup's 64 columns)
       if (!(alive = wait(kSDone, ph))) break;
@@ -449,9 +474,11 @@ bwd_scan_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 #pragma unroll
           for (int j = 0; j < 32; j += 2) sb[j >> 1] = pack2<T>(__uint_as_float(sf[j]), __uint_as_float(sf[j + 1]));
           ptx::tmem_st16(tm + kColSbf + col_half / 2 + 16 * h, sb);
+          if (!state_only) {
 #pragma unroll
-          for (int j = 0; j < 16; j += 4)
-            *reinterpret_cast<uint4*>(hp + col_half + 32 * h + 2 * j) = make_uint4(sb[j], sb[j + 1], sb[j + 2], sb[j + 3]);
+            for (int j = 0; j < 16; j += 4)
+              *reinterpret_cast<uint4*>(hp + col_half + 32 * h + 2 * j) = make_uint4(sb[j], sb[j + 1], sb[j + 2], sb[j + 3]);
+          }
         }
         ptx::tmem_wait_st();
         ptx::tc_fence_before_sync();
@@ -482,20 +509,21 @@ bwd_scan_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 
 }  // namespace
 
-int launch_bwd_scan(const BwdParams& p, int64_t total_tokens, bool is_bf16, cudaStream_t stream) {
+int launch_bwd_scan(const BwdParams& p, const BwdScanMode& mode, int64_t total_tokens, bool is_bf16,
+                    cudaStream_t stream) {
   CUtensorMap tm_q, tm_k, tm_do, tm_w;
   int rc;
   if ((rc = make_tmap_3d(&tm_k, p.k, total_tokens, p.num_k_heads, kHeadDim, 64, 64, true, is_bf16)) != QLA_OK) return rc;
   if ((rc = make_tmap_3d(&tm_q, p.q, total_tokens, p.num_k_heads, kHeadDim, 64, 64, true, is_bf16)) != QLA_OK) return rc;
   if ((rc = make_tmap_3d(&tm_do, p.d_o, total_tokens, p.num_v_heads, kHeadDim, 64, 64, true, is_bf16)) != QLA_OK) return rc;
   if ((rc = make_tmap_3d(&tm_w, p.w, total_tokens, p.num_v_heads, kHeadDim, 64, 64, true, is_bf16)) != QLA_OK) return rc;
-  const unsigned grid = static_cast<unsigned>(p.num_seqs) * p.num_v_heads;
+  const unsigned grid = static_cast<unsigned>(p.num_seqs) * p.num_v_heads * (mode.dual ? 2 : 1);
   if (is_bf16) {
     if ((rc = ensure_dynamic_smem<bwd_scan_kernel<__nv_bfloat16>>(kSmemBytes)) != QLA_OK) return rc;
-    bwd_scan_kernel<__nv_bfloat16><<<grid, kThreads, kSmemBytes, stream>>>(tm_q, tm_k, tm_do, tm_w, p);
+    bwd_scan_kernel<__nv_bfloat16><<<grid, kThreads, kSmemBytes, stream>>>(tm_q, tm_k, tm_do, tm_w, p, mode);
   } else {
     if ((rc = ensure_dynamic_smem<bwd_scan_kernel<__half>>(kSmemBytes)) != QLA_OK) return rc;
-    bwd_scan_kernel<__half><<<grid, kThreads, kSmemBytes, stream>>>(tm_q, tm_k, tm_do, tm_w, p);
+    bwd_scan_kernel<__half><<<grid, kThreads, kSmemBytes, stream>>>(tm_q, tm_k, tm_do, tm_w, p, mode);
   }
   QLA_CHECK_CUDA(cudaGetLastError());
   return QLA_OK;

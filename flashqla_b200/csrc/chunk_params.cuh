@@ -86,10 +86,23 @@ struct BwdParams {
   int num_seqs, seq_len, num_k_heads, num_v_heads;
   int beta_dtype;
   int transpose_state;
+  int dht_kv;                   // dht is [K, V] whatever transpose_state says for dh0 (segment end gradients)
   float scale;
 };
 
-int launch_bwd_scan(const BwdParams& p, int64_t total_tokens, bool is_bf16, cudaStream_t stream);
+// The reverse scan by itself, over `num_seqs` token intervals `cu_seqlens` (sequences, or the segments of a
+// context-parallel plan), with the switches of its state-only passes.
+struct BwdScanMode {
+  const int32_t* chunk_limit;   // [num_seqs, Hv] or NULL: only the FIRST chunk_limit chunks of an interval (<= 0: none)
+  const int32_t* out_map;       // [num_seqs] row of dh0 an interval writes (< 0: none) or NULL (identity)
+  int state_only;               // no du / dh: only the state gradient leaving the interval on the left
+  int dual;                     // second half of the grid: transition pass (identity start, dO treated as zero) with
+  const int32_t* chunk_limit_b; //   its limits,
+  const int32_t* out_map_b;     //   its output rows
+  float* out_b;                 //   and its output [rows, Hv, 128, 128]
+};
+int launch_bwd_scan(const BwdParams& p, const BwdScanMode& mode, int64_t total_tokens, bool is_bf16,
+                    cudaStream_t stream);
 int launch_chunk_bwd(const BwdParams& p, int64_t total_tokens, int total_chunks_upper, bool is_bf16,
                      cudaStream_t stream);
 

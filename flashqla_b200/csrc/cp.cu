@@ -25,7 +25,8 @@ __global__ void __launch_bounds__(256) cp_plan_kernel(const QlaCpPlanArgs a) {
     if (a.seg_next[seg] >= 0 && nchunks > 0) {
       float acc = 0.f;
       bool reached = false;
-      for (int c = nchunks - 1; c >= 0; --c) {
+      for (int i = 0; i < nchunks; ++i) {
+        const int c = a.reverse ? i : nchunks - 1 - i;  // backward: the decay accumulates from the segment's start
         const int last = min(end, start + (c + 1) * kChunk) - 1;
         acc += a.g_cumsum[static_cast<int64_t>(last) * num_heads + h];
         ++warm;
@@ -59,15 +60,19 @@ __global__ void __launch_bounds__(256) cp_plan_kernel(const QlaCpPlanArgs a) {
 // One CTA: one (raw sequence, head, 32-column slab of the state).  Thread t owns row k = t of the slab.
 __global__ void __launch_bounds__(128) cp_chain_kernel(float* __restrict__ h0, const float* __restrict__ M,
                                                        const int32_t* __restrict__ m_limit,
-                                                       const int32_t* __restrict__ raw_first_seg, int num_heads) {
+                                                       const int32_t* __restrict__ raw_first_seg, int num_heads,
+                                                       int reverse) {
   const int vt = blockIdx.x, h = blockIdx.y, r = blockIdx.z;
   const int s0 = raw_first_seg[r], s1 = raw_first_seg[r + 1];
   const int k = threadIdx.x;
   __shared__ float sh[kHeadDim][33];
-  for (int seg = s0; seg + 1 < s1; ++seg) {
+  for (int i = 0; i + 1 < s1 - s0; ++i) {
+    // forward: segment s0 + i feeds s0 + i + 1; backward: segment s1 - 1 - i feeds s1 - 2 - i
+    const int seg = reverse ? s1 - 1 - i : s0 + i;
+    const int to = reverse ? seg - 1 : seg + 1;
     if (m_limit[seg * num_heads + h] == 0) continue;  // uniform across the CTA
     const float* src = h0 + (static_cast<int64_t>(seg) * num_heads + h) * kHeadDim * kHeadDim + vt * 32;
-    float* dst = h0 + (static_cast<int64_t>(seg + 1) * num_heads + h) * kHeadDim * kHeadDim + vt * 32;
+    float* dst = h0 + (static_cast<int64_t>(to) * num_heads + h) * kHeadDim * kHeadDim + vt * 32;
     const float* m = M + (static_cast<int64_t>(seg) * num_heads + h) * kHeadDim * kHeadDim;
     __syncthreads();
     for (int i = threadIdx.x; i < kHeadDim * 32; i += 128) sh[i >> 5][i & 31] = src[(i >> 5) * kHeadDim + (i & 31)];
@@ -109,7 +114,7 @@ extern "C" QLA_API int qla_cp_chain(const QlaCpChainArgs* a, void* stream) {
   QLA_CHECK_ARG(a->num_raw_seqs > 0 && a->num_v_heads > 0, "bad sizes");
   dim3 grid(kHeadDim / 32, a->num_v_heads, a->num_raw_seqs);
   cp_chain_kernel<<<grid, 128, 0, static_cast<cudaStream_t>(stream)>>>(a->h0, a->M, a->m_limit, a->raw_first_seg,
-                                                                       a->num_v_heads);
+                                                                       a->num_v_heads, a->reverse);
   QLA_CHECK_CUDA(cudaGetLastError());
   return QLA_OK;
 }

@@ -290,6 +290,24 @@ typedef struct QlaChunkBwdArgs {
   void* workspace;
   size_t workspace_bytes;
   int32_t* status;
+  /* Context parallelism of the reverse scan (long sequences, few heads; the reference's backward has none: its
+   * grid is sequences x heads, chunk/hopper/fused_bwd.py:79).  Main call: with num_segments > 0 the scan runs over
+   * the intervals seg_cu (multiples of 64 tokens inside a sequence) starting from seg_dht (fp32 [num_segments,Hv,
+   * K,V]: the state gradient entering every segment from the right) and the first segment of every sequence
+   * writes dh0 (seg_dh0_map: row of dh0 or < 0).  State-only call (QLA_CHUNK_STATE_ONLY): cu_seqlens are the
+   * intervals; only the first chunk_limit[n,h] chunks of an interval are scanned and the gradient leaving them on
+   * the left goes to row out_map[n] of dh0; with QLA_CHUNK_DUAL_TRANSITION the same launch also produces the
+   * K x K transition matrices of those scans (chunk_limit_b, out_map_b, out_b). */
+  int32_t num_segments;
+  int32_t reserved;
+  const int32_t* seg_cu;
+  const float* seg_dht;
+  const int32_t* seg_dh0_map;
+  const int32_t* chunk_limit;
+  const int32_t* out_map;
+  const int32_t* chunk_limit_b;
+  const int32_t* out_map_b;
+  float* out_b;
 } QlaChunkBwdArgs;
 
 QLA_API size_t qla_chunk_bwd_workspace_bytes(const QlaChunkBwdArgs* args);
@@ -326,6 +344,10 @@ typedef struct QlaCpPlanArgs {
   const int32_t* h0_map;      /* [number of original sequences] or NULL                         */
   int32_t h0_dtype;           /* QLA_DT_F32 | QLA_DT_BF16                                       */
   int32_t h0_transposed;      /* caller's states are [V,K]                                      */
+  int32_t reverse;            /* plan for the backward scan: count LEADING chunks of a segment (the
+                                 accumulated decay from its start) instead of trailing ones; seg_next
+                                 then names the segment's predecessor (< 0: none)                 */
+  int32_t reserved;
 } QlaCpPlanArgs;
 
 QLA_API int qla_cp_plan(const QlaCpPlanArgs* args, void* stream);
@@ -343,6 +365,8 @@ typedef struct QlaCpChainArgs {
   const float* M;
   const int32_t* m_limit;
   const int32_t* raw_first_seg;
+  int32_t reverse;            /* backward: h0[seg - 1] += M[seg] * h0[seg], last segment first  */
+  int32_t reserved;
 } QlaCpChainArgs;
 
 QLA_API int qla_cp_chain(const QlaCpChainArgs* args, void* stream);

@@ -26,8 +26,8 @@ def _cuda(d):
     return {n: t.cuda() for n, t in d.items()}
 
 
-def _report(got: dict, ref: dict, rms_tol=None):
-    lines, ok = [], True
+def _report(got: dict, ref: dict, rms_tol=None, what=""):
+    lines, ok = [what] if what else [], True
     for n in GRADS:
         if ref.get(n) is None:
             assert got.get(n) is None
@@ -39,7 +39,7 @@ def _report(got: dict, ref: dict, rms_tol=None):
     assert ok, "; ".join(lines)
 
 
-def _raw_bwd(fq, c, cu=None, with_h0=True, with_dht=True, saved=True):
+def _raw_bwd(fq, c, cu=None, with_h0=True, with_dht=True, saved=True, auto_cp=True):
     h0 = c.get("h0") if with_h0 else None
     out = fq.chunk_gated_delta_rule_fwd(c["q"], c["k"], c["v"], c["g"], c["beta"], initial_state=h0,
                                         cu_seqlens=cu, output_h=saved, output_v_new=saved, output_w=saved)
@@ -47,7 +47,7 @@ def _raw_bwd(fq, c, cu=None, with_h0=True, with_dht=True, saved=True):
     v_new, w = (out[5], out[6]) if saved else (None, None)  # not saved: h, v_new and w are recomputed
     res = fq.chunk_gated_delta_rule_bwd(c["q"], c["k"], c["v"], g_cs, c["beta"], A, c["do"],
                                         dht=c["dht"] if with_dht else None, initial_state=h0, cu_seqlens=cu,
-                                        h=h, v_new=v_new, w=w)
+                                        h=h, v_new=v_new, w=w, auto_cp=auto_cp)
     fq.check_device_status()
     return dict(zip(GRADS, res))
 
@@ -126,3 +126,54 @@ def test_backward_repeatable_bitwise(fq):
         again = _raw_bwd(fq, inp)
         for n in GRADS:
             assert torch.equal(first[n], again[n]), n
+
+
+@pytest.mark.parametrize("gate_div,zero_gate,T", [(1.0, 0.0, 4096 + 37), (16.0, 0.25, 2048 + 37)])
+def test_backward_context_parallel_matches_oracle(fq, gate_div, zero_gate, T):
+    """One long sequence on few heads: the reverse scan runs over segments whose right-end gradients come from
+    state-only passes over each segment's leading chunks; with g/16 and zero-gate heads the decay never passes
+    the threshold and the transition-matrix chain is exercised.  Checked against the oracle and against the
+    uncut backward."""
+    from flashqla_b200 import cp
+    inp = orc.make_prefill_inputs(1, T, 2, 4, seed=41, with_h0=True, with_grads=True, gate_div=gate_div,
+                                  zero_gate_heads=zero_gate)
+    c = _cuda(inp)
+    assert cp.get_plan([T], 4, c["q"].device).use_cp
+    got = _raw_bwd(fq, c)
+    uncut = _raw_bwd(fq, c, auto_cp=False)
+    ref = orc.chunk_gdr_bwd(inp["q"], inp["k"], inp["v"], inp["g"], inp["beta"], inp["do"], dht=inp["dht"],
+                            h0=inp["h0"])
+    tol = {"dg": 1e-2} if gate_div > 1 else None
+    _report(uncut, ref, rms_tol=tol, what="uncut")
+    _report(got, ref, rms_tol=tol, what="segments")
+    # zero-gate heads never forget: the fp32 transition chain and the chunk-by-chunk 16-bit states round differently
+    mutual = 2e-3 if zero_gate == 0 else 5e-3
+    for n in GRADS:
+        assert orc.rel_rms(got[n].float().cpu(), uncut[n].float().cpu()) <= mutual, n
+
+
+def test_backward_context_parallel_varlen_transposed(fq):
+    """Mixed lengths (one cut, one short, one cut with a ragged tail) with [V, K] states."""
+    from flashqla_b200 import cp
+    lens = [3000, 100, 2077]
+    cu = torch.tensor([0, 3000, 3100, 5177], dtype=torch.int32)
+    inp = orc.make_prefill_inputs(1, 5177, 1, 2, seed=42, with_h0=True, with_grads=True, n_states=3, gate_div=4.0)
+    c = _cuda(inp)
+    assert cp.get_plan(lens, 2, c["q"].device).use_cp
+    got = _raw_bwd(fq, c, cu=cu.cuda())
+    ref = orc.chunk_gdr_bwd(inp["q"], inp["k"], inp["v"], inp["g"], inp["beta"], inp["do"], dht=inp["dht"],
+                            h0=inp["h0"], cu_seqlens=cu)
+    _report(got, ref)
+    # the same through the transposed state layout
+    h0t, dhtt = c["h0"].transpose(-1, -2).contiguous(), c["dht"].transpose(-1, -2).contiguous()
+    out = fq.chunk_gated_delta_rule_fwd(c["q"], c["k"], c["v"], c["g"], c["beta"], initial_state=h0t,
+                                        cu_seqlens=cu.cuda(), output_h=True, output_v_new=True, output_w=True,
+                                        transpose_state_layout=True)
+    g_cs, A, o, h, fs, v_new, w = out
+    res = fq.chunk_gated_delta_rule_bwd(c["q"], c["k"], c["v"], g_cs, c["beta"], A, c["do"], dht=dhtt,
+                                        initial_state=h0t, cu_seqlens=cu.cuda(), h=h, v_new=v_new, w=w,
+                                        transpose_state_layout=True)
+    fq.check_device_status()
+    gt = dict(zip(GRADS, res))
+    gt["dh0"] = gt["dh0"].transpose(-1, -2)
+    _report(gt, ref)
