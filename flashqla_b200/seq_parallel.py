@@ -1,5 +1,6 @@
-"""Cross-GPU sequence parallelism for the chunked forward: ONE long sequence cut into contiguous slices,
-one slice per rank, with a single all-gather of chunk-boundary states.
+"""Cross-GPU sequence parallelism for the chunked forward and backward: ONE long sequence cut into contiguous
+slices, one slice per rank, with a single all-gather of chunk-boundary states (forward) or of their gradients
+(backward).
 
 The reference has no multi-GPU path; the math is that of its intra-card context parallelism
 (flash_qla/ops/gated_delta_rule/chunk/cp_context.py:117-176 and ``correct_initial_states``,
@@ -22,6 +23,12 @@ Per rank:
 
 The final state of the sequence is the one the last rank computes.  Received data is ordinary local memory
 (NCCL writes it there); no kernel of this library reads a peer's memory.
+
+The backward mirrors this from the right: the gradient of the state at the START of a slice is an affine
+function of the gradient at its end, ``dS_start = G + Md @ dS_end``; every rank computes ``(G, Md)`` of its slice
+with one state-only launch of the reverse scan (zero start for ``G``, identity start and ``dO`` taken as zero
+for ``Md``), one all-gather moves them, every rank folds the summaries of the ranks AFTER it into the gradient
+entering its slice from the right and runs the ordinary backward on the slice.
 """
 from __future__ import annotations
 
@@ -163,6 +170,7 @@ def chunk_gated_delta_rule_fwd_sp(
     group=None,
     broadcast_final_state: bool = False,
     gather: Optional[Callable[[torch.Tensor], torch.Tensor]] = None,
+    return_incoming_state: bool = False,
 ) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
     """Forward of one sequence whose tokens are spread over the ranks of ``group`` in rank order; every rank
     passes ITS slice (``[1, T_rank, ...]``, a whole number of 64-token chunks; slices may differ in length)
@@ -171,7 +179,9 @@ def chunk_gated_delta_rule_fwd_sp(
     so pass the same tensor everywhere or ``None``).  The final state is returned on the last rank (on every
     rank with ``broadcast_final_state``), ``None`` elsewhere.  One collective: an all-gather of
     ``2 * Hv * 64 KiB`` per rank.  ``gather`` replaces the collective (a callable from the local summary to
-    the ``[world, 2, Hv, 128, 128]`` stack) for callers that move the summaries themselves."""
+    the ``[world, 2, Hv, 128, 128]`` stack) for callers that move the summaries themselves.  With
+    ``return_incoming_state`` a third value is returned: the state entering this rank's slice ``[1,Hv,128,128]``
+    (``None`` when it is zero), which ``chunk_gated_delta_rule_bwd_sp`` takes."""
     import torch.distributed as dist
     rank, world = dist.get_rank(group), dist.get_world_size(group)
     ctx = slice_summary(q, k, v, g, beta, scale)
@@ -184,8 +194,112 @@ def chunk_gated_delta_rule_fwd_sp(
     if rank > 0 or initial_state is not None:
         incoming = fold_incoming_state(gathered, rank, initial_state)
     o, end_state = slice_forward(ctx, incoming)
+    extra = ((incoming.unsqueeze(0) if incoming is not None else None),) if return_incoming_state else ()
     if broadcast_final_state:
         dist.broadcast(end_state, src=dist.get_global_rank(group, world - 1) if group is not None else world - 1,
                        group=group)
-        return o, end_state
-    return o, (end_state if rank == world - 1 else None)
+        return (o, end_state) + extra
+    return (o, (end_state if rank == world - 1 else None)) + extra
+
+
+# ------------------------------------------------------------------------------------------------ backward
+
+def fold_incoming_gradient(gathered: torch.Tensor, rank: int, dht: Optional[torch.Tensor]) -> torch.Tensor:
+    """Gradient of the state BEHIND the slice of ``rank`` (what enters its reverse scan).  ``gathered`` is
+    ``[world, 2, Hv, K, V]``: per rank ``G`` (the start-state gradient of its slice for a zero gradient behind
+    it) and ``Md``.  ``dht`` is the gradient of the sequence's final state.  Pure torch, any device."""
+    world = gathered.shape[0]
+    Hv, K, V = gathered.shape[2:]
+    D = (torch.zeros(Hv, K, V, dtype=torch.float32, device=gathered.device) if dht is None
+         else dht.reshape(Hv, K, V).to(torch.float32))
+    for j in range(world - 1, rank, -1):
+        D = gathered[j, 0] + torch.bmm(gathered[j, 1], D)
+    return D
+
+
+@dataclass
+class _SliceBackwardContext:
+    tensors: tuple          # q, k, v, beta, do, g_cumsum, A, h, v_new, w, incoming
+    scale: float
+    summary: torch.Tensor   # [2, Hv, 128, 128] = (G_slice, Md_slice)
+
+
+def slice_backward_summary(q, k, v, g, beta, do, incoming: Optional[torch.Tensor] = None,
+                           scale: Optional[float] = None) -> _SliceBackwardContext:
+    """Forward recomputation of the slice from the state entering it (``g_cumsum``, ``A``, ``w``, ``h``,
+    ``v_new``) and the slice's ``(G, Md)``: ONE launch of the reverse scan, state-only, its two halves starting
+    from zero and from the identity."""
+    from .chunk import chunk_gated_delta_rule_fwd
+    from .utils import device_status
+    if q.shape[0] != 1:
+        raise ValueError(f"one sequence: the batch size is expected to be 1 rather than {q.shape[0]}")
+    T, Hk, Hv = k.shape[1], k.shape[2], beta.shape[2]
+    if T % CHUNK != 0:
+        raise ValueError(f"a slice must be a whole number of {CHUNK}-token chunks (the last rank included), got {T}")
+    dev = k.device
+    scale = q.shape[-1] ** -0.5 if scale is None else float(scale)
+    q, k, v, beta, do = (x if x.is_contiguous() else x.contiguous() for x in (q, k, v, beta, do))
+    if do.dtype != q.dtype:
+        do = do.to(q.dtype)
+    g_cumsum, A, _, h, _, v_new, w = chunk_gated_delta_rule_fwd(
+        q, k, v, g, beta, scale=scale, initial_state=incoming, output_h=True, output_v_new=True, output_w=True)
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=dev)
+    n_chunks = T // CHUNK
+    summary = torch.empty(2, 1, Hv, 128, 128, dtype=torch.float32, device=dev)
+    limit = torch.full((1, Hv), n_chunks, dtype=torch.int32, device=dev)
+    cu, row0 = i32([0, T]), i32([0])
+    sa = _cabi.QlaChunkBwdArgs(
+        batch=1, seq_len=T, num_seqs=1, num_k_heads=Hk, num_v_heads=Hv, qkv_dtype=_cabi.dtype_code(q.dtype),
+        beta_dtype=_cabi.QLA_DT_F32, flags=_cabi.CHUNK_STATE_ONLY | _cabi.CHUNK_DUAL_TRANSITION, scale=scale,
+        q=_cabi.ptr(q), k=_cabi.ptr(k), g_cumsum=_cabi.ptr(g_cumsum), w=_cabi.ptr(w), d_o=_cabi.ptr(do),
+        cu_seqlens=cu.data_ptr(), dh0=summary[0].data_ptr(), status=_cabi.ptr(device_status(dev)),
+        chunk_limit=limit.data_ptr(), out_map=row0.data_ptr(), chunk_limit_b=limit.data_ptr(),
+        out_map_b=row0.data_ptr(), out_b=summary[1].data_ptr())
+    with torch.cuda.device(dev):
+        _cabi.check(_cabi.lib().qla_chunk_bwd(sa, _cabi.current_stream(dev)), "qla_chunk_bwd (state-only)")
+    return _SliceBackwardContext((q, k, v, beta, do, g_cumsum, A, h, v_new, w, incoming), scale, summary[:, 0])
+
+
+def slice_backward(ctx: _SliceBackwardContext, incoming_gradient: Optional[torch.Tensor]):
+    """The ordinary backward on the slice with ``incoming_gradient`` ``[Hv,128,128]`` entering from the right
+    (``None`` = zero).  Returns ``(dq, dk, dv, dbeta, dg, dS_start)``; ``dS_start`` is the gradient of the state
+    entering the slice: on the first rank that of the sequence's initial state."""
+    from .chunk import chunk_gated_delta_rule_bwd
+    q, k, v, beta, do, g_cumsum, A, h, v_new, w, incoming = ctx.tensors
+    Hv = beta.shape[2]
+    h0 = incoming if incoming is not None else torch.zeros(1, Hv, 128, 128, dtype=torch.float32, device=q.device)
+    dht = incoming_gradient.unsqueeze(0).contiguous() if incoming_gradient is not None else None
+    return chunk_gated_delta_rule_bwd(q, k, v, g_cumsum, beta, A, do, dht=dht, scale=ctx.scale, initial_state=h0,
+                                      h=h, v_new=v_new, w=w)
+
+
+def chunk_gated_delta_rule_bwd_sp(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    g: torch.Tensor,
+    beta: torch.Tensor,
+    do: torch.Tensor,
+    incoming_state: Optional[torch.Tensor] = None,
+    dht: Optional[torch.Tensor] = None,
+    scale: Optional[float] = None,
+    group=None,
+    gather: Optional[Callable[[torch.Tensor], torch.Tensor]] = None,
+):
+    """Backward of ``chunk_gated_delta_rule_fwd_sp``: every rank passes its slice of the inputs (``g`` the raw
+    gates), ``do`` of its slice and the state that entered its slice in the forward (``incoming_state``, the third
+    value of the forward with ``return_incoming_state``); ``dht`` ``[1,Hv,128,128]`` is the gradient of the
+    sequence's final state (same tensor on every rank, or ``None``).  Returns ``(dq, dk, dv, dbeta, dg, dS_start)``
+    of the slice.  One collective: an all-gather of ``2 * Hv * 64 KiB`` per rank."""
+    import torch.distributed as dist
+    rank, world = dist.get_rank(group), dist.get_world_size(group)
+    ctx = slice_backward_summary(q, k, v, g, beta, do, incoming_state, scale)
+    if gather is not None:
+        gathered = gather(ctx.summary)
+    else:
+        gathered = torch.empty((world,) + tuple(ctx.summary.shape), dtype=torch.float32, device=q.device)
+        dist.all_gather_into_tensor(gathered, ctx.summary.contiguous(), group=group)
+    incoming_gradient = None
+    if rank < world - 1 or dht is not None:
+        incoming_gradient = fold_incoming_gradient(gathered, rank, dht)
+    return slice_backward(ctx, incoming_gradient)

@@ -56,6 +56,40 @@ def test_slices_reproduce_whole_sequence(cuts, gate_div, with_h0):
     assert orc.rel_rms(end.cpu(), fs1.cpu()) <= RMS_TOL
 
 
+@pytest.mark.parametrize("cuts,gate_div", [((1024, 1024), 1.0), ((2048, 1024, 3072), 4.0), ((512, 512), 64.0)])
+def test_backward_slices_reproduce_whole_sequence(cuts, gate_div):
+    """Forward carry, then the reverse carry: per slice (G, Md) from one state-only launch of the reverse scan,
+    the stack stands in for the all-gather, fold from the right, ordinary backward per slice.  Tolerance as for
+    the backward: relative rms 5e-3 per gradient (dg 1e-2 with weak gates) against the fp64 oracle on the whole
+    sequence."""
+    from flashqla_b200 import seq_parallel as sp
+    T, Hk, Hv = sum(cuts), 2, 4
+    inp = orc.make_prefill_inputs(1, T, Hk, Hv, seed=35, with_h0=True, with_grads=True, gate_div=gate_div)
+    c = {n: t.cuda() for n, t in inp.items()}
+    _, _, fctx = _run_slices(sp, c, cuts, c["h0"])
+    fgathered = torch.stack([x.summary for x in fctx])
+    bctx, t0 = [], 0
+    for r, n in enumerate(cuts):
+        sl = slice(t0, t0 + n)
+        incoming = sp.fold_incoming_state(fgathered, r, c["h0"]).unsqueeze(0)
+        bctx.append(sp.slice_backward_summary(c["q"][:, sl], c["k"][:, sl], c["v"][:, sl], c["g"][:, sl],
+                                              c["beta"][:, sl], c["do"][:, sl], incoming))
+        t0 += n
+    gathered = torch.stack([x.summary for x in bctx])
+    if gate_div > 4.0:
+        assert float(gathered[1, 1].abs().max()) > 1e-5   # a gradient transition matrix really crosses
+    parts = [sp.slice_backward(ctx, sp.fold_incoming_gradient(gathered, r, c["dht"])) for r, ctx in enumerate(bctx)]
+    import flashqla_b200 as fq
+    fq.check_device_status()
+    ref = orc.chunk_gdr_bwd(inp["q"], inp["k"], inp["v"], inp["g"], inp["beta"], inp["do"], dht=inp["dht"],
+                            h0=inp["h0"])
+    for i, n in enumerate(("dq", "dk", "dv", "db", "dg")):
+        got = torch.cat([p[i] for p in parts], dim=1).float().cpu()
+        tol = 1e-2 if (n == "dg" and gate_div > 1.0) else RMS_TOL
+        assert orc.rel_rms(got, ref[n]) <= tol, (n, orc.rel_rms(got, ref[n]))
+    assert orc.rel_rms(parts[0][5].float().cpu(), ref["dh0"]) <= RMS_TOL
+
+
 def test_slice_must_be_whole_chunks():
     from flashqla_b200 import seq_parallel as sp
     inp = orc.make_prefill_inputs(1, 100, 1, 2, seed=1)
@@ -78,8 +112,20 @@ def _nccl_rank(rank, world, port, out):
     o, fs = fq.chunk_gated_delta_rule_fwd_sp(c["q"], c["k"], c["v"], c["g"], c["beta"], initial_state=c["h0"],
                                              broadcast_final_state=True)
     ref = orc.chunk_gdr_fwd(inp["q"], inp["k"], inp["v"], inp["g"], inp["beta"], h0=inp["h0"], dtype=torch.float64)
+    # backward: the reverse carry over the same group
+    full = orc.make_prefill_inputs(1, T, Hk, Hv, seed=33, with_h0=True, with_grads=True)
+    do, dht = full["do"][:, sl].cuda(), full["dht"].cuda()
+    _, _, incoming = fq.chunk_gated_delta_rule_fwd_sp(c["q"], c["k"], c["v"], c["g"], c["beta"],
+                                                      initial_state=c["h0"], return_incoming_state=True)
+    grads = fq.chunk_gated_delta_rule_bwd_sp(c["q"], c["k"], c["v"], c["g"], c["beta"], do, incoming_state=incoming,
+                                             dht=dht)
+    bref = orc.chunk_gdr_bwd(full["q"], full["k"], full["v"], full["g"], full["beta"], full["do"], dht=full["dht"],
+                             h0=full["h0"])
+    e_b = max(orc.rel_rms(grads[i].float().cpu(), bref[n][:, sl]) for i, n in enumerate(("dq", "dk", "dv", "db", "dg")))
+    if rank == 0:
+        e_b = max(e_b, orc.rel_rms(grads[5].float().cpu(), bref["dh0"]))
     err = torch.tensor([orc.rel_rms(o.float().cpu(), ref["o"][:, sl]),
-                        orc.rel_rms(fs.float().cpu(), ref["final_state"])], device="cuda")
+                        orc.rel_rms(fs.float().cpu(), ref["final_state"]), e_b], device="cuda")
     dist.all_reduce(err, op=dist.ReduceOp.MAX)
     if rank == 0:
         out.put(err.cpu().tolist())
@@ -104,5 +150,5 @@ def test_two_gpus_nccl_all_gather():
     for p in procs:
         p.join(300)
         assert p.exitcode == 0
-    e_o, e_fs = out.get()
-    assert e_o <= RMS_TOL and e_fs <= RMS_TOL
+    e_o, e_fs, e_b = out.get()
+    assert e_o <= RMS_TOL and e_fs <= RMS_TOL and e_b <= RMS_TOL

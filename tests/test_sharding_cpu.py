@@ -142,3 +142,59 @@ def test_sequence_parallel_carry_reproduces_single_rank(world):
         p.join(180)
         assert p.exitcode == 0
     assert out.get() < 1e-5
+
+
+def _sp_bwd_rank_main(rank, world, port, out):
+    """Reverse carry of the sequence-parallel backward with the oracle standing in for the kernels: every rank
+    summarises its slice as (start-state gradient for a zero gradient behind it, gradient transition matrix),
+    one all_gather, fold from the right, then the slice's backward with its incoming gradient."""
+    from flashqla_b200.seq_parallel import fold_incoming_gradient, fold_incoming_state
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    Hv, K, T = 2, 64, 64 * 2 * world
+    inp = orc.make_prefill_inputs(1, T, 1, Hv, K=K, V=K, seed=11, with_h0=True, with_grads=True,
+                                  dtype=torch.float32, gate_div=4.0)
+    sl = slice(rank * T // world, (rank + 1) * T // world)
+    mine = {n: inp[n][:, sl] for n in ("q", "k", "v", "g", "beta", "do")}
+    # forward carry first: the state entering the slice
+    fwd = lambda v, h0: orc.chunk_gdr_fwd(mine["q"], mine["k"], v, mine["g"], mine["beta"], h0=h0, dtype=torch.float64)
+    eye = torch.eye(K).expand(1, Hv, K, K)
+    fsum = torch.stack((fwd(mine["v"], None)["final_state"][0], fwd(torch.zeros_like(mine["v"]), eye)["final_state"][0])).float()
+    fg = [torch.empty_like(fsum) for _ in range(world)]
+    dist.all_gather(fg, fsum)
+    incoming = fold_incoming_state(torch.stack(fg), rank, inp["h0"])[None]
+    bwd = lambda do, dht: orc.chunk_gdr_bwd(mine["q"], mine["k"], mine["v"], mine["g"], mine["beta"], do, dht=dht,
+                                            h0=incoming)
+    G = bwd(mine["do"], None)["dh0"][0]
+    Md = bwd(torch.zeros_like(mine["do"]), eye.contiguous())["dh0"][0]
+    bsum = torch.stack((G, Md)).float()
+    bg = [torch.empty_like(bsum) for _ in range(world)]
+    dist.all_gather(bg, bsum)
+    D = fold_incoming_gradient(torch.stack(bg), rank, inp["dht"])
+    res = bwd(mine["do"], D[None])
+    full = orc.chunk_gdr_bwd(inp["q"], inp["k"], inp["v"], inp["g"], inp["beta"], inp["do"], dht=inp["dht"], h0=inp["h0"])
+    err = 0.0
+    for n in ("dq", "dk", "dv", "db", "dg"):
+        err = max(err, float((res[n].float() - full[n][:, sl].float()).abs().max() / full[n].float().abs().max()))
+    if rank == 0:
+        err = max(err, float((res["dh0"] - full["dh0"]).abs().max() / full["dh0"].abs().max()))
+    t = torch.tensor([err])
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        out.put(float(t.item()))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_sequence_parallel_reverse_carry_reproduces_single_rank(world):
+    ctx = mp.get_context("spawn")
+    out = ctx.SimpleQueue()
+    port = _free_port()
+    procs = [ctx.Process(target=_sp_bwd_rank_main, args=(r, world, port, out)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(180)
+        assert p.exitcode == 0
+    assert out.get() < 1e-4
