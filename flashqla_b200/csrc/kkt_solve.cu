@@ -26,15 +26,18 @@ namespace qla {
 
 namespace {
 
+// The inverse is formed IN PLACE: every block of X = (I + L)^-1 overwrites the block of L it was computed from, and
+// the products L21 X11 pass through the (never used) upper-right 32 x 32 block of the same tile.  One fp32 tile
+// per chunk keeps a CTA at 67 KiB of shared memory and 128 tensor-memory columns: three CTAs per SM.
 constexpr int kLStride = 68;  // floats per L row: 16-byte aligned rows, conflict-free float4 stores
-constexpr int kXStride = 68;  // two 64 x 68 fp32 X tiles = 34 816 B, so the L area after them stays 1 KiB aligned
+constexpr int kXStride = kLStride;
 // Product precision of the blocked inverse.  Block size 16 keeps 3xTF32; block size 32 uses single TF32
 // products like the reference's fp32-tile gemm there (chunk/hopper/kkt_solve.py:181-183): against an fp64
 // inverse the error of that block is 1.70e-3 relative rms instead of 1.68e-3 (the 16-bit rounding of A
 // dominates both), and o / final state do not move in the fourth digit.
 constexpr bool kSplit32 = false;
 constexpr bool kSplit16 = true;
-constexpr int kTStride = 40;  // 32 columns + 8: conflict-free fragment loads
+constexpr int kTStride = kLStride;  // the products live in columns 32..63 of rows 0..31 of the chunk's tile
 
 __device__ __forceinline__ uint32_t to_tf32(float x) {
   uint32_t r;
@@ -112,12 +115,11 @@ __device__ __forceinline__ void pair_sync(int ci) {  // the two warps that own o
   asm volatile("bar.sync %0, 64;" ::"r"(ci + 1) : "memory");
 }
 
-// K tile 32 KiB + X tiles + L tiles (later the Aw tile) + T
-constexpr size_t kKktSmemBytes = 1024 + 32768 + 2 * 64 * kXStride * sizeof(float) + 2 * 64 * kLStride * sizeof(float) +
-                                 2 * 32 * kTStride * sizeof(float);
+// K tile 32 KiB + one fp32 L / X tile per chunk (later the Aw, A and w staging tiles)
+constexpr size_t kKktSmemBytes = 1024 + 32768 + 2 * 64 * kLStride * sizeof(float);
 
 template <typename T>
-__global__ void __launch_bounds__(128) kkt_solve_kernel(const __grid_constant__ CUtensorMap tm_k,
+__global__ void __launch_bounds__(128, 3) kkt_solve_kernel(const __grid_constant__ CUtensorMap tm_k,
                                                         const __grid_constant__ CUtensorMap tm_q,
                                                         const __grid_constant__ CUtensorMap tm_a,
                                                         const __grid_constant__ CUtensorMap tm_w,
@@ -150,12 +152,10 @@ __global__ void __launch_bounds__(128) kkt_solve_kernel(const __grid_constant__ 
 
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* sK = smem_raw + ((1024u - (ptx::smem_u32(smem_raw) & 1023u)) & 1023u);
-  float* sX = reinterpret_cast<float*>(sK + 32768);                                       // [2][64][kXStride]
-  float* sL = reinterpret_cast<float*>(sK + 32768 + 2 * 64 * kXStride * sizeof(float));  // [2][64][kLStride]
+  float* sL = reinterpret_cast<float*>(sK + 32768);  // [2][64][kLStride]: L, then X in place
   uint8_t* sAw = reinterpret_cast<uint8_t*>(sL);     // 16 KiB [128 tokens][64] tile -A diag(beta gamma) (SW128), overlays L once solved
   uint8_t* sAst = sAw + 16384;                       // 16 KiB [128 tokens][64] staging tile of A for the TMA store (SW128)
   uint8_t* sW = sAw;                                 // 32 KiB staging tile of w (two [128][64] halves, SW128), once both are consumed
-  float* sT = sL + 2 * 64 * kLStride;                // [2][32][kTStride] products L21 X11
   __shared__ __align__(16) float s_bg[128];          // -beta * gamma per token
   __shared__ __align__(16) float s_g[128];
   __shared__ __align__(16) float s_rk[128];          // 1 / |k_t| per token (in-kernel q/k L2 norm), else unused
@@ -169,7 +169,7 @@ __global__ void __launch_bounds__(128) kkt_solve_kernel(const __grid_constant__ 
     ptx::fence_mbar_init();
   }
   if (warp == 0) {
-    ptx::tmem_alloc(&tmem_base_s, 256);
+    ptx::tmem_alloc(&tmem_base_s, 128);
     ptx::tmem_relinquish();
   }
   ptx::tc_fence_before_sync();
@@ -282,14 +282,6 @@ __global__ void __launch_bounds__(128) kkt_solve_kernel(const __grid_constant__ 
 
   float* Lc = sL + ci * 64 * kLStride;
   T* Ab = static_cast<T*>(p.A);
-  // The inverse only ever writes the lower block triangle of the X tiles (diagonal blocks in full), so the
-  // zeros above it are written once per CTA, not once per head.  The first barrier of the head loop orders
-  // them before any other thread's writes.
-  if (ok && p.A_in == nullptr) {
-    float* xrow = sX + tid * kXStride;
-#pragma unroll 1
-    for (int j4 = 0; j4 < kXStride; j4 += 4) *reinterpret_cast<float4*>(xrow + j4) = make_float4(0.f, 0.f, 0.f, 0.f);
-  }
 
   int mma_uses = 0;  // completed phases of bar_mma after the first (K K^T)
   bool w_store_pending = false;
@@ -337,7 +329,7 @@ __global__ void __launch_bounds__(128) kkt_solve_kernel(const __grid_constant__ 
     }
     __syncthreads();
 
-    float* Xc = sX + ci * 64 * kXStride;
+    float* Xc = Lc;  // in place
     if (p.A_in != nullptr) {
       // A comes from an earlier call: row c of this chunk straight into the X tile
       const T* arow = static_cast<const T*>(p.A_in) + ((static_cast<int64_t>(tok0) + tid) * p.num_v_heads + hv) * 64;
@@ -351,7 +343,7 @@ __global__ void __launch_bounds__(128) kkt_solve_kernel(const __grid_constant__ 
       pair_sync(ci);
     } else {
     // ---- blocked inverse of I + L for this chunk (64 threads = warps 2 ci, 2 ci + 1)
-    float* Tc = sT + ci * 32 * kTStride;
+    float* Tc = Lc + 32;  // rows 0..31, columns 32..63 of the tile
     const int wl = warp & 1;  // warp within the chunk
     {
       // the four 16 x 16 diagonal blocks: thread = (block, column)
@@ -364,6 +356,7 @@ __global__ void __launch_bounds__(128) kkt_solve_kernel(const __grid_constant__ 
         for (int j = 0; j < i; ++j) acc -= Lc[(b0 + i) * kLStride + b0 + j] * x[j];
         x[i] = acc;
       }
+      __syncwarp();  // a block's 16 threads sit in one warp: all have read the block before it is overwritten
 #pragma unroll
       for (int i = 0; i < 16; ++i) Xc[(b0 + i) * kXStride + b0 + cc] = x[i];
     }
@@ -403,23 +396,38 @@ __global__ void __launch_bounds__(128) kkt_solve_kernel(const __grid_constant__ 
     __syncthreads();
     const bool full_pair = tok0 + 128 <= seq_end;
     {
+      // The staging tiles overlay the fp32 tile they are built from: every thread first takes its whole row into
+      // registers (both 16-bit forms), and writes after a barrier.  Columns 32..63 of rows 0..31 hold the scratch
+      // products, not zeros: they are skipped.
       const float* xr = Xc + c * kXStride;
       const float* bg = s_bg + ci * 64;
-      T* arow = Ab + (tok * p.num_v_heads + hv) * 64;
-#pragma unroll 2
+      uint32_t aw[32], av[32];
+#pragma unroll
       for (int c16 = 0; c16 < 8; ++c16) {
-        const float4 x0 = *reinterpret_cast<const float4*>(xr + c16 * 8);
-        const float4 x1 = *reinterpret_cast<const float4*>(xr + c16 * 8 + 4);
+        float4 x0 = *reinterpret_cast<const float4*>(xr + c16 * 8);
+        float4 x1 = *reinterpret_cast<const float4*>(xr + c16 * 8 + 4);
+        if (c16 >= 4 && c < 32) x0 = x1 = make_float4(0.f, 0.f, 0.f, 0.f);
         const float4 b0 = *reinterpret_cast<const float4*>(bg + c16 * 8);
         const float4 b1 = *reinterpret_cast<const float4*>(bg + c16 * 8 + 4);
+        aw[4 * c16 + 0] = pack2<T>(x0.x * b0.x, x0.y * b0.y);
+        aw[4 * c16 + 1] = pack2<T>(x0.z * b0.z, x0.w * b0.w);
+        aw[4 * c16 + 2] = pack2<T>(x1.x * b1.x, x1.y * b1.y);
+        aw[4 * c16 + 3] = pack2<T>(x1.z * b1.z, x1.w * b1.w);
+        av[4 * c16 + 0] = pack2<T>(x0.x, x0.y);
+        av[4 * c16 + 1] = pack2<T>(x0.z, x0.w);
+        av[4 * c16 + 2] = pack2<T>(x1.x, x1.y);
+        av[4 * c16 + 3] = pack2<T>(x1.z, x1.w);
+      }
+      __syncthreads();
+      T* arow = Ab + (tok * p.num_v_heads + hv) * 64;
+#pragma unroll
+      for (int c16 = 0; c16 < 8; ++c16) {
         const uint32_t off = ptx::sw128_offset(tid, c16);  // row = token within the pair
-        *reinterpret_cast<uint4*>(sAw + off) =
-            make_uint4(pack2<T>(x0.x * b0.x, x0.y * b0.y), pack2<T>(x0.z * b0.z, x0.w * b0.w),
-                       pack2<T>(x1.x * b1.x, x1.y * b1.y), pack2<T>(x1.z * b1.z, x1.w * b1.w));
+        *reinterpret_cast<uint4*>(sAw + off) = make_uint4(aw[4 * c16], aw[4 * c16 + 1], aw[4 * c16 + 2], aw[4 * c16 + 3]);
         if (p.A_in == nullptr) {
-          const uint4 av = make_uint4(pack2<T>(x0.x, x0.y), pack2<T>(x0.z, x0.w), pack2<T>(x1.x, x1.y), pack2<T>(x1.z, x1.w));
-          if (full_pair) *reinterpret_cast<uint4*>(sAst + off) = av;
-          else if (valid) *reinterpret_cast<uint4*>(arow + c16 * 8) = av;  // ragged tail: the next sequence owns the rest
+          const uint4 a4 = make_uint4(av[4 * c16], av[4 * c16 + 1], av[4 * c16 + 2], av[4 * c16 + 3]);
+          if (full_pair) *reinterpret_cast<uint4*>(sAst + off) = a4;
+          else if (valid) *reinterpret_cast<uint4*>(arow + c16 * 8) = a4;  // ragged tail: the next sequence owns the rest
         }
       }
     }
@@ -433,11 +441,13 @@ __global__ void __launch_bounds__(128) kkt_solve_kernel(const __grid_constant__ 
       }
       __syncwarp();
       ptx::tc_fence_after_sync();
-      const uint32_t idesc = ptx::mma_idesc(128, 128, fmt, ptx::kMajorK, ptx::kMajorMN);
+      // two M = 64 products into the same 128 columns: row r of chunk 0 lands in lane (r % 16) + 32 (r / 16), the
+      // rows of chunk 1 in the 16 lanes above them
+      const uint32_t idesc = ptx::mma_idesc(64, 128, fmt, ptx::kMajorK, ptx::kMajorMN);
       const uint64_t da = ptx::smem_desc_sw128(ptx::smem_u32(sAw), 16, 1024);
       const uint64_t db = ptx::smem_desc_sw128(ptx::smem_u32(sK), 16384, 1024);
-      ptx::umma_ss_k64<2, 128>(tmem, da, db, idesc, false);                       // chunk 0: K rows 0..63
-      ptx::umma_ss_k64<2, 128>(tmem + 128, da, db + (8192 >> 4), idesc, false);   // chunk 1: K rows 64..127
+      ptx::umma_ss_k64<2, 128>(tmem, da, db, idesc, false);                                            // chunk 0: K rows 0..63
+      ptx::umma_ss_k64<2, 128>(tmem + (16u << 16), da + (8192 >> 4), db + (8192 >> 4), idesc, false);  // chunk 1: K rows 64..127
       ptx::umma_commit(&bar_mma);
       // the w rows are staged where the A tile sits: its store has to have read it before anybody passes
       // the barrier below
@@ -448,11 +458,14 @@ __global__ void __launch_bounds__(128) kkt_solve_kernel(const __grid_constant__ 
     const bool ok2 = __syncthreads_and(ptx::mbar_wait(&bar_mma, mma_uses & 1, p.status, kStatusBarrierTimeout)) != 0;
     ptx::tc_fence_after_sync();
     if (ok2) {
-      // Row `tid` of w: 128 values.  A full pair goes through a swizzled staging tile and two TMA stores
-      // (whole 128-byte lines per token row); a ragged tail is written row by row, only by lanes with a valid
-      // token.  tcgen05.ld is warp-collective: every lane runs the loop.
-      T* wrow = static_cast<T*>(p.w) + (tok * p.num_v_heads + hv) * kHeadDim;
-      const uint32_t taddr = tmem + (static_cast<uint32_t>(warp * 32) << 16) + ci * 128;
+      // One row of w per thread: 128 values; lane l of warp w holds row 16 w + (l & 15) of chunk l >> 4.  A full
+      // pair goes through a swizzled staging tile and two TMA stores (whole 128-byte lines per token row); a ragged
+      // tail is written row by row, only by lanes with a valid token.  tcgen05.ld is warp-collective: every lane
+      // runs the loop.
+      const int tp = (lane >> 4) * 64 + warp * 16 + (lane & 15);  // token within the pair
+      const bool valid_w = static_cast<int64_t>(tok0) + tp < seq_end;
+      T* wrow = static_cast<T*>(p.w) + ((static_cast<int64_t>(tok0) + tp) * p.num_v_heads + hv) * kHeadDim;
+      const uint32_t taddr = tmem + (static_cast<uint32_t>(warp * 32) << 16);
 #pragma unroll 1
       for (int kb = 0; kb < 128; kb += 32) {
         uint32_t r[32];
@@ -465,8 +478,8 @@ __global__ void __launch_bounds__(128) kkt_solve_kernel(const __grid_constant__ 
                                        pack2<T>(__uint_as_float(r[e + 2]), __uint_as_float(r[e + 3])),
                                        pack2<T>(__uint_as_float(r[e + 4]), __uint_as_float(r[e + 5])),
                                        pack2<T>(__uint_as_float(r[e + 6]), __uint_as_float(r[e + 7])));
-          if (full_pair) *reinterpret_cast<uint4*>(half + ptx::sw128_offset(tid, ((kb & 63) + e) >> 3)) = val;
-          else if (valid) *reinterpret_cast<uint4*>(wrow + kb + e) = val;
+          if (full_pair) *reinterpret_cast<uint4*>(half + ptx::sw128_offset(tp, ((kb & 63) + e) >> 3)) = val;
+          else if (valid_w) *reinterpret_cast<uint4*>(wrow + kb + e) = val;
         }
       }
     }
@@ -484,7 +497,7 @@ __global__ void __launch_bounds__(128) kkt_solve_kernel(const __grid_constant__ 
 
   ptx::tc_fence_before_sync();
   __syncthreads();
-  if (warp == 0) ptx::tmem_dealloc(tmem, 256);
+  if (warp == 0) ptx::tmem_dealloc(tmem, 128);
 }
 
 // pair_offsets[n] = sum_{m<n} ceil(len_m / 128), chunk_offsets[n] = sum_{m<n} ceil(len_m / 64).

@@ -51,7 +51,7 @@ KERNEL_RULES = {
         params=[_TMAP + " q", _TMAP + " k", _TMAP + " v", _TMAP + " A", _TMAP + " w", _TMAP + " o", "FwdParams (by value)"],
         tensor_maps="3-D (width, heads, tokens), 16-bit elements, box 64 x 1 x 64 with 128B swizzle (o: 128 x 1 x 64, none)"),
     "kkt_solve_kernel": dict(
-        block=128, dynamic_smem=113664, cluster=1, grid="(pairs of 64-token chunks, Hk)",
+        block=128, dynamic_smem=68608, cluster=1, grid="(pairs of 64-token chunks, Hk)",
         params=[_TMAP + " k", _TMAP + " q", _TMAP + " A", _TMAP + " w", "KktParams (by value)"],
         tensor_maps="3-D (width, heads, tokens), box 64 x 1 x 128 with 128B swizzle"),
     "bwd_scan_kernel": dict(
