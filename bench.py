@@ -31,7 +31,7 @@ ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
 K = V = 128
-MEASURED_SCAN_DRAM_BYTES_PER_TOKEN_HK16_HV32 = 42.9e3
+MEASURED_SCAN_DRAM_BYTES_PER_TOKEN_HK16_HV32 = 39648.0
 CHUNK = 64
 
 
@@ -164,7 +164,7 @@ def measure(fn, steps, warmup, world, device, flush_l2=False, min_seconds=None):
 # ------------------------------------------------------------------------------------ workloads
 def SCAN_DRAM_BYTES_PER_TOKEN_HEADS(Hk, Hv):
     """DRAM bytes per token moved by one launch of the chunk scan: dram__bytes_read + dram__bytes_write of an
-    ncu capture of this kernel on a smaller case (8192 tokens, 16 k-heads / 32 v-heads: 351.2 MB = 42.9 KB
+    ncu capture of this kernel on a smaller case (8192 tokens, 16 k-heads / 32 v-heads: 324.8 MB = 39.6 KB
     per token), scaled by the head counts of this rank."""
     # the scan reads q, k per k-head (512 B) and v, w, A, gates per v-head and writes o (904 B)
     return MEASURED_SCAN_DRAM_BYTES_PER_TOKEN_HK16_HV32 * (Hk * 512 + Hv * 904) / (16 * 512 + 32 * 904)
@@ -453,6 +453,8 @@ def run_train(args, rank, world, device):
         return fq.chunk_gated_delta_rule_bwd(q, k, v, g_cs, beta, A, do, dht=dht, initial_state=h0, h=h, v_new=vn,
                                              w=w)
 
+    use_cp = fq.cp.get_plan([T] * B, H, device).use_cp
+    launches_per_step = fq.chunk.launches_per_forward(False, use_cp) + fq.chunk.launches_per_backward(False, use_cp)
     with ClockSampler(device.index or 0) as cs:
         ms, blocks = measure(step, args.steps, args.warmup, world, device)
     fq.check_device_status()
@@ -467,7 +469,7 @@ def run_train(args, rank, world, device):
         "blocks": blocks,
         "config": {"workload": f"train_fwd_bwd_B{B_all}_T{T}_Hk{H_all}_Hv{H_all}_K128_V128_chunk64", "sharding": sharding,
                    "l2": "inputs (>= 1 GB per step) exceed the 126 MB L2; no flush needed", "tokens": tokens},
-        "clocks": cs.summary(), "gpu_launches": 4 * args.steps * blocks,
+        "clocks": cs.summary(), "gpu_launches": launches_per_step * args.steps * blocks,
         "roofline": {"kernel": "fwd+bwd (kkt_solve, chunk scan, bwd_scan, bwd_chunk)", "bound": "tensor", "achieved": flops / world / (per_step * 1e-3) / 1e12,
                      "peak": pk["tf_sus"], "unit": "TFLOP/s",
                      "frac": flops / world / (per_step * 1e-3) / 1e12 / pk["tf_sus"], "peak_source": pk["src"],
@@ -532,9 +534,15 @@ def main():
     ap.add_argument("--eager", action="store_true", help="time plain calls instead of CUDA-graph replays")
     ap.add_argument("--compare-fla", action="store_true",
                     help="also time FLA's Triton forward on the same inputs (adds a same_box entry)")
+    ap.add_argument("--min-seconds", type=float, default=None,
+                    help="total timed time to reach by repeating the K-step block (default 1.0; 0 = one block, "
+                         "for profiler captures)")
     args = ap.parse_args()
     rank, world, local = dist_env()
     args.warmup = max(args.warmup, 3)
+    if args.min_seconds is not None:
+        global MIN_TIMED_SECONDS
+        MIN_TIMED_SECONDS = args.min_seconds
 
     if args.impl == "reference":
         if rank != 0:

@@ -149,6 +149,13 @@ def launches_per_forward(varlen: bool, use_cp: bool = False) -> int:
     return 3 if varlen else 2
 
 
+def launches_per_backward(varlen: bool, use_cp: bool = False) -> int:
+    """Kernels one backward call launches with h, v_new and w saved by the forward: [chunk tables] + reverse scan +
+    per-chunk kernel; context parallelism adds the reverse plan, the state-only / transition scan (one launch), the
+    reverse chain and the segments' chunk tables."""
+    return (3 if varlen else 2) + (4 if use_cp else 0)
+
+
 def make_scan_only(q, k, v, beta, g_cumsum, A, o, final_state, initial_state=None, cu_seqlens=None,
                    scale=None, auto_cp=True):
     """Return a callable that launches only the chunk scan (the dominant kernel) exactly as a forward

@@ -66,6 +66,11 @@ __global__ void __launch_bounds__(128) cp_chain_kernel(float* __restrict__ h0, c
   const int s0 = raw_first_seg[r], s1 = raw_first_seg[r + 1];
   const int k = threadIdx.x;
   __shared__ float sh[kHeadDim][33];
+  // the usual case (every segment decays below the threshold) has nothing to chain: find that out with one
+  // parallel look at the flags instead of a serial walk
+  int mine = 0;
+  for (int seg = s0 + threadIdx.x; seg < s1; seg += 128) mine |= m_limit[seg * num_heads + h];
+  if (__syncthreads_or(mine) == 0) return;
   for (int i = 0; i + 1 < s1 - s0; ++i) {
     // forward: segment s0 + i feeds s0 + i + 1; backward: segment s1 - 1 - i feeds s1 - 2 - i
     const int seg = reverse ? s1 - 1 - i : s0 + i;
@@ -75,7 +80,7 @@ __global__ void __launch_bounds__(128) cp_chain_kernel(float* __restrict__ h0, c
     float* dst = h0 + (static_cast<int64_t>(to) * num_heads + h) * kHeadDim * kHeadDim + vt * 32;
     const float* m = M + (static_cast<int64_t>(seg) * num_heads + h) * kHeadDim * kHeadDim;
     __syncthreads();
-    for (int i = threadIdx.x; i < kHeadDim * 32; i += 128) sh[i >> 5][i & 31] = src[(i >> 5) * kHeadDim + (i & 31)];
+    for (int e = threadIdx.x; e < kHeadDim * 32; e += 128) sh[e >> 5][e & 31] = src[(e >> 5) * kHeadDim + (e & 31)];
     __syncthreads();
     float acc[32];
 #pragma unroll
