@@ -381,7 +381,7 @@ def run_recurrent(args, rank, world, device, verify: bool):
     with ClockSampler(device.index or 0) as cs:
         ms, blocks = measure(step, args.steps, args.warmup, world, device)
     per_step = ms / args.steps
-    same_box = None
+    same_box = []
     if args.compare_fla and not verify:
         # same-box bar: FLA's Triton recurrent kernel on the same inputs (what the reference compares its decode
         # kernels with); it returns the new states instead of updating the pool in place
@@ -392,18 +392,49 @@ def run_recurrent(args, rank, world, device, verify: bool):
                                           output_final_state=True, use_qk_l2norm_in_kernel=False, cu_seqlens=cu_fla,
                                           transpose_state_layout=True)
             ms_fla = measure(fla_step, args.steps, args.warmup, world, device, min_seconds=0.3)[0] / args.steps
-            same_box = {"impl": "fla %s fused_recurrent_gated_delta_rule (Triton)" % __import__("fla").__version__,
-                        "ms_per_step": ms_fla}
+            same_box.append({"impl": "fla %s fused_recurrent_gated_delta_rule (Triton)" % __import__("fla").__version__,
+                             "ms_per_step": ms_fla})
         except Exception as exc:
-            same_box = {"impl": "fla fused_recurrent_gated_delta_rule", "unavailable": f"{type(exc).__name__}: {str(exc)[:160]}"}
+            same_box.append({"impl": "fla fused_recurrent_gated_delta_rule",
+                             "unavailable": f"{type(exc).__name__}: {str(exc)[:160]}"})
+    if args.compare_fla:
+        # same-box bar: the reference's own recurrent op (TileLang kernels compiled on this box), loaded by path
+        # from the copy that oracle/build_ref.py places beside the oracle; same inputs, same pool rotation
+        ref_file = ROOT / "oracle" / "_ref" / "recurrent_fused.py"
+        if ref_file.exists():
+            try:
+                import importlib.util
+                os.environ.setdefault("TILELANG_CACHE_DIR", "/tmp/flashqla_b200_tilelang_cache")
+                spec = importlib.util.spec_from_file_location("reference_recurrent_fused", ref_file)
+                rec = importlib.util.module_from_spec(spec)
+                sys.modules["reference_recurrent_fused"] = rec
+                spec.loader.exec_module(rec)
+                zeros_h = torch.zeros(Hv, dtype=torch.float32, device=device)  # A_log / dt_bias: unused with log decays
+                rcalls = [0]
+
+                # (its verify kernel applies the layer's gate activation whatever a_is_log_decay / b_is_beta say:
+                # the arithmetic of that step differs a little, the memory traffic does not)
+                def ref_step():
+                    rcalls[0] += 1
+                    return rec.fused_sigmoid_gating_delta_rule_update(
+                        zeros_h, g, zeros_h, q, k, v, beta, pools[rcalls[0] % copies], use_qk_l2norm_in_kernel=False,
+                        a_is_log_decay=True, b_is_beta=True, assume_regular=True, disable_state_update=verify,
+                        intermediate_states_buffer=inter)
+                ms_ref = measure(ref_step, args.steps, args.warmup, world, device, min_seconds=0.3)[0] / args.steps
+                same_box.append({"impl": "reference flash_qla recurrent_fused.py (TileLang %s, compiled here)"
+                                         % __import__("tilelang").__version__, "ms_per_step": ms_ref})
+            except Exception as exc:
+                same_box.append({"impl": "reference flash_qla recurrent_fused.py (TileLang)",
+                                 "unavailable": f"{type(exc).__name__}: {str(exc)[:160]}"})
     cache_b = 0 if not verify else (2 if args.bf16_scratch else 4)
     nbytes = orc.state_bytes_decode(N, Hv, T=T, Hk=Hk, cache_bytes=cache_b, write_back=not verify)
     gbs = nbytes * world / (per_step * 1e-3) / 1e9
     pk = peaks()
-    if same_box is not None and "ms_per_step" in same_box:
-        same_box["gb_per_s"] = nbytes * world / (same_box["ms_per_step"] * 1e-3) / 1e9
+    for bar in same_box:
+        if "ms_per_step" in bar:
+            bar["gb_per_s"] = nbytes * world / (bar["ms_per_step"] * 1e-3) / 1e9
     return {
-        **({"same_box": same_box} if same_box is not None else {}),
+        **({"same_box": same_box} if same_box else {}),
         "metric": "gdn_%s_hbm_gb_per_s" % ("verify" if verify else "decode"), "value": gbs, "unit": "GB/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_step,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
@@ -593,7 +624,7 @@ def main():
         for wl, extra in workloads:
             a2 = copy.copy(args)
             a2.workload, a2.steps, a2.tokens, a2.bf16_scratch = wl, min(args.steps, 20), 32768, False
-            a2.compare_fla = wl == "decode" and world == 1
+            a2.compare_fla = wl in ("decode", "verify") and world == 1  # same-box bars: FLA (decode), the reference's own op
             for name, val in extra.items():
                 setattr(a2, name, val)
             try:

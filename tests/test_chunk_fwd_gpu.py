@@ -116,17 +116,22 @@ def test_fp16_inputs(fq):
     _check("final_state", fs, ref["final_state"])
 
 
-def test_repeatable_bitwise(fq):
-    """Race check in the spirit of the reference's 1000x loops (tests/test_gdr.py:211)."""
-    inp = _cuda(orc.make_prefill_inputs(2, 700, 2, 4, seed=13, with_h0=True))
-    outs = []
-    for _ in range(30):
+@pytest.mark.parametrize("B,T,Hk,Hv", [(2, 700, 2, 4), (1, 2048 + 70, 1, 2)])
+def test_repeatable_bitwise(fq, B, T, Hk, Hv):
+    """Race check with the reference's loop count (1000 runs, tests/test_gdr.py:211): every run bit-identical to
+    the first.  The second shape is cut into context-parallel segments (plan, dual state-only launch, chain)."""
+    inp = _cuda(orc.make_prefill_inputs(B, T, Hk, Hv, seed=13, with_h0=True))
+    first = None
+    bad = torch.zeros((), dtype=torch.int32, device="cuda")
+    for _ in range(1000):
         _, _, o, _, fs = fq.chunk_gated_delta_rule_fwd(inp["q"], inp["k"], inp["v"], inp["g"], inp["beta"],
                                                        initial_state=inp["h0"])
-        outs.append((o, fs))
+        if first is None:
+            first = (o, fs)
+        else:  # compared on the device, one host read at the end
+            bad += (o != first[0]).any().int() + (fs != first[1]).any().int()
     fq.check_device_status()
-    for o, fs in outs[1:]:
-        assert torch.equal(o, outs[0][0]) and torch.equal(fs, outs[0][1])
+    assert int(bad) == 0
 
 
 def test_api_errors(fq):

@@ -318,3 +318,72 @@ def test_decode_step_in_a_cuda_graph(fq):
     graph.replay()
     torch.cuda.synchronize()
     assert torch.equal(o, o_ref) and torch.equal(state, ref_state)
+
+
+def _reference_recurrent():
+    """The reference's own recurrent op (TileLang kernels, compiled on this box), loaded by path from the copy
+    that oracle/build_ref.py places under oracle/_ref/ (the way the reference's own test loads it,
+    tests/test_recurrent_verify_scratch_dtype.py:93-107).  None when the file or TileLang is missing."""
+    import importlib.util
+    import os
+    import sys
+    from pathlib import Path
+    src = Path(__file__).resolve().parent.parent / "oracle" / "_ref" / "recurrent_fused.py"
+    if not src.exists():
+        return None
+    if "reference_recurrent_fused" in sys.modules:
+        return sys.modules["reference_recurrent_fused"]
+    try:
+        import tilelang  # noqa: F401
+    except Exception:
+        return None
+    os.environ.setdefault("TILELANG_CACHE_DIR", "/tmp/flashqla_b200_tilelang_cache")
+    spec = importlib.util.spec_from_file_location("reference_recurrent_fused", src)
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules["reference_recurrent_fused"] = mod
+    spec.loader.exec_module(mod)
+    return mod
+
+
+@pytest.mark.parametrize("mode", ["decode_plain", "decode_gated_l2norm", "verify_f32", "verify_bf16"])
+def test_against_the_reference_kernel_on_this_gpu(fq, mode):
+    """Same inputs through the reference's TileLang kernel and through this library: outputs, updated pool and
+    cached per-token states, with the gates of the reference's own comparison
+    (benchmark/bench_recurrent_fused_matrix.py:515-517).  Skips where the reference file is absent or its kernel
+    does not compile for this GPU."""
+    rec = _reference_recurrent()
+    if rec is None:
+        pytest.skip("reference recurrent op not available (oracle/_ref/recurrent_fused.py or TileLang missing)")
+    verify = mode.startswith("verify")
+    N, T, Hk, Hv = 48, (4 if verify else 1), 4, 8
+    c = _cuda(_inputs(N, T, Hk, Hv, seed=71))
+    # the reference's verify kernel applies the layer's gate activation whatever a_is_log_decay / b_is_beta say, so
+    # the verify cases use raw gate inputs (as the reference's own verify test does)
+    gated = mode != "decode_plain"
+    kw = dict(use_qk_l2norm_in_kernel=gated, a_is_log_decay=not gated, b_is_beta=not gated, assume_regular=True)
+    a_in, b_in = (c["a"], c["b"]) if gated else (c["g"], c["beta"])
+    A_log = c["A_log"].float()
+    dt_bias = c["dt_bias"]
+    inter_dt = torch.bfloat16 if mode == "verify_bf16" else torch.float32
+    outs = []
+    for impl in ("reference", "ours"):
+        pool = c["state"].clone()
+        inter = torch.zeros(N, T, Hv, 128, 128, dtype=inter_dt, device="cuda") if verify else None
+        fn = rec.fused_sigmoid_gating_delta_rule_update if impl == "reference" else fq.fused_sigmoid_gating_delta_rule_update
+        try:
+            o = fn(A_log, a_in, dt_bias, c["q"], c["k"], c["v"], b_in, pool, disable_state_update=verify,
+                   intermediate_states_buffer=inter, **kw)
+            torch.cuda.synchronize()
+        except Exception as exc:  # the reference's JIT may not support this GPU or toolchain
+            if impl == "reference":
+                pytest.skip(f"reference kernel did not run here: {type(exc).__name__}: {str(exc)[:120]}")
+            raise
+        outs.append((o.float(), pool, inter))
+    fq.check_device_status()
+    (o_r, pool_r, inter_r), (o_m, pool_m, inter_m) = outs
+    assert float((o_r - o_m).abs().max()) <= O_TOL
+    assert float((pool_r - pool_m).abs().max()) <= STATE_TOL
+    if verify:
+        assert torch.equal(pool_m, c["state"]) and torch.equal(pool_r, c["state"])
+        tol = STATE_TOL if inter_dt == torch.float32 else 8e-3  # two bf16 roundings of |S| ~ 1
+        assert float((inter_r.float() - inter_m.float()).abs().max()) <= tol
