@@ -60,7 +60,8 @@ def test_golden_backward(fq, golden_dir, name):
     _report(got, {n: fx[n] for n in GRADS}, rms_tol={"dg": 1e-2} if name == "weak_gate_bwd" else None)
 
 
-@pytest.mark.parametrize("B,T,Hk,Hv", [(1, 64, 1, 1), (2, 200, 2, 4), (1, 1024, 2, 2), (1, 448, 1, 3)])
+# (the last shape is a batch of two ragged sequences that the context-parallel plan cuts into segments)
+@pytest.mark.parametrize("B,T,Hk,Hv", [(1, 64, 1, 1), (2, 200, 2, 4), (1, 1024, 2, 2), (1, 448, 1, 3), (2, 1100, 1, 2)])
 @pytest.mark.parametrize("saved", [True, False])
 def test_backward_matches_oracle(fq, B, T, Hk, Hv, saved):
     inp = orc.make_prefill_inputs(B, T, Hk, Hv, seed=300 + T, with_h0=True, with_grads=True)
