@@ -329,3 +329,26 @@ def test_bounded_wait_runs_out_and_reports(fq):
         fq.check_device_status()
     fq.check_device_status()  # cleared
     _run_case(fq, 1, 130, 1, 2, seed=5, with_h0=True)
+
+
+def test_reference_import_paths_run_on_the_gpu(fq):
+    """A caller written against the reference (`from flash_qla import ...`, `from flash_qla.utils import l2norm`,
+    tests/test_gdr.py:18-21) reaches these kernels: forward + autograd backward through the reference's names."""
+    from flash_qla import chunk_gated_delta_rule, chunk_gated_delta_rule_fwd
+    from flash_qla.utils import l2norm
+    gen = torch.Generator().manual_seed(51)
+    B, T, H = 1, 300, 2
+    q = l2norm(torch.randn(B, T, H, 128, generator=gen)).bfloat16().cuda().requires_grad_(True)
+    k = l2norm(torch.randn(B, T, H, 128, generator=gen)).bfloat16().cuda().requires_grad_(True)
+    v = torch.randn(B, T, H, 128, generator=gen).bfloat16().cuda().requires_grad_(True)
+    g = torch.nn.functional.logsigmoid(torch.randn(B, T, H, generator=gen)).cuda().requires_grad_(True)
+    beta = torch.sigmoid(torch.randn(B, T, H, generator=gen)).cuda().requires_grad_(True)
+    o, fs = chunk_gated_delta_rule(q, k, v, g, beta, output_final_state=True)
+    o.float().square().sum().backward()
+    fq.check_device_status()
+    ref = orc.chunk_gdr_fwd(q.detach().cpu(), k.detach().cpu(), v.detach().cpu(), g.detach().cpu(), beta.detach().cpu())
+    _check("o", o.detach(), ref["o"])
+    _check("final_state", fs, ref["final_state"])
+    assert all(t.grad is not None and torch.isfinite(t.grad.float()).all() for t in (q, k, v, g, beta))
+    raw = chunk_gated_delta_rule_fwd(q.detach(), k.detach(), v.detach(), g.detach(), beta.detach())
+    assert orc.rel_rms(raw[2].float().cpu(), o.detach().float().cpu()) <= 1e-3
