@@ -232,6 +232,7 @@ extern "C" QLA_API int qla_chunk_bwd(const QlaChunkBwdArgs* args, void* stream_)
   // chunks, so the chunk numbering of the workspace is that of the sequences)
   BwdParams sp = p;
   BwdScanMode mode{};
+  mode.chunks_upper = w.chunks_upper;
   if (a.num_segments > 0) {
     QLA_CHECK_ARG(a.seg_cu && a.seg_dht && a.seg_dh0_map, "segments need seg_cu, seg_dht and seg_dh0_map");
     int32_t* seg_tables = reinterpret_cast<int32_t*>(ws + w.tables + w.dh + w.du);

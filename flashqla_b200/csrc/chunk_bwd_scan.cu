@@ -20,9 +20,12 @@
 //   MMA3  dS^T[128,128] += du^T_bf16 w                     (TS, B = w tile read MN-major)  chain
 // Thread v of a compute warpgroup owns TMEM lane v (column v of dS): it forms du = Du0 + rho .* D2, writes
 // the 16-bit operand of the next product back with tcgen05.st and its 128 bytes of du^T to the workspace.
-// Warp roles (384 threads): warps 0-7 compute (both warpgroups take half of the token columns of every
+// Warp roles (416 threads): warps 0-7 compute (both warpgroups take half of the token columns of every
 // chain phase and half of the state columns of the state conversion), warp 8 TMA producer + gate vectors,
-// warp 9 MMA issuer, warps 10-11 operand tiles (Pg, s gamma .* Q in place).
+// warp 9 MMA issuer, warps 10-11 operand tiles (Pg, s gamma .* Q in place), warp 12 sends du^T and dh^T of every
+// chunk to the workspace with TMA stores from swizzled staging tiles (a thread owns a whole row of either: stored
+// straight from registers, every 16-byte piece of a warp's store instruction would fall into a different
+// 128-byte line).
 // Every wait is a bounded mbarrier wait that raises the status word instead of hanging.
 #include "chunk_params.cuh"
 
@@ -43,7 +46,9 @@ constexpr uint32_t kStageDO = 32768;     // 16 KiB: dO tile as two [64][64] halv
 constexpr uint32_t kStageW = 49152;      // 16 KiB: w tile as two [64][64] halves, SW128
 constexpr uint32_t kStageBytes = 65536;  // 64 KiB
 constexpr uint32_t kOffPg = 2 * kStageBytes;  // 2 x 8 KiB Pg tiles [c][d], SW128 (chunk parity)
-constexpr uint32_t kSmemBytes = kOffPg + 2 * 8192 + 1024;
+constexpr uint32_t kOffDuT = kOffPg + 2 * 8192;   // 2 x 16 KiB du^T staging tiles [128 v][64 tokens], SW128 (chunk parity)
+constexpr uint32_t kOffDhT = kOffDuT + 2 * 16384;  // 32 KiB dh^T staging tile [128 v][128 k] as two [128][64] halves, SW128
+constexpr uint32_t kSmemBytes = kOffDhT + 32768 + 1024;
 
 struct alignas(16) Gates {
   float g2[64];    // g log2(e)
@@ -58,9 +63,11 @@ constexpr int kGateRing = 4;
 enum Bar {
   kFull0 = 0, kFull1, kEmpty0, kEmpty1, kPDone0, kPDone1,
   kPgReady, kQsReady, kD2Done, kDu0Done, kDuReady, kSDone, kSbfReady, kSScaled,
+  kTileReady,  // the compute warps have written this chunk's staging tiles (8 arrivals)
+  kTileFree,   // the store warp's TMA stores of this chunk have read them (1 arrival)
   kNumBars
 };
-constexpr int kThreads = 384;
+constexpr int kThreads = 416;
 
 __device__ __forceinline__ void warp_arrive(uint64_t* bar, int lane) {
   __syncwarp();
@@ -84,6 +91,7 @@ template <typename T>
 __global__ void __launch_bounds__(kThreads, 1)
 bwd_scan_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_do, const __grid_constant__ CUtensorMap tm_w,
+                const __grid_constant__ CUtensorMap tm_dh, const __grid_constant__ CUtensorMap tm_du,
                 const BwdParams p, const BwdScanMode mode) {
   constexpr uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? ptx::kFmtBF16 : ptx::kFmtF16;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -129,7 +137,7 @@ bwd_scan_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       if (b == kFull0 || b == kFull1) count = 33;
       else if (b == kEmpty0 || b == kEmpty1) count = 3;
       else if (b == kPgReady || b == kQsReady) count = 2;
-      else if (b == kDuReady || b == kSbfReady || b == kSScaled) count = 8;
+      else if (b == kDuReady || b == kSbfReady || b == kSScaled || b == kTileReady) count = 8;
       ptx::mbar_init(&bars[b], count);
     }
     ptx::fence_mbar_init();
@@ -280,6 +288,30 @@ bwd_scan_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                                      id_u, false, bar_addr(kDu0Done));
       }
     }
+  } else if (warp == 12) {
+    // =========================================================== store warp: du^T and dh^T tiles -> workspace
+    if (!state_only) {
+      bool ok = true;
+#pragma unroll 1
+      for (int i = 0; ok && i < nproc; ++i) {
+        if (!(ok = wait(kTileReady, i & 1))) break;
+        if (lane == 0) {
+          const int chunk = chunk_of(i);
+          const int row = static_cast<int>(((chunk_base + chunk) * p.num_v_heads + hv) * kHeadDim);
+          ptx::tma_store_3d(&tm_du, smem + kOffDuT + (i & 1) * 16384, 0, 0, row);
+          if (i + 1 < nproc) {  // dh of the chunk before: the state this chunk's update produced
+            const int row2 = row - p.num_v_heads * kHeadDim;
+            ptx::tma_store_3d(&tm_dh, smem + kOffDhT, 0, 0, row2);
+            ptx::tma_store_3d(&tm_dh, smem + kOffDhT + 16384, 64, 0, row2);
+          }
+          ptx::tma_store_commit();
+          ptx::tma_store_wait_read();
+          ptx::mbar_arrive(&bars[kTileFree]);
+        }
+        __syncwarp();
+      }
+      if (lane == 0) ptx::tma_store_wait_all();
+    }
   } else if (warp >= 10) {
     // =========================================================== aux warps 10, 11: operand tiles
     const int r = tid - 320;  // 0..63: row of the A / Pg / Q tiles
@@ -365,7 +397,6 @@ bwd_scan_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                       ? out_states + (static_cast<int64_t>(out_row) * p.num_v_heads + hv) * kHeadDim * kHeadDim
                       : nullptr;
     T* dh_ws = static_cast<T*>(p.dh);  // [chunk][Hv][128 v][128 k]
-    T* du_ws = static_cast<T*>(p.du);  // [chunk][Hv][128 v][64 tokens]
     auto dh_row = [&](int chunk) {
       return dh_ws + (((chunk_base + chunk) * p.num_v_heads + hv) * kHeadDim + v) * kHeadDim;
     };
@@ -443,10 +474,13 @@ bwd_scan_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         ptx::tc_fence_before_sync();
         warp_arrive(&bars[kDuReady], lane);
         if (!state_only) {
-          T* dup = du_ws + (((chunk_base + chunk) * p.num_v_heads + hv) * kHeadDim + v) * kChunk + 32 * wg;
+          // this thread's 32 tokens of du^T (64 bytes of row v) into the staging tile of this chunk's parity;
+          // its last tenant (chunk i - 2) was stored before the compute warps passed TileFree of chunk i - 2
+          uint8_t* dt = smem + kOffDuT + (i & 1) * 16384 + v * 128;
 #pragma unroll
-          for (int j = 0; j < 16; j += 4)
-            *reinterpret_cast<uint4*>(dup + 2 * j) = make_uint4(pk[j], pk[j + 1], pk[j + 2], pk[j + 3]);
+          for (int j = 0; j < 4; ++j)
+            *reinterpret_cast<uint4*>(dt + (((4 * wg + j) ^ (v & 7)) << 4)) =
+                make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
         }
       }
       // ---------------- state conversion after MMA3 (this warpgroup's 64 columns)
@@ -463,9 +497,16 @@ bwd_scan_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             for (int j = 0; j < 16; ++j) dh0p[(col_half + kb + j) * st_k + v * st_v] = __uint_as_float(sf[j]);
           }
         }
+        if (!state_only) {
+          ptx::fence_proxy_async_smem();
+          warp_arrive(&bars[kTileReady], lane);  // only du^T this time
+        }
       } else {
-        T* hp = dh_row(chunk - 1);
+        // the dh^T staging tile is single: the stores of the previous chunk (issued a chunk period ago) must
+        // have read it
+        if (!state_only && i > 0 && !(alive = wait(kTileFree, (i - 1) & 1))) break;
         // (a) critical: 16-bit copy of the new state -> MMA2 of the next chunk may start; the same values are dh
+        uint8_t* ht = smem + kOffDhT + wg * 16384 + v * 128;  // this warpgroup's 64 columns = half wg of the tile
 #pragma unroll 1
         for (int h = 0; h < 2; ++h) {
           uint32_t sf[32], sb[16];
@@ -476,13 +517,18 @@ bwd_scan_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           ptx::tmem_st16(tm + kColSbf + col_half / 2 + 16 * h, sb);
           if (!state_only) {
 #pragma unroll
-            for (int j = 0; j < 16; j += 4)
-              *reinterpret_cast<uint4*>(hp + col_half + 32 * h + 2 * j) = make_uint4(sb[j], sb[j + 1], sb[j + 2], sb[j + 3]);
+            for (int j = 0; j < 4; ++j)
+              *reinterpret_cast<uint4*>(ht + (((4 * h + j) ^ (v & 7)) << 4)) =
+                  make_uint4(sb[4 * j], sb[4 * j + 1], sb[4 * j + 2], sb[4 * j + 3]);
           }
         }
         ptx::tmem_wait_st();
         ptx::tc_fence_before_sync();
         warp_arrive(&bars[kSbfReady], lane);
+        if (!state_only) {
+          ptx::fence_proxy_async_smem();
+          warp_arrive(&bars[kTileReady], lane);
+        }
         // (b) off the critical path: decay of the fp32 state for the next chunk (needed by MMAq / MMA3 only)
         if (!(alive = wait(kFull0 + ((i + 1) & 1), ((i + 1) >> 1) & 1))) break;
         const float egl_next = gates_of(i + 1)->egl;
@@ -517,13 +563,22 @@ int launch_bwd_scan(const BwdParams& p, const BwdScanMode& mode, int64_t total_t
   if ((rc = make_tmap_3d(&tm_q, p.q, total_tokens, p.num_k_heads, kHeadDim, 64, 64, true, is_bf16)) != QLA_OK) return rc;
   if ((rc = make_tmap_3d(&tm_do, p.d_o, total_tokens, p.num_v_heads, kHeadDim, 64, 64, true, is_bf16)) != QLA_OK) return rc;
   if ((rc = make_tmap_3d(&tm_w, p.w, total_tokens, p.num_v_heads, kHeadDim, 64, 64, true, is_bf16)) != QLA_OK) return rc;
+  // store maps of the workspace tensors dh^T [chunks * Hv * 128 rows][128] and du^T [... rows][64] (boxes of 128 rows
+  // x 64 columns, 128B swizzle: the form bwd_chunk_kernel loads them in); a state-only pass stores nothing and
+  // gets placeholder maps
+  CUtensorMap tm_dh = tm_k, tm_du = tm_k;
+  if (!mode.state_only) {
+    const uint64_t rows = static_cast<uint64_t>(mode.chunks_upper) * p.num_v_heads * kHeadDim;
+    if ((rc = make_tmap_3d(&tm_dh, p.dh, rows, 1, kHeadDim, 128, 64, true, is_bf16)) != QLA_OK) return rc;
+    if ((rc = make_tmap_3d(&tm_du, p.du, rows, 1, kChunk, 128, 64, true, is_bf16)) != QLA_OK) return rc;
+  }
   const unsigned grid = static_cast<unsigned>(p.num_seqs) * p.num_v_heads * (mode.dual ? 2 : 1);
   if (is_bf16) {
     if ((rc = ensure_dynamic_smem<bwd_scan_kernel<__nv_bfloat16>>(kSmemBytes)) != QLA_OK) return rc;
-    bwd_scan_kernel<__nv_bfloat16><<<grid, kThreads, kSmemBytes, stream>>>(tm_q, tm_k, tm_do, tm_w, p, mode);
+    bwd_scan_kernel<__nv_bfloat16><<<grid, kThreads, kSmemBytes, stream>>>(tm_q, tm_k, tm_do, tm_w, tm_dh, tm_du, p, mode);
   } else {
     if ((rc = ensure_dynamic_smem<bwd_scan_kernel<__half>>(kSmemBytes)) != QLA_OK) return rc;
-    bwd_scan_kernel<__half><<<grid, kThreads, kSmemBytes, stream>>>(tm_q, tm_k, tm_do, tm_w, p, mode);
+    bwd_scan_kernel<__half><<<grid, kThreads, kSmemBytes, stream>>>(tm_q, tm_k, tm_do, tm_w, tm_dh, tm_du, p, mode);
   }
   QLA_CHECK_CUDA(cudaGetLastError());
   return QLA_OK;

@@ -55,9 +55,11 @@ KERNEL_RULES = {
         params=[_TMAP + " k", _TMAP + " q", _TMAP + " A", _TMAP + " w", "KktParams (by value)"],
         tensor_maps="3-D (width, heads, tokens), box 64 x 1 x 128 with 128B swizzle"),
     "bwd_scan_kernel": dict(
-        block=384, dynamic_smem=148480, cluster=1, grid="num_seqs * Hv",
-        params=[_TMAP + " q", _TMAP + " k", _TMAP + " dO", _TMAP + " w", "BwdParams (by value)"],
-        tensor_maps="3-D (width, heads, tokens), box 64 x 1 x 64 with 128B swizzle"),
+        block=416, dynamic_smem=214016, cluster=1, grid="num_seqs * Hv (twice that for a dual state-only launch)",
+        params=[_TMAP + " q", _TMAP + " k", _TMAP + " dO", _TMAP + " w", _TMAP + " dh (store)", _TMAP + " du (store)",
+                "BwdParams (by value)", "BwdScanMode (by value)"],
+        tensor_maps="loads: 3-D (width, heads, tokens), box 64 x 1 x 64 with 128B swizzle; stores: workspace rows "
+                    "(chunks * Hv * 128) x 128 (dh) or x 64 (du), box 64 x 1 x 128 with 128B swizzle"),
     "bwd_chunk_kernel": dict(
         block=576, dynamic_smem=205824, cluster=1, grid="min(chunks * Hk, SMs), persistent",
         params=[_TMAP + " " + n for n in ("q", "k", "v", "v_new", "dO", "A", "h", "dh", "du", "dq", "dk", "dv")] +
