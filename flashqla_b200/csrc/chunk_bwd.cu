@@ -353,7 +353,7 @@ bwd_chunk_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         trace(step, 29);
       }
     }
-  } else {
+  } else if (warp < kComputeWarps) {
     // =========================================================== epilogue warps
     const int g = lane >> 2, c4 = lane & 3;
     const int mt = warp & 3, nh = warp >> 2;  // rows 16 mt .., column quarter nh
@@ -509,6 +509,17 @@ bwd_chunk_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         if (!(ok = wait(kC45, ph))) break;
         ptx::tc_fence_after_sync();
         if (warp == 0) trace(step, 2);
+        // decay factors of this thread's eight (row, column) pairs of the 64 x 64 products, exp(min(g_row - g_col, 0)),
+        // and exp(g_col) of its four columns: formed once per head, used by levels 0, 1 and 3
+        float gw[2][4], ecol[2][2];
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float gc = gs[nh * 16 + nt * 8 + 2 * c4 + (e & 1)];
+            gw[nt][e] = __expf(fminf(((e >> 1) ? g1 : g0) - gc, 0.f));
+            if (e < 2) ecol[nt][e] = __expf(gc);
+          }
         {
           float acc[2][4], pq[2][4];
           narrow2(kColP, acc, kColP + kBank1, pq);
@@ -517,7 +528,7 @@ bwd_chunk_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
               const int row = (e >> 1) ? r1 : r0, col = nh * 16 + nt * 8 + 2 * c4 + (e & 1);
-              const float w = p.scale * __expf(fminf(((e >> 1) ? g1 : g0) - gs[col], 0.f));
+              const float w = p.scale * gw[nt][e];
               const float ds = (col <= row && row < valid) ? acc[nt][e] * w : 0.f;
               acc[nt][e] = ds;
               const float ds2 = ds * pq[nt][e];
@@ -637,7 +648,7 @@ bwd_chunk_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
               const int row = (e >> 1) ? r1 : r0, col = nh * 16 + nt * 8 + 2 * c4 + (e & 1);
-              const float val = bs[col] * (__expf(gs[col]) * a1[nt][e] + a2[nt][e]);
+              const float val = bs[col] * (ecol[nt][e & 1] * a1[nt][e] + a2[nt][e]);
               a1[nt][e] = (col < row) ? val : 0.f;
             }
           st_narrow(smem + kOffY, a1);
@@ -673,8 +684,7 @@ bwd_chunk_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
               const int row = (e >> 1) ? r1 : r0, col = nh * 16 + nt * 8 + 2 * c4 + (e & 1);
-              const float w = __expf(fminf(((e >> 1) ? g1 : g0) - gs[col], 0.f));
-              const float dl = (col < row) ? -acc[nt][e] * w : 0.f;
+              const float dl = (col < row) ? -acc[nt][e] * gw[nt][e] : 0.f;
               const float be = (e >> 1) ? be1 : be0;
               acc[nt][e] = dl;
               lb[nt][e] = be * dl;
