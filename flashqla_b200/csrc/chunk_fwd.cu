@@ -511,8 +511,19 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     const bool write_final = fs_out != nullptr || (kState16 && fs_out16 != nullptr);
     const int64_t vn_stride = static_cast<int64_t>(p.num_v_heads) * kHeadDim;
 
-    // ---- initial state: S = exp(gL_0) * S_init (fp32) and its 16-bit copy
+    // ---- initial state: S = exp(gL_0) * S_init (fp32) and its 16-bit copy.  This thread's 64 values are requested
+    // before anything is waited for: their latency then overlaps the arrival of the first stage instead of
+    // following it (with context-parallel segments of a dozen chunks a CTA's start-up is a tenth of its life).
     {
+      float x[64];
+#pragma unroll
+      for (int j = 0; j < 64; ++j) {
+        const int k = col_half + j;
+        x[j] = 0.f;
+        if (init_identity) x[j] = (k == v) ? 1.f : 0.f;
+        else if (h0p != nullptr) x[j] = h0p[k * h0_k + v * h0_v];
+        else if (kState16 && h0p16 != nullptr) x[j] = __bfloat162float(h0p16[k * h0_k + v * h0_v]);
+      }
       float egl0 = 1.f;
       if (nproc > 0) {
         alive = wait(kFull0, 0);
@@ -521,23 +532,14 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       T* hp0 = (kAux && p.h != nullptr && nproc > 0)
                    ? static_cast<T*>(p.h) + ((chunk_base + first_chunk) * p.num_v_heads + hv) * kHeadDim * kHeadDim + v
                    : nullptr;
-#pragma unroll 1
+#pragma unroll
       for (int kb = 0; kb < 64; kb += 16) {
-        float x[16];
         uint32_t sf[16], sb[8];
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const int k = col_half + kb + j;
-          x[j] = 0.f;
-          if (init_identity) x[j] = (k == v) ? 1.f : 0.f;
-          else if (h0p != nullptr) x[j] = h0p[k * h0_k + v * h0_v];
-          else if (kState16 && h0p16 != nullptr) x[j] = __bfloat162float(h0p16[k * h0_k + v * h0_v]);
-        }
-#pragma unroll
         for (int j = 0; j < 16; j += 2) {
-          sf[j] = __float_as_uint(x[j] * egl0);
-          sf[j + 1] = __float_as_uint(x[j + 1] * egl0);
-          sb[j >> 1] = pack2<T>(x[j], x[j + 1]);
+          sf[j] = __float_as_uint(x[kb + j] * egl0);
+          sf[j + 1] = __float_as_uint(x[kb + j + 1] * egl0);
+          sb[j >> 1] = pack2<T>(x[kb + j], x[kb + j + 1]);
         }
         ptx::tmem_st16(tm + kColS + col_half + kb, sf);
         ptx::tmem_st8(tm + kColSbf + (col_half + kb) / 2, sb);
@@ -548,7 +550,7 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         }
         if (nproc == 0 && write_final) {
 #pragma unroll
-          for (int j = 0; j < 16; ++j) store_final(col_half + kb + j, x[j]);
+          for (int j = 0; j < 16; ++j) store_final(col_half + kb + j, x[kb + j]);
         }
       }
       ptx::tmem_wait_st();
