@@ -402,22 +402,24 @@ bwd_scan_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     };
 
     // ---- initial state: dS = exp(gL) * dht (fp32), its 16-bit copy, and dh of the last chunk
+    // (this thread's 64 values are requested before the first stage is waited for: the two latencies overlap)
     {
+      float xs[64];
+#pragma unroll
+      for (int j = 0; j < 64; ++j) {
+        const int k = col_half + j;
+        xs[j] = dhtp != nullptr ? dhtp[k * ht_k + v * ht_v] : ((init_identity && k == v) ? 1.f : 0.f);
+      }
       float egl0 = 1.f;
       if (nproc > 0) {
         alive = wait(kFull0, 0);
         egl0 = gates_of(0)->egl;
       }
       T* hp = (nproc > 0 && !state_only) ? dh_row(nproc - 1) : nullptr;
-#pragma unroll 1
-      for (int kb = 0; kb < 64; kb += 16) {
-        float x[16];
-        uint32_t sf[16], sb[8];
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const int k = col_half + kb + j;
-          x[j] = dhtp != nullptr ? dhtp[k * ht_k + v * ht_v] : ((init_identity && k == v) ? 1.f : 0.f);
-        }
+      for (int kb = 0; kb < 64; kb += 16) {
+        const float* x = xs + kb;
+        uint32_t sf[16], sb[8];
 #pragma unroll
         for (int j = 0; j < 16; j += 2) {
           sf[j] = __float_as_uint(x[j] * egl0);
