@@ -267,6 +267,8 @@ __global__ void __launch_bounds__(128) recurrent_kernel(const QlaRecurrentArgs p
     const float a_raw = a_in, b_raw = b_in;
     if (step + 1 < len) fetch_inputs(t + 1);
 
+    // q and k stay as loaded: the factors scale / |q| and 1 / |k| are folded into the three scalars that use them
+    // (the k . S product, the update coefficient, the output), which saves 32 multiplies per thread and step
     float qs = p.scale, ks = 1.f;
     if (l2norm) {
       float qq = 0.f, kk = 0.f;
@@ -282,13 +284,6 @@ __global__ void __launch_bounds__(128) recurrent_kernel(const QlaRecurrentArgs p
       qs *= rsqrtf(qq + 1e-6f);
       ks = rsqrtf(kk + 1e-6f);
     }
-#pragma unroll
-    for (int j = 0; j < 4; ++j)
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        qv[j][i] *= qs;
-        kv[j][i] *= ks;
-      }
 
     float g;
     if (p.flags & QLA_REC_A_IS_LOG_DECAY) {
@@ -317,12 +312,12 @@ __global__ void __launch_bounds__(128) recurrent_kernel(const QlaRecurrentArgs p
       dot[r] = (acc[0] + acc[1]) + (acc[2] + acc[3]);
     }
 #pragma unroll
-    for (int r = 0; r < R; ++r) dot[r] = group8_sum(dot[r]);
+    for (int r = 0; r < R; ++r) dot[r] = group8_sum(dot[r]) * ks;
 
     float out[R];
 #pragma unroll
     for (int r = 0; r < R; ++r) {
-      const float delta = (vrow[r] - dot[r]) * beta;
+      const float delta = (vrow[r] - dot[r]) * beta * ks;  // times k / |k| below: one factor here
       float acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int i = 0; i < 4; ++i)
@@ -334,7 +329,7 @@ __global__ void __launch_bounds__(128) recurrent_kernel(const QlaRecurrentArgs p
       out[r] = (acc[0] + acc[1]) + (acc[2] + acc[3]);
     }
 #pragma unroll
-    for (int r = 0; r < R; ++r) out[r] = group8_sum(out[r]);
+    for (int r = 0; r < R; ++r) out[r] = group8_sum(out[r]) * qs;
     if (sub == 0) {
 #pragma unroll
       for (int r = 0; r < R; ++r)
