@@ -116,6 +116,8 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                  const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_o,
                  const FwdParams p) {
   constexpr uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? ptx::kFmtBF16 : ptx::kFmtF16;
+  grid_dep_wait();    // earlier kernels of the stream have completed (see launch_dependent)
+  grid_dep_launch();  // the next one may be scheduled; it waits the same way
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   // A "dual" launch carries two passes over the same sequences in one grid: the CTAs of the second half run
   // the transition-matrix pass of context parallelism (start from the identity, V treated as zero) with their
@@ -827,17 +829,17 @@ int launch_chunk_fwd(const FwdParams& p, const void* q, const void* k, const voi
 #define QLA_LAUNCH_FWD(T, SO, AUX, TR)                                                                          \
   do {                                                                                                          \
     { const int rc_ = ensure_dynamic_smem<chunk_fwd_kernel<T, SO, AUX, TR>>(kSmemBytes); if (rc_ != QLA_OK) return rc_; }  \
-    chunk_fwd_kernel<T, SO, AUX, TR><<<grid, kThreads, kSmemBytes, stream>>>(tm_q, tm_k, tm_v, tm_a, tm_w, tm_o, p); \
+    QLA_CHECK_CUDA(launch_dependent(chunk_fwd_kernel<T, SO, AUX, TR>, dim3(grid), dim3(kThreads), kSmemBytes, stream, tm_q, tm_k, tm_v, tm_a, tm_w, tm_o, p)); \
   } while (0)
 #define QLA_LAUNCH_FWD_NORM(T)                                                                                   \
   do {                                                                                                          \
     { const int rc_ = ensure_dynamic_smem<chunk_fwd_kernel<T, false, false, false, true>>(kSmemBytes); if (rc_ != QLA_OK) return rc_; }  \
-    chunk_fwd_kernel<T, false, false, false, true><<<grid, kThreads, kSmemBytes, stream>>>(tm_q, tm_k, tm_v, tm_a, tm_w, tm_o, p); \
+    QLA_CHECK_CUDA(launch_dependent(chunk_fwd_kernel<T, false, false, false, true>, dim3(grid), dim3(kThreads), kSmemBytes, stream, tm_q, tm_k, tm_v, tm_a, tm_w, tm_o, p)); \
   } while (0)
 #define QLA_LAUNCH_FWD_ST16(T)                                                                                   \
   do {                                                                                                          \
     { const int rc_ = ensure_dynamic_smem<chunk_fwd_kernel<T, false, false, false, false, true>>(kSmemBytes); if (rc_ != QLA_OK) return rc_; }  \
-    chunk_fwd_kernel<T, false, false, false, false, true><<<grid, kThreads, kSmemBytes, stream>>>(tm_q, tm_k, tm_v, tm_a, tm_w, tm_o, p); \
+    QLA_CHECK_CUDA(launch_dependent(chunk_fwd_kernel<T, false, false, false, false, true>, dim3(grid), dim3(kThreads), kSmemBytes, stream, tm_q, tm_k, tm_v, tm_a, tm_w, tm_o, p)); \
   } while (0)
 #define QLA_DISPATCH_FWD(T)                                                                  \
   do {                                                                                       \

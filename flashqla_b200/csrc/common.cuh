@@ -1,6 +1,7 @@
 // Shared host/device helpers for the flashqla_b200 kernels (sm_100a only).
 #pragma once
 
+#include <cstdlib>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
@@ -63,6 +64,36 @@ inline int ensure_dynamic_smem(size_t bytes) {
   if (dev >= 0 && dev < 64) done[dev] = true;
   return QLA_OK;
 }
+
+// Programmatic dependent launch: the kernels of one forward call are launched with this attribute, so that the
+// CTAs of a kernel are scheduled while the kernel before it in the stream drains; every kernel of the library
+// executes grid_dep_wait() as its first statement (before any global-memory access and before any early exit),
+// which returns when all earlier grids have completed and their writes are visible, so ordering is unchanged.
+// QLA_PDL=0 in the environment turns the attribute off (plain stream-ordered launches).
+inline bool pdl_enabled() {
+  static const bool on = []() {
+    const char* e = std::getenv("QLA_PDL");
+    return e == nullptr || e[0] != '0';
+  }();
+  return on;
+}
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                    Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+__device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_dep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 // Load one scalar of a runtime dtype (gates, biases: tiny tensors whose dtype varies by caller).
 __device__ __forceinline__ float load_scalar(const void* p, int dtype, int64_t i) {

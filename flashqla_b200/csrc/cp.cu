@@ -16,6 +16,8 @@ namespace {
 
 // One CTA per (segment, head): thread 0 walks the chunk-end gates; all threads write the segment's start state.
 __global__ void __launch_bounds__(256) cp_plan_kernel(const QlaCpPlanArgs a) {
+  grid_dep_wait();    // earlier kernels of the stream have completed (see launch_dependent)
+  grid_dep_launch();
   const int seg = blockIdx.x, h = blockIdx.y;
   const int num_heads = a.num_v_heads;
   if (threadIdx.x == 0) {
@@ -62,6 +64,8 @@ __global__ void __launch_bounds__(128) cp_chain_kernel(float* __restrict__ h0, c
                                                        const int32_t* __restrict__ m_limit,
                                                        const int32_t* __restrict__ raw_first_seg, int num_heads,
                                                        int reverse) {
+  grid_dep_wait();
+  grid_dep_launch();
   const int vt = blockIdx.x, h = blockIdx.y, r = blockIdx.z;
   const int s0 = raw_first_seg[r], s1 = raw_first_seg[r + 1];
   const int k = threadIdx.x;
@@ -108,8 +112,7 @@ extern "C" QLA_API int qla_cp_plan(const QlaCpPlanArgs* a, void* stream) {
   QLA_CHECK_SUPPORTED(a->h0 == nullptr || a->h0_dtype == QLA_DT_F32 || a->h0_dtype == QLA_DT_BF16,
                       "initial states must be fp32 or bf16");
   dim3 grid(a->num_segments, a->num_v_heads);
-  cp_plan_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(*a);
-  QLA_CHECK_CUDA(cudaGetLastError());
+  QLA_CHECK_CUDA(launch_dependent(cp_plan_kernel, grid, dim3(256), 0, static_cast<cudaStream_t>(stream), *a));
   return QLA_OK;
 }
 
@@ -118,8 +121,7 @@ extern "C" QLA_API int qla_cp_chain(const QlaCpChainArgs* a, void* stream) {
   QLA_CHECK_ARG(a != nullptr && a->h0 && a->M && a->m_limit && a->raw_first_seg, "NULL pointer in QlaCpChainArgs");
   QLA_CHECK_ARG(a->num_raw_seqs > 0 && a->num_v_heads > 0, "bad sizes");
   dim3 grid(kHeadDim / 32, a->num_v_heads, a->num_raw_seqs);
-  cp_chain_kernel<<<grid, 128, 0, static_cast<cudaStream_t>(stream)>>>(a->h0, a->M, a->m_limit, a->raw_first_seg,
-                                                                       a->num_v_heads, a->reverse);
-  QLA_CHECK_CUDA(cudaGetLastError());
+  QLA_CHECK_CUDA(launch_dependent(cp_chain_kernel, grid, dim3(128), 0, static_cast<cudaStream_t>(stream), a->h0, a->M,
+                                  a->m_limit, a->raw_first_seg, a->num_v_heads, a->reverse));
   return QLA_OK;
 }

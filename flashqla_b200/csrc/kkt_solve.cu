@@ -124,6 +124,8 @@ __global__ void __launch_bounds__(128, 3) kkt_solve_kernel(const __grid_constant
                                                         const __grid_constant__ CUtensorMap tm_a,
                                                         const __grid_constant__ CUtensorMap tm_w,
                                                         const KktParams p) {
+  grid_dep_wait();    // earlier kernels of the stream have completed (see launch_dependent)
+  grid_dep_launch();  // the next one may be scheduled; it waits the same way
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int hk = blockIdx.y;
   const int group = p.num_v_heads / p.num_k_heads;
@@ -502,6 +504,8 @@ __global__ void __launch_bounds__(128, 3) kkt_solve_kernel(const __grid_constant
 
 // pair_offsets[n] = sum_{m<n} ceil(len_m / 128), chunk_offsets[n] = sum_{m<n} ceil(len_m / 64).
 __global__ void chunk_tables_kernel(const int32_t* cu, int n, int32_t* pair_offsets, int32_t* chunk_offsets) {
+  grid_dep_wait();
+  grid_dep_launch();
   if (threadIdx.x == 0 && blockIdx.x == 0) {
     int po = 0, co = 0;
     for (int i = 0; i < n; ++i) {
@@ -520,7 +524,7 @@ __global__ void chunk_tables_kernel(const int32_t* cu, int n, int32_t* pair_offs
 
 int launch_chunk_tables(const int32_t* cu, int n, int32_t* pair_offsets, int32_t* chunk_offsets,
                         cudaStream_t stream) {
-  chunk_tables_kernel<<<1, 32, 0, stream>>>(cu, n, pair_offsets, chunk_offsets);
+  QLA_CHECK_CUDA(launch_dependent(chunk_tables_kernel, dim3(1), dim3(32), 0, stream, cu, n, pair_offsets, chunk_offsets));
   QLA_CHECK_CUDA(cudaGetLastError());
   return QLA_OK;
 }
@@ -543,10 +547,10 @@ int launch_kkt_solve(const KktParams& p, const void* k, const void* q, int64_t t
   dim3 grid(pairs_upper, p.num_k_heads);
   if (is_bf16) {
     if ((rc = ensure_dynamic_smem<kkt_solve_kernel<__nv_bfloat16>>(smem)) != QLA_OK) return rc;
-    kkt_solve_kernel<__nv_bfloat16><<<grid, 128, smem, stream>>>(tm_k, tm_q, tm_a, tm_w, p);
+    QLA_CHECK_CUDA(launch_dependent(kkt_solve_kernel<__nv_bfloat16>, grid, dim3(128), smem, stream, tm_k, tm_q, tm_a, tm_w, p));
   } else {
     if ((rc = ensure_dynamic_smem<kkt_solve_kernel<__half>>(smem)) != QLA_OK) return rc;
-    kkt_solve_kernel<__half><<<grid, 128, smem, stream>>>(tm_k, tm_q, tm_a, tm_w, p);
+    QLA_CHECK_CUDA(launch_dependent(kkt_solve_kernel<__half>, grid, dim3(128), smem, stream, tm_k, tm_q, tm_a, tm_w, p));
   }
   QLA_CHECK_CUDA(cudaGetLastError());
   return QLA_OK;
