@@ -156,6 +156,8 @@ bwd_chunk_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                  const __grid_constant__ CUtensorMap tm_dk, const __grid_constant__ CUtensorMap tm_dv, const BwdParams p,
                  const int total_items) {
   constexpr uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? ptx::kFmtBF16 : ptx::kFmtF16;
+  grid_dep_wait();    // earlier kernels of the stream have completed (see launch_dependent)
+  grid_dep_launch();  // the next one may be scheduled; it waits the same way
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int group = p.num_v_heads / p.num_k_heads;
   const int real_chunks = p.cu_seqlens != nullptr ? p.chunk_offsets[p.num_seqs] : 0x7fffffff;
@@ -843,8 +845,8 @@ int launch_chunk_bwd(const BwdParams& p, int64_t total_tokens, int total_chunks_
 #define QLA_LAUNCH_BWD_CHUNK(T, TR)                                                                         \
   do {                                                                                                     \
     if ((rc = ensure_dynamic_smem<bwd_chunk_kernel<T, TR>>(kSmemBytes)) != QLA_OK) return rc;              \
-    bwd_chunk_kernel<T, TR><<<grid, kThreads, kSmemBytes, stream>>>(tm_q, tm_k, tm_v, tm_vn, tm_do, tm_a, tm_h, tm_dh, \
-                                                                    tm_du, tm_dq, tm_dk, tm_dv, p, total_items); \
+    QLA_CHECK_CUDA(launch_dependent(bwd_chunk_kernel<T, TR>, dim3(grid), dim3(kThreads), kSmemBytes, stream, tm_q, tm_k, tm_v, \
+                                    tm_vn, tm_do, tm_a, tm_h, tm_dh, tm_du, tm_dq, tm_dk, tm_dv, p, total_items)); \
   } while (0)
   const bool traced = p.trace != nullptr;
   if (is_bf16) {

@@ -94,6 +94,8 @@ bwd_scan_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                 const __grid_constant__ CUtensorMap tm_dh, const __grid_constant__ CUtensorMap tm_du,
                 const BwdParams p, const BwdScanMode mode) {
   constexpr uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? ptx::kFmtBF16 : ptx::kFmtF16;
+  grid_dep_wait();    // earlier kernels of the stream have completed (see launch_dependent)
+  grid_dep_launch();  // the next one may be scheduled; it waits the same way
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   // context-parallel passes: the second half of a "dual" grid computes the K x K transition matrix of the reverse
   // recurrence over an interval's first chunks (identity start, dO treated as zero)
@@ -577,10 +579,12 @@ int launch_bwd_scan(const BwdParams& p, const BwdScanMode& mode, int64_t total_t
   const unsigned grid = static_cast<unsigned>(p.num_seqs) * p.num_v_heads * (mode.dual ? 2 : 1);
   if (is_bf16) {
     if ((rc = ensure_dynamic_smem<bwd_scan_kernel<__nv_bfloat16>>(kSmemBytes)) != QLA_OK) return rc;
-    bwd_scan_kernel<__nv_bfloat16><<<grid, kThreads, kSmemBytes, stream>>>(tm_q, tm_k, tm_do, tm_w, tm_dh, tm_du, p, mode);
+    QLA_CHECK_CUDA(launch_dependent(bwd_scan_kernel<__nv_bfloat16>, dim3(grid), dim3(kThreads), kSmemBytes, stream, tm_q, tm_k,
+                                    tm_do, tm_w, tm_dh, tm_du, p, mode));
   } else {
     if ((rc = ensure_dynamic_smem<bwd_scan_kernel<__half>>(kSmemBytes)) != QLA_OK) return rc;
-    bwd_scan_kernel<__half><<<grid, kThreads, kSmemBytes, stream>>>(tm_q, tm_k, tm_do, tm_w, tm_dh, tm_du, p, mode);
+    QLA_CHECK_CUDA(launch_dependent(bwd_scan_kernel<__half>, dim3(grid), dim3(kThreads), kSmemBytes, stream, tm_q, tm_k, tm_do,
+                                    tm_w, tm_dh, tm_du, p, mode));
   }
   QLA_CHECK_CUDA(cudaGetLastError());
   return QLA_OK;

@@ -110,6 +110,8 @@ __global__ void __launch_bounds__(128) recurrent_kernel(const QlaRecurrentArgs p
   using Piece = StatePiece<StateT>;
   extern __shared__ __align__(16) uint8_t s_stage_raw[];
   typename Piece::Raw* s_stage = reinterpret_cast<typename Piece::Raw*>(s_stage_raw);
+  grid_dep_wait();    // earlier kernels of the stream have completed (see launch_dependent)
+  grid_dep_launch();  // the next one may be scheduled; it waits the same way
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int sub = lane & 7, grp = lane >> 3;
   const int col0 = sub * 4;  // first owned column of j = 0; j-th is col0 + 32 j
@@ -385,7 +387,7 @@ int launch_recurrent_rows(const QlaRecurrentArgs& a, cudaStream_t stream) {
   // one CTA per item while they all fit at once; otherwise as many CTAs as are resident, each walking the
   // items with stride gridDim.x
   const unsigned grid = static_cast<unsigned>(items < resident ? items : resident);
-  recurrent_kernel<T, InterT, StateT, R><<<grid, 128, smem, stream>>>(a, items);
+  QLA_CHECK_CUDA(launch_dependent(recurrent_kernel<T, InterT, StateT, R>, dim3(grid), dim3(128), smem, stream, a, items));
   QLA_CHECK_CUDA(cudaGetLastError());
   return QLA_OK;
 }
