@@ -402,13 +402,22 @@ def run_recurrent(args, rank, world, device, verify: bool):
         # from the copy that oracle/build_ref.py places beside the oracle; same inputs, same pool rotation
         ref_file = ROOT / "oracle" / "_ref" / "recurrent_fused.py"
         if ref_file.exists():
+            import contextlib
+            import importlib.util
+            import logging
+            # TileLang logs its compilations to stdout, which carries this program's one JSON line: its loggers are
+            # created (and anything it prints is sent) with stdout pointing at stderr
+            redirect = contextlib.ExitStack()
             try:
-                import importlib.util
                 os.environ.setdefault("TILELANG_CACHE_DIR", "/tmp/flashqla_b200_tilelang_cache")
+                redirect.enter_context(contextlib.redirect_stdout(sys.stderr))
                 spec = importlib.util.spec_from_file_location("reference_recurrent_fused", ref_file)
                 rec = importlib.util.module_from_spec(spec)
                 sys.modules["reference_recurrent_fused"] = rec
                 spec.loader.exec_module(rec)
+                for name in list(logging.root.manager.loggerDict):
+                    if name.lower().startswith("tilelang"):
+                        logging.getLogger(name).setLevel(logging.ERROR)
                 zeros_h = torch.zeros(Hv, dtype=torch.float32, device=device)  # A_log / dt_bias: unused with log decays
                 rcalls = [0]
 
@@ -426,6 +435,8 @@ def run_recurrent(args, rank, world, device, verify: bool):
             except Exception as exc:
                 same_box.append({"impl": "reference flash_qla recurrent_fused.py (TileLang)",
                                  "unavailable": f"{type(exc).__name__}: {str(exc)[:160]}"})
+            finally:
+                redirect.close()
     cache_b = 0 if not verify else (2 if args.bf16_scratch else 4)
     nbytes = orc.state_bytes_decode(N, Hv, T=T, Hk=Hk, cache_bytes=cache_b, write_back=not verify)
     gbs = nbytes * world / (per_step * 1e-3) / 1e9
