@@ -64,6 +64,7 @@ class QlaChunkFwdArgs(C.Structure):
         ("h0_map", C.c_void_p), ("state_dtype", C.c_int32), ("reserved", C.c_int32),
         ("chunk_limit_b", C.c_void_p), ("seq_map_b", C.c_void_p), ("final_state_b", C.c_void_p),
         ("norm_gate", C.c_void_p), ("norm_weight", C.c_void_p), ("norm_eps", C.c_float), ("reserved2", C.c_int32),
+        ("lead", C.c_void_p),
     ]
 
 
@@ -99,7 +100,8 @@ class QlaCpPlanArgs(C.Structure):
         ("g_cumsum", C.c_void_p), ("cu_seqlens", C.c_void_p), ("seg_next", C.c_void_p),
         ("warm_limit", C.c_void_p), ("m_limit", C.c_void_p),
         ("cp_h0", C.c_void_p), ("seg_start_of", C.c_void_p), ("h0", C.c_void_p), ("h0_map", C.c_void_p),
-        ("h0_dtype", C.c_int32), ("h0_transposed", C.c_int32), ("reverse", C.c_int32), ("reserved", C.c_int32),
+        ("h0_dtype", C.c_int32), ("h0_transposed", C.c_int32), ("reverse", C.c_int32), ("num_raw_seqs", C.c_int32),
+        ("lead", C.c_void_p), ("raw_first_seg", C.c_void_p),
     ]
 
 

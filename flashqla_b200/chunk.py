@@ -46,7 +46,7 @@ def _check_common(q, k, v, g, beta, initial_state, cu_seqlens, transpose_state_l
 
 def _launch_fwd(q, k, v, g, beta, h0, cu, g_cumsum, A, o, h, v_new, final_state, scale, flags=0,
                 seq_map=None, chunk_limit=None, num_seqs=None, w=None, tables=None, seq_order=None, rnorm=None,
-                A_log=None, dt_bias=None, beta_out=None, h0_map=None, dual=None, out_norm=None):
+                A_log=None, dt_bias=None, beta_out=None, h0_map=None, dual=None, out_norm=None, lead=None):
     """Fill ``QlaChunkFwdArgs`` from tensors and call ``qla_chunk_fwd`` on the current stream.  ``w`` is
     the per-chunk operand ``-(A diag(beta e^g) K)`` that the preparation step writes and the scan reads;
     it is allocated here when the call does both.  ``tables`` is an optional dict holding the ready-made
@@ -55,7 +55,8 @@ def _launch_fwd(q, k, v, g, beta, h0, cu, g_cumsum, A, o, h, v_new, final_state,
     norm on: the preparation step writes the reciprocal row norms there, the scan reads them.  ``h0_map`` /
     ``seq_map`` are per-sequence rows of ``h0`` / ``final_state`` (state pools; ``-1`` = zero state / no output);
     the two share a dtype (fp32 or bf16).  ``dual = (chunk_limit_b, seq_map_b, final_state_b)`` adds the
-    transition-matrix pass of context parallelism to a state-only launch."""
+    transition-matrix pass of context parallelism to a state-only launch.  ``lead`` ``[num_seqs, Hv]``: chunks in
+    front of every interval that its scan runs first from a zero state (cp.segment_initial_states)."""
     dev = k.device
     if w is None:
         assert not flags & _cabi.CHUNK_SKIP_PREPARE, "a scan without preparation needs the prepared w"
@@ -93,7 +94,7 @@ def _launch_fwd(q, k, v, g, beta, h0, cu, g_cumsum, A, o, h, v_new, final_state,
         A_log=_cabi.ptr(A_log), dt_bias=_cabi.ptr(dt_bias), beta_out=_cabi.ptr(beta_out), o=_cabi.ptr(o),
         h=_cabi.ptr(h), v_new=_cabi.ptr(v_new), final_state=_cabi.ptr(final_state), workspace=None,
         workspace_bytes=0, status=_cabi.ptr(status), h0_map=_cabi.ptr(h0_map),
-        state_dtype=_cabi.dtype_code(state_dtype), **dual_args)
+        state_dtype=_cabi.dtype_code(state_dtype), lead=_cabi.ptr(lead), **dual_args)
     lib = _cabi.lib()
     if tables is not None and "ws" in tables:
         ws = tables["ws"]
@@ -170,12 +171,12 @@ def make_scan_only(q, k, v, beta, g_cumsum, A, o, final_state, initial_state=Non
     plan = cp.get_plan(lens, Hv, dev) if auto_cp else None
     w = rebuild_w(k, beta, g_cumsum, A, cu)
     if plan is not None and plan.use_cp:
-        cp_h0 = cp.segment_initial_states(plan, k, v, beta, g_cumsum, A, w, initial_state, scale, _launch_fwd)
+        cp_h0, lead = cp.segment_initial_states(plan, k, v, beta, g_cumsum, A, w, initial_state, scale, _launch_fwd)
 
         def run():
             _launch_fwd(q, k, v, None, beta, cp_h0, plan.dev["cu"], g_cumsum, A, o, None, None, final_state,
                         scale, flags=_cabi.CHUNK_SKIP_PREPARE | _cabi.CHUNK_H0_KV_F32, seq_map=plan.dev["seg_raw"],
-                        num_seqs=len(plan.seg_next), w=w, tables=plan.tables)
+                        num_seqs=len(plan.seg_next), w=w, tables=plan.tables, lead=lead)
         return run
 
     def run():
@@ -329,8 +330,8 @@ def chunk_gated_delta_rule_fwd(
                     scale, flags=_cabi.CHUNK_PREPARE_ONLY, w=w, rnorm=rnorm, **act)
         if beta_act is not None:
             beta = beta_act  # every later stage reads the activated values
-        cp_h0 = cp.segment_initial_states(plan, k, v, beta, g_cumsum, A, w, h0, scale, _launch_fwd, rnorm=rnorm,
-                                          h0_map=h0_map, h0_transposed=transpose_state_layout)
+        cp_h0, lead = cp.segment_initial_states(plan, k, v, beta, g_cumsum, A, w, h0, scale, _launch_fwd, rnorm=rnorm,
+                                                h0_map=h0_map, h0_transposed=transpose_state_layout)
         seg_rows = plan.dev["seg_raw"]
         if fs_map is not None:  # segment -> sequence -> row of the caller's pool
             seg_rows = torch.where(seg_rows >= 0, fs_map[seg_rows.clamp(min=0).long()], seg_rows)
@@ -338,7 +339,7 @@ def chunk_gated_delta_rule_fwd(
                     flags=_cabi.CHUNK_SKIP_PREPARE | _cabi.CHUNK_H0_KV_F32 |
                     (_cabi.CHUNK_TRANSPOSE_STATE if transpose_state_layout else 0),
                     seq_map=seg_rows, num_seqs=len(plan.seg_next), w=w, tables=plan.tables, rnorm=rnorm,
-                    out_norm=out_norm)
+                    out_norm=out_norm, lead=lead)
     else:
         # packed batches of unequal lengths: the longest sequences are handed to the GPU first
         order = longest_first_order(cu_seqlens, dev) if cu_seqlens is not None else None

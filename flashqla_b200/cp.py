@@ -30,7 +30,8 @@ CHUNK = 64
 MIN_SEG_CHUNKS = 8
 WARMUP_CHUNKS = 10        # typical length of the warm-up pass (chunks until the decay passes the threshold)
 WARMUP_COST = 0.6         # cost of a state-only chunk relative to a full one
-WARMUP_THRESHOLD = -10.0  # exp(-10) ~ 4.5e-5: what a dropped prefix may contribute (cp_fwd.py:29-61)
+WARMUP_THRESHOLD = -10.0
+INLINE_WARMUP = True      # fold the warm-up of a segment into its own scan where no transition matrix is needed  # exp(-10) ~ 4.5e-5: what a dropped prefix may contribute (cp_fwd.py:29-61)
 
 
 @dataclass
@@ -110,11 +111,14 @@ def get_plan(lens: Sequence[int], num_v_heads: int, device: torch.device) -> CpP
 
 
 def segment_initial_states(plan: CpPlan, k, v, beta, g_cumsum, A, w, h0, scale, launch_fwd, rnorm=None,
-                           h0_map=None, h0_transposed=False):
-    """Run plan (+ start states) -> warm-up and transition passes (one launch) -> chaining.  Returns ``cp_h0``
-    fp32 ``[n_seg, Hv, 128(K), 128(V)]``: the state every segment starts from.  ``launch_fwd`` is
-    ``chunk._launch_fwd``; ``w`` is the prepared chunk operand that goes with ``A``; ``h0`` are the caller's
-    initial states (fp32 or bf16, ``[V, K]`` with ``h0_transposed``, rows picked by ``h0_map`` if given)."""
+                           h0_map=None, h0_transposed=False, inline_warmup=None):
+    """Run plan (+ start states) -> warm-up and transition passes (one launch) -> chaining.  Returns ``(cp_h0,
+    lead)``: ``cp_h0`` fp32 ``[n_seg, Hv, 128(K), 128(V)]`` is the state a segment starts from, ``lead`` int32
+    ``[n_seg, Hv]`` (or ``None``) the number of chunks in front of a segment that the main scan runs first from a
+    zero state INSTEAD of reading ``cp_h0`` (the warm-up folded into the scan: every sequence and head whose
+    segments all decay below the threshold; the state-only launch then finds nothing to do for them).
+    ``launch_fwd`` is ``chunk._launch_fwd``; ``w`` is the prepared chunk operand that goes with ``A``; ``h0`` are
+    the caller's initial states (fp32 or bf16, ``[V, K]`` with ``h0_transposed``, rows picked by ``h0_map``)."""
     dev = k.device
     Hv = beta.shape[2]
     d = plan.dev
@@ -124,13 +128,17 @@ def segment_initial_states(plan: CpPlan, k, v, beta, g_cumsum, A, w, h0, scale, 
     warm_limit = torch.empty(n_seg, Hv, dtype=torch.int32, device=dev)
     m_limit = torch.empty(n_seg, Hv, dtype=torch.int32, device=dev)
     cp_h0 = torch.empty(n_seg, Hv, 128, 128, dtype=torch.float32, device=dev)
+    if inline_warmup is None:
+        inline_warmup = INLINE_WARMUP
+    lead = torch.empty(n_seg, Hv, dtype=torch.int32, device=dev) if inline_warmup else None
     pa = _cabi.QlaCpPlanArgs(num_segments=n_seg, num_v_heads=Hv, threshold=WARMUP_THRESHOLD,
                              g_cumsum=g_cumsum.data_ptr(), cu_seqlens=d["cu"].data_ptr(),
                              seg_next=d["seg_next"].data_ptr(), warm_limit=warm_limit.data_ptr(),
                              m_limit=m_limit.data_ptr(), cp_h0=cp_h0.data_ptr(), seg_start_of=d["seg_start_of"].data_ptr(),
                              h0=_cabi.ptr(h0), h0_map=_cabi.ptr(h0_map),
                              h0_dtype=_cabi.dtype_code(h0.dtype) if h0 is not None else 0,
-                             h0_transposed=1 if h0_transposed else 0)
+                             h0_transposed=1 if h0_transposed else 0, lead=_cabi.ptr(lead),
+                             raw_first_seg=d["raw_first"].data_ptr(), num_raw_seqs=len(plan.raw_first) - 1)
     with torch.cuda.device(dev):
         _cabi.check(lib.qla_cp_plan(pa, stream), "qla_cp_plan")
     # One launch, two passes: segment-end states from the trailing `warm_limit` chunks, written straight into the
@@ -144,7 +152,7 @@ def segment_initial_states(plan: CpPlan, k, v, beta, g_cumsum, A, w, h0, scale, 
                               M=M.data_ptr(), m_limit=m_limit.data_ptr(), raw_first_seg=d["raw_first"].data_ptr())
     with torch.cuda.device(dev):
         _cabi.check(lib.qla_cp_chain(ca, stream), "qla_cp_chain")
-    return cp_h0
+    return cp_h0, lead
 
 
 def segment_end_gradients(plan: CpPlan, q, k, do, w, g_cumsum, dht, scale, transposed=False):

@@ -116,6 +116,7 @@ extern "C" QLA_API int qla_chunk_fwd(const QlaChunkFwdArgs* args, void* stream_)
   fp.state_dtype = a.state_dtype; fp.h0_kv = (a.flags & QLA_CHUNK_H0_KV_F32) ? 1 : 0;
   fp.cu_seqlens = a.cu_seqlens; fp.seq_map = a.seq_map; fp.seq_order = a.seq_order;
   fp.rnorm = l2norm ? a.qk_rnorm : nullptr; fp.chunk_offsets = chunk_offsets;
+  fp.lead = a.lead;
   fp.chunk_limit = a.chunk_limit; fp.o = a.o; fp.v_new = a.v_new; fp.h = a.h; fp.final_state = a.final_state;
   fp.status = a.status; fp.num_seqs = a.num_seqs; fp.seq_len = a.seq_len;
   fp.num_k_heads = a.num_k_heads; fp.num_v_heads = a.num_v_heads; fp.beta_dtype = a.beta_dtype;

@@ -148,6 +148,10 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     if (lim <= 0) return;  // nothing asked of this (sequence, head); uniform for the whole CTA
     if (lim < nchunks) first_chunk = nchunks - lim;
   }
+  // warm-up inside the scan: `lead` chunks of the interval in front (same sequence) are run first from a zero
+  // state; nothing of them is stored (their own interval's CTA computes them exactly)
+  const int lead = (p.lead != nullptr && !pass_b) ? p.lead[seq * p.num_v_heads + hv] : 0;
+  first_chunk -= lead;
   const int nproc = nchunks - first_chunk;
   const int out_row = seq_map ? seq_map[seq] : seq;
   const int64_t chunk_base =
@@ -503,7 +507,7 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     const bool h0_16 = st16 && !p.h0_kv;
     const int h0_k = (p.transpose_state && !p.h0_kv) ? 1 : kHeadDim, h0_v = (p.transpose_state && !p.h0_kv) ? kHeadDim : 1;
     const int64_t h0_off = (static_cast<int64_t>(h0_row) * p.num_v_heads + hv) * kHeadDim * kHeadDim;
-    const bool has_h0 = !init_identity && p.h0 != nullptr && h0_row >= 0;
+    const bool has_h0 = !init_identity && p.h0 != nullptr && h0_row >= 0 && lead == 0;
     const float* h0p = (has_h0 && !h0_16) ? static_cast<const float*>(p.h0) + h0_off : nullptr;
     const __nv_bfloat16* h0p16 = (has_h0 && h0_16) ? static_cast<const __nv_bfloat16*>(p.h0) + h0_off : nullptr;
     auto store_final = [&](int k, float x) {
@@ -531,7 +535,7 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         alive = wait(kFull0, 0);
         egl0 = gates_of(0)->egl;
       }
-      T* hp0 = (kAux && p.h != nullptr && nproc > 0)
+      T* hp0 = (kAux && p.h != nullptr && nproc > 0 && lead == 0)
                    ? static_cast<T*>(p.h) + ((chunk_base + first_chunk) * p.num_v_heads + hv) * kHeadDim * kHeadDim + v
                    : nullptr;
 #pragma unroll
@@ -583,7 +587,7 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         ptx::tc_fence_after_sync();
         if (tid == 0) trace(1, i, 2);
         uint8_t* vt = smem + kOffVd + (i & 1) * 16384;
-        T* vn_dst = (kAux && p.v_new != nullptr)
+        T* vn_dst = (kAux && p.v_new != nullptr && i >= lead)
                         ? static_cast<T*>(p.v_new) + (static_cast<int64_t>(t0) * p.num_v_heads + hv) * kHeadDim + v
                         : nullptr;
 #pragma unroll 1
@@ -761,7 +765,7 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           }
         }
       } else {
-        T* hp = (kAux && p.h != nullptr)
+        T* hp = (kAux && p.h != nullptr && i + 1 >= lead)
                     ? static_cast<T*>(p.h) + ((chunk_base + chunk + 1) * p.num_v_heads + hv) * kHeadDim * kHeadDim + v
                     : nullptr;
         // (a) critical: 16-bit copy of the new state -> MMA2 of the next chunk may start
@@ -801,7 +805,7 @@ chunk_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         ptx::tc_fence_before_sync();
         warp_arrive(&bars[kSScaled], lane);
       }
-      prev_valid = valid;
+      prev_valid = i < lead ? 0 : valid;  // nothing of a warm-up chunk is stored
       prev_t0 = t0;
     }
     if (!kStateOnly && tid == 128) ptx::tma_store_wait_all();

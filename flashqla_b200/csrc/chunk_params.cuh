@@ -35,6 +35,7 @@ struct FwdParams {
   const float* rnorm;           // [NT, Hk, 2] = 1/|q_t|, 1/|k_t| or NULL (q, k used as they are)
   const int32_t* chunk_offsets; // [num_seqs + 1] first chunk index of each sequence (varlen h output)
   const int32_t* chunk_limit;   // [num_seqs, Hv] optional: only the LAST chunk_limit chunks are processed
+  const int32_t* lead;          // [num_seqs, Hv] optional: chunks in front of the interval run first from a zero state, outputs not stored
   void* o;                      // [NT, Hv, 128]
   void* v_new;                  // [NT, Hv, 128] or NULL
   void* h;                      // [total_chunks, Hv, 128, 128] bf16/fp16 or NULL

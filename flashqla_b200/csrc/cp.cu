@@ -59,6 +59,61 @@ __global__ void __launch_bounds__(256) cp_plan_kernel(const QlaCpPlanArgs a) {
   }
 }
 
+// The forward plan with the warm-up folded into the main scan: one CTA per (original sequence, head), a thread
+// per segment.  A (sequence, head) in which every segment decays below the threshold needs no state-only pass:
+// the main scan's CTA of segment s simply starts lead[s] = warm(s - 1) chunks early, from a zero state.  If some
+// segment never decays that far the limits are those of cp_plan_kernel (state-only pass, transition matrices,
+// chain) and lead is 0.  Only the row of cp_h0 that starts the sequence is written here.
+__global__ void __launch_bounds__(256) cp_plan_lead_kernel(const QlaCpPlanArgs a) {
+  grid_dep_wait();
+  grid_dep_launch();
+  const int r = blockIdx.x, h = blockIdx.y;
+  const int num_heads = a.num_v_heads;
+  const int s0 = a.raw_first_seg[r], s1 = a.raw_first_seg[r + 1];
+  int any = 0;
+  for (int seg = s0 + threadIdx.x; seg < s1; seg += 256) {
+    const int start = a.cu_seqlens[seg], end = a.cu_seqlens[seg + 1];
+    const int nchunks = (end - start + kChunk - 1) / kChunk;
+    int warm = 0, ml = 0;
+    if (a.seg_next[seg] >= 0 && nchunks > 0) {
+      float acc = 0.f;
+      bool reached = false;
+      for (int i = 0; i < nchunks; ++i) {
+        const int last = min(end, start + (nchunks - i) * kChunk) - 1;
+        acc += a.g_cumsum[static_cast<int64_t>(last) * num_heads + h];
+        ++warm;
+        if (acc < a.threshold) { reached = true; break; }
+      }
+      if (!reached) ml = nchunks;
+    }
+    a.warm_limit[seg * num_heads + h] = warm;
+    a.m_limit[seg * num_heads + h] = ml;
+    any |= ml;
+  }
+  any = __syncthreads_or(any);  // (also orders the limits written above before the reads below)
+  for (int seg = s0 + threadIdx.x; seg < s1; seg += 256)
+    a.lead[seg * num_heads + h] = (!any && seg > s0) ? a.warm_limit[(seg - 1) * num_heads + h] : 0;
+  __syncthreads();
+  if (!any)
+    for (int seg = s0 + threadIdx.x; seg < s1; seg += 256) a.warm_limit[seg * num_heads + h] = 0;
+  // start state of the sequence: the caller's (any dtype / layout, through h0_map) or zero
+  constexpr int kElems = kHeadDim * kHeadDim;
+  float* dst = a.cp_h0 + (static_cast<int64_t>(s0) * num_heads + h) * kElems;
+  int row = -1;
+  if (a.h0 != nullptr) row = a.h0_map != nullptr ? a.h0_map[r] : r;
+  if (row < 0) {
+    for (int i = threadIdx.x * 4; i < kElems; i += 256 * 4) *reinterpret_cast<float4*>(dst + i) = make_float4(0.f, 0.f, 0.f, 0.f);
+    return;
+  }
+  const int64_t off = (static_cast<int64_t>(row) * num_heads + h) * kElems;
+  const float* s32 = static_cast<const float*>(a.h0) + off;
+  const __nv_bfloat16* s16 = static_cast<const __nv_bfloat16*>(a.h0) + off;
+  for (int i = threadIdx.x; i < kElems; i += 256) {
+    const int di = a.h0_transposed ? (i & (kHeadDim - 1)) * kHeadDim + (i >> 7) : i;
+    dst[di] = a.h0_dtype == QLA_DT_BF16 ? __bfloat162float(s16[i]) : s32[i];
+  }
+}
+
 // One CTA: one (raw sequence, head, 32-column slab of the state).  Thread t owns row k = t of the slab.
 __global__ void __launch_bounds__(128) cp_chain_kernel(float* __restrict__ h0, const float* __restrict__ M,
                                                        const int32_t* __restrict__ m_limit,
@@ -111,6 +166,13 @@ extern "C" QLA_API int qla_cp_plan(const QlaCpPlanArgs* a, void* stream) {
   QLA_CHECK_ARG(a->cp_h0 == nullptr || a->seg_start_of != nullptr, "cp_h0 needs seg_start_of");
   QLA_CHECK_SUPPORTED(a->h0 == nullptr || a->h0_dtype == QLA_DT_F32 || a->h0_dtype == QLA_DT_BF16,
                       "initial states must be fp32 or bf16");
+  if (a->lead != nullptr) {
+    QLA_CHECK_ARG(a->cp_h0 != nullptr && a->raw_first_seg != nullptr && a->num_raw_seqs > 0 && !a->reverse,
+                  "lead needs cp_h0, raw_first_seg, num_raw_seqs (forward plan only)");
+    dim3 grid_lead(a->num_raw_seqs, a->num_v_heads);
+    QLA_CHECK_CUDA(launch_dependent(cp_plan_lead_kernel, grid_lead, dim3(256), 0, static_cast<cudaStream_t>(stream), *a));
+    return QLA_OK;
+  }
   dim3 grid(a->num_segments, a->num_v_heads);
   QLA_CHECK_CUDA(launch_dependent(cp_plan_kernel, grid, dim3(256), 0, static_cast<cudaStream_t>(stream), *a));
   return QLA_OK;

@@ -227,6 +227,10 @@ typedef struct QlaChunkFwdArgs {
   const float* norm_weight;     /* QLA_CHUNK_OUT_GATED_RMSNORM: fp32 [128]                            */
   float norm_eps;
   int32_t reserved2;
+  const int32_t* lead;          /* [num_seqs, Hv] or NULL: chunks in FRONT of an interval (tokens of the interval
+                                   before it in the same sequence) that are run first from a zero state, their
+                                   outputs not stored: the warm-up of a context-parallel segment inside its own
+                                   scan (qla_cp_plan writes it); an interval with lead > 0 ignores h0          */
 } QlaChunkFwdArgs;
 
 QLA_API size_t qla_chunk_fwd_workspace_bytes(const QlaChunkFwdArgs* args);
@@ -347,7 +351,15 @@ typedef struct QlaCpPlanArgs {
   int32_t reverse;            /* plan for the backward scan: count LEADING chunks of a segment (the
                                  accumulated decay from its start) instead of trailing ones; seg_next
                                  then names the segment's predecessor (< 0: none)                 */
-  int32_t reserved;
+  int32_t num_raw_seqs;       /* with lead: number of original sequences                        */
+  /* optional (forward plan, with cp_h0): warm-up inside the main scan.  lead[s,h] = trailing chunks of the
+   * segment before s that the main scan's CTA of s runs first, from a zero state and without storing their
+   * output (QlaChunkFwdArgs.lead): the state-only pass then has nothing to do for that sequence and head
+   * (warm_limit = 0).  A sequence and head in which some segment never decays below the threshold keeps the
+   * state-only pass, the transition matrices and the chain (lead = 0 there).  Only the rows of cp_h0 that start a
+   * sequence are initialised in this mode (the others are written by the state-only pass or not read at all).  */
+  int32_t* lead;              /* out [num_segments, Hv] or NULL                                 */
+  const int32_t* raw_first_seg; /* [num_raw_seqs + 1] first segment of every original sequence; with lead */
 } QlaCpPlanArgs;
 
 QLA_API int qla_cp_plan(const QlaCpPlanArgs* args, void* stream);

@@ -352,3 +352,29 @@ def test_reference_import_paths_run_on_the_gpu(fq):
     assert all(t.grad is not None and torch.isfinite(t.grad.float()).all() for t in (q, k, v, g, beta))
     raw = chunk_gated_delta_rule_fwd(q.detach(), k.detach(), v.detach(), g.detach(), beta.detach())
     assert orc.rel_rms(raw[2].float().cpu(), o.detach().float().cpu()) <= 1e-3
+
+
+@pytest.mark.parametrize("gate_div,zero_gate", [(1.0, 0.0), (16.0, 0.25)])
+def test_cp_warmup_inside_the_scan_equals_the_separate_pass(fq, gate_div, zero_gate):
+    """The warm-up of a context-parallel segment runs inside its own scan (`lead` chunks in front, zero start,
+    nothing stored) wherever no transition matrix is needed; the separate state-only pass remains for the rest.
+    Both routes see the same chunks, so the results agree to rounding; training outputs (h, v_new) too."""
+    from flashqla_b200 import cp
+    T = 4096 + 37
+    inp = orc.make_prefill_inputs(1, T, 2, 4, seed=61, with_h0=True, gate_div=gate_div, zero_gate_heads=zero_gate)
+    c = _cuda(inp)
+    run = lambda: fq.chunk_gated_delta_rule_fwd(c["q"], c["k"], c["v"], c["g"], c["beta"], initial_state=c["h0"],
+                                                output_h=True, output_v_new=True)
+    assert cp.INLINE_WARMUP
+    a = run()
+    cp.INLINE_WARMUP = False
+    try:
+        b = run()
+    finally:
+        cp.INLINE_WARMUP = True
+    fq.check_device_status()
+    for name, x, y in (("o", a[2], b[2]), ("h", a[3], b[3]), ("final_state", a[4], b[4]), ("v_new", a[5], b[5])):
+        assert orc.rel_rms(x.float().cpu(), y.float().cpu()) <= 1e-3, name
+    ref = orc.chunk_gdr_fwd(inp["q"], inp["k"], inp["v"], inp["g"], inp["beta"], h0=inp["h0"])
+    _check("o", a[2], ref["o"])
+    _check("h", a[3], ref["h"])
