@@ -108,6 +108,14 @@ __global__ void __launch_bounds__(256) cp_plan_lead_kernel(const QlaCpPlanArgs a
   const int64_t off = (static_cast<int64_t>(row) * num_heads + h) * kElems;
   const float* s32 = static_cast<const float*>(a.h0) + off;
   const __nv_bfloat16* s16 = static_cast<const __nv_bfloat16*>(a.h0) + off;
+  if (!a.h0_transposed && a.h0_dtype != QLA_DT_BF16) {
+    // the common case (a carried fp32 [K, V] state): 16-byte copies, four in flight per thread
+#pragma unroll 4
+    for (int i = threadIdx.x * 4; i < kElems; i += 256 * 4)
+      *reinterpret_cast<float4*>(dst + i) = *reinterpret_cast<const float4*>(s32 + i);
+    return;
+  }
+#pragma unroll 4
   for (int i = threadIdx.x; i < kElems; i += 256) {
     const int di = a.h0_transposed ? (i & (kHeadDim - 1)) * kHeadDim + (i >> 7) : i;
     dst[di] = a.h0_dtype == QLA_DT_BF16 ? __bfloat162float(s16[i]) : s32[i];
