@@ -81,7 +81,7 @@ class QlaChunkBwdArgs(C.Structure):
         ("workspace_bytes", C.c_size_t), ("status", C.c_void_p),
         ("num_segments", C.c_int32), ("reserved", C.c_int32), ("seg_cu", C.c_void_p), ("seg_dht", C.c_void_p),
         ("seg_dh0_map", C.c_void_p), ("chunk_limit", C.c_void_p), ("out_map", C.c_void_p),
-        ("chunk_limit_b", C.c_void_p), ("out_map_b", C.c_void_p), ("out_b", C.c_void_p),
+        ("chunk_limit_b", C.c_void_p), ("out_map_b", C.c_void_p), ("out_b", C.c_void_p), ("seg_lead", C.c_void_p),
     ]
 
 

@@ -425,9 +425,10 @@ def chunk_gated_delta_rule_bwd(
     plan = cp.get_plan(lens if lens is not None else [T] * B, Hv, dev) if auto_cp else None
     seg = {}
     if plan is not None and plan.use_cp:
-        seg_dht = cp.segment_end_gradients(plan, q, k, do, w, g_cumsum, dht, scale, transposed=transpose_state_layout)
+        seg_dht, seg_lead = cp.segment_end_gradients(plan, q, k, do, w, g_cumsum, dht, scale,
+                                                     transposed=transpose_state_layout)
         seg = dict(num_segments=len(plan.seg_next), seg_cu=_cabi.ptr(plan.dev["cu"]), seg_dht=_cabi.ptr(seg_dht),
-                   seg_dh0_map=_cabi.ptr(plan.dev["seg_start_of"]))
+                   seg_dh0_map=_cabi.ptr(plan.dev["seg_start_of"]), seg_lead=_cabi.ptr(seg_lead))
     args = _cabi.QlaChunkBwdArgs(
         batch=Bk, seq_len=Tk, num_seqs=N, num_k_heads=Hk, num_v_heads=Hv, qkv_dtype=_cabi.dtype_code(q.dtype),
         beta_dtype=_cabi.dtype_code(beta.dtype), flags=flags, scale=float(scale),

@@ -157,8 +157,10 @@ def segment_initial_states(plan: CpPlan, k, v, beta, g_cumsum, A, w, h0, scale, 
 
 def segment_end_gradients(plan: CpPlan, q, k, do, w, g_cumsum, dht, scale, transposed=False):
     """The backward's counterpart of :func:`segment_initial_states` (the reference's backward has no context
-    parallelism: its grid is sequences x heads, chunk/hopper/fused_bwd.py:79).  Returns ``seg_dht`` fp32
-    ``[n_seg, Hv, 128(K), 128(V)]``: the state gradient entering every segment from its right end.
+    parallelism: its grid is sequences x heads, chunk/hopper/fused_bwd.py:79).  Returns ``(seg_dht, lead)``:
+    ``seg_dht`` fp32 ``[n_seg, Hv, 128(K), 128(V)]`` is the state gradient entering a segment from its right end,
+    ``lead`` (or ``None``) the number of chunks behind a segment that its reverse scan runs first from a zero
+    gradient instead (the warm-up folded into the scan, as in the forward).
 
     plan (reverse: decay accumulated from a segment's START; rows of the last segments take the caller's ``dht``)
     -> one launch of the reverse scan in state-only mode over the leading chunks of every segment (zero start,
@@ -174,12 +176,14 @@ def segment_end_gradients(plan: CpPlan, q, k, do, w, g_cumsum, dht, scale, trans
     warm_limit = torch.empty(n_seg, Hv, dtype=torch.int32, device=dev)
     m_limit = torch.empty(n_seg, Hv, dtype=torch.int32, device=dev)
     seg_dht = torch.empty(n_seg, Hv, 128, 128, dtype=torch.float32, device=dev)
+    lead = torch.empty(n_seg, Hv, dtype=torch.int32, device=dev) if INLINE_WARMUP else None
     pa = _cabi.QlaCpPlanArgs(num_segments=n_seg, num_v_heads=Hv, threshold=WARMUP_THRESHOLD,
                              g_cumsum=g_cumsum.data_ptr(), cu_seqlens=d["cu"].data_ptr(),
                              seg_next=d["seg_prev"].data_ptr(), warm_limit=warm_limit.data_ptr(),
                              m_limit=m_limit.data_ptr(), cp_h0=seg_dht.data_ptr(), seg_start_of=d["seg_raw"].data_ptr(),
                              h0=_cabi.ptr(dht), h0_map=None, h0_dtype=_cabi.QLA_DT_F32,
-                             h0_transposed=1 if transposed else 0, reverse=1)
+                             h0_transposed=1 if transposed else 0, reverse=1, lead=_cabi.ptr(lead),
+                             raw_first_seg=d["raw_first"].data_ptr(), num_raw_seqs=len(plan.raw_first) - 1)
     M = torch.empty(n_seg, Hv, 128, 128, dtype=torch.float32, device=dev)
     total = q.shape[0] * q.shape[1]
     from .utils import device_status
@@ -197,4 +201,4 @@ def segment_end_gradients(plan: CpPlan, q, k, do, w, g_cumsum, dht, scale, trans
         _cabi.check(lib.qla_cp_plan(pa, stream), "qla_cp_plan")
         _cabi.check(lib.qla_chunk_bwd(sa, stream), "qla_chunk_bwd (state-only)")
         _cabi.check(lib.qla_cp_chain(ca, stream), "qla_cp_chain")
-    return seg_dht
+    return seg_dht, lead

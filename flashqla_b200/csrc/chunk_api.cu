@@ -243,6 +243,7 @@ extern "C" QLA_API int qla_chunk_bwd(const QlaChunkBwdArgs* args, void* stream_)
     sp.cu_seqlens = a.seg_cu; sp.num_seqs = a.num_segments; sp.chunk_offsets = seg_chunk_offsets;
     sp.dht = a.seg_dht; sp.dht_kv = 1;
     mode.out_map = a.seg_dh0_map;
+    mode.lead = a.seg_lead;
   }
   int rc = launch_bwd_scan(sp, mode, total_tokens, is_bf16, stream);
   if (rc != QLA_OK) return rc;

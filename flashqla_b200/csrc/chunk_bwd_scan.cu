@@ -122,6 +122,12 @@ bwd_scan_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     if (lim <= 0) return;  // nothing asked of this (interval, head); uniform for the whole CTA
     nproc = min(nproc, lim);
   }
+  // warm-up inside the scan: `lead` chunks of the interval behind this one (same sequence: its end is the next
+  // boundary) are scanned first from a zero gradient; nothing of them is stored
+  const int lead = (mode.lead != nullptr && !state_only) ? mode.lead[seq * p.num_v_heads + hv] : 0;
+  const int own_chunks = nproc;
+  nproc += lead;
+  const int tok_end = lead > 0 ? p.cu_seqlens[seq + 2] : seq_end;  // where the tokens of the scanned chunks end
   const int64_t chunk_base =
       p.chunk_offsets ? p.chunk_offsets[seq] : static_cast<int64_t>(seq) * ((p.seq_len + kChunk - 1) / kChunk);
 
@@ -177,7 +183,7 @@ bwd_scan_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       if (i < 0) continue;
       const int s = i & 1, use = i >> 1;
       const int t0 = seq_start + chunk_of(i) * kChunk;
-      const int valid = min(kChunk, seq_end - t0);
+      const int valid = min(kChunk, (chunk_of(i) >= own_chunks ? tok_end : seq_end) - t0);
       const int64_t last_tok = static_cast<int64_t>(t0) + valid - 1;
       const float gl = p.g_cumsum[last_tok * p.num_v_heads + hv];
       float gcv[2];
@@ -300,8 +306,10 @@ bwd_scan_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         if (lane == 0) {
           const int chunk = chunk_of(i);
           const int row = static_cast<int>(((chunk_base + chunk) * p.num_v_heads + hv) * kHeadDim);
-          ptx::tma_store_3d(&tm_du, smem + kOffDuT + (i & 1) * 16384, 0, 0, row);
-          if (i + 1 < nproc) {  // dh of the chunk before: the state this chunk's update produced
+          // (chunks of the warm-up belong to the interval behind: nothing of theirs is stored, except that the
+          // last of them produces dh of this interval's last chunk)
+          if (chunk < own_chunks) ptx::tma_store_3d(&tm_du, smem + kOffDuT + (i & 1) * 16384, 0, 0, row);
+          if (i + 1 < nproc && chunk - 1 < own_chunks) {  // dh of the chunk before: the state this chunk's update produced
             const int row2 = row - p.num_v_heads * kHeadDim;
             ptx::tma_store_3d(&tm_dh, smem + kOffDhT, 0, 0, row2);
             ptx::tma_store_3d(&tm_dh, smem + kOffDhT + 16384, 64, 0, row2);
@@ -391,7 +399,7 @@ bwd_scan_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     bool alive = true;
     const int st_k = p.transpose_state ? 1 : kHeadDim, st_v = p.transpose_state ? kHeadDim : 1;
     const int ht_k = (p.transpose_state && !p.dht_kv) ? 1 : kHeadDim, ht_v = (p.transpose_state && !p.dht_kv) ? kHeadDim : 1;
-    const float* dhtp = (p.dht != nullptr && !init_identity)
+    const float* dhtp = (p.dht != nullptr && !init_identity && lead == 0)
                             ? p.dht + (static_cast<int64_t>(seq) * p.num_v_heads + hv) * kHeadDim * kHeadDim
                             : nullptr;
     const int out_row = out_map != nullptr ? out_map[seq] : seq;
@@ -417,7 +425,7 @@ bwd_scan_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         alive = wait(kFull0, 0);
         egl0 = gates_of(0)->egl;
       }
-      T* hp = (nproc > 0 && !state_only) ? dh_row(nproc - 1) : nullptr;
+      T* hp = (nproc > 0 && !state_only && lead == 0) ? dh_row(nproc - 1) : nullptr;
 #pragma unroll
       for (int kb = 0; kb < 64; kb += 16) {
         const float* x = xs + kb;

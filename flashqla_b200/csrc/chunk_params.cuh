@@ -96,6 +96,8 @@ struct BwdParams {
 struct BwdScanMode {
   const int32_t* chunk_limit;   // [num_seqs, Hv] or NULL: only the FIRST chunk_limit chunks of an interval (<= 0: none)
   const int32_t* out_map;       // [num_seqs] row of dh0 an interval writes (< 0: none) or NULL (identity)
+  const int32_t* lead;          // [num_seqs, Hv] or NULL: chunks BEHIND an interval (same sequence) that are scanned first
+                                // from a zero gradient, nothing of them stored: the warm-up of a segment inside its own scan
   int chunks_upper;             // rows of the dh / du workspace in chunks (extent of the store maps); unused when state_only
   int state_only;               // no du / dh: only the state gradient leaving the interval on the left
   int dual;                     // second half of the grid: transition pass (identity start, dO treated as zero) with

@@ -59,8 +59,8 @@ __global__ void __launch_bounds__(256) cp_plan_kernel(const QlaCpPlanArgs a) {
   }
 }
 
-// The forward plan with the warm-up folded into the main scan: one CTA per (original sequence, head), a thread
-// per segment.  A (sequence, head) in which every segment decays below the threshold needs no state-only pass:
+// The plan with the warm-up folded into the main scan (forward, or reverse for the backward scan): one CTA per
+// (original sequence, head), a thread per segment.  A (sequence, head) in which every segment decays below the threshold needs no state-only pass:
 // the main scan's CTA of segment s simply starts lead[s] = warm(s - 1) chunks early, from a zero state.  If some
 // segment never decays that far the limits are those of cp_plan_kernel (state-only pass, transition matrices,
 // chain) and lead is 0.  Only the row of cp_h0 that starts the sequence is written here.
@@ -79,7 +79,8 @@ __global__ void __launch_bounds__(256) cp_plan_lead_kernel(const QlaCpPlanArgs a
       float acc = 0.f;
       bool reached = false;
       for (int i = 0; i < nchunks; ++i) {
-        const int last = min(end, start + (nchunks - i) * kChunk) - 1;
+        const int c = a.reverse ? i : nchunks - 1 - i;  // backward: the decay accumulates from the segment's start
+        const int last = min(end, start + (c + 1) * kChunk) - 1;
         acc += a.g_cumsum[static_cast<int64_t>(last) * num_heads + h];
         ++warm;
         if (acc < a.threshold) { reached = true; break; }
@@ -91,14 +92,18 @@ __global__ void __launch_bounds__(256) cp_plan_lead_kernel(const QlaCpPlanArgs a
     any |= ml;
   }
   any = __syncthreads_or(any);  // (also orders the limits written above before the reads below)
-  for (int seg = s0 + threadIdx.x; seg < s1; seg += 256)
-    a.lead[seg * num_heads + h] = (!any && seg > s0) ? a.warm_limit[(seg - 1) * num_heads + h] : 0;
+  // the neighbour whose warm-up this segment's scan runs itself: the segment before it (forward), behind it (backward)
+  for (int seg = s0 + threadIdx.x; seg < s1; seg += 256) {
+    const int nb = a.reverse ? seg + 1 : seg - 1;
+    a.lead[seg * num_heads + h] = (!any && nb >= s0 && nb < s1) ? a.warm_limit[nb * num_heads + h] : 0;
+  }
   __syncthreads();
   if (!any)
     for (int seg = s0 + threadIdx.x; seg < s1; seg += 256) a.warm_limit[seg * num_heads + h] = 0;
-  // start state of the sequence: the caller's (any dtype / layout, through h0_map) or zero
+  // start state of the sequence (backward: the gradient of its final state, into the last segment's row): the
+  // caller's (any dtype / layout, through h0_map) or zero
   constexpr int kElems = kHeadDim * kHeadDim;
-  float* dst = a.cp_h0 + (static_cast<int64_t>(s0) * num_heads + h) * kElems;
+  float* dst = a.cp_h0 + (static_cast<int64_t>(a.reverse ? s1 - 1 : s0) * num_heads + h) * kElems;
   int row = -1;
   if (a.h0 != nullptr) row = a.h0_map != nullptr ? a.h0_map[r] : r;
   if (row < 0) {
@@ -175,8 +180,8 @@ extern "C" QLA_API int qla_cp_plan(const QlaCpPlanArgs* a, void* stream) {
   QLA_CHECK_SUPPORTED(a->h0 == nullptr || a->h0_dtype == QLA_DT_F32 || a->h0_dtype == QLA_DT_BF16,
                       "initial states must be fp32 or bf16");
   if (a->lead != nullptr) {
-    QLA_CHECK_ARG(a->cp_h0 != nullptr && a->raw_first_seg != nullptr && a->num_raw_seqs > 0 && !a->reverse,
-                  "lead needs cp_h0, raw_first_seg, num_raw_seqs (forward plan only)");
+    QLA_CHECK_ARG(a->cp_h0 != nullptr && a->raw_first_seg != nullptr && a->num_raw_seqs > 0,
+                  "lead needs cp_h0, raw_first_seg and num_raw_seqs");
     dim3 grid_lead(a->num_raw_seqs, a->num_v_heads);
     QLA_CHECK_CUDA(launch_dependent(cp_plan_lead_kernel, grid_lead, dim3(256), 0, static_cast<cudaStream_t>(stream), *a));
     return QLA_OK;

@@ -312,6 +312,9 @@ typedef struct QlaChunkBwdArgs {
   const int32_t* chunk_limit_b;
   const int32_t* out_map_b;
   float* out_b;
+  const int32_t* seg_lead;   /* with num_segments: [num_segments, Hv] chunks BEHIND a segment that its reverse scan runs
+                                first from a zero gradient, nothing of them stored (qla_cp_plan with reverse and lead
+                                writes it); a segment with seg_lead > 0 ignores its row of seg_dht; NULL: none        */
 } QlaChunkBwdArgs;
 
 QLA_API size_t qla_chunk_bwd_workspace_bytes(const QlaChunkBwdArgs* args);
@@ -352,7 +355,7 @@ typedef struct QlaCpPlanArgs {
                                  accumulated decay from its start) instead of trailing ones; seg_next
                                  then names the segment's predecessor (< 0: none)                 */
   int32_t num_raw_seqs;       /* with lead: number of original sequences                        */
-  /* optional (forward plan, with cp_h0): warm-up inside the main scan.  lead[s,h] = trailing chunks of the
+  /* optional (with cp_h0; with reverse the roles of predecessor and successor swap): warm-up inside the main scan.  lead[s,h] = trailing chunks of the
    * segment before s that the main scan's CTA of s runs first, from a zero state and without storing their
    * output (QlaChunkFwdArgs.lead): the state-only pass then has nothing to do for that sequence and head
    * (warm_limit = 0).  A sequence and head in which some segment never decays below the threshold keeps the
