@@ -1,7 +1,7 @@
 // Thin inline-PTX wrappers for the Blackwell (sm_100a) primitives the kernels use:
 // mbarriers with BOUNDED waits, TMA tiled copies (cp.async.bulk.tensor), tensor memory
 // (tcgen05.alloc / ld / st) and the 5th-generation tensor-core MMA (tcgen05.mma) with its shared
-// memory / instruction descriptors.  No cluster multicast is used anywhere.
+// memory / instruction descriptors.  Every copy has one destination CTA (no clusters are launched).
 #pragma once
 
 #include <cuda.h>
